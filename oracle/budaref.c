@@ -1,0 +1,498 @@
+/*
+ * budaref.c -- CPU ORACLE for the TT-Buda data-format path.  TEST INFRASTRUCTURE ONLY.
+ *
+ * This file is a plain-C restatement of the algorithms on the data-format path of
+ * tenstorrent/tt-buda.  It exists so the CUDA kernels can be checked bit-for-bit; it is never
+ * linked into, loaded by, or called from the shipped library.  Only tests, the smoke check and
+ * the benchmark's CPU-baseline leg may use it.
+ *
+ * PARITY STATUS
+ *   - Tile-level queue ordering: PINNED by the reference's own model, TileLayout::map
+ *     (pybuda/csrc/balancer/types.cpp:629-666) and its exhaustive round-trip test
+ *     (pybuda/csrc/balancer/tests/test_tile_layout.cpp:250-281), restated in ref_tile_map /
+ *     ref_tile_unmap below.
+ *   - Quantize / Dequantize / Requantize: PINNED by golden vectors generated from the
+ *     reference's own eval (pybuda/pybuda/op/eval/pybuda/quantize.py:55-122,
+ *     pybuda/pybuda/op/eval/buda/quantize.py:23-53).
+ *   - Byte sizes: PINNED by pybuda/csrc/lower_to_buda/common.cpp:167-190 and
+ *     pybuda/csrc/balancer/balancer_utils.hpp:24-51.
+ *   - Face order inside a tile and the Bfp byte encoding: PARITY UNPINNED.  The converter that
+ *     produces those bytes lives in tenstorrent/tt-budabackend (git submodule
+ *     third_party/budabackend, branch main, no pinned commit, directory empty in the reference
+ *     checkout).  The restatement follows the published description
+ *     (docs/public/dataformats.rst:59-89 and docs/public/images/bfp{8,4,2}_blocks.png) and freezes
+ *     every choice the description leaves open; each such choice is marked "POLICY" below.
+ *
+ * The Bfp encoder here works in integers (shift / mask / explicit round-to-nearest-even) on
+ * purpose: the CUDA kernels use a floating-point formulation of the same arithmetic, so agreement
+ * between the two is a real check and not the same code compiled twice.
+ *
+ * Build: see oracle/Makefile  (gcc -O3 -mavx2 -ffp-contract=off -fopenmp).
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* DataFormat values: pybuda/csrc/lower_to_buda/common.hpp:92-111 */
+enum {
+    DF_Float32 = 0, DF_Float16 = 1, DF_Bfp8 = 2, DF_Bfp4 = 3, DF_Bfp2 = 11, DF_Float16_b = 5,
+    DF_Bfp8_b = 6, DF_Bfp4_b = 7, DF_Bfp2_b = 15, DF_Lf8 = 10, DF_UInt16 = 12, DF_Int8 = 14,
+    DF_Int32 = 8, DF_RawUInt8 = 0xf0, DF_RawUInt16 = 0xf1, DF_RawUInt32 = 0xf2, DF_Invalid = 0xff
+};
+
+/* Queue geometry as emitted per queue by the reference compiler
+ * (pybuda/csrc/lower_to_buda/netlist.cpp:141-232) and carried by DramIODesc
+ * (pybuda/csrc/backend_api/backend_api.cpp:409-426). */
+typedef struct {
+    uint32_t grid_r, grid_c;       /* bufq_grid_dim_r/c: one buffer per grid core        */
+    uint32_t mblock_m, mblock_n;   /* macro-block, in micro-blocks                       */
+    uint32_t ublock_rt, ublock_ct; /* micro-block, in tiles                              */
+    uint32_t t;                    /* z dimension of one entry                           */
+    uint32_t ublock_order;         /* 0 = row-major ublock scan (R), 1 = column-major (C)*/
+} ref_geom;
+
+int ref_threads(void)
+{
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * Sizes
+ * ------------------------------------------------------------------------------------------- */
+
+/* bytes of one 32x32 tile; follows balancer_utils.hpp:24-51 (header_padding = 32 when asked) */
+long ref_tile_bytes(int df, int with_header)
+{
+    long h = with_header ? 32 : 0;
+    switch (df) {
+        case DF_Float32: case DF_Int32: case DF_RawUInt32: return 4096 + h;
+        case DF_Float16: case DF_Float16_b: case DF_UInt16: case DF_RawUInt16: return 2048 + h;
+        case DF_Bfp8: case DF_Bfp8_b: return 1024 + 64 + h;
+        case DF_Bfp4: case DF_Bfp4_b: return 512 + 64 + h;
+        case DF_Bfp2: case DF_Bfp2_b: return 256 + 64 + h;
+        case DF_Lf8: case DF_Int8: case DF_RawUInt8: return 1024 + h;
+        default: return -1;
+    }
+}
+
+/* follows data_format_byte_size, common.cpp:167-190 */
+long ref_data_format_byte_size(int df, long elements)
+{
+    switch (df) {
+        case DF_Float32: case DF_Int32: case DF_RawUInt32: return 4 * elements;
+        case DF_UInt16: case DF_Float16_b: case DF_Float16: case DF_RawUInt16: return 2 * elements;
+        case DF_Bfp8_b: case DF_Bfp8: return elements + elements / 16;
+        case DF_Bfp4_b: case DF_Bfp4: return elements / 2 + elements / 16;
+        case DF_Bfp2_b: case DF_Bfp2: return elements / 4 + elements / 16;
+        case DF_Lf8: case DF_Int8: case DF_RawUInt8: return elements;
+        case DF_Invalid: return 0;
+        default: return -1;
+    }
+}
+
+static int bfp_mant_bits(int df)
+{
+    switch (df) {
+        case DF_Bfp8_b: case DF_Bfp8: return 7;
+        case DF_Bfp4_b: case DF_Bfp4: return 3;
+        case DF_Bfp2_b: case DF_Bfp2: return 1;
+        default: return 0;
+    }
+}
+
+static int elem_bytes(int df)
+{
+    switch (df) {
+        case DF_Float32: case DF_Int32: case DF_RawUInt32: return 4;
+        case DF_Float16: case DF_Float16_b: case DF_UInt16: case DF_RawUInt16: return 2;
+        case DF_Lf8: case DF_Int8: case DF_RawUInt8: return 1;
+        default: return 0;
+    }
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * Tile-level ordering: TileLayout::map, types.cpp:629-648 (forward) and 650-666 (inverse).
+ * Canonical coordinate = (t, r, c) in tiles over the whole tensor; linear coordinate = (grid
+ * core, tile address inside that core's buffer).
+ * ------------------------------------------------------------------------------------------- */
+void ref_tile_map(const ref_geom *g, uint32_t t, uint32_t r, uint32_t c, uint32_t *core_r,
+                  uint32_t *core_c, uint64_t *addr)
+{
+    uint32_t block_rt = g->mblock_m * g->ublock_rt;
+    uint32_t block_ct = g->mblock_n * g->ublock_ct;
+    uint32_t u_r = r % g->ublock_rt, u_c = c % g->ublock_ct;
+    uint32_t m = (r / g->ublock_rt) % g->mblock_m;
+    uint32_t n = (c / g->ublock_ct) % g->mblock_n;
+    uint64_t ublock_vol = (uint64_t)g->ublock_rt * g->ublock_ct;
+    uint64_t mblock_vol = (uint64_t)g->mblock_m * g->mblock_n * ublock_vol;
+    uint64_t mblock_lin = (g->ublock_order == 0) ? ((uint64_t)m * g->mblock_n + n) * ublock_vol
+                                                 : ((uint64_t)n * g->mblock_m + m) * ublock_vol;
+    *core_r = r / block_rt;
+    *core_c = c / block_ct;
+    *addr = (uint64_t)t * mblock_vol + mblock_lin + (uint64_t)u_r * g->ublock_ct + u_c;
+}
+
+void ref_tile_unmap(const ref_geom *g, uint32_t core_r, uint32_t core_c, uint64_t addr, uint32_t *t,
+                    uint32_t *r, uint32_t *c)
+{
+    uint64_t ublock_vol = (uint64_t)g->ublock_rt * g->ublock_ct;
+    uint64_t mblock_vol = (uint64_t)g->mblock_m * g->mblock_n * ublock_vol;
+    uint64_t mblock_off = addr % mblock_vol;
+    uint64_t ublock_off = mblock_off % ublock_vol;
+    uint64_t num_ublocks = mblock_off / ublock_vol;
+    uint32_t m = (g->ublock_order == 0) ? (uint32_t)(num_ublocks / g->mblock_n)
+                                        : (uint32_t)(num_ublocks % g->mblock_m);
+    uint32_t n = (g->ublock_order == 0) ? (uint32_t)(num_ublocks % g->mblock_n)
+                                        : (uint32_t)(num_ublocks / g->mblock_m);
+    *t = (uint32_t)(addr / mblock_vol);
+    *r = core_r * g->mblock_m * g->ublock_rt + m * g->ublock_rt + (uint32_t)(ublock_off / g->ublock_ct);
+    *c = core_c * g->mblock_n * g->ublock_ct + n * g->ublock_ct + (uint32_t)(ublock_off % g->ublock_ct);
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * Bfp block encode / decode  (dataformats.rst:74-83: steps 3-8)
+ *
+ * A block is 16 values that share one 8-bit exponent ("_b" formats: the fp32/bf16 exponent
+ * itself).  Each datum is sign + m magnitude bits, m = 7 / 3 / 1, with NO implied one.
+ * ------------------------------------------------------------------------------------------- */
+
+/* Encode one value against the block exponent.  bits: IEEE-754 binary32 pattern. */
+static inline uint32_t bfp_encode_datum(uint32_t bits, uint32_t block_exp, int m)
+{
+    uint32_t sign = bits >> 31;
+    uint32_t e = (bits >> 23) & 0xffu;
+    uint32_t qmax = (1u << m) - 1u;
+    uint32_t q;
+    if (e == 0) {
+        q = 0; /* POLICY: zero and denormal inputs encode as zero (flush) */
+    } else if (e == 255) {
+        q = qmax; /* POLICY: Inf and NaN encode the largest magnitude, keeping their sign */
+    } else {
+        /* step 4: make the implied one explicit -> 24-bit significand */
+        uint32_t sig = (bits & 0x7fffffu) | 0x800000u;
+        /* steps 5-7: shift right by the exponent delta, then keep m bits of the 24 */
+        uint32_t shift = (block_exp - e) + (uint32_t)(24 - m);
+        if (shift > 25) {
+            q = 0; /* less than half of the last kept bit: rounds to zero */
+        } else {
+            /* POLICY: round to nearest, ties to even, on the dropped bits ("optionally round") */
+            uint32_t kept = sig >> shift;
+            uint32_t rem = sig & ((1u << shift) - 1u);
+            uint32_t half = 1u << (shift - 1);
+            if (rem > half || (rem == half && (kept & 1u))) kept++;
+            /* POLICY: a round-up past the largest magnitude saturates; the block exponent is
+             * not bumped */
+            q = kept > qmax ? qmax : kept;
+        }
+    }
+    if (q == 0) sign = 0; /* POLICY: a zero magnitude is stored as +0 */
+    return (sign << m) | q;
+}
+
+/* Encode one 16-value block.  out receives 16/8/4 bytes for m = 7/3/1.
+ * POLICY (sub-byte order): datum i of the block occupies the lower-numbered bits first, i.e.
+ * Bfp4 datum i -> bits [4(i&1)+3 : 4(i&1)] of byte i/2, Bfp2 datum i -> bits [2(i&3)+1 : 2(i&3)]
+ * of byte i/4 (little-endian inside the 32-bit rows drawn in bfp4_blocks.png / bfp2_blocks.png). */
+void ref_bfp_pack_block(const uint32_t bits[16], int m, uint8_t *exp_out, uint8_t *out)
+{
+    uint32_t block_exp = 0;
+    for (int i = 0; i < 16; i++) {
+        uint32_t e = (bits[i] >> 23) & 0xffu; /* step 3: maximum exponent of the block */
+        if (e > block_exp) block_exp = e;
+    }
+    *exp_out = (uint8_t)block_exp;
+    int w = m + 1;             /* datum width in bits: 8, 4, 2 */
+    int per_byte = 8 / w;      /* 1, 2, 4 */
+    memset(out, 0, 16 / per_byte);
+    for (int i = 0; i < 16; i++) {
+        uint32_t d = bfp_encode_datum(bits[i], block_exp, m);
+        out[i / per_byte] |= (uint8_t)(d << (w * (i % per_byte)));
+    }
+}
+
+/* Decode: value = (-1)^s * q * 2^(E - 127 - (m-1)), rounded to binary32 (exact unless it
+ * overflows, which yields infinity).  q == 0 decodes to +0.0. */
+static inline float bfp_decode_datum(uint32_t d, uint32_t block_exp, int m)
+{
+    uint32_t q = d & ((1u << m) - 1u);
+    uint32_t sign = (d >> m) & 1u;
+    if (q == 0) return 0.0f;
+    double v = ldexp((double)q, (int)block_exp - 127 - (m - 1));
+    float f = (float)v;
+    return sign ? -f : f;
+}
+
+void ref_bfp_unpack_block(uint8_t exp_in, const uint8_t *in, int m, float out[16])
+{
+    int w = m + 1, per_byte = 8 / w;
+    for (int i = 0; i < 16; i++) {
+        uint32_t d = (in[i / per_byte] >> (w * (i % per_byte))) & ((1u << w) - 1u);
+        out[i] = bfp_decode_datum(d, exp_in, m);
+    }
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * Element access helpers
+ * ------------------------------------------------------------------------------------------- */
+static inline uint32_t load_as_f32_bits(const uint8_t *p, int df)
+{
+    if (df == DF_Float32) { uint32_t v; memcpy(&v, p, 4); return v; }
+    /* bfloat16 widens exactly: it is the upper half of a binary32 */
+    uint16_t h; memcpy(&h, p, 2); return (uint32_t)h << 16;
+}
+
+static inline void store_from_f32(uint8_t *p, int df, float f)
+{
+    if (df == DF_Float32) { memcpy(p, &f, 4); return; }
+    /* every decoded Bfp value has at most 7 significant bits, so the upper half of the
+     * binary32 is the exact bfloat16 */
+    uint32_t b; memcpy(&b, &f, 4);
+    uint16_t h = (uint16_t)(b >> 16);
+    memcpy(p, &h, 2);
+}
+
+/* Tile record layout (POLICY where marked):
+ *   [optional 32-byte header, zero filled (POLICY: contents unknown, balancer_utils.hpp:27)]
+ *   Bfp:   [64 exponent bytes: exponent k belongs to block k][mantissas of block 0..63]
+ *          block k = face k/16, face row k%16 (POLICY: faces in order F0 F1 F2 F3 =
+ *          (rows 0-15, cols 0-15), (rows 0-15, cols 16-31), (rows 16-31, cols 0-15),
+ *          (rows 16-31, cols 16-31); rows top-down)
+ *   plain: the four faces in the same order, each 16x16 row-major, native element bytes. */
+
+typedef struct {
+    const ref_geom *g;
+    uint32_t W, Z, R, C;       /* tensor dims; Z must equal g->t                */
+    uint64_t tiles_per_entry;  /* per core buffer: t * mblock volume            */
+    uint64_t tile_bytes;
+    uint64_t buf_bytes;        /* one core's buffer: W entries                  */
+} layout_ctx;
+
+static int make_ctx(layout_ctx *c, const ref_geom *g, const uint32_t shape[4], int df, int with_header)
+{
+    long tb = ref_tile_bytes(df, with_header);
+    if (tb < 0) return 1;
+    c->g = g; c->W = shape[0]; c->Z = shape[1]; c->R = shape[2]; c->C = shape[3];
+    if (c->R % 32 || c->C % 32) return 1;
+    if (g->t != c->Z) return 1;
+    if ((uint64_t)g->grid_r * g->mblock_m * g->ublock_rt * 32 != c->R) return 1;
+    if ((uint64_t)g->grid_c * g->mblock_n * g->ublock_ct * 32 != c->C) return 1;
+    c->tiles_per_entry = (uint64_t)g->t * g->mblock_m * g->mblock_n * g->ublock_rt * g->ublock_ct;
+    c->tile_bytes = (uint64_t)tb;
+    c->buf_bytes = (uint64_t)c->W * c->tiles_per_entry * c->tile_bytes;
+    return 0;
+}
+
+static inline uint64_t tile_offset(const layout_ctx *c, uint32_t w, uint32_t z, uint32_t rt, uint32_t ct)
+{
+    uint32_t cr, cc; uint64_t addr;
+    ref_tile_map(c->g, z, rt, ct, &cr, &cc, &addr);
+    uint64_t core = (uint64_t)cr * c->g->grid_c + cc;
+    return core * c->buf_bytes + ((uint64_t)w * c->tiles_per_entry + addr) * c->tile_bytes;
+}
+
+/* total bytes of the tilized image of a tensor of this shape in this queue */
+long long ref_tilized_bytes(const ref_geom *g, const uint32_t shape[4], int df, int with_header)
+{
+    layout_ctx c;
+    if (make_ctx(&c, g, shape, df, with_header)) return -1;
+    return (long long)(c.buf_bytes * g->grid_r * g->grid_c);
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * tilize (+ Bfp pack): row-major [W,Z,R,C] with BYTE strides -> queue image.
+ * Restates what tt::backend::tilize_tensor / push_input do for this path
+ * (bound at backend_api.cpp:688-704).  Returns 0 on success.
+ * ------------------------------------------------------------------------------------------- */
+int ref_tilize_pack(const void *src_, int src_df, const uint32_t shape[4], const uint32_t strides[4],
+                    const ref_geom *g, int dst_df, int with_header, void *dst_)
+{
+    const uint8_t *src = (const uint8_t *)src_;
+    uint8_t *dst = (uint8_t *)dst_;
+    layout_ctx c;
+    if (make_ctx(&c, g, shape, dst_df, with_header)) return 1;
+    int m = bfp_mant_bits(dst_df);
+    int es = elem_bytes(src_df);
+    if (m) {
+        if (!(dst_df == DF_Bfp8_b || dst_df == DF_Bfp4_b || dst_df == DF_Bfp2_b)) return 1;
+        if (!(src_df == DF_Float32 || src_df == DF_Float16_b)) return 1;
+    } else {
+        if (es == 0 || es != elem_bytes(dst_df)) return 1; /* layout-only: same element width */
+    }
+    uint32_t Rt = c.R / 32, Ct = c.C / 32;
+    long hdr = with_header ? 32 : 0;
+    long long ntiles = (long long)c.W * c.Z * Rt * Ct;
+#pragma omp parallel for schedule(static)
+    for (long long ti = 0; ti < ntiles; ti++) {
+        uint32_t ct = (uint32_t)(ti % Ct);
+        uint32_t rt = (uint32_t)((ti / Ct) % Rt);
+        uint32_t z = (uint32_t)((ti / ((long long)Ct * Rt)) % c.Z);
+        uint32_t w = (uint32_t)(ti / ((long long)Ct * Rt * c.Z));
+        uint8_t *rec = dst + tile_offset(&c, w, z, rt, ct);
+        if (hdr) memset(rec, 0, 32);
+        rec += hdr;
+        const uint8_t *base = src + (uint64_t)w * strides[0] + (uint64_t)z * strides[1];
+        for (int face = 0; face < 4; face++) {
+            for (int fr = 0; fr < 16; fr++) {
+                uint64_t r = (uint64_t)rt * 32 + (face >> 1) * 16 + fr;
+                uint64_t col0 = (uint64_t)ct * 32 + (face & 1) * 16;
+                const uint8_t *p = base + r * strides[2] + col0 * strides[3];
+                int blk = face * 16 + fr;
+                if (m) {
+                    uint32_t bits[16];
+                    for (int i = 0; i < 16; i++) bits[i] = load_as_f32_bits(p + (uint64_t)i * strides[3], src_df);
+                    int bpb = 16 * (m + 1) / 8;
+                    ref_bfp_pack_block(bits, m, rec + blk, rec + 64 + (long)blk * bpb);
+                } else {
+                    for (int i = 0; i < 16; i++)
+                        memcpy(rec + ((long)blk * 16 + i) * es, p + (uint64_t)i * strides[3], es);
+                }
+            }
+        }
+    }
+    return 0;
+}
+
+/* inverse: queue image -> row-major [W,Z,R,C] with byte strides (get_output, backend_api.cpp:701).
+ * Bfp sources decode to Float32 or Float16_b; plain sources keep their element bytes. */
+int ref_unpack_untilize(const void *src_, int src_df, int with_header, const ref_geom *g, void *dst_,
+                        int dst_df, const uint32_t shape[4], const uint32_t strides[4])
+{
+    const uint8_t *src = (const uint8_t *)src_;
+    uint8_t *dst = (uint8_t *)dst_;
+    layout_ctx c;
+    if (make_ctx(&c, g, shape, src_df, with_header)) return 1;
+    int m = bfp_mant_bits(src_df);
+    int es = elem_bytes(dst_df);
+    if (m) {
+        if (!(src_df == DF_Bfp8_b || src_df == DF_Bfp4_b || src_df == DF_Bfp2_b)) return 1;
+        if (!(dst_df == DF_Float32 || dst_df == DF_Float16_b)) return 1;
+    } else {
+        if (es == 0 || es != elem_bytes(src_df)) return 1;
+    }
+    uint32_t Rt = c.R / 32, Ct = c.C / 32;
+    long hdr = with_header ? 32 : 0;
+    long long ntiles = (long long)c.W * c.Z * Rt * Ct;
+#pragma omp parallel for schedule(static)
+    for (long long ti = 0; ti < ntiles; ti++) {
+        uint32_t ct = (uint32_t)(ti % Ct);
+        uint32_t rt = (uint32_t)((ti / Ct) % Rt);
+        uint32_t z = (uint32_t)((ti / ((long long)Ct * Rt)) % c.Z);
+        uint32_t w = (uint32_t)(ti / ((long long)Ct * Rt * c.Z));
+        const uint8_t *rec = src + tile_offset(&c, w, z, rt, ct) + hdr;
+        uint8_t *base = dst + (uint64_t)w * strides[0] + (uint64_t)z * strides[1];
+        for (int face = 0; face < 4; face++) {
+            for (int fr = 0; fr < 16; fr++) {
+                uint64_t r = (uint64_t)rt * 32 + (face >> 1) * 16 + fr;
+                uint64_t col0 = (uint64_t)ct * 32 + (face & 1) * 16;
+                uint8_t *p = base + r * strides[2] + col0 * strides[3];
+                int blk = face * 16 + fr;
+                if (m) {
+                    float vals[16];
+                    int bpb = 16 * (m + 1) / 8;
+                    ref_bfp_unpack_block(rec[blk], rec + 64 + (long)blk * bpb, m, vals);
+                    for (int i = 0; i < 16; i++) store_from_f32(p + (uint64_t)i * strides[3], dst_df, vals[i]);
+                } else {
+                    for (int i = 0; i < 16; i++)
+                        memcpy(p + (uint64_t)i * strides[3], rec + ((long)blk * 16 + i) * es, es);
+                }
+            }
+        }
+    }
+    return 0;
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * Golden int8 quantisation ops.  Each follows the torch expression of the reference eval, one
+ * IEEE binary32 operation per torch operator (this file is compiled with -ffp-contract=off so
+ * no multiply-add is fused).  torch.round is round-half-to-even = rintf in the default mode.
+ * The scale of element i is scale[(i / inner) % scale_len]: inner = product of the dims after
+ * `axis`; scale_len == 1 gives a per-tensor scale (reshape_to_match_input, quantize.py:38-52).
+ * The final cast follows torch's float -> integer conversion of an already clamped value
+ * (NaN survives clamp and converts to 0).
+ * ------------------------------------------------------------------------------------------- */
+static inline float clampf(float v, float lo, float hi)
+{
+    if (v != v) return v;
+    return v < lo ? lo : (v > hi ? hi : v);
+}
+
+static inline int8_t to_i8(float v) { return (v != v) ? 0 : (int8_t)(int32_t)v; }
+
+/* mode 0: Quantize, quantize.py:56-66      clamp(round(x / scale) + zp, lo, hi)
+ * mode 1: BudaQuantize, quantize.py:68-77 and buda/quantize.py:24-33   round(x * scale) + zp */
+void ref_quantize(const float *x, long long n, const float *scale, long long scale_len, long long inner,
+                  float zp, int mode, float lo, float hi, int8_t *out)
+{
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < n; i++) {
+        float s = scale[(i / inner) % scale_len];
+        float q = (mode == 0) ? (x[i] / s) : (x[i] * s);
+        float r = rintf(q) + zp;
+        out[i] = to_i8(clampf(r, lo, hi));
+    }
+}
+
+/* Dequantize, quantize.py:79-93 and buda/quantize.py:35-40      (float(x) - zp) * scale */
+void ref_dequantize(const int8_t *x, long long n, const float *scale, long long scale_len, long long inner,
+                    float zp, float *out)
+{
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < n; i++) {
+        float s = scale[(i / inner) % scale_len];
+        out[i] = ((float)x[i] - zp) * s;
+    }
+}
+
+/* mode 0: Requantize, quantize.py:95-110   s = inp_scale / out_scale; round(s * float(x) + zp)
+ *         (scale_b = out_scale; the int32 input is promoted to binary32 by the multiply)
+ * mode 1: BudaRequantize, quantize.py:112-122 and buda/quantize.py:42-53  round(float(x) * scale + zp)
+ *         (scale_b unused) */
+void ref_requantize(const int32_t *x, long long n, const float *scale_a, const float *scale_b,
+                    long long scale_len, long long inner, float zp, int mode, float lo, float hi, int8_t *out)
+{
+#pragma omp parallel for schedule(static)
+    for (long long i = 0; i < n; i++) {
+        long long k = (i / inner) % scale_len;
+        float s = (mode == 0) ? (scale_a[k] / scale_b[k]) : scale_a[k];
+        float p = s * (float)x[i];
+        float r = rintf(p + zp);
+        out[i] = to_i8(clampf(r, lo, hi));
+    }
+}
+
+/* ---------------------------------------------------------------------------------------------
+ * Matmul with Bfp8_b weights, golden semantics (op/eval/pybuda/matmul.py:20-33 evaluates
+ * torch.matmul on the operand values): C = A @ decode(W), binary32 accumulation in k order.
+ * A: bfloat16 row-major [M,K]; W: Bfp8_b queue image of a [K,N] tensor in geometry g;
+ * C: binary32 row-major [M,N].  Small sizes only; the tests use it for spot checks.
+ * ------------------------------------------------------------------------------------------- */
+int ref_bfp8b_matmul(const uint16_t *A, long M, long K, const void *W, const ref_geom *g, long N, float *C)
+{
+    uint32_t shape[4] = {1, 1, (uint32_t)K, (uint32_t)N};
+    uint32_t strides[4] = {(uint32_t)(K * N * 4), (uint32_t)(K * N * 4), (uint32_t)(N * 4), 4};
+    float *Wf = (float *)__builtin_malloc((size_t)K * N * 4);
+    if (!Wf) return 1;
+    if (ref_unpack_untilize(W, DF_Bfp8_b, 0, g, Wf, DF_Float32, shape, strides)) { __builtin_free(Wf); return 1; }
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < M; i++) {
+        float *c = C + i * N;
+        for (long j = 0; j < N; j++) c[j] = 0.0f;
+        for (long k = 0; k < K; k++) {
+            uint32_t ab = (uint32_t)A[i * K + k] << 16;
+            float a; memcpy(&a, &ab, 4);
+            const float *wr = Wf + k * N;
+            for (long j = 0; j < N; j++) c[j] += a * wr[j];
+        }
+    }
+    __builtin_free(Wf);
+    return 0;
+}
