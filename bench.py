@@ -1,0 +1,337 @@
+"""Benchmark of the data-format hot path: fused tilize + Bfp8_b pack.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (per GPU): a batch of 64 fp32 activation tensors [1,1,4096,4096], values N(0,1) with 1 %
+of the elements scaled x1e3 and 0.5 % exact zeros, packed to Bfp8_b tiles (17,825,792 bytes per
+tensor).  One step = one pass over the batch.  With N GPUs every rank packs its own batch of 64
+(weak scaling, no collective on the data path).
+
+  value : whole-job GB/s of algorithmic bytes (5.0625 B per element: 4 read + 1.0625 written),
+          inputs resident in HBM, one batched launch per step, timed with CUDA events.
+  e2e   : the same metric through the host-buffer entry point (pinned host tensors in, host
+          images out; copies inside the timed region).
+  roofline / cpu_baseline : see DESIGN.md.
+
+--impl reference times the CPU implementation of the same path (the oracle port, OpenMP over all
+host cores) on the same workload and prints the same line with "impl": "reference".
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tt-buda_b200"))
+
+N_TENSORS = 64
+SHAPE = (1, 1, 4096, 4096)
+ELEMS = 4096 * 4096
+BYTES_PER_ELEM = 4 + 1.0625
+IMAGE_BYTES = 17825792
+WORKLOAD = "64 x fp32 [1,1,4096,4096] N(0,1), 1% x1e3 outliers, 0.5% zeros -> Bfp8_b tiles"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q,
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                f = [s.strip() for s in out.strip().split(",")]
+                if len(f) >= 6:
+                    self.samples.append(float(f[0]))
+                    self.max_mhz = float(f[1])
+                    for n, v in zip(names, f[2:6]):
+                        if v.lower().startswith("active"):
+                            self.reasons.add(n)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def make_batch(torch, device, seed0):
+    """Synthetic batch with the value distribution of the config (generated on the device)."""
+    xs = []
+    g = torch.Generator(device=device)
+    for i in range(N_TENSORS):
+        g.manual_seed(seed0 + i)
+        x = torch.randn(SHAPE, generator=g, device=device)
+        x = torch.where(torch.rand(SHAPE, generator=g, device=device) < 0.01, x * 1e3, x)
+        x = torch.where(torch.rand(SHAPE, generator=g, device=device) < 0.005, torch.zeros((), device=device), x)
+        xs.append(x)
+    return xs
+
+
+def run_reference(args, rank, world):
+    """The reference path on the host cores: tilize + Bfp8_b pack by the CPU port, all threads."""
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import budaref as R
+
+    R.build()
+    n_sample = 4  # tensors per step: a bounded sample of the 64-tensor batch
+    rng = np.random.default_rng(1000)
+    xs = []
+    for _ in range(n_sample):
+        x = rng.standard_normal(SHAPE, dtype=np.float32)
+        x[rng.random(SHAPE) < 0.01] *= 1e3
+        x[rng.random(SHAPE) < 0.005] = 0.0
+        xs.append(x)
+    for _ in range(max(1, args.warmup)):
+        R.tilize_pack(xs[0], R.Bfp8_b)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for x in xs:
+            R.tilize_pack(x, R.Bfp8_b)
+    dt = time.perf_counter() - t0
+    gbs = args.steps * n_sample * ELEMS * BYTES_PER_ELEM / dt / 1e9
+    line = {
+        "impl": "reference", "metric": "bfp8b_tilize_pack_throughput", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": f"{n_sample} of the 64 tensors per step"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": R.threads(), "kind": "port",
+                         "sample": f"{n_sample} tensors x {args.steps} steps"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary kernels' figures")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback")
+    from pybuda import _cabi, cuda_ops
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if dist is None:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    hbm_peak, peak_kind = peaks()
+    xs = make_batch(torch, dev, 1000 + N_TENSORS * rank)
+    outs = [torch.empty(IMAGE_BYTES, dtype=torch.uint8, device=dev) for _ in range(N_TENSORS)]
+    algo_bytes_step = N_TENSORS * ELEMS * BYTES_PER_ELEM
+
+    def step():
+        cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b, outs=outs)
+
+    # ------------------------------------------------------------------ value: device resident
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    launches0 = _cabi.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        t_begin = torch.cuda.Event(enable_timing=True)
+        t_end = torch.cuda.Event(enable_timing=True)
+        t_begin.record()
+        for a, b in ev:
+            a.record()
+            step()
+            b.record()
+        t_end.record()
+        barrier()
+    launches = _cabi.launch_count() - launches0
+    total_ms = max_over_ranks(t_begin.elapsed_time(t_end))
+    kernel_ms = sum(a.elapsed_time(b) for a, b in ev) / len(ev)
+    rc, st = _cabi.device_status()
+    if rc != 0:
+        raise SystemExit(f"device status {st}: a kernel gave up waiting")
+    value = world * args.steps * algo_bytes_step / (total_ms * 1e-3) / 1e9
+    achieved = algo_bytes_step / (kernel_ms * 1e-3) / 1e9
+
+    # ------------------------------------------------------------------ e2e: host buffers in and out
+    e2e = None
+    try:
+        hx = [torch.empty(SHAPE, dtype=torch.float32).pin_memory() for _ in range(N_TENSORS)]
+        for h, x in zip(hx, xs):
+            h.copy_(x)
+        himg = [torch.empty(IMAGE_BYTES, dtype=torch.uint8).pin_memory() for _ in range(N_TENSORS)]
+        geom = _cabi.QueueGeom.for_shape(SHAPE)
+        shape_c, strides_c = _cabi.u32x4(SHAPE), _cabi.u64x4(_cabi.dense_strides(list(SHAPE), 4))
+
+        def e2e_step():
+            for h, o in zip(hx, himg):
+                _cabi.check(_cabi.lib.buda_tilize_pack_host(h.data_ptr(), 0, shape_c, strides_c, ctypes.byref(geom), 6, 0,
+                                                            o.data_ptr(), IMAGE_BYTES, None))
+
+        e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.e2e_steps):
+            e2e_step()
+        barrier()
+        e2e_s = max_over_ranks(time.perf_counter() - t0)
+        same = bool(torch.equal(himg[-1], outs[-1].cpu()))
+        e2e = {"value": world * args.e2e_steps * algo_bytes_step / e2e_s / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": N_TENSORS * ELEMS * 4, "d2h_bytes_per_step": N_TENSORS * IMAGE_BYTES,
+               "steps": args.e2e_steps, "api": "buda_tilize_pack_host (pinned host tensors)", "matches_device_path": same}
+        del hx, himg
+    except Exception as exc:  # report, never hide
+        e2e = {"value": None, "unit": "GB/s", "error": str(exc)}
+
+    # ------------------------------------------------------------------ secondary kernels (not the headline)
+    extras = {}
+    if not args.no_extras:
+        def timed(fn, nbytes, reps=10):
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(reps):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / reps
+            return {"GB/s": round(nbytes / (ms * 1e-3) / 1e9, 1), "frac_hbm": round(nbytes / (ms * 1e-3) / 1e9 / hbm_peak, 3),
+                    "ms": round(ms, 4)}
+
+        try:
+            for name, df, ib in (("pack_bfp4_b", cuda_ops.DF.Bfp4_b, 9437184), ("pack_bfp2_b", cuda_ops.DF.Bfp2_b, 5242880)):
+                o2 = [o[:ib] for o in outs]
+                extras[name] = timed(lambda: cuda_ops.tilize_pack_batch(xs, df, outs=o2), N_TENSORS * (ELEMS * 4 + ib))
+            extras["pack_bfp8_b_direct_kernel"] = timed(
+                lambda: cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b, outs=outs, path=1), algo_bytes_step)
+            ys = [torch.empty(SHAPE, dtype=torch.float32, device=dev) for _ in range(16)]
+            extras["unpack_bfp8_b"] = timed(
+                lambda: cuda_ops.unpack_untilize_batch(outs[:16], cuda_ops.DF.Bfp8_b, SHAPE, outs=ys), 16 * ELEMS * BYTES_PER_ELEM)
+            del ys
+            n3 = 32 * 1024 * 1024
+            x3 = torch.rand(32, 1024, 1024, device=dev) * 12 - 6
+            sc = torch.tensor([0.05], device=dev)
+            extras["quantize"] = timed(lambda: cuda_ops.quantize(x3, sc, 3), n3 * 5)
+            q3 = cuda_ops.quantize(x3, sc, 3)
+            extras["dequantize"] = timed(lambda: cuda_ops.dequantize(q3, sc, 3), n3 * 5)
+            acc = torch.randint(-2 ** 20, 2 ** 20, (32, 1024, 1024), device=dev, dtype=torch.int32)
+            scs = torch.rand(1024, device=dev) * (1e-2 - 1e-4) + 1e-4
+            extras["requantize"] = timed(lambda: cuda_ops.buda_requantize(acc, scs, 0), n3 * 5)
+            del x3, q3, acc
+        except Exception as exc:
+            extras["error"] = str(exc)
+        try:
+            M, K, N = 8192, 4096, 16384
+            a = torch.randn(M, K, device=dev).bfloat16()
+            w = torch.randn(1, 1, K, N, device=dev) * 0.02
+            wimg = cuda_ops.tilize_pack(w, cuda_ops.DF.Bfp8_b)
+            c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            r = timed(lambda: cuda_ops.bfp8b_matmul(a, wimg, N, out=c), 0, reps=5)
+            extras["bfp8b_gemm_8192x4096x16384"] = {"TFLOP/s": round(2.0 * M * N * K / (r["ms"] * 1e-3) / 1e12, 1), "ms": r["ms"]}
+        except Exception as exc:
+            extras["bfp8b_gemm_8192x4096x16384"] = {"error": str(exc)}
+
+    # ------------------------------------------------------------------ CPU baseline (rank 0, N = 1 only)
+    cpu = None
+    if rank == 0 and world == 1:
+        try:
+            from oracle import budaref as R
+
+            R.build()
+            n_cpu = 8
+            hs = [x.cpu().numpy() for x in xs[:n_cpu]]
+            R.tilize_pack(hs[0], R.Bfp8_b)
+            t0 = time.perf_counter()
+            for h in hs:
+                R.tilize_pack(h, R.Bfp8_b)
+            dt = time.perf_counter() - t0
+            cpu = {"value": n_cpu * ELEMS * BYTES_PER_ELEM / dt / 1e9, "unit": "GB/s", "cores": R.threads(), "kind": "port",
+                   "sample": f"first {n_cpu} of the 64 tensors, one pass, OpenMP over all host cores"}
+        except Exception as exc:
+            cpu = {"value": None, "unit": "GB/s", "error": str(exc)}
+
+    if rank == 0:
+        line = {
+            "metric": "bfp8b_tilize_pack_throughput", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "per_gpu_batch": N_TENSORS, "l2": "inputs (4 GiB per step) larger than L2",
+                       "launches_per_step": 1},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                         "traffic": None, "peak_kind": peak_kind, "kernel": "pack_staged_kernel<7,4>",
+                         "kernel_ms": kernel_ms},
+            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
+            "other_kernels": extras,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

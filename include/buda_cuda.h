@@ -1,0 +1,198 @@
+/*
+ * buda_cuda.h -- C ABI of libbuda_cuda.so: the B200 (sm_100a) implementation of TT-Buda's
+ * data-format path (tilize / untilize, Bfp8_b / Bfp4_b / Bfp2_b pack and unpack, the golden int8
+ * quantise ops, and the matmul whose weights are stored as Bfp8_b tiles).
+ *
+ * Conventions
+ *   - Every function returns a buda_status (the reference's DEVICE_STATUS_CODE values,
+ *     pybuda/csrc/backend_api/backend_api.cpp:622-625) and never throws.  After a non-zero
+ *     return, buda_last_error() gives the reason for the calling thread.
+ *   - Pointers are DEVICE pointers unless the parameter name ends in _host.
+ *   - `stream` is a cudaStream_t passed as void*; NULL is the legacy default stream.  Device
+ *     entry points only enqueue work; the _host entry points return after the result is in the
+ *     caller's host buffer.
+ *   - Shapes are [w, z, r, c], strides are in BYTES, outermost first, exactly as in the
+ *     reference's PytorchTensorDesc (pybuda/csrc/lower_to_buda/common.hpp:251-258), widened to
+ *     64 bits so tensors above 4 GiB keep working.
+ *   - Data formats are the integer values of the reference's DataFormat enum
+ *     (pybuda/csrc/lower_to_buda/common.hpp:92-111).
+ *   - There is no CPU fallback: without a CUDA device every compute entry point fails.
+ */
+#ifndef BUDA_CUDA_H
+#define BUDA_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum buda_status {
+    BUDA_SUCCESS = 0,
+    BUDA_RUNTIME_ERROR = 1,
+    BUDA_TIMEOUT_ERROR = 2
+} buda_status;
+
+/* DataFormat, pybuda/csrc/lower_to_buda/common.hpp:92-111 */
+enum {
+    BUDA_DF_Float32 = 0, BUDA_DF_Float16 = 1, BUDA_DF_Bfp8 = 2, BUDA_DF_Bfp4 = 3, BUDA_DF_Bfp2 = 11,
+    BUDA_DF_Float16_b = 5, BUDA_DF_Bfp8_b = 6, BUDA_DF_Bfp4_b = 7, BUDA_DF_Bfp2_b = 15, BUDA_DF_Lf8 = 10,
+    BUDA_DF_UInt16 = 12, BUDA_DF_Int8 = 14, BUDA_DF_Int32 = 8, BUDA_DF_RawUInt8 = 0xf0,
+    BUDA_DF_RawUInt16 = 0xf1, BUDA_DF_RawUInt32 = 0xf2, BUDA_DF_Invalid = 0xff
+};
+
+/* Queue geometry: the DramIODesc fields that decide where a tile lands
+ * (pybuda/csrc/backend_api/backend_api.cpp:409-426; tile-level order per TileLayout::map,
+ * pybuda/csrc/balancer/types.cpp:629-648).  A tensor [w,z,R,C] fits when z == t,
+ * R == grid_r*mblock_m*ublock_rt*32 and C == grid_c*mblock_n*ublock_ct*32.  The queue image is
+ * grid_r*grid_c buffers (one per grid core, row-major over the grid); each buffer holds w entries
+ * of t*mblock_m*mblock_n*ublock_rt*ublock_ct tile records. */
+typedef struct buda_queue_geom {
+    uint32_t grid_r, grid_c;
+    uint32_t mblock_m, mblock_n;
+    uint32_t ublock_rt, ublock_ct;
+    uint32_t t;
+    uint32_t ublock_order; /* 0 = R (row-major scan of ublocks inside the mblock), 1 = C */
+} buda_queue_geom;
+
+/* ------------------------------------------------------------------ sizes (host only, no GPU) */
+
+/* Bytes of one 32x32 tile record; with_header adds the 32-byte header/pad.
+ * Replaces tile_size_bytes, pybuda/csrc/balancer/balancer_utils.hpp:24-51.  -1: unknown format. */
+int64_t buda_tile_bytes(int df, int with_header);
+
+/* Replaces data_format_byte_size, pybuda/csrc/lower_to_buda/common.cpp:167-190. */
+int64_t buda_data_format_byte_size(int df, int64_t elements);
+
+/* Replaces tt::backend::get_io_size_in_bytes (bound at backend_api.cpp:710-722; called from
+ * pybuda/csrc/placer/allocator_utils.cpp:17-48).  Tilized queues are sized with the 32-byte
+ * per-tile header, as the reference compiler sizes them. */
+int64_t buda_io_size_bytes(int df, int untilized, uint32_t ublock_ct, uint32_t ublock_rt, uint32_t mblock_m,
+                           uint32_t mblock_n, uint32_t t, uint32_t entries, uint32_t tile_height,
+                           uint32_t tile_width);
+
+/* Total bytes of the queue image of a [w,z,R,C] tensor (all grid buffers); -1 if it does not fit. */
+int64_t buda_tilized_bytes(const buda_queue_geom *geom, const uint32_t shape[4], int df, int with_header);
+
+/* Linear position of tile (t, r, c): which grid core and which tile address in its buffer.
+ * Replaces TileLayout::map, pybuda/csrc/balancer/types.cpp:629-648. */
+int buda_tile_map(const buda_queue_geom *geom, uint32_t t, uint32_t r, uint32_t c, uint32_t *core_r,
+                  uint32_t *core_c, uint64_t *addr);
+
+/* ------------------------------------------------------------------ tilize + pack */
+
+/* Row-major tensor -> queue image, converting to dst_df on the way.
+ * src_df Float32 or Float16_b -> dst_df Bfp8_b / Bfp4_b / Bfp2_b (block-float pack), or
+ * src_df == dst_df of a plain format (Float32, Float16, Float16_b, Int8, Int32, UInt16, Lf8,
+ * RawUInt8/16/32): layout only.
+ * Replaces the conversion half of tt::backend::tilize_tensor / push_input
+ * (bound at backend_api.cpp:688-704). */
+int buda_tilize_pack(const void *src, int src_df, const uint32_t shape[4], const uint64_t strides_bytes[4],
+                     const buda_queue_geom *geom, int dst_df, int with_header, void *dst, uint64_t dst_bytes,
+                     void *stream);
+
+/* The same over n independent tensors of one shape and geometry in ONE launch (the caller loop of
+ * push_to_queues / push_constants_and_parameters, pybuda/pybuda/backend.py:448-493, hoisted into
+ * the kernel).  srcs_host / dsts_host are HOST arrays of n device pointers. */
+int buda_tilize_pack_batch(int n, const void *const *srcs_host, int src_df, const uint32_t shape[4],
+                           const uint64_t strides_bytes[4], const buda_queue_geom *geom, int dst_df,
+                           int with_header, void *const *dsts_host, uint64_t dst_bytes_each, void *stream);
+
+/* buda_tilize_pack_batch with the kernel chosen by the caller: path 0 = staged (shared-memory
+ * staging by bulk async copies; needs 16-byte aligned rows), 1 = direct (4 lanes per block, warp
+ * shuffle exponent reduction; any alignment).  For tests and for measuring one kernel against the
+ * other; no counterpart in the reference. */
+int buda_tilize_pack_batch_path(int n, const void *const *srcs_host, int src_df, const uint32_t shape[4],
+                                const uint64_t strides_bytes[4], const buda_queue_geom *geom, int dst_df,
+                                int with_header, void *const *dsts_host, uint64_t dst_bytes_each, void *stream,
+                                int path);
+
+/* Host-buffer form: copies the tensor to the device, converts, and copies the image back to
+ * dst_host (what tt::backend::tilize_tensor returns to tti/archive.py:133).  Chunked so the two
+ * copy directions and the kernel overlap.  Blocks until dst_host is complete. */
+int buda_tilize_pack_host(const void *src_host, int src_df, const uint32_t shape[4],
+                          const uint64_t strides_bytes[4], const buda_queue_geom *geom, int dst_df,
+                          int with_header, void *dst_host, uint64_t dst_bytes, void *stream);
+
+/* ------------------------------------------------------------------ unpack + untilize */
+
+/* Queue image -> row-major tensor.  Bfp*_b sources decode to Float32 or Float16_b; plain sources
+ * keep their format.  Replaces the conversion half of tt::backend::get_output
+ * (bound at backend_api.cpp:701). */
+int buda_unpack_untilize(const void *src, int src_df, int with_header, const buda_queue_geom *geom, void *dst,
+                         int dst_df, const uint32_t shape[4], const uint64_t strides_bytes[4], void *stream);
+
+int buda_unpack_untilize_batch(int n, const void *const *srcs_host, int src_df, int with_header,
+                               const buda_queue_geom *geom, void *const *dsts_host, int dst_df,
+                               const uint32_t shape[4], const uint64_t strides_bytes[4], void *stream);
+
+int buda_unpack_untilize_batch_path(int n, const void *const *srcs_host, int src_df, int with_header,
+                                    const buda_queue_geom *geom, void *const *dsts_host, int dst_df,
+                                    const uint32_t shape[4], const uint64_t strides_bytes[4], void *stream,
+                                    int path);
+
+int buda_unpack_untilize_host(const void *src_host, int src_df, int with_header, const buda_queue_geom *geom,
+                              void *dst_host, int dst_df, const uint32_t shape[4],
+                              const uint64_t strides_bytes[4], void *stream);
+
+/* ------------------------------------------------------------------ golden int8 quantise ops
+ * The scale used for element i is scale[(i / inner) % scale_len]; scale_len == 1 is a per-tensor
+ * scale, otherwise inner is the product of the dims after the quantisation axis
+ * (reshape_to_match_input, pybuda/pybuda/op/eval/pybuda/quantize.py:38-52).  Results are
+ * bit-identical to the reference's torch expressions. */
+
+/* mode 0 Quantize      clamp(round(x / scale) + zp, lo, hi)   quantize.py:56-66
+ * mode 1 BudaQuantize  clamp(round(x * scale) + zp, lo, hi)   quantize.py:68-77, buda/quantize.py:24-33 */
+int buda_quantize(const float *x, int64_t n, const float *scale, int64_t scale_len, int64_t inner, float zero_point,
+                  int mode, float lo, float hi, int8_t *out, void *stream);
+
+/* Dequantize  (float(x) - zp) * scale   quantize.py:79-93, buda/quantize.py:35-40 */
+int buda_dequantize(const int8_t *x, int64_t n, const float *scale, int64_t scale_len, int64_t inner,
+                    float zero_point, float *out, void *stream);
+
+/* mode 0 Requantize      round((inp_scale / out_scale) * float(x) + zp)   quantize.py:95-110
+ * mode 1 BudaRequantize  round(float(x) * scale + zp)   quantize.py:112-122, buda/quantize.py:42-53
+ * (mode 1 ignores out_scale) */
+int buda_requantize(const int32_t *x, int64_t n, const float *inp_scale, const float *out_scale, int64_t scale_len,
+                    int64_t inner, float zero_point, int mode, float lo, float hi, int8_t *out, void *stream);
+
+/* ------------------------------------------------------------------ matmul with Bfp8_b weights
+ * C[M,N] (bfloat16, row stride ldc elements) = A[M,K] (bfloat16, row stride lda elements) @ W,
+ * W a [K,N] tensor stored as the Bfp8_b queue image of geometry grid 1x1, ublock 1x1, order R,
+ * no tile header (tile (kt,nt) at record kt*(N/32)+nt).  binary32 accumulation on tcgen05 tensor
+ * cores; weights are decoded in registers inside the kernel.  The device counterpart of the golden
+ * matmul (pybuda/pybuda/op/eval/pybuda/matmul.py:20-33) for a weight queue whose df is Bfp8_b
+ * (pybuda/csrc/passes/amp.cpp:457-500).  M % 128 == 0, N % 128 == 0, K % 64 == 0. */
+int buda_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N, void *C,
+                    int64_t ldc, void *stream);
+
+/* ------------------------------------------------------------------ errors and status */
+
+/* Copies the calling thread's last error text (NUL terminated) into buf; returns its length. */
+size_t buda_last_error(char *buf, size_t buf_len);
+
+/* Synchronises the current device, reads and clears the device status word.  *status_out gets 0 if every
+ * kernel since the last call completed normally, otherwise a code naming the bounded wait that
+ * gave up (see BUDA_DEVSTAT_*); the function then returns BUDA_TIMEOUT_ERROR. */
+int buda_device_status(int *status_out);
+
+enum {
+    BUDA_DEVSTAT_OK = 0,
+    BUDA_DEVSTAT_PACK_FULL_WAIT = 1,   /* pack: consumer waited too long for a staged band     */
+    BUDA_DEVSTAT_PACK_EMPTY_WAIT = 2,  /* pack: producer waited too long for a free stage      */
+    BUDA_DEVSTAT_UNPACK_FULL_WAIT = 3,
+    BUDA_DEVSTAT_UNPACK_EMPTY_WAIT = 4,
+    BUDA_DEVSTAT_GEMM_WAIT = 5
+};
+
+/* Number of kernels this library has launched in this process (for launch accounting). */
+uint64_t buda_launch_count(void);
+
+/* Library / build identification, e.g. "buda_cuda sm_100a". */
+const char *buda_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BUDA_CUDA_H */

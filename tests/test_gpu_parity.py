@@ -1,0 +1,314 @@
+"""GPU parity tests: the CUDA kernels, called through the C ABI, against the CPU oracle on the
+same seeded inputs.  Bit-exact for every integer / byte result."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+BFP = ["Bfp8_b", "Bfp4_b", "Bfp2_b"]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.fail("these tests need a CUDA device; there is no CPU fallback to test")
+    from pybuda import cuda_ops
+
+    return cuda_ops
+
+
+def _geom_pair(ops, oracle, shape, grid=(1, 1), ublock=(1, 1), order=0):
+    return (ops.QueueGeom.for_shape(shape, grid, ublock, order), oracle.Geom.for_shape(shape, grid, ublock, order))
+
+
+def _special_values(shape, seed):
+    """Values that exercise every branch of the encoder: outliers, zeros, denormals, ties,
+    Inf / NaN, blocks at both ends of the exponent range."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(shape, generator=g)
+    flat = x.view(-1)
+    n = flat.numel()
+    m1 = torch.rand(n, generator=g) < 0.01
+    flat[m1] *= 1e3
+    flat[torch.rand(n, generator=g) < 0.005] = 0.0
+    rows = flat.view(-1, 16)  # a row here is one block only when the last dim is a multiple of 16
+    k = rows.shape[0]
+    rows[k // 7] = 0.0                                           # all-zero block
+    rows[k // 6] = torch.randn(16, generator=g) * 2.0 ** -124    # shared exponent below the mantissa width
+    rows[k // 5] = torch.randn(16, generator=g) * 1e-41          # denormals only
+    rows[k // 4] = torch.randn(16, generator=g) * 2.0 ** 126     # top of the range
+    rows[k // 3] = torch.tensor([float("inf"), float("-inf"), float("nan"), 1e38, -1e30, 1.0, 0.0, -0.0] * 2)
+    rows[k // 2] = torch.tensor([64.0, 0.5, 1.5, 2.5, -0.5, -1.5, 3.5, 0.25, 0.75, -0.25, 1.0, 2.0, 63.5, 63.75, 0.0, 4.5])
+    rows[k // 2 + 1] = torch.tensor([1.0, 1.9999, -1.9999, 1.984375, 1.9921875, 1.99609375, 1.0078125, 1.00390625] * 2)
+    return x
+
+
+def _bits(a):
+    return np.ascontiguousarray(a).view(np.uint8)
+
+
+# ------------------------------------------------------------------------------------------------
+# config 1: [1,1,1024,1024] N(0,1) seed 0 -> Bfp8_b (1,114,112 bytes) -> back, byte for byte
+# ------------------------------------------------------------------------------------------------
+def test_config1_pack_unpack_bit_exact(ops, oracle):
+    x = torch.randn(1, 1, 1024, 1024, generator=torch.Generator().manual_seed(0))
+    img = ops.tilize_pack(x.cuda(), ops.DF.Bfp8_b)
+    assert img.numel() == 1114112
+    ref = oracle.tilize_pack(x.numpy(), oracle.Bfp8_b)
+    assert np.array_equal(img.cpu().numpy(), ref)
+    y = ops.unpack_untilize(img, ops.DF.Bfp8_b, x.shape)
+    yref = oracle.unpack_untilize(ref, oracle.Bfp8_b, x.shape)
+    assert np.array_equal(_bits(y.cpu().numpy()), _bits(yref))
+    assert (y.cpu() - x).abs().max() < 2.0 ** -5
+
+
+@pytest.mark.parametrize("df", BFP)
+@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("src", ["f32", "bf16"])
+def test_pack_special_values(ops, oracle, df, path, src):
+    x = _special_values((2, 2, 64, 160), seed=11)
+    gq, go = _geom_pair(ops, oracle, x.shape)
+    if src == "bf16":
+        xb = x.bfloat16()
+        img = ops.tilize_pack(xb.cuda(), getattr(ops.DF, df), gq, path=path)
+        ref = oracle.tilize_pack(xb.view(torch.int16).numpy().view(np.uint16), getattr(oracle, df), go,
+                                 src_df=oracle.Float16_b)
+    else:
+        img = ops.tilize_pack(x.cuda(), getattr(ops.DF, df), gq, path=path)
+        ref = oracle.tilize_pack(x.numpy(), getattr(oracle, df), go)
+    got = img.cpu().numpy()
+    if not np.array_equal(got, ref):
+        bad = np.nonzero(got != ref)[0]
+        pytest.fail(f"{bad.size} bytes differ, first at {bad[:8]}: got {got[bad[:8]]} want {ref[bad[:8]]}")
+
+
+@pytest.mark.parametrize("df", BFP)
+@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("dst", [torch.float32, torch.bfloat16])
+def test_unpack_arbitrary_bytes(ops, oracle, df, path, dst):
+    # any byte string is a valid image: sign bits on zero magnitudes, exponents 0 and 255 included
+    shape = (1, 3, 96, 64)
+    gq, go = _geom_pair(ops, oracle, shape)
+    n = oracle.lib().ref_tilized_bytes(go, (ctypes.c_uint32 * 4)(*shape), getattr(oracle, df), 0)
+    rng = np.random.default_rng(5)
+    img = rng.integers(0, 256, n, dtype=np.uint8)
+    img[:64] = np.arange(64) * 4          # exponents 0..252 in the first tile
+    img[1088 if df == "Bfp8_b" else 0] = 255
+    y = ops.unpack_untilize(torch.from_numpy(img).cuda(), getattr(ops.DF, df), shape, dtype=dst, geom=gq, path=path)
+    if dst == torch.float32:
+        ref = oracle.unpack_untilize(img, getattr(oracle, df), shape, geom=go)
+        assert np.array_equal(_bits(y.cpu().numpy()), _bits(ref))
+    else:
+        ref = oracle.unpack_untilize(img, getattr(oracle, df), shape, dst_dtype=np.uint16, geom=go, dst_df=oracle.Float16_b)
+        assert np.array_equal(y.cpu().view(torch.int16).numpy().view(np.uint16), ref)
+
+
+@pytest.mark.parametrize("grid,ublock,order", [((1, 1), (1, 1), 0), ((2, 2), (1, 1), 0), ((1, 1), (2, 4), 0),
+                                               ((2, 1), (3, 2), 1), ((1, 4), (1, 1), 1)])
+@pytest.mark.parametrize("hdr", [False, True])
+def test_queue_geometry_and_header(ops, oracle, grid, ublock, order, hdr):
+    shape = (3, 2, 192, 256)
+    x = torch.randn(shape, generator=torch.Generator().manual_seed(21))
+    gq, go = _geom_pair(ops, oracle, shape, grid, ublock, order)
+    for df in ("Bfp8_b", "Bfp4_b"):
+        ref = oracle.tilize_pack(x.numpy(), getattr(oracle, df), go, with_header=hdr)
+        for path in (0, 1):
+            img = ops.tilize_pack(x.cuda(), getattr(ops.DF, df), gq, with_header=hdr, path=path)
+            assert np.array_equal(img.cpu().numpy(), ref), (df, path)
+            y = ops.unpack_untilize(img, getattr(ops.DF, df), shape, geom=gq, with_header=hdr, path=path)
+            yref = oracle.unpack_untilize(ref, getattr(oracle, df), shape, geom=go, with_header=hdr)
+            assert np.array_equal(_bits(y.cpu().numpy()), _bits(yref)), (df, path)
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 32, 32), (1, 1, 32, 96), (1, 1, 64, 160), (1, 1, 32, 4128), (2, 1, 96, 224)])
+def test_ragged_widths(ops, oracle, shape):
+    # tile columns not a multiple of the 4-tile work item; one tile; a very wide single band
+    x = _special_values(shape, seed=31) if shape[-1] * shape[-2] >= 16 * 64 else torch.randn(shape)
+    for df in BFP:
+        ref = oracle.tilize_pack(x.numpy(), getattr(oracle, df))
+        for path in (0, 1):
+            img = ops.tilize_pack(x.cuda(), getattr(ops.DF, df), path=path)
+            assert np.array_equal(img.cpu().numpy(), ref), (df, path)
+            y = ops.unpack_untilize(img, getattr(ops.DF, df), shape, path=path)
+            assert np.array_equal(_bits(y.cpu().numpy()), _bits(oracle.unpack_untilize(ref, getattr(oracle, df), shape)))
+
+
+def test_unaligned_and_strided_sources(ops, oracle):
+    # a view whose rows start 4 bytes off a 16-byte boundary, and one with padded rows
+    base = torch.randn(1, 1, 64, 132, generator=torch.Generator().manual_seed(41)).cuda()
+    v = base[..., 1:129]            # 128 columns starting at element 1: unaligned rows, row stride 132
+    assert v.data_ptr() % 16 != 0
+    ref = oracle.tilize_pack(v.cpu().contiguous().numpy(), oracle.Bfp8_b)
+    img = ops.tilize_pack(v, ops.DF.Bfp8_b)   # must pick the direct kernel by itself
+    assert np.array_equal(img.cpu().numpy(), ref)
+    base2 = torch.randn(1, 1, 64, 256, generator=torch.Generator().manual_seed(42)).cuda()
+    v2 = base2[..., :128]           # aligned rows with a 1024-byte pitch: staged kernel, strided
+    ref2 = oracle.tilize_pack(v2.cpu().contiguous().numpy(), oracle.Bfp4_b)
+    assert np.array_equal(ops.tilize_pack(v2, ops.DF.Bfp4_b).cpu().numpy(), ref2)
+    # untilize into a strided destination leaves the gaps alone
+    out = torch.full((1, 1, 64, 256), 7.0, device="cuda")
+    ops.unpack_untilize(torch.from_numpy(ref2).cuda(), ops.DF.Bfp4_b, (1, 1, 64, 128), out=out[..., :128])
+    assert torch.all(out[..., 128:] == 7.0)
+    assert np.array_equal(_bits(out[..., :128].cpu().contiguous().numpy()),
+                          _bits(oracle.unpack_untilize(ref2, oracle.Bfp4_b, (1, 1, 64, 128))))
+
+
+@pytest.mark.parametrize("dt,df", [(torch.float32, "Float32"), (torch.bfloat16, "Float16_b"), (torch.float16, "Float16"),
+                                   (torch.int8, "Int8"), (torch.int32, "Int32")])
+def test_plain_tilize_untilize(ops, oracle, dt, df):
+    shape = (2, 2, 96, 160)
+    g = torch.Generator().manual_seed(51)
+    x = (torch.randn(shape, generator=g) * 50).to(dt)
+    np_view = {torch.bfloat16: np.uint16, torch.float16: np.float16}.get(dt)
+    xn = x.view(torch.int16).numpy().view(np.uint16) if dt == torch.bfloat16 else x.numpy()
+    odf = getattr(oracle, df)
+    gq, go = _geom_pair(ops, oracle, shape, (1, 1), (3, 1), 1)
+    ref = oracle.tilize_pack(xn, odf, go, src_df=odf)
+    for path in (0, 1):
+        img = ops.tilize_pack(x.cuda(), getattr(ops.DF, df), gq, path=path)
+        assert np.array_equal(img.cpu().numpy(), ref), path
+        y = ops.unpack_untilize(img, getattr(ops.DF, df), shape, dtype=dt, geom=gq, path=path)
+        assert torch.equal(y.cpu().view(torch.uint8), x.view(torch.uint8)), path
+
+
+def test_batch_launch_matches_single(ops, oracle):
+    g = torch.Generator().manual_seed(61)
+    xs = [torch.randn(1, 1, 128, 256, generator=g).cuda() for _ in range(5)]
+    before = ops._cabi.launch_count()
+    imgs = ops.tilize_pack_batch(xs, ops.DF.Bfp8_b)
+    assert ops._cabi.launch_count() - before == 1
+    for x, im in zip(xs, imgs):
+        assert np.array_equal(im.cpu().numpy(), oracle.tilize_pack(x.cpu().numpy(), oracle.Bfp8_b))
+    ys = ops.unpack_untilize_batch(imgs, ops.DF.Bfp8_b, (1, 1, 128, 256))
+    for im, y in zip(imgs, ys):
+        assert np.array_equal(_bits(y.cpu().numpy()),
+                              _bits(oracle.unpack_untilize(im.cpu().numpy(), oracle.Bfp8_b, (1, 1, 128, 256))))
+
+
+def test_config2_tensor_full_size(ops, oracle):
+    # one tensor of the batch config at full size: [1,1,4096,4096], 1% outliers x1e3, 0.5% zeros
+    g = torch.Generator().manual_seed(1000)
+    x = torch.randn(1, 1, 4096, 4096, generator=g)
+    m1 = torch.rand(x.shape, generator=g) < 0.01
+    x[m1] *= 1e3
+    m0 = torch.rand(x.shape, generator=g) < 0.005
+    x[m0] = 0.0
+    xd = x.cuda()
+    for df, nbytes in (("Bfp8_b", 17825792), ("Bfp4_b", 9437184), ("Bfp2_b", 5242880)):
+        img = ops.tilize_pack(xd, getattr(ops.DF, df))
+        assert img.numel() == nbytes
+        ref = oracle.tilize_pack(x.numpy(), getattr(oracle, df))
+        assert np.array_equal(img.cpu().numpy(), ref), df
+        # size-independent properties: decode/encode is idempotent, and the direct kernel agrees
+        y = ops.unpack_untilize(img, getattr(ops.DF, df), x.shape)
+        assert torch.equal(ops.tilize_pack(y, getattr(ops.DF, df)), img)
+        assert torch.equal(ops.tilize_pack(xd, getattr(ops.DF, df), path=1), img)
+
+
+def test_host_buffer_entry_points(ops, oracle):
+    cabi = ops._cabi
+    # the last case is 8 pipeline slices, so the four staging slots are reused
+    for shape, grid in (((2, 2, 256, 512), (1, 1)), ((1, 1, 1024, 1024), (1, 1)), ((1, 2, 128, 256), (2, 2)),
+                        ((2, 1, 8192, 1024), (1, 1))):
+        x = torch.randn(shape, generator=torch.Generator().manual_seed(71))
+        gq, go = _geom_pair(ops, oracle, shape, grid)
+        n = cabi.tilized_bytes(gq, shape, int(ops.DF.Bfp8_b))
+        img = torch.empty(n, dtype=torch.uint8).pin_memory()
+        xp = x.pin_memory()
+        st = cabi.u64x4(cabi.dense_strides(list(shape), 4))
+        cabi.check(cabi.lib.buda_tilize_pack_host(xp.data_ptr(), int(ops.DF.Float32), cabi.u32x4(shape), st,
+                                                  ctypes.byref(gq), int(ops.DF.Bfp8_b), 0, img.data_ptr(), n, None))
+        ref = oracle.tilize_pack(x.numpy(), oracle.Bfp8_b, go)
+        assert np.array_equal(img.numpy(), ref), shape
+        y = torch.empty(shape, dtype=torch.float32)  # pageable destination works too
+        cabi.check(cabi.lib.buda_unpack_untilize_host(img.data_ptr(), int(ops.DF.Bfp8_b), 0, ctypes.byref(gq),
+                                                      y.data_ptr(), int(ops.DF.Float32), cabi.u32x4(shape), st, None))
+        assert np.array_equal(_bits(y.numpy()), _bits(oracle.unpack_untilize(ref, oracle.Bfp8_b, shape, geom=go)))
+
+
+# ------------------------------------------------------------------------------------------------
+# quantise ops: golden vectors of the reference, then the full-size config against the oracle
+# ------------------------------------------------------------------------------------------------
+def test_quant_ops_match_reference_golden(ops, golden):
+    g = {k: torch.from_numpy(np.asarray(v)).cuda() if np.asarray(v).ndim else float(v) for k, v in golden.items()}
+    eq = lambda a, b: torch.equal(a.view(torch.uint8) if a.dtype != torch.int8 else a, b.view(torch.uint8) if b.dtype != torch.int8 else b)
+    assert eq(ops.quantize(g["a_x"], g["a_scale"], g["a_zp"]), g["a_q"])
+    assert eq(ops.dequantize(g["a_q"], g["a_scale"], 3), g["a_dq"])
+    assert eq(ops.quantize(g["b_x"], g["b_scale_last"], -5, axis=-1), g["b_q_last"])
+    assert eq(ops.quantize(g["b_x"], g["b_scale_mid"], 7, axis=1), g["b_q_mid"])
+    assert eq(ops.dequantize(g["b_q_last"], g["b_scale_last"], -5, axis=-1), g["b_dq_last"])
+    assert eq(ops.dequantize(g["b_q_mid"], g["b_scale_mid"], 7, axis=1), g["b_dq_mid"])
+    assert eq(ops.quantize(g["b_x"], g["c_recip"][0, 0], 2, axis=-1, buda=True), g["c_q"])
+    ones = torch.ones(128, device="cuda")
+    assert eq(ops.requantize(g["d_acc"], g["d_scales"], ones, 0), g["d_rq"])
+    assert eq(ops.requantize(g["d_acc"], g["d_scales"], ones, 11), g["d_rq_zp11"])
+    assert eq(ops.requantize(g["d_acc"], g["d_scales"], g["d_out_scale"], -3), g["d_rq_div_zpm3"])
+    assert eq(ops.buda_requantize(g["d_acc"], g["d_scales"], 0), g["d_brq"])
+    assert eq(ops.requantize(g["d_acc"], g["d_scales_mid"], torch.ones(32, device="cuda"), 5, axis=1), g["d_rq_mid_zp5"])
+
+
+def test_quant_config3_full_size(ops, oracle):
+    # fp32 [32,1024,1024] ~ U(-6,6): Quantize (scale 0.05, zp 3) then Dequantize; int32 accumulators
+    # ~ U(-2^20, 2^20) requantised per output channel with 1024 scales ~ U(1e-4, 1e-2), zp 0
+    x = torch.rand(32, 1024, 1024, generator=torch.Generator().manual_seed(3)) * 12 - 6
+    scale = torch.tensor([0.05])
+    q = ops.quantize(x.cuda(), scale.cuda(), 3)
+    qref = oracle.quantize(x.numpy(), scale.numpy(), 3)
+    assert np.array_equal(q.cpu().numpy(), qref)
+    dq = ops.dequantize(q, scale.cuda(), 3)
+    assert np.array_equal(_bits(dq.cpu().numpy()), _bits(oracle.dequantize(qref, scale.numpy(), 3)))
+    del x, q, dq
+    acc = torch.randint(-2 ** 20, 2 ** 20, (32, 1024, 1024), generator=torch.Generator().manual_seed(4), dtype=torch.int32)
+    scales = torch.rand(1024, generator=torch.Generator().manual_seed(5)) * (1e-2 - 1e-4) + 1e-4
+    ones = torch.ones(1024)
+    rq = ops.requantize(acc.cuda(), scales.cuda(), ones.cuda(), 0)
+    rref = oracle.requantize(acc.numpy(), scales.numpy(), ones.numpy(), 0)
+    assert np.array_equal(rq.cpu().numpy(), rref)
+    brq = ops.buda_requantize(acc.cuda(), scales.cuda(), 0)
+    assert np.array_equal(brq.cpu().numpy(), rref)
+    assert rq.min() == -128 and rq.max() == 127  # the config saturates both ways
+
+
+def test_quant_odd_sizes_and_axes(ops, oracle):
+    g = torch.Generator().manual_seed(81)
+    for shape, axis in (((7,), -1), ((3, 5, 17), 1), ((2, 33, 48), 1), ((4, 1000), -1), ((5, 16, 16), 0)):
+        x = torch.randn(shape, generator=g) * 4
+        ax = axis if axis >= 0 else len(shape) + axis
+        s = torch.rand(shape[ax], generator=g) * 0.1 + 0.01
+        q = ops.quantize(x.cuda(), s.cuda(), 1, axis=axis)
+        qref = oracle.quantize(x.numpy(), s.numpy(), 1, axis=axis)
+        assert np.array_equal(q.cpu().numpy(), qref), (shape, axis)
+        dq = ops.dequantize(q, s.cuda(), 1, axis=axis)
+        assert np.array_equal(_bits(dq.cpu().numpy()), _bits(oracle.dequantize(qref, s.numpy(), 1, axis=axis)))
+        acc = torch.randint(-2 ** 24, 2 ** 24, shape, generator=g, dtype=torch.int32)
+        s2 = torch.rand(shape[ax], generator=g) + 0.5
+        rq = ops.requantize(acc.cuda(), (s * 1e-4).cuda(), s2.cuda(), -2, axis=axis)
+        assert np.array_equal(rq.cpu().numpy(), oracle.requantize(acc.numpy(), (s * 1e-4).numpy(), s2.numpy(), -2, axis=axis))
+    # misaligned base pointers take the scalar path
+    x = torch.randn(1001, generator=g).cuda()[1:]
+    s = torch.tensor([0.1])
+    assert np.array_equal(ops.quantize(x, s.cuda(), 0).cpu().numpy(), oracle.quantize(x.cpu().numpy(), s.numpy(), 0))
+
+
+# ------------------------------------------------------------------------------------------------
+# error behaviour at the C ABI: status codes, never an exception or a fault
+# ------------------------------------------------------------------------------------------------
+def test_bad_arguments_return_runtime_error(ops):
+    cabi = ops._cabi
+    x = torch.zeros(1, 1, 32, 48, device="cuda")
+    with pytest.raises(cabi.BudaError) as e:
+        ops.tilize_pack(x, ops.DF.Bfp8_b, geom=cabi.QueueGeom(1, 1, 1, 1, 1, 1, 1, 0))
+    assert e.value.code == cabi.RUNTIME_ERROR and "multiples of the 32x32 tile" in str(e.value)
+    y = torch.zeros(1, 1, 64, 64, device="cuda")
+    with pytest.raises(cabi.BudaError) as e:
+        ops.tilize_pack(y, ops.DF.Bfp8_b, geom=cabi.QueueGeom(1, 1, 1, 1, 1, 1, 1, 0))
+    assert "queue geometry covers" in str(e.value)
+    with pytest.raises(cabi.BudaError):
+        ops.tilize_pack(y.to(torch.int8), ops.DF.Bfp8_b)
+    with pytest.raises(cabi.BudaError):
+        ops.tilize_pack(y, ops.DF.Bfp8)  # 'a' formats are not on this path yet
+    rc, st = cabi.device_status()
+    assert rc == cabi.SUCCESS and st == 0

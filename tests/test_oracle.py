@@ -1,0 +1,263 @@
+"""CPU tests that pin the oracle: against the reference's golden quantise outputs, against the
+reference's own tile-order round-trip property, against its byte-size tables, and (for the
+unpinned Bfp encoding) against hand-worked blocks and an independent pure-Python statement of the
+frozen spec."""
+import itertools
+import math
+import struct
+
+import numpy as np
+import pytest
+
+
+# ------------------------------------------------------------------------------------------------
+# quantise ops vs the reference's golden vectors (tests/golden/gen_quant_golden.py)
+# ------------------------------------------------------------------------------------------------
+def test_quantize_matches_reference_golden(oracle, golden):
+    g = golden
+    assert np.array_equal(oracle.quantize(g["a_x"], g["a_scale"], float(g["a_zp"])), g["a_q"])
+    assert np.array_equal(oracle.quantize(g["b_x"], g["b_scale_last"], -5, axis=-1), g["b_q_last"])
+    assert np.array_equal(oracle.quantize(g["b_x"], g["b_scale_mid"], 7, axis=1), g["b_q_mid"])
+    # BudaQuantize takes a pre-broadcast reciprocal scale: row 0 of it is the per-column vector
+    assert np.array_equal(oracle.quantize(g["b_x"], g["c_recip"][0, 0], 2, axis=-1, buda=True), g["c_q"])
+
+
+def test_dequantize_matches_reference_golden(oracle, golden):
+    g = golden
+    bits = lambda a: np.ascontiguousarray(a).view(np.uint32)
+    assert np.array_equal(bits(oracle.dequantize(g["a_q"], g["a_scale"], 3)), bits(g["a_dq"]))
+    assert np.array_equal(bits(oracle.dequantize(g["b_q_last"], g["b_scale_last"], -5, axis=-1)), bits(g["b_dq_last"]))
+    assert np.array_equal(bits(oracle.dequantize(g["b_q_mid"], g["b_scale_mid"], 7, axis=1)), bits(g["b_dq_mid"]))
+    assert np.array_equal(bits(oracle.dequantize(g["c_q"], g["b_scale_last"], 2, axis=-1)), bits(g["c_dq"]))
+
+
+def test_requantize_matches_reference_golden(oracle, golden):
+    g = golden
+    ones = np.ones(128, np.float32)
+    assert np.array_equal(oracle.requantize(g["d_acc"], g["d_scales"], ones, 0), g["d_rq"])
+    assert np.array_equal(oracle.requantize(g["d_acc"], g["d_scales"], ones, 11), g["d_rq_zp11"])
+    assert np.array_equal(oracle.requantize(g["d_acc"], g["d_scales"], g["d_out_scale"], -3), g["d_rq_div_zpm3"])
+    assert np.array_equal(oracle.buda_requantize(g["d_acc"], g["d_scales"], 0), g["d_brq"])
+    assert np.array_equal(oracle.requantize(g["d_acc"], g["d_scales_mid"], np.ones(32, np.float32), 5, axis=1),
+                          g["d_rq_mid_zp5"])
+
+
+def test_quantize_saturates_and_rounds_half_even(oracle):
+    x = np.array([0.025, 0.075, 0.125, -0.025, -0.075, 1e9, -1e9, np.nan, np.inf, -np.inf], np.float32)
+    q = oracle.quantize(x, np.array([0.05], np.float32), 0)
+    # 0.025/0.05 = 0.5 in binary32 arithmetic rounds to even 0; 0.075/0.05 = 1.5 -> 2; 2.5 -> 2
+    assert list(q) == [0, 2, 2, 0, -2, 127, -128, 0, 127, -128]
+
+
+# ------------------------------------------------------------------------------------------------
+# sizes: pybuda/csrc/lower_to_buda/common.cpp:167-190, pybuda/csrc/balancer/balancer_utils.hpp:24-51
+# ------------------------------------------------------------------------------------------------
+def test_tile_and_format_sizes(oracle):
+    R = oracle
+    expect = {R.Float32: 4096, R.Float16: 2048, R.Float16_b: 2048, R.Bfp8: 1088, R.Bfp8_b: 1088, R.Bfp4: 576,
+              R.Bfp4_b: 576, R.Bfp2: 320, R.Bfp2_b: 320, R.Lf8: 1024, R.UInt16: 2048, R.Int8: 1024, R.Int32: 4096,
+              R.RawUInt8: 1024, R.RawUInt16: 2048, R.RawUInt32: 4096}
+    for df, n in expect.items():
+        assert R.tile_bytes(df, False) == n
+        assert R.tile_bytes(df, True) == n + 32
+        assert R.lib().ref_data_format_byte_size(df, 1024) == n
+    assert R.tile_bytes(R.Invalid) == -1
+
+
+# ------------------------------------------------------------------------------------------------
+# tile order: the reference's exhaustive round trip (balancer/tests/test_tile_layout.cpp:250-281),
+# on a reduced range so it runs in seconds, plus direct checks of the address formula
+# ------------------------------------------------------------------------------------------------
+def _factors(n):
+    return [f for f in range(1, n + 1) if n % f == 0]
+
+
+def test_tile_layout_round_trip(oracle):
+    R = oracle
+    count = 0
+    for tdim, rdim, cdim in itertools.product((1, 3), (1, 4, 6), (1, 4, 6)):
+        for grid_r in _factors(rdim):
+            for grid_c in _factors(cdim):
+                for ur in _factors(rdim // grid_r):
+                    for uc in _factors(cdim // grid_c):
+                        for order in (0, 1):
+                            g = R.Geom(grid_r, grid_c, rdim // (grid_r * ur), cdim // (grid_c * uc), ur, uc, tdim, order)
+                            seen = set()
+                            for t in range(tdim):
+                                for r in range(rdim):
+                                    for c in range(cdim):
+                                        cr, cc, addr = R.tile_map(g, t, r, c)
+                                        assert R.tile_unmap(g, cr, cc, addr) == (t, r, c)
+                                        seen.add((cr, cc, addr))
+                            assert len(seen) == tdim * rdim * cdim  # a bijection
+                            count += 1
+    assert count > 200
+
+
+def test_tile_layout_formula(oracle):
+    R = oracle
+    # grid 2x1, mblock 2x3, ublock 2x2, t = 2
+    g = R.Geom(2, 1, 2, 3, 2, 2, 2, 0)
+    # tile (t=1, r=5, c=3): core row 5 // 4 = 1; inside the core r=1, c=3 -> m=0, n=1, u=(1,1)
+    cr, cc, addr = R.tile_map(g, 1, 5, 3)
+    assert (cr, cc) == (1, 0)
+    assert addr == 1 * (2 * 3 * 4) + (0 * 3 + 1) * 4 + 1 * 2 + 1
+    gc = R.Geom(2, 1, 2, 3, 2, 2, 2, 1)
+    _, _, addr_c = R.tile_map(gc, 1, 5, 3)
+    assert addr_c == 1 * (2 * 3 * 4) + (1 * 2 + 0) * 4 + 1 * 2 + 1
+
+
+# ------------------------------------------------------------------------------------------------
+# Bfp encoding: hand-worked blocks and an independent restatement in exact rational arithmetic
+# ------------------------------------------------------------------------------------------------
+def f2b(x):
+    return struct.unpack("<I", struct.pack("<f", x))[0]
+
+
+def spec_encode_block(bits16, m):
+    """The frozen spec in exact integer/rational arithmetic, written independently of the C code:
+    q = round_half_even(|x| * 2^(m-1) / 2^(E-127)), saturated; zero/denormal -> 0; Inf/NaN -> max."""
+    from fractions import Fraction
+
+    exps = [(b >> 23) & 0xFF for b in bits16]
+    E = max(exps)
+    qmax = (1 << m) - 1
+    datums = []
+    for b, e in zip(bits16, exps):
+        sign = b >> 31
+        if e == 0:
+            q = 0
+        elif e == 255:
+            q = qmax
+        else:
+            mag = Fraction((b & 0x7FFFFF) | 0x800000, 1 << 23) * Fraction(2) ** (e - 127)
+            v = mag * Fraction(2) ** (m - 1) / Fraction(2) ** (E - 127)
+            fl = math.floor(v)
+            rem = v - fl
+            if rem > Fraction(1, 2) or (rem == Fraction(1, 2) and fl % 2 == 1):
+                fl += 1
+            q = min(fl, qmax)
+        datums.append(((sign << m) | q) if q else 0)
+    w = m + 1
+    bitstring = 0
+    for i, d in enumerate(datums):
+        bitstring |= d << (w * i)
+    return E, np.frombuffer(bitstring.to_bytes(2 * w, "little"), dtype=np.uint8)
+
+
+def test_bfp8_hand_worked_blocks(oracle):
+    R = oracle
+    # all zero
+    E, d = R.bfp_pack_block(np.zeros(16, np.uint32), 7)
+    assert E == 0 and not d.any()
+    # 1.0 alone: exponent 127, magnitude 64 (1.0 * 2^6)
+    v = [1.0] + [0.0] * 15
+    E, d = R.bfp_pack_block([f2b(x) for x in v], 7)
+    assert E == 127 and d[0] == 0x40 and not d[1:].any()
+    # equal exponents: 1.0, -1.5, 1.984375 (= 127/64), 1.9999 (rounds up to 128 -> saturates to 127)
+    v = [1.0, -1.5, 1.984375, 1.9999] + [0.0] * 12
+    E, d = R.bfp_pack_block([f2b(x) for x in v], 7)
+    assert E == 127 and list(d[:4]) == [0x40, 0x80 | 0x60, 0x7F, 0x7F]
+    # an outlier x1000 flattens the rest: 1000 = 1.953125 * 2^9 -> E = 136; 1.0 * 2^6 / 2^9 = 0.125 -> 0
+    v = [1000.0, 1.0, 4.0, -8.0, 12.0] + [0.0] * 11
+    E, d = R.bfp_pack_block([f2b(x) for x in v], 7)
+    assert E == 136
+    assert d[0] == 125            # 1000 / 2^9 * 64 = 125
+    assert d[1] == 0              # 0.125 rounds to 0 (and loses its sign slot)
+    assert d[2] == 0              # 4 / 512 * 64 = 0.5: tie, rounds to even 0
+    assert d[3] == 0x80 | 1       # 8 / 512 * 64 = 1.0, negative
+    assert d[4] == 2              # 12 / 512 * 64 = 1.5: tie, rounds to even 2
+    # denormal input flushes; -0.0 stores +0
+    v = [1e-40, -0.0, 2.0 ** -126] + [0.0] * 13
+    E, d = R.bfp_pack_block([f2b(x) for x in v], 7)
+    assert E == 1 and list(d[:3]) == [0, 0, 0x40]
+    # Inf / NaN take the largest magnitude and keep their sign; finite values vanish next to them
+    v = [float("inf"), float("-inf"), float("nan"), 3.0e38] + [0.0] * 12
+    E, d = R.bfp_pack_block([f2b(x) for x in v], 7)
+    assert E == 255 and list(d[:3]) == [0x7F, 0xFF, 0x7F]
+    assert d[3] == 56  # 3e38 = 1.7632 * 2^127: 1.7632 * 64 / 2 = 56.4
+
+
+def test_bfp4_bfp2_sub_byte_order(oracle):
+    R = oracle
+    v = [1.0, -1.0, 0.5, 0.25] + [0.0] * 12
+    E, d = R.bfp_pack_block([f2b(x) for x in v], 3)
+    # datums: 1.0 -> 4, -1.0 -> 8|4, 0.5 -> 2, 0.25 -> 1; datum 0 in the low nibble
+    assert E == 127 and d[0] == (0xC << 4 | 0x4) and d[1] == (0x1 << 4 | 0x2)
+    E, d = R.bfp_pack_block([f2b(x) for x in v], 1)
+    # one magnitude bit: 1.0 -> 1, -1.0 -> 2|1, 0.5 -> tie 0.5 -> even 0, 0.25 -> 0
+    assert E == 127 and d[0] == (0b11 << 2 | 0b01)
+
+
+@pytest.mark.parametrize("m", [7, 3, 1])
+def test_bfp_oracle_matches_rational_spec(oracle, m):
+    rng = np.random.default_rng(100 + m)
+    for trial in range(300):
+        kind = trial % 6
+        if kind == 0:
+            x = rng.standard_normal(16).astype(np.float32)
+        elif kind == 1:
+            x = (rng.standard_normal(16) * 10.0 ** rng.integers(-30, 30, 16)).astype(np.float32)
+        elif kind == 2:   # exact ties: small integers against a large power of two
+            x = (rng.integers(-9, 10, 16) * 0.5).astype(np.float32)
+            x[0] = 64.0
+        elif kind == 3:   # raw bit patterns: denormals, NaN, Inf included
+            x = rng.integers(0, 2 ** 32, 16, dtype=np.uint64).astype(np.uint32).view(np.float32)
+        elif kind == 4:   # tiny blocks (shared exponent below the mantissa width)
+            x = (rng.standard_normal(16) * 2.0 ** -124).astype(np.float32)
+        else:             # huge blocks
+            x = (rng.standard_normal(16) * 2.0 ** 126).astype(np.float32)
+        bits = x.view(np.uint32)
+        E, d = oracle.bfp_pack_block(bits, m)
+        E2, d2 = spec_encode_block([int(b) for b in bits], m)
+        assert E == E2 and np.array_equal(d, d2), (trial, x)
+        # decode: q * 2^(E-127-(m-1)), exact
+        y = oracle.bfp_unpack_block(E, d, m)
+        w = m + 1
+        word = int.from_bytes(d.tobytes(), "little")
+        for i in range(16):
+            dat = (word >> (w * i)) & ((1 << w) - 1)
+            q, s = dat & ((1 << m) - 1), dat >> m
+            with np.errstate(over="ignore"):
+                want = np.float32(math.ldexp(q, E - 127 - (m - 1))) if q else np.float32(0.0)
+            want = -want if (s and q) else want
+            assert y[i].view(np.uint32) == np.float32(want).view(np.uint32)
+
+
+@pytest.mark.parametrize("df_name", ["Bfp8_b", "Bfp4_b", "Bfp2_b"])
+def test_pack_is_idempotent_and_sized(oracle, df_name):
+    R = oracle
+    df = getattr(R, df_name)
+    x = np.random.default_rng(7).standard_normal((2, 3, 64, 96)).astype(np.float32)
+    g = R.Geom.for_shape(x.shape, grid=(2, 1), ublock=(1, 3), ublock_order=1)
+    for hdr in (False, True):
+        img = R.tilize_pack(x, df, geom=g, with_header=hdr)
+        assert img.size == 2 * 3 * 2 * 3 * R.tile_bytes(df, hdr)
+        y = R.unpack_untilize(img, df, x.shape, geom=g, with_header=hdr)
+        assert np.array_equal(R.tilize_pack(y, df, geom=g, with_header=hdr), img)
+    # bfloat16 source = same bytes as its widened binary32
+    xb = (x.view(np.uint32) >> 16).astype(np.uint16)
+    xw = (xb.astype(np.uint32) << 16).view(np.float32)
+    assert np.array_equal(R.tilize_pack(xb, df, src_df=R.Float16_b), R.tilize_pack(xw, df))
+
+
+def test_face_order_and_plain_layout(oracle):
+    R = oracle
+    x = np.arange(32 * 32, dtype=np.float32).reshape(1, 1, 32, 32)
+    img = R.tilize_pack(x, R.Float32).view(np.float32)
+    # F0 = rows 0-15 x cols 0-15, F1 = rows 0-15 x cols 16-31, F2 = rows 16-31 x cols 0-15, F3
+    assert np.array_equal(img[:256].reshape(16, 16), x[0, 0, :16, :16])
+    assert np.array_equal(img[256:512].reshape(16, 16), x[0, 0, :16, 16:])
+    assert np.array_equal(img[512:768].reshape(16, 16), x[0, 0, 16:, :16])
+    assert np.array_equal(img[768:].reshape(16, 16), x[0, 0, 16:, 16:])
+    for dt, df in ((np.int8, R.Int8), (np.int32, R.Int32), (np.float16, R.Float16)):
+        a = np.random.default_rng(1).integers(-100, 100, (1, 2, 64, 64)).astype(dt)
+        assert np.array_equal(R.unpack_untilize(R.tilize_pack(a, df), df, a.shape, dst_dtype=dt), a)
+
+
+def test_config1_size(oracle):
+    R = oracle
+    # [1,1,1024,1024] -> 1024 tiles -> 1,114,112 bytes of Bfp8_b
+    g = R.Geom.for_shape([1, 1, 1024, 1024])
+    n = R.lib().ref_tilized_bytes(g, (np.ctypeslib.ctypes.c_uint32 * 4)(1, 1, 1024, 1024), R.Bfp8_b, 0)
+    assert n == 1114112

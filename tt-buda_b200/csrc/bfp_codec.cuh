@@ -1,0 +1,175 @@
+// Block-float (Bfp8_b / Bfp4_b / Bfp2_b) encode and decode of one 16-value block in registers.
+//
+// Format (published description: docs/public/dataformats.rst:59-89 of the reference, drawings
+// docs/public/images/bfp{8,4,2}_blocks.png): the 16 values of a block share one 8-bit exponent E,
+// the largest biased binary32 exponent in the block; a datum is sign + M magnitude bits
+// (M = 7 / 3 / 1) with no implied one:  q = round(|x| * 2^(M-1) / 2^(E-127)).
+// Choices the description leaves open, frozen here and in the CPU oracle alike:
+//   round to nearest, ties to even; a round-up past 2^M-1 saturates (E is not bumped);
+//   zero / denormal inputs encode as 0; Inf / NaN encode the largest magnitude;
+//   a zero magnitude is stored with sign 0; datum i sits in bits [i*(M+1), (i+1)*(M+1)) of the
+//   block's little-endian bit string;  q == 0 decodes to +0.0.
+//
+// The encoder is a floating-point formulation: one fused multiply-add per value computes
+// |x| * 2^(M-1+127-E) + 1.5*2^23, whose single rounding IS round-to-nearest-even at integer
+// granularity, leaving q in the low mantissa byte; flush-to-zero on the inputs gives the denormal
+// policy for free.  Blocks whose scale 2^(M-1+127-E) is not a normal binary32 (E < M-1, or
+// E > M+252) take an integer path instead.
+#pragma once
+
+#include <stdint.h>
+
+namespace buda {
+
+constexpr uint32_t kMagicBits = 0x4b400000u;  // 1.5 * 2^23: ulp 1, even
+
+template <int M>
+struct BfpTraits {
+    static constexpr uint32_t qmax = (1u << M) - 1u;
+    static constexpr int words = 16 * (M + 1) / 32;  // 32-bit words of mantissa data per block: 4 / 2 / 1
+    static constexpr int bytes = 16 * (M + 1) / 8;   // 16 / 8 / 4
+};
+
+// Integer encoder of one value (used for blocks at the ends of the exponent range).
+__device__ __forceinline__ uint32_t bfp_encode_datum_int(uint32_t bits, uint32_t E, int m)
+{
+    const uint32_t qmax = (1u << m) - 1u;
+    uint32_t e = (bits >> 23) & 0xffu, q;
+    if (e == 0) {
+        q = 0;
+    } else if (e == 255) {
+        q = qmax;
+    } else {
+        uint32_t sig = (bits & 0x7fffffu) | 0x800000u;
+        uint32_t shift = E - e + 24u - (uint32_t)m;
+        if (shift > 25u) {
+            q = 0;
+        } else {
+            uint32_t kept = sig >> shift, rem = sig & ((1u << shift) - 1u), half = 1u << (shift - 1u);
+            kept += (rem > half || (rem == half && (kept & 1u))) ? 1u : 0u;
+            q = kept < qmax ? kept : qmax;
+        }
+    }
+    return q ? (((bits >> 31) << m) | q) : 0u;
+}
+
+// Encode one block.  x: the 16 values as binary32 bit patterns.  Returns the shared exponent and
+// the packed datums (out[0] holds datums 0.., little-endian).
+template <int M>
+__device__ __forceinline__ void bfp_encode16(const uint32_t (&x)[16], uint32_t &E_out,
+                                             uint32_t (&out)[BfpTraits<M>::words])
+{
+    constexpr uint32_t qmax = BfpTraits<M>::qmax;
+    uint32_t a[16];
+    uint32_t maxa = 0;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        a[i] = x[i] & 0x7fffffffu;
+        maxa = max(maxa, a[i]);
+    }
+    const uint32_t E = maxa >> 23;  // the magnitude with the largest exponent also has the largest bits
+    E_out = E;
+
+    if (E + 1u >= (uint32_t)M && E <= (uint32_t)(M + 252)) {
+        const float S = __uint_as_float((uint32_t)(M + 253 - (int)E) << 23);  // 2^(M-1+127-E)
+        uint32_t y[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            float r;
+            asm("fma.rn.ftz.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(__uint_as_float(a[i])), "f"(S), "f"(12582912.0f));
+            y[i] = min(__float_as_uint(r), kMagicBits + qmax);  // Inf / NaN and round-ups saturate here
+        }
+        uint32_t D[4];
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            // Q: the four magnitudes, one per byte.  T: the four sign-carrying top bytes.
+            uint32_t Q = __byte_perm(__byte_perm(y[4 * w], y[4 * w + 1], 0x0040),
+                                     __byte_perm(y[4 * w + 2], y[4 * w + 3], 0x0040), 0x5410);
+            uint32_t T = __byte_perm(__byte_perm(x[4 * w], x[4 * w + 1], 0x0073),
+                                     __byte_perm(x[4 * w + 2], x[4 * w + 3], 0x0073), 0x5410);
+            if (M == 7) {
+                uint32_t nz = (Q + 0x7f7f7f7fu) & 0x80808080u;  // bit 7 of a byte set iff its q > 0
+                D[w] = Q | (T & nz);
+            } else if (M == 3) {
+                uint32_t nz = (Q + 0x07070707u) & 0x08080808u;
+                D[w] = Q | ((T >> 4) & nz);
+            } else {
+                uint32_t nz = (Q + 0x01010101u) & 0x02020202u;
+                D[w] = Q | ((T >> 6) & nz);
+            }
+        }
+        if (M == 7) {
+#pragma unroll
+            for (int w = 0; w < 4; w++) out[w % BfpTraits<M>::words] = D[w];
+        } else if (M == 3) {
+            // two 4-bit datums per byte: bytes 0 and 2 of (D | D >> 4)
+            uint32_t t0 = D[0] | (D[0] >> 4), t1 = D[1] | (D[1] >> 4);
+            uint32_t t2 = D[2] | (D[2] >> 4), t3 = D[3] | (D[3] >> 4);
+            out[0] = __byte_perm(t0, t1, 0x6420);
+            out[1 % BfpTraits<M>::words] = __byte_perm(t2, t3, 0x6420);
+        } else {
+            // four 2-bit datums per byte: byte 0 of u, u = t | t >> 12, t = D | D >> 6
+            uint32_t u[4];
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                uint32_t t = D[w] | (D[w] >> 6);
+                u[w] = t | (t >> 12);
+            }
+            out[0] = __byte_perm(__byte_perm(u[0], u[1], 0x0040), __byte_perm(u[2], u[3], 0x0040), 0x5410);
+        }
+    } else {
+#pragma unroll
+        for (int w = 0; w < BfpTraits<M>::words; w++) out[w] = 0;
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            uint32_t d = bfp_encode_datum_int(x[i], E, M);
+            out[(i * (M + 1)) / 32] |= d << ((i * (M + 1)) % 32);
+        }
+    }
+}
+
+// Scale of a block: 2^(E - 127 - (M-1)) as a binary32 (denormal when needed).  For M == 1 and
+// E == 255 the scale 2^128 is not representable: the caller multiplies by `post` (2.0) as well.
+template <int M>
+__device__ __forceinline__ float bfp_block_scale(uint32_t E, float &post)
+{
+    int k = (int)E - 127 - (M - 1);
+    post = 1.0f;
+    if (k > 127) {
+        post = 2.0f;
+        k = 127;
+    }
+    if (k >= -126) return __uint_as_float((uint32_t)(k + 127) << 23);
+    return __uint_as_float(1u << (k + 149));
+}
+
+// Decode one block to 16 binary32 values (exact; overflow gives infinity).
+template <int M>
+__device__ __forceinline__ void bfp_decode16(uint32_t E, const uint32_t (&in)[BfpTraits<M>::words], float (&v)[16])
+{
+    float post;
+    const float sc = bfp_block_scale<M>(E, post);
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        uint32_t q, signbit;
+        if (M == 7) {
+            const uint32_t w = in[(i / 4) % BfpTraits<M>::words];
+            const int j = i % 4;
+            // magnitude byte j spliced under the upper three bytes of the magic constant
+            q = __byte_perm(w & 0x7f7f7f7fu, kMagicBits, 0x7650 + j);
+            signbit = (w << (24 - 8 * j)) & 0x80000000u;
+        } else {
+            const uint32_t w = in[((i * (M + 1)) / 32) % BfpTraits<M>::words];
+            const int sh = (i * (M + 1)) % 32;
+            const uint32_t d = w >> sh;
+            q = kMagicBits | (d & BfpTraits<M>::qmax);
+            signbit = (d << (31 - M)) & 0x80000000u;
+        }
+        float mag = __fmul_rn(__fadd_rn(__uint_as_float(q), -12582912.0f), sc);
+        if (M == 1) mag = __fmul_rn(mag, post);
+        // (+-0) + (+0) = +0: a zero magnitude decodes to +0.0 whatever its sign bit says
+        v[i] = __fadd_rn(__uint_as_float(__float_as_uint(mag) | signbit), 0.0f);
+    }
+}
+
+}  // namespace buda

@@ -1,0 +1,217 @@
+// Shared device/host helpers for the sm_100a data-format kernels: data-format tables, the tile
+// order of a queue, mbarrier + bulk-copy (TMA) wrappers with BOUNDED waits, and the device status
+// word that records a wait that gave up.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/buda_cuda.h"
+
+namespace buda {
+
+// ------------------------------------------------------------------------------------------------
+// Data formats (values: reference enum DataFormat, pybuda/csrc/lower_to_buda/common.hpp:92-111)
+// ------------------------------------------------------------------------------------------------
+__host__ __device__ inline int bfp_mant_bits(int df)
+{
+    switch (df) {
+        case BUDA_DF_Bfp8_b: case BUDA_DF_Bfp8: return 7;
+        case BUDA_DF_Bfp4_b: case BUDA_DF_Bfp4: return 3;
+        case BUDA_DF_Bfp2_b: case BUDA_DF_Bfp2: return 1;
+        default: return 0;
+    }
+}
+
+__host__ __device__ inline int plain_elem_bytes(int df)
+{
+    switch (df) {
+        case BUDA_DF_Float32: case BUDA_DF_Int32: case BUDA_DF_RawUInt32: return 4;
+        case BUDA_DF_Float16: case BUDA_DF_Float16_b: case BUDA_DF_UInt16: case BUDA_DF_RawUInt16: return 2;
+        case BUDA_DF_Lf8: case BUDA_DF_Int8: case BUDA_DF_RawUInt8: return 1;
+        default: return 0;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Launch-time description of one tilize/untilize job (uniform over a batch of tensors)
+// ------------------------------------------------------------------------------------------------
+constexpr int kMaxBatch = 64;    // tensors per launch (pointer table lives in kernel parameters)
+constexpr int kBoxTiles = 4;     // a work item is a 32-row band of up to 4 tiles (128 columns)
+
+struct TileJob {
+    // row-major side
+    uint32_t W, Z, Rt, Ct;              // entries, t, tile rows, tile columns
+    uint64_t stride_w, stride_z, stride_r;  // bytes
+    uint32_t boxes_per_band;            // ceil(Ct / kBoxTiles)
+    uint32_t total_items;               // batch * W * Z * Rt * boxes_per_band  (< 2^31)
+    uint32_t items_per_tensor;
+    // queue side
+    buda_queue_geom g;
+    uint32_t tile_bytes;                // record size including the optional header
+    uint32_t header_bytes;              // 0 or 32
+    uint64_t tiles_per_entry;           // per grid core
+    uint64_t buf_bytes;                 // bytes of one grid core's buffer (all W entries)
+    int trivial_geom;                   // grid 1x1, ublock 1x1, order R: address = (z*Rt + rt)*Ct + ct
+};
+
+struct PtrTable {
+    const uint8_t *src[kMaxBatch];
+    uint8_t *dst[kMaxBatch];
+};
+
+// Tile (z, rt, ct) of entry w -> byte offset of its record inside the queue image.
+// Restates TileLayout::map (pybuda/csrc/balancer/types.cpp:629-648): the grid core owning the
+// tile, then t-major, macro-block scan in ublock order, row-major inside the ublock.
+__host__ __device__ inline uint64_t tile_record_offset(const TileJob &j, uint32_t w, uint32_t z, uint32_t rt,
+                                                       uint32_t ct)
+{
+    if (j.trivial_geom) {
+        uint64_t addr = ((uint64_t)z * j.Rt + rt) * j.Ct + ct;
+        return ((uint64_t)w * j.tiles_per_entry + addr) * j.tile_bytes;
+    }
+    const buda_queue_geom &g = j.g;
+    uint32_t block_rt = g.mblock_m * g.ublock_rt, block_ct = g.mblock_n * g.ublock_ct;
+    uint32_t core_r = rt / block_rt, core_c = ct / block_ct;
+    uint32_t u_r = rt % g.ublock_rt, u_c = ct % g.ublock_ct;
+    uint32_t m = (rt / g.ublock_rt) % g.mblock_m, n = (ct / g.ublock_ct) % g.mblock_n;
+    uint64_t uvol = (uint64_t)g.ublock_rt * g.ublock_ct;
+    uint64_t mvol = (uint64_t)g.mblock_m * g.mblock_n * uvol;
+    uint64_t mlin = (g.ublock_order == 0 ? (uint64_t)m * g.mblock_n + n : (uint64_t)n * g.mblock_m + m) * uvol;
+    uint64_t addr = (uint64_t)z * mvol + mlin + (uint64_t)u_r * g.ublock_ct + u_c;
+    uint64_t core = (uint64_t)core_r * g.grid_c + core_c;
+    return core * j.buf_bytes + ((uint64_t)w * j.tiles_per_entry + addr) * j.tile_bytes;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Device status word: set by a bounded wait that gave up, read (and cleared) by
+// buda_device_status().  One word per device that loads the library; kernels receive its address.
+// ------------------------------------------------------------------------------------------------
+#ifdef __CUDACC__
+__device__ __forceinline__ void report_status(unsigned int *status, unsigned int code)
+{
+    atomicCAS(status, 0u, code);
+}
+
+// ------------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_fence_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Longest time any single wait may take before the kernel gives up (a healthy wait is microseconds).
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+// Bounded wait on an mbarrier phase.  Returns false if the wait gave up (after recording `code`
+// in the device status word and raising *abort_flag so every other wait in the CTA ends at once).
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                                  unsigned int *status, unsigned int code)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    uint64_t t0 = global_timer_ns();
+    uint32_t spins = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 0xffu) == 0) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                report_status(status, code);
+                return false;
+            }
+        }
+    }
+}
+
+// 1-D bulk async copy (TMA engine) global -> shared, completion counted on an mbarrier.
+// Both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar)
+{
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// 1-D bulk async copy shared -> global, tracked by the issuing thread's bulk group.
+__device__ __forceinline__ void bulk_s2g(void *gdst, const void *smem_src, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst),
+                 "r"(smem_u32(smem_src)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+
+// all of this thread's bulk stores have finished READING shared memory
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
+// all of this thread's bulk stores are complete
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// order this thread's generic-proxy shared-memory writes before later async-proxy (bulk copy) reads
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+// Barrier over `threads` threads that also ORs a predicate across them: every participant learns
+// whether any of them gave up, so they all leave a loop together and nobody waits alone.
+__device__ __forceinline__ bool named_bar_or(int id, int threads, bool pred)
+{
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.or.pred p, %2, %3, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"((uint32_t)pred), "r"(id), "r"(threads)
+        : "memory");
+    return r != 0;
+}
+#endif  // __CUDACC__
+
+}  // namespace buda

@@ -1,0 +1,717 @@
+// C ABI of libbuda_cuda.so (declared in include/buda_cuda.h): argument checking, job set-up,
+// kernel selection, the host-buffer pipelines, error text and the device status word.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "buda_common.cuh"
+
+namespace buda {
+cudaError_t launch_tilize(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int path,
+                          int vec_ok, int sm_count, cudaStream_t stream, unsigned int *status);
+cudaError_t launch_untilize(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int path,
+                            int vec_ok, int sm_count, cudaStream_t stream, unsigned int *status);
+cudaError_t launch_quantize(const float *x, int64_t n, const float *scale, int64_t scale_len, int64_t inner, float zp,
+                            int mode, float lo, float hi, int8_t *out, int sm_count, cudaStream_t stream);
+cudaError_t launch_dequantize(const int8_t *x, int64_t n, const float *scale, int64_t scale_len, int64_t inner, float zp,
+                              float *out, int sm_count, cudaStream_t stream);
+cudaError_t launch_requantize(const int32_t *x, int64_t n, const float *scale_a, const float *scale_b, int64_t scale_len,
+                              int64_t inner, float zp, int mode, float lo, float hi, int8_t *out, int sm_count,
+                              cudaStream_t stream);
+cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W, int64_t N, void *C,
+                              int64_t ldc, int sm_count, cudaStream_t stream, unsigned int *status, char *err,
+                              size_t err_len);
+
+// One status word per device that loads the library; kernels get its device address.
+__device__ unsigned int g_device_status = 0;
+}  // namespace buda
+
+using namespace buda;
+
+namespace {
+
+thread_local char t_err[512] = "";
+std::atomic<uint64_t> g_launches{0};
+
+int fail(int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_err, sizeof(t_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char *what)
+{
+    return fail(BUDA_RUNTIME_ERROR, "%s: %s", what, cudaGetErrorString(e));
+}
+
+constexpr int kMaxDevices = 64;
+constexpr int kPipeDepth = 4;
+
+struct DevCtx {
+    std::once_flag once;
+    cudaError_t init_err = cudaSuccess;
+    int sm_count = 0;
+    unsigned int *status = nullptr;
+    // host-buffer pipeline resources (guarded by host_mu)
+    std::mutex host_mu;
+    cudaStream_t s_in = nullptr, s_out = nullptr, s_comp = nullptr;
+    cudaEvent_t ev_in[kPipeDepth] = {}, ev_comp[kPipeDepth] = {}, ev_out[kPipeDepth] = {};
+    uint8_t *stage_a[kPipeDepth] = {};  // row-major side
+    uint8_t *stage_b[kPipeDepth] = {};  // queue-image side
+    size_t cap_a = 0, cap_b = 0;
+    bool pipe_ready = false;
+};
+
+DevCtx g_ctx[kMaxDevices];
+
+int get_ctx(DevCtx **out)
+{
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "no usable CUDA device (this library has no CPU path)");
+    if (dev < 0 || dev >= kMaxDevices) return fail(BUDA_RUNTIME_ERROR, "device ordinal %d out of range", dev);
+    DevCtx &c = g_ctx[dev];
+    std::call_once(c.once, [&]() {
+        cudaError_t r = cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (r == cudaSuccess) r = cudaGetSymbolAddress((void **)&c.status, g_device_status);
+        c.init_err = r;
+    });
+    if (c.init_err != cudaSuccess) return cuda_fail(c.init_err, "device set-up failed");
+    *out = &c;
+    return BUDA_SUCCESS;
+}
+
+bool is_bfp_b(int df) { return df == BUDA_DF_Bfp8_b || df == BUDA_DF_Bfp4_b || df == BUDA_DF_Bfp2_b; }
+
+// Fills the job for a [w,z,R,C] tensor in a queue of geometry g holding format qdf.
+int make_job(const uint32_t shape[4], const uint64_t strides[4], const buda_queue_geom *g, int qdf, int with_header,
+             int batch, TileJob &j)
+{
+    if (!shape || !strides || !g) return fail(BUDA_RUNTIME_ERROR, "null shape / strides / geometry");
+    const int64_t tb = buda_tile_bytes(qdf, with_header);
+    if (tb < 0) return fail(BUDA_RUNTIME_ERROR, "unsupported queue data format %d", qdf);
+    if (shape[2] == 0 || shape[3] == 0 || shape[0] == 0 || shape[1] == 0)
+        return fail(BUDA_RUNTIME_ERROR, "empty tensor [%u,%u,%u,%u]", shape[0], shape[1], shape[2], shape[3]);
+    if (shape[2] % 32 || shape[3] % 32)
+        return fail(BUDA_RUNTIME_ERROR, "rows and columns must be multiples of the 32x32 tile, got [%u,%u]", shape[2],
+                    shape[3]);
+    if (!g->grid_r || !g->grid_c || !g->mblock_m || !g->mblock_n || !g->ublock_rt || !g->ublock_ct || !g->t ||
+        g->ublock_order > 1)
+        return fail(BUDA_RUNTIME_ERROR, "invalid queue geometry");
+    if (g->t != shape[1]) return fail(BUDA_RUNTIME_ERROR, "queue t=%u does not match tensor z=%u", g->t, shape[1]);
+    if ((uint64_t)g->grid_r * g->mblock_m * g->ublock_rt * 32u != shape[2] ||
+        (uint64_t)g->grid_c * g->mblock_n * g->ublock_ct * 32u != shape[3])
+        return fail(BUDA_RUNTIME_ERROR, "queue geometry covers %llux%llu, tensor is %ux%u",
+                    (unsigned long long)g->grid_r * g->mblock_m * g->ublock_rt * 32u,
+                    (unsigned long long)g->grid_c * g->mblock_n * g->ublock_ct * 32u, shape[2], shape[3]);
+    j.W = shape[0]; j.Z = shape[1]; j.Rt = shape[2] / 32; j.Ct = shape[3] / 32;
+    j.stride_w = strides[0]; j.stride_z = strides[1]; j.stride_r = strides[2];
+    j.boxes_per_band = (j.Ct + kBoxTiles - 1) / kBoxTiles;
+    const uint64_t items_per_tensor = (uint64_t)j.W * j.Z * j.Rt * j.boxes_per_band;
+    if (items_per_tensor * (uint64_t)batch >= (1ull << 31))
+        return fail(BUDA_RUNTIME_ERROR, "too many tile bands in one launch (%llu); split the batch",
+                    (unsigned long long)(items_per_tensor * batch));
+    j.items_per_tensor = (uint32_t)items_per_tensor;
+    j.total_items = (uint32_t)(items_per_tensor * batch);
+    j.g = *g;
+    j.tile_bytes = (uint32_t)tb;
+    j.header_bytes = with_header ? 32u : 0u;
+    j.tiles_per_entry = (uint64_t)g->t * g->mblock_m * g->mblock_n * g->ublock_rt * g->ublock_ct;
+    j.buf_bytes = (uint64_t)j.W * j.tiles_per_entry * j.tile_bytes;
+    j.trivial_geom = (g->grid_r == 1 && g->grid_c == 1 && g->ublock_rt == 1 && g->ublock_ct == 1 && g->ublock_order == 0);
+    return BUDA_SUCCESS;
+}
+
+// Which conversion a (row-major format, queue format) pair asks for.  mant = 7/3/1 for a Bfp
+// pack/unpack, 0 for a plain relayout; es = element bytes on the row-major side.
+int classify(int rm_df, int q_df, int &mant, int &es)
+{
+    if (is_bfp_b(q_df)) {
+        if (rm_df != BUDA_DF_Float32 && rm_df != BUDA_DF_Float16_b)
+            return fail(BUDA_RUNTIME_ERROR, "Bfp*_b queues convert from/to Float32 or Float16_b, not format %d", rm_df);
+        mant = bfp_mant_bits(q_df);
+        es = rm_df == BUDA_DF_Float32 ? 4 : 2;
+        return BUDA_SUCCESS;
+    }
+    if (bfp_mant_bits(q_df))
+        return fail(BUDA_RUNTIME_ERROR, "Bfp 'a' formats (5-bit shared exponent) are not implemented");
+    es = plain_elem_bytes(q_df);
+    if (es == 0) return fail(BUDA_RUNTIME_ERROR, "unsupported queue data format %d", q_df);
+    if (plain_elem_bytes(rm_df) != es)
+        return fail(BUDA_RUNTIME_ERROR, "plain tilize keeps the element width: format %d vs queue format %d", rm_df, q_df);
+    mant = 0;
+    return BUDA_SUCCESS;
+}
+
+inline bool aligned16(uint64_t v) { return (v & 15u) == 0; }
+
+// The staged (bulk-copy) kernels need every row start 16-byte aligned on both sides; the direct
+// kernels use 4-element vector accesses when rows are aligned to 4 elements.
+void pick_path(const TileJob &j, const PtrTable &p, int batch, int es, int &path, int &vec_ok)
+{
+    const uint64_t valign = 4u * (uint64_t)es - 1u;
+    uint64_t bits = j.stride_w | j.stride_z | j.stride_r;
+    for (int b = 0; b < batch; b++) bits |= (uint64_t)p.src[b] | (uint64_t)p.dst[b];
+    path = (bits & 15u) == 0 ? 0 : 1;
+    vec_ok = (bits & valign) == 0 ? 1 : 0;
+}
+
+int check_queue_ptrs_aligned(const void *const *q, int n)
+{
+    for (int b = 0; b < n; b++)
+        if (!aligned16((uint64_t)q[b])) return fail(BUDA_RUNTIME_ERROR, "queue image pointers must be 16-byte aligned");
+    return BUDA_SUCCESS;
+}
+
+int tilize_device(int n, const void *const *srcs, int src_df, const uint32_t shape[4], const uint64_t strides[4],
+                  const buda_queue_geom *geom, int dst_df, int with_header, void *const *dsts, uint64_t dst_bytes_each,
+                  cudaStream_t stream, int force_path)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    if (n <= 0) return BUDA_SUCCESS;
+    if (!srcs || !dsts) return fail(BUDA_RUNTIME_ERROR, "null pointer table");
+    int mant, es;
+    if (int rc = classify(src_df, dst_df, mant, es)) return rc;
+    if (strides && strides[3] != (uint64_t)es)
+        return fail(BUDA_RUNTIME_ERROR, "innermost stride must equal the element size (%d), got %llu", es,
+                    (unsigned long long)strides[3]);
+    if (int rc = check_queue_ptrs_aligned(dsts, n)) return rc;
+    for (int b0 = 0; b0 < n; b0 += kMaxBatch) {
+        const int nb = (n - b0 < kMaxBatch) ? (n - b0) : kMaxBatch;
+        TileJob job;
+        if (int rc = make_job(shape, strides, geom, dst_df, with_header, nb, job)) return rc;
+        const uint64_t need = job.buf_bytes * geom->grid_r * geom->grid_c;
+        if (dst_bytes_each < need)
+            return fail(BUDA_RUNTIME_ERROR, "destination holds %llu bytes, the queue image needs %llu",
+                        (unsigned long long)dst_bytes_each, (unsigned long long)need);
+        PtrTable pt;
+        memset(&pt, 0, sizeof(pt));
+        for (int b = 0; b < nb; b++) {
+            if (!srcs[b0 + b] || !dsts[b0 + b]) return fail(BUDA_RUNTIME_ERROR, "null tensor pointer in batch");
+            pt.src[b] = (const uint8_t *)srcs[b0 + b];
+            pt.dst[b] = (uint8_t *)dsts[b0 + b];
+        }
+        int path, vec_ok;
+        pick_path(job, pt, nb, es, path, vec_ok);
+        if (force_path >= 0) {
+            if (force_path == 0 && path != 0) return fail(BUDA_RUNTIME_ERROR, "staged path needs 16-byte aligned rows");
+            path = force_path;
+        }
+        cudaError_t e = launch_tilize(job, pt, nb, mant, es, path, vec_ok, ctx->sm_count, stream, ctx->status);
+        if (e != cudaSuccess) return cuda_fail(e, "tilize launch failed");
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+    }
+    return BUDA_SUCCESS;
+}
+
+int untilize_device(int n, const void *const *srcs, int src_df, int with_header, const buda_queue_geom *geom,
+                    void *const *dsts, int dst_df, const uint32_t shape[4], const uint64_t strides[4], cudaStream_t stream,
+                    int force_path)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    if (n <= 0) return BUDA_SUCCESS;
+    if (!srcs || !dsts) return fail(BUDA_RUNTIME_ERROR, "null pointer table");
+    int mant, es;
+    if (int rc = classify(dst_df, src_df, mant, es)) return rc;
+    if (strides && strides[3] != (uint64_t)es)
+        return fail(BUDA_RUNTIME_ERROR, "innermost stride must equal the element size (%d), got %llu", es,
+                    (unsigned long long)strides[3]);
+    if (int rc = check_queue_ptrs_aligned(srcs, n)) return rc;
+    for (int b0 = 0; b0 < n; b0 += kMaxBatch) {
+        const int nb = (n - b0 < kMaxBatch) ? (n - b0) : kMaxBatch;
+        TileJob job;
+        if (int rc = make_job(shape, strides, geom, src_df, with_header, nb, job)) return rc;
+        PtrTable pt;
+        memset(&pt, 0, sizeof(pt));
+        for (int b = 0; b < nb; b++) {
+            if (!srcs[b0 + b] || !dsts[b0 + b]) return fail(BUDA_RUNTIME_ERROR, "null tensor pointer in batch");
+            pt.src[b] = (const uint8_t *)srcs[b0 + b];
+            pt.dst[b] = (uint8_t *)dsts[b0 + b];
+        }
+        int path, vec_ok;
+        pick_path(job, pt, nb, es, path, vec_ok);
+        if (force_path >= 0) {
+            if (force_path == 0 && path != 0) return fail(BUDA_RUNTIME_ERROR, "staged path needs 16-byte aligned rows");
+            path = force_path;
+        }
+        cudaError_t e = launch_untilize(job, pt, nb, mant, es, path, vec_ok, ctx->sm_count, stream, ctx->status);
+        if (e != cudaSuccess) return cuda_fail(e, "untilize launch failed");
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+    }
+    return BUDA_SUCCESS;
+}
+
+// ------------------------------------------------------------------------------------------------
+// host-buffer pipeline: the tensor moves in slices of whole tile-row bands through kPipeDepth
+// staging slots; copy-in, kernel and copy-out of different slices run on three streams.
+// ------------------------------------------------------------------------------------------------
+int ensure_pipe(DevCtx *c, size_t need_a, size_t need_b)
+{
+    if (!c->pipe_ready) {
+        cudaError_t e;
+        if ((e = cudaStreamCreateWithFlags(&c->s_in, cudaStreamNonBlocking)) != cudaSuccess) return cuda_fail(e, "stream");
+        if ((e = cudaStreamCreateWithFlags(&c->s_out, cudaStreamNonBlocking)) != cudaSuccess) return cuda_fail(e, "stream");
+        if ((e = cudaStreamCreateWithFlags(&c->s_comp, cudaStreamNonBlocking)) != cudaSuccess) return cuda_fail(e, "stream");
+        for (int i = 0; i < kPipeDepth; i++) {
+            if ((e = cudaEventCreateWithFlags(&c->ev_in[i], cudaEventDisableTiming)) != cudaSuccess) return cuda_fail(e, "event");
+            if ((e = cudaEventCreateWithFlags(&c->ev_comp[i], cudaEventDisableTiming)) != cudaSuccess) return cuda_fail(e, "event");
+            if ((e = cudaEventCreateWithFlags(&c->ev_out[i], cudaEventDisableTiming)) != cudaSuccess) return cuda_fail(e, "event");
+        }
+        c->pipe_ready = true;
+    }
+    if (need_a > c->cap_a) {
+        for (int i = 0; i < kPipeDepth; i++) {
+            if (c->stage_a[i]) cudaFree(c->stage_a[i]);
+            c->stage_a[i] = nullptr;
+            cudaError_t e = cudaMalloc((void **)&c->stage_a[i], need_a);
+            if (e != cudaSuccess) { c->cap_a = 0; return cuda_fail(e, "staging allocation"); }
+        }
+        c->cap_a = need_a;
+    }
+    if (need_b > c->cap_b) {
+        for (int i = 0; i < kPipeDepth; i++) {
+            if (c->stage_b[i]) cudaFree(c->stage_b[i]);
+            c->stage_b[i] = nullptr;
+            cudaError_t e = cudaMalloc((void **)&c->stage_b[i], need_b);
+            if (e != cudaSuccess) { c->cap_b = 0; return cuda_fail(e, "staging allocation"); }
+        }
+        c->cap_b = need_b;
+    }
+    return BUDA_SUCCESS;
+}
+
+constexpr uint64_t kSliceTargetBytes = 8ull << 20;  // row-major bytes per pipeline slice
+
+struct SlicePlan {
+    bool sliced;          // true: slices of whole tile-row bands of one (w,z) plane
+    uint32_t bands_per_slice, slices_per_plane;
+};
+
+// Slicing needs the bands of a plane to be contiguous in the queue image (trivial geometry) and
+// the plane's rows to be evenly pitched.
+SlicePlan plan_slices(const TileJob &j, uint64_t row_bytes)
+{
+    SlicePlan p{false, j.Rt, 1};
+    if (!j.trivial_geom) return p;
+    const uint64_t band_bytes = 32ull * row_bytes;
+    uint64_t bps = kSliceTargetBytes / (band_bytes ? band_bytes : 1);
+    if (bps < 1) bps = 1;
+    if (bps > j.Rt) bps = j.Rt;
+    p.sliced = true;
+    p.bands_per_slice = (uint32_t)bps;
+    p.slices_per_plane = (uint32_t)((j.Rt + bps - 1) / bps);
+    return p;
+}
+
+int status_after_sync(DevCtx *ctx)
+{
+    unsigned int st = 0;
+    cudaError_t e = cudaMemcpy(&st, ctx->status, sizeof(st), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail(e, "reading the device status word");
+    if (st != 0) {
+        unsigned int zero = 0;
+        cudaMemcpy(ctx->status, &zero, sizeof(zero), cudaMemcpyHostToDevice);
+        return fail(BUDA_TIMEOUT_ERROR, "a kernel gave up waiting (device status %u)", st);
+    }
+    return BUDA_SUCCESS;
+}
+
+// direction 0: host row-major -> host queue image; 1: host queue image -> host row-major
+int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_t shape[4], const uint64_t strides[4],
+                  const buda_queue_geom *geom, int q_df, int with_header, const void *q_host_c, uint64_t q_bytes)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    if (!rm_host_c || !q_host_c) return fail(BUDA_RUNTIME_ERROR, "null host buffer");
+    uint8_t *rm_host = (uint8_t *)rm_host_c;
+    uint8_t *q_host = (uint8_t *)q_host_c;
+    int mant, es;
+    if (int rc = classify(rm_df, q_df, mant, es)) return rc;
+    TileJob full;
+    if (int rc = make_job(shape, strides, geom, q_df, with_header, 1, full)) return rc;
+    if (strides[3] != (uint64_t)es) return fail(BUDA_RUNTIME_ERROR, "innermost stride must equal the element size");
+    const uint64_t image_bytes = full.buf_bytes * geom->grid_r * geom->grid_c;
+    if (q_bytes < image_bytes)
+        return fail(BUDA_RUNTIME_ERROR, "queue image buffer holds %llu bytes, needs %llu", (unsigned long long)q_bytes,
+                    (unsigned long long)image_bytes);
+    const uint64_t row_bytes = (uint64_t)shape[3] * es;
+    if (strides[2] < row_bytes) return fail(BUDA_RUNTIME_ERROR, "row stride smaller than a row");
+    const SlicePlan plan = plan_slices(full, row_bytes);
+
+    std::lock_guard<std::mutex> lock(ctx->host_mu);
+    // a slice on the device is always dense: [rows][row_bytes]
+    const uint32_t slice_bands = plan.sliced ? plan.bands_per_slice : full.Rt;
+    const uint64_t slice_a = plan.sliced ? (uint64_t)slice_bands * 32u * row_bytes
+                                         : (uint64_t)shape[0] * shape[1] * shape[2] * row_bytes;
+    const uint64_t slice_b = plan.sliced ? (uint64_t)slice_bands * full.Ct * full.tile_bytes : image_bytes;
+    if (int rc = ensure_pipe(ctx, slice_a, slice_b)) return rc;
+
+    cudaError_t e = cudaSuccess;
+    auto copy_rows = [&](uint8_t *dev, uint8_t *host, uint64_t rows, cudaStream_t s, bool to_dev) -> cudaError_t {
+        // rows of `row_bytes` at pitch strides[2] on the host, dense on the device
+        if (strides[2] == row_bytes)
+            return cudaMemcpyAsync(to_dev ? (void *)dev : (void *)host, to_dev ? (void *)host : (void *)dev,
+                                   rows * row_bytes, to_dev ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, s);
+        return to_dev ? cudaMemcpy2DAsync(dev, row_bytes, host, strides[2], row_bytes, rows, cudaMemcpyHostToDevice, s)
+                      : cudaMemcpy2DAsync(host, strides[2], dev, row_bytes, row_bytes, rows, cudaMemcpyDeviceToHost, s);
+    };
+
+    if (!plan.sliced) {
+        // one shot: whole tensor in slot 0
+        uint8_t *a = ctx->stage_a[0], *b = ctx->stage_b[0];
+        const uint64_t dense[4] = {(uint64_t)shape[1] * shape[2] * row_bytes, (uint64_t)shape[2] * row_bytes, row_bytes,
+                                   (uint64_t)es};
+        const void *srcs[1];
+        void *dsts[1];
+        if (direction == 0) {
+            for (uint32_t w = 0; w < shape[0] && e == cudaSuccess; w++)
+                for (uint32_t z = 0; z < shape[1] && e == cudaSuccess; z++)
+                    e = copy_rows(a + w * dense[0] + z * dense[1], rm_host + w * strides[0] + z * strides[1], shape[2],
+                                  ctx->s_comp, true);
+            if (e != cudaSuccess) return cuda_fail(e, "host to device copy");
+            srcs[0] = a; dsts[0] = b;
+            if (int rc = tilize_device(1, srcs, rm_df, shape, dense, geom, q_df, with_header, dsts, image_bytes, ctx->s_comp, -1))
+                return rc;
+            e = cudaMemcpyAsync(q_host, b, image_bytes, cudaMemcpyDeviceToHost, ctx->s_comp);
+        } else {
+            e = cudaMemcpyAsync(b, q_host, image_bytes, cudaMemcpyHostToDevice, ctx->s_comp);
+            if (e != cudaSuccess) return cuda_fail(e, "host to device copy");
+            srcs[0] = b; dsts[0] = a;
+            if (int rc = untilize_device(1, srcs, q_df, with_header, geom, dsts, rm_df, shape, dense, ctx->s_comp, -1))
+                return rc;
+            for (uint32_t w = 0; w < shape[0] && e == cudaSuccess; w++)
+                for (uint32_t z = 0; z < shape[1] && e == cudaSuccess; z++)
+                    e = copy_rows(a + w * dense[0] + z * dense[1], rm_host + w * strides[0] + z * strides[1], shape[2],
+                                  ctx->s_comp, false);
+        }
+        if (e != cudaSuccess) return cuda_fail(e, "copy");
+        e = cudaStreamSynchronize(ctx->s_comp);
+        if (e != cudaSuccess) return cuda_fail(e, "synchronize");
+        return status_after_sync(ctx);
+    }
+
+    // sliced: each slice is a [1,1,bands*32,C] tensor in a one-plane queue of its own
+    uint64_t k = 0;
+    for (uint32_t w = 0; w < shape[0]; w++) {
+        for (uint32_t z = 0; z < shape[1]; z++) {
+            for (uint32_t sl = 0; sl < plan.slices_per_plane; sl++, k++) {
+                const int slot = (int)(k % kPipeDepth);
+                const uint32_t band0 = sl * plan.bands_per_slice;
+                const uint32_t nb = (full.Rt - band0 < plan.bands_per_slice) ? (full.Rt - band0) : plan.bands_per_slice;
+                const uint32_t sshape[4] = {1, 1, nb * 32u, shape[3]};
+                const uint64_t sstr[4] = {(uint64_t)nb * 32u * row_bytes, (uint64_t)nb * 32u * row_bytes, row_bytes,
+                                          (uint64_t)es};
+                buda_queue_geom sg = *geom;
+                sg.t = 1;
+                sg.mblock_m = nb;
+                uint8_t *a = ctx->stage_a[slot], *b = ctx->stage_b[slot];
+                uint8_t *rm_ptr = rm_host + w * strides[0] + z * strides[1] + (uint64_t)band0 * 32u * strides[2];
+                uint8_t *q_ptr = q_host + tile_record_offset(full, w, z, band0, 0);
+                const uint64_t q_len = (uint64_t)nb * full.Ct * full.tile_bytes;
+                const void *srcs[1];
+                void *dsts[1];
+                cudaStream_t first = direction == 0 ? ctx->s_in : ctx->s_in;
+                // the slot is free once the copy-out of its previous slice has finished
+                if (k >= (uint64_t)kPipeDepth) {
+                    if ((e = cudaStreamWaitEvent(first, ctx->ev_out[slot], 0)) != cudaSuccess) return cuda_fail(e, "wait");
+                }
+                if (direction == 0) {
+                    if ((e = copy_rows(a, rm_ptr, (uint64_t)nb * 32u, ctx->s_in, true)) != cudaSuccess)
+                        return cuda_fail(e, "host to device copy");
+                } else {
+                    if ((e = cudaMemcpyAsync(b, q_ptr, q_len, cudaMemcpyHostToDevice, ctx->s_in)) != cudaSuccess)
+                        return cuda_fail(e, "host to device copy");
+                }
+                cudaEventRecord(ctx->ev_in[slot], ctx->s_in);
+                cudaStreamWaitEvent(ctx->s_comp, ctx->ev_in[slot], 0);
+                if (direction == 0) {
+                    srcs[0] = a; dsts[0] = b;
+                    if (int rc = tilize_device(1, srcs, rm_df, sshape, sstr, &sg, q_df, with_header, dsts, q_len, ctx->s_comp, -1))
+                        return rc;
+                } else {
+                    srcs[0] = b; dsts[0] = a;
+                    if (int rc = untilize_device(1, srcs, q_df, with_header, &sg, dsts, rm_df, sshape, sstr, ctx->s_comp, -1))
+                        return rc;
+                }
+                cudaEventRecord(ctx->ev_comp[slot], ctx->s_comp);
+                cudaStreamWaitEvent(ctx->s_out, ctx->ev_comp[slot], 0);
+                if (direction == 0) {
+                    if ((e = cudaMemcpyAsync(q_ptr, b, q_len, cudaMemcpyDeviceToHost, ctx->s_out)) != cudaSuccess)
+                        return cuda_fail(e, "device to host copy");
+                } else {
+                    if ((e = copy_rows(a, rm_ptr, (uint64_t)nb * 32u, ctx->s_out, false)) != cudaSuccess)
+                        return cuda_fail(e, "device to host copy");
+                }
+                cudaEventRecord(ctx->ev_out[slot], ctx->s_out);
+            }
+        }
+    }
+    if ((e = cudaStreamSynchronize(ctx->s_out)) != cudaSuccess) return cuda_fail(e, "synchronize");
+    if ((e = cudaStreamSynchronize(ctx->s_comp)) != cudaSuccess) return cuda_fail(e, "synchronize");
+    if ((e = cudaStreamSynchronize(ctx->s_in)) != cudaSuccess) return cuda_fail(e, "synchronize");
+    return status_after_sync(ctx);
+}
+
+}  // namespace
+
+// ================================================================================================
+// exported functions
+// ================================================================================================
+extern "C" {
+
+int64_t buda_tile_bytes(int df, int with_header)
+{
+    const int64_t h = with_header ? 32 : 0;
+    switch (df) {
+        case BUDA_DF_Float32: case BUDA_DF_Int32: case BUDA_DF_RawUInt32: return 4096 + h;
+        case BUDA_DF_Float16: case BUDA_DF_Float16_b: case BUDA_DF_UInt16: case BUDA_DF_RawUInt16: return 2048 + h;
+        case BUDA_DF_Bfp8: case BUDA_DF_Bfp8_b: return 1024 + 64 + h;
+        case BUDA_DF_Bfp4: case BUDA_DF_Bfp4_b: return 512 + 64 + h;
+        case BUDA_DF_Bfp2: case BUDA_DF_Bfp2_b: return 256 + 64 + h;
+        case BUDA_DF_Lf8: case BUDA_DF_Int8: case BUDA_DF_RawUInt8: return 1024 + h;
+        default: return -1;
+    }
+}
+
+int64_t buda_data_format_byte_size(int df, int64_t elements)
+{
+    switch (df) {
+        case BUDA_DF_Float32: case BUDA_DF_Int32: case BUDA_DF_RawUInt32: return 4 * elements;
+        case BUDA_DF_UInt16: case BUDA_DF_Float16_b: case BUDA_DF_Float16: case BUDA_DF_RawUInt16: return 2 * elements;
+        case BUDA_DF_Bfp8_b: case BUDA_DF_Bfp8: return elements + elements / 16;
+        case BUDA_DF_Bfp4_b: case BUDA_DF_Bfp4: return elements / 2 + elements / 16;
+        case BUDA_DF_Bfp2_b: case BUDA_DF_Bfp2: return elements / 4 + elements / 16;
+        case BUDA_DF_Lf8: case BUDA_DF_Int8: case BUDA_DF_RawUInt8: return elements;
+        case BUDA_DF_Invalid: return 0;
+        default: return -1;
+    }
+}
+
+int64_t buda_io_size_bytes(int df, int untilized, uint32_t ublock_ct, uint32_t ublock_rt, uint32_t mblock_m,
+                           uint32_t mblock_n, uint32_t t, uint32_t entries, uint32_t tile_height, uint32_t tile_width)
+{
+    const int64_t tiles = (int64_t)ublock_ct * ublock_rt * mblock_m * mblock_n * t * entries;
+    if (untilized) {
+        // a flat queue holds plain elements; block-float formats are read back as 16-bit floats
+        int64_t es = plain_elem_bytes(df);
+        if (es == 0) es = bfp_mant_bits(df) ? 2 : 0;
+        if (es == 0) return -1;
+        return tiles * tile_height * tile_width * es;
+    }
+    const int64_t tb = buda_tile_bytes(df, 1);
+    if (tb < 0) return -1;
+    if (tile_height == 32 && tile_width == 32) return tiles * tb;
+    // smaller tiles keep the header and scale the payload
+    const int64_t payload = (tb - 32) * (int64_t)tile_height * tile_width / 1024;
+    return tiles * (payload + 32);
+}
+
+int64_t buda_tilized_bytes(const buda_queue_geom *geom, const uint32_t shape[4], int df, int with_header)
+{
+    TileJob j;
+    const uint64_t st[4] = {0, 0, 0, 0};
+    if (make_job(shape, st, geom, df, with_header, 1, j)) return -1;
+    return (int64_t)(j.buf_bytes * geom->grid_r * geom->grid_c);
+}
+
+int buda_tile_map(const buda_queue_geom *g, uint32_t t, uint32_t r, uint32_t c, uint32_t *core_r, uint32_t *core_c,
+                  uint64_t *addr)
+{
+    if (!g || !core_r || !core_c || !addr) return fail(BUDA_RUNTIME_ERROR, "null argument");
+    if (!g->grid_r || !g->grid_c || !g->mblock_m || !g->mblock_n || !g->ublock_rt || !g->ublock_ct || g->ublock_order > 1)
+        return fail(BUDA_RUNTIME_ERROR, "invalid queue geometry");
+    if (t >= g->t || r >= g->grid_r * g->mblock_m * g->ublock_rt || c >= g->grid_c * g->mblock_n * g->ublock_ct)
+        return fail(BUDA_RUNTIME_ERROR, "tile coordinate (%u,%u,%u) outside the queue", t, r, c);
+    TileJob j;
+    memset(&j, 0, sizeof(j));
+    j.g = *g;
+    j.tile_bytes = 1;
+    j.tiles_per_entry = (uint64_t)g->t * g->mblock_m * g->mblock_n * g->ublock_rt * g->ublock_ct;
+    j.buf_bytes = 1ull << 40;  // splits the offset into (core, address)
+    j.trivial_geom = 0;
+    const uint64_t off = tile_record_offset(j, 0, t, r, c);
+    const uint64_t core = off >> 40;
+    *core_r = (uint32_t)(core / g->grid_c);
+    *core_c = (uint32_t)(core % g->grid_c);
+    *addr = off & ((1ull << 40) - 1);
+    return BUDA_SUCCESS;
+}
+
+int buda_tilize_pack(const void *src, int src_df, const uint32_t shape[4], const uint64_t strides_bytes[4],
+                     const buda_queue_geom *geom, int dst_df, int with_header, void *dst, uint64_t dst_bytes, void *stream)
+{
+    const void *srcs[1] = {src};
+    void *dsts[1] = {dst};
+    return tilize_device(1, srcs, src_df, shape, strides_bytes, geom, dst_df, with_header, dsts, dst_bytes,
+                         (cudaStream_t)stream, -1);
+}
+
+int buda_tilize_pack_batch(int n, const void *const *srcs_host, int src_df, const uint32_t shape[4],
+                           const uint64_t strides_bytes[4], const buda_queue_geom *geom, int dst_df, int with_header,
+                           void *const *dsts_host, uint64_t dst_bytes_each, void *stream)
+{
+    return tilize_device(n, srcs_host, src_df, shape, strides_bytes, geom, dst_df, with_header, dsts_host, dst_bytes_each,
+                         (cudaStream_t)stream, -1);
+}
+
+// Same as buda_tilize_pack_batch with the kernel chosen by the caller: 0 staged, 1 direct.
+// For tests and measurements of the two kernels on the same input.
+int buda_tilize_pack_batch_path(int n, const void *const *srcs_host, int src_df, const uint32_t shape[4],
+                                const uint64_t strides_bytes[4], const buda_queue_geom *geom, int dst_df, int with_header,
+                                void *const *dsts_host, uint64_t dst_bytes_each, void *stream, int path)
+{
+    return tilize_device(n, srcs_host, src_df, shape, strides_bytes, geom, dst_df, with_header, dsts_host, dst_bytes_each,
+                         (cudaStream_t)stream, path);
+}
+
+int buda_tilize_pack_host(const void *src_host, int src_df, const uint32_t shape[4], const uint64_t strides_bytes[4],
+                          const buda_queue_geom *geom, int dst_df, int with_header, void *dst_host, uint64_t dst_bytes,
+                          void *stream)
+{
+    (void)stream;
+    return host_pipeline(0, src_host, src_df, shape, strides_bytes, geom, dst_df, with_header, dst_host, dst_bytes);
+}
+
+int buda_unpack_untilize(const void *src, int src_df, int with_header, const buda_queue_geom *geom, void *dst, int dst_df,
+                         const uint32_t shape[4], const uint64_t strides_bytes[4], void *stream)
+{
+    const void *srcs[1] = {src};
+    void *dsts[1] = {dst};
+    return untilize_device(1, srcs, src_df, with_header, geom, dsts, dst_df, shape, strides_bytes, (cudaStream_t)stream, -1);
+}
+
+int buda_unpack_untilize_batch(int n, const void *const *srcs_host, int src_df, int with_header,
+                               const buda_queue_geom *geom, void *const *dsts_host, int dst_df, const uint32_t shape[4],
+                               const uint64_t strides_bytes[4], void *stream)
+{
+    return untilize_device(n, srcs_host, src_df, with_header, geom, dsts_host, dst_df, shape, strides_bytes,
+                           (cudaStream_t)stream, -1);
+}
+
+int buda_unpack_untilize_batch_path(int n, const void *const *srcs_host, int src_df, int with_header,
+                                    const buda_queue_geom *geom, void *const *dsts_host, int dst_df,
+                                    const uint32_t shape[4], const uint64_t strides_bytes[4], void *stream, int path)
+{
+    return untilize_device(n, srcs_host, src_df, with_header, geom, dsts_host, dst_df, shape, strides_bytes,
+                           (cudaStream_t)stream, path);
+}
+
+int buda_unpack_untilize_host(const void *src_host, int src_df, int with_header, const buda_queue_geom *geom,
+                              void *dst_host, int dst_df, const uint32_t shape[4], const uint64_t strides_bytes[4],
+                              void *stream)
+{
+    (void)stream;
+    int64_t need = buda_tilized_bytes(geom, shape, src_df, with_header);
+    if (need < 0) return fail(BUDA_RUNTIME_ERROR, "tensor does not fit the queue geometry");
+    return host_pipeline(1, dst_host, dst_df, shape, strides_bytes, geom, src_df, with_header, src_host, (uint64_t)need);
+}
+
+static int check_quant_args(const void *x, int64_t n, const void *scale, int64_t scale_len, int64_t inner, const void *out)
+{
+    if (n < 0) return fail(BUDA_RUNTIME_ERROR, "negative element count");
+    if (n == 0) return BUDA_SUCCESS;
+    if (!x || !scale || !out) return fail(BUDA_RUNTIME_ERROR, "null tensor pointer");
+    if (scale_len < 1 || inner < 1) return fail(BUDA_RUNTIME_ERROR, "scale_len and inner must be >= 1");
+    return BUDA_SUCCESS;
+}
+
+int buda_quantize(const float *x, int64_t n, const float *scale, int64_t scale_len, int64_t inner, float zero_point,
+                  int mode, float lo, float hi, int8_t *out, void *stream)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    if (int rc = check_quant_args(x, n, scale, scale_len, inner, out)) return rc;
+    if (n == 0) return BUDA_SUCCESS;
+    if (mode != 0 && mode != 1) return fail(BUDA_RUNTIME_ERROR, "quantize mode must be 0 or 1");
+    cudaError_t e = launch_quantize(x, n, scale, scale_len, inner, zero_point, mode, lo, hi, out, ctx->sm_count,
+                                    (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "quantize launch failed");
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return BUDA_SUCCESS;
+}
+
+int buda_dequantize(const int8_t *x, int64_t n, const float *scale, int64_t scale_len, int64_t inner, float zero_point,
+                    float *out, void *stream)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    if (int rc = check_quant_args(x, n, scale, scale_len, inner, out)) return rc;
+    if (n == 0) return BUDA_SUCCESS;
+    cudaError_t e = launch_dequantize(x, n, scale, scale_len, inner, zero_point, out, ctx->sm_count, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "dequantize launch failed");
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return BUDA_SUCCESS;
+}
+
+int buda_requantize(const int32_t *x, int64_t n, const float *inp_scale, const float *out_scale, int64_t scale_len,
+                    int64_t inner, float zero_point, int mode, float lo, float hi, int8_t *out, void *stream)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    if (int rc = check_quant_args(x, n, inp_scale, scale_len, inner, out)) return rc;
+    if (n == 0) return BUDA_SUCCESS;
+    if (mode != 0 && mode != 1) return fail(BUDA_RUNTIME_ERROR, "requantize mode must be 0 or 1");
+    if (mode == 0 && !out_scale) return fail(BUDA_RUNTIME_ERROR, "Requantize needs out_scale");
+    cudaError_t e = launch_requantize(x, n, inp_scale, out_scale, scale_len, inner, zero_point, mode, lo, hi, out,
+                                      ctx->sm_count, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "requantize launch failed");
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return BUDA_SUCCESS;
+}
+
+int buda_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N, void *C, int64_t ldc,
+                    void *stream)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    if (!A || !W_tiles || !C) return fail(BUDA_RUNTIME_ERROR, "null matrix pointer");
+    char msg[256] = "";
+    cudaError_t e = launch_bfp8b_gemm(A, M, K, lda, W_tiles, N, C, ldc, ctx->sm_count, (cudaStream_t)stream, ctx->status,
+                                      msg, sizeof(msg));
+    if (e != cudaSuccess) return msg[0] ? fail(BUDA_RUNTIME_ERROR, "%s", msg) : cuda_fail(e, "gemm launch failed");
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return BUDA_SUCCESS;
+}
+
+size_t buda_last_error(char *buf, size_t buf_len)
+{
+    const size_t n = strlen(t_err);
+    if (buf && buf_len) {
+        const size_t c = n < buf_len - 1 ? n : buf_len - 1;
+        memcpy(buf, t_err, c);
+        buf[c] = 0;
+    }
+    return n;
+}
+
+int buda_device_status(int *status_out)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return cuda_fail(e, "device synchronize");
+    unsigned int st = 0;
+    e = cudaMemcpy(&st, ctx->status, sizeof(st), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail(e, "reading the device status word");
+    if (status_out) *status_out = (int)st;
+    if (st != 0) {
+        unsigned int zero = 0;
+        cudaMemcpy(ctx->status, &zero, sizeof(zero), cudaMemcpyHostToDevice);
+        return fail(BUDA_TIMEOUT_ERROR, "a kernel gave up waiting (device status %u)", st);
+    }
+    return BUDA_SUCCESS;
+}
+
+uint64_t buda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char *buda_version(void) { return "buda_cuda 0.1 sm_100a"; }
+
+}  // extern "C"

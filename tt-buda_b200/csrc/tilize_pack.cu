@@ -1,0 +1,383 @@
+// K1 / K3: row-major tensor -> queue image of 32x32 tiles (four 16x16 faces), fused with the
+// Bfp8_b / Bfp4_b / Bfp2_b block-float pack (or a plain relayout for same-width formats).
+//
+// Device counterpart of the conversion the reference performs inside tt::backend::tilize_tensor
+// and push_input (bound at pybuda/csrc/backend_api/backend_api.cpp:688-704).
+//
+// Two kernels:
+//   pack_staged_kernel  (16-byte aligned rows; the hot path)
+//     A persistent CTA per SM slot walks work items; an item is a band of 32 rows x up to 4 tiles
+//     (128 columns).  One producer warp stages the band in shared memory with 32 bulk async
+//     copies (one per row, TMA engine, completion on an mbarrier) several items ahead; eight
+//     consumer warps then each own one 16-column face column of the band: lane = row, so a thread
+//     reads one whole 16-value block (one face row) from shared memory, encodes it in registers
+//     and drops its 16/8/4 mantissa bytes plus the exponent byte into the tile record being
+//     assembled in shared memory.  Finished records leave with one bulk async store per tile.
+//     Row pitch in shared memory is row bytes + 16, which makes the 16-byte reads of the 32 lanes
+//     (32 different rows) conflict free.
+//   pack_direct_kernel  (any alignment / stride; the general path)
+//     Four lanes own one block: each loads 4 values (one 128-bit load when aligned), the shared
+//     exponent is a 4-lane-wide warp-shuffle maximum, and a warp covers 8 consecutive rows of one
+//     face so its stores form one contiguous run of the record.
+#include "bfp_codec.cuh"
+#include "buda_common.cuh"
+
+namespace buda {
+
+// ------------------------------------------------------------------------------------------------
+// staged kernel
+// ------------------------------------------------------------------------------------------------
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kStagedThreads = kConsumerThreads + 32;  // + one producer warp
+
+struct ItemMeta {
+    uint32_t b, w, z, rt, ct0, ntiles, pad0, pad1;
+};
+
+template <int M, int ES>
+struct PackCfg {
+    static constexpr int row_bytes = kBoxTiles * 32 * ES;
+    static constexpr int pitch = row_bytes + 16;
+    static constexpr int in_stage_bytes = 32 * pitch;
+    static constexpr int payload = (M > 0) ? (64 + 1024 * (M + 1) / 8) : (1024 * ES);
+    static constexpr int rec_max = payload + 32;
+    static constexpr int out_buf_bytes = kBoxTiles * rec_max;
+    static constexpr int stages = (in_stage_bytes > 12000) ? 3 : 4;
+    static constexpr int smem_bytes = stages * in_stage_bytes + 2 * out_buf_bytes + stages * (int)sizeof(ItemMeta) +
+                                      2 * stages * 8 + 16;
+};
+
+__device__ __forceinline__ void decode_item(const TileJob &job, uint32_t item, ItemMeta &m)
+{
+    uint32_t cb = item % job.boxes_per_band;
+    uint32_t q = item / job.boxes_per_band;
+    m.rt = q % job.Rt;
+    q /= job.Rt;
+    m.z = q % job.Z;
+    q /= job.Z;
+    m.w = q % job.W;
+    m.b = q / job.W;
+    m.ct0 = cb * kBoxTiles;
+    m.ntiles = min((uint32_t)kBoxTiles, job.Ct - m.ct0);
+}
+
+template <int M, int ES>
+__global__ void __launch_bounds__(kStagedThreads)
+pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ PtrTable ptrs, unsigned int *status)
+{
+    using Cfg = PackCfg<M, ES>;
+    constexpr int S = Cfg::stages;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t *in_stage = smem;
+    uint8_t *out_buf = smem + S * Cfg::in_stage_bytes;
+    ItemMeta *meta = reinterpret_cast<ItemMeta *>(out_buf + 2 * Cfg::out_buf_bytes);
+    uint64_t *full = reinterpret_cast<uint64_t *>(meta + S);
+    uint64_t *empty = full + S;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + S);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rec = job.tile_bytes, hdr = job.header_bytes;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    // header bytes of the staged records are written once: they stay zero for every item
+    for (int i = tid; i < 2 * Cfg::out_buf_bytes / 4; i += kStagedThreads) reinterpret_cast<uint32_t *>(out_buf)[i] = 0;
+    fence_async_smem();
+    __syncthreads();
+
+    if (warp == kConsumerWarps) {
+        // ---------------------------------------------------------------- producer warp
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t item = blockIdx.x; item < job.total_items; item += gridDim.x, ++it) {
+            const int s = it % S;
+            const uint32_t ph = (it / S) & 1u;
+            if (!mbar_wait_bounded(&empty[s], ph ^ 1u, abort_flag, status, BUDA_DEVSTAT_PACK_EMPTY_WAIT)) {
+                ok = false;
+                break;
+            }
+            ItemMeta m;
+            decode_item(job, item, m);
+            const uint32_t row_copy = m.ntiles * 32u * ES;
+            if (lane == 0) {
+                meta[s] = m;
+                mbar_arrive_expect_tx(&full[s], 32u * row_copy);
+            }
+            __syncwarp();
+            const uint8_t *src = ptrs.src[m.b] + (uint64_t)m.w * job.stride_w + (uint64_t)m.z * job.stride_z +
+                                 ((uint64_t)m.rt * 32u + lane) * job.stride_r + (uint64_t)m.ct0 * 32u * ES;
+            bulk_g2s(in_stage + s * Cfg::in_stage_bytes + lane * Cfg::pitch, src, row_copy, &full[s]);
+        }
+        if (!ok || *abort_flag) {
+            // gave up: let the copies already issued land before the CTA releases its shared memory
+            const uint32_t back = it < (uint32_t)S ? it : (uint32_t)S;
+            for (uint32_t k = 1; k <= back; k++) {
+                const uint32_t j = it - k;
+                uint64_t t0 = global_timer_ns();
+                while (!mbar_try_wait(&full[j % S], (j / S) & 1u) && global_timer_ns() - t0 < 100000000ull) {}
+            }
+        }
+        return;
+    }
+
+    // -------------------------------------------------------------------- consumer warps
+    const int bc = warp;              // face column of the band: tile bc/2, left/right face bc%2
+    const int tile_in_box = bc >> 1;
+    const int face = ((lane >> 4) << 1) | (bc & 1);
+    const int fr = lane & 15;
+    uint32_t it = 0;
+    for (uint32_t item = blockIdx.x; item < job.total_items; item += gridDim.x, ++it) {
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1u;
+        const bool ok = mbar_wait_bounded(&full[s], ph, abort_flag, status, BUDA_DEVSTAT_PACK_FULL_WAIT);
+        const ItemMeta m = meta[s];
+        uint8_t *ob = out_buf + (it & 1u) * Cfg::out_buf_bytes;
+        const uint8_t *stage = in_stage + s * Cfg::in_stage_bytes;
+
+        if (!ok) {
+            // fall through to the barrier below so the whole CTA leaves together
+        } else if (M > 0) {
+            if ((uint32_t)tile_in_box < m.ntiles) {
+                uint32_t x[16];
+                const uint8_t *p = stage + lane * Cfg::pitch + bc * 16 * ES;
+                if (ES == 4) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        uint4 v = *reinterpret_cast<const uint4 *>(p + 16 * j);
+                        x[4 * j] = v.x; x[4 * j + 1] = v.y; x[4 * j + 2] = v.z; x[4 * j + 3] = v.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        uint4 v = *reinterpret_cast<const uint4 *>(p + 16 * j);
+                        const uint32_t h[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {  // bfloat16 widens exactly: it is the upper half
+                            x[8 * j + 2 * k] = h[k] << 16;
+                            x[8 * j + 2 * k + 1] = h[k] & 0xffff0000u;
+                        }
+                    }
+                }
+                constexpr int MM = M > 0 ? M : 7;
+                uint32_t E, d[BfpTraits<MM>::words];
+                bfp_encode16<MM>(x, E, d);
+                uint8_t *r = ob + tile_in_box * rec + hdr;
+                const int blk = face * 16 + fr;
+                r[blk] = (uint8_t)E;
+                uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
+                if (MM == 7) *reinterpret_cast<uint4 *>(q) = make_uint4(d[0], d[1 % BfpTraits<MM>::words], d[2 % BfpTraits<MM>::words], d[3 % BfpTraits<MM>::words]);
+                else if (MM == 3) *reinterpret_cast<uint2 *>(q) = make_uint2(d[0], d[1 % BfpTraits<MM>::words]);
+                else *reinterpret_cast<uint32_t *>(q) = d[0];
+            }
+        } else {
+            // plain relayout: the record is moved as 16-byte chunks; chunk c of a record is face
+            // c / (16*cpr), face row (c / cpr) % 16, part c % cpr  (cpr = chunks per 16-value face row)
+            constexpr int cpr = ES;                   // 16 * ES / 16
+            constexpr int chunks_per_tile = 64 * cpr; // 1024 * ES / 16
+            const int nchunks = (int)m.ntiles * chunks_per_tile;
+            for (int c = tid; c < nchunks; c += kConsumerThreads) {
+                const int t = c / chunks_per_tile, k = c % chunks_per_tile;
+                const int f = k / (16 * cpr), r16 = (k / cpr) % 16, part = k % cpr;
+                const int row = (f >> 1) * 16 + r16;
+                const uint4 v = *reinterpret_cast<const uint4 *>(stage + row * Cfg::pitch + t * 32 * ES +
+                                                                 (f & 1) * 16 * ES + part * 16);
+                *reinterpret_cast<uint4 *>(ob + t * rec + hdr + k * 16) = v;
+            }
+        }
+        fence_async_smem();
+        if (warp == 0 && lane < kBoxTiles) bulk_wait_read_all();  // the previous item's stores have left shared memory
+        if (named_bar_or(1, kConsumerThreads, !ok)) break;
+        if (tid == 0) mbar_arrive(&empty[s]);
+        if (warp == 0 && (uint32_t)lane < m.ntiles) {
+            uint8_t *dst = ptrs.dst[m.b] + tile_record_offset(job, m.w, m.z, m.rt, m.ct0 + lane);
+            bulk_s2g(dst, ob + lane * rec, rec);
+            bulk_commit();
+        }
+    }
+    if (warp == 0 && lane < kBoxTiles) bulk_wait_all();
+}
+
+// ------------------------------------------------------------------------------------------------
+// direct kernel: 4 lanes per block, warp-shuffle exponent reduction, any alignment
+// ------------------------------------------------------------------------------------------------
+template <int M>
+__device__ __forceinline__ uint32_t encode4_shared_exp(const uint32_t (&x)[4], uint32_t E)
+{
+    constexpr uint32_t qmax = BfpTraits<M>::qmax;
+    uint32_t packed = 0;
+    const bool fast = (E + 1u >= (uint32_t)M) && (E <= (uint32_t)(M + 252));
+    const float S = __uint_as_float((uint32_t)(M + 253 - (int)E) << 23);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        uint32_t d;
+        if (fast) {
+            float r;
+            asm("fma.rn.ftz.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(__uint_as_float(x[i] & 0x7fffffffu)), "f"(S), "f"(12582912.0f));
+            uint32_t q = min(__float_as_uint(r), kMagicBits + qmax) - kMagicBits;
+            d = q ? (((x[i] >> 31) << M) | q) : 0u;
+        } else {
+            d = bfp_encode_datum_int(x[i], E, M);
+        }
+        packed |= d << (i * (M + 1));
+    }
+    return packed;
+}
+
+template <int ES>
+__device__ __forceinline__ void load4(const uint8_t *p, bool vec, uint32_t (&x)[4])
+{
+    if (ES == 4) {
+        if (vec) {
+            uint4 v = *reinterpret_cast<const uint4 *>(p);
+            x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+        } else if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) x[i] = *reinterpret_cast<const uint32_t *>(p + 4 * i);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                x[i] = (uint32_t)p[4 * i] | ((uint32_t)p[4 * i + 1] << 8) | ((uint32_t)p[4 * i + 2] << 16) |
+                       ((uint32_t)p[4 * i + 3] << 24);
+        }
+    } else if (ES == 2) {
+        if (vec) {
+            uint2 v = *reinterpret_cast<const uint2 *>(p);
+            x[0] = v.x & 0xffffu; x[1] = v.x >> 16; x[2] = v.y & 0xffffu; x[3] = v.y >> 16;
+        } else if ((reinterpret_cast<uintptr_t>(p) & 1u) == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) x[i] = *reinterpret_cast<const uint16_t *>(p + 2 * i);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; i++) x[i] = (uint32_t)p[2 * i] | ((uint32_t)p[2 * i + 1] << 8);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) x[i] = p[i];
+    }
+}
+
+template <int M, int ES>
+__global__ void __launch_bounds__(256)
+pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ PtrTable ptrs, int batch, int vec_ok)
+{
+    const int lane = threadIdx.x & 31;
+    const uint64_t warps_total = (uint64_t)gridDim.x * (blockDim.x >> 5);
+    const uint64_t warp_id = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint64_t tiles_per_tensor = (uint64_t)job.W * job.Z * job.Rt * job.Ct;
+    const uint64_t units = (uint64_t)batch * tiles_per_tensor * 8u;  // a unit is 8 rows of one face
+    const uint32_t rec = job.tile_bytes, hdr = job.header_bytes;
+    for (uint64_t u = warp_id; u < units; u += warps_total) {
+        const uint32_t hf = (uint32_t)(u & 7u);
+        uint64_t t = u >> 3;
+        const uint32_t ct = (uint32_t)(t % job.Ct); t /= job.Ct;
+        const uint32_t rt = (uint32_t)(t % job.Rt); t /= job.Rt;
+        const uint32_t z = (uint32_t)(t % job.Z); t /= job.Z;
+        const uint32_t w = (uint32_t)(t % job.W);
+        const uint32_t b = (uint32_t)(t / job.W);
+        const uint32_t face = hf >> 1, half = hf & 1u;
+        const uint32_t fr = half * 8u + (lane >> 2);
+        const uint64_t row = (uint64_t)rt * 32u + (face >> 1) * 16u + fr;
+        const uint64_t col = (uint64_t)ct * 32u + (face & 1u) * 16u + (lane & 3) * 4u;
+        const uint8_t *p = ptrs.src[b] + (uint64_t)w * job.stride_w + (uint64_t)z * job.stride_z + row * job.stride_r +
+                           col * ES;
+        uint8_t *r = ptrs.dst[b] + tile_record_offset(job, w, z, rt, ct);
+        if (hdr && hf == 0 && lane < 8) reinterpret_cast<uint32_t *>(r)[lane] = 0;
+        r += hdr;
+        uint32_t x[4];
+        load4<ES>(p, vec_ok != 0, x);
+        const uint32_t blk = face * 16u + fr;
+        if (M > 0) {
+            constexpr int MM = M > 0 ? M : 7;
+            if (ES == 2) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) x[i] <<= 16;
+            }
+            uint32_t mx = max(max(x[0] & 0x7fffffffu, x[1] & 0x7fffffffu), max(x[2] & 0x7fffffffu, x[3] & 0x7fffffffu));
+            mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1, 4));
+            mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2, 4));
+            const uint32_t E = mx >> 23;
+            const uint32_t packed = encode4_shared_exp<MM>(x, E);
+            if ((lane & 3) == 0) r[blk] = (uint8_t)E;
+            uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
+            if (MM == 7) reinterpret_cast<uint32_t *>(q)[lane & 3] = packed;
+            else if (MM == 3) reinterpret_cast<uint16_t *>(q)[lane & 3] = (uint16_t)packed;
+            else q[lane & 3] = (uint8_t)packed;
+        } else {
+            uint8_t *q = r + ((uint64_t)blk * 16u + (lane & 3) * 4u) * ES;
+            if (ES == 4) *reinterpret_cast<uint4 *>(q) = make_uint4(x[0], x[1], x[2], x[3]);
+            else if (ES == 2) *reinterpret_cast<uint2 *>(q) = make_uint2(x[0] | (x[1] << 16), x[2] | (x[3] << 16));
+            else *reinterpret_cast<uint32_t *>(q) = x[0] | (x[1] << 8) | (x[2] << 16) | (x[3] << 24);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host launchers
+// ------------------------------------------------------------------------------------------------
+template <int M, int ES>
+static cudaError_t launch_staged(const TileJob &job, const PtrTable &ptrs, int sm_count, cudaStream_t stream,
+                                 unsigned int *status)
+{
+    using Cfg = PackCfg<M, ES>;
+    static int per_sm_cache[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev &= 63;
+    if (per_sm_cache[dev] == 0) {
+        cudaError_t e = cudaFuncSetAttribute(pack_staged_kernel<M, ES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             Cfg::smem_bytes);
+        if (e != cudaSuccess) return e;
+        int n = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, pack_staged_kernel<M, ES>, kStagedThreads,
+                                                          Cfg::smem_bytes);
+        if (e != cudaSuccess) return e;
+        per_sm_cache[dev] = n < 1 ? 1 : (n > 4 ? 4 : n);
+    }
+    uint32_t grid = (uint32_t)(sm_count * per_sm_cache[dev]);
+    if (grid > job.total_items) grid = job.total_items;
+    pack_staged_kernel<M, ES><<<grid, kStagedThreads, Cfg::smem_bytes, stream>>>(job, ptrs, status);
+    return cudaGetLastError();
+}
+
+template <int M, int ES>
+static cudaError_t launch_direct(const TileJob &job, const PtrTable &ptrs, int batch, int vec_ok, int sm_count,
+                                 cudaStream_t stream)
+{
+    const uint64_t units = (uint64_t)batch * job.W * job.Z * job.Rt * job.Ct * 8u;
+    uint64_t blocks = (units + 7) / 8;
+    const uint64_t cap = (uint64_t)sm_count * 32;
+    if (blocks > cap) blocks = cap;
+    pack_direct_kernel<M, ES><<<(unsigned)blocks, 256, 0, stream>>>(job, ptrs, batch, vec_ok);
+    return cudaGetLastError();
+}
+
+// mant_bits 7/3/1 = Bfp pack, 0 = plain relayout; es = source element bytes.
+// path: 0 = staged (needs 16-byte aligned rows), 1 = direct.
+cudaError_t launch_tilize(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int path,
+                          int vec_ok, int sm_count, cudaStream_t stream, unsigned int *status)
+{
+#define BUDA_DISPATCH(MM, EE)                                                                  \
+    if (mant_bits == MM && es == EE)                                                           \
+        return path == 0 ? launch_staged<MM, EE>(job, ptrs, sm_count, stream, status)          \
+                         : launch_direct<MM, EE>(job, ptrs, batch, vec_ok, sm_count, stream);
+    BUDA_DISPATCH(7, 4)
+    BUDA_DISPATCH(3, 4)
+    BUDA_DISPATCH(1, 4)
+    BUDA_DISPATCH(7, 2)
+    BUDA_DISPATCH(3, 2)
+    BUDA_DISPATCH(1, 2)
+    BUDA_DISPATCH(0, 4)
+    BUDA_DISPATCH(0, 2)
+    BUDA_DISPATCH(0, 1)
+#undef BUDA_DISPATCH
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace buda

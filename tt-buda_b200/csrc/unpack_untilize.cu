@@ -1,0 +1,339 @@
+// K2 / K3 (inverse): queue image of 32x32 tiles -> row-major tensor, fused with the
+// Bfp8_b / Bfp4_b / Bfp2_b decode to binary32 or bfloat16 (or a plain relayout).
+//
+// Device counterpart of the conversion the reference performs inside tt::backend::get_output
+// (bound at pybuda/csrc/backend_api/backend_api.cpp:701).
+//
+// Mirror image of the pack kernels: the staged kernel brings whole tile records into shared
+// memory with bulk async copies (one per tile), a thread decodes one 16-value block and writes it
+// into a padded row-major band in shared memory, and the band leaves with one bulk async store
+// per row.  The direct kernel (any alignment) gives each block to four lanes.
+#include "bfp_codec.cuh"
+#include "buda_common.cuh"
+
+namespace buda {
+
+constexpr int kUConsumerWarps = 8;
+constexpr int kUConsumerThreads = kUConsumerWarps * 32;
+constexpr int kUStagedThreads = kUConsumerThreads + 32;
+
+struct UItemMeta {
+    uint32_t b, w, z, rt, ct0, ntiles, pad0, pad1;
+};
+
+template <int M, int ES>
+struct UnpackCfg {
+    static constexpr int row_bytes = kBoxTiles * 32 * ES;
+    static constexpr int pitch = row_bytes + 16;
+    static constexpr int out_buf_bytes = 32 * pitch;
+    static constexpr int payload = (M > 0) ? (64 + 1024 * (M + 1) / 8) : (1024 * ES);
+    static constexpr int rec_max = payload + 32;
+    static constexpr int in_stage_bytes = kBoxTiles * rec_max;
+    static constexpr int stages = 4;
+    static constexpr int smem_bytes = stages * in_stage_bytes + 2 * out_buf_bytes + stages * (int)sizeof(UItemMeta) +
+                                      2 * stages * 8 + 16;
+};
+
+__device__ __forceinline__ void decode_uitem(const TileJob &job, uint32_t item, UItemMeta &m)
+{
+    uint32_t cb = item % job.boxes_per_band;
+    uint32_t q = item / job.boxes_per_band;
+    m.rt = q % job.Rt;
+    q /= job.Rt;
+    m.z = q % job.Z;
+    q /= job.Z;
+    m.w = q % job.W;
+    m.b = q / job.W;
+    m.ct0 = cb * kBoxTiles;
+    m.ntiles = min((uint32_t)kBoxTiles, job.Ct - m.ct0);
+}
+
+// In this file PtrTable.src is the queue image and PtrTable.dst the row-major tensor.
+template <int M, int ES>
+__global__ void __launch_bounds__(kUStagedThreads)
+unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ PtrTable ptrs, unsigned int *status)
+{
+    using Cfg = UnpackCfg<M, ES>;
+    constexpr int S = Cfg::stages;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t *in_stage = smem;
+    uint8_t *out_buf = smem + S * Cfg::in_stage_bytes;
+    UItemMeta *meta = reinterpret_cast<UItemMeta *>(out_buf + 2 * Cfg::out_buf_bytes);
+    uint64_t *full = reinterpret_cast<uint64_t *>(meta + S);
+    uint64_t *empty = full + S;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + S);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rec = job.tile_bytes, hdr = job.header_bytes;
+
+    if (tid == 0) {
+        for (int s = 0; s < S; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == kUConsumerWarps) {
+        // ---------------------------------------------------------------- producer warp
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t item = blockIdx.x; item < job.total_items; item += gridDim.x, ++it) {
+            const int s = it % S;
+            const uint32_t ph = (it / S) & 1u;
+            if (!mbar_wait_bounded(&empty[s], ph ^ 1u, abort_flag, status, BUDA_DEVSTAT_UNPACK_EMPTY_WAIT)) {
+                ok = false;
+                break;
+            }
+            UItemMeta m;
+            decode_uitem(job, item, m);
+            if (lane == 0) {
+                meta[s] = m;
+                mbar_arrive_expect_tx(&full[s], m.ntiles * rec);
+            }
+            __syncwarp();
+            if ((uint32_t)lane < m.ntiles) {
+                const uint8_t *src = ptrs.src[m.b] + tile_record_offset(job, m.w, m.z, m.rt, m.ct0 + lane);
+                bulk_g2s(in_stage + s * Cfg::in_stage_bytes + lane * rec, src, rec, &full[s]);
+            }
+        }
+        if (!ok || *abort_flag) {
+            const uint32_t back = it < (uint32_t)S ? it : (uint32_t)S;
+            for (uint32_t k = 1; k <= back; k++) {
+                const uint32_t j = it - k;
+                uint64_t t0 = global_timer_ns();
+                while (!mbar_try_wait(&full[j % S], (j / S) & 1u) && global_timer_ns() - t0 < 100000000ull) {}
+            }
+        }
+        return;
+    }
+
+    // -------------------------------------------------------------------- consumer warps
+    const int bc = warp;
+    const int tile_in_box = bc >> 1;
+    const int face = ((lane >> 4) << 1) | (bc & 1);
+    const int fr = lane & 15;
+    uint32_t it = 0;
+    for (uint32_t item = blockIdx.x; item < job.total_items; item += gridDim.x, ++it) {
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1u;
+        const bool ok = mbar_wait_bounded(&full[s], ph, abort_flag, status, BUDA_DEVSTAT_UNPACK_FULL_WAIT);
+        const UItemMeta m = meta[s];
+        uint8_t *ob = out_buf + (it & 1u) * Cfg::out_buf_bytes;
+        const uint8_t *stage = in_stage + s * Cfg::in_stage_bytes;
+
+        if (!ok) {
+            // fall through to the barrier below so the whole CTA leaves together
+        } else if (M > 0) {
+            if ((uint32_t)tile_in_box < m.ntiles) {
+                constexpr int MM = M > 0 ? M : 7;
+                const uint8_t *r = stage + tile_in_box * rec + hdr;
+                const int blk = face * 16 + fr;
+                const uint32_t E = r[blk];
+                const uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
+                uint32_t d[BfpTraits<MM>::words];
+                if (MM == 7) {
+                    uint4 t = *reinterpret_cast<const uint4 *>(q);
+                    d[0] = t.x; d[1 % BfpTraits<MM>::words] = t.y; d[2 % BfpTraits<MM>::words] = t.z; d[3 % BfpTraits<MM>::words] = t.w;
+                } else if (MM == 3) {
+                    uint2 t = *reinterpret_cast<const uint2 *>(q);
+                    d[0] = t.x; d[1 % BfpTraits<MM>::words] = t.y;
+                } else {
+                    d[0] = *reinterpret_cast<const uint32_t *>(q);
+                }
+                float v[16];
+                bfp_decode16<MM>(E, d, v);
+                uint8_t *p = ob + lane * Cfg::pitch + bc * 16 * ES;
+                if (ES == 4) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        *reinterpret_cast<float4 *>(p + 16 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                } else {
+                    // at most 7 significant bits: the upper half of the binary32 is the exact bfloat16
+                    uint32_t h[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++)
+                        h[j] = __byte_perm(__float_as_uint(v[2 * j]), __float_as_uint(v[2 * j + 1]), 0x7632);
+                    *reinterpret_cast<uint4 *>(p) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4 *>(p + 16) = make_uint4(h[4], h[5], h[6], h[7]);
+                }
+            }
+        } else {
+            constexpr int cpr = ES;
+            constexpr int chunks_per_tile = 64 * cpr;
+            const int nchunks = (int)m.ntiles * chunks_per_tile;
+            for (int c = tid; c < nchunks; c += kUConsumerThreads) {
+                const int t = c / chunks_per_tile, k = c % chunks_per_tile;
+                const int f = k / (16 * cpr), r16 = (k / cpr) % 16, part = k % cpr;
+                const int row = (f >> 1) * 16 + r16;
+                const uint4 v = *reinterpret_cast<const uint4 *>(stage + t * rec + hdr + k * 16);
+                *reinterpret_cast<uint4 *>(ob + row * Cfg::pitch + t * 32 * ES + (f & 1) * 16 * ES + part * 16) = v;
+            }
+        }
+        fence_async_smem();
+        if (warp == 0) bulk_wait_read_all();  // the previous item's row stores have left shared memory
+        if (named_bar_or(1, kUConsumerThreads, !ok)) break;
+        if (tid == 0) mbar_arrive(&empty[s]);
+        if (warp == 0) {
+            uint8_t *dst = ptrs.dst[m.b] + (uint64_t)m.w * job.stride_w + (uint64_t)m.z * job.stride_z +
+                           ((uint64_t)m.rt * 32u + lane) * job.stride_r + (uint64_t)m.ct0 * 32u * ES;
+            bulk_s2g(dst, ob + lane * Cfg::pitch, m.ntiles * 32u * ES);
+            bulk_commit();
+        }
+    }
+    if (warp == 0) bulk_wait_all();
+}
+
+// ------------------------------------------------------------------------------------------------
+// direct kernel
+// ------------------------------------------------------------------------------------------------
+template <int M, int ES>
+__global__ void __launch_bounds__(256)
+unpack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ PtrTable ptrs, int batch, int vec_ok)
+{
+    const int lane = threadIdx.x & 31;
+    const uint64_t warps_total = (uint64_t)gridDim.x * (blockDim.x >> 5);
+    const uint64_t warp_id = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint64_t tiles_per_tensor = (uint64_t)job.W * job.Z * job.Rt * job.Ct;
+    const uint64_t units = (uint64_t)batch * tiles_per_tensor * 8u;
+    const uint32_t hdr = job.header_bytes;
+    for (uint64_t u = warp_id; u < units; u += warps_total) {
+        const uint32_t hf = (uint32_t)(u & 7u);
+        uint64_t t = u >> 3;
+        const uint32_t ct = (uint32_t)(t % job.Ct); t /= job.Ct;
+        const uint32_t rt = (uint32_t)(t % job.Rt); t /= job.Rt;
+        const uint32_t z = (uint32_t)(t % job.Z); t /= job.Z;
+        const uint32_t w = (uint32_t)(t % job.W);
+        const uint32_t b = (uint32_t)(t / job.W);
+        const uint32_t face = hf >> 1, half = hf & 1u;
+        const uint32_t fr = half * 8u + (lane >> 2);
+        const uint64_t row = (uint64_t)rt * 32u + (face >> 1) * 16u + fr;
+        const uint64_t col = (uint64_t)ct * 32u + (face & 1u) * 16u + (lane & 3) * 4u;
+        uint8_t *p = ptrs.dst[b] + (uint64_t)w * job.stride_w + (uint64_t)z * job.stride_z + row * job.stride_r + col * ES;
+        const uint8_t *r = ptrs.src[b] + tile_record_offset(job, w, z, rt, ct) + hdr;
+        const uint32_t blk = face * 16u + fr;
+        uint32_t x[4];
+        if (M > 0) {
+            constexpr int MM = M > 0 ? M : 7;
+            const uint32_t E = r[blk];
+            const uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
+            uint32_t packed;
+            if (MM == 7) packed = reinterpret_cast<const uint32_t *>(q)[lane & 3];
+            else if (MM == 3) packed = reinterpret_cast<const uint16_t *>(q)[lane & 3];
+            else packed = q[lane & 3];
+            float post;
+            const float sc = bfp_block_scale<MM>(E, post);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t d = packed >> (i * (MM + 1));
+                const uint32_t qb = kMagicBits | (d & BfpTraits<MM>::qmax);
+                const uint32_t signbit = (d << (31 - MM)) & 0x80000000u;
+                float mag = __fmul_rn(__fadd_rn(__uint_as_float(qb), -12582912.0f), sc);
+                if (MM == 1) mag = __fmul_rn(mag, post);
+                x[i] = __float_as_uint(__fadd_rn(__uint_as_float(__float_as_uint(mag) | signbit), 0.0f));
+                if (ES == 2) x[i] >>= 16;
+            }
+        } else {
+            const uint8_t *q = r + ((uint64_t)blk * 16u + (lane & 3) * 4u) * ES;
+            if (ES == 4) {
+                uint4 v = *reinterpret_cast<const uint4 *>(q);
+                x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+            } else if (ES == 2) {
+                uint2 v = *reinterpret_cast<const uint2 *>(q);
+                x[0] = v.x & 0xffffu; x[1] = v.x >> 16; x[2] = v.y & 0xffffu; x[3] = v.y >> 16;
+            } else {
+                uint32_t v = *reinterpret_cast<const uint32_t *>(q);
+                x[0] = v & 0xffu; x[1] = (v >> 8) & 0xffu; x[2] = (v >> 16) & 0xffu; x[3] = v >> 24;
+            }
+        }
+        if (ES == 4) {
+            if (vec_ok) {
+                *reinterpret_cast<uint4 *>(p) = make_uint4(x[0], x[1], x[2], x[3]);
+            } else if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) reinterpret_cast<uint32_t *>(p)[i] = x[i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; i++) p[i] = (uint8_t)(x[i >> 2] >> (8 * (i & 3)));
+            }
+        } else if (ES == 2) {
+            if (vec_ok) {
+                *reinterpret_cast<uint2 *>(p) = make_uint2(x[0] | (x[1] << 16), x[2] | (x[3] << 16));
+            } else if ((reinterpret_cast<uintptr_t>(p) & 1u) == 0) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) reinterpret_cast<uint16_t *>(p)[i] = (uint16_t)x[i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; i++) p[i] = (uint8_t)(x[i >> 1] >> (8 * (i & 1)));
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; i++) p[i] = (uint8_t)x[i];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host launchers
+// ------------------------------------------------------------------------------------------------
+template <int M, int ES>
+static cudaError_t launch_ustaged(const TileJob &job, const PtrTable &ptrs, int sm_count, cudaStream_t stream,
+                                  unsigned int *status)
+{
+    using Cfg = UnpackCfg<M, ES>;
+    static int per_sm_cache[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev &= 63;
+    if (per_sm_cache[dev] == 0) {
+        cudaError_t e = cudaFuncSetAttribute(unpack_staged_kernel<M, ES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             Cfg::smem_bytes);
+        if (e != cudaSuccess) return e;
+        int n = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, unpack_staged_kernel<M, ES>, kUStagedThreads,
+                                                          Cfg::smem_bytes);
+        if (e != cudaSuccess) return e;
+        per_sm_cache[dev] = n < 1 ? 1 : (n > 4 ? 4 : n);
+    }
+    uint32_t grid = (uint32_t)(sm_count * per_sm_cache[dev]);
+    if (grid > job.total_items) grid = job.total_items;
+    unpack_staged_kernel<M, ES><<<grid, kUStagedThreads, Cfg::smem_bytes, stream>>>(job, ptrs, status);
+    return cudaGetLastError();
+}
+
+template <int M, int ES>
+static cudaError_t launch_udirect(const TileJob &job, const PtrTable &ptrs, int batch, int vec_ok, int sm_count,
+                                  cudaStream_t stream)
+{
+    const uint64_t units = (uint64_t)batch * job.W * job.Z * job.Rt * job.Ct * 8u;
+    uint64_t blocks = (units + 7) / 8;
+    const uint64_t cap = (uint64_t)sm_count * 32;
+    if (blocks > cap) blocks = cap;
+    unpack_direct_kernel<M, ES><<<(unsigned)blocks, 256, 0, stream>>>(job, ptrs, batch, vec_ok);
+    return cudaGetLastError();
+}
+
+// mant_bits 7/3/1 = Bfp decode, 0 = plain relayout; es = destination element bytes.
+cudaError_t launch_untilize(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int path,
+                            int vec_ok, int sm_count, cudaStream_t stream, unsigned int *status)
+{
+#define BUDA_DISPATCH(MM, EE)                                                                   \
+    if (mant_bits == MM && es == EE)                                                            \
+        return path == 0 ? launch_ustaged<MM, EE>(job, ptrs, sm_count, stream, status)          \
+                         : launch_udirect<MM, EE>(job, ptrs, batch, vec_ok, sm_count, stream);
+    BUDA_DISPATCH(7, 4)
+    BUDA_DISPATCH(3, 4)
+    BUDA_DISPATCH(1, 4)
+    BUDA_DISPATCH(7, 2)
+    BUDA_DISPATCH(3, 2)
+    BUDA_DISPATCH(1, 2)
+    BUDA_DISPATCH(0, 4)
+    BUDA_DISPATCH(0, 2)
+    BUDA_DISPATCH(0, 1)
+#undef BUDA_DISPATCH
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace buda

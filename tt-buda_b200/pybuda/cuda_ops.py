@@ -1,0 +1,214 @@
+"""Device-resident entry points: the data-format kernels applied to CUDA torch tensors.
+
+torch is used for device memory and streams only; every byte of arithmetic happens in
+libbuda_cuda.so (hand-written sm_100a kernels) reached through its C ABI.  Functions raise if
+the tensor is not on a CUDA device: there is no CPU path here.
+"""
+import ctypes
+import enum
+
+import torch
+
+from . import _cabi
+from ._cabi import QueueGeom, check
+
+
+class DF(enum.IntEnum):
+    """Integer values of the reference's DataFormat (pybuda/csrc/lower_to_buda/common.hpp:92-111)."""
+
+    Float32 = 0
+    Float16 = 1
+    Bfp8 = 2
+    Bfp4 = 3
+    Bfp2 = 11
+    Float16_b = 5
+    Bfp8_b = 6
+    Bfp4_b = 7
+    Bfp2_b = 15
+    Lf8 = 10
+    UInt16 = 12
+    Int8 = 14
+    Int32 = 8
+    RawUInt8 = 0xF0
+    RawUInt16 = 0xF1
+    RawUInt32 = 0xF2
+    Invalid = 0xFF
+
+
+_TORCH_TO_DF = {
+    torch.float32: DF.Float32, torch.bfloat16: DF.Float16_b, torch.float16: DF.Float16,
+    torch.int8: DF.Int8, torch.int32: DF.Int32, torch.uint8: DF.RawUInt8, torch.int16: DF.RawUInt16,
+}
+_DF_TO_TORCH = {
+    DF.Float32: torch.float32, DF.Float16_b: torch.bfloat16, DF.Float16: torch.float16, DF.Int8: torch.int8,
+    DF.Int32: torch.int32, DF.RawUInt8: torch.uint8, DF.RawUInt16: torch.int16, DF.RawUInt32: torch.int32,
+    DF.UInt16: torch.int16, DF.Lf8: torch.uint8,
+}
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if not t.is_cuda:
+            raise RuntimeError("pybuda.cuda_ops works on CUDA tensors only (no CPU fallback)")
+
+
+def _desc(t):
+    """[w,z,r,c] shape and byte strides of a tensor of up to 4 dims (leading 1s dropped above 4),
+    as pytorch_tensor_to_tensor_desc builds them (pybuda/pybuda/tensor.py:695-713)."""
+    shape = list(t.shape)
+    strides = list(t.stride())
+    while len(shape) > 4:
+        if shape[0] != 1:
+            raise RuntimeError("Dropping a dimension that's not 1 to reduce shape to 4D: " + str(tuple(t.shape)))
+        shape, strides = shape[1:], strides[1:]
+    while len(shape) < 4:
+        shape = [1] + shape
+        strides = [strides[0] if strides else 1] + strides
+    es = t.element_size()
+    return shape, [s * es for s in strides]
+
+
+def tilize_pack_batch(tensors, dst_df, geom=None, with_header=False, outs=None, path=None):
+    """Tilize (and block-float pack) n same-shaped CUDA tensors into n queue images in one launch.
+    Returns the list of uint8 image tensors."""
+    _need_cuda(*tensors)
+    t0 = tensors[0]
+    shape, strides = _desc(t0)
+    for t in tensors[1:]:
+        if _desc(t) != (shape, strides):
+            raise RuntimeError("tilize_pack_batch needs tensors of one shape and stride pattern")
+    src_df = _TORCH_TO_DF[t0.dtype]
+    if geom is None:
+        geom = QueueGeom.for_shape(shape)
+    nbytes = _cabi.tilized_bytes(geom, shape, int(dst_df), with_header)
+    if outs is None:
+        outs = [torch.empty(nbytes, dtype=torch.uint8, device=t0.device) for _ in tensors]
+    srcs = _cabi.ptr_array([t.data_ptr() for t in tensors])
+    dsts = _cabi.ptr_array([o.data_ptr() for o in outs])
+    with torch.cuda.device(t0.device):
+        if path is None:
+            rc = _cabi.lib.buda_tilize_pack_batch(len(tensors), srcs, int(src_df), _cabi.u32x4(shape), _cabi.u64x4(strides),
+                                                  ctypes.byref(geom), int(dst_df), int(with_header), dsts, nbytes, _stream())
+        else:
+            rc = _cabi.lib.buda_tilize_pack_batch_path(len(tensors), srcs, int(src_df), _cabi.u32x4(shape),
+                                                       _cabi.u64x4(strides), ctypes.byref(geom), int(dst_df),
+                                                       int(with_header), dsts, nbytes, _stream(), int(path))
+    check(rc)
+    return outs
+
+
+def tilize_pack(t, dst_df, geom=None, with_header=False, out=None, path=None):
+    return tilize_pack_batch([t], dst_df, geom, with_header, None if out is None else [out], path)[0]
+
+
+def unpack_untilize_batch(images, src_df, shape, dtype=torch.float32, geom=None, with_header=False, outs=None, path=None):
+    """Inverse of tilize_pack_batch: n queue images -> n row-major tensors of `shape` and `dtype`."""
+    _need_cuda(*images)
+    if outs is None:
+        outs = [torch.empty(tuple(shape), dtype=dtype, device=images[0].device) for _ in images]
+    shape4, strides = _desc(outs[0])
+    dst_df = _TORCH_TO_DF[outs[0].dtype]
+    if geom is None:
+        geom = QueueGeom.for_shape(shape4)
+    need = _cabi.tilized_bytes(geom, shape4, int(src_df), with_header)
+    for im in images:
+        if im.numel() * im.element_size() < need:
+            raise RuntimeError(f"queue image holds {im.numel() * im.element_size()} bytes, needs {need}")
+    srcs = _cabi.ptr_array([im.data_ptr() for im in images])
+    dsts = _cabi.ptr_array([o.data_ptr() for o in outs])
+    with torch.cuda.device(images[0].device):
+        if path is None:
+            rc = _cabi.lib.buda_unpack_untilize_batch(len(images), srcs, int(src_df), int(with_header), ctypes.byref(geom),
+                                                      dsts, int(dst_df), _cabi.u32x4(shape4), _cabi.u64x4(strides), _stream())
+        else:
+            rc = _cabi.lib.buda_unpack_untilize_batch_path(len(images), srcs, int(src_df), int(with_header),
+                                                           ctypes.byref(geom), dsts, int(dst_df), _cabi.u32x4(shape4),
+                                                           _cabi.u64x4(strides), _stream(), int(path))
+    check(rc)
+    return outs
+
+
+def unpack_untilize(image, src_df, shape, dtype=torch.float32, geom=None, with_header=False, out=None, path=None):
+    return unpack_untilize_batch([image], src_df, shape, dtype, geom, with_header, None if out is None else [out], path)[0]
+
+
+def _scale_args(x, scale, axis):
+    scale = scale.reshape(-1)
+    if scale.numel() == 1:
+        return scale, 1, 1
+    ax = axis if axis >= 0 else x.dim() + axis
+    if x.shape[ax] != scale.numel():
+        raise RuntimeError(f"scale has {scale.numel()} entries, axis {axis} of the input has {x.shape[ax]}")
+    inner = 1
+    for d in x.shape[ax + 1:]:
+        inner *= d
+    return scale, scale.numel(), inner
+
+
+def quantize(x, scale, zero_point, axis=-1, buda=False, lo=-128.0, hi=127.0):
+    """Quantize (divide by scale) or BudaQuantize (multiply by scale): float32 -> int8."""
+    _need_cuda(x, scale)
+    x = x.contiguous().float()
+    s, sl, inner = _scale_args(x, scale.float().contiguous(), axis)
+    out = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    with torch.cuda.device(x.device):
+        check(_cabi.lib.buda_quantize(x.data_ptr(), x.numel(), s.data_ptr(), sl, inner, float(zero_point), int(buda),
+                                      float(lo), float(hi), out.data_ptr(), _stream()))
+    return out
+
+
+def dequantize(x, scale, zero_point, axis=-1):
+    _need_cuda(x, scale)
+    x = x.contiguous()
+    assert x.dtype == torch.int8
+    s, sl, inner = _scale_args(x, scale.float().contiguous(), axis)
+    out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(_cabi.lib.buda_dequantize(x.data_ptr(), x.numel(), s.data_ptr(), sl, inner, float(zero_point),
+                                        out.data_ptr(), _stream()))
+    return out
+
+
+def requantize(x, inp_scale, out_scale, out_zp, axis=-1, lo=-128.0, hi=127.0):
+    """Requantize: int32 -> int8 with scale inp_scale / out_scale."""
+    _need_cuda(x, inp_scale, out_scale)
+    x = x.contiguous()
+    assert x.dtype == torch.int32
+    a, sl, inner = _scale_args(x, inp_scale.float().contiguous(), axis)
+    b = out_scale.float().reshape(-1).expand(a.shape).contiguous()
+    out = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    with torch.cuda.device(x.device):
+        check(_cabi.lib.buda_requantize(x.data_ptr(), x.numel(), a.data_ptr(), b.data_ptr(), sl, inner, float(out_zp), 0,
+                                        float(lo), float(hi), out.data_ptr(), _stream()))
+    return out
+
+
+def buda_requantize(x, scale, zp, axis=-1, lo=-128.0, hi=127.0):
+    """BudaRequantize: int32 -> int8 with the given (already combined) scale."""
+    _need_cuda(x, scale)
+    x = x.contiguous()
+    assert x.dtype == torch.int32
+    a, sl, inner = _scale_args(x, scale.float().contiguous(), axis)
+    out = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    with torch.cuda.device(x.device):
+        check(_cabi.lib.buda_requantize(x.data_ptr(), x.numel(), a.data_ptr(), None, sl, inner, float(zp), 1, float(lo),
+                                        float(hi), out.data_ptr(), _stream()))
+    return out
+
+
+def bfp8b_matmul(a, w_image, n, out=None):
+    """C = A @ W with A bfloat16 [M,K] and W the Bfp8_b queue image of a [K,N] tensor (default
+    geometry, no header).  Returns bfloat16 [M,N]."""
+    _need_cuda(a, w_image)
+    assert a.dtype == torch.bfloat16 and a.dim() == 2 and a.stride(1) == 1
+    m, k = a.shape
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+    with torch.cuda.device(a.device):
+        check(_cabi.lib.buda_bfp8b_gemm(a.data_ptr(), m, k, a.stride(0), w_image.data_ptr(), n, out.data_ptr(),
+                                        out.stride(0), _stream()))
+    return out
