@@ -46,34 +46,67 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons (NVML, read-only queries) while the timed region runs."""
 
-    def __init__(self, index):
+    def __init__(self, index, period_s=0.01):
         self.index = index
+        self.period = period_s
         self.samples = []
         self.reasons = set()
         self.max_mhz = None
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, daemon=True)
+        self._nvml = None
+        self._h = None
+        try:
+            import pynvml
 
-    def _run(self):
+            pynvml.nvmlInit()
+            # NVML indexes physical devices; honour CUDA_VISIBLE_DEVICES when it lists ordinals
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            phys = index
+            if vis and all(v.strip().isdigit() for v in vis.split(",")):
+                phys = int(vis.split(",")[index])
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
+        except Exception:
+            self._nvml = None
+
+    def _sample_nvml(self):
+        n = self._nvml
+        self.samples.append(float(n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM)))
+        r = n.nvmlDeviceGetCurrentClocksEventReasons(self._h) if hasattr(n, "nvmlDeviceGetCurrentClocksEventReasons") \
+            else n.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+        for name, bit in (("hw_slowdown", 0x8), ("sw_power_cap", 0x4), ("sw_thermal_slowdown", 0x20),
+                          ("hw_thermal_slowdown", 0x40), ("hw_power_brake_slowdown", 0x80)):
+            if r & bit:
+                self.reasons.add(name)
+
+    def _sample_smi(self):
         q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q, "--format=csv,noheader,nounits"],
+                             capture_output=True, text=True, timeout=5).stdout
+        f = [x.strip() for x in out.strip().split(",")]
+        if len(f) >= 6:
+            self.samples.append(float(f[0]))
+            self.max_mhz = float(f[1])
+            for nme, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    self.reasons.add(nme)
+
+    def _run(self):
         while not self._stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q,
-                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
-                f = [s.strip() for s in out.strip().split(",")]
-                if len(f) >= 6:
-                    self.samples.append(float(f[0]))
-                    self.max_mhz = float(f[1])
-                    for n, v in zip(names, f[2:6]):
-                        if v.lower().startswith("active"):
-                            self.reasons.add(n)
+                if self._nvml is not None:
+                    self._sample_nvml()
+                else:
+                    self._sample_smi()
             except Exception:
                 pass
-            self._stop.wait(0.2)
+            self._stop.wait(self.period if self._nvml is not None else 0.2)
 
     def __enter__(self):
         self._thread.start()
@@ -86,14 +119,14 @@ class ClockSampler:
     def summary(self):
         s = sorted(self.samples)
         return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
-                "samples": len(s)}
+                "samples": len(s), "source": "nvml" if self._nvml is not None else "nvidia-smi"}
 
 
-def make_batch(torch, device, seed0):
+def make_batch(torch, device, seed0, n):
     """Synthetic batch with the value distribution of the config (generated on the device)."""
     xs = []
     g = torch.Generator(device=device)
-    for i in range(N_TENSORS):
+    for i in range(n):
         g.manual_seed(seed0 + i)
         x = torch.randn(SHAPE, generator=g, device=device)
         x = torch.where(torch.rand(SHAPE, generator=g, device=device) < 0.01, x * 1e3, x)
@@ -142,11 +175,15 @@ def run_reference(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary kernels' figures")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler captures)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (for profiler captures)")
+    ap.add_argument("--tensors", type=int, default=N_TENSORS,
+                    help="tensors per GPU batch; anything but 64 is a reduced case for profiler captures")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -184,9 +221,10 @@ def main():
         return float(t.item())
 
     hbm_peak, peak_kind = peaks()
-    xs = make_batch(torch, dev, 1000 + N_TENSORS * rank)
-    outs = [torch.empty(IMAGE_BYTES, dtype=torch.uint8, device=dev) for _ in range(N_TENSORS)]
-    algo_bytes_step = N_TENSORS * ELEMS * BYTES_PER_ELEM
+    NT = args.tensors
+    xs = make_batch(torch, dev, 1000 + N_TENSORS * rank, NT)
+    outs = [torch.empty(IMAGE_BYTES, dtype=torch.uint8, device=dev) for _ in range(NT)]
+    algo_bytes_step = NT * ELEMS * BYTES_PER_ELEM
 
     def step():
         cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b, outs=outs)
@@ -219,10 +257,12 @@ def main():
     # ------------------------------------------------------------------ e2e: host buffers in and out
     e2e = None
     try:
-        hx = [torch.empty(SHAPE, dtype=torch.float32).pin_memory() for _ in range(N_TENSORS)]
+        if args.no_e2e:
+            raise RuntimeError("skipped (--no-e2e)")
+        hx = [torch.empty(SHAPE, dtype=torch.float32).pin_memory() for _ in range(NT)]
         for h, x in zip(hx, xs):
             h.copy_(x)
-        himg = [torch.empty(IMAGE_BYTES, dtype=torch.uint8).pin_memory() for _ in range(N_TENSORS)]
+        himg = [torch.empty(IMAGE_BYTES, dtype=torch.uint8).pin_memory() for _ in range(NT)]
         geom = _cabi.QueueGeom.for_shape(SHAPE)
         shape_c, strides_c = _cabi.u32x4(SHAPE), _cabi.u64x4(_cabi.dense_strides(list(SHAPE), 4))
 
@@ -240,7 +280,7 @@ def main():
         e2e_s = max_over_ranks(time.perf_counter() - t0)
         same = bool(torch.equal(himg[-1], outs[-1].cpu()))
         e2e = {"value": world * args.e2e_steps * algo_bytes_step / e2e_s / 1e9, "unit": "GB/s",
-               "h2d_bytes_per_step": N_TENSORS * ELEMS * 4, "d2h_bytes_per_step": N_TENSORS * IMAGE_BYTES,
+               "h2d_bytes_per_step": NT * ELEMS * 4, "d2h_bytes_per_step": NT * IMAGE_BYTES,
                "steps": args.e2e_steps, "api": "buda_tilize_pack_host (pinned host tensors)", "matches_device_path": same}
         del hx, himg
     except Exception as exc:  # report, never hide
@@ -266,12 +306,13 @@ def main():
         try:
             for name, df, ib in (("pack_bfp4_b", cuda_ops.DF.Bfp4_b, 9437184), ("pack_bfp2_b", cuda_ops.DF.Bfp2_b, 5242880)):
                 o2 = [o[:ib] for o in outs]
-                extras[name] = timed(lambda: cuda_ops.tilize_pack_batch(xs, df, outs=o2), N_TENSORS * (ELEMS * 4 + ib))
+                extras[name] = timed(lambda: cuda_ops.tilize_pack_batch(xs, df, outs=o2), NT * (ELEMS * 4 + ib))
             extras["pack_bfp8_b_direct_kernel"] = timed(
                 lambda: cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b, outs=outs, path=1), algo_bytes_step)
-            ys = [torch.empty(SHAPE, dtype=torch.float32, device=dev) for _ in range(16)]
+            nu = min(16, NT)
+            ys = [torch.empty(SHAPE, dtype=torch.float32, device=dev) for _ in range(nu)]
             extras["unpack_bfp8_b"] = timed(
-                lambda: cuda_ops.unpack_untilize_batch(outs[:16], cuda_ops.DF.Bfp8_b, SHAPE, outs=ys), 16 * ELEMS * BYTES_PER_ELEM)
+                lambda: cuda_ops.unpack_untilize_batch(outs[:nu], cuda_ops.DF.Bfp8_b, SHAPE, outs=ys), nu * ELEMS * BYTES_PER_ELEM)
             del ys
             n3 = 32 * 1024 * 1024
             x3 = torch.rand(32, 1024, 1024, device=dev) * 12 - 6
@@ -298,12 +339,12 @@ def main():
 
     # ------------------------------------------------------------------ CPU baseline (rank 0, N = 1 only)
     cpu = None
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and not args.no_cpu:
         try:
             from oracle import budaref as R
 
             R.build()
-            n_cpu = 8
+            n_cpu = min(8, NT)
             hs = [x.cpu().numpy() for x in xs[:n_cpu]]
             R.tilize_pack(hs[0], R.Bfp8_b)
             t0 = time.perf_counter()
@@ -320,7 +361,7 @@ def main():
             "metric": "bfp8b_tilize_pack_throughput", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "u8", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "per_gpu_batch": N_TENSORS, "l2": "inputs (4 GiB per step) larger than L2",
+            "config": {"workload": WORKLOAD if NT == N_TENSORS else WORKLOAD + f" (REDUCED to {NT} tensors)", "per_gpu_batch": NT, "l2": "inputs (4 GiB per step) larger than L2",
                        "launches_per_step": 1},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": None, "peak_kind": peak_kind, "kernel": "pack_staged_kernel<7,4>",
