@@ -136,6 +136,40 @@ int buda_unpack_untilize_host(const void *src_host, int src_df, int with_header,
                               void *dst_host, int dst_df, const uint32_t shape[4],
                               const uint64_t strides_bytes[4], void *stream);
 
+/* ------------------------------------------------------------------ device-resident queues
+ * A queue is a ring of `slots` entries per grid core in device memory: core buffers of
+ * slots * t*mblock_m*mblock_n*ublock_rt*ublock_ct tile records, laid out core after core (the
+ * bufq_num_slots / bufq_entry_size of the reference's DramIODesc, backend_api.cpp:428-447).
+ * Entry w of the tensor goes to slot (first_slot + w) % slots.  These are the device halves of
+ * tt::backend::push_input and get_output (backend_api.cpp:688-701): the host layer keeps the
+ * read / write pointers, this library moves and converts the data.  With a host tensor
+ * (src_is_host / dst_is_host != 0) the call copies in slices overlapped with the kernel and blocks
+ * until done; with a device tensor it only enqueues on `stream`. */
+int64_t buda_queue_bytes(const buda_queue_geom *geom, int df, int with_header, uint32_t slots);
+
+int buda_queue_write(const void *src, int src_is_host, int src_df, const uint32_t shape[4],
+                     const uint64_t strides_bytes[4], const buda_queue_geom *geom, int dst_df, int with_header,
+                     void *queue_base, uint32_t slots, uint32_t first_slot, void *stream);
+
+int buda_queue_read(const void *queue_base, int src_df, int with_header, const buda_queue_geom *geom, uint32_t slots,
+                    uint32_t first_slot, void *dst, int dst_is_host, int dst_df, const uint32_t shape[4],
+                    const uint64_t strides_bytes[4], void *stream);
+
+/* ------------------------------------------------------------------ memory and device plumbing
+ * What the host layer needs so that it links against this library only and never against the
+ * CUDA runtime itself.  No counterpart in the reference (its backend owns device memory). */
+int buda_malloc(void **ptr, uint64_t bytes);
+int buda_free(void *ptr);
+int buda_host_alloc(void **ptr, uint64_t bytes);  /* pinned host memory */
+int buda_host_free(void *ptr);
+/* kind 0 host->device, 1 device->host, 2 device->device; returns after the copy is complete */
+int buda_memcpy(void *dst, const void *src, uint64_t bytes, int kind, void *stream);
+int buda_stream_synchronize(void *stream);
+int buda_pointer_is_device(const void *ptr, int *is_device, int *device_ordinal);
+int buda_get_device(int *ordinal);
+int buda_set_device(int ordinal);
+int buda_device_count(int *count);
+
 /* ------------------------------------------------------------------ golden int8 quantise ops
  * The scale used for element i is scale[(i / inner) % scale_len]; scale_len == 1 is a per-tensor
  * scale, otherwise inner is the product of the dims after the quantisation axis

@@ -53,6 +53,7 @@ struct TileJob {
     uint64_t tiles_per_entry;           // per grid core
     uint64_t buf_bytes;                 // bytes of one grid core's buffer (all W entries)
     int trivial_geom;                   // grid 1x1, ublock 1x1, order R: address = (z*Rt + rt)*Ct + ct
+    uint32_t slots, slot0;              // ring queue: entry w lives in slot (slot0 + w) % slots; slots == 0: dense image
 };
 
 struct PtrTable {
@@ -66,6 +67,7 @@ struct PtrTable {
 __host__ __device__ inline uint64_t tile_record_offset(const TileJob &j, uint32_t w, uint32_t z, uint32_t rt,
                                                        uint32_t ct)
 {
+    if (j.slots) w = (j.slot0 + w) % j.slots;
     if (j.trivial_geom) {
         uint64_t addr = ((uint64_t)z * j.Rt + rt) * j.Ct + ct;
         return ((uint64_t)w * j.tiles_per_entry + addr) * j.tile_bytes;

@@ -91,7 +91,7 @@ bool is_bfp_b(int df) { return df == BUDA_DF_Bfp8_b || df == BUDA_DF_Bfp4_b || d
 
 // Fills the job for a [w,z,R,C] tensor in a queue of geometry g holding format qdf.
 int make_job(const uint32_t shape[4], const uint64_t strides[4], const buda_queue_geom *g, int qdf, int with_header,
-             int batch, TileJob &j)
+             int batch, TileJob &j, uint32_t slots = 0, uint32_t slot0 = 0)
 {
     if (!shape || !strides || !g) return fail(BUDA_RUNTIME_ERROR, "null shape / strides / geometry");
     const int64_t tb = buda_tile_bytes(qdf, with_header);
@@ -123,7 +123,11 @@ int make_job(const uint32_t shape[4], const uint64_t strides[4], const buda_queu
     j.tile_bytes = (uint32_t)tb;
     j.header_bytes = with_header ? 32u : 0u;
     j.tiles_per_entry = (uint64_t)g->t * g->mblock_m * g->mblock_n * g->ublock_rt * g->ublock_ct;
-    j.buf_bytes = (uint64_t)j.W * j.tiles_per_entry * j.tile_bytes;
+    if (slots && (slot0 >= slots || j.W > slots))
+        return fail(BUDA_RUNTIME_ERROR, "ring of %u slots cannot take %u entries at slot %u", slots, j.W, slot0);
+    j.slots = slots;
+    j.slot0 = slot0;
+    j.buf_bytes = (uint64_t)(slots ? slots : j.W) * j.tiles_per_entry * j.tile_bytes;
     j.trivial_geom = (g->grid_r == 1 && g->grid_c == 1 && g->ublock_rt == 1 && g->ublock_ct == 1 && g->ublock_order == 0);
     return BUDA_SUCCESS;
 }
@@ -171,7 +175,7 @@ int check_queue_ptrs_aligned(const void *const *q, int n)
 
 int tilize_device(int n, const void *const *srcs, int src_df, const uint32_t shape[4], const uint64_t strides[4],
                   const buda_queue_geom *geom, int dst_df, int with_header, void *const *dsts, uint64_t dst_bytes_each,
-                  cudaStream_t stream, int force_path)
+                  cudaStream_t stream, int force_path, uint32_t slots = 0, uint32_t slot0 = 0)
 {
     DevCtx *ctx;
     if (int rc = get_ctx(&ctx)) return rc;
@@ -186,7 +190,7 @@ int tilize_device(int n, const void *const *srcs, int src_df, const uint32_t sha
     for (int b0 = 0; b0 < n; b0 += kMaxBatch) {
         const int nb = (n - b0 < kMaxBatch) ? (n - b0) : kMaxBatch;
         TileJob job;
-        if (int rc = make_job(shape, strides, geom, dst_df, with_header, nb, job)) return rc;
+        if (int rc = make_job(shape, strides, geom, dst_df, with_header, nb, job, slots, slot0)) return rc;
         const uint64_t need = job.buf_bytes * geom->grid_r * geom->grid_c;
         if (dst_bytes_each < need)
             return fail(BUDA_RUNTIME_ERROR, "destination holds %llu bytes, the queue image needs %llu",
@@ -213,7 +217,7 @@ int tilize_device(int n, const void *const *srcs, int src_df, const uint32_t sha
 
 int untilize_device(int n, const void *const *srcs, int src_df, int with_header, const buda_queue_geom *geom,
                     void *const *dsts, int dst_df, const uint32_t shape[4], const uint64_t strides[4], cudaStream_t stream,
-                    int force_path)
+                    int force_path, uint32_t slots = 0, uint32_t slot0 = 0)
 {
     DevCtx *ctx;
     if (int rc = get_ctx(&ctx)) return rc;
@@ -228,7 +232,7 @@ int untilize_device(int n, const void *const *srcs, int src_df, int with_header,
     for (int b0 = 0; b0 < n; b0 += kMaxBatch) {
         const int nb = (n - b0 < kMaxBatch) ? (n - b0) : kMaxBatch;
         TileJob job;
-        if (int rc = make_job(shape, strides, geom, src_df, with_header, nb, job)) return rc;
+        if (int rc = make_job(shape, strides, geom, src_df, with_header, nb, job, slots, slot0)) return rc;
         PtrTable pt;
         memset(&pt, 0, sizeof(pt));
         for (int b = 0; b < nb; b++) {
@@ -276,7 +280,7 @@ int ensure_pipe(DevCtx *c, size_t need_a, size_t need_b)
         }
         c->cap_a = need_a;
     }
-    if (need_b > c->cap_b) {
+    if (need_b > c->cap_b && need_b > 0) {
         for (int i = 0; i < kPipeDepth; i++) {
             if (c->stage_b[i]) cudaFree(c->stage_b[i]);
             c->stage_b[i] = nullptr;
@@ -324,19 +328,22 @@ int status_after_sync(DevCtx *ctx)
     return BUDA_SUCCESS;
 }
 
-// direction 0: host row-major -> host queue image; 1: host queue image -> host row-major
+// The row-major tensor is in HOST memory; the queue image is in host memory (q_on_device == 0) or
+// already in device memory, possibly as a ring of `slots` entries (q_on_device == 1).
+// direction 0: row-major -> queue image; 1: queue image -> row-major.
 int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_t shape[4], const uint64_t strides[4],
-                  const buda_queue_geom *geom, int q_df, int with_header, const void *q_host_c, uint64_t q_bytes)
+                  const buda_queue_geom *geom, int q_df, int with_header, const void *q_c, uint64_t q_bytes, int q_on_device,
+                  uint32_t slots, uint32_t slot0)
 {
     DevCtx *ctx;
     if (int rc = get_ctx(&ctx)) return rc;
-    if (!rm_host_c || !q_host_c) return fail(BUDA_RUNTIME_ERROR, "null host buffer");
+    if (!rm_host_c || !q_c) return fail(BUDA_RUNTIME_ERROR, "null buffer");
     uint8_t *rm_host = (uint8_t *)rm_host_c;
-    uint8_t *q_host = (uint8_t *)q_host_c;
+    uint8_t *q_mem = (uint8_t *)q_c;
     int mant, es;
     if (int rc = classify(rm_df, q_df, mant, es)) return rc;
     TileJob full;
-    if (int rc = make_job(shape, strides, geom, q_df, with_header, 1, full)) return rc;
+    if (int rc = make_job(shape, strides, geom, q_df, with_header, 1, full, slots, slot0)) return rc;
     if (strides[3] != (uint64_t)es) return fail(BUDA_RUNTIME_ERROR, "innermost stride must equal the element size");
     const uint64_t image_bytes = full.buf_bytes * geom->grid_r * geom->grid_c;
     if (q_bytes < image_bytes)
@@ -351,7 +358,7 @@ int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_
     const uint32_t slice_bands = plan.sliced ? plan.bands_per_slice : full.Rt;
     const uint64_t slice_a = plan.sliced ? (uint64_t)slice_bands * 32u * row_bytes
                                          : (uint64_t)shape[0] * shape[1] * shape[2] * row_bytes;
-    const uint64_t slice_b = plan.sliced ? (uint64_t)slice_bands * full.Ct * full.tile_bytes : image_bytes;
+    const uint64_t slice_b = q_on_device ? 0 : (plan.sliced ? (uint64_t)slice_bands * full.Ct * full.tile_bytes : image_bytes);
     if (int rc = ensure_pipe(ctx, slice_a, slice_b)) return rc;
 
     cudaError_t e = cudaSuccess;
@@ -365,8 +372,9 @@ int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_
     };
 
     if (!plan.sliced) {
-        // one shot: whole tensor in slot 0
-        uint8_t *a = ctx->stage_a[0], *b = ctx->stage_b[0];
+        // one shot: the whole tensor goes through slot 0
+        uint8_t *a = ctx->stage_a[0];
+        uint8_t *b = q_on_device ? q_mem : ctx->stage_b[0];
         const uint64_t dense[4] = {(uint64_t)shape[1] * shape[2] * row_bytes, (uint64_t)shape[2] * row_bytes, row_bytes,
                                    (uint64_t)es};
         const void *srcs[1];
@@ -378,14 +386,16 @@ int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_
                                   ctx->s_comp, true);
             if (e != cudaSuccess) return cuda_fail(e, "host to device copy");
             srcs[0] = a; dsts[0] = b;
-            if (int rc = tilize_device(1, srcs, rm_df, shape, dense, geom, q_df, with_header, dsts, image_bytes, ctx->s_comp, -1))
+            if (int rc = tilize_device(1, srcs, rm_df, shape, dense, geom, q_df, with_header, dsts, image_bytes, ctx->s_comp, -1,
+                                       q_on_device ? slots : 0, q_on_device ? slot0 : 0))
                 return rc;
-            e = cudaMemcpyAsync(q_host, b, image_bytes, cudaMemcpyDeviceToHost, ctx->s_comp);
+            if (!q_on_device) e = cudaMemcpyAsync(q_mem, b, image_bytes, cudaMemcpyDeviceToHost, ctx->s_comp);
         } else {
-            e = cudaMemcpyAsync(b, q_host, image_bytes, cudaMemcpyHostToDevice, ctx->s_comp);
+            if (!q_on_device) e = cudaMemcpyAsync(b, q_mem, image_bytes, cudaMemcpyHostToDevice, ctx->s_comp);
             if (e != cudaSuccess) return cuda_fail(e, "host to device copy");
             srcs[0] = b; dsts[0] = a;
-            if (int rc = untilize_device(1, srcs, q_df, with_header, geom, dsts, rm_df, shape, dense, ctx->s_comp, -1))
+            if (int rc = untilize_device(1, srcs, q_df, with_header, geom, dsts, rm_df, shape, dense, ctx->s_comp, -1,
+                                         q_on_device ? slots : 0, q_on_device ? slot0 : 0))
                 return rc;
             for (uint32_t w = 0; w < shape[0] && e == cudaSuccess; w++)
                 for (uint32_t z = 0; z < shape[1] && e == cudaSuccess; z++)
@@ -398,7 +408,7 @@ int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_
         return status_after_sync(ctx);
     }
 
-    // sliced: each slice is a [1,1,bands*32,C] tensor in a one-plane queue of its own
+    // sliced: each slice is a [1,1,bands*32,C] tensor whose records are one contiguous run of the image
     uint64_t k = 0;
     for (uint32_t w = 0; w < shape[0]; w++) {
         for (uint32_t z = 0; z < shape[1]; z++) {
@@ -412,24 +422,26 @@ int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_
                 buda_queue_geom sg = *geom;
                 sg.t = 1;
                 sg.mblock_m = nb;
-                uint8_t *a = ctx->stage_a[slot], *b = ctx->stage_b[slot];
+                uint8_t *a = ctx->stage_a[slot];
                 uint8_t *rm_ptr = rm_host + w * strides[0] + z * strides[1] + (uint64_t)band0 * 32u * strides[2];
-                uint8_t *q_ptr = q_host + tile_record_offset(full, w, z, band0, 0);
+                uint8_t *q_ptr = q_mem + tile_record_offset(full, w, z, band0, 0);
+                uint8_t *b = q_on_device ? q_ptr : ctx->stage_b[slot];
                 const uint64_t q_len = (uint64_t)nb * full.Ct * full.tile_bytes;
                 const void *srcs[1];
                 void *dsts[1];
-                cudaStream_t first = direction == 0 ? ctx->s_in : ctx->s_in;
-                // the slot is free once the copy-out of its previous slice has finished
+                // the staging slot is free once the last stream that used it has passed ev_out
                 if (k >= (uint64_t)kPipeDepth) {
-                    if ((e = cudaStreamWaitEvent(first, ctx->ev_out[slot], 0)) != cudaSuccess) return cuda_fail(e, "wait");
+                    if ((e = cudaStreamWaitEvent(ctx->s_in, ctx->ev_out[slot], 0)) != cudaSuccess) return cuda_fail(e, "wait");
                 }
+                cudaStream_t kernel_after = ctx->s_in;
                 if (direction == 0) {
                     if ((e = copy_rows(a, rm_ptr, (uint64_t)nb * 32u, ctx->s_in, true)) != cudaSuccess)
                         return cuda_fail(e, "host to device copy");
-                } else {
+                } else if (!q_on_device) {
                     if ((e = cudaMemcpyAsync(b, q_ptr, q_len, cudaMemcpyHostToDevice, ctx->s_in)) != cudaSuccess)
                         return cuda_fail(e, "host to device copy");
                 }
+                (void)kernel_after;
                 cudaEventRecord(ctx->ev_in[slot], ctx->s_in);
                 cudaStreamWaitEvent(ctx->s_comp, ctx->ev_in[slot], 0);
                 if (direction == 0) {
@@ -444,7 +456,7 @@ int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_
                 cudaEventRecord(ctx->ev_comp[slot], ctx->s_comp);
                 cudaStreamWaitEvent(ctx->s_out, ctx->ev_comp[slot], 0);
                 if (direction == 0) {
-                    if ((e = cudaMemcpyAsync(q_ptr, b, q_len, cudaMemcpyDeviceToHost, ctx->s_out)) != cudaSuccess)
+                    if (!q_on_device && (e = cudaMemcpyAsync(q_ptr, b, q_len, cudaMemcpyDeviceToHost, ctx->s_out)) != cudaSuccess)
                         return cuda_fail(e, "device to host copy");
                 } else {
                     if ((e = copy_rows(a, rm_ptr, (uint64_t)nb * 32u, ctx->s_out, false)) != cudaSuccess)
@@ -577,7 +589,7 @@ int buda_tilize_pack_host(const void *src_host, int src_df, const uint32_t shape
                           void *stream)
 {
     (void)stream;
-    return host_pipeline(0, src_host, src_df, shape, strides_bytes, geom, dst_df, with_header, dst_host, dst_bytes);
+    return host_pipeline(0, src_host, src_df, shape, strides_bytes, geom, dst_df, with_header, dst_host, dst_bytes, 0, 0, 0);
 }
 
 int buda_unpack_untilize(const void *src, int src_df, int with_header, const buda_queue_geom *geom, void *dst, int dst_df,
@@ -611,7 +623,130 @@ int buda_unpack_untilize_host(const void *src_host, int src_df, int with_header,
     (void)stream;
     int64_t need = buda_tilized_bytes(geom, shape, src_df, with_header);
     if (need < 0) return fail(BUDA_RUNTIME_ERROR, "tensor does not fit the queue geometry");
-    return host_pipeline(1, dst_host, dst_df, shape, strides_bytes, geom, src_df, with_header, src_host, (uint64_t)need);
+    return host_pipeline(1, dst_host, dst_df, shape, strides_bytes, geom, src_df, with_header, src_host, (uint64_t)need, 0, 0, 0);
+}
+
+int64_t buda_queue_bytes(const buda_queue_geom *geom, int df, int with_header, uint32_t slots)
+{
+    if (!geom) return -1;
+    const int64_t tb = buda_tile_bytes(df, with_header);
+    if (tb < 0 || slots == 0) return -1;
+    return (int64_t)geom->grid_r * geom->grid_c * slots * geom->t * geom->mblock_m * geom->mblock_n * geom->ublock_rt *
+           geom->ublock_ct * tb;
+}
+
+int buda_queue_write(const void *src, int src_is_host, int src_df, const uint32_t shape[4], const uint64_t strides_bytes[4],
+                     const buda_queue_geom *geom, int dst_df, int with_header, void *queue_base, uint32_t slots,
+                     uint32_t first_slot, void *stream)
+{
+    if (slots == 0) return fail(BUDA_RUNTIME_ERROR, "a queue has at least one slot");
+    const int64_t qb = buda_queue_bytes(geom, dst_df, with_header, slots);
+    if (qb < 0) return fail(BUDA_RUNTIME_ERROR, "invalid queue geometry or format");
+    if (src_is_host)
+        return host_pipeline(0, src, src_df, shape, strides_bytes, geom, dst_df, with_header, queue_base, (uint64_t)qb, 1, slots,
+                             first_slot);
+    const void *srcs[1] = {src};
+    void *dsts[1] = {queue_base};
+    return tilize_device(1, srcs, src_df, shape, strides_bytes, geom, dst_df, with_header, dsts, (uint64_t)qb,
+                         (cudaStream_t)stream, -1, slots, first_slot);
+}
+
+int buda_queue_read(const void *queue_base, int src_df, int with_header, const buda_queue_geom *geom, uint32_t slots,
+                    uint32_t first_slot, void *dst, int dst_is_host, int dst_df, const uint32_t shape[4],
+                    const uint64_t strides_bytes[4], void *stream)
+{
+    if (slots == 0) return fail(BUDA_RUNTIME_ERROR, "a queue has at least one slot");
+    const int64_t qb = buda_queue_bytes(geom, src_df, with_header, slots);
+    if (qb < 0) return fail(BUDA_RUNTIME_ERROR, "invalid queue geometry or format");
+    if (dst_is_host)
+        return host_pipeline(1, dst, dst_df, shape, strides_bytes, geom, src_df, with_header, queue_base, (uint64_t)qb, 1, slots,
+                             first_slot);
+    const void *srcs[1] = {queue_base};
+    void *dsts[1] = {dst};
+    return untilize_device(1, srcs, src_df, with_header, geom, dsts, dst_df, shape, strides_bytes, (cudaStream_t)stream, -1,
+                           slots, first_slot);
+}
+
+int buda_malloc(void **ptr, uint64_t bytes)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    if (!ptr) return fail(BUDA_RUNTIME_ERROR, "null argument");
+    cudaError_t e = cudaMalloc(ptr, bytes ? bytes : 1);
+    return e == cudaSuccess ? BUDA_SUCCESS : cuda_fail(e, "device allocation");
+}
+
+int buda_free(void *ptr)
+{
+    cudaError_t e = cudaFree(ptr);
+    return e == cudaSuccess ? BUDA_SUCCESS : cuda_fail(e, "device free");
+}
+
+int buda_host_alloc(void **ptr, uint64_t bytes)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    if (!ptr) return fail(BUDA_RUNTIME_ERROR, "null argument");
+    cudaError_t e = cudaMallocHost(ptr, bytes ? bytes : 1);
+    return e == cudaSuccess ? BUDA_SUCCESS : cuda_fail(e, "pinned host allocation");
+}
+
+int buda_host_free(void *ptr)
+{
+    cudaError_t e = cudaFreeHost(ptr);
+    return e == cudaSuccess ? BUDA_SUCCESS : cuda_fail(e, "pinned host free");
+}
+
+int buda_memcpy(void *dst, const void *src, uint64_t bytes, int kind, void *stream)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    cudaMemcpyKind k = kind == 0 ? cudaMemcpyHostToDevice : kind == 1 ? cudaMemcpyDeviceToHost : cudaMemcpyDeviceToDevice;
+    cudaError_t e = cudaMemcpyAsync(dst, src, bytes, k, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    return e == cudaSuccess ? BUDA_SUCCESS : cuda_fail(e, "memcpy");
+}
+
+int buda_stream_synchronize(void *stream)
+{
+    cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+    return e == cudaSuccess ? BUDA_SUCCESS : cuda_fail(e, "stream synchronize");
+}
+
+int buda_pointer_is_device(const void *ptr, int *is_device, int *device_ordinal)
+{
+    cudaPointerAttributes a;
+    cudaError_t e = cudaPointerGetAttributes(&a, ptr);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return cuda_fail(e, "pointer query");
+    }
+    if (is_device) *is_device = (a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged) ? 1 : 0;
+    if (device_ordinal) *device_ordinal = a.device;
+    return BUDA_SUCCESS;
+}
+
+int buda_get_device(int *ordinal)
+{
+    cudaError_t e = cudaGetDevice(ordinal);
+    return e == cudaSuccess ? BUDA_SUCCESS : cuda_fail(e, "no usable CUDA device (this library has no CPU path)");
+}
+
+int buda_set_device(int ordinal)
+{
+    cudaError_t e = cudaSetDevice(ordinal);
+    return e == cudaSuccess ? BUDA_SUCCESS : cuda_fail(e, "set device");
+}
+
+int buda_device_count(int *count)
+{
+    cudaError_t e = cudaGetDeviceCount(count);
+    if (e != cudaSuccess) {
+        if (count) *count = 0;
+        cudaGetLastError();
+        return cuda_fail(e, "no usable CUDA device (this library has no CPU path)");
+    }
+    return BUDA_SUCCESS;
 }
 
 static int check_quant_args(const void *x, int64_t n, const void *scale, int64_t scale_len, int64_t inner, const void *out)

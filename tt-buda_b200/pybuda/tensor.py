@@ -1,0 +1,498 @@
+"""Tensor wrappers and the torch <-> backend descriptor conversions of the data-format path.
+
+Same names, arguments and results as the reference's pybuda/pybuda/tensor.py for the part of it
+that feeds the converters: dtype <-> DataFormat maps (563-651), descriptor building (653-745),
+padding to 4-D tile-aligned shapes (799-877) and narrowing back (879-954), and the Tensor
+wrappers around a torch value or a descriptor (151-546).  TensorFlow / JAX / sparse / traced
+tensors of the reference are not part of this path.
+"""
+from functools import reduce
+from operator import mul
+from typing import List, Optional, Tuple
+
+import torch
+
+from . import TILE_DIM
+from ._C import DataFormat
+from ._C.backend_api import PytorchTensorDesc, TilizedTensorDesc
+
+SomeTensor = torch.Tensor
+
+
+def align_up_tile(v: int) -> int:
+    return (v + TILE_DIM - 1) // TILE_DIM * TILE_DIM
+
+
+class TensorShape:
+    """Shape of up to four named dims (w, z, r, c counted from the back)."""
+
+    def __init__(self, *dims):
+        self.dims = tuple(int(d) for d in dims)
+
+    def _from_back(self, i):
+        return self.dims[-i] if len(self.dims) >= i else 1
+
+    @property
+    def c(self):
+        return self._from_back(1)
+
+    @property
+    def r(self):
+        return self._from_back(2)
+
+    @property
+    def z(self):
+        return self._from_back(3)
+
+    @property
+    def w(self):
+        return self._from_back(4)
+
+    @property
+    def rt(self):
+        return (self.r + TILE_DIM - 1) // TILE_DIM
+
+    @property
+    def ct(self):
+        return (self.c + TILE_DIM - 1) // TILE_DIM
+
+    def rc_divisible_by_tile_dim(self) -> bool:
+        return self.r % TILE_DIM == 0 and self.c % TILE_DIM == 0
+
+    def get_pytorch_shape(self) -> Tuple[int, ...]:
+        return self.dims
+
+    @classmethod
+    def from_pytorch_tuple(cls, w, z, r, c):
+        return cls(w, z, r, c)
+
+    def numel(self):
+        return reduce(mul, self.dims, 1)
+
+    def __len__(self):
+        return len(self.dims)
+
+    def __getitem__(self, i):
+        return self.dims[i]
+
+    def __repr__(self):
+        return str(self.dims)
+
+    def __eq__(self, other):
+        return tuple(other) == self.dims if not isinstance(other, TensorShape) else other.dims == self.dims
+
+
+# ------------------------------------------------------------------------------------------------
+# torch dtype <-> DataFormat
+# ------------------------------------------------------------------------------------------------
+_DTYPE_TO_DF = {
+    torch.float16: DataFormat.Float16,
+    torch.bfloat16: DataFormat.Float16_b,
+    torch.float32: DataFormat.Float32,
+    torch.int8: DataFormat.Int8,
+    torch.bool: DataFormat.Bfp2_b,
+    torch.int32: DataFormat.Int32,
+    torch.int64: DataFormat.Int8,  # the reference narrows int64 parameters to int8 (with a warning)
+}
+
+_DF_TO_DTYPE = {
+    DataFormat.Float32: torch.float32,
+    DataFormat.Float16: torch.float16,
+    DataFormat.Float16_b: torch.bfloat16,
+    DataFormat.Bfp8_b: torch.bfloat16, DataFormat.Bfp4_b: torch.bfloat16, DataFormat.Bfp2_b: torch.bfloat16,
+    DataFormat.Bfp8: torch.float16, DataFormat.Bfp4: torch.float16, DataFormat.Bfp2: torch.float16,
+    DataFormat.Int8: torch.int8,
+    DataFormat.RawUInt32: torch.int,
+    DataFormat.UInt16: torch.int,
+    DataFormat.Int32: torch.int32,
+}
+
+_EXACT_PAIRS = {
+    DataFormat.Float32: torch.float32, DataFormat.Float16: torch.float16, DataFormat.Float16_b: torch.bfloat16,
+    DataFormat.Int8: torch.int8,
+}
+
+
+def pytorch_dtype_to_buda_dataformat(dtype, fp32_fallback: Optional[DataFormat] = None) -> DataFormat:
+    if isinstance(dtype, DataFormat):
+        return dtype
+    assert isinstance(dtype, torch.dtype)
+    if dtype == torch.float32 and fp32_fallback is not None:
+        return fp32_fallback
+    try:
+        return _DTYPE_TO_DF[dtype]
+    except KeyError:
+        raise RuntimeError("Unsupported torch dtype " + str(dtype))
+
+
+def buda_dataformat_to_pytorch_dtype(data_format: DataFormat) -> torch.dtype:
+    assert isinstance(data_format, DataFormat)
+    try:
+        return _DF_TO_DTYPE[data_format]
+    except KeyError:
+        raise RuntimeError("Unsupported DataFormat for conversion to torch dtype: " + str(data_format))
+
+
+def is_equivalent_data_format(pt_df: torch.dtype, tt_df: DataFormat) -> bool:
+    """True when the torch dtype and the device format hold exactly the same values."""
+    return _EXACT_PAIRS.get(tt_df) == pt_df
+
+
+# ------------------------------------------------------------------------------------------------
+# descriptors
+# ------------------------------------------------------------------------------------------------
+_TILIZE_NDIM = 4
+
+_INFERRED_FORMAT = {
+    torch.float32: DataFormat.Float32, torch.bfloat16: DataFormat.Float16_b, torch.float16: DataFormat.Float16,
+    torch.int32: DataFormat.Int32, torch.int8: DataFormat.Int8,
+}
+
+
+def _to_4d(values: list, what: str, fill) -> list:
+    values = list(values)
+    while len(values) > _TILIZE_NDIM:
+        if what == "shape" and values[0] != 1:
+            raise RuntimeError("Dropping a dimension that's not 1 to reduce shape to 4D: " + str(values))
+        values = values[1:]
+    while len(values) < _TILIZE_NDIM:
+        values = [fill(values)] + values
+    return values
+
+
+def pytorch_tensor_to_tensor_desc(t: torch.Tensor, df: DataFormat = None, element_size=None) -> "PytorchTensorDesc":
+    """Describe a torch tensor (host or CUDA) to the converters: 4-D [w,z,r,c] shape and BYTE strides.
+    With `df` given the tensor is first cast to the torch dtype that format travels as."""
+    if isinstance(t, (PytorchTensorDesc, TilizedTensorDesc)):
+        return t
+    if not t.is_contiguous():
+        t = t.contiguous()
+    if df is None:
+        if t.dtype == torch.int64:
+            t = t.to(torch.int32)  # the reference pushes int64 as raw 32-bit words
+            fmt = DataFormat.RawUInt32
+        elif t.dtype in _INFERRED_FORMAT:
+            fmt = _INFERRED_FORMAT[t.dtype]
+        else:
+            raise RuntimeError("Unsupported torch tensor type for tilization: " + str(t.dtype))
+    else:
+        fmt = df
+        want = buda_dataformat_to_pytorch_dtype(fmt)
+        if t.dtype != want:
+            t = t.type(want)
+
+    dim = 3 if t.dim() == 2 else t.dim()
+    shape = _to_4d(t.shape, "shape", lambda v: 1)
+    strides = _to_4d(t.stride(), "strides", lambda v: v[0])
+    if element_size is None:
+        element_size = t.element_size()
+    return PytorchTensorDesc(t, element_size, fmt, dim, shape, [s * element_size for s in strides])
+
+
+_READBACK_DTYPE = {
+    DataFormat.Float32: torch.float32, DataFormat.Float16_b: torch.bfloat16, DataFormat.Float16: torch.float16,
+    DataFormat.RawUInt32: torch.int,
+}
+
+
+def tensor_desc_to_pytorch_tensor(desc: "PytorchTensorDesc") -> torch.Tensor:
+    """Zero-copy torch view of a (host) descriptor's memory."""
+    try:
+        dtype = _READBACK_DTYPE[desc.format]
+    except KeyError:
+        raise RuntimeError(f"Unsupported tensor type({desc.format}) for untilization")
+    return torch.frombuffer(desc, dtype=dtype).reshape(list(desc.shape))
+
+
+def buffer_to_pytorch_tensor(buf_ptr: int, shape: Tuple, format: DataFormat) -> torch.Tensor:
+    """Torch view of a dense row-major host buffer at address buf_ptr."""
+    sizes = {DataFormat.Float32: 4, DataFormat.Float16_b: 2, DataFormat.Float16: 2}
+    if format not in sizes:
+        raise RuntimeError("Unsupported format")
+    dim = len(shape)
+    shape = list(shape)
+    while len(shape) > _TILIZE_NDIM:
+        if shape[0] != 1:
+            raise RuntimeError("Trimming a dimension that's not 1")
+        shape = shape[1:]
+    shape = [1] * (_TILIZE_NDIM - len(shape)) + shape
+    es = sizes[format]
+    strides = [es] * _TILIZE_NDIM
+    for i in range(_TILIZE_NDIM - 2, -1, -1):
+        strides[i] = strides[i + 1] * shape[i + 1]
+    return tensor_desc_to_pytorch_tensor(PytorchTensorDesc(int(buf_ptr), es, format, dim, shape, strides))
+
+
+# ------------------------------------------------------------------------------------------------
+# padding to tile-aligned 4-D shapes and back
+# ------------------------------------------------------------------------------------------------
+def is_buda_shape(tensor: torch.Tensor, min_dim=-1) -> bool:
+    nd = len(tensor.shape)
+    if nd > 4 or (nd < min_dim if min_dim > 0 else nd != 4):
+        return False
+    return tensor.shape[-1] % TILE_DIM == 0 and tensor.shape[-2] % TILE_DIM == 0
+
+
+def pad_pytorch_tensor_to_buda(tensor: torch.Tensor, tile_broadcast_dims: List[int], squeeze: bool = False, microbatch=1,
+                               tile_r=TILE_DIM, tile_c=TILE_DIM) -> torch.Tensor:
+    """Pad a torch tensor to 4-D with rows / columns rounded up to the tile.  Dims listed in
+    tile_broadcast_dims (size 1) are replicated across the tile instead of zero padded."""
+    if tensor.dim() == 0:
+        tensor = tensor.reshape(1)  # a scalar pads like a one-element vector
+    min_dim = 2 if (squeeze and tensor.shape[0] != microbatch and len(tensor.shape) > 2) else 4
+    if is_buda_shape(tensor, min_dim):
+        return tensor
+    out = tensor
+    while out.dim() < min_dim:
+        out = out.unsqueeze(1 if out.shape[0] == microbatch else 0)
+    while out.dim() > 5:
+        assert out.shape[0] == 1, "Invalid dimension size above dim 5"
+        out = out.squeeze(0)
+    if out.shape[0] < microbatch:
+        out = out.broadcast_to([microbatch, *out.shape[1:]]).contiguous()
+    if is_buda_shape(out):
+        return out.detach().contiguous()
+
+    rows, cols = out.shape[-2], out.shape[-1]
+    pad_c = (-cols) % tile_c
+    pad_r = (-rows) % tile_r
+    rep_c = -1 in tile_broadcast_dims or 3 in tile_broadcast_dims
+    rep_r = -2 in tile_broadcast_dims or 2 in tile_broadcast_dims
+    if rep_c:
+        assert cols == 1, "Trying to broadcast to tile dim a dimension that's not 1"
+    if rep_r:
+        assert rows == 1, "Trying to broadcast to tile dim a dimension that's not 1"
+
+    # torch pads floating 3-D+ tensors only
+    dtype, ndim = out.dtype, out.dim()
+    work = out if dtype == torch.float32 else out.type(torch.float32)
+    while work.dim() < 3:
+        work = work.unsqueeze(0)
+    work = torch.nn.functional.pad(work, (0, pad_c, 0, 0), mode="replicate" if rep_c else "constant")
+    work = torch.nn.functional.pad(work, (0, 0, 0, pad_r), mode="replicate" if rep_r else "constant")
+    while work.dim() > ndim:
+        work = work.squeeze(0)
+    if work.dtype != dtype:
+        work = work.type(dtype)
+    work = work.detach()
+    work.requires_grad = tensor.requires_grad
+    return work
+
+
+def narrow_buda_tensor_to_pytorch(tensor: torch.Tensor, shape: List[int], has_microbatch_dim: bool = False) -> torch.Tensor:
+    """Undo pad_pytorch_tensor_to_buda: cut the tile padding off and reshape to `shape`."""
+    shape = tuple(shape)
+    if len(shape) == 0:  # a scalar that was padded to one tile
+        return tensor.narrow(-1, 0, 1).narrow(-2, 0, 1).squeeze()
+    out = tensor
+    if len(shape) == 1:  # a vector that was padded to tiles
+        if out.dim() == 1:
+            out = out.narrow(0, 0, shape[0])
+        elif out.dim() > 2 and out.shape[0] == shape[0]:
+            out = out.narrow(-1, 0, 1).narrow(-2, 0, 1)
+        else:
+            out = out.narrow(-1, 0, shape[0]).narrow(-2, 0, 1)
+    elif reduce(mul, shape, 1) != reduce(mul, out.shape, 1):
+        # z may have been swapped with r by a transform attached upstream: narrow in that frame
+        swap = out.dim() == 4 and len(shape) == 4 and out.shape[-3] != shape[-3]
+        if swap:
+            out = out.transpose(-3, -2)
+        inner = shape[1:] if has_microbatch_dim else shape
+        out = out.narrow(-2, 0, 1 if len(inner) == 1 else inner[-2])
+        out = out.narrow(-1, 0, inner[-1])
+        if swap:
+            out = out.transpose(-3, -2)
+    return out.reshape(shape)
+
+
+def change_rank(tensor: torch.Tensor, rank: int):
+    while tensor.dim() > rank:
+        assert tensor.shape[0] == 1
+        tensor = tensor.select(0, 0)
+    while tensor.dim() < rank:
+        tensor = tensor.unsqueeze(0)
+    return tensor
+
+
+# ------------------------------------------------------------------------------------------------
+# Tensor wrappers
+# ------------------------------------------------------------------------------------------------
+class Tensor:
+    """A tensor on its way to or from a device queue: a torch value plus the device data format."""
+
+    def __init__(self):
+        self.src_layer = None
+
+    def set_src_layer(self, layer: str):
+        self.src_layer = layer
+        return self
+
+    def to_pytorch(self) -> torch.Tensor:
+        return self.value()
+
+    def has_value(self) -> bool:
+        raise RuntimeError("Children should override")
+
+    def value(self) -> torch.Tensor:
+        raise RuntimeError("Children should override")
+
+    def is_constant(self) -> bool:
+        return False
+
+    def __repr__(self):
+        if self.has_value():
+            return f"Buda Tensor: {self.value()}, {self.data_format}"
+        return f"Buda Empty Tensor: {self.shape}"
+
+    @classmethod
+    def create_from_torch(cls, torch_tensor: torch.Tensor, dev_data_format: Optional[DataFormat] = None,
+                          constant: bool = False) -> "TensorFromPytorch":
+        return TensorFromPytorch(torch_tensor, dev_data_format, constant)
+
+    @classmethod
+    def create_from_tensor_descriptor(cls, descriptor: "PytorchTensorDesc") -> "TensorFromDescriptor":
+        return TensorFromDescriptor(descriptor)
+
+
+class TensorFromPytorch(Tensor):
+    """Tensor wrapper around a concrete torch tensor."""
+
+    def __init__(self, torch_tensor: torch.Tensor, dev_data_format: Optional[DataFormat], constant: bool):
+        super().__init__()
+        self._value = torch_tensor
+        self._data_format = dev_data_format if dev_data_format is not None else pytorch_dtype_to_buda_dataformat(
+            torch_tensor.dtype)
+        self._constant = constant
+
+    def has_value(self) -> bool:
+        return True
+
+    def value(self) -> torch.Tensor:
+        return self._value
+
+    def is_constant(self) -> bool:
+        return self._constant
+
+    @property
+    def requires_grad(self) -> bool:
+        return self._value.requires_grad
+
+    def set_requires_grad(self, requires_grad: bool):
+        self._value.requires_grad = requires_grad
+
+    def to_buda_shape(self, tile_broadcast_dims: List[int], reinterpret_shape: Optional[List[int]] = None, clone: bool = False,
+                      squeeze: bool = False, microbatch=1, tile_r=TILE_DIM, tile_c=TILE_DIM) -> "Tensor":
+        """This tensor padded to the 4-D tile-aligned shape the queues take."""
+        value = self._value.clone() if clone else self._value
+        if not clone and reinterpret_shape is None and is_buda_shape(value):
+            return self
+        if reinterpret_shape is not None:
+            if reinterpret_shape[0] == 1:
+                reinterpret_shape[0] = microbatch
+            value = value.view(reinterpret_shape)
+        return Tensor.create_from_torch(pad_pytorch_tensor_to_buda(value, tile_broadcast_dims, squeeze, microbatch, tile_r, tile_c))
+
+    def to_tensor_desc(self) -> "PytorchTensorDesc":
+        return pytorch_tensor_to_tensor_desc(self._value)
+
+    @property
+    def pt_data_format(self) -> torch.dtype:
+        return self._value.dtype
+
+    @property
+    def data_format(self) -> DataFormat:
+        return self._data_format
+
+    def to_format(self, data_format: DataFormat) -> "Tensor":
+        """Tag the tensor with a device format and cast the torch value to the dtype that format
+        travels as (Bfp*_b -> bfloat16).  No packing happens here: bytes are produced at push time."""
+        return Tensor.create_from_torch(self._value.type(buda_dataformat_to_pytorch_dtype(data_format)),
+                                        dev_data_format=data_format)
+
+    @property
+    def shape(self):
+        return TensorShape(*self._value.shape)
+
+    def clone(self) -> Tensor:
+        return Tensor.create_from_torch(self._value.clone())
+
+    def detach(self) -> Tensor:
+        return Tensor.create_from_torch(self._value.detach())
+
+
+class TensorFromDescriptor(Tensor):
+    """Tensor wrapper around a descriptor returned by the backend (e.g. by get_output)."""
+
+    def __init__(self, descriptor: "PytorchTensorDesc"):
+        super().__init__()
+        self.descriptor = descriptor
+        self.requires_grad = False
+
+    def clone(self) -> "TensorFromPytorch":
+        return Tensor.create_from_torch(self.value(clone=True))
+
+    def has_value(self) -> bool:
+        return True
+
+    def value(self, clone=False) -> torch.Tensor:
+        t = tensor_desc_to_pytorch_tensor(self.descriptor)
+        return t.clone() if clone else t
+
+    def to_buda_shape(self) -> "Tensor":
+        raise RuntimeError("Tensor descriptor should not be converted to buda shape")
+
+    def to_tensor_desc(self) -> "PytorchTensorDesc":
+        return self.descriptor
+
+    def narrow_to_original_shape(self, original_shape: Tuple[int, ...], reinterpret_shape: Optional[Tuple[int, ...]] = None,
+                                 has_microbatch_dim: bool = False, unpadded_shape: Optional[Tuple[int, ...]] = None) -> "Tensor":
+        """Cut the tile padding off a read-back tensor and give it its original shape."""
+        assert type(original_shape) == tuple, "original_shape must be a tuple"
+        tensor = self.value()
+        reinterpret = reinterpret_shape if reinterpret_shape else None
+        if reinterpret is None and self.shape.get_pytorch_shape() == original_shape:
+            return Tensor.create_from_torch(tensor)
+        target = original_shape if reinterpret is None else tuple(reinterpret)
+        if len(target) > 1:
+            new_shape = (*target[:-2], target[-2], target[-1])
+        else:
+            new_shape = (target[-1],)
+        narrowed = narrow_buda_tensor_to_pytorch(tensor, new_shape, has_microbatch_dim=has_microbatch_dim)
+        return Tensor.create_from_torch(narrowed.reshape(original_shape))
+
+    @property
+    def pt_data_format(self) -> torch.dtype:
+        return buda_dataformat_to_pytorch_dtype(self.descriptor.format)
+
+    @property
+    def data_format(self) -> DataFormat:
+        return self.descriptor.format
+
+    def to_format(self, data_format: DataFormat) -> "Tensor":
+        t = self.value().type(buda_dataformat_to_pytorch_dtype(data_format))
+        t.requires_grad = self.requires_grad
+        return Tensor.create_from_torch(t, dev_data_format=data_format)
+
+    @property
+    def shape(self):
+        return TensorShape(*self.descriptor.shape)
+
+
+def to_pt_tensors(tensors, convert_format: bool = False) -> Tuple[torch.Tensor, ...]:
+    """torch tensors out of a mix of torch tensors and Tensor wrappers."""
+    if not isinstance(tensors, (list, tuple)):
+        tensors = (tensors,)
+    out = []
+    for t in tensors:
+        if isinstance(t, torch.Tensor):
+            out.append(t)
+        elif isinstance(t, Tensor):
+            v = t.value()
+            out.append(v.type(buda_dataformat_to_pytorch_dtype(t.data_format)) if convert_format else v)
+        else:
+            raise RuntimeError(f"Unsupported tensor type {type(t)}")
+    return tuple(out)
+
+
+def to_buda_tensors(tensors) -> Tuple[Tensor, ...]:
+    return tuple(t if isinstance(t, Tensor) else Tensor.create_from_torch(t) for t in tensors)
