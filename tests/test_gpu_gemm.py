@@ -1,0 +1,114 @@
+"""GPU tests of the Bfp8_b-weight matmul (tcgen05 kernel) against binary32 matmul of the
+oracle-decoded operands.
+
+Tolerance (stated by the target: rel-err 1e-3 against an fp32 matmul of the decoded operands):
+  * norm-wise   ||C - bf16(ref)||_F / ||ref||_F <= 1e-3, the reference rounded to the kernel's
+    bfloat16 output type first (rounding to bfloat16 alone costs ~1.5e-3 norm-wise);
+  * element-wise |C - ref| <= 2^-8 |ref| + 1e-3 max|ref|  (half an ulp of bfloat16 plus a floor).
+One-hot activations make the product a copy of decoded weight rows, which must then be exact."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.fail("these tests need a CUDA device; there is no CPU fallback to test")
+    from pybuda import cuda_ops
+
+    torch.backends.cuda.matmul.allow_tf32 = False
+    return cuda_ops
+
+
+def _weights(oracle, ops, K, N, seed, scale=0.02):
+    w = torch.randn(1, 1, K, N, generator=torch.Generator().manual_seed(seed)) * scale
+    img = ops.tilize_pack(w.cuda(), ops.DF.Bfp8_b)
+    ref_img = oracle.tilize_pack(w.numpy(), oracle.Bfp8_b)
+    assert np.array_equal(img.cpu().numpy(), ref_img)
+    wd = torch.from_numpy(oracle.unpack_untilize(ref_img, oracle.Bfp8_b, (1, 1, K, N)))[0, 0]
+    return img, wd
+
+
+def _check(c, ref):
+    c = c.float()
+    refb = ref.bfloat16().float()
+    rel = ((c - refb).norm() / ref.norm()).item()
+    assert rel <= 1e-3, f"norm-wise relative error {rel}"
+    bound = ref.abs() * 2.0 ** -8 + 1e-3 * ref.abs().max()
+    bad = (c - ref).abs() > bound
+    assert not bad.any(), f"{int(bad.sum())} elements outside the element-wise bound; first {bad.nonzero()[:5].tolist()}"
+
+
+def test_one_hot_rows_copy_decoded_weights_exactly(ops, oracle):
+    K, N, M = 128, 512, 256
+    img, wd = _weights(oracle, ops, K, N, seed=7, scale=1.0)
+    a = torch.zeros(M, K)
+    ks = torch.arange(M) % K
+    a[torch.arange(M), ks] = 1.0
+    c = ops.bfp8b_matmul(a.bfloat16().cuda(), img, N).cpu().float()
+    want = wd[ks]            # decoded values have 7 significant bits: exact in bfloat16
+    if not torch.equal(c, want):
+        bad = (c != want).nonzero()
+        pytest.fail(f"{bad.shape[0]} of {c.numel()} elements differ; first {bad[:8].tolist()}; "
+                    f"got {c[tuple(bad[0])].item()} want {want[tuple(bad[0])].item()}")
+
+
+@pytest.mark.parametrize("M,K,N", [(256, 64, 256), (256, 256, 256), (512, 512, 768), (128, 192, 256), (300, 128, 512),
+                                   (1024, 1024, 1024)])
+def test_matmul_small_shapes(ops, oracle, M, K, N):
+    img, wd = _weights(oracle, ops, K, N, seed=M + K + N)
+    a = torch.randn(M, K, generator=torch.Generator().manual_seed(1)).bfloat16()
+    c = ops.bfp8b_matmul(a.cuda(), img, N).cpu()
+    _check(c, a.float() @ wd)
+    if M * K * N <= 256 * 256 * 256:
+        # and against the oracle's own k-ordered binary32 accumulation
+        ref2 = torch.from_numpy(oracle.bfp8b_matmul(a.view(torch.int16).numpy().view(np.uint16), img.cpu().numpy(), K, N))
+        _check(c, ref2)
+
+
+def test_strided_operands_and_reuse(ops, oracle):
+    M, K, N = 256, 128, 256
+    img, wd = _weights(oracle, ops, K, N, seed=3)
+    big = torch.randn(M, K + 64, generator=torch.Generator().manual_seed(2)).bfloat16().cuda()
+    a = big[:, :K]                                    # row stride K + 64
+    out = torch.zeros(M, N + 128, dtype=torch.bfloat16, device="cuda")
+    for _ in range(3):                                # the persistent kernel is relaunched safely
+        ops.bfp8b_matmul(a, img, N, out=out[:, :N])
+    _check(out[:, :N].cpu(), a.cpu().float() @ wd)
+    assert torch.all(out[:, N:] == 0)
+    rc, st = ops._cabi.device_status()
+    assert rc == 0 and st == 0
+
+
+def test_bad_shapes_are_refused(ops):
+    a = torch.zeros(128, 96, dtype=torch.bfloat16, device="cuda")
+    img = torch.zeros(3 * 8 * 1088, dtype=torch.uint8, device="cuda")
+    with pytest.raises(ops._cabi.BudaError) as e:
+        ops.bfp8b_matmul(a, img, 256)
+    assert "K % 64" in str(e.value)
+
+
+def test_config4_full_size(ops, oracle):
+    # activations bf16 [8192,4096] ~ N(0,1); weights fp32 [4096,16384] ~ N(0,0.02) packed to Bfp8_b
+    M, K, N = 8192, 4096, 16384
+    a = torch.randn(M, K, generator=torch.Generator().manual_seed(6)).bfloat16().cuda()
+    w = torch.randn(1, 1, K, N, generator=torch.Generator().manual_seed(7)) * 0.02
+    img = ops.tilize_pack(w.cuda(), ops.DF.Bfp8_b)
+    assert img.numel() == 71303168
+    c = ops.bfp8b_matmul(a, img, N)
+    # decoded weights: the kernel's own unpack was proven bit-exact against the oracle above
+    wd = ops.unpack_untilize(img, ops.DF.Bfp8_b, (1, 1, K, N))[0, 0]
+    ref = a.float() @ wd                               # binary32 matmul (TF32 off)
+    cf = c.float()
+    rel = ((cf - ref.bfloat16().float()).norm() / ref.norm()).item()
+    assert rel <= 1e-3, rel
+    bound = ref.abs() * 2.0 ** -8 + 1e-3 * ref.abs().max()
+    assert not ((cf - ref).abs() > bound).any()
+    # a sample of rows against the CPU oracle's decode + matmul, end to end
+    rows = torch.tensor([0, 1, 127, 128, 255, 256, 4095, 8191])
+    wd_cpu = torch.from_numpy(oracle.unpack_untilize(oracle.tilize_pack(w.numpy(), oracle.Bfp8_b), oracle.Bfp8_b, (1, 1, K, N)))[0, 0]
+    ref_rows = a[rows.cuda()].cpu().float() @ wd_cpu
+    _check(c[rows.cuda()].cpu(), ref_rows)

@@ -1,11 +1,424 @@
-// placeholder until the tcgen05 kernel lands
+// K7: C[M,N] (bfloat16) = A[M,K] (bfloat16) @ W[K,N], W stored as Bfp8_b tiles, binary32
+// accumulation on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory).
+//
+// The device counterpart of a matmul whose weight queue has data format Bfp8_b (the reference
+// evaluates it as torch.matmul on the decoded operands, pybuda/pybuda/op/eval/pybuda/matmul.py:20-33;
+// the weight format rule is pybuda/csrc/passes/dataformat.cpp:409-418).
+//
+// One persistent CTA per SM computes 256x256 output tiles as two 128x256 accumulators (all 512
+// tensor-memory columns), so every decoded weight element feeds 256 rows of activations:
+//   warp 4        producer: per 64-deep k-block, TMA-loads two 128x64 activation boxes (128B swizzle,
+//                 K-major) and bulk-copies the 16 raw Bfp8_b tile records (2 k-tiles x 8 n-tiles)
+//   warps 6-13    decode: each thread takes one 16-value block (one face row: fixed k, 16 consecutive
+//                 n, one shared exponent) from the raw records, turns sign + 7-bit magnitude into
+//                 bfloat16 pairs in registers with one packed fma per pair ((128+m)*s - 128*s, exact)
+//                 and writes them into the N-major ("MN-major") 128B-swizzled operand tile
+//   warp 5        one thread issues tcgen05.mma (M=128, N=256, K=16; 2 halves x 4 k-steps per
+//                 k-block) and commits completion to the mbarriers that free the stages
+//   warps 0-3     epilogue: tcgen05.ld the accumulators, round to bfloat16, store C
+// Every mbarrier wait is bounded; a wait that gives up raises the device status word and the CTA
+// winds down (tensor memory is freed on every path).
+#include <cuda.h>
+
 #include <cstdio>
+
 #include "buda_common.cuh"
+
 namespace buda {
-cudaError_t launch_bfp8b_gemm(const void *, int64_t, int64_t, int64_t, const void *, int64_t, void *, int64_t, int,
-                              cudaStream_t, unsigned int *, char *err, size_t err_len)
+
+namespace gemm {
+
+constexpr int kBM = 256;           // rows of C per tile (two UMMA M=128 halves)
+constexpr int kBN = 256;           // columns of C per tile
+constexpr int kBK = 64;            // k-block
+constexpr int kLoadStages = 3;     // activation + raw-weight ring
+constexpr int kBStages = 2;        // decoded-weight ring
+constexpr int kABytes = kBM * kBK * 2;           // 32768
+constexpr int kBBytes = kBN * kBK * 2;           // 32768
+constexpr int kRecord = 1088;                    // Bfp8_b tile record, no header
+constexpr int kRawBytes = 16 * kRecord;          // 2 k-tiles x 8 n-tiles = 17408
+constexpr int kDecodeWarps = 8;
+constexpr int kThreads = 32 * (4 + 1 + 1 + kDecodeWarps);  // 448
+constexpr int kTmemCols = 512;
+
+constexpr int kSmemA = 0;
+constexpr int kSmemB = kSmemA + kLoadStages * kABytes;
+constexpr int kSmemRaw = kSmemB + kBStages * kBBytes;
+constexpr int kSmemBar = kSmemRaw + kLoadStages * kRawBytes;
+constexpr int kNumBars = 4 * kLoadStages + 2 * kBStages + 2;
+constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 16 + 1024;  // + tmem holder / abort flag, + alignment slack
+
+// instruction descriptor: D = F32, A = B = BF16, A K-major, B MN-major, N = 256, M = 128
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) | ((uint32_t)(kBN >> 3) << 17) |
+                            ((uint32_t)(128 >> 4) << 24);
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
 {
-    snprintf(err, err_len, "bfp8b gemm kernel not built");
-    return cudaErrorNotSupported;
+    // start address, leading / stride byte offsets in 16-byte units, descriptor version 1, 128B swizzle
+    return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | (2ull << 61);
 }
+
+__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *tmap, int x, int y, uint64_t *bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// arrive on an mbarrier once every tcgen05.mma issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint64_t *bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, "
+        "[%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t c)
+{
+    uint32_t d;
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
+{
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+
+struct Params {
+    const uint8_t *W;     // Bfp8_b image: record (kt, nt) at (kt * Nt + nt) * 1088
+    uint16_t *C;          // bfloat16, row stride ldc
+    int64_t M, N, K, ldc;
+    uint32_t m_tiles, n_tiles, k_blocks, Nt;
+    unsigned int *status;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ Params p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    // 128B-swizzled operand tiles repeat every 1024 bytes: align the carve-up to that
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *sA = smem + kSmemA;
+    uint8_t *sB = smem + kSmemB;
+    uint8_t *sRaw = smem + kSmemRaw;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kSmemBar);
+    uint64_t *full_a = bars;                       // [kLoadStages] activations landed (TMA bytes)
+    uint64_t *full_w = full_a + kLoadStages;       // [kLoadStages] raw weight records landed
+    uint64_t *empty_a = full_w + kLoadStages;      // [kLoadStages] MMAs reading the activations are done
+    uint64_t *empty_w = empty_a + kLoadStages;     // [kLoadStages] decode warps are done with the raw records
+    uint64_t *full_b = empty_w + kLoadStages;      // [kBStages] decoded weights written
+    uint64_t *empty_b = full_b + kBStages;         // [kBStages] MMAs reading the decoded weights are done
+    uint64_t *acc_full = empty_b + kBStages;       // accumulators complete
+    uint64_t *acc_empty = acc_full + 1;            // accumulators drained by the epilogue
+    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + kNumBars);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t total_tiles = p.m_tiles * p.n_tiles;
+
+    if (tid == 0) {
+        for (int s = 0; s < kLoadStages; s++) {
+            mbar_init(&full_a[s], 1);
+            mbar_init(&full_w[s], 1);
+            mbar_init(&empty_a[s], 1);
+            mbar_init(&empty_w[s], kDecodeWarps);
+        }
+        for (int t = 0; t < kBStages; t++) {
+            mbar_init(&full_b[t], kDecodeWarps);
+            mbar_init(&empty_b[t], 1);
+        }
+        mbar_init(acc_full, 1);
+        mbar_init(acc_empty, 4);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 4) {
+        // the whole warp allocates all 512 tensor-memory columns and gives up the right to allocate more
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            uint32_t i = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const uint32_t m_blk = tile % p.m_tiles, n_blk = tile / p.m_tiles;
+                for (uint32_t kb = 0; kb < p.k_blocks; kb++, i++) {
+                    const int s = i % kLoadStages;
+                    const uint32_t ph = ((i / kLoadStages) & 1u) ^ 1u;
+                    if (!mbar_wait_bounded(&empty_a[s], ph, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT) ||
+                        !mbar_wait_bounded(&empty_w[s], ph, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(&full_a[s], kABytes);
+                    tma_load_2d(sA + s * kABytes, &tmap_a, (int)(kb * kBK), (int)(m_blk * kBM), &full_a[s]);
+                    tma_load_2d(sA + s * kABytes + kABytes / 2, &tmap_a, (int)(kb * kBK), (int)(m_blk * kBM + 128), &full_a[s]);
+                    mbar_arrive_expect_tx(&full_w[s], kRawBytes);
+                    const uint8_t *w0 = p.W + ((uint64_t)(kb * 2) * p.Nt + (uint64_t)n_blk * 8) * kRecord;
+                    bulk_g2s(sRaw + s * kRawBytes, w0, 8 * kRecord, &full_w[s]);
+                    bulk_g2s(sRaw + s * kRawBytes + 8 * kRecord, w0 + (uint64_t)p.Nt * kRecord, 8 * kRecord, &full_w[s]);
+                }
+            }
+            if (!ok || *abort_flag) {
+                // let the copies already issued land before shared memory is released
+                const uint32_t back = i < (uint32_t)kLoadStages ? i : (uint32_t)kLoadStages;
+                for (uint32_t k = 1; k <= back; k++) {
+                    const uint32_t j = i - k;
+                    uint64_t t0 = global_timer_ns();
+                    while (!(mbar_try_wait(&full_a[j % kLoadStages], (j / kLoadStages) & 1u) &&
+                             mbar_try_wait(&full_w[j % kLoadStages], (j / kLoadStages) & 1u)) &&
+                           global_timer_ns() - t0 < 100000000ull) {
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------ MMA issue
+        if (lane == 0) {
+            uint32_t i = 0, tile_iter = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, tile_iter++) {
+                if (tile_iter > 0) {  // the epilogue must have drained the previous tile's accumulators
+                    if (!mbar_wait_bounded(acc_empty, (tile_iter - 1) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT)) break;
+                    tc_fence_after();
+                }
+                for (uint32_t kb = 0; kb < p.k_blocks; kb++, i++) {
+                    const int s = i % kLoadStages, t = i % kBStages;
+                    if (!mbar_wait_bounded(&full_a[s], (i / kLoadStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT) ||
+                        !mbar_wait_bounded(&full_b[t], (i / kBStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(sA + s * kABytes), b_addr = smem_u32(sB + t * kBBytes);
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+#pragma unroll
+                        for (int j = 0; j < kBK / 16; j++) {
+                            // A: K-major, 8-row groups 1024 B apart, 32 B per 16-deep k-step inside the swizzled row
+                            const uint64_t adesc = smem_desc(a_addr + h * (kABytes / 2) + j * 32, 16, 1024);
+                            // B: N-major, 64-column atoms 1024 B apart, 8-deep k groups 4096 B apart
+                            const uint64_t bdesc = smem_desc(b_addr + j * 8192, 1024, 4096);
+                            umma_bf16(tmem_base + h * kBN, adesc, bdesc, kIdesc, (kb > 0 || j > 0) ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(&empty_a[s]);
+                    umma_commit(&empty_b[t]);
+                }
+                if (ok) umma_commit(acc_full);
+            }
+        }
+        __syncwarp();
+    } else if (warp >= 6) {
+        // ------------------------------------------------------------------ decode warps
+        const int dw = warp - 6;
+        uint32_t i = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (uint32_t kb = 0; kb < p.k_blocks; kb++, i++) {
+                const int s = i % kLoadStages, t = i % kBStages;
+                const bool got = mbar_wait_bounded(&full_w[s], (i / kLoadStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT) &&
+                                 mbar_wait_bounded(&empty_b[t], ((i / kBStages) & 1u) ^ 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT);
+                if (!__all_sync(0xffffffffu, got)) {  // the whole warp leaves together
+                    ok = false;
+                    break;
+                }
+                const uint8_t *raw = sRaw + s * kRawBytes;
+                uint8_t *bst = sB + t * kBBytes;
+#pragma unroll
+                for (int it = 0; it < 4; it++) {
+                    const int u = it * kDecodeWarps + dw;          // 32 units: (record, half of its 64 blocks)
+                    const int r = u >> 1;                           // record: k-tile r / 8, n-tile r % 8
+                    const int blk = (u & 1) * 32 + lane;            // block = face * 16 + face row
+                    const uint8_t *rec = raw + r * kRecord;
+                    const uint4 mant = *reinterpret_cast<const uint4 *>(rec + 64 + blk * 16);
+                    const uint32_t E = rec[blk];
+                    // scale 2^(E-133) as bfloat16 bits (exponent field E-6); blocks below 2^-126 flush to zero
+                    const uint32_t e6 = E > 6u ? E - 6u : 0u;
+                    const uint32_t sc = (e6 << 7) * 0x00010001u;
+                    const uint32_t off = e6 ? ((((e6 + 7u) << 7) | 0x8000u) * 0x00010001u) : 0u;  // -128 * scale
+                    const uint32_t w[4] = {mant.x, mant.y, mant.z, mant.w};
+                    uint32_t o[8];
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const uint32_t mg = w[q] & 0x7f7f7f7fu, sg = w[q] & 0x80808080u;
+                        // (128 + m) as bfloat16 is 0x4300 | m: splice each magnitude byte under 0x43
+                        const uint32_t p01 = __byte_perm(mg, 0x43434343u, 0x4140);
+                        const uint32_t p23 = __byte_perm(mg, 0x43434343u, 0x4342);
+                        o[2 * q] = fma_bf16x2(p01, sc, off) | __byte_perm(sg, 0u, 0x1404);
+                        o[2 * q + 1] = fma_bf16x2(p23, sc, off) | __byte_perm(sg, 0u, 0x3424);
+                    }
+                    const int k_local = (r >> 3) * 32 + (blk >> 5) * 16 + (blk & 15);
+                    const int n_local = (r & 7) * 32 + ((blk >> 4) & 1) * 16;
+                    const int kr = k_local & 7, c0 = (n_local & 63) >> 3;
+                    uint8_t *dst = bst + ((k_local >> 3) * 4 + (n_local >> 6)) * 1024 + kr * 128;
+                    *reinterpret_cast<uint4 *>(dst + ((c0 ^ kr) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4 *>(dst + (((c0 + 1) ^ kr) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                }
+                fence_async_smem();  // the tensor core reads shared memory through the async proxy
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&full_b[t]);
+                    mbar_arrive(&empty_w[s]);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps 0-3
+        uint32_t tile_iter = 0;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tile_iter++) {
+            const uint32_t m_blk = tile % p.m_tiles, n_blk = tile / p.m_tiles;
+            const bool got = mbar_wait_bounded(acc_full, tile_iter & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT);
+            if (!__all_sync(0xffffffffu, got)) break;  // the whole warp leaves together
+            tc_fence_after();
+#pragma unroll 1
+            for (int h = 0; h < 2; h++) {
+                const int64_t row = (int64_t)m_blk * kBM + h * 128 + warp * 32 + lane;
+                uint16_t *crow = p.C + row * p.ldc + (int64_t)n_blk * kBN;
+#pragma unroll 1
+                for (int c = 0; c < kBN / 32; c++) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(h * kBN + c * 32), v);
+                    if (row < p.M) {
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            uint4 o;
+                            o.x = pack_bf16x2(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1]));
+                            o.y = pack_bf16x2(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
+                            o.z = pack_bf16x2(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
+                            o.w = pack_bf16x2(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
+                            *reinterpret_cast<uint4 *>(crow + c * 32 + q * 8) = o;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty);
+        }
+    }
+
+    // every path ends here; the allocating warp frees tensor memory
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+}  // namespace gemm
+
+cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W, int64_t N, void *C, int64_t ldc,
+                              int sm_count, cudaStream_t stream, unsigned int *status, char *err, size_t err_len)
+{
+    using namespace gemm;
+    if (M <= 0 || N <= 0 || K <= 0 || (N % kBN) || (K % kBK)) {
+        snprintf(err, err_len, "bfp8b gemm needs N %% %d == 0 and K %% %d == 0 (got M=%lld N=%lld K=%lld)", kBN, kBK, (long long)M,
+                 (long long)N, (long long)K);
+        return cudaErrorInvalidValue;
+    }
+    if (lda < K || ldc < N || (lda % 8) || (ldc % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+        (reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) {
+        snprintf(err, err_len, "bfp8b gemm needs 16-byte aligned A, W, C and row strides that are multiples of 8 elements");
+        return cudaErrorInvalidValue;
+    }
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) {
+        snprintf(err, err_len, "cuTensorMapEncodeTiled is not available from this driver");
+        return cudaErrorNotSupported;
+    }
+    CUtensorMap tmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)lda * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(A), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) {
+        snprintf(err, err_len, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
+        return cudaErrorInvalidValue;
+    }
+    static bool attr_done[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev &= 63;
+    if (!attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(bfp8b_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return e;
+        attr_done[dev] = true;
+    }
+    Params p;
+    p.W = static_cast<const uint8_t *>(W);
+    p.C = static_cast<uint16_t *>(C);
+    p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+    p.m_tiles = (uint32_t)((M + kBM - 1) / kBM);
+    p.n_tiles = (uint32_t)(N / kBN);
+    p.k_blocks = (uint32_t)(K / kBK);
+    p.Nt = (uint32_t)(N / 32);
+    p.status = status;
+    uint32_t grid = p.m_tiles * p.n_tiles;
+    if (grid > (uint32_t)sm_count) grid = (uint32_t)sm_count;
+    bfp8b_gemm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap, p);
+    return cudaGetLastError();
+}
+
 }  // namespace buda
