@@ -115,6 +115,25 @@ int buda_tilize_pack_host(const void *src_host, int src_df, const uint32_t shape
                           const uint64_t strides_bytes[4], const buda_queue_geom *geom, int dst_df,
                           int with_header, void *dst_host, uint64_t dst_bytes, void *stream);
 
+/* buda_tilize_pack_host for callers that must not allocate.  It has no counterpart in the reference.
+ * Same arguments and result, but the device staging for the tensor and its image is a fixed 8 MiB
+ * array inside the library (held by every GPU that loads the library until the process exits)
+ * instead of cudaMalloc'd buffers, and the call makes no cudaMalloc / cudaFree and creates no stream
+ * or event: copies and kernel run on `stream`, and the call returns when dst_host is complete.
+ * Meant for a pusher thread inside a process whose own allocator already owns the device heap, or a
+ * loop that cannot take the device-wide synchronisation an allocation implies.
+ * Limit: tensor bytes (rounded up to 256) + image bytes <= 8 MiB, e.g. fp32 [1,1,1024,1024] -> Bfp8_b;
+ * anything larger is refused with BUDA_RUNTIME_ERROR and a message naming the limit.
+ * The first call on a device also looks up the array's device address (cudaGetSymbolAddress) and
+ * sets kernel attributes; make that first call before any stream capture begins.
+ * All calls on a device share the one array, which keeps the previous call's bytes.  The library
+ * lets one host thread at a time through per device; GPU work of two calls that still overlapped
+ * (e.g. issued around that lock from forked copies of a context) would race on the array.
+ * Nothing needs clearing between calls: the kernel overwrites every byte it later copies out. */
+int buda_tilize_pack_host_noalloc(const void *src_host, int src_df, const uint32_t shape[4],
+                                  const uint64_t strides_bytes[4], const buda_queue_geom *geom, int dst_df,
+                                  int with_header, void *dst_host, uint64_t dst_bytes, void *stream);
+
 /* ------------------------------------------------------------------ unpack + untilize */
 
 /* Queue image -> row-major tensor.  Bfp*_b sources decode to Float32 or Float16_b; plain sources

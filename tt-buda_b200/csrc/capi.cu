@@ -850,3 +850,90 @@ uint64_t buda_launch_count(void) { return g_launches.load(std::memory_order_rela
 const char *buda_version(void) { return "buda_cuda 0.1 sm_100a"; }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Tilize + pack for callers that must not allocate.
+//
+// The host-buffer entry point above stages the tensor and its image in device buffers it gets from
+// cudaMalloc.  Some hosts of this library cannot do that: a pusher thread that lives inside a
+// training process whose own allocator has already claimed the device heap (a fresh cudaMalloc there
+// fails or fragments the pool), or a feeder loop that cannot afford the device-wide synchronisation a
+// cudaMalloc / cudaFree implies.  For them the staging area is a fixed array that is part of the
+// library image: every GPU that loads the library carries these 8 MiB until the process exits.
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr uint64_t kNoAllocScratchBytes = 8ull << 20;
+
+// File-scope device array.  In host code this name is only a stand-in for the symbol, never a device
+// address: the address each device gives it is looked up with cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+struct NoAllocDev {
+    std::once_flag once;
+    cudaError_t err = cudaSuccess;
+    unsigned char *base = nullptr;  // device address of g_noalloc_scratch on this device
+    std::mutex mu;                  // one call at a time per device: the array is shared
+};
+NoAllocDev g_noalloc[kMaxDevices];
+
+}  // namespace
+
+extern "C" int buda_tilize_pack_host_noalloc(const void *src_host, int src_df, const uint32_t shape[4],
+                                             const uint64_t strides_bytes[4], const buda_queue_geom *geom, int dst_df,
+                                             int with_header, void *dst_host, uint64_t dst_bytes, void *stream)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return fail(BUDA_RUNTIME_ERROR, "no current device");
+    NoAllocDev &na = g_noalloc[dev];
+    // set-up, once per device, with that device current (this is the first call's extra work)
+    std::call_once(na.once, [&]() { na.err = cudaGetSymbolAddress((void **)&na.base, g_noalloc_scratch); });
+    if (na.err != cudaSuccess || na.base == nullptr) return cuda_fail(na.err, "looking up the static scratch array");
+
+    if (!src_host || !dst_host || !shape || !strides_bytes || !geom) return fail(BUDA_RUNTIME_ERROR, "null argument");
+    int mant, es;
+    if (int rc = classify(src_df, dst_df, mant, es)) return rc;
+    TileJob job;
+    if (int rc = make_job(shape, strides_bytes, geom, dst_df, with_header, 1, job)) return rc;
+    if (strides_bytes[3] != (uint64_t)es) return fail(BUDA_RUNTIME_ERROR, "innermost stride must equal the element size");
+    const uint64_t row_bytes = (uint64_t)shape[3] * es;
+    if (strides_bytes[2] < row_bytes) return fail(BUDA_RUNTIME_ERROR, "row stride smaller than a row");
+    const uint64_t src_bytes = (uint64_t)shape[0] * shape[1] * shape[2] * row_bytes;
+    const uint64_t image_bytes = job.buf_bytes * geom->grid_r * geom->grid_c;
+    const uint64_t image_off = (src_bytes + 255u) & ~255ull;
+    if (image_off + image_bytes > kNoAllocScratchBytes)
+        return fail(BUDA_RUNTIME_ERROR,
+                    "tensor (%llu bytes) plus its image (%llu bytes) exceed the %llu-byte static scratch of the no-allocation "
+                    "entry point; use buda_tilize_pack_host",
+                    (unsigned long long)src_bytes, (unsigned long long)image_bytes, (unsigned long long)kNoAllocScratchBytes);
+    if (dst_bytes < image_bytes)
+        return fail(BUDA_RUNTIME_ERROR, "destination holds %llu bytes, the queue image needs %llu", (unsigned long long)dst_bytes,
+                    (unsigned long long)image_bytes);
+
+    std::lock_guard<std::mutex> lock(na.mu);
+    cudaStream_t s = (cudaStream_t)stream;
+    unsigned char *d_src = na.base, *d_img = na.base + image_off;
+    const uint64_t dense[4] = {(uint64_t)shape[1] * shape[2] * row_bytes, (uint64_t)shape[2] * row_bytes, row_bytes, (uint64_t)es};
+    cudaError_t e = cudaSuccess;
+    for (uint32_t w = 0; w < shape[0] && e == cudaSuccess; w++) {
+        for (uint32_t z = 0; z < shape[1] && e == cudaSuccess; z++) {
+            const uint8_t *h = (const uint8_t *)src_host + w * strides_bytes[0] + z * strides_bytes[1];
+            unsigned char *d = d_src + w * dense[0] + z * dense[1];
+            e = (strides_bytes[2] == row_bytes)
+                    ? cudaMemcpyAsync(d, h, (uint64_t)shape[2] * row_bytes, cudaMemcpyHostToDevice, s)
+                    : cudaMemcpy2DAsync(d, row_bytes, h, strides_bytes[2], row_bytes, shape[2], cudaMemcpyHostToDevice, s);
+        }
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "host to device copy");
+    // the kernel writes every byte of every tile record (header included), so nothing left in the
+    // array by an earlier call can show through and nothing has to be cleared first
+    const void *srcs[1] = {d_src};
+    void *dsts[1] = {d_img};
+    if (int rc = tilize_device(1, srcs, src_df, shape, dense, geom, dst_df, with_header, dsts, image_bytes, s, -1)) return rc;
+    if ((e = cudaMemcpyAsync(dst_host, d_img, image_bytes, cudaMemcpyDeviceToHost, s)) != cudaSuccess)
+        return cuda_fail(e, "device to host copy");
+    if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return cuda_fail(e, "synchronize");
+    return status_after_sync(ctx);
+}

@@ -50,10 +50,24 @@ _SIGS = {
     "buda_tilize_pack_batch": (_i, [_i, _vpp, _i, _u32p, _u64p, _gp, _i, _i, _vpp, _u64, _vp]),
     "buda_tilize_pack_batch_path": (_i, [_i, _vpp, _i, _u32p, _u64p, _gp, _i, _i, _vpp, _u64, _vp, _i]),
     "buda_tilize_pack_host": (_i, [_vp, _i, _u32p, _u64p, _gp, _i, _i, _vp, _u64, _vp]),
+    "buda_tilize_pack_host_noalloc": (_i, [_vp, _i, _u32p, _u64p, _gp, _i, _i, _vp, _u64, _vp]),
     "buda_unpack_untilize": (_i, [_vp, _i, _i, _gp, _vp, _i, _u32p, _u64p, _vp]),
     "buda_unpack_untilize_batch": (_i, [_i, _vpp, _i, _i, _gp, _vpp, _i, _u32p, _u64p, _vp]),
     "buda_unpack_untilize_batch_path": (_i, [_i, _vpp, _i, _i, _gp, _vpp, _i, _u32p, _u64p, _vp, _i]),
     "buda_unpack_untilize_host": (_i, [_vp, _i, _i, _gp, _vp, _i, _u32p, _u64p, _vp]),
+    "buda_queue_bytes": (_i64, [_gp, _i, _i, _u32]),
+    "buda_queue_write": (_i, [_vp, _i, _i, _u32p, _u64p, _gp, _i, _i, _vp, _u32, _u32, _vp]),
+    "buda_queue_read": (_i, [_vp, _i, _i, _gp, _u32, _u32, _vp, _i, _i, _u32p, _u64p, _vp]),
+    "buda_malloc": (_i, [_vpp, _u64]),
+    "buda_free": (_i, [_vp]),
+    "buda_host_alloc": (_i, [_vpp, _u64]),
+    "buda_host_free": (_i, [_vp]),
+    "buda_memcpy": (_i, [_vp, _vp, _u64, _i, _vp]),
+    "buda_stream_synchronize": (_i, [_vp]),
+    "buda_pointer_is_device": (_i, [_vp, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]),
+    "buda_get_device": (_i, [ctypes.POINTER(ctypes.c_int)]),
+    "buda_set_device": (_i, [_i]),
+    "buda_device_count": (_i, [ctypes.POINTER(ctypes.c_int)]),
     "buda_quantize": (_i, [_vp, _i64, _vp, _i64, _i64, _f, _i, _f, _f, _vp, _vp]),
     "buda_dequantize": (_i, [_vp, _i64, _vp, _i64, _i64, _f, _vp, _vp]),
     "buda_requantize": (_i, [_vp, _i64, _vp, _vp, _i64, _i64, _f, _i, _f, _f, _vp, _vp]),
