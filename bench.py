@@ -337,6 +337,38 @@ def main():
         except Exception as exc:
             extras["bfp8b_gemm_8192x4096x16384"] = {"error": str(exc)}
 
+    # ------------------------------------------------------------------ column-parallel matmul over the ranks (N > 1)
+    if world > 1 and not args.no_extras:
+        try:
+            from pybuda.parallel_matmul import ColumnParallelBfp8Matmul
+
+            M, K, N = 8192, 4096, 16384
+            a = torch.randn(M, K, device=dev).bfloat16()
+            op = ColumnParallelBfp8Matmul(K, N, bands=8)
+            op.load_weight_shard(torch.randn(1, 1, K, op.n_local, device=dev) * 0.02, already_sharded=True)
+            cfull = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+
+            def run(gather):
+                for _ in range(2):
+                    op(a, out=cfull, gather=gather)
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(5):
+                    op(a, out=cfull, gather=gather)
+                e1.record()
+                barrier()
+                return max_over_ranks(e0.elapsed_time(e1) / 5)
+
+            ms_local, ms_gather = run(False), run(True)
+            extras["column_parallel_gemm_8192x4096x16384"] = {
+                "TFLOP/s_without_gather": round(2.0 * M * N * K / (ms_local * 1e-3) / 1e12, 1), "ms_without_gather": round(ms_local, 4),
+                "TFLOP/s_with_all_gather": round(2.0 * M * N * K / (ms_gather * 1e-3) / 1e12, 1), "ms_with_all_gather": round(ms_gather, 4),
+                "bands": 8}
+            del a, cfull
+        except Exception as exc:
+            extras["column_parallel_gemm_8192x4096x16384"] = {"error": str(exc)}
+
     # ------------------------------------------------------------------ CPU baseline (rank 0, N = 1 only)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:

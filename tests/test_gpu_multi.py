@@ -1,0 +1,63 @@
+"""Two-GPU tests (skipped on a one-GPU box): tensors sharded round-robin with no collective, and the
+column-parallel Bfp8_b matmul whose output slices are exchanged by an NCCL all-gather."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    for p in (ROOT, os.path.join(ROOT, "tt-buda_b200")):
+        sys.path.insert(0, p)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import numpy as np
+        from oracle import budaref as R
+        from pybuda import cuda_ops
+        from pybuda.parallel_matmul import ColumnParallelBfp8Matmul
+        from pybuda.sharding import units_of_rank
+
+        torch.backends.cuda.matmul.allow_tf32 = False
+        ok = True
+        # independent tensors: tensor i -> rank i % world, packed on that rank's GPU, checked against the oracle
+        for i in units_of_rank(6, rank, world):
+            x = torch.randn(1, 1, 256, 512, generator=torch.Generator().manual_seed(1000 + i))
+            img = cuda_ops.tilize_pack(x.cuda(), cuda_ops.DF.Bfp8_b)
+            ok = ok and np.array_equal(img.cpu().numpy(), R.tilize_pack(x.numpy(), R.Bfp8_b))
+        # column-parallel matmul: every rank ends with the full [M, N] product
+        m, k, n = 1024, 512, 1024
+        g = torch.Generator().manual_seed(6)
+        a = torch.randn(m, k, generator=g).bfloat16().cuda()
+        w = torch.randn(k, n, generator=g) * 0.02
+        op = ColumnParallelBfp8Matmul(k, n, bands=4)
+        op.load_weight_shard(w)
+        c = op(a)
+        full_img = cuda_ops.tilize_pack(w.reshape(1, 1, k, n).cuda(), cuda_ops.DF.Bfp8_b)
+        wd = cuda_ops.unpack_untilize(full_img, cuda_ops.DF.Bfp8_b, (1, 1, k, n))[0, 0]
+        ref = a.float() @ wd
+        rel = ((c.float() - ref.bfloat16().float()).norm() / ref.norm()).item()
+        ok = ok and rel <= 1e-3 and c.shape == (m, n)
+        single = cuda_ops.bfp8b_matmul(a, full_img, n)
+        ok = ok and torch.equal(single, c)            # same kernel, same k order: identical bits
+        results[rank] = (bool(ok), rel)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_sharding_and_column_parallel_matmul():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    mgr = mp.Manager()
+    results = mgr.dict()
+    port = 29700 + (os.getpid() % 200)
+    mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
+    assert all(v[0] for v in results.values()), dict(results)
