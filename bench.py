@@ -135,6 +135,45 @@ def make_batch(torch, device, seed0, n):
     return xs
 
 
+def profile_one(torch, cuda_ops, dev, name, reps=6):
+    """One secondary kernel on a case that ends by itself in milliseconds: for ncu captures."""
+    if name == "gemm":
+        M, K, N = 8192, 4096, 16384
+        a = torch.randn(M, K, device=dev).bfloat16()
+        wimg = cuda_ops.tilize_pack(torch.randn(1, 1, K, N, device=dev) * 0.02, cuda_ops.DF.Bfp8_b)
+        c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        fn, work, unit = (lambda: cuda_ops.bfp8b_matmul(a, wimg, N, out=c)), 2.0 * M * N * K / 1e12, "TFLOP/s"
+    elif name == "unpack":
+        xs = [torch.randn(SHAPE, device=dev) for _ in range(8)]
+        imgs = cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b)
+        fn, work, unit = (lambda: cuda_ops.unpack_untilize_batch(imgs, cuda_ops.DF.Bfp8_b, SHAPE, outs=xs)), 8 * ELEMS * BYTES_PER_ELEM / 1e9, "GB/s"
+    else:
+        n = 32 * 1024 * 1024 * 4  # 512 MiB of fp32: larger than L2
+        sc = torch.tensor([0.05], device=dev)
+        if name == "quantize":
+            x = torch.rand(n, device=dev) * 12 - 6
+            fn = lambda: cuda_ops.quantize(x, sc, 3)
+        elif name == "dequantize":
+            q = torch.randint(-128, 128, (n,), device=dev, dtype=torch.int8)
+            fn = lambda: cuda_ops.dequantize(q, sc, 3)
+        else:
+            acc = torch.randint(-2 ** 20, 2 ** 20, (n // 1024, 1024), device=dev, dtype=torch.int32)
+            scs = torch.rand(1024, device=dev) * (1e-2 - 1e-4) + 1e-4
+            fn = lambda: cuda_ops.buda_requantize(acc, scs, 0)
+        work, unit = n * 5 / 1e9, "GB/s"
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record()
+    for _ in range(reps):
+        fn()
+    a1.record()
+    torch.cuda.synchronize()
+    ms = a0.elapsed_time(a1) / reps
+    print(json.dumps({"kernel": name, "ms": ms, unit: work / (ms * 1e-3)}), flush=True)
+
+
 def run_reference(args, rank, world):
     """The reference path on the host cores: tilize + Bfp8_b pack by the CPU port, all threads."""
     if rank != 0:
@@ -184,6 +223,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (for profiler captures)")
     ap.add_argument("--tensors", type=int, default=N_TENSORS,
                     help="tensors per GPU batch; anything but 64 is a reduced case for profiler captures")
+    ap.add_argument("--profile-kernel", default=None, choices=["gemm", "unpack", "quantize", "dequantize", "requantize"],
+                    help="run only this secondary kernel a few times and exit (small, self-ending case for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -221,6 +262,9 @@ def main():
         return float(t.item())
 
     hbm_peak, peak_kind = peaks()
+    if args.profile_kernel:
+        profile_one(torch, cuda_ops, dev, args.profile_kernel)
+        return
     NT = args.tensors
     xs = make_batch(torch, dev, 1000 + N_TENSORS * rank, NT)
     outs = [torch.empty(IMAGE_BYTES, dtype=torch.uint8, device=dev) for _ in range(NT)]
@@ -396,7 +440,9 @@ def main():
             "config": {"workload": WORKLOAD if NT == N_TENSORS else WORKLOAD + f" (REDUCED to {NT} tensors)", "per_gpu_batch": NT, "l2": "inputs (4 GiB per step) larger than L2",
                        "launches_per_step": 1},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                         "traffic": None, "peak_kind": peak_kind, "kernel": "pack_staged_kernel<7,4>",
+                         # dram read+write per launch: ncu on an 8-tensor launch measured 82.85 MB per tensor
+                         # (profiles/pack_staged_kernel_bfp8b_cfg2.md); traffic grows with the tensor count
+                         "traffic": NT * 82.85e6, "traffic_unit": "bytes per launch, scaled from an 8-tensor ncu capture", "peak_kind": peak_kind, "kernel": "pack_staged_kernel<7,4>",
                          "kernel_ms": kernel_ms},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
             "other_kernels": extras,

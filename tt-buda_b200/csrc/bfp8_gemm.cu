@@ -8,11 +8,13 @@
 // One persistent CTA per SM computes 256x256 output tiles as two 128x256 accumulators (all 512
 // tensor-memory columns), so every decoded weight element feeds 256 rows of activations:
 //   warp 4        producer: per 64-deep k-block, TMA-loads two 128x64 activation boxes (128B swizzle,
-//                 K-major) and bulk-copies the 16 raw Bfp8_b tile records (2 k-tiles x 8 n-tiles)
-//   warps 6-13    decode: each thread takes one 16-value block (one face row: fixed k, 16 consecutive
-//                 n, one shared exponent) from the raw records, turns sign + 7-bit magnitude into
-//                 bfloat16 pairs in registers with one packed fma per pair ((128+m)*s - 128*s, exact)
-//                 and writes them into the N-major ("MN-major") 128B-swizzled operand tile
+//                 K-major)
+//   warps 6..     decode: each thread loads one 16-value block (one face row: fixed k, 16 consecutive
+//                 n, one shared exponent) of the raw Bfp8_b records straight from global memory into
+//                 registers, one k-block ahead; turns sign + 7-bit magnitude into bfloat16 pairs with
+//                 one packed fma per pair ((128+m)*s - 128*s, exact) and writes them into the N-major
+//                 ("MN-major") 128B-swizzled operand tile.  Shared memory only ever holds operands the
+//                 tensor core reads: its bandwidth is what bounds this kernel.
 //   warp 5        one thread issues tcgen05.mma (M=128, N=256, K=16; 2 halves x 4 k-steps per
 //                 k-block) and commits completion to the mbarriers that free the stages
 //   warps 0-3     epilogue: tcgen05.ld the accumulators, round to bfloat16, store C
@@ -21,6 +23,7 @@
 #include <cuda.h>
 
 #include <cstdio>
+#include <cstdlib>
 
 #include "buda_common.cuh"
 
@@ -31,21 +34,25 @@ namespace gemm {
 constexpr int kBM = 256;           // rows of C per tile (two UMMA M=128 halves)
 constexpr int kBN = 256;           // columns of C per tile
 constexpr int kBK = 64;            // k-block
-constexpr int kLoadStages = 3;     // activation + raw-weight ring
-constexpr int kBStages = 2;        // decoded-weight ring
+#ifndef GEMM_A_STAGES
+#define GEMM_A_STAGES 3
+#endif
+#ifndef GEMM_B_STAGES
+#define GEMM_B_STAGES 3
+#endif
+constexpr int kLoadStages = GEMM_A_STAGES;  // activation ring
+constexpr int kBStages = GEMM_B_STAGES;     // decoded-weight ring
 constexpr int kABytes = kBM * kBK * 2;           // 32768
 constexpr int kBBytes = kBN * kBK * 2;           // 32768
 constexpr int kRecord = 1088;                    // Bfp8_b tile record, no header
-constexpr int kRawBytes = 16 * kRecord;          // 2 k-tiles x 8 n-tiles = 17408
-constexpr int kDecodeWarps = 8;
-constexpr int kThreads = 32 * (4 + 1 + 1 + kDecodeWarps);  // 448
+template <int DW>
+constexpr int threads_for() { return 32 * (4 + 1 + 1 + DW); }  // epilogue + producer + MMA + decode warps
 constexpr int kTmemCols = 512;
 
 constexpr int kSmemA = 0;
 constexpr int kSmemB = kSmemA + kLoadStages * kABytes;
-constexpr int kSmemRaw = kSmemB + kBStages * kBBytes;
-constexpr int kSmemBar = kSmemRaw + kLoadStages * kRawBytes;
-constexpr int kNumBars = 4 * kLoadStages + 2 * kBStages + 2;
+constexpr int kSmemBar = kSmemB + kBStages * kBBytes;
+constexpr int kNumBars = 2 * kLoadStages + 2 * kBStages + 2;
 constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 16 + 1024;  // + tmem holder / abort flag, + alignment slack
 
 // instruction descriptor: D = F32, A = B = BF16, A K-major, B MN-major, N = 256, M = 128
@@ -124,21 +131,20 @@ struct Params {
     unsigned int *status;
 };
 
-__global__ void __launch_bounds__(kThreads, 1)
+template <int kDecodeWarps>
+__global__ void __launch_bounds__(threads_for<kDecodeWarps>(), 1)
 bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ Params p)
 {
+    static_assert(32 % kDecodeWarps == 0, "32 decode units per k-block");
     extern __shared__ uint8_t smem_raw[];
     // 128B-swizzled operand tiles repeat every 1024 bytes: align the carve-up to that
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *sA = smem + kSmemA;
     uint8_t *sB = smem + kSmemB;
-    uint8_t *sRaw = smem + kSmemRaw;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kSmemBar);
     uint64_t *full_a = bars;                       // [kLoadStages] activations landed (TMA bytes)
-    uint64_t *full_w = full_a + kLoadStages;       // [kLoadStages] raw weight records landed
-    uint64_t *empty_a = full_w + kLoadStages;      // [kLoadStages] MMAs reading the activations are done
-    uint64_t *empty_w = empty_a + kLoadStages;     // [kLoadStages] decode warps are done with the raw records
-    uint64_t *full_b = empty_w + kLoadStages;      // [kBStages] decoded weights written
+    uint64_t *empty_a = full_a + kLoadStages;      // [kLoadStages] MMAs reading the activations are done
+    uint64_t *full_b = empty_a + kLoadStages;      // [kBStages] decoded weights written
     uint64_t *empty_b = full_b + kBStages;         // [kBStages] MMAs reading the decoded weights are done
     uint64_t *acc_full = empty_b + kBStages;       // accumulators complete
     uint64_t *acc_empty = acc_full + 1;            // accumulators drained by the epilogue
@@ -151,9 +157,7 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     if (tid == 0) {
         for (int s = 0; s < kLoadStages; s++) {
             mbar_init(&full_a[s], 1);
-            mbar_init(&full_w[s], 1);
             mbar_init(&empty_a[s], 1);
-            mbar_init(&empty_w[s], kDecodeWarps);
         }
         for (int t = 0; t < kBStages; t++) {
             mbar_init(&full_b[t], kDecodeWarps);
@@ -181,22 +185,17 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             uint32_t i = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const uint32_t m_blk = tile % p.m_tiles, n_blk = tile / p.m_tiles;
+                const uint32_t m_blk = tile % p.m_tiles;
                 for (uint32_t kb = 0; kb < p.k_blocks; kb++, i++) {
                     const int s = i % kLoadStages;
                     const uint32_t ph = ((i / kLoadStages) & 1u) ^ 1u;
-                    if (!mbar_wait_bounded(&empty_a[s], ph, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT) ||
-                        !mbar_wait_bounded(&empty_w[s], ph, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT)) {
+                    if (!mbar_wait_bounded(&empty_a[s], ph, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT)) {
                         ok = false;
                         break;
                     }
                     mbar_arrive_expect_tx(&full_a[s], kABytes);
                     tma_load_2d(sA + s * kABytes, &tmap_a, (int)(kb * kBK), (int)(m_blk * kBM), &full_a[s]);
                     tma_load_2d(sA + s * kABytes + kABytes / 2, &tmap_a, (int)(kb * kBK), (int)(m_blk * kBM + 128), &full_a[s]);
-                    mbar_arrive_expect_tx(&full_w[s], kRawBytes);
-                    const uint8_t *w0 = p.W + ((uint64_t)(kb * 2) * p.Nt + (uint64_t)n_blk * 8) * kRecord;
-                    bulk_g2s(sRaw + s * kRawBytes, w0, 8 * kRecord, &full_w[s]);
-                    bulk_g2s(sRaw + s * kRawBytes + 8 * kRecord, w0 + (uint64_t)p.Nt * kRecord, 8 * kRecord, &full_w[s]);
                 }
             }
             if (!ok || *abort_flag) {
@@ -205,8 +204,7 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 for (uint32_t k = 1; k <= back; k++) {
                     const uint32_t j = i - k;
                     uint64_t t0 = global_timer_ns();
-                    while (!(mbar_try_wait(&full_a[j % kLoadStages], (j / kLoadStages) & 1u) &&
-                             mbar_try_wait(&full_w[j % kLoadStages], (j / kLoadStages) & 1u)) &&
+                    while (!mbar_try_wait(&full_a[j % kLoadStages], (j / kLoadStages) & 1u) &&
                            global_timer_ns() - t0 < 100000000ull) {
                     }
                 }
@@ -240,7 +238,11 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                             const uint64_t adesc = smem_desc(a_addr + h * (kABytes / 2) + j * 32, 16, 1024);
                             // B: N-major, 64-column atoms 1024 B apart, 8-deep k groups 4096 B apart
                             const uint64_t bdesc = smem_desc(b_addr + j * 8192, 1024, 4096);
+#ifndef GEMM_EXP_NO_MMA
                             umma_bf16(tmem_base + h * kBN, adesc, bdesc, kIdesc, (kb > 0 || j > 0) ? 1u : 0u);
+#else
+                            (void)adesc; (void)bdesc;
+#endif
                         }
                     }
                     umma_commit(&empty_a[s]);
@@ -252,32 +254,64 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         __syncwarp();
     } else if (warp >= 6) {
         // ------------------------------------------------------------------ decode warps
+        // Raw records go global -> registers (coalesced 16-byte loads, one block per thread per unit),
+        // one k-block ahead of the decode, so they never cost shared-memory bandwidth.
+        constexpr int kUnits = 32 / kDecodeWarps;  // units of 32 blocks per warp per k-block
         const int dw = warp - 6;
+        uint4 mant_next[kUnits];
+        uint32_t exp_next[kUnits];
+        auto fetch = [&](uint32_t n_blk, uint32_t kb) {
+#pragma unroll
+            for (int it = 0; it < kUnits; it++) {
+                const int u = it * kDecodeWarps + dw;          // 32 units: (record, half of its 64 blocks)
+                const int r = u >> 1;                           // record: k-tile r / 8, n-tile r % 8
+                const int blk = (u & 1) * 32 + lane;            // block = face * 16 + face row
+                const uint8_t *rec = p.W + ((uint64_t)(kb * 2 + (r >> 3)) * p.Nt + (uint64_t)n_blk * 8 + (r & 7)) * kRecord;
+                mant_next[it] = __ldg(reinterpret_cast<const uint4 *>(rec + 64 + blk * 16));
+                exp_next[it] = __ldg(rec + blk);
+            }
+        };
         uint32_t i = 0;
         bool ok = true;
+        if (blockIdx.x < total_tiles) fetch(blockIdx.x / p.m_tiles, 0);
         for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const uint32_t n_blk = tile / p.m_tiles;
             for (uint32_t kb = 0; kb < p.k_blocks; kb++, i++) {
-                const int s = i % kLoadStages, t = i % kBStages;
-                const bool got = mbar_wait_bounded(&full_w[s], (i / kLoadStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT) &&
-                                 mbar_wait_bounded(&empty_b[t], ((i / kBStages) & 1u) ^ 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT);
+                const int t = i % kBStages;
+                uint4 mant_cur[kUnits];
+                uint32_t exp_cur[kUnits];
+#pragma unroll
+                for (int it = 0; it < kUnits; it++) {
+                    mant_cur[it] = mant_next[it];
+                    exp_cur[it] = exp_next[it];
+                }
+                // issue the next k-block's loads before waiting for a free stage
+                if (kb + 1 < p.k_blocks) {
+                    fetch(n_blk, kb + 1);
+                } else if (tile + gridDim.x < total_tiles) {
+                    fetch((tile + gridDim.x) / p.m_tiles, 0);
+                }
+                const bool got = mbar_wait_bounded(&empty_b[t], ((i / kBStages) & 1u) ^ 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT);
                 if (!__all_sync(0xffffffffu, got)) {  // the whole warp leaves together
                     ok = false;
                     break;
                 }
-                const uint8_t *raw = sRaw + s * kRawBytes;
                 uint8_t *bst = sB + t * kBBytes;
+#ifdef GEMM_EXP_NO_DECODE
+                if (exp_cur[0] == 0x12345u) bst[lane] = (uint8_t)mant_cur[0].x;
+                if (false)
+#endif
 #pragma unroll
-                for (int it = 0; it < 4; it++) {
-                    const int u = it * kDecodeWarps + dw;          // 32 units: (record, half of its 64 blocks)
-                    const int r = u >> 1;                           // record: k-tile r / 8, n-tile r % 8
-                    const int blk = (u & 1) * 32 + lane;            // block = face * 16 + face row
-                    const uint8_t *rec = raw + r * kRecord;
-                    const uint4 mant = *reinterpret_cast<const uint4 *>(rec + 64 + blk * 16);
-                    const uint32_t E = rec[blk];
-                    // scale 2^(E-133) as bfloat16 bits (exponent field E-6); blocks below 2^-126 flush to zero
-                    const uint32_t e6 = E > 6u ? E - 6u : 0u;
-                    const uint32_t sc = (e6 << 7) * 0x00010001u;
-                    const uint32_t off = e6 ? ((((e6 + 7u) << 7) | 0x8000u) * 0x00010001u) : 0u;  // -128 * scale
+                for (int it = 0; it < kUnits; it++) {
+                    const int u = it * kDecodeWarps + dw;
+                    const int r = u >> 1;
+                    const int blk = (u & 1) * 32 + lane;
+                    const uint4 mant = mant_cur[it];
+                    // scale 2^(E-133) as bfloat16 bits (exponent field E-6) in both halves; -128 * scale beside it.
+                    // Blocks below 2^-126 (E < 7) flush to zero.
+                    const uint32_t e6 = max(exp_cur[it], 6u) - 6u;
+                    const uint32_t sc = e6 * 0x00800080u;
+                    const uint32_t off = e6 ? sc + 0x83808380u : 0u;
                     const uint32_t w[4] = {mant.x, mant.y, mant.z, mant.w};
                     uint32_t o[8];
 #pragma unroll
@@ -298,10 +332,7 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 }
                 fence_async_smem();  // the tensor core reads shared memory through the async proxy
                 __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(&full_b[t]);
-                    mbar_arrive(&empty_w[s]);
-                }
+                if (lane == 0) mbar_arrive(&full_b[t]);
             }
         }
     } else {
@@ -320,7 +351,11 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 for (int c = 0; c < kBN / 32; c++) {
                     uint32_t v[32];
                     tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(h * kBN + c * 32), v);
+#ifdef GEMM_EXP_NO_STORE
+                    if (row < p.M && v[0] == 0x7fc12345u) {
+#else
                     if (row < p.M) {
+#endif
 #pragma unroll
                         for (int q = 0; q < 4; q++) {
                             uint4 o;
@@ -397,12 +432,19 @@ cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, 
         snprintf(err, err_len, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
         return cudaErrorInvalidValue;
     }
+    static int decode_warps = 0;
+    if (decode_warps == 0) {
+        const char *env = getenv("BUDA_GEMM_DECODE_WARPS");  // tuning knob: 8 (default, measured fastest) or 16
+        decode_warps = (env && atoi(env) == 16) ? 16 : 8;
+    }
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     dev &= 63;
     if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(bfp8b_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(bfp8b_gemm_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(bfp8b_gemm_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
@@ -417,7 +459,10 @@ cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, 
     p.status = status;
     uint32_t grid = p.m_tiles * p.n_tiles;
     if (grid > (uint32_t)sm_count) grid = (uint32_t)sm_count;
-    bfp8b_gemm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap, p);
+    if (decode_warps == 8)
+        bfp8b_gemm_kernel<8><<<grid, threads_for<8>(), kSmemBytes, stream>>>(tmap, p);
+    else
+        bfp8b_gemm_kernel<16><<<grid, threads_for<16>(), kSmemBytes, stream>>>(tmap, p);
     return cudaGetLastError();
 }
 

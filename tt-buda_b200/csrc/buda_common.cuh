@@ -134,6 +134,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
     return ok != 0;
 }
 
+// try_wait that lets the hardware park the thread for up to `hint_ns` (it wakes as soon as the phase
+// completes), so a long wait costs no issue slots that working warps could use
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t *bar, uint32_t parity, uint32_t hint_ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+
 __device__ __forceinline__ uint64_t global_timer_ns()
 {
     uint64_t t;
@@ -150,17 +165,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
                                                   unsigned int *status, unsigned int code)
 {
     if (mbar_try_wait(bar, parity)) return true;
-    uint64_t t0 = global_timer_ns();
-    uint32_t spins = 0;
+    const uint64_t t0 = global_timer_ns();
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 0xffu) == 0) {
-            if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
-                *abort_flag = 1;
-                report_status(status, code);
-                return false;
-            }
+        // parked for up to 20 us at a time: no spinning, and the abort flag / deadline are still looked at
+        if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
+        if (*abort_flag) return false;
+        if (global_timer_ns() - t0 > kWaitLimitNs) {
+            *abort_flag = 1;
+            report_status(status, code);
+            return false;
         }
     }
 }

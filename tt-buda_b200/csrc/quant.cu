@@ -48,22 +48,46 @@ __device__ __forceinline__ void load_scales16(const float *__restrict__ scale, c
     }
 }
 
-__device__ __forceinline__ int clamp_cast_i8(float r, float lo, float hi)
+// torch.round (half to even) of 16 values in place.  Below 2^22 adding and subtracting 1.5 * 2^23 IS
+// that rounding (one binary32 add rounds to nearest even at integer granularity) and runs on the
+// full-rate pipe; a thread that holds any larger magnitude takes the conversion instruction for its
+// chunk instead (one branch per 16 values, rarely taken).  NaN stays NaN on either path.
+__device__ __forceinline__ void round_half_even16(float (&t)[16])
 {
-    // torch.clamp keeps NaN, and the cast of NaN gives 0
-    const float c = fminf(fmaxf(r, lo), hi);
-    return (r != r) ? 0 : (int)c;
+    bool big = false;
+#pragma unroll
+    for (int k = 0; k < 16; k++) big = big || (fabsf(t[k]) >= 4194304.0f);
+    if (big) {
+#pragma unroll
+        for (int k = 0; k < 16; k++) t[k] = rintf(t[k]);
+    } else {
+#pragma unroll
+        for (int k = 0; k < 16; k++) t[k] = __fadd_rn(__fadd_rn(t[k], 12582912.0f), -12582912.0f);
+    }
 }
 
-__device__ __forceinline__ uint32_t pack_i8x4(int a, int b, int c, int d)
+// clamp (torch.clamp keeps NaN; the cast of NaN gives 0) and cast to int8, returned in the low byte.
+// FAST (bounds within +-2^22): the two's-complement low byte of an integer-valued float c is the low
+// byte of the bits of c + 1.5 * 2^23, so no float->int conversion instruction is needed.
+template <bool FAST>
+__device__ __forceinline__ uint32_t clamp_cast_i8(float r, float lo, float hi)
 {
-    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
+    float c = fminf(fmaxf(r, lo), hi);
+    c = (r != r) ? 0.0f : c;
+    if (FAST) return __float_as_uint(__fadd_rn(c, 12582912.0f));
+    return (uint32_t)(int)c;
+}
+
+// low bytes of four words -> one word
+__device__ __forceinline__ uint32_t pack_i8x4(uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
 
 // ------------------------------------------------------------------------------------------------
 // quantize: MODE 0 divides by the scale, MODE 1 multiplies by it
 // ------------------------------------------------------------------------------------------------
-template <int MODE, int SM, bool VEC>
+template <int MODE, int SM, bool VEC, bool FAST>
 __global__ void __launch_bounds__(256)
 quantize_kernel(const float *__restrict__ x, int64_t n, const float *__restrict__ scale, ScaleSel sel, float zp, float lo,
                 float hi, int8_t *__restrict__ out)
@@ -85,12 +109,12 @@ quantize_kernel(const float *__restrict__ x, int64_t n, const float *__restrict_
             for (int k = 0; k < 16; k++) v[k] = (k < cnt) ? x[i0 + k] : 0.0f;
         }
         load_scales16<SM>(scale, sel, i0, cnt, s);
-        int q[16];
+        uint32_t q[16];
 #pragma unroll
-        for (int k = 0; k < 16; k++) {
-            const float t = (MODE == 0) ? __fdiv_rn(v[k], s[k]) : __fmul_rn(v[k], s[k]);
-            q[k] = clamp_cast_i8(__fadd_rn(rintf(t), zp), lo, hi);
-        }
+        for (int k = 0; k < 16; k++) v[k] = (MODE == 0) ? __fdiv_rn(v[k], s[k]) : __fmul_rn(v[k], s[k]);
+        round_half_even16(v);
+#pragma unroll
+        for (int k = 0; k < 16; k++) q[k] = clamp_cast_i8<FAST>(__fadd_rn(v[k], zp), lo, hi);
         if (VEC && cnt == 16) {
             uint4 o = make_uint4(pack_i8x4(q[0], q[1], q[2], q[3]), pack_i8x4(q[4], q[5], q[6], q[7]),
                                  pack_i8x4(q[8], q[9], q[10], q[11]), pack_i8x4(q[12], q[13], q[14], q[15]));
@@ -98,7 +122,7 @@ quantize_kernel(const float *__restrict__ x, int64_t n, const float *__restrict_
         } else {
 #pragma unroll
             for (int k = 0; k < 16; k++)
-                if (k < cnt) out[i0 + k] = (int8_t)q[k];
+                if (k < cnt) out[i0 + k] = (int8_t)(q[k] & 0xffu);
         }
     }
 }
@@ -115,21 +139,23 @@ dequantize_kernel(const int8_t *__restrict__ x, int64_t n, const float *__restri
     for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * blockDim.x) {
         const int64_t i0 = c << 4;
         const int cnt = (n - i0 >= 16) ? 16 : (int)(n - i0);
-        int xi[16];
+        float xf[16];
         float s[16];
         if (VEC && cnt == 16) {
             const uint4 t = __ldcs(reinterpret_cast<const uint4 *>(x + i0));
-            const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+            const uint32_t w[4] = {t.x ^ 0x80808080u, t.y ^ 0x80808080u, t.z ^ 0x80808080u, t.w ^ 0x80808080u};
+            // int8 -> float without a conversion instruction: byte + 128 spliced under 1.5 * 2^23, minus the bias
 #pragma unroll
-            for (int k = 0; k < 16; k++) xi[k] = (int)(int8_t)(w[k >> 2] >> (8 * (k & 3)));
+            for (int k = 0; k < 16; k++)
+                xf[k] = __fadd_rn(__uint_as_float(__byte_perm(w[k >> 2], 0x4b400000u, 0x7650 + (k & 3))), -12583040.0f);
         } else {
 #pragma unroll
-            for (int k = 0; k < 16; k++) xi[k] = (k < cnt) ? (int)x[i0 + k] : 0;
+            for (int k = 0; k < 16; k++) xf[k] = (k < cnt) ? (float)x[i0 + k] : 0.0f;
         }
         load_scales16<SM>(scale, sel, i0, cnt, s);
         float r[16];
 #pragma unroll
-        for (int k = 0; k < 16; k++) r[k] = __fmul_rn(__fsub_rn((float)xi[k], zp), s[k]);
+        for (int k = 0; k < 16; k++) r[k] = __fmul_rn(__fsub_rn(xf[k], zp), s[k]);
         if (VEC && cnt == 16) {
             float4 *o = reinterpret_cast<float4 *>(out + i0);
 #pragma unroll
@@ -145,7 +171,7 @@ dequantize_kernel(const int8_t *__restrict__ x, int64_t n, const float *__restri
 // ------------------------------------------------------------------------------------------------
 // requantize: MODE 0 uses inp_scale / out_scale, MODE 1 uses scale_a alone
 // ------------------------------------------------------------------------------------------------
-template <int MODE, int SM, bool VEC>
+template <int MODE, int SM, bool VEC, bool FAST>
 __global__ void __launch_bounds__(256)
 requantize_kernel(const int32_t *__restrict__ x, int64_t n, const float *__restrict__ scale_a,
                   const float *__restrict__ scale_b, ScaleSel sel, float zp, float lo, float hi, int8_t *__restrict__ out)
@@ -174,13 +200,16 @@ requantize_kernel(const int32_t *__restrict__ x, int64_t n, const float *__restr
 #pragma unroll
             for (int k = 0; k < 16; k++) s[k] = __fdiv_rn(s[k], sb[k]);
         }
-        int q[16];
+        uint32_t q[16];
+        float pz[16];
 #pragma unroll
         for (int k = 0; k < 16; k++) {
             // the int32 operand is promoted to binary32 (round to nearest even) by the multiply
-            const float p = __fmul_rn(s[k], __int2float_rn(xi[k]));
-            q[k] = clamp_cast_i8(rintf(__fadd_rn(p, zp)), lo, hi);
+            pz[k] = __fadd_rn(__fmul_rn(s[k], __int2float_rn(xi[k])), zp);
         }
+        round_half_even16(pz);
+#pragma unroll
+        for (int k = 0; k < 16; k++) q[k] = clamp_cast_i8<FAST>(pz[k], lo, hi);
         if (VEC && cnt == 16) {
             uint4 o = make_uint4(pack_i8x4(q[0], q[1], q[2], q[3]), pack_i8x4(q[4], q[5], q[6], q[7]),
                                  pack_i8x4(q[8], q[9], q[10], q[11]), pack_i8x4(q[12], q[13], q[14], q[15]));
@@ -188,7 +217,7 @@ requantize_kernel(const int32_t *__restrict__ x, int64_t n, const float *__restr
         } else {
 #pragma unroll
             for (int k = 0; k < 16; k++)
-                if (k < cnt) out[i0 + k] = (int8_t)q[k];
+                if (k < cnt) out[i0 + k] = (int8_t)(q[k] & 0xffu);
         }
     }
 }
@@ -230,13 +259,16 @@ cudaError_t launch_quantize(const float *x, int64_t n, const float *scale, int64
     const int sm = pick_scale_mode(scale_len, inner, scale, nullptr);
     const bool vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
     const unsigned grid = grid_for(n, sm_count);
-#define CALL(SMV)                                                                                              \
-    if (mode == 0) {                                                                                           \
-        if (vec) quantize_kernel<0, SMV, true><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out);   \
-        else quantize_kernel<0, SMV, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out);      \
-    } else {                                                                                                   \
-        if (vec) quantize_kernel<1, SMV, true><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out);   \
-        else quantize_kernel<1, SMV, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out);      \
+    const bool fast = lo >= -4194304.0f && hi <= 4194304.0f;
+#define CALL(SMV)                                                                                                     \
+    if (mode == 0) {                                                                                                  \
+        if (vec && fast) quantize_kernel<0, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out);   \
+        else if (vec) quantize_kernel<0, SMV, true, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out);     \
+        else quantize_kernel<0, SMV, false, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out);             \
+    } else {                                                                                                          \
+        if (vec && fast) quantize_kernel<1, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out);   \
+        else if (vec) quantize_kernel<1, SMV, true, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out);     \
+        else quantize_kernel<1, SMV, false, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out);             \
     }
     BUDA_SM_SWITCH(sm, CALL)
 #undef CALL
@@ -266,13 +298,16 @@ cudaError_t launch_requantize(const int32_t *x, int64_t n, const float *scale_a,
     const int sm = pick_scale_mode(scale_len, inner, scale_a, mode == 0 ? scale_b : nullptr);
     const bool vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
     const unsigned grid = grid_for(n, sm_count);
-#define CALL(SMV)                                                                                                          \
-    if (mode == 0) {                                                                                                       \
-        if (vec) requantize_kernel<0, SMV, true><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out);  \
-        else requantize_kernel<0, SMV, false><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out);     \
-    } else {                                                                                                               \
-        if (vec) requantize_kernel<1, SMV, true><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out);  \
-        else requantize_kernel<1, SMV, false><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out);     \
+    const bool fast = lo >= -4194304.0f && hi <= 4194304.0f;
+#define CALL(SMV)                                                                                                                 \
+    if (mode == 0) {                                                                                                              \
+        if (vec && fast) requantize_kernel<0, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out);  \
+        else if (vec) requantize_kernel<0, SMV, true, false><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out);    \
+        else requantize_kernel<0, SMV, false, false><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out);            \
+    } else {                                                                                                                      \
+        if (vec && fast) requantize_kernel<1, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out);  \
+        else if (vec) requantize_kernel<1, SMV, true, false><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out);    \
+        else requantize_kernel<1, SMV, false, false><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out);            \
     }
     BUDA_SM_SWITCH(sm, CALL)
 #undef CALL

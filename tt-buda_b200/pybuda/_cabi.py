@@ -5,7 +5,9 @@ raises at import, and every compute call needs a CUDA device.
 import ctypes
 import os
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libbuda_cuda.so")
+# BUDA_CUDA_LIB points at another build of the same library (e.g. one compiled with tuning macros)
+_LIB_PATH = os.environ.get("BUDA_CUDA_LIB") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libbuda_cuda.so")
 if not os.path.exists(_LIB_PATH):
     raise ImportError(
         f"{_LIB_PATH} is missing: build it with `python tt-buda_b200/build.py` (there is no CPU fallback)")
