@@ -6,10 +6,10 @@
 //
 // Two kernels:
 //   pack_staged_kernel  (16-byte aligned rows; the hot path)
-//     A persistent CTA per SM slot walks work items; an item is a band of 32 rows x up to 4 tiles
-//     (128 columns).  One producer warp stages the band in shared memory with 32 bulk async
-//     copies (one per row, TMA engine, completion on an mbarrier) several items ahead; eight
-//     consumer warps then each own one 16-column face column of the band: lane = row, so a thread
+//     A persistent CTA per SM slot walks work items; an item is a band of 32 rows x up to 8 tiles
+//     (256 columns).  One producer warp stages the band in shared memory with 32 bulk async
+//     copies (one per row, TMA engine, completion on an mbarrier) one item ahead; eight
+//     consumer warps then each own 16-column face columns of the band: lane = row, so a thread
 //     reads one whole 16-value block (one face row) from shared memory, encodes it in registers
 //     and drops its 16/8/4 mantissa bytes plus the exponent byte into the tile record being
 //     assembled in shared memory.  Finished records leave with one bulk async store per tile.
@@ -43,7 +43,11 @@ struct PackCfg {
     static constexpr int payload = (M > 0) ? (64 + 1024 * (M + 1) / 8) : (1024 * ES);
     static constexpr int rec_max = payload + 32;
     static constexpr int out_buf_bytes = kBoxTiles * rec_max;
-    static constexpr int stages = (in_stage_bytes > 12000) ? 3 : 4;
+#ifdef BUDA_PACK_STAGES
+    static constexpr int stages = BUDA_PACK_STAGES;
+#else
+    static constexpr int stages = 2;  // depth comes from the CTAs resident per SM, not from stages per CTA
+#endif
     static constexpr int smem_bytes = stages * in_stage_bytes + 2 * out_buf_bytes + stages * (int)sizeof(ItemMeta) +
                                       2 * stages * 8 + 16;
 };
@@ -128,9 +132,6 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
     }
 
     // -------------------------------------------------------------------- consumer warps
-    const int bc = warp;              // face column of the band: tile bc/2, left/right face bc%2
-    const int tile_in_box = bc >> 1;
-    const int face = ((lane >> 4) << 1) | (bc & 1);
     const int fr = lane & 15;
     uint32_t it = 0;
     for (uint32_t item = blockIdx.x; item < job.total_items; item += gridDim.x, ++it) {
@@ -144,6 +145,10 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
         if (!ok) {
             // fall through to the barrier below so the whole CTA leaves together
         } else if (M > 0) {
+#pragma unroll
+          for (int bc = warp; bc < 2 * kBoxTiles; bc += kConsumerWarps) {  // face column: tile bc/2, left/right face bc%2
+            const int tile_in_box = bc >> 1;
+            const int face = ((lane >> 4) << 1) | (bc & 1);
             if ((uint32_t)tile_in_box < m.ntiles) {
                 uint32_t x[16];
                 const uint8_t *p = stage + lane * Cfg::pitch + bc * 16 * ES;
@@ -176,6 +181,7 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
                 else if (MM == 3) *reinterpret_cast<uint2 *>(q) = make_uint2(d[0], d[1 % BfpTraits<MM>::words]);
                 else *reinterpret_cast<uint32_t *>(q) = d[0];
             }
+          }
         } else {
             // plain relayout: the record is moved as 16-byte chunks; chunk c of a record is face
             // c / (16*cpr), face row (c / cpr) % 16, part c % cpr  (cpr = chunks per 16-value face row)

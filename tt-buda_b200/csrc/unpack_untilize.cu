@@ -29,7 +29,11 @@ struct UnpackCfg {
     static constexpr int payload = (M > 0) ? (64 + 1024 * (M + 1) / 8) : (1024 * ES);
     static constexpr int rec_max = payload + 32;
     static constexpr int in_stage_bytes = kBoxTiles * rec_max;
+#ifdef BUDA_UNPACK_STAGES
+    static constexpr int stages = BUDA_UNPACK_STAGES;
+#else
     static constexpr int stages = 4;
+#endif
     static constexpr int smem_bytes = stages * in_stage_bytes + 2 * out_buf_bytes + stages * (int)sizeof(UItemMeta) +
                                       2 * stages * 8 + 16;
 };
@@ -111,9 +115,6 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
     }
 
     // -------------------------------------------------------------------- consumer warps
-    const int bc = warp;
-    const int tile_in_box = bc >> 1;
-    const int face = ((lane >> 4) << 1) | (bc & 1);
     const int fr = lane & 15;
     uint32_t it = 0;
     for (uint32_t item = blockIdx.x; item < job.total_items; item += gridDim.x, ++it) {
@@ -127,6 +128,10 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
         if (!ok) {
             // fall through to the barrier below so the whole CTA leaves together
         } else if (M > 0) {
+#pragma unroll
+          for (int bc = warp; bc < 2 * kBoxTiles; bc += kUConsumerWarps) {  // face column: tile bc/2, left/right face bc%2
+            const int tile_in_box = bc >> 1;
+            const int face = ((lane >> 4) << 1) | (bc & 1);
             if ((uint32_t)tile_in_box < m.ntiles) {
                 constexpr int MM = M > 0 ? M : 7;
                 const uint8_t *r = stage + tile_in_box * rec + hdr;
@@ -160,6 +165,7 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
                     *reinterpret_cast<uint4 *>(p + 16) = make_uint4(h[4], h[5], h[6], h[7]);
                 }
             }
+          }
         } else {
             constexpr int cpr = ES;
             constexpr int chunks_per_tile = 64 * cpr;
