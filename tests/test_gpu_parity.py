@@ -312,3 +312,30 @@ def test_bad_arguments_return_runtime_error(ops):
         ops.tilize_pack(y, ops.DF.Bfp8)  # 'a' formats are not on this path yet
     rc, st = cabi.device_status()
     assert rc == cabi.SUCCESS and st == 0
+
+
+def test_config5_bert_large_weight_set_round_trip(ops, oracle):
+    # 24 layers x {Q, K, V, O [1024,1024], FFN [1024,4096] and [4096,1024]}, fp32 ~ N(0, 0.02):
+    # fp32 -> Bfp8_b -> fp32, untilized back to row-major; layers are the sharding unit across GPUs
+    from pybuda.sharding import units_of_rank
+
+    assert sorted(sum((units_of_rank(24, r, 8) for r in range(8)), [])) == list(range(24))
+    total = 0
+    for layer in units_of_rank(24, 0, 1):
+        shapes = [(1024, 1024)] * 4 + [(1024, 4096), (4096, 1024)]
+        ws = [torch.randn(s, generator=torch.Generator().manual_seed(2000 + 6 * layer + j)) * 0.02 for j, s in enumerate(shapes)]
+        # the four attention matrices of a layer go as one batched launch
+        imgs = ops.tilize_pack_batch([w.reshape(1, 1, *w.shape).cuda() for w in ws[:4]], ops.DF.Bfp8_b)
+        imgs += [ops.tilize_pack(w.reshape(1, 1, *w.shape).cuda(), ops.DF.Bfp8_b) for w in ws[4:]]
+        check = layer in (0, 11, 23)          # the oracle round trip on three layers, properties on all
+        for w, img in zip(ws, imgs):
+            y = ops.unpack_untilize(img, ops.DF.Bfp8_b, (1, 1, *w.shape))[0, 0]
+            total += w.numel()
+            assert (y.cpu() - w).abs().max() <= w.abs().max() * 2.0 ** -6      # 7 magnitude bits under a shared exponent
+            assert torch.equal(ops.tilize_pack(y.reshape(1, 1, *w.shape), ops.DF.Bfp8_b), img)   # idempotent
+            if check:
+                ref = oracle.tilize_pack(w.numpy().reshape(1, 1, *w.shape), oracle.Bfp8_b)
+                assert np.array_equal(img.cpu().numpy(), ref)
+                yref = oracle.unpack_untilize(ref, oracle.Bfp8_b, (1, 1, *w.shape))[0, 0]
+                assert np.array_equal(_bits(y.cpu().numpy()), _bits(yref))
+    assert total == 301989888

@@ -5,9 +5,11 @@
 // pybuda/pybuda/op/eval/buda/quantize.py:23-53): IEEE division, separate multiply and add (never
 // fused), round-half-to-even, clamp, truncating cast; NaN survives the clamp and casts to 0.
 //
-// A thread owns 16 consecutive elements: four 128-bit streaming loads in flight, one 128-bit store
-// (quantise / requantise) or four (dequantise).  The scale of element i is
-// scale[(i / inner) % scale_len].
+// Quantise / requantise: a thread owns 16 consecutive elements (four 128-bit streaming loads in
+// flight, one 128-bit store).  Dequantise, whose traffic is 4/5 stores: a warp owns 512 consecutive
+// elements and a thread takes the groups of 4 at lane, lane + 32, lane + 64, lane + 96, so every
+// store instruction of a warp writes one contiguous 512-byte run.  (Measured on B200: each layout
+// is the faster one for its kernel.)  The scale of element i is scale[(i / inner) % scale_len].
 #include "buda_common.cuh"
 
 namespace buda {
@@ -16,7 +18,10 @@ enum ScaleMode : int {
     kScalePerTensor = 0,   // scale_len == 1
     kScaleLastAxis16 = 1,  // inner == 1, scale_len % 16 == 0: 16 consecutive scales per thread
     kScaleChunk = 2,       // inner % 16 == 0: one scale per 16-element chunk
-    kScaleGeneral = 3      // per-element index arithmetic
+    kScaleGeneral = 3,     // per-element index arithmetic
+    // the dequantise kernel deals groups of 4 elements instead of chunks of 16
+    kScaleLastAxis4 = 4,   // inner == 1, scale_len % 4 == 0, aligned: 4 consecutive scales per group
+    kScaleGroup = 5        // inner % 4 == 0: one scale per group
 };
 
 struct ScaleSel {
@@ -47,6 +52,29 @@ __device__ __forceinline__ void load_scales16(const float *__restrict__ scale, c
         for (int k = 0; k < 16; k++) s[k] = (k < cnt) ? __ldg(scale + ((i0 + k) / sel.inner) % sel.scale_len) : 1.0f;
     }
 }
+
+constexpr int kGroupsPerThread = 4;
+constexpr int kThreadsPerBlock = 256;
+
+template <int SM>
+__device__ __forceinline__ void load_scales4(const float *__restrict__ scale, const ScaleSel sel, int64_t i0, float (&s)[4])
+{
+    if (SM == kScalePerTensor) {
+        s[0] = s[1] = s[2] = s[3] = __ldg(scale);
+    } else if (SM == kScaleLastAxis4) {
+        const float4 v = __ldg(reinterpret_cast<const float4 *>(scale + (i0 % sel.scale_len)));
+        s[0] = v.x; s[1] = v.y; s[2] = v.z; s[3] = v.w;
+    } else if (SM == kScaleGroup) {
+        s[0] = s[1] = s[2] = s[3] = __ldg(scale + (i0 / sel.inner) % sel.scale_len);
+    } else {
+#pragma unroll
+        for (int k = 0; k < 4; k++) s[k] = __ldg(scale + ((i0 + k) / sel.inner) % sel.scale_len);
+    }
+}
+
+// Which groups a thread owns: warp w of the grid covers groups [w*128, w*128 + 128); lane takes
+// w*128 + j*32 + lane for j = 0..3.
+__device__ __forceinline__ int64_t first_group(int64_t warp_index, int lane) { return warp_index * 128 + lane; }
 
 // torch.round (half to even) of 16 values in place.  Below 2^22 adding and subtracting 1.5 * 2^23 IS
 // that rounding (one binary32 add rounds to nearest even at integer granularity) and runs on the
@@ -90,13 +118,17 @@ __device__ __forceinline__ uint32_t pack_i8x4(uint32_t a, uint32_t b, uint32_t c
 template <int MODE, int SM, bool VEC, bool FAST>
 __global__ void __launch_bounds__(256)
 quantize_kernel(const float *__restrict__ x, int64_t n, const float *__restrict__ scale, ScaleSel sel, float zp, float lo,
-                float hi, int8_t *__restrict__ out)
+                float hi, int8_t *__restrict__ out, int hoist)
 {
     const int64_t chunks = (n + 15) >> 4;
+    float s[16];
+    // when the grid stride is a whole number of scale periods a thread meets the same 16 scales in
+    // every sweep: fetch them once
+    if (hoist) load_scales16<SM>(scale, sel, ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) << 4, 16, s);
     for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * blockDim.x) {
         const int64_t i0 = c << 4;
         const int cnt = (n - i0 >= 16) ? 16 : (int)(n - i0);
-        float v[16], s[16];
+        float v[16];
         if (VEC && cnt == 16) {
             const float4 *p = reinterpret_cast<const float4 *>(x + i0);
 #pragma unroll
@@ -108,7 +140,7 @@ quantize_kernel(const float *__restrict__ x, int64_t n, const float *__restrict_
 #pragma unroll
             for (int k = 0; k < 16; k++) v[k] = (k < cnt) ? x[i0 + k] : 0.0f;
         }
-        load_scales16<SM>(scale, sel, i0, cnt, s);
+        if (!hoist) load_scales16<SM>(scale, sel, i0, cnt, s);
         uint32_t q[16];
 #pragma unroll
         for (int k = 0; k < 16; k++) v[k] = (MODE == 0) ? __fdiv_rn(v[k], s[k]) : __fmul_rn(v[k], s[k]);
@@ -130,42 +162,46 @@ quantize_kernel(const float *__restrict__ x, int64_t n, const float *__restrict_
 // ------------------------------------------------------------------------------------------------
 // dequantize
 // ------------------------------------------------------------------------------------------------
-template <int SM, bool VEC>
-__global__ void __launch_bounds__(256)
-dequantize_kernel(const int8_t *__restrict__ x, int64_t n, const float *__restrict__ scale, ScaleSel sel, float zp,
-                  float *__restrict__ out)
+template <int SM>
+__global__ void __launch_bounds__(kThreadsPerBlock)
+dequantize_vec_kernel(const int8_t *__restrict__ x, int64_t groups, const float *__restrict__ scale, ScaleSel sel, float zp,
+                      float *__restrict__ out)
 {
-    const int64_t chunks = (n + 15) >> 4;
-    for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t i0 = c << 4;
-        const int cnt = (n - i0 >= 16) ? 16 : (int)(n - i0);
-        float xf[16];
-        float s[16];
-        if (VEC && cnt == 16) {
-            const uint4 t = __ldcs(reinterpret_cast<const uint4 *>(x + i0));
-            const uint32_t w[4] = {t.x ^ 0x80808080u, t.y ^ 0x80808080u, t.z ^ 0x80808080u, t.w ^ 0x80808080u};
-            // int8 -> float without a conversion instruction: byte + 128 spliced under 1.5 * 2^23, minus the bias
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * (kThreadsPerBlock / 32);
+    for (int64_t w = (int64_t)blockIdx.x * (kThreadsPerBlock / 32) + (threadIdx.x >> 5); w * 128 < groups; w += warps) {
+        const int64_t g0 = first_group(w, lane);
+        uint32_t xw[kGroupsPerThread];
 #pragma unroll
-            for (int k = 0; k < 16; k++)
-                xf[k] = __fadd_rn(__uint_as_float(__byte_perm(w[k >> 2], 0x4b400000u, 0x7650 + (k & 3))), -12583040.0f);
-        } else {
-#pragma unroll
-            for (int k = 0; k < 16; k++) xf[k] = (k < cnt) ? (float)x[i0 + k] : 0.0f;
+        for (int j = 0; j < kGroupsPerThread; j++) {
+            const int64_t g = g0 + j * 32;
+            xw[j] = (g < groups) ? __ldcs(reinterpret_cast<const uint32_t *>(x) + g) : 0u;
         }
-        load_scales16<SM>(scale, sel, i0, cnt, s);
-        float r[16];
 #pragma unroll
-        for (int k = 0; k < 16; k++) r[k] = __fmul_rn(__fsub_rn(xf[k], zp), s[k]);
-        if (VEC && cnt == 16) {
-            float4 *o = reinterpret_cast<float4 *>(out + i0);
+        for (int j = 0; j < kGroupsPerThread; j++) {
+            const int64_t g = g0 + j * 32;
+            if (g < groups) {
+                float s[4], r[4];
+                load_scales4<SM>(scale, sel, g * 4, s);
+                // int8 -> float without a conversion instruction: byte + 128 spliced under 1.5 * 2^23, minus the bias
+                const uint32_t b = xw[j] ^ 0x80808080u;
 #pragma unroll
-            for (int j = 0; j < 4; j++) __stcs(o + j, make_float4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]));
-        } else {
-#pragma unroll
-            for (int k = 0; k < 16; k++)
-                if (k < cnt) out[i0 + k] = r[k];
+                for (int k = 0; k < 4; k++) {
+                    const float xf = __fadd_rn(__uint_as_float(__byte_perm(b, 0x4b400000u, 0x7650 + k)), -12583040.0f);
+                    r[k] = __fmul_rn(__fsub_rn(xf, zp), s[k]);
+                }
+                __stcs(reinterpret_cast<float4 *>(out) + g, make_float4(r[0], r[1], r[2], r[3]));
+            }
         }
     }
+}
+
+__global__ void __launch_bounds__(kThreadsPerBlock)
+dequantize_scalar_kernel(const int8_t *__restrict__ x, int64_t first, int64_t n, const float *__restrict__ scale, ScaleSel sel,
+                         float zp, float *__restrict__ out)
+{
+    for (int64_t i = first + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = __fmul_rn(__fsub_rn((float)x[i], zp), scale[(i / sel.inner) % sel.scale_len]);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -174,14 +210,27 @@ dequantize_kernel(const int8_t *__restrict__ x, int64_t n, const float *__restri
 template <int MODE, int SM, bool VEC, bool FAST>
 __global__ void __launch_bounds__(256)
 requantize_kernel(const int32_t *__restrict__ x, int64_t n, const float *__restrict__ scale_a,
-                  const float *__restrict__ scale_b, ScaleSel sel, float zp, float lo, float hi, int8_t *__restrict__ out)
+                  const float *__restrict__ scale_b, ScaleSel sel, float zp, float lo, float hi, int8_t *__restrict__ out,
+                  int hoist)
 {
     const int64_t chunks = (n + 15) >> 4;
+    float s[16];
+    // when the grid stride is a whole number of scale periods a thread meets the same 16 scales in
+    // every sweep: fetch (and, for Requantize, divide) them once
+    if (hoist) {
+        const int64_t i00 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) << 4;
+        load_scales16<SM>(scale_a, sel, i00, 16, s);
+        if (MODE == 0) {
+            float sb[16];
+            load_scales16<SM>(scale_b, sel, i00, 16, sb);
+#pragma unroll
+            for (int k = 0; k < 16; k++) s[k] = __fdiv_rn(s[k], sb[k]);
+        }
+    }
     for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * blockDim.x) {
         const int64_t i0 = c << 4;
         const int cnt = (n - i0 >= 16) ? 16 : (int)(n - i0);
         int xi[16];
-        float s[16];
         if (VEC && cnt == 16) {
             const int4 *p = reinterpret_cast<const int4 *>(x + i0);
 #pragma unroll
@@ -193,12 +242,14 @@ requantize_kernel(const int32_t *__restrict__ x, int64_t n, const float *__restr
 #pragma unroll
             for (int k = 0; k < 16; k++) xi[k] = (k < cnt) ? x[i0 + k] : 0;
         }
-        load_scales16<SM>(scale_a, sel, i0, cnt, s);
-        if (MODE == 0) {
-            float sb[16];
-            load_scales16<SM>(scale_b, sel, i0, cnt, sb);
+        if (!hoist) {
+            load_scales16<SM>(scale_a, sel, i0, cnt, s);
+            if (MODE == 0) {
+                float sb[16];
+                load_scales16<SM>(scale_b, sel, i0, cnt, sb);
 #pragma unroll
-            for (int k = 0; k < 16; k++) s[k] = __fdiv_rn(s[k], sb[k]);
+                for (int k = 0; k < 16; k++) s[k] = __fdiv_rn(s[k], sb[k]);
+            }
         }
         uint32_t q[16];
         float pz[16];
@@ -234,11 +285,32 @@ static int pick_scale_mode(int64_t scale_len, int64_t inner, const void *sa, con
     return kScaleGeneral;
 }
 
-static unsigned grid_for(int64_t n, int sm_count)
+static unsigned grid_for_groups(int64_t groups, int sm_count)
+{
+    const int64_t per_block = (int64_t)(kThreadsPerBlock / 32) * 128;  // groups one block covers per sweep
+    int64_t blocks = (groups + per_block - 1) / per_block;
+    const int64_t cap = (int64_t)sm_count * 64;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (unsigned)blocks;
+}
+
+static unsigned grid_for_tail(int64_t n)
+{
+    int64_t blocks = (n + kThreadsPerBlock - 1) / kThreadsPerBlock;
+    if (blocks > 65535) blocks = 65535;
+    if (blocks < 1) blocks = 1;
+    return (unsigned)blocks;
+}
+
+// Per-axis scales: one resident wave of blocks (8 x 256 threads per SM) sweeps the tensor, so a thread
+// does several sweeps and the scales it fetched once pay off.  Per-tensor scale: many short-lived blocks
+// measured faster.
+static unsigned grid_for(int64_t n, int sm_count, bool per_axis)
 {
     const int64_t chunks = (n + 15) >> 4;
     int64_t blocks = (chunks + 255) / 256;
-    const int64_t cap = (int64_t)sm_count * 64;
+    const int64_t cap = (int64_t)sm_count * (per_axis ? 8 : 64);
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     return (unsigned)blocks;
@@ -258,17 +330,19 @@ cudaError_t launch_quantize(const float *x, int64_t n, const float *scale, int64
     const ScaleSel sel{scale_len, inner};
     const int sm = pick_scale_mode(scale_len, inner, scale, nullptr);
     const bool vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
-    const unsigned grid = grid_for(n, sm_count);
+    const unsigned grid = grid_for(n, sm_count, sm != kScalePerTensor);
     const bool fast = lo >= -4194304.0f && hi <= 4194304.0f;
+    // same scales in every sweep of the grid?  (per-tensor: trivially; last axis: stride a multiple of the period)
+    const int hoist = (sm == kScalePerTensor || (sm == kScaleLastAxis16 && ((int64_t)grid * 256 * 16) % scale_len == 0)) ? 1 : 0;
 #define CALL(SMV)                                                                                                     \
     if (mode == 0) {                                                                                                  \
-        if (vec && fast) quantize_kernel<0, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out);   \
-        else if (vec) quantize_kernel<0, SMV, true, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out);     \
-        else quantize_kernel<0, SMV, false, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out);             \
+        if (vec && fast) quantize_kernel<0, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist);   \
+        else if (vec) quantize_kernel<0, SMV, true, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist);     \
+        else quantize_kernel<0, SMV, false, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist);             \
     } else {                                                                                                          \
-        if (vec && fast) quantize_kernel<1, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out);   \
-        else if (vec) quantize_kernel<1, SMV, true, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out);     \
-        else quantize_kernel<1, SMV, false, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out);             \
+        if (vec && fast) quantize_kernel<1, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist);   \
+        else if (vec) quantize_kernel<1, SMV, true, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist);     \
+        else quantize_kernel<1, SMV, false, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist);             \
     }
     BUDA_SM_SWITCH(sm, CALL)
 #undef CALL
@@ -279,14 +353,26 @@ cudaError_t launch_dequantize(const int8_t *x, int64_t n, const float *scale, in
                               float *out, int sm_count, cudaStream_t stream)
 {
     const ScaleSel sel{scale_len, inner};
-    const int sm = pick_scale_mode(scale_len, inner, scale, nullptr);
-    const bool vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
-    const unsigned grid = grid_for(n, sm_count);
-#define CALL(SMV)                                                                                   \
-    if (vec) dequantize_kernel<SMV, true><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, out);     \
-    else dequantize_kernel<SMV, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, out);
-    BUDA_SM_SWITCH(sm, CALL)
-#undef CALL
+    int sm = kScaleGeneral;
+    if (scale_len == 1) sm = kScalePerTensor;
+    else if (inner == 1 && (scale_len % 4) == 0 && (reinterpret_cast<uintptr_t>(scale) & 15u) == 0) sm = kScaleLastAxis4;
+    else if ((inner % 4) == 0) sm = kScaleGroup;
+    // the vector kernel takes the aligned body in groups of 4; a scalar kernel finishes the tail, or does
+    // everything when a base pointer is not aligned for the vector accesses
+    const bool vec = ((reinterpret_cast<uintptr_t>(x) & 3u) | (reinterpret_cast<uintptr_t>(out) & 15u)) == 0;
+    const int64_t groups = vec ? n / 4 : 0;
+    if (groups > 0) {
+        const unsigned grid = grid_for_groups(groups, sm_count);
+        switch (sm) {
+            case kScalePerTensor: dequantize_vec_kernel<kScalePerTensor><<<grid, kThreadsPerBlock, 0, stream>>>(x, groups, scale, sel, zp, out); break;
+            case kScaleLastAxis4: dequantize_vec_kernel<kScaleLastAxis4><<<grid, kThreadsPerBlock, 0, stream>>>(x, groups, scale, sel, zp, out); break;
+            case kScaleGroup: dequantize_vec_kernel<kScaleGroup><<<grid, kThreadsPerBlock, 0, stream>>>(x, groups, scale, sel, zp, out); break;
+            default: dequantize_vec_kernel<kScaleGeneral><<<grid, kThreadsPerBlock, 0, stream>>>(x, groups, scale, sel, zp, out); break;
+        }
+    }
+    const int64_t first = groups * 4;
+    if (first < n)
+        dequantize_scalar_kernel<<<grid_for_tail(n - first), kThreadsPerBlock, 0, stream>>>(x, first, n, scale, sel, zp, out);
     return cudaGetLastError();
 }
 
@@ -297,17 +383,19 @@ cudaError_t launch_requantize(const int32_t *x, int64_t n, const float *scale_a,
     const ScaleSel sel{scale_len, inner};
     const int sm = pick_scale_mode(scale_len, inner, scale_a, mode == 0 ? scale_b : nullptr);
     const bool vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
-    const unsigned grid = grid_for(n, sm_count);
+    const unsigned grid = grid_for(n, sm_count, sm != kScalePerTensor);
     const bool fast = lo >= -4194304.0f && hi <= 4194304.0f;
+    // same scales in every sweep of the grid?  (per-tensor: trivially; last axis: stride a multiple of the period)
+    const int hoist = (sm == kScalePerTensor || (sm == kScaleLastAxis16 && ((int64_t)grid * 256 * 16) % scale_len == 0)) ? 1 : 0;
 #define CALL(SMV)                                                                                                                 \
     if (mode == 0) {                                                                                                              \
-        if (vec && fast) requantize_kernel<0, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out);  \
-        else if (vec) requantize_kernel<0, SMV, true, false><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out);    \
-        else requantize_kernel<0, SMV, false, false><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out);            \
+        if (vec && fast) requantize_kernel<0, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out, hoist);  \
+        else if (vec) requantize_kernel<0, SMV, true, false><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out, hoist);    \
+        else requantize_kernel<0, SMV, false, false><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out, hoist);            \
     } else {                                                                                                                      \
-        if (vec && fast) requantize_kernel<1, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out);  \
-        else if (vec) requantize_kernel<1, SMV, true, false><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out);    \
-        else requantize_kernel<1, SMV, false, false><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out);            \
+        if (vec && fast) requantize_kernel<1, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out, hoist);  \
+        else if (vec) requantize_kernel<1, SMV, true, false><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out, hoist);    \
+        else requantize_kernel<1, SMV, false, false><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out, hoist);            \
     }
     BUDA_SM_SWITCH(sm, CALL)
 #undef CALL
