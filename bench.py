@@ -440,9 +440,9 @@ def main():
             "config": {"workload": WORKLOAD if NT == N_TENSORS else WORKLOAD + f" (REDUCED to {NT} tensors)", "per_gpu_batch": NT, "l2": "inputs (4 GiB per step) larger than L2",
                        "launches_per_step": 1},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                         # dram read+write per launch: ncu on an 8-tensor launch measured 82.85 MB per tensor
+                         # dram read+write per launch: ncu on an 8-tensor launch measured 82.57 MB per tensor
                          # (profiles/pack_staged_kernel_bfp8b_cfg2.md); traffic grows with the tensor count
-                         "traffic": NT * 82.85e6, "traffic_unit": "bytes per launch, scaled from an 8-tensor ncu capture", "peak_kind": peak_kind, "kernel": "pack_staged_kernel<7,4>",
+                         "traffic": NT * 82.57e6, "traffic_unit": "bytes per launch, scaled from an 8-tensor ncu capture", "peak_kind": peak_kind, "kernel": "pack_staged_kernel<7,4>",
                          "kernel_ms": kernel_ms},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
             "other_kernels": extras,
