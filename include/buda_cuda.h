@@ -174,6 +174,17 @@ int buda_queue_read(const void *queue_base, int src_df, int with_header, const b
                     uint32_t first_slot, void *dst, int dst_is_host, int dst_df, const uint32_t shape[4],
                     const uint64_t strides_bytes[4], void *stream);
 
+/* Read `entries` entries and apply the output host transforms on the way: the t slices of an
+ * entry are laid side by side, hstack across (columns) and vstack down (rows), giving a dense
+ * [entries, t/(hstack*vstack), R*vstack, C*hstack] device tensor.  stack_row_major != 0: slice z sits
+ * at row (z / hstack) % vstack, column z % hstack; otherwise at column (z / vstack) % hstack, row
+ * z % vstack.  Same result as the golden hstack / vstack (pybuda/pybuda/op/eval/buda/tm.py:114-137)
+ * applied to the untilized tensor; this is what tt::backend::get_output does for descriptors whose
+ * hstack_factor / vstack_factor / stack_row_major are set (pybuda/pybuda/backend.py:294-302). */
+int buda_queue_read_stacked(const void *queue_base, int src_df, int with_header, const buda_queue_geom *geom,
+                            uint32_t slots, uint32_t first_slot, uint32_t entries, uint32_t hstack, uint32_t vstack,
+                            int stack_row_major, void *dst, int dst_df, void *stream);
+
 /* ------------------------------------------------------------------ memory and device plumbing
  * What the host layer needs so that it links against this library only and never against the
  * CUDA runtime itself.  No counterpart in the reference (its backend owns device memory). */

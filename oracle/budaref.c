@@ -241,6 +241,78 @@ void ref_bfp_unpack_block(uint8_t exp_in, const uint8_t *in, int m, float out[16
 }
 
 /* ---------------------------------------------------------------------------------------------
+ * "a" formats (Bfp8 / Bfp4 / Bfp2): the shared exponent is the 5-bit binary16 exponent "padded to 8b"
+ * (dataformats.rst:68); the source is binary16 (pybuda/pybuda/device_connector.py:188-192 casts to
+ * float16 for these queues).  Same datum rules as the "b" formats, in the binary16 domain:
+ * 11-bit significand, zero / denormal -> 0, Inf / NaN (e == 31) -> largest magnitude.
+ * decode: (-1)^s * q * 2^(E - 15 - (m-1)).   PARITY UNPINNED like the "b" encoding.
+ * ------------------------------------------------------------------------------------------- */
+static inline uint32_t bfp_a_encode_datum(uint16_t h, uint32_t block_exp, int m)
+{
+    uint32_t sign = h >> 15, e = (h >> 10) & 31u, qmax = (1u << m) - 1u, q;
+    if (e == 0) {
+        q = 0;
+    } else if (e == 31) {
+        q = qmax;
+    } else {
+        uint32_t sig = (h & 0x3ffu) | 0x400u;                 /* 11-bit significand */
+        uint32_t shift = (block_exp - e) + (uint32_t)(11 - m);
+        if (shift > 12) {
+            q = 0;
+        } else {
+            uint32_t kept = sig >> shift, rem = sig & ((1u << shift) - 1u), half = 1u << (shift - 1);
+            if (rem > half || (rem == half && (kept & 1u))) kept++;
+            q = kept > qmax ? qmax : kept;
+        }
+    }
+    if (q == 0) sign = 0;
+    return (sign << m) | q;
+}
+
+void ref_bfp_a_pack_block(const uint16_t h[16], int m, uint8_t *exp_out, uint8_t *out)
+{
+    uint32_t block_exp = 0;
+    for (int i = 0; i < 16; i++) {
+        uint32_t e = (h[i] >> 10) & 31u;
+        if (e > block_exp) block_exp = e;
+    }
+    *exp_out = (uint8_t)block_exp;
+    int w = m + 1, per_byte = 8 / w;
+    memset(out, 0, 16 / per_byte);
+    for (int i = 0; i < 16; i++) out[i / per_byte] |= (uint8_t)(bfp_a_encode_datum(h[i], block_exp, m) << (w * (i % per_byte)));
+}
+
+void ref_bfp_a_unpack_block(uint8_t exp_in, const uint8_t *in, int m, float out[16])
+{
+    int w = m + 1, per_byte = 8 / w;
+    for (int i = 0; i < 16; i++) {
+        uint32_t d = (in[i / per_byte] >> (w * (i % per_byte))) & ((1u << w) - 1u);
+        uint32_t q = d & ((1u << m) - 1u), sign = (d >> m) & 1u;
+        float f = q ? (float)ldexp((double)q, (int)(exp_in & 31u) - 15 - (m - 1)) : 0.0f;
+        out[i] = (sign && q) ? -f : f;
+    }
+}
+
+/* binary32 -> binary16, round to nearest even, overflow to infinity */
+static inline uint16_t float_to_half_bits(float f)
+{
+    uint32_t b; memcpy(&b, &f, 4);
+    uint32_t sign = (b >> 16) & 0x8000u, a = b & 0x7fffffffu;
+    if (a >= 0x7f800000u) return (uint16_t)(sign | 0x7c00u | ((a > 0x7f800000u) ? 0x200u : 0u));
+    if (a >= 0x477ff000u) return (uint16_t)(sign | 0x7c00u);            /* rounds to >= 65520: infinity */
+    if (a < 0x33000001u) return (uint16_t)sign;                         /* below half the smallest denormal */
+    int e = (int)(a >> 23) - 127;
+    uint32_t sig = (a & 0x7fffffu) | 0x800000u;
+    int shift = (e < -14) ? (13 + (-14 - e)) : 13;                      /* bits dropped from the 24-bit significand */
+    uint32_t kept = sig >> shift, rem = sig & ((1u << shift) - 1u), half = 1u << (shift - 1);
+    if (rem > half || (rem == half && (kept & 1u))) kept++;
+    uint32_t h = (e < -14) ? kept : (((uint32_t)(e + 15) << 10) + (kept - 0x400u));
+    return (uint16_t)(sign | h);
+}
+
+static int is_bfp_a(int df) { return df == DF_Bfp8 || df == DF_Bfp4 || df == DF_Bfp2; }
+
+/* ---------------------------------------------------------------------------------------------
  * Element access helpers
  * ------------------------------------------------------------------------------------------- */
 static inline uint32_t load_as_f32_bits(const uint8_t *p, int df)
@@ -321,7 +393,9 @@ int ref_tilize_pack(const void *src_, int src_df, const uint32_t shape[4], const
     if (make_ctx(&c, g, shape, dst_df, with_header)) return 1;
     int m = bfp_mant_bits(dst_df);
     int es = elem_bytes(src_df);
-    if (m) {
+    if (m && is_bfp_a(dst_df)) {
+        if (src_df != DF_Float16) return 1;
+    } else if (m) {
         if (!(dst_df == DF_Bfp8_b || dst_df == DF_Bfp4_b || dst_df == DF_Bfp2_b)) return 1;
         if (!(src_df == DF_Float32 || src_df == DF_Float16_b)) return 1;
     } else {
@@ -346,7 +420,12 @@ int ref_tilize_pack(const void *src_, int src_df, const uint32_t shape[4], const
                 uint64_t col0 = (uint64_t)ct * 32 + (face & 1) * 16;
                 const uint8_t *p = base + r * strides[2] + col0 * strides[3];
                 int blk = face * 16 + fr;
-                if (m) {
+                if (m && is_bfp_a(dst_df)) {
+                    uint16_t hv[16];
+                    for (int i = 0; i < 16; i++) memcpy(&hv[i], p + (uint64_t)i * strides[3], 2);
+                    int bpb = 16 * (m + 1) / 8;
+                    ref_bfp_a_pack_block(hv, m, rec + blk, rec + 64 + (long)blk * bpb);
+                } else if (m) {
                     uint32_t bits[16];
                     for (int i = 0; i < 16; i++) bits[i] = load_as_f32_bits(p + (uint64_t)i * strides[3], src_df);
                     int bpb = 16 * (m + 1) / 8;
@@ -372,7 +451,9 @@ int ref_unpack_untilize(const void *src_, int src_df, int with_header, const ref
     if (make_ctx(&c, g, shape, src_df, with_header)) return 1;
     int m = bfp_mant_bits(src_df);
     int es = elem_bytes(dst_df);
-    if (m) {
+    if (m && is_bfp_a(src_df)) {
+        if (!(dst_df == DF_Float32 || dst_df == DF_Float16)) return 1;
+    } else if (m) {
         if (!(src_df == DF_Bfp8_b || src_df == DF_Bfp4_b || src_df == DF_Bfp2_b)) return 1;
         if (!(dst_df == DF_Float32 || dst_df == DF_Float16_b)) return 1;
     } else {
@@ -395,7 +476,19 @@ int ref_unpack_untilize(const void *src_, int src_df, int with_header, const ref
                 uint64_t col0 = (uint64_t)ct * 32 + (face & 1) * 16;
                 uint8_t *p = base + r * strides[2] + col0 * strides[3];
                 int blk = face * 16 + fr;
-                if (m) {
+                if (m && is_bfp_a(src_df)) {
+                    float vals[16];
+                    int bpb = 16 * (m + 1) / 8;
+                    ref_bfp_a_unpack_block(rec[blk], rec + 64 + (long)blk * bpb, m, vals);
+                    for (int i = 0; i < 16; i++) {
+                        if (dst_df == DF_Float32) {
+                            memcpy(p + (uint64_t)i * strides[3], &vals[i], 4);
+                        } else {
+                            uint16_t hb = float_to_half_bits(vals[i]);
+                            memcpy(p + (uint64_t)i * strides[3], &hb, 2);
+                        }
+                    }
+                } else if (m) {
                     float vals[16];
                     int bpb = 16 * (m + 1) / 8;
                     ref_bfp_unpack_block(rec[blk], rec + 64 + (long)blk * bpb, m, vals);

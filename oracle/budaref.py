@@ -84,6 +84,10 @@ def lib():
         L.ref_bfp_pack_block.argtypes = [vp, i32, vp, vp]
         L.ref_bfp_unpack_block.restype = None
         L.ref_bfp_unpack_block.argtypes = [ctypes.c_uint8, vp, i32, vp]
+        L.ref_bfp_a_pack_block.restype = None
+        L.ref_bfp_a_pack_block.argtypes = [vp, i32, vp, vp]
+        L.ref_bfp_a_unpack_block.restype = None
+        L.ref_bfp_a_unpack_block.argtypes = [ctypes.c_uint8, vp, i32, vp]
         L.ref_quantize.restype = None
         L.ref_quantize.argtypes = [vp, i64, vp, i64, i64, ctypes.c_float, i32, ctypes.c_float, ctypes.c_float, vp]
         L.ref_dequantize.restype = None
@@ -186,6 +190,23 @@ def bfp_unpack_block(exp, data, mant_bits):
     data = np.ascontiguousarray(data, dtype=np.uint8)
     out = np.zeros(16, dtype=np.float32)
     lib().ref_bfp_unpack_block(int(exp), data.ctypes.data, mant_bits, out.ctypes.data)
+    return out
+
+
+def bfp_a_pack_block(half_bits16, mant_bits):
+    """One block of an "a" format (5-bit shared exponent) from 16 binary16 bit patterns."""
+    h = np.ascontiguousarray(half_bits16, dtype=np.uint16)
+    assert h.size == 16
+    exp = np.zeros(1, dtype=np.uint8)
+    out = np.zeros(16 * (mant_bits + 1) // 8, dtype=np.uint8)
+    lib().ref_bfp_a_pack_block(h.ctypes.data, mant_bits, exp.ctypes.data, out.ctypes.data)
+    return int(exp[0]), out
+
+
+def bfp_a_unpack_block(exp, data, mant_bits):
+    data = np.ascontiguousarray(data, dtype=np.uint8)
+    out = np.zeros(16, dtype=np.float32)
+    lib().ref_bfp_a_unpack_block(int(exp), data.ctypes.data, mant_bits, out.ctypes.data)
     return out
 
 

@@ -196,3 +196,41 @@ def test_binarize_pytorch_desc(api, tmp_path):
     B.free_tensor(d)
     d.shape = [2, 1, 32, 32]
     assert B.debinarize_tensor(d, path) == B.BackendStatusCode.RuntimeError
+
+
+def _golden_stack(x, h, v, row_major):
+    """hstack / vstack of the t slices as the reference's golden TMs define them
+    (pybuda/pybuda/op/eval/buda/tm.py:114-137), in the order the output host TM applies them."""
+    def hstack(t, f):
+        w, z, r, c = t.shape
+        return t.reshape(w, z // f, f, r, c).permute(0, 1, 3, 2, 4).reshape(w, z // f, r, c * f)
+
+    def vstack(t, f):
+        w, z, r, c = t.shape
+        return t.reshape(w, z // f, r * f, c)
+
+    return vstack(hstack(x, h), v) if row_major else hstack(vstack(x, v), h)
+
+
+@pytest.mark.parametrize("h,v,row_major,t", [(4, 1, True, 4), (1, 3, True, 6), (2, 2, True, 4), (2, 3, False, 12), (3, 2, True, 12)])
+def test_output_host_transforms(api, oracle, h, v, row_major, t):
+    C, B, DF, T = api
+    shape = [2, t, 64, 96]
+    x = torch.randn(shape, generator=torch.Generator().manual_seed(33))
+    for df_name in ("Float32", "Bfp8_b"):
+        q = B.DramIODesc.for_tensor(f"tm_{df_name}_{h}{v}{int(row_major)}{t}", shape, getattr(DF, df_name), ublock=(2, 1))
+        _ok(B, B.push_input(q, T.pytorch_tensor_to_tensor_desc(x), False, 1, -1))
+        q.hstack_factor, q.vstack_factor, q.stack_row_major = h, v, row_major
+        out = B.PytorchTensorDesc()
+        out.format = DF.Float32
+        _ok(B, B.get_output(q, out, False, 1, -1))
+        y = T.tensor_desc_to_pytorch_tensor(out).clone()
+        B.free_tensor(out)
+        _ok(B, B.pop_output(q, False, 1))
+        assert list(y.shape) == [2, t // (h * v), 64 * v, 96 * h]
+        if df_name == "Float32":
+            want = x
+        else:
+            go = oracle.Geom.for_shape(shape, (1, 1), (2, 1), 0)
+            want = torch.from_numpy(oracle.unpack_untilize(oracle.tilize_pack(x.numpy(), oracle.Bfp8_b, go), oracle.Bfp8_b, shape, geom=go))
+        assert torch.equal(y, _golden_stack(want, h, v, row_major)), df_name

@@ -339,3 +339,32 @@ def test_config5_bert_large_weight_set_round_trip(ops, oracle):
                 yref = oracle.unpack_untilize(ref, oracle.Bfp8_b, (1, 1, *w.shape))[0, 0]
                 assert np.array_equal(_bits(y.cpu().numpy()), _bits(yref))
     assert total == 301989888
+
+
+@pytest.mark.parametrize("df", ["Bfp8", "Bfp4", "Bfp2"])
+@pytest.mark.parametrize("path", [0, 1])
+def test_a_formats_five_bit_exponent(ops, oracle, df, path):
+    # Bfp8 / Bfp4 / Bfp2: shared exponent = the 5-bit binary16 exponent; source and result binary16
+    shape = (2, 1, 64, 160)
+    x = _special_values(shape, seed=91).clamp(-6e4, 6e4)
+    x.view(-1, 16)[3] = torch.tensor([float("inf"), float("-inf"), float("nan"), 65504.0, -1.0, 1.0, 0.0, -0.0] * 2)
+    x.view(-1, 16)[5] = torch.randn(16) * 1e-6                  # binary16 denormals only
+    x.view(-1, 16)[6] = torch.tensor([6.1e-5, 3e-5, 1e-7, -6.2e-5] * 4)   # around the smallest normal
+    xh = x.half()
+    odf, gdf = getattr(oracle, df), getattr(ops.DF, df)
+    ref = oracle.tilize_pack(xh.numpy(), odf)
+    img = ops.tilize_pack(xh.cuda(), gdf, path=path)
+    got = img.cpu().numpy()
+    if not np.array_equal(got, ref):
+        bad = np.nonzero(got != ref)[0]
+        pytest.fail(f"{bad.size} bytes differ, first at {bad[:8]}: got {got[bad[:8]]} want {ref[bad[:8]]}")
+    y16 = ops.unpack_untilize(img, gdf, shape, dtype=torch.float16, path=path)
+    assert np.array_equal(y16.cpu().view(torch.int16).numpy(), oracle.unpack_untilize(ref, odf, shape, dst_dtype=np.float16).view(np.int16))
+    y32 = ops.unpack_untilize(img, gdf, shape, dtype=torch.float32, path=path)
+    assert np.array_equal(_bits(y32.cpu().numpy()), _bits(oracle.unpack_untilize(ref, odf, shape)))
+    # arbitrary bytes decode the same way too (exponent bytes above 31 use their low 5 bits)
+    rnd = np.random.default_rng(9).integers(0, 256, ref.size, dtype=np.uint8)
+    z = ops.unpack_untilize(torch.from_numpy(rnd).cuda(), gdf, shape, dtype=torch.float32, path=path)
+    assert np.array_equal(_bits(z.cpu().numpy()), _bits(oracle.unpack_untilize(rnd, odf, shape)))
+    with pytest.raises(ops._cabi.BudaError):
+        ops.tilize_pack(x.cuda(), gdf)                          # these queues pack from binary16 only

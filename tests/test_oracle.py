@@ -261,3 +261,58 @@ def test_config1_size(oracle):
     g = R.Geom.for_shape([1, 1, 1024, 1024])
     n = R.lib().ref_tilized_bytes(g, (np.ctypeslib.ctypes.c_uint32 * 4)(1, 1, 1024, 1024), R.Bfp8_b, 0)
     assert n == 1114112
+
+
+@pytest.mark.parametrize("m", [7, 3, 1])
+def test_bfp_a_oracle_matches_rational_spec(oracle, m):
+    """The "a" formats: 5-bit shared exponent of binary16 sources, same datum rules."""
+    from fractions import Fraction
+
+    rng = np.random.default_rng(200 + m)
+    for trial in range(200):
+        if trial % 3 == 0:
+            h = rng.standard_normal(16).astype(np.float16).view(np.uint16)
+        elif trial % 3 == 1:
+            h = rng.integers(0, 2 ** 16, 16, dtype=np.uint32).astype(np.uint16)   # raw patterns: denormals, Inf, NaN
+        else:
+            h = (rng.integers(-9, 10, 16) * 0.5).astype(np.float16)
+            h[0] = np.float16(64.0)
+            h = h.view(np.uint16)
+        E, d = oracle.bfp_a_pack_block(h, m)
+        exps = [(int(x) >> 10) & 31 for x in h]
+        assert E == max(exps)
+        qmax, w = (1 << m) - 1, m + 1
+        word = int.from_bytes(d.tobytes(), "little")
+        for i, (x, e) in enumerate(zip(h, exps)):
+            x = int(x)
+            if e == 0:
+                q = 0
+            elif e == 31:
+                q = qmax
+            else:
+                v = Fraction((x & 0x3FF) | 0x400, 1 << 10) * Fraction(2) ** (e - 15) * Fraction(2) ** (m - 1) / Fraction(2) ** (E - 15)
+                fl = math.floor(v)
+                rem = v - fl
+                if rem > Fraction(1, 2) or (rem == Fraction(1, 2) and fl % 2 == 1):
+                    fl += 1
+                q = min(fl, qmax)
+            want = (((x >> 15) << m) | q) if q else 0
+            assert (word >> (w * i)) & ((1 << w) - 1) == want, (trial, i)
+        y = oracle.bfp_a_unpack_block(E, d, m)
+        for i in range(16):
+            dat = (word >> (w * i)) & ((1 << w) - 1)
+            q, s = dat & qmax, dat >> m
+            val = math.ldexp(q, E - 15 - (m - 1)) * (-1 if s and q else 1)
+            assert float(y[i]) == val
+
+
+def test_bfp_a_tilize_round_trip(oracle):
+    R = oracle
+    x = (np.random.default_rng(3).standard_normal((2, 1, 64, 96)) * 5).astype(np.float16)
+    for df in (R.Bfp8, R.Bfp4, R.Bfp2):
+        img = R.tilize_pack(x, df)
+        assert img.size == 2 * 2 * 3 * R.tile_bytes(df)
+        y16 = R.unpack_untilize(img, df, x.shape, dst_dtype=np.float16)
+        y32 = R.unpack_untilize(img, df, x.shape)
+        assert np.array_equal(y16.astype(np.float32), y32)          # decoded values are exact in binary16
+        assert np.array_equal(R.tilize_pack(y16, df), img)           # idempotent

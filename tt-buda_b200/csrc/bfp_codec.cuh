@@ -128,6 +128,28 @@ __device__ __forceinline__ void bfp_encode16(const uint32_t (&x)[16], uint32_t &
     }
 }
 
+// "a" formats (Bfp8 / Bfp4 / Bfp2): same datums, but the shared exponent is the 5-bit exponent of
+// binary16 (bias 15), stored in a byte.  The source is binary16; it is widened to binary32 bit patterns
+// so the encoder above can be reused: binary16 zeros / denormals become 0 (flush); Inf / NaN become the
+// largest binary32 below 2^17, i.e. exponent field 31 + 112 with a full mantissa, so they round up past
+// the largest magnitude and saturate to it while finite neighbours keep their distance 31 - e from the
+// block exponent; everything else converts exactly.
+__device__ __forceinline__ uint32_t half_bits_to_float_bits(uint32_t h)
+{
+    const uint32_t hm = h & 0x7fffu;
+    uint32_t a = (hm << 13) + 0x38000000u;   // re-bias the exponent by 127 - 15
+    a = hm < 0x0400u ? 0u : a;
+    a = hm >= 0x7c00u ? 0x47ffffffu : a;
+    return a | ((h & 0x8000u) << 16);
+}
+
+// binary32 block exponent of widened binary16 data -> the 5-bit exponent byte
+__device__ __forceinline__ uint32_t a_exponent_byte(uint32_t e32) { return e32 > 112u ? e32 - 112u : 0u; }
+
+// scale 2^(E5 - 15 - (M-1)) of an "a" block: always a normal binary32
+template <int M>
+__device__ __forceinline__ float bfp_a_block_scale(uint32_t e5) { return __uint_as_float((e5 + 127u - 15u - (uint32_t)(M - 1)) << 23); }
+
 // Scale of a block: 2^(E - 127 - (M-1)) as a binary32 (denormal when needed).  For M == 1 and
 // E == 255 the scale 2^128 is not representable: the caller multiplies by `post` (2.0) as well.
 template <int M>
@@ -144,11 +166,11 @@ __device__ __forceinline__ float bfp_block_scale(uint32_t E, float &post)
 }
 
 // Decode one block to 16 binary32 values (exact; overflow gives infinity).
-template <int M>
+template <int M, bool AF = false>
 __device__ __forceinline__ void bfp_decode16(uint32_t E, const uint32_t (&in)[BfpTraits<M>::words], float (&v)[16])
 {
-    float post;
-    const float sc = bfp_block_scale<M>(E, post);
+    float post = 1.0f;
+    const float sc = AF ? bfp_a_block_scale<M>(E & 31u) : bfp_block_scale<M>(E, post);
 #pragma unroll
     for (int i = 0; i < 16; i++) {
         uint32_t q, signbit;
@@ -166,7 +188,7 @@ __device__ __forceinline__ void bfp_decode16(uint32_t E, const uint32_t (&in)[Bf
             signbit = (d << (31 - M)) & 0x80000000u;
         }
         float mag = __fmul_rn(__fadd_rn(__uint_as_float(q), -12582912.0f), sc);
-        if (M == 1) mag = __fmul_rn(mag, post);
+        if (M == 1 && !AF) mag = __fmul_rn(mag, post);
         // (+-0) + (+0) = +0: a zero magnitude decodes to +0.0 whatever its sign bit says
         v[i] = __fadd_rn(__uint_as_float(__float_as_uint(mag) | signbit), 0.0f);
     }

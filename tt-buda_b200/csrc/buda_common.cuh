@@ -59,7 +59,19 @@ struct TileJob {
     uint64_t buf_bytes;                 // bytes of one grid core's buffer (all W entries)
     int trivial_geom;                   // grid 1x1, ublock 1x1, order R: address = (z*Rt + rt)*Ct + ct
     uint32_t slots, slot0;              // ring queue: entry w lives in slot (slot0 + w) % slots; slots == 0: dense image
+    // Row-major side, optional split of z into (outer, middle, inner) with their own strides: how the
+    // hstack / vstack host transforms place the t slices of a queue entry.  zn1 == 0: plain z * stride_z.
+    uint32_t zn1, zn2;
+    uint64_t stride_z_mid, stride_z_out;
 };
+
+// byte offset of slice z on the row-major side
+__host__ __device__ inline uint64_t rm_z_offset(const TileJob &j, uint32_t z)
+{
+    if (j.zn1 == 0) return (uint64_t)z * j.stride_z;
+    return (uint64_t)(z % j.zn1) * j.stride_z + (uint64_t)((z / j.zn1) % j.zn2) * j.stride_z_mid +
+           (uint64_t)(z / (j.zn1 * j.zn2)) * j.stride_z_out;
+}
 
 struct PtrTable {
     const uint8_t *src[kMaxBatch];

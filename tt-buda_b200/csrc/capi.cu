@@ -10,9 +10,9 @@
 #include "buda_common.cuh"
 
 namespace buda {
-cudaError_t launch_tilize(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int path,
+cudaError_t launch_tilize(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int a_format, int path,
                           int vec_ok, int sm_count, cudaStream_t stream, unsigned int *status);
-cudaError_t launch_untilize(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int path,
+cudaError_t launch_untilize(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int a_format, int path,
                             int vec_ok, int sm_count, cudaStream_t stream, unsigned int *status);
 cudaError_t launch_quantize(const float *x, int64_t n, const float *scale, int64_t scale_len, int64_t inner, float zp,
                             int mode, float lo, float hi, int8_t *out, int sm_count, cudaStream_t stream);
@@ -88,6 +88,7 @@ int get_ctx(DevCtx **out)
 }
 
 bool is_bfp_b(int df) { return df == BUDA_DF_Bfp8_b || df == BUDA_DF_Bfp4_b || df == BUDA_DF_Bfp2_b; }
+bool is_bfp_a(int df) { return df == BUDA_DF_Bfp8 || df == BUDA_DF_Bfp4 || df == BUDA_DF_Bfp2; }
 
 // Fills the job for a [w,z,R,C] tensor in a queue of geometry g holding format qdf.
 int make_job(const uint32_t shape[4], const uint64_t strides[4], const buda_queue_geom *g, int qdf, int with_header,
@@ -127,6 +128,8 @@ int make_job(const uint32_t shape[4], const uint64_t strides[4], const buda_queu
         return fail(BUDA_RUNTIME_ERROR, "ring of %u slots cannot take %u entries at slot %u", slots, j.W, slot0);
     j.slots = slots;
     j.slot0 = slot0;
+    j.zn1 = j.zn2 = 0;
+    j.stride_z_mid = j.stride_z_out = 0;
     j.buf_bytes = (uint64_t)(slots ? slots : j.W) * j.tiles_per_entry * j.tile_bytes;
     j.trivial_geom = (g->grid_r == 1 && g->grid_c == 1 && g->ublock_rt == 1 && g->ublock_ct == 1 && g->ublock_order == 0);
     return BUDA_SUCCESS;
@@ -134,7 +137,7 @@ int make_job(const uint32_t shape[4], const uint64_t strides[4], const buda_queu
 
 // Which conversion a (row-major format, queue format) pair asks for.  mant = 7/3/1 for a Bfp
 // pack/unpack, 0 for a plain relayout; es = element bytes on the row-major side.
-int classify(int rm_df, int q_df, int &mant, int &es)
+int classify(int rm_df, int q_df, int &mant, int &es, bool unpacking = false)
 {
     if (is_bfp_b(q_df)) {
         if (rm_df != BUDA_DF_Float32 && rm_df != BUDA_DF_Float16_b)
@@ -143,8 +146,16 @@ int classify(int rm_df, int q_df, int &mant, int &es)
         es = rm_df == BUDA_DF_Float32 ? 4 : 2;
         return BUDA_SUCCESS;
     }
-    if (bfp_mant_bits(q_df))
-        return fail(BUDA_RUNTIME_ERROR, "Bfp 'a' formats (5-bit shared exponent) are not implemented");
+    if (is_bfp_a(q_df)) {
+        // 5-bit shared exponent: packs from Float16 (the torch dtype these formats travel as); unpacks to
+        // Float16 or Float32
+        if (rm_df != BUDA_DF_Float16 && !(unpacking && rm_df == BUDA_DF_Float32))
+            return fail(BUDA_RUNTIME_ERROR, "Bfp8 / Bfp4 / Bfp2 queues pack from Float16 and unpack to Float16 or Float32, not format %d",
+                        rm_df);
+        mant = bfp_mant_bits(q_df);
+        es = rm_df == BUDA_DF_Float32 ? 4 : 2;
+        return BUDA_SUCCESS;
+    }
     es = plain_elem_bytes(q_df);
     if (es == 0) return fail(BUDA_RUNTIME_ERROR, "unsupported queue data format %d", q_df);
     if (plain_elem_bytes(rm_df) != es)
@@ -208,7 +219,7 @@ int tilize_device(int n, const void *const *srcs, int src_df, const uint32_t sha
             if (force_path == 0 && path != 0) return fail(BUDA_RUNTIME_ERROR, "staged path needs 16-byte aligned rows");
             path = force_path;
         }
-        cudaError_t e = launch_tilize(job, pt, nb, mant, es, path, vec_ok, ctx->sm_count, stream, ctx->status);
+        cudaError_t e = launch_tilize(job, pt, nb, mant, es, is_bfp_a(dst_df) ? 1 : 0, path, vec_ok, ctx->sm_count, stream, ctx->status);
         if (e != cudaSuccess) return cuda_fail(e, "tilize launch failed");
         g_launches.fetch_add(1, std::memory_order_relaxed);
     }
@@ -224,7 +235,7 @@ int untilize_device(int n, const void *const *srcs, int src_df, int with_header,
     if (n <= 0) return BUDA_SUCCESS;
     if (!srcs || !dsts) return fail(BUDA_RUNTIME_ERROR, "null pointer table");
     int mant, es;
-    if (int rc = classify(dst_df, src_df, mant, es)) return rc;
+    if (int rc = classify(dst_df, src_df, mant, es, true)) return rc;
     if (strides && strides[3] != (uint64_t)es)
         return fail(BUDA_RUNTIME_ERROR, "innermost stride must equal the element size (%d), got %llu", es,
                     (unsigned long long)strides[3]);
@@ -246,7 +257,7 @@ int untilize_device(int n, const void *const *srcs, int src_df, int with_header,
             if (force_path == 0 && path != 0) return fail(BUDA_RUNTIME_ERROR, "staged path needs 16-byte aligned rows");
             path = force_path;
         }
-        cudaError_t e = launch_untilize(job, pt, nb, mant, es, path, vec_ok, ctx->sm_count, stream, ctx->status);
+        cudaError_t e = launch_untilize(job, pt, nb, mant, es, is_bfp_a(src_df) ? 1 : 0, path, vec_ok, ctx->sm_count, stream, ctx->status);
         if (e != cudaSuccess) return cuda_fail(e, "untilize launch failed");
         g_launches.fetch_add(1, std::memory_order_relaxed);
     }
@@ -341,7 +352,7 @@ int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_
     uint8_t *rm_host = (uint8_t *)rm_host_c;
     uint8_t *q_mem = (uint8_t *)q_c;
     int mant, es;
-    if (int rc = classify(rm_df, q_df, mant, es)) return rc;
+    if (int rc = classify(rm_df, q_df, mant, es, direction == 1)) return rc;
     TileJob full;
     if (int rc = make_job(shape, strides, geom, q_df, with_header, 1, full, slots, slot0)) return rc;
     if (strides[3] != (uint64_t)es) return fail(BUDA_RUNTIME_ERROR, "innermost stride must equal the element size");
@@ -665,6 +676,48 @@ int buda_queue_read(const void *queue_base, int src_df, int with_header, const b
     void *dsts[1] = {dst};
     return untilize_device(1, srcs, src_df, with_header, geom, dsts, dst_df, shape, strides_bytes, (cudaStream_t)stream, -1,
                            slots, first_slot);
+}
+
+int buda_queue_read_stacked(const void *queue_base, int src_df, int with_header, const buda_queue_geom *geom, uint32_t slots,
+                            uint32_t first_slot, uint32_t entries, uint32_t hstack, uint32_t vstack, int stack_row_major, void *dst,
+                            int dst_df, void *stream)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    if (!queue_base || !dst || !geom) return fail(BUDA_RUNTIME_ERROR, "null argument");
+    if (slots == 0 || entries == 0) return fail(BUDA_RUNTIME_ERROR, "a queue has at least one slot and a read at least one entry");
+    if (hstack == 0 || vstack == 0 || geom->t % (hstack * vstack))
+        return fail(BUDA_RUNTIME_ERROR, "t = %u is not a multiple of hstack %u x vstack %u", geom->t, hstack, vstack);
+    int mant, es;
+    if (int rc = classify(dst_df, src_df, mant, es, true)) return rc;
+    const uint32_t R = geom->grid_r * geom->mblock_m * geom->ublock_rt * 32u, C = geom->grid_c * geom->mblock_n * geom->ublock_ct * 32u;
+    const uint64_t out_row = (uint64_t)C * hstack * es;                 // bytes of one row of the stacked result
+    const uint64_t out_plane = (uint64_t)R * vstack * out_row;          // one [R*v, C*h] slice
+    const uint32_t shape[4] = {entries, geom->t, R, C};
+    const uint64_t strides[4] = {(uint64_t)(geom->t / (hstack * vstack)) * out_plane, 0, out_row, (uint64_t)es};
+    TileJob job;
+    if (int rc = make_job(shape, strides, geom, src_df, with_header, 1, job, slots, first_slot)) return rc;
+    // slice z of an entry sits at grid position (vv, hh) of output slice zo
+    if (stack_row_major) {  // z = (zo * v + vv) * h + hh
+        job.zn1 = hstack; job.stride_z = (uint64_t)C * es;
+        job.zn2 = vstack; job.stride_z_mid = (uint64_t)R * out_row;
+    } else {                // z = (zo * h + hh) * v + vv
+        job.zn1 = vstack; job.stride_z = (uint64_t)R * out_row;
+        job.zn2 = hstack; job.stride_z_mid = (uint64_t)C * es;
+    }
+    job.stride_z_out = out_plane;
+    if (!aligned16((uint64_t)queue_base)) return fail(BUDA_RUNTIME_ERROR, "queue image pointers must be 16-byte aligned");
+    PtrTable pt;
+    memset(&pt, 0, sizeof(pt));
+    pt.src[0] = (const uint8_t *)queue_base;
+    pt.dst[0] = (uint8_t *)dst;
+    int path, vec_ok;
+    pick_path(job, pt, 1, es, path, vec_ok);
+    if (((job.stride_z | job.stride_z_mid | job.stride_z_out) & 15u) != 0) path = 1, vec_ok = 0;
+    cudaError_t e = launch_untilize(job, pt, 1, mant, es, is_bfp_a(src_df) ? 1 : 0, path, vec_ok, ctx->sm_count, (cudaStream_t)stream, ctx->status);
+    if (e != cudaSuccess) return cuda_fail(e, "untilize launch failed");
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return BUDA_SUCCESS;
 }
 
 int buda_malloc(void **ptr, uint64_t bytes)

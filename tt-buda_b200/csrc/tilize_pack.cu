@@ -66,7 +66,7 @@ __device__ __forceinline__ void decode_item(const TileJob &job, uint32_t item, I
     m.ntiles = min((uint32_t)kBoxTiles, job.Ct - m.ct0);
 }
 
-template <int M, int ES>
+template <int M, int ES, bool AF>
 __global__ void __launch_bounds__(kStagedThreads)
 pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ PtrTable ptrs, unsigned int *status)
 {
@@ -115,7 +115,7 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
                 mbar_arrive_expect_tx(&full[s], 32u * row_copy);
             }
             __syncwarp();
-            const uint8_t *src = ptrs.src[m.b] + (uint64_t)m.w * job.stride_w + (uint64_t)m.z * job.stride_z +
+            const uint8_t *src = ptrs.src[m.b] + (uint64_t)m.w * job.stride_w + rm_z_offset(job, m.z) +
                                  ((uint64_t)m.rt * 32u + lane) * job.stride_r + (uint64_t)m.ct0 * 32u * ES;
             bulk_g2s(in_stage + s * Cfg::in_stage_bytes + lane * Cfg::pitch, src, row_copy, &full[s]);
         }
@@ -164,9 +164,14 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
                         uint4 v = *reinterpret_cast<const uint4 *>(p + 16 * j);
                         const uint32_t h[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-                        for (int k = 0; k < 4; k++) {  // bfloat16 widens exactly: it is the upper half
-                            x[8 * j + 2 * k] = h[k] << 16;
-                            x[8 * j + 2 * k + 1] = h[k] & 0xffff0000u;
+                        for (int k = 0; k < 4; k++) {
+                            if (AF) {  // binary16 source of the "a" formats
+                                x[8 * j + 2 * k] = half_bits_to_float_bits(h[k] & 0xffffu);
+                                x[8 * j + 2 * k + 1] = half_bits_to_float_bits(h[k] >> 16);
+                            } else {   // bfloat16 widens exactly: it is the upper half
+                                x[8 * j + 2 * k] = h[k] << 16;
+                                x[8 * j + 2 * k + 1] = h[k] & 0xffff0000u;
+                            }
                         }
                     }
                 }
@@ -175,7 +180,7 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
                 bfp_encode16<MM>(x, E, d);
                 uint8_t *r = ob + tile_in_box * rec + hdr;
                 const int blk = face * 16 + fr;
-                r[blk] = (uint8_t)E;
+                r[blk] = (uint8_t)(AF ? a_exponent_byte(E) : E);
                 uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
                 if (MM == 7) *reinterpret_cast<uint4 *>(q) = make_uint4(d[0], d[1 % BfpTraits<MM>::words], d[2 % BfpTraits<MM>::words], d[3 % BfpTraits<MM>::words]);
                 else if (MM == 3) *reinterpret_cast<uint2 *>(q) = make_uint2(d[0], d[1 % BfpTraits<MM>::words]);
@@ -269,7 +274,7 @@ __device__ __forceinline__ void load4(const uint8_t *p, bool vec, uint32_t (&x)[
     }
 }
 
-template <int M, int ES>
+template <int M, int ES, bool AF>
 __global__ void __launch_bounds__(256)
 pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ PtrTable ptrs, int batch, int vec_ok)
 {
@@ -291,7 +296,7 @@ pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
         const uint32_t fr = half * 8u + (lane >> 2);
         const uint64_t row = (uint64_t)rt * 32u + (face >> 1) * 16u + fr;
         const uint64_t col = (uint64_t)ct * 32u + (face & 1u) * 16u + (lane & 3) * 4u;
-        const uint8_t *p = ptrs.src[b] + (uint64_t)w * job.stride_w + (uint64_t)z * job.stride_z + row * job.stride_r +
+        const uint8_t *p = ptrs.src[b] + (uint64_t)w * job.stride_w + rm_z_offset(job, z) + row * job.stride_r +
                            col * ES;
         uint8_t *r = ptrs.dst[b] + tile_record_offset(job, w, z, rt, ct);
         if (hdr && hf == 0 && lane < 8) reinterpret_cast<uint32_t *>(r)[lane] = 0;
@@ -303,14 +308,14 @@ pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
             constexpr int MM = M > 0 ? M : 7;
             if (ES == 2) {
 #pragma unroll
-                for (int i = 0; i < 4; i++) x[i] <<= 16;
+                for (int i = 0; i < 4; i++) x[i] = AF ? half_bits_to_float_bits(x[i]) : (x[i] << 16);
             }
             uint32_t mx = max(max(x[0] & 0x7fffffffu, x[1] & 0x7fffffffu), max(x[2] & 0x7fffffffu, x[3] & 0x7fffffffu));
             mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1, 4));
             mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2, 4));
             const uint32_t E = mx >> 23;
             const uint32_t packed = encode4_shared_exp<MM>(x, E);
-            if ((lane & 3) == 0) r[blk] = (uint8_t)E;
+            if ((lane & 3) == 0) r[blk] = (uint8_t)(AF ? a_exponent_byte(E) : E);
             uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
             if (MM == 7) reinterpret_cast<uint32_t *>(q)[lane & 3] = packed;
             else if (MM == 3) reinterpret_cast<uint16_t *>(q)[lane & 3] = (uint16_t)packed;
@@ -327,7 +332,7 @@ pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
 // ------------------------------------------------------------------------------------------------
 // host launchers
 // ------------------------------------------------------------------------------------------------
-template <int M, int ES>
+template <int M, int ES, bool AF>
 static cudaError_t launch_staged(const TileJob &job, const PtrTable &ptrs, int sm_count, cudaStream_t stream,
                                  unsigned int *status)
 {
@@ -337,22 +342,22 @@ static cudaError_t launch_staged(const TileJob &job, const PtrTable &ptrs, int s
     cudaGetDevice(&dev);
     dev &= 63;
     if (per_sm_cache[dev] == 0) {
-        cudaError_t e = cudaFuncSetAttribute(pack_staged_kernel<M, ES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(pack_staged_kernel<M, ES, AF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Cfg::smem_bytes);
         if (e != cudaSuccess) return e;
         int n = 0;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, pack_staged_kernel<M, ES>, kStagedThreads,
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, pack_staged_kernel<M, ES, AF>, kStagedThreads,
                                                           Cfg::smem_bytes);
         if (e != cudaSuccess) return e;
         per_sm_cache[dev] = n < 1 ? 1 : (n > 4 ? 4 : n);
     }
     uint32_t grid = (uint32_t)(sm_count * per_sm_cache[dev]);
     if (grid > job.total_items) grid = job.total_items;
-    pack_staged_kernel<M, ES><<<grid, kStagedThreads, Cfg::smem_bytes, stream>>>(job, ptrs, status);
+    pack_staged_kernel<M, ES, AF><<<grid, kStagedThreads, Cfg::smem_bytes, stream>>>(job, ptrs, status);
     return cudaGetLastError();
 }
 
-template <int M, int ES>
+template <int M, int ES, bool AF>
 static cudaError_t launch_direct(const TileJob &job, const PtrTable &ptrs, int batch, int vec_ok, int sm_count,
                                  cudaStream_t stream)
 {
@@ -360,28 +365,31 @@ static cudaError_t launch_direct(const TileJob &job, const PtrTable &ptrs, int b
     uint64_t blocks = (units + 7) / 8;
     const uint64_t cap = (uint64_t)sm_count * 32;
     if (blocks > cap) blocks = cap;
-    pack_direct_kernel<M, ES><<<(unsigned)blocks, 256, 0, stream>>>(job, ptrs, batch, vec_ok);
+    pack_direct_kernel<M, ES, AF><<<(unsigned)blocks, 256, 0, stream>>>(job, ptrs, batch, vec_ok);
     return cudaGetLastError();
 }
 
-// mant_bits 7/3/1 = Bfp pack, 0 = plain relayout; es = source element bytes.
-// path: 0 = staged (needs 16-byte aligned rows), 1 = direct.
-cudaError_t launch_tilize(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int path,
+// mant_bits 7/3/1 = Bfp pack, 0 = plain relayout; es = source element bytes; a_format: 5-bit shared
+// exponent with a binary16 source.  path: 0 = staged (needs 16-byte aligned rows), 1 = direct.
+cudaError_t launch_tilize(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int a_format, int path,
                           int vec_ok, int sm_count, cudaStream_t stream, unsigned int *status)
 {
-#define BUDA_DISPATCH(MM, EE)                                                                  \
-    if (mant_bits == MM && es == EE)                                                           \
-        return path == 0 ? launch_staged<MM, EE>(job, ptrs, sm_count, stream, status)          \
-                         : launch_direct<MM, EE>(job, ptrs, batch, vec_ok, sm_count, stream);
-    BUDA_DISPATCH(7, 4)
-    BUDA_DISPATCH(3, 4)
-    BUDA_DISPATCH(1, 4)
-    BUDA_DISPATCH(7, 2)
-    BUDA_DISPATCH(3, 2)
-    BUDA_DISPATCH(1, 2)
-    BUDA_DISPATCH(0, 4)
-    BUDA_DISPATCH(0, 2)
-    BUDA_DISPATCH(0, 1)
+#define BUDA_DISPATCH(MM, EE, AA)                                                                  \
+    if (mant_bits == MM && es == EE && (a_format != 0) == AA)                                      \
+        return path == 0 ? launch_staged<MM, EE, AA>(job, ptrs, sm_count, stream, status)          \
+                         : launch_direct<MM, EE, AA>(job, ptrs, batch, vec_ok, sm_count, stream);
+    BUDA_DISPATCH(7, 4, false)
+    BUDA_DISPATCH(3, 4, false)
+    BUDA_DISPATCH(1, 4, false)
+    BUDA_DISPATCH(7, 2, false)
+    BUDA_DISPATCH(3, 2, false)
+    BUDA_DISPATCH(1, 2, false)
+    BUDA_DISPATCH(7, 2, true)
+    BUDA_DISPATCH(3, 2, true)
+    BUDA_DISPATCH(1, 2, true)
+    BUDA_DISPATCH(0, 4, false)
+    BUDA_DISPATCH(0, 2, false)
+    BUDA_DISPATCH(0, 1, false)
 #undef BUDA_DISPATCH
     return cudaErrorInvalidValue;
 }

@@ -53,7 +53,14 @@ __device__ __forceinline__ void decode_uitem(const TileJob &job, uint32_t item, 
 }
 
 // In this file PtrTable.src is the queue image and PtrTable.dst the row-major tensor.
-template <int M, int ES>
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi)
+{
+    uint32_t d;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));  // exact for decoded values; overflow gives infinity
+    return d;
+}
+
+template <int M, int ES, bool AF>
 __global__ void __launch_bounds__(kUStagedThreads)
 unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ PtrTable ptrs, unsigned int *status)
 {
@@ -149,7 +156,7 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
                     d[0] = *reinterpret_cast<const uint32_t *>(q);
                 }
                 float v[16];
-                bfp_decode16<MM>(E, d, v);
+                bfp_decode16<MM, AF>(E, d, v);
                 uint8_t *p = ob + lane * Cfg::pitch + bc * 16 * ES;
                 if (ES == 4) {
 #pragma unroll
@@ -160,7 +167,8 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
                     uint32_t h[8];
 #pragma unroll
                     for (int j = 0; j < 8; j++)
-                        h[j] = __byte_perm(__float_as_uint(v[2 * j]), __float_as_uint(v[2 * j + 1]), 0x7632);
+                        h[j] = AF ? pack_half2(v[2 * j], v[2 * j + 1])
+                                  : __byte_perm(__float_as_uint(v[2 * j]), __float_as_uint(v[2 * j + 1]), 0x7632);
                     *reinterpret_cast<uint4 *>(p) = make_uint4(h[0], h[1], h[2], h[3]);
                     *reinterpret_cast<uint4 *>(p + 16) = make_uint4(h[4], h[5], h[6], h[7]);
                 }
@@ -183,7 +191,7 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
         if (named_bar_or(1, kUConsumerThreads, !ok)) break;
         if (tid == 0) mbar_arrive(&empty[s]);
         if (warp == 0) {
-            uint8_t *dst = ptrs.dst[m.b] + (uint64_t)m.w * job.stride_w + (uint64_t)m.z * job.stride_z +
+            uint8_t *dst = ptrs.dst[m.b] + (uint64_t)m.w * job.stride_w + rm_z_offset(job, m.z) +
                            ((uint64_t)m.rt * 32u + lane) * job.stride_r + (uint64_t)m.ct0 * 32u * ES;
             bulk_s2g(dst, ob + lane * Cfg::pitch, m.ntiles * 32u * ES);
             bulk_commit();
@@ -195,7 +203,7 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
 // ------------------------------------------------------------------------------------------------
 // direct kernel
 // ------------------------------------------------------------------------------------------------
-template <int M, int ES>
+template <int M, int ES, bool AF>
 __global__ void __launch_bounds__(256)
 unpack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ PtrTable ptrs, int batch, int vec_ok)
 {
@@ -217,7 +225,7 @@ unpack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant_
         const uint32_t fr = half * 8u + (lane >> 2);
         const uint64_t row = (uint64_t)rt * 32u + (face >> 1) * 16u + fr;
         const uint64_t col = (uint64_t)ct * 32u + (face & 1u) * 16u + (lane & 3) * 4u;
-        uint8_t *p = ptrs.dst[b] + (uint64_t)w * job.stride_w + (uint64_t)z * job.stride_z + row * job.stride_r + col * ES;
+        uint8_t *p = ptrs.dst[b] + (uint64_t)w * job.stride_w + rm_z_offset(job, z) + row * job.stride_r + col * ES;
         const uint8_t *r = ptrs.src[b] + tile_record_offset(job, w, z, rt, ct) + hdr;
         const uint32_t blk = face * 16u + fr;
         uint32_t x[4];
@@ -229,17 +237,18 @@ unpack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant_
             if (MM == 7) packed = reinterpret_cast<const uint32_t *>(q)[lane & 3];
             else if (MM == 3) packed = reinterpret_cast<const uint16_t *>(q)[lane & 3];
             else packed = q[lane & 3];
-            float post;
-            const float sc = bfp_block_scale<MM>(E, post);
+            float post = 1.0f;
+            const float sc = AF ? bfp_a_block_scale<MM>(E & 31u) : bfp_block_scale<MM>(E, post);
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const uint32_t d = packed >> (i * (MM + 1));
                 const uint32_t qb = kMagicBits | (d & BfpTraits<MM>::qmax);
                 const uint32_t signbit = (d << (31 - MM)) & 0x80000000u;
                 float mag = __fmul_rn(__fadd_rn(__uint_as_float(qb), -12582912.0f), sc);
-                if (MM == 1) mag = __fmul_rn(mag, post);
-                x[i] = __float_as_uint(__fadd_rn(__uint_as_float(__float_as_uint(mag) | signbit), 0.0f));
-                if (ES == 2) x[i] >>= 16;
+                if (MM == 1 && !AF) mag = __fmul_rn(mag, post);
+                const float val = __fadd_rn(__uint_as_float(__float_as_uint(mag) | signbit), 0.0f);
+                x[i] = __float_as_uint(val);
+                if (ES == 2) x[i] = AF ? (pack_half2(val, 0.0f) & 0xffffu) : (x[i] >> 16);
             }
         } else {
             const uint8_t *q = r + ((uint64_t)blk * 16u + (lane & 3) * 4u) * ES;
@@ -284,7 +293,7 @@ unpack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant_
 // ------------------------------------------------------------------------------------------------
 // host launchers
 // ------------------------------------------------------------------------------------------------
-template <int M, int ES>
+template <int M, int ES, bool AF>
 static cudaError_t launch_ustaged(const TileJob &job, const PtrTable &ptrs, int sm_count, cudaStream_t stream,
                                   unsigned int *status)
 {
@@ -294,22 +303,22 @@ static cudaError_t launch_ustaged(const TileJob &job, const PtrTable &ptrs, int 
     cudaGetDevice(&dev);
     dev &= 63;
     if (per_sm_cache[dev] == 0) {
-        cudaError_t e = cudaFuncSetAttribute(unpack_staged_kernel<M, ES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(unpack_staged_kernel<M, ES, AF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Cfg::smem_bytes);
         if (e != cudaSuccess) return e;
         int n = 0;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, unpack_staged_kernel<M, ES>, kUStagedThreads,
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, unpack_staged_kernel<M, ES, AF>, kUStagedThreads,
                                                           Cfg::smem_bytes);
         if (e != cudaSuccess) return e;
         per_sm_cache[dev] = n < 1 ? 1 : (n > 4 ? 4 : n);
     }
     uint32_t grid = (uint32_t)(sm_count * per_sm_cache[dev]);
     if (grid > job.total_items) grid = job.total_items;
-    unpack_staged_kernel<M, ES><<<grid, kUStagedThreads, Cfg::smem_bytes, stream>>>(job, ptrs, status);
+    unpack_staged_kernel<M, ES, AF><<<grid, kUStagedThreads, Cfg::smem_bytes, stream>>>(job, ptrs, status);
     return cudaGetLastError();
 }
 
-template <int M, int ES>
+template <int M, int ES, bool AF>
 static cudaError_t launch_udirect(const TileJob &job, const PtrTable &ptrs, int batch, int vec_ok, int sm_count,
                                   cudaStream_t stream)
 {
@@ -317,27 +326,34 @@ static cudaError_t launch_udirect(const TileJob &job, const PtrTable &ptrs, int 
     uint64_t blocks = (units + 7) / 8;
     const uint64_t cap = (uint64_t)sm_count * 32;
     if (blocks > cap) blocks = cap;
-    unpack_direct_kernel<M, ES><<<(unsigned)blocks, 256, 0, stream>>>(job, ptrs, batch, vec_ok);
+    unpack_direct_kernel<M, ES, AF><<<(unsigned)blocks, 256, 0, stream>>>(job, ptrs, batch, vec_ok);
     return cudaGetLastError();
 }
 
-// mant_bits 7/3/1 = Bfp decode, 0 = plain relayout; es = destination element bytes.
-cudaError_t launch_untilize(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int path,
+// mant_bits 7/3/1 = Bfp decode, 0 = plain relayout; es = destination element bytes; a_format: 5-bit
+// shared exponent (destination binary16 when es == 2).
+cudaError_t launch_untilize(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int a_format, int path,
                             int vec_ok, int sm_count, cudaStream_t stream, unsigned int *status)
 {
-#define BUDA_DISPATCH(MM, EE)                                                                   \
-    if (mant_bits == MM && es == EE)                                                            \
-        return path == 0 ? launch_ustaged<MM, EE>(job, ptrs, sm_count, stream, status)          \
-                         : launch_udirect<MM, EE>(job, ptrs, batch, vec_ok, sm_count, stream);
-    BUDA_DISPATCH(7, 4)
-    BUDA_DISPATCH(3, 4)
-    BUDA_DISPATCH(1, 4)
-    BUDA_DISPATCH(7, 2)
-    BUDA_DISPATCH(3, 2)
-    BUDA_DISPATCH(1, 2)
-    BUDA_DISPATCH(0, 4)
-    BUDA_DISPATCH(0, 2)
-    BUDA_DISPATCH(0, 1)
+#define BUDA_DISPATCH(MM, EE, AA)                                                                   \
+    if (mant_bits == MM && es == EE && (a_format != 0) == AA)                                       \
+        return path == 0 ? launch_ustaged<MM, EE, AA>(job, ptrs, sm_count, stream, status)          \
+                         : launch_udirect<MM, EE, AA>(job, ptrs, batch, vec_ok, sm_count, stream);
+    BUDA_DISPATCH(7, 4, false)
+    BUDA_DISPATCH(3, 4, false)
+    BUDA_DISPATCH(1, 4, false)
+    BUDA_DISPATCH(7, 2, false)
+    BUDA_DISPATCH(3, 2, false)
+    BUDA_DISPATCH(1, 2, false)
+    BUDA_DISPATCH(7, 4, true)
+    BUDA_DISPATCH(3, 4, true)
+    BUDA_DISPATCH(1, 4, true)
+    BUDA_DISPATCH(7, 2, true)
+    BUDA_DISPATCH(3, 2, true)
+    BUDA_DISPATCH(1, 2, true)
+    BUDA_DISPATCH(0, 4, false)
+    BUDA_DISPATCH(0, 2, false)
+    BUDA_DISPATCH(0, 1, false)
 #undef BUDA_DISPATCH
     return cudaErrorInvalidValue;
 }

@@ -60,6 +60,7 @@ _SIGS = {
     "buda_queue_bytes": (_i64, [_gp, _i, _i, _u32]),
     "buda_queue_write": (_i, [_vp, _i, _i, _u32p, _u64p, _gp, _i, _i, _vp, _u32, _u32, _vp]),
     "buda_queue_read": (_i, [_vp, _i, _i, _gp, _u32, _u32, _vp, _i, _i, _u32p, _u64p, _vp]),
+    "buda_queue_read_stacked": (_i, [_vp, _i, _i, _gp, _u32, _u32, _u32, _u32, _u32, _i, _vp, _i, _vp]),
     "buda_malloc": (_i, [_vpp, _u64]),
     "buda_free": (_i, [_vp]),
     "buda_host_alloc": (_i, [_vpp, _u64]),

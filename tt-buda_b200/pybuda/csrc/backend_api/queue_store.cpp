@@ -376,8 +376,9 @@ DEVICE_STATUS_CODE get_output(const tt_dram_io_desc &q, tt_PytorchTensorDesc &ou
 {
     if (q.tile_height != 32 || q.tile_width != 32 || q.layout != IO_LAYOUT::Tilized)
         return fail(DEVICE_STATUS_CODE::RuntimeError, "get_output: only tilized queues of 32x32 tiles are supported");
-    if (q.hstack_factor != 1 || q.vstack_factor != 1)
-        return fail(DEVICE_STATUS_CODE::RuntimeError, "get_output: hstack / vstack host transforms are not supported");
+    const std::uint32_t hs = std::max<std::uint32_t>(1, q.hstack_factor), vs = std::max<std::uint32_t>(1, q.vstack_factor);
+    if (q.t % (hs * vs))
+        return fail(DEVICE_STATUS_CODE::RuntimeError, "get_output: t is not a multiple of hstack_factor x vstack_factor");
     std::shared_ptr<QueueState> st;
     if (auto rc = get_queue(q, false, st); rc != DEVICE_STATUS_CODE::Success)
         return rc;
@@ -413,19 +414,38 @@ DEVICE_STATUS_CODE get_output(const tt_dram_io_desc &q, tt_PytorchTensorDesc &ou
         fmt = q.bufq_target_format;
     }
     const std::uint32_t itemsize = data_format_byte_size(fmt, 1);
-    const std::array<std::uint32_t, 4> shape = {entries, q.t, q.rows(), q.cols()};
+    // output host transforms: the t slices are stacked hs across and vs down
+    const std::array<std::uint32_t, 4> shape = {entries, q.t / (hs * vs), q.rows() * vs, q.cols() * hs};
     const std::uint64_t bytes = (std::uint64_t)entries * q.t * q.rows() * q.cols() * itemsize;
     if ((std::uint64_t)q.t * q.rows() * q.cols() * itemsize > 0xffffffffull)
         return fail(DEVICE_STATUS_CODE::RuntimeError, "get_output: an entry above 4 GiB does not fit 32-bit byte strides");
     void *host = host_acquire(bytes);
     if (!host)
         return fail(DEVICE_STATUS_CODE::RuntimeError, "get_output: " + cabi_error());
-    const std::array<std::uint64_t, 4> st64 = {(std::uint64_t)q.t * q.rows() * q.cols() * itemsize,
-                                               (std::uint64_t)q.rows() * q.cols() * itemsize, (std::uint64_t)q.cols() * itemsize,
+    const std::array<std::uint64_t, 4> st64 = {(std::uint64_t)shape[1] * shape[2] * shape[3] * itemsize,
+                                               (std::uint64_t)shape[2] * shape[3] * itemsize, (std::uint64_t)shape[3] * itemsize,
                                                itemsize};
     const buda_queue_geom g = geom_of(q);
-    const int rc = buda_queue_read(st->base, (int)q.bufq_target_format, q.tile_header ? 1 : 0, &g, st->slots, first_slot, host, 1,
-                                   (int)fmt, shape.data(), st64.data(), nullptr);
+    int rc;
+    if (hs * vs == 1)
+    {
+        rc = buda_queue_read(st->base, (int)q.bufq_target_format, q.tile_header ? 1 : 0, &g, st->slots, first_slot, host, 1, (int)fmt,
+                             shape.data(), st64.data(), nullptr);
+    }
+    else
+    {
+        // untilize into the stacked layout on the device, then one copy to the host
+        void *dev = nullptr;
+        rc = buda_malloc(&dev, bytes);
+        if (rc == BUDA_SUCCESS)
+        {
+            rc = buda_queue_read_stacked(st->base, (int)q.bufq_target_format, q.tile_header ? 1 : 0, &g, st->slots, first_slot, entries,
+                                         hs, vs, q.stack_row_major ? 1 : 0, dev, (int)fmt, nullptr);
+            if (rc == BUDA_SUCCESS)
+                rc = buda_memcpy(host, dev, bytes, 1, nullptr);
+            buda_free(dev);
+        }
+    }
     if (rc != BUDA_SUCCESS)
     {
         host_release(host);
