@@ -231,6 +231,29 @@ int buda_requantize(const int32_t *x, int64_t n, const float *inp_scale, const f
 int buda_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N, void *C,
                     int64_t ldc, void *stream);
 
+/* The same product written to n_dst (1..8) destinations: C_dsts[0] in this device's memory, the others
+ * typically the same matrix in peer devices' memory (buda_ipc_open), each already pointing at the
+ * column block this device owns.  The epilogue stores every output tile to all destinations, so a
+ * column-parallel matmul (pybuda/csrc/passes/dataformat.cpp:409-418 fixes the weight format; the
+ * split of the weight columns over devices follows the reference's grid-column split of a matmul,
+ * pybuda/csrc/balancer/types.cpp:629-648) leaves the gathered result on every device with no
+ * separate all-gather.  Nothing is read from a peer.  Peers' stores are complete when the kernel is;
+ * the caller synchronises the devices (a barrier) before reading. */
+int buda_bfp8b_gemm_scatter(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N,
+                            void *const *C_dsts, int n_dst, int64_t ldc, void *stream);
+
+/* Which tensor-core kernel buda_bfp8b_gemm* launches: 0 = automatic (CTA-pair kernel for M > 256, single-CTA
+ * kernel otherwise), 1 = single-CTA, 2 = CTA pair.  Process-wide; a negative value only reads.  Returns the
+ * previous setting.  Results are identical bit for bit; the knob exists for measurement. */
+int buda_gemm_select_kernel(int which);
+
+/* Inter-process handles for device memory from buda_malloc, so that one process per GPU can hand its
+ * output matrix to its peers.  export: 64-byte handle of an allocation's base pointer.  open: maps a
+ * peer's allocation into this process (peer access is enabled on demand).  close: unmaps it. */
+int buda_ipc_export(const void *dev_ptr, unsigned char handle_out[64]);
+int buda_ipc_open(const unsigned char handle[64], void **dev_ptr_out);
+int buda_ipc_close(void *dev_ptr);
+
 /* ------------------------------------------------------------------ errors and status */
 
 /* Copies the calling thread's last error text (NUL terminated) into buf; returns its length. */

@@ -56,9 +56,17 @@ def test_one_hot_rows_copy_decoded_weights_exactly(ops, oracle):
                     f"got {c[tuple(bad[0])].item()} want {want[tuple(bad[0])].item()}")
 
 
+@pytest.fixture(params=["single", "pair"])
+def kernel(request, ops):
+    """Both tensor-core kernels (one CTA per tile; a CTA pair per tile) run every shape."""
+    prev = ops.select_gemm_kernel(request.param)
+    yield request.param
+    ops.select_gemm_kernel(prev)
+
+
 @pytest.mark.parametrize("M,K,N", [(256, 64, 256), (256, 256, 256), (512, 512, 768), (128, 192, 256), (300, 128, 512),
-                                   (1024, 1024, 1024)])
-def test_matmul_small_shapes(ops, oracle, M, K, N):
+                                   (1024, 1024, 1024), (1500, 320, 1280)])
+def test_matmul_small_shapes(ops, oracle, kernel, M, K, N):
     img, wd = _weights(oracle, ops, K, N, seed=M + K + N)
     a = torch.randn(M, K, generator=torch.Generator().manual_seed(1)).bfloat16()
     c = ops.bfp8b_matmul(a.cuda(), img, N).cpu()
@@ -69,7 +77,87 @@ def test_matmul_small_shapes(ops, oracle, M, K, N):
         _check(c, ref2)
 
 
-def test_strided_operands_and_reuse(ops, oracle):
+def test_pair_and_single_kernels_agree_bit_for_bit(ops, oracle):
+    M, K, N = 2048, 1024, 1536
+    img, _ = _weights(oracle, ops, K, N, seed=11)
+    a = torch.randn(M, K, generator=torch.Generator().manual_seed(12)).bfloat16().cuda()
+    prev = ops.select_gemm_kernel("single")
+    try:
+        c1 = ops.bfp8b_matmul(a, img, N)
+        ops.select_gemm_kernel("pair")
+        c2 = ops.bfp8b_matmul(a, img, N)
+    finally:
+        ops.select_gemm_kernel(prev)
+    assert torch.equal(c1, c2)    # same k order, same binary32 accumulation
+    rc, st = ops._cabi.device_status()
+    assert rc == 0 and st == 0
+
+
+def test_scatter_writes_every_destination(ops, oracle, kernel):
+    M, K, N = 768, 256, 512
+    img, wd = _weights(oracle, ops, K, N, seed=21)
+    a = torch.randn(M, K, generator=torch.Generator().manual_seed(22)).bfloat16().cuda()
+    # three full-width outputs [M, 2N]; this "rank" owns columns N..2N of each
+    outs = [torch.zeros(M, 2 * N, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    ops.bfp8b_matmul_scatter(a, img, N, [o.data_ptr() + N * 2 for o in outs], 2 * N)
+    torch.cuda.synchronize()
+    _check(outs[0][:, N:].cpu(), a.cpu().float() @ wd)
+    for o in outs:
+        assert torch.all(o[:, :N] == 0)
+        assert torch.equal(o, outs[0])
+    with pytest.raises(ops._cabi.BudaError):
+        ops.bfp8b_matmul_scatter(a, img, N, [outs[0].data_ptr()] * 9, 2 * N)
+
+
+def _ipc_child(handle, m, k, n, seed, q):
+    """Another process of the box: maps the parent's matrix and lets the matmul epilogue store into it."""
+    import os, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path[:0] = [root, os.path.join(root, "tt-buda_b200")]
+    try:
+        from pybuda import cuda_ops
+        g = torch.Generator().manual_seed(seed)
+        a = torch.randn(m, k, generator=g).bfloat16().cuda()
+        w = torch.randn(1, 1, k, n, generator=g) * 0.02
+        img = cuda_ops.tilize_pack(w.cuda(), cuda_ops.DF.Bfp8_b)
+        mine = cuda_ops.SharedDeviceMatrix(m, n)
+        peer = mine.open_peer(handle)
+        cuda_ops.bfp8b_matmul_scatter(a, img, n, [mine.ptr, peer], n)
+        torch.cuda.synchronize()
+        local = mine.tensor.cpu().view(torch.int16).numpy().tobytes()   # plain bytes: nothing shared with this process
+        mine.close()
+        q.put(("ok", local))
+    except Exception as e:  # noqa: BLE001
+        q.put(("error", repr(e)))
+
+
+def test_scatter_into_another_process_memory(ops, oracle):
+    """The inter-process mapping the column-parallel matmul relies on, exercised on one GPU: a child process
+    computes the product and its epilogue stores it into THIS process's matrix as well as its own."""
+    import torch.multiprocessing as mp
+    m, k, n, seed = 512, 128, 256, 31
+    shared = ops.SharedDeviceMatrix(m, n)
+    shared.tensor.zero_()
+    torch.cuda.synchronize()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    child = ctx.Process(target=_ipc_child, args=(shared.handle(), m, k, n, seed, q))
+    child.start()
+    status, payload = q.get(timeout=300)
+    child.join(timeout=60)
+    assert status == "ok", payload
+    torch.cuda.synchronize()
+    got = shared.tensor.cpu()
+    shared.close()
+    assert got.view(torch.int16).numpy().tobytes() == payload
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    w = torch.randn(1, 1, k, n, generator=g) * 0.02
+    wd = torch.from_numpy(oracle.unpack_untilize(oracle.tilize_pack(w.numpy(), oracle.Bfp8_b), oracle.Bfp8_b, (1, 1, k, n)))[0, 0]
+    _check(got, a.float() @ wd)
+
+
+def test_strided_operands_and_reuse(ops, oracle, kernel):
     M, K, N = 256, 128, 256
     img, wd = _weights(oracle, ops, K, N, seed=3)
     big = torch.randn(M, K + 64, generator=torch.Generator().manual_seed(2)).bfloat16().cuda()
@@ -91,7 +179,7 @@ def test_bad_shapes_are_refused(ops):
     assert "K % 64" in str(e.value)
 
 
-def test_config4_full_size(ops, oracle):
+def test_config4_full_size(ops, oracle, kernel):
     # activations bf16 [8192,4096] ~ N(0,1); weights fp32 [4096,16384] ~ N(0,0.02) packed to Bfp8_b
     M, K, N = 8192, 4096, 16384
     a = torch.randn(M, K, generator=torch.Generator().manual_seed(6)).bfloat16().cuda()

@@ -47,7 +47,19 @@ def _worker(rank, world, port, results):
         ok = ok and rel <= 1e-3 and c.shape == (m, n)
         single = cuda_ops.bfp8b_matmul(a, full_img, n)
         ok = ok and torch.equal(single, c)            # same kernel, same k order: identical bits
-        results[rank] = (bool(ok), rel)
+        # the same product with the exchange fused into the kernel: each rank's epilogue stores its column
+        # block into every rank's output through peer-mapped memory
+        out = op.enable_fused_scatter(m)
+        out.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        for _ in range(2):
+            cf = op.fused(a)
+        torch.cuda.synchronize()
+        fused_equal = torch.equal(cf, single)
+        ok = ok and fused_equal
+        op.disable_fused_scatter()
+        results[rank] = (bool(ok), rel, bool(fused_equal))
     finally:
         dist.destroy_process_group()
 

@@ -20,12 +20,11 @@
 //   warps 0-3     epilogue: tcgen05.ld the accumulators, round to bfloat16, store C
 // Every mbarrier wait is bounded; a wait that gives up raises the device status word and the CTA
 // winds down (tensor memory is freed on every path).
-#include <cuda.h>
-
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 
-#include "buda_common.cuh"
+#include "gemm_common.cuh"
 
 namespace buda {
 
@@ -44,10 +43,13 @@ constexpr int kLoadStages = GEMM_A_STAGES;  // activation ring
 constexpr int kBStages = GEMM_B_STAGES;     // decoded-weight ring
 constexpr int kABytes = kBM * kBK * 2;           // 32768
 constexpr int kBBytes = kBN * kBK * 2;           // 32768
-constexpr int kRecord = 1088;                    // Bfp8_b tile record, no header
 template <int DW>
 constexpr int threads_for() { return 32 * (4 + 1 + 1 + DW); }  // epilogue + producer + MMA + decode warps
 constexpr int kTmemCols = 512;
+#ifndef GEMM_PREFETCH
+#define GEMM_PREFETCH 2
+#endif
+constexpr int kPrefetch = GEMM_PREFETCH;   // k-blocks of raw weight records in flight per decode thread
 
 constexpr int kSmemA = 0;
 constexpr int kSmemB = kSmemA + kLoadStages * kABytes;
@@ -59,77 +61,6 @@ constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 16 + 1024;  // + tmem holde
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) | ((uint32_t)(kBN >> 3) << 17) |
                             ((uint32_t)(128 >> 4) << 24);
 
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
-{
-    // start address, leading / stride byte offsets in 16-byte units, descriptor version 1, 128B swizzle
-    return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) |
-           ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | (2ull << 61);
-}
-
-__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *tmap, int x, int y, uint64_t *bar)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-            smem_u32(smem_dst)),
-        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(smem_u32(bar))
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// arrive on an mbarrier once every tcgen05.mma issued so far by this thread has completed
-__device__ __forceinline__ void umma_commit(uint64_t *bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, "
-        "[%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ uint32_t fma_bf16x2(uint32_t a, uint32_t b, uint32_t c)
-{
-    uint32_t d;
-    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi)
-{
-    uint32_t d;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
-    return d;
-}
-
-struct Params {
-    const uint8_t *W;     // Bfp8_b image: record (kt, nt) at (kt * Nt + nt) * 1088
-    uint16_t *C;          // bfloat16, row stride ldc
-    int64_t M, N, K, ldc;
-    uint32_t m_tiles, n_tiles, k_blocks, Nt;
-    unsigned int *status;
-};
 
 template <int kDecodeWarps>
 __global__ void __launch_bounds__(threads_for<kDecodeWarps>(), 1)
@@ -193,9 +124,13 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         ok = false;
                         break;
                     }
+#ifndef GEMM_EXP_NO_A
                     mbar_arrive_expect_tx(&full_a[s], kABytes);
                     tma_load_2d(sA + s * kABytes, &tmap_a, (int)(kb * kBK), (int)(m_blk * kBM), &full_a[s]);
                     tma_load_2d(sA + s * kABytes + kABytes / 2, &tmap_a, (int)(kb * kBK), (int)(m_blk * kBM + 128), &full_a[s]);
+#else
+                    mbar_arrive(&full_a[s]);
+#endif
                 }
             }
             if (!ok || *abort_flag) {
@@ -255,42 +190,60 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     } else if (warp >= 6) {
         // ------------------------------------------------------------------ decode warps
         // Raw records go global -> registers (coalesced 16-byte loads, one block per thread per unit),
-        // one k-block ahead of the decode, so they never cost shared-memory bandwidth.
+        // kPrefetch k-blocks ahead of the decode, so they never cost shared-memory bandwidth and the
+        // loop never waits for a load it just issued.
         constexpr int kUnits = 32 / kDecodeWarps;  // units of 32 blocks per warp per k-block
         const int dw = warp - 6;
-        uint4 mant_next[kUnits];
-        uint32_t exp_next[kUnits];
-        auto fetch = [&](uint32_t n_blk, uint32_t kb) {
+        uint4 mq[kPrefetch][kUnits];
+        uint32_t eq[kPrefetch][kUnits];
+        uint32_t f_tile = blockIdx.x, f_kb = 0;   // fetch cursor: walks the same (tile, k-block) sequence, kPrefetch ahead
+        auto fetch_into = [&](uint4 (&m)[kUnits], uint32_t (&e)[kUnits]) {
+            if (f_tile < total_tiles) {
+                const uint32_t n_blk = f_tile / p.m_tiles;
 #pragma unroll
-            for (int it = 0; it < kUnits; it++) {
-                const int u = it * kDecodeWarps + dw;          // 32 units: (record, half of its 64 blocks)
-                const int r = u >> 1;                           // record: k-tile r / 8, n-tile r % 8
-                const int blk = (u & 1) * 32 + lane;            // block = face * 16 + face row
-                const uint8_t *rec = p.W + ((uint64_t)(kb * 2 + (r >> 3)) * p.Nt + (uint64_t)n_blk * 8 + (r & 7)) * kRecord;
-                mant_next[it] = __ldg(reinterpret_cast<const uint4 *>(rec + 64 + blk * 16));
-                exp_next[it] = __ldg(rec + blk);
+                for (int it = 0; it < kUnits; it++) {
+                    const int u = it * kDecodeWarps + dw;          // 32 units: (record, half of its 64 blocks)
+                    const int r = u >> 1;                           // record: k-tile r / 8, n-tile r % 8
+                    const int blk = (u & 1) * 32 + lane;            // block = face * 16 + face row
+                    const uint8_t *rec = p.W + ((uint64_t)(f_kb * 2 + (r >> 3)) * p.Nt + (uint64_t)n_blk * 8 + (r & 7)) * kRecord;
+                    m[it] = __ldg(reinterpret_cast<const uint4 *>(rec + 64 + blk * 16));
+                    e[it] = __ldg(rec + blk);
+                }
+                if (++f_kb == p.k_blocks) {
+                    f_kb = 0;
+                    f_tile += gridDim.x;
+                }
+            } else {
+#pragma unroll
+                for (int it = 0; it < kUnits; it++) {
+                    m[it] = make_uint4(0u, 0u, 0u, 0u);
+                    e[it] = 0u;
+                }
             }
         };
+#pragma unroll
+        for (int d = 0; d < kPrefetch; d++) fetch_into(mq[d], eq[d]);
         uint32_t i = 0;
         bool ok = true;
-        if (blockIdx.x < total_tiles) fetch(blockIdx.x / p.m_tiles, 0);
         for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const uint32_t n_blk = tile / p.m_tiles;
             for (uint32_t kb = 0; kb < p.k_blocks; kb++, i++) {
                 const int t = i % kBStages;
                 uint4 mant_cur[kUnits];
                 uint32_t exp_cur[kUnits];
 #pragma unroll
                 for (int it = 0; it < kUnits; it++) {
-                    mant_cur[it] = mant_next[it];
-                    exp_cur[it] = exp_next[it];
+                    mant_cur[it] = mq[0][it];
+                    exp_cur[it] = eq[0][it];
                 }
-                // issue the next k-block's loads before waiting for a free stage
-                if (kb + 1 < p.k_blocks) {
-                    fetch(n_blk, kb + 1);
-                } else if (tile + gridDim.x < total_tiles) {
-                    fetch((tile + gridDim.x) / p.m_tiles, 0);
+#pragma unroll
+                for (int d = 0; d + 1 < kPrefetch; d++) {
+#pragma unroll
+                    for (int it = 0; it < kUnits; it++) {
+                        mq[d][it] = mq[d + 1][it];
+                        eq[d][it] = eq[d + 1][it];
+                    }
                 }
+                fetch_into(mq[kPrefetch - 1], eq[kPrefetch - 1]);
                 const bool got = mbar_wait_bounded(&empty_b[t], ((i / kBStages) & 1u) ^ 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT);
                 if (!__all_sync(0xffffffffu, got)) {  // the whole warp leaves together
                     ok = false;
@@ -306,29 +259,9 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     const int u = it * kDecodeWarps + dw;
                     const int r = u >> 1;
                     const int blk = (u & 1) * 32 + lane;
-                    const uint4 mant = mant_cur[it];
-                    // scale 2^(E-133) as bfloat16 bits (exponent field E-6) in both halves; -128 * scale beside it.
-                    // Blocks below 2^-126 (E < 7) flush to zero.
-                    const uint32_t e6 = max(exp_cur[it], 6u) - 6u;
-                    const uint32_t sc = e6 * 0x00800080u;
-                    const uint32_t off = e6 ? sc + 0x83808380u : 0u;
-                    const uint32_t w[4] = {mant.x, mant.y, mant.z, mant.w};
-                    uint32_t o[8];
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        const uint32_t mg = w[q] & 0x7f7f7f7fu, sg = w[q] & 0x80808080u;
-                        // (128 + m) as bfloat16 is 0x4300 | m: splice each magnitude byte under 0x43
-                        const uint32_t p01 = __byte_perm(mg, 0x43434343u, 0x4140);
-                        const uint32_t p23 = __byte_perm(mg, 0x43434343u, 0x4342);
-                        o[2 * q] = fma_bf16x2(p01, sc, off) | __byte_perm(sg, 0u, 0x1404);
-                        o[2 * q + 1] = fma_bf16x2(p23, sc, off) | __byte_perm(sg, 0u, 0x3424);
-                    }
                     const int k_local = (r >> 3) * 32 + (blk >> 5) * 16 + (blk & 15);
                     const int n_local = (r & 7) * 32 + ((blk >> 4) & 1) * 16;
-                    const int kr = k_local & 7, c0 = (n_local & 63) >> 3;
-                    uint8_t *dst = bst + ((k_local >> 3) * 4 + (n_local >> 6)) * 1024 + kr * 128;
-                    *reinterpret_cast<uint4 *>(dst + ((c0 ^ kr) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                    *reinterpret_cast<uint4 *>(dst + (((c0 + 1) ^ kr) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                    decode_block_to_operand<kBN / 64>(mant_cur[it], exp_cur[it], bst, k_local, n_local);
                 }
                 fence_async_smem();  // the tensor core reads shared memory through the async proxy
                 __syncwarp();
@@ -346,26 +279,17 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll 1
             for (int h = 0; h < 2; h++) {
                 const int64_t row = (int64_t)m_blk * kBM + h * 128 + warp * 32 + lane;
-                uint16_t *crow = p.C + row * p.ldc + (int64_t)n_blk * kBN;
+                const int64_t off = row * p.ldc + (int64_t)n_blk * kBN;
 #pragma unroll 1
                 for (int c = 0; c < kBN / 32; c++) {
                     uint32_t v[32];
                     tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(h * kBN + c * 32), v);
 #ifdef GEMM_EXP_NO_STORE
-                    if (row < p.M && v[0] == 0x7fc12345u) {
+                    if (row < p.M && v[0] == 0x7fc12345u)
 #else
-                    if (row < p.M) {
+                    if (row < p.M)
 #endif
-#pragma unroll
-                        for (int q = 0; q < 4; q++) {
-                            uint4 o;
-                            o.x = pack_bf16x2(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1]));
-                            o.y = pack_bf16x2(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3]));
-                            o.z = pack_bf16x2(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5]));
-                            o.w = pack_bf16x2(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7]));
-                            *reinterpret_cast<uint4 *>(crow + c * 32 + q * 8) = o;
-                        }
-                    }
+                        store_row32(v, p.C, p.n_dst, off + c * 32);
                 }
             }
             tc_fence_before();
@@ -382,27 +306,30 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn()
-{
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void *ptr = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-    return fn;
-}
-
 }  // namespace gemm
 
-cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W, int64_t N, void *C, int64_t ldc,
-                              int sm_count, cudaStream_t stream, unsigned int *status, char *err, size_t err_len)
+// Process-wide choice of matmul kernel: 0 auto, 1 single-CTA, 2 CTA pair.  which < 0 only reads.  The
+// environment variable BUDA_GEMM_KERNEL (single | pair) sets the initial value.  Returns the previous value.
+int gemm_kernel_choice(int which)
+{
+    static std::atomic<int> choice{-1};
+    int cur = choice.load();
+    if (cur < 0) {
+        const char *k = getenv("BUDA_GEMM_KERNEL");
+        int init = (k && k[0] == 's') ? 1 : (k && k[0] == 'p') ? 2 : 0;
+        choice.compare_exchange_strong(cur, init);
+        cur = choice.load();
+    }
+    if (which >= 0 && which <= 2) choice.store(which);
+    return cur;
+}
+
+cudaError_t launch_bfp8b_gemm_pair(const CUtensorMap &tmap, const gemm::Params &p, int sm_count, cudaStream_t stream);
+
+// C[d] (d < n_dst) all receive the product: C[0] on this device, the rest may be peers' memory mapped into
+// this process (plain stores from the epilogue; nothing is read from a peer).
+cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W, int64_t N, void *const *C, int n_dst,
+                              int64_t ldc, int sm_count, cudaStream_t stream, unsigned int *status, char *err, size_t err_len)
 {
     using namespace gemm;
     if (M <= 0 || N <= 0 || K <= 0 || (N % kBN) || (K % kBK)) {
@@ -410,8 +337,13 @@ cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, 
                  (long long)N, (long long)K);
         return cudaErrorInvalidValue;
     }
-    if (lda < K || ldc < N || (lda % 8) || (ldc % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
-        (reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) {
+    if (n_dst < 1 || n_dst > kMaxDst) {
+        snprintf(err, err_len, "bfp8b gemm writes 1..%d destinations (got %d)", kMaxDst, n_dst);
+        return cudaErrorInvalidValue;
+    }
+    bool aligned = !(reinterpret_cast<uintptr_t>(A) & 15) && !(reinterpret_cast<uintptr_t>(W) & 15);
+    for (int d = 0; d < n_dst; d++) aligned = aligned && C[d] && !(reinterpret_cast<uintptr_t>(C[d]) & 15);
+    if (lda < K || ldc < N || (lda % 8) || (ldc % 8) || !aligned) {
         snprintf(err, err_len, "bfp8b gemm needs 16-byte aligned A, W, C and row strides that are multiples of 8 elements");
         return cudaErrorInvalidValue;
     }
@@ -432,11 +364,27 @@ cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, 
         snprintf(err, err_len, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
         return cudaErrorInvalidValue;
     }
+    // Kernel choice: gemm_kernel_choice() (0 auto, 1 single-CTA, 2 CTA pair).  Auto gives the pair kernel every
+    // problem with more than 256 rows (below that its 512-row tile would be mostly padding).
     static int decode_warps = 0;
     if (decode_warps == 0) {
-        const char *env = getenv("BUDA_GEMM_DECODE_WARPS");  // tuning knob: 8 (default, measured fastest) or 16
+        const char *env = getenv("BUDA_GEMM_DECODE_WARPS");  // single-CTA kernel only: 8 (default, measured fastest) or 16
         decode_warps = (env && atoi(env) == 16) ? 16 : 8;
     }
+    const int forced = gemm_kernel_choice(-1);
+    Params p;
+    p.W = static_cast<const uint8_t *>(W);
+    for (int d = 0; d < kMaxDst; d++) p.C[d] = d < n_dst ? static_cast<uint16_t *>(C[d]) : nullptr;
+    p.n_dst = n_dst;
+    p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+    p.m_tiles = (uint32_t)((M + kBM - 1) / kBM);
+    p.n_tiles = (uint32_t)(N / kBN);
+    p.k_blocks = (uint32_t)(K / kBK);
+    p.Nt = (uint32_t)(N / 32);
+    p.status = status;
+    const bool use_pair = forced == 2 || (forced == 0 && M > 256);
+    if (use_pair) return launch_bfp8b_gemm_pair(tmap, p, sm_count, stream);
+
     static bool attr_done[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -448,15 +396,6 @@ cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, 
         if (e != cudaSuccess) return e;
         attr_done[dev] = true;
     }
-    Params p;
-    p.W = static_cast<const uint8_t *>(W);
-    p.C = static_cast<uint16_t *>(C);
-    p.M = M; p.N = N; p.K = K; p.ldc = ldc;
-    p.m_tiles = (uint32_t)((M + kBM - 1) / kBM);
-    p.n_tiles = (uint32_t)(N / kBN);
-    p.k_blocks = (uint32_t)(K / kBK);
-    p.Nt = (uint32_t)(N / 32);
-    p.status = status;
     uint32_t grid = p.m_tiles * p.n_tiles;
     if (grid > (uint32_t)sm_count) grid = (uint32_t)sm_count;
     if (decode_warps == 8)

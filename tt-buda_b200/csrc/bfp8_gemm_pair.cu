@@ -1,0 +1,418 @@
+// K7, CTA-pair variant: C[M,N] (bfloat16) = A[M,K] (bfloat16) @ W[K,N], W stored as Bfp8_b tiles.
+//
+// The single-CTA kernel is bound by the integer work of turning Bfp8_b blocks into bfloat16 operands:
+// every CTA decodes a 256-column slab of W for 256 rows of A.  Here two CTAs on neighbouring SMs
+// (a cluster of 2) issue tcgen05.mma.cta_group::2: one instruction covers M = 256 (128 rows in each
+// CTA's tensor memory) x N = 256, and the hardware reads the weight operand half from each CTA's
+// shared memory.  So each CTA decodes only 128 columns per k-block while its tensor core still sees
+// all 256: half the decode work per flop, and half the decoded bytes written to shared memory.
+//
+// Pair tile: 512 rows x 256 columns (two M = 256 accumulators, all 512 tensor-memory columns of both
+// SMs).  In each CTA (rank r = 0 leader, 1 peer):
+//   warp 8        producer: TMA-loads this CTA's two 128x64 activation boxes per k-block
+//   warps 10..17  decode this CTA's 128 weight columns (4 tile records x 2 k-tiles per k-block) into
+//                 the N-major swizzled operand stage, then arrive on the LEADER's full_b barrier
+//   warp 9        leader: one thread issues the MMAs for the pair and commits completion to both
+//                 CTAs' barriers (multicast commit).  peer: relays "my activations landed" to the leader
+//   warps 0-7     epilogue for this CTA's 2 x 128 rows (two warps per tensor-memory lane quadrant, half
+//                 of the columns each); both CTAs' epilogues release the accumulators on the leader's
+//                 acc_empty barrier
+// Every mbarrier wait is bounded; a wait that gives up raises the device status word, the CTA winds
+// down, its partner runs into its own limit, and both meet at the closing cluster barrier (tensor
+// memory is freed on every path).
+#include <cstdio>
+#include <cstdlib>
+
+#include "gemm_common.cuh"
+
+namespace buda {
+
+namespace gemm_pair {
+
+using namespace gemm;
+
+constexpr int kPairM = 512;        // rows of C per pair tile
+constexpr int kBN = 256;           // columns of C per pair tile
+constexpr int kHalfN = 128;        // weight columns decoded by one CTA
+constexpr int kBK = 64;            // k-block
+#ifndef PAIR_A_STAGES
+#define PAIR_A_STAGES 4
+#endif
+#ifndef PAIR_B_STAGES
+#define PAIR_B_STAGES 4
+#endif
+constexpr int kAStages = PAIR_A_STAGES;   // activation ring (per CTA: two 128x64 boxes per stage)
+constexpr int kBStages = PAIR_B_STAGES;   // decoded-weight ring (per CTA: 128 columns x 64 deep)
+constexpr int kABytes = 2 * 128 * kBK * 2;   // 32768
+constexpr int kBBytes = kHalfN * kBK * 2;    // 16384
+constexpr int kDecodeWarps = 8;
+#ifndef GEMM_PREFETCH
+#define GEMM_PREFETCH 3
+#endif
+constexpr int kPrefetch = GEMM_PREFETCH;   // k-blocks of raw weight records in flight per decode thread
+constexpr int kEpiWarps = 8;        // two per tensor-memory lane quadrant: each takes half of the columns
+constexpr int kProducerWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1, kFirstDecodeWarp = kEpiWarps + 2;
+constexpr int kThreads = 32 * (kEpiWarps + 1 + 1 + kDecodeWarps);
+constexpr int kTmemCols = 512;
+
+constexpr int kSmemA = 0;
+constexpr int kSmemB = kSmemA + kAStages * kABytes;
+constexpr int kSmemBar = kSmemB + kBStages * kBBytes;
+constexpr int kNumBars = 3 * kAStages + 2 * kBStages + 2;
+constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 16 + 1024;
+
+// instruction descriptor: D = F32, A = B = BF16, A K-major, B MN-major, N = 256, M = 256 (pair)
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) | ((uint32_t)(kBN >> 3) << 17) |
+                            ((uint32_t)(256 >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// arrive on the barrier at this shared-memory offset in BOTH CTAs of the pair once every MMA issued so far is complete
+__device__ __forceinline__ void umma_commit_pair(uint64_t *bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                     smem_u32(bar)),
+                 "h"((uint16_t)3)
+                 : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+bfp8b_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ Params p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    // identical carve-up in both CTAs: the MMA addresses the peer's operands by the leader's offsets
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *sA = smem + kSmemA;
+    uint8_t *sB = smem + kSmemB;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kSmemBar);
+    uint64_t *full_a = bars;                    // [kAStages] this CTA's activations landed (TMA bytes)
+    uint64_t *peer_a = full_a + kAStages;       // [kAStages] leader only: the peer's activations landed
+    uint64_t *empty_a = peer_a + kAStages;      // [kAStages] MMAs reading the activations are done (both CTAs)
+    uint64_t *full_b = empty_a + kAStages;      // [kBStages] leader only: both CTAs' decoded weights written
+    uint64_t *empty_b = full_b + kBStages;      // [kBStages] MMAs reading the decoded weights are done (both CTAs)
+    uint64_t *acc_full = empty_b + kBStages;    // accumulators complete (both CTAs)
+    uint64_t *acc_empty = acc_full + 1;         // leader only: both CTAs' epilogues drained the accumulators
+    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + kNumBars);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_ctarank();
+    const uint32_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const uint32_t total_tiles = p.m_tiles * p.n_tiles;
+
+    if (tid == 0) {
+        for (int s = 0; s < kAStages; s++) {
+            mbar_init(&full_a[s], 1);
+            mbar_init(&peer_a[s], 1);
+            mbar_init(&empty_a[s], 1);
+        }
+        for (int t = 0; t < kBStages; t++) {
+            mbar_init(&full_b[t], 2 * kDecodeWarps);
+            mbar_init(&empty_b[t], 1);
+        }
+        mbar_init(acc_full, 1);
+        mbar_init(acc_empty, 2 * kEpiWarps);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == kProducerWarp) {
+        // one warp of each CTA of the pair allocates all 512 tensor-memory columns of its SM
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    cluster_sync_all();  // both CTAs' barriers are initialised before anything arrives on them remotely
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == kProducerWarp) {
+        // ------------------------------------------------------------------ producer (both CTAs)
+        if (lane == 0) {
+            uint32_t i = 0;
+            bool ok = true;
+            for (uint32_t tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+                const uint32_t m_blk = tile % p.m_tiles;
+                const int row0 = (int)(m_blk * kPairM + rank * 128);
+                for (uint32_t kb = 0; kb < p.k_blocks; kb++, i++) {
+                    const int s = i % kAStages;
+                    const uint32_t ph = ((i / kAStages) & 1u) ^ 1u;
+                    if (!mbar_wait_bounded(&empty_a[s], ph, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT)) {
+                        ok = false;
+                        break;
+                    }
+#ifndef GEMM_EXP_NO_A
+                    mbar_arrive_expect_tx(&full_a[s], kABytes);
+                    tma_load_2d(sA + s * kABytes, &tmap_a, (int)(kb * kBK), row0, &full_a[s]);
+                    tma_load_2d(sA + s * kABytes + kABytes / 2, &tmap_a, (int)(kb * kBK), row0 + 256, &full_a[s]);
+#else
+                    mbar_arrive(&full_a[s]);
+#endif
+                }
+            }
+            const uint32_t back = i < (uint32_t)kAStages ? i : (uint32_t)kAStages;
+            if (!ok || *abort_flag) {
+                // let the copies already issued land before shared memory is released
+                for (uint32_t k = 1; k <= back; k++) {
+                    const uint32_t j = i - k;
+                    uint64_t t0 = global_timer_ns();
+                    while (!mbar_try_wait(&full_a[j % kAStages], (j / kAStages) & 1u) && global_timer_ns() - t0 < 100000000ull) {
+                    }
+                }
+            } else {
+                // the leader's last commits arrive on this CTA's barriers asynchronously: see them land before leaving
+                for (uint32_t k = 1; k <= back; k++) {
+                    const uint32_t j = i - k;
+                    if (!mbar_wait_bounded(&empty_a[j % kAStages], (j / kAStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT)) break;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == kMmaWarp) {
+        if (lane == 0 && rank == 0) {
+            // -------------------------------------------------------------- MMA issue (leader)
+            uint32_t i = 0, tile_iter = 0;
+            bool ok = true;
+            for (uint32_t tile = pair; tile < total_tiles && ok; tile += num_pairs, tile_iter++) {
+                if (tile_iter > 0) {  // both epilogues must have drained the previous tile's accumulators
+                    if (!mbar_wait_bounded_cluster(acc_empty, (tile_iter - 1) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT)) break;
+                    tc_fence_after();
+                }
+                for (uint32_t kb = 0; kb < p.k_blocks; kb++, i++) {
+                    const int s = i % kAStages, t = i % kBStages;
+                    if (!mbar_wait_bounded(&full_a[s], (i / kAStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT) ||
+                        !mbar_wait_bounded_cluster(&peer_a[s], (i / kAStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT) ||
+                        !mbar_wait_bounded_cluster(&full_b[t], (i / kBStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(sA + s * kABytes), b_addr = smem_u32(sB + t * kBBytes);
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+#pragma unroll
+                        for (int j = 0; j < kBK / 16; j++) {
+                            // A: K-major, 8-row groups 1024 B apart, 32 B per 16-deep k-step inside the swizzled row
+                            const uint64_t adesc = smem_desc(a_addr + h * (kABytes / 2) + j * 32, 16, 1024);
+                            // B (this CTA's 128 columns): 64-column atoms 1024 B apart, 8-deep k groups 2048 B apart
+                            const uint64_t bdesc = smem_desc(b_addr + j * 4096, 1024, 2048);
+#ifndef PAIR_EXP_NO_MMA
+                            umma_bf16_pair(tmem_base + h * kBN, adesc, bdesc, kIdesc, (kb > 0 || j > 0) ? 1u : 0u);
+#else
+                            (void)adesc; (void)bdesc;
+#endif
+                        }
+                    }
+                    umma_commit_pair(&empty_a[s]);
+                    umma_commit_pair(&empty_b[t]);
+                }
+                if (ok) umma_commit_pair(acc_full);
+            }
+        } else if (lane == 0) {
+            // -------------------------------------------------------------- relay (peer): activations landed
+            uint32_t i = 0;
+            bool ok = true;
+            for (uint32_t tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+                for (uint32_t kb = 0; kb < p.k_blocks; kb++, i++) {
+                    const int s = i % kAStages;
+                    if (!mbar_wait_bounded(&full_a[s], (i / kAStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_cluster(map_to_cta(smem_u32(&peer_a[s]), 0));
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp >= kFirstDecodeWarp) {
+        // ------------------------------------------------------------------ decode warps (both CTAs)
+        // 16 units of 32 blocks per k-block: 8 records (2 k-tiles x 4 n-tiles) x two halves of their 64 blocks.
+        constexpr int kUnits = 16 / kDecodeWarps;
+        const int dw = warp - kFirstDecodeWarp;
+        // Raw records go global -> registers kPrefetch k-blocks ahead of their decode (a fetch cursor walks the
+        // same (tile, k-block) sequence as the loop below), so the loop never waits for a load it just issued.
+        uint4 mq[kPrefetch][kUnits];
+        uint32_t eq[kPrefetch][kUnits];
+        uint32_t f_tile = pair, f_kb = 0;
+        auto fetch_into = [&](uint4 (&m)[kUnits], uint32_t (&e)[kUnits]) {
+            if (f_tile < total_tiles) {
+                const uint32_t n_blk = f_tile / p.m_tiles;
+#pragma unroll
+                for (int it = 0; it < kUnits; it++) {
+                    const int u = it * kDecodeWarps + dw;
+                    const int r = u >> 1;                           // record: k-tile r / 4, n-tile r % 4
+                    const int blk = (u & 1) * 32 + lane;            // block = face * 16 + face row
+                    const uint8_t *rec =
+                        p.W + ((uint64_t)(f_kb * 2 + (r >> 2)) * p.Nt + (uint64_t)n_blk * 8 + rank * 4 + (r & 3)) * kRecord;
+                    m[it] = __ldg(reinterpret_cast<const uint4 *>(rec + 64 + blk * 16));
+                    e[it] = __ldg(rec + blk);
+                }
+                if (++f_kb == p.k_blocks) {
+                    f_kb = 0;
+                    f_tile += num_pairs;
+                }
+            } else {
+#pragma unroll
+                for (int it = 0; it < kUnits; it++) {
+                    m[it] = make_uint4(0u, 0u, 0u, 0u);
+                    e[it] = 0u;
+                }
+            }
+        };
+#pragma unroll
+        for (int d = 0; d < kPrefetch; d++) fetch_into(mq[d], eq[d]);
+        uint32_t i = 0;
+        bool ok = true;
+        for (uint32_t tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+            for (uint32_t kb = 0; kb < p.k_blocks; kb++, i++) {
+                const int t = i % kBStages;
+                uint4 mant_cur[kUnits];
+                uint32_t exp_cur[kUnits];
+#pragma unroll
+                for (int it = 0; it < kUnits; it++) {
+                    mant_cur[it] = mq[0][it];
+                    exp_cur[it] = eq[0][it];
+                }
+#pragma unroll
+                for (int d = 0; d + 1 < kPrefetch; d++) {
+#pragma unroll
+                    for (int it = 0; it < kUnits; it++) {
+                        mq[d][it] = mq[d + 1][it];
+                        eq[d][it] = eq[d + 1][it];
+                    }
+                }
+                fetch_into(mq[kPrefetch - 1], eq[kPrefetch - 1]);
+                const bool got = mbar_wait_bounded(&empty_b[t], ((i / kBStages) & 1u) ^ 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT);
+                if (!__all_sync(0xffffffffu, got)) {  // the whole warp leaves together
+                    ok = false;
+                    break;
+                }
+                uint8_t *bst = sB + t * kBBytes;
+#ifdef PAIR_EXP_NO_DECODE
+                if (exp_cur[0] == 0x12345u) bst[lane] = (uint8_t)mant_cur[0].x;
+                if (false)
+#endif
+#pragma unroll
+                for (int it = 0; it < kUnits; it++) {
+                    const int u = it * kDecodeWarps + dw;
+                    const int r = u >> 1;
+                    const int blk = (u & 1) * 32 + lane;
+                    const int k_local = (r >> 2) * 32 + (blk >> 5) * 16 + (blk & 15);
+                    const int n_local = (r & 3) * 32 + ((blk >> 4) & 1) * 16;
+                    decode_block_to_operand<kHalfN / 64>(mant_cur[it], exp_cur[it], bst, k_local, n_local);
+                }
+                fence_async_smem();  // the tensor cores read shared memory through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&full_b[t]), 0));
+            }
+        }
+        if (ok && dw == 0 && lane == 0) {
+            // as in the producer: the last stage releases must have landed on this CTA's barriers
+            const uint32_t back = i < (uint32_t)kBStages ? i : (uint32_t)kBStages;
+            for (uint32_t k = 1; k <= back; k++) {
+                const uint32_t j = i - k;
+                if (!mbar_wait_bounded(&empty_b[j % kBStages], (j / kBStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT)) break;
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ epilogue warps (both CTAs)
+        // A warp reads the tensor-memory lanes of its quadrant (warp % 4); the two warps of a quadrant split the
+        // 256 columns of each accumulator.  Two 32-column loads are in flight before the first is waited for.
+        const int quad = warp & 3, col_half = warp >> 2;
+        uint32_t tile_iter = 0;
+        for (uint32_t tile = pair; tile < total_tiles; tile += num_pairs, tile_iter++) {
+            const uint32_t m_blk = tile % p.m_tiles, n_blk = tile / p.m_tiles;
+            const bool got = mbar_wait_bounded(acc_full, tile_iter & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT);
+            if (!__all_sync(0xffffffffu, got)) break;  // the whole warp leaves together
+            tc_fence_after();
+#pragma unroll 1
+            for (int h = 0; h < 2; h++) {
+                const int64_t row = (int64_t)m_blk * kPairM + h * 256 + rank * 128 + quad * 32 + lane;
+                const int64_t off = row * p.ldc + (int64_t)n_blk * kBN + col_half * (kBN / 2);
+                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(h * kBN + col_half * (kBN / 2));
+#pragma unroll 1
+                for (int c = 0; c < kBN / 2 / 64; c++) {
+                    uint32_t v0[32], v1[32];
+                    tmem_ld32_issue(taddr + c * 64, v0);
+                    tmem_ld32_issue(taddr + c * 64 + 32, v1);
+                    tmem_ld_wait();
+#ifdef PAIR_EXP_NO_STORE
+                    if (row < p.M && v0[0] == 0x7fc12345u)
+#else
+                    if (row < p.M)
+#endif
+                    {
+                        store_row32(v0, p.C, p.n_dst, off + c * 64);
+                        store_row32(v1, p.C, p.n_dst, off + c * 64 + 32);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(acc_empty), 0));
+        }
+    }
+
+    // every path ends here: neither CTA leaves while its partner may still touch its shared memory or barriers
+    tc_fence_before();
+    cluster_sync_all();
+    if (warp == kProducerWarp) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+}  // namespace gemm_pair
+
+// Launch of the CTA-pair kernel.  Same contract as the single-CTA launch; the caller has validated the shapes.
+cudaError_t launch_bfp8b_gemm_pair(const CUtensorMap &tmap, const gemm::Params &p_in, int sm_count, cudaStream_t stream)
+{
+    using namespace gemm_pair;
+    static bool attr_done[64] = {};
+    static int max_pairs[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev &= 63;
+    if (!attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(bfp8b_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return e;
+        // how many pairs the device can hold at once (SMs that cannot be paired inside their GPC stay idle)
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(sm_count & ~1), 1, 1);
+        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = kSmemBytes;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        e = cudaOccupancyMaxActiveClusters(&n, bfp8b_gemm_pair_kernel, &cfg);
+        if (e != cudaSuccess || n <= 0) {
+            (void)cudaGetLastError();
+            n = sm_count / 2;
+        }
+        max_pairs[dev] = n;
+        if (getenv("BUDA_GEMM_VERBOSE")) fprintf(stderr, "bfp8b gemm pair kernel: %d resident CTA pairs on %d SMs\n", n, sm_count);
+        attr_done[dev] = true;
+    }
+    gemm::Params p = p_in;
+    p.m_tiles = (uint32_t)((p.M + kPairM - 1) / kPairM);
+    p.n_tiles = (uint32_t)(p.N / kBN);
+    uint32_t pairs = p.m_tiles * p.n_tiles;
+    if (pairs > (uint32_t)max_pairs[dev]) pairs = (uint32_t)max_pairs[dev];
+    bfp8b_gemm_pair_kernel<<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap, p);
+    return cudaGetLastError();
+}
+
+}  // namespace buda

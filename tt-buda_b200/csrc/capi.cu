@@ -21,9 +21,11 @@ cudaError_t launch_dequantize(const int8_t *x, int64_t n, const float *scale, in
 cudaError_t launch_requantize(const int32_t *x, int64_t n, const float *scale_a, const float *scale_b, int64_t scale_len,
                               int64_t inner, float zp, int mode, float lo, float hi, int8_t *out, int sm_count,
                               cudaStream_t stream);
-cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W, int64_t N, void *C,
-                              int64_t ldc, int sm_count, cudaStream_t stream, unsigned int *status, char *err,
+cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W, int64_t N, void *const *C,
+                              int n_dst, int64_t ldc, int sm_count, cudaStream_t stream, unsigned int *status, char *err,
                               size_t err_len);
+
+int gemm_kernel_choice(int which);
 
 // One status word per device that loads the library; kernels get its device address.
 __device__ unsigned int g_device_status = 0;
@@ -855,17 +857,60 @@ int buda_requantize(const int32_t *x, int64_t n, const float *inp_scale, const f
     return BUDA_SUCCESS;
 }
 
-int buda_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N, void *C, int64_t ldc,
-                    void *stream)
+int buda_bfp8b_gemm_scatter(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N, void *const *C_dsts,
+                            int n_dst, int64_t ldc, void *stream)
 {
     DevCtx *ctx;
     if (int rc = get_ctx(&ctx)) return rc;
-    if (!A || !W_tiles || !C) return fail(BUDA_RUNTIME_ERROR, "null matrix pointer");
+    if (!A || !W_tiles || !C_dsts) return fail(BUDA_RUNTIME_ERROR, "null matrix pointer");
+    for (int d = 0; d < n_dst && d < 8; d++)
+        if (!C_dsts[d]) return fail(BUDA_RUNTIME_ERROR, "null destination %d", d);
     char msg[256] = "";
-    cudaError_t e = launch_bfp8b_gemm(A, M, K, lda, W_tiles, N, C, ldc, ctx->sm_count, (cudaStream_t)stream, ctx->status,
-                                      msg, sizeof(msg));
+    cudaError_t e = launch_bfp8b_gemm(A, M, K, lda, W_tiles, N, C_dsts, n_dst, ldc, ctx->sm_count, (cudaStream_t)stream,
+                                      ctx->status, msg, sizeof(msg));
     if (e != cudaSuccess) return msg[0] ? fail(BUDA_RUNTIME_ERROR, "%s", msg) : cuda_fail(e, "gemm launch failed");
     g_launches.fetch_add(1, std::memory_order_relaxed);
+    return BUDA_SUCCESS;
+}
+
+int buda_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N, void *C, int64_t ldc,
+                    void *stream)
+{
+    if (!C) return fail(BUDA_RUNTIME_ERROR, "null matrix pointer");
+    void *dst[1] = {C};
+    return buda_bfp8b_gemm_scatter(A, M, K, lda, W_tiles, N, dst, 1, ldc, stream);
+}
+
+int buda_gemm_select_kernel(int which) { return gemm_kernel_choice(which); }
+
+int buda_ipc_export(const void *dev_ptr, unsigned char handle_out[64])
+{
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    if (!dev_ptr || !handle_out) return fail(BUDA_RUNTIME_ERROR, "null argument");
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, const_cast<void *>(dev_ptr));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaIpcGetMemHandle failed");
+    memcpy(handle_out, &h, 64);
+    return BUDA_SUCCESS;
+}
+
+int buda_ipc_open(const unsigned char handle[64], void **dev_ptr_out)
+{
+    if (!handle || !dev_ptr_out) return fail(BUDA_RUNTIME_ERROR, "null argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    void *ptr = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaIpcOpenMemHandle failed");
+    *dev_ptr_out = ptr;
+    return BUDA_SUCCESS;
+}
+
+int buda_ipc_close(void *dev_ptr)
+{
+    if (!dev_ptr) return BUDA_SUCCESS;
+    cudaError_t e = cudaIpcCloseMemHandle(dev_ptr);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaIpcCloseMemHandle failed");
     return BUDA_SUCCESS;
 }
 

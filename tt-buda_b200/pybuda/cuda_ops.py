@@ -212,3 +212,74 @@ def bfp8b_matmul(a, w_image, n, out=None):
         check(_cabi.lib.buda_bfp8b_gemm(a.data_ptr(), m, k, a.stride(0), w_image.data_ptr(), n, out.data_ptr(),
                                         out.stride(0), _stream()))
     return out
+
+
+def select_gemm_kernel(which):
+    """'auto' (default), 'single' or 'pair': which tensor-core kernel the matmul launches.  Returns the previous choice."""
+    names = ["auto", "single", "pair"]
+    return names[_cabi.lib.buda_gemm_select_kernel(names.index(which))]
+
+
+def bfp8b_matmul_scatter(a, w_image, n, dst_ptrs, ldc):
+    """The same product stored to every device address in `dst_ptrs` (this device's first; the others
+    usually peers' copies of the output mapped with SharedDeviceMatrix), row stride `ldc` elements."""
+    _need_cuda(a, w_image)
+    assert a.dtype == torch.bfloat16 and a.dim() == 2 and a.stride(1) == 1
+    m, k = a.shape
+    with torch.cuda.device(a.device):
+        check(_cabi.lib.buda_bfp8b_gemm_scatter(a.data_ptr(), m, k, a.stride(0), w_image.data_ptr(), n,
+                                                _cabi.ptr_array(dst_ptrs), len(dst_ptrs), ldc, _stream()))
+
+
+class _RawCudaBuffer:
+    """Lets torch view memory it did not allocate (buda_malloc / a mapped peer allocation)."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
+
+
+class SharedDeviceMatrix:
+    """A [rows, cols] bfloat16 matrix in plain device memory that the other processes of the box can map:
+    `handle()` is the 64-byte token to send them, `open_peer(handle)` maps one of theirs here."""
+
+    def __init__(self, rows, cols, device=None):
+        import ctypes
+
+        self.rows, self.cols = int(rows), int(cols)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.nbytes = self.rows * self.cols * 2
+        ptr = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            check(_cabi.lib.buda_malloc(ctypes.byref(ptr), self.nbytes))
+        self.ptr = ptr.value
+        self._peers = []
+        self.tensor = torch.as_tensor(_RawCudaBuffer(self.ptr, self.nbytes), device=self.device).view(torch.bfloat16).view(
+            self.rows, self.cols)
+
+    def handle(self) -> bytes:
+        import ctypes
+
+        buf = ctypes.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            check(_cabi.lib.buda_ipc_export(self.ptr, buf))
+        return buf.raw
+
+    def open_peer(self, handle: bytes) -> int:
+        import ctypes
+
+        ptr = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            check(_cabi.lib.buda_ipc_open(ctypes.create_string_buffer(handle, 64), ctypes.byref(ptr)))
+        self._peers.append(ptr.value)
+        return ptr.value
+
+    def close(self):
+        with torch.cuda.device(self.device):
+            for p in self._peers:
+                _cabi.lib.buda_ipc_close(p)
+            self._peers = []
+            if self.ptr:
+                self.tensor = None
+                _cabi.lib.buda_free(self.ptr)
+                self.ptr = None
+

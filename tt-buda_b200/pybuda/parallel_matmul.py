@@ -2,9 +2,15 @@
 
 Rank r holds columns [r*N/g, (r+1)*N/g) of the weight as a Bfp8_b queue image and all of the
 activations; it computes its [M, N/g] slice with the tcgen05 kernel, and the slices are exchanged
-with an NCCL all-gather over NVLink.  At 8 GPUs the gather of the 256 MiB output takes longer than
-the 1/8-size matmul, so the rows are cut into bands: while band k is gathered on a side stream,
-band k+1 is computed.
+in one of two ways:
+
+  * fused (`enable_fused_scatter`, the fast path on GPUs): every rank keeps the full [M, N] output in
+    device memory its peers have mapped, and the matmul kernel's epilogue stores each finished tile
+    into its own copy AND straight into every peer's copy over NVLink, while the tensor cores work on
+    the next tile.  No all-gather, no staging, no permute pass: a barrier after the kernel is the only
+    host-visible exchange step.
+  * library all-gather (the baseline, and what CPU ranks test): the rows are cut into bands and band k
+    is gathered with NCCL on a side stream while band k+1 is computed.
 """
 from typing import Callable, Optional
 
@@ -31,6 +37,50 @@ class ColumnParallelBfp8Matmul:
             local_matmul = lambda a, w, nl, out: cuda_ops.bfp8b_matmul(a, w, nl, out=out)
         self._mm = local_matmul
         self.weight_image = None
+        self._shared = None        # SharedDeviceMatrix: this rank's full output, mapped by the peers
+        self._dst_ptrs = None
+
+    def enable_fused_scatter(self, m: int):
+        """Allocate this rank's full [m, n] output where the peers can map it, exchange the handles and map
+        theirs.  Collective: every rank of the group calls it with the same m."""
+        from . import cuda_ops
+
+        self.disable_fused_scatter()
+        self._shared = cuda_ops.SharedDeviceMatrix(m, self.n)
+        handles = [None] * self.world
+        if self.world > 1:
+            dist.all_gather_object(handles, self._shared.handle(), group=self.group)
+        col_bytes = self.col0 * 2
+        ptrs = [self._shared.ptr + col_bytes]
+        for r in range(self.world):
+            if r != self.rank:
+                ptrs.append(self._shared.open_peer(handles[r]) + col_bytes)
+        self._dst_ptrs = ptrs
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        return self._shared.tensor
+
+    def disable_fused_scatter(self):
+        if self._shared is not None:
+            torch.cuda.synchronize()
+            if self.world > 1:
+                dist.barrier(group=self.group)   # nobody unmaps while a peer may still be storing
+            self._shared.close()
+            self._shared, self._dst_ptrs = None, None
+
+    def fused(self, a: torch.Tensor, sync: bool = True) -> torch.Tensor:
+        """One kernel: this rank's column block, written into every rank's output.  With sync (default) a
+        barrier follows, after which the returned [m, n] matrix is complete on every rank."""
+        from . import cuda_ops
+
+        if self._shared is None or a.shape[0] != self._shared.rows:
+            raise RuntimeError("enable_fused_scatter(m) first, with m = a.shape[0]")
+        if self.weight_image is None:
+            raise RuntimeError("load_weight_shard() first")
+        cuda_ops.bfp8b_matmul_scatter(a, self.weight_image, self.n_local, self._dst_ptrs, self.n)
+        if sync and self.world > 1:
+            dist.barrier(group=self.group)
+        return self._shared.tensor
 
     def load_weight_shard(self, w_full_or_shard: torch.Tensor, already_sharded: bool = False):
         """Pack this rank's columns of a [K, N] float weight to a Bfp8_b queue image on its device."""
