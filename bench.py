@@ -37,6 +37,15 @@ IMAGE_BYTES = 17825792
 WORKLOAD = "64 x fp32 [1,1,4096,4096] N(0,1), 1% x1e3 outliers, 0.5% zeros -> Bfp8_b tiles"
 
 
+def tensor_peak_tflops():
+    """Measured dense bf16 burst peak of this pool's B200s, else the stated fallback."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f).get("bf16_tflops", 1590.0))
+    return 1590.0
+
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -143,6 +152,12 @@ def profile_one(torch, cuda_ops, dev, name, reps=6):
         wimg = cuda_ops.tilize_pack(torch.randn(1, 1, K, N, device=dev) * 0.02, cuda_ops.DF.Bfp8_b)
         c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
         fn, work, unit = (lambda: cuda_ops.bfp8b_matmul(a, wimg, N, out=c)), 2.0 * M * N * K / 1e12, "TFLOP/s"
+    elif name == "i8gemm":
+        M, K, N = 8192, 4096, 16384
+        a = torch.randint(-128, 128, (M, K), device=dev, dtype=torch.int8)
+        wimg = cuda_ops.tilize_pack(torch.randint(-128, 128, (1, 1, K, N), device=dev, dtype=torch.int8), cuda_ops.DF.Int8)
+        sc = torch.rand(N, device=dev) * 2e-5
+        fn, work, unit = (lambda: cuda_ops.i8_matmul(a, wimg, N, scale=sc, zero_point=0.0, out="int8")), 2.0 * M * N * K / 1e12, "TOP/s"
     elif name == "unpack":
         xs = [torch.randn(SHAPE, device=dev) for _ in range(8)]
         imgs = cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b)
@@ -223,7 +238,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (for profiler captures)")
     ap.add_argument("--tensors", type=int, default=N_TENSORS,
                     help="tensors per GPU batch; anything but 64 is a reduced case for profiler captures")
-    ap.add_argument("--profile-kernel", default=None, choices=["gemm", "unpack", "quantize", "dequantize", "requantize"],
+    ap.add_argument("--profile-kernel", default=None, choices=["gemm", "i8gemm", "unpack", "quantize", "dequantize", "requantize"],
                     help="run only this secondary kernel a few times and exit (small, self-ending case for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -405,9 +420,31 @@ def main():
                 return max_over_ranks(e0.elapsed_time(e1) / 5)
 
             ms_local, ms_gather = run(False), run(True)
+
+            # the exchange fused into the kernel: the epilogue stores each tile into every rank's output
+            # through peer-mapped memory (timed with the closing barrier that makes the result readable)
+            op.enable_fused_scatter(M)
+            for _ in range(2):
+                op.fused(a)
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(5):
+                op.fused(a, sync=False)
+            e1.record()
+            barrier()
+            ms_fused = max_over_ranks(e0.elapsed_time(e1) / 5)
+            op.disable_fused_scatter()
+            # what bounds the fused kernel: the tensor cores, or this rank's stores leaving over NVLink
+            flops_rank = 2.0 * M * (N / world) * K
+            link_bytes = M * (N / world) * 2 * (world - 1)
+            t_floor = max(flops_rank / (tensor_peak_tflops() * 1e12), link_bytes / 770e9)
             extras["column_parallel_gemm_8192x4096x16384"] = {
                 "TFLOP/s_without_gather": round(2.0 * M * N * K / (ms_local * 1e-3) / 1e12, 1), "ms_without_gather": round(ms_local, 4),
                 "TFLOP/s_with_all_gather": round(2.0 * M * N * K / (ms_gather * 1e-3) / 1e12, 1), "ms_with_all_gather": round(ms_gather, 4),
+                "TFLOP/s_fused_scatter": round(2.0 * M * N * K / (ms_fused * 1e-3) / 1e12, 1), "ms_fused_scatter": round(ms_fused, 4),
+                "fused_scatter_floor_ms": round(t_floor * 1e3, 4), "fused_scatter_frac_of_floor": round(t_floor * 1e3 / ms_fused, 3),
+                "floor": "max(flops / measured bf16 burst peak, bytes leaving this GPU / 770 GB/s measured peer copy)",
                 "bands": 8}
             del a, cfull
         except Exception as exc:

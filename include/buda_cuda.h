@@ -242,6 +242,24 @@ int buda_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void
 int buda_bfp8b_gemm_scatter(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N,
                             void *const *C_dsts, int n_dst, int64_t ldc, void *stream);
 
+/* acc[M,N] (int32) = A[M,K] (int8, row-major, row stride lda bytes) @ W[K,N], W the tilized image of an
+ * Int8 queue (default geometry: 32x32 tiles row-major over [K/32][N/32], four 16x16 faces of 16-byte
+ * rows, 1024 bytes per tile, no header) -- what buda_tilize_pack writes for a [1,1,K,N] int8 tensor.
+ * The epilogue finishes the reference's matmul -> requantization chain in the same kernel
+ * (pybuda/csrc/graph_lib/python_bindings.cpp:655-676; an int8 matmul yields int32,
+ * pybuda/pybuda/op/eval/common.py:50-65):
+ *   BUDA_I8_OUT_INT32        C int32  = acc
+ *   BUDA_I8_OUT_REQUANT_I8   C int8   = clamp(round(float(acc) * scale + zero_point), -128, 127)
+ *                                        (pybuda/pybuda/op/eval/buda/quantize.py:42-53)
+ *   BUDA_I8_OUT_DEQUANT_F32  C float32 = (float(acc) - zero_point) * scale   (quantize.py:35-40)
+ * scale: device pointer, scale_len == 1 (per tensor) or == N (per output column).  ldc in elements of
+ * the output type.  Needs K % 128 == 0, N % 256 == 0, 16-byte aligned pointers and rows; any M. */
+#define BUDA_I8_OUT_INT32 0
+#define BUDA_I8_OUT_REQUANT_I8 1
+#define BUDA_I8_OUT_DEQUANT_F32 2
+int buda_i8_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N, const float *scale,
+                 int64_t scale_len, float zero_point, int out_mode, void *C, int64_t ldc, void *stream);
+
 /* Which tensor-core kernel buda_bfp8b_gemm* launches: 0 = automatic (CTA-pair kernel for M > 256, single-CTA
  * kernel otherwise), 1 = single-CTA, 2 = CTA pair.  Process-wide; a negative value only reads.  Returns the
  * previous setting.  Results are identical bit for bit; the knob exists for measurement. */

@@ -589,3 +589,52 @@ int ref_bfp8b_matmul(const uint16_t *A, long M, long K, const void *W, const ref
     __builtin_free(Wf);
     return 0;
 }
+
+/* ---------------------------------------------------------------------------------------------
+ * int8 matmul with the requantisation / dequantisation that follows it in the reference
+ * (csrc/graph_lib/python_bindings.cpp:655-676: a matmul with the "requant" attribute is evaluated,
+ * then "requantization" is applied to its result; op/eval/common.py:50-65: an int8 matmul yields int32).
+ * A: int8 row-major [M,K]; W: Int8 queue image of a [K,N] tensor in geometry g; acc in int32 (exact;
+ * the reference's float32 torch.matmul gives the same integers while partial sums stay below 2^24).
+ *   mode 0  out int32  = acc
+ *   mode 1  out int8   = clamp(round(float(acc) * scale + zp), -128, 127)   op/eval/buda/quantize.py:42-53
+ *   mode 2  out float  = (float(acc) - zp) * scale                            op/eval/buda/quantize.py:35-40
+ * scale: 1 value or N values (per output column).
+ * ------------------------------------------------------------------------------------------- */
+int ref_i8_matmul(const int8_t *A, long M, long K, const void *W, const ref_geom *g, long N, const float *scale, long scale_len,
+                  float zp, int mode, void *out)
+{
+    uint32_t shape[4] = {1, 1, (uint32_t)K, (uint32_t)N};
+    uint32_t strides[4] = {(uint32_t)(K * N), (uint32_t)(K * N), (uint32_t)N, 1};
+    int8_t *Wi = (int8_t *)__builtin_malloc((size_t)K * N);
+    if (!Wi) return 1;
+    if (ref_unpack_untilize(W, DF_Int8, 0, g, Wi, DF_Int8, shape, strides)) { __builtin_free(Wi); return 1; }
+#pragma omp parallel for schedule(static)
+    for (long i = 0; i < M; i++) {
+        int32_t *acc = (int32_t *)__builtin_malloc((size_t)N * 4);
+        for (long j = 0; j < N; j++) acc[j] = 0;
+        for (long k = 0; k < K; k++) {
+            const int32_t a = A[i * K + k];
+            const int8_t *wr = Wi + k * N;
+            for (long j = 0; j < N; j++) acc[j] += a * (int32_t)wr[j];
+        }
+        for (long j = 0; j < N; j++) {
+            const float sc = scale ? scale[scale_len == 1 ? 0 : j] : 1.0f;
+            if (mode == 0) {
+                ((int32_t *)out)[i * N + j] = acc[j];
+            } else if (mode == 1) {
+                float f = (float)acc[j] * sc;
+                f = f + zp;
+                f = nearbyintf(f);
+                f = f < -128.0f ? -128.0f : (f > 127.0f ? 127.0f : f);
+                ((int8_t *)out)[i * N + j] = (f != f) ? 0 : (int8_t)f;
+            } else {
+                float f = (float)acc[j] - zp;
+                ((float *)out)[i * N + j] = f * sc;
+            }
+        }
+        __builtin_free(acc);
+    }
+    __builtin_free(Wi);
+    return 0;
+}

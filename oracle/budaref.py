@@ -97,6 +97,9 @@ def lib():
                                      ctypes.c_float, vp]
         L.ref_bfp8b_matmul.restype = i32
         L.ref_bfp8b_matmul.argtypes = [vp, ctypes.c_long, ctypes.c_long, vp, gp, ctypes.c_long, vp]
+        L.ref_i8_matmul.restype = i32
+        L.ref_i8_matmul.argtypes = [vp, ctypes.c_long, ctypes.c_long, vp, gp, ctypes.c_long, vp, ctypes.c_long, ctypes.c_float,
+                                    i32, vp]
         _lib = L
     return _lib
 
@@ -265,5 +268,22 @@ def bfp8b_matmul(a_bf16_bits, w_img, K, N, geom=None):
     w = np.ascontiguousarray(w_img, dtype=np.uint8)
     out = np.zeros((M, N), dtype=np.float32)
     rc = lib().ref_bfp8b_matmul(a.ctypes.data, M, K, w.ctypes.data, ctypes.byref(geom), N, out.ctypes.data)
+    assert rc == 0
+    return out
+
+
+def i8_matmul(a_i8, w_img, K, N, scale=None, zp=0.0, mode=0, geom=None):
+    """int8 [M,K] @ Int8 queue image of [K,N]: mode 0 int32 accumulators, 1 requantised int8, 2 dequantised float32."""
+    a = np.ascontiguousarray(a_i8, dtype=np.int8)
+    M = a.shape[0]
+    assert a.shape[1] == K
+    if geom is None:
+        geom = Geom.for_shape([1, 1, K, N])
+    w = np.ascontiguousarray(w_img, dtype=np.uint8)
+    out = np.zeros((M, N), dtype=[np.int32, np.int8, np.float32][mode])
+    sc = None if scale is None else np.ascontiguousarray(scale, dtype=np.float32).reshape(-1)
+    rc = lib().ref_i8_matmul(a.ctypes.data, M, K, w.ctypes.data, ctypes.byref(geom), N,
+                             None if sc is None else sc.ctypes.data, 0 if sc is None else sc.size, ctypes.c_float(zp), mode,
+                             out.ctypes.data)
     assert rc == 0
     return out

@@ -200,3 +200,77 @@ def test_config4_full_size(ops, oracle, kernel):
     wd_cpu = torch.from_numpy(oracle.unpack_untilize(oracle.tilize_pack(w.numpy(), oracle.Bfp8_b), oracle.Bfp8_b, (1, 1, K, N)))[0, 0]
     ref_rows = a[rows.cuda()].cpu().float() @ wd_cpu
     _check(c[rows.cuda()].cpu(), ref_rows)
+
+
+# ------------------------------------------------------------------------------------------------
+# int8 matmul with the requantisation / dequantisation epilogue (bit-exact: integer accumulation, then the
+# golden evaluation's float operations one by one)
+# ------------------------------------------------------------------------------------------------
+def _i8_operands(ops, oracle, M, K, N, seed):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8)
+    w = torch.randint(-128, 128, (K, N), generator=g, dtype=torch.int8)
+    img = ops.tilize_pack(w.reshape(1, 1, K, N).cuda(), ops.DF.Int8)
+    ref_img = oracle.tilize_pack(w.reshape(1, 1, K, N).numpy(), oracle.Int8)
+    assert np.array_equal(img.cpu().numpy(), ref_img)
+    return a, w, img
+
+
+@pytest.mark.parametrize("M,K,N", [(512, 128, 256), (128, 256, 256), (700, 384, 512), (1024, 1024, 1024)])
+def test_i8_matmul_accumulators_exact(ops, oracle, M, K, N):
+    a, w, img = _i8_operands(ops, oracle, M, K, N, seed=M + K + N)
+    c = ops.i8_matmul(a.cuda(), img, N).cpu()
+    want = a.int() @ w.int()
+    assert torch.equal(c, want)
+    if M * K * N <= 512 * 384 * 512:
+        assert np.array_equal(c.numpy(), oracle.i8_matmul(a.numpy(), img.cpu().numpy(), K, N))
+    rc, st = ops._cabi.device_status()
+    assert rc == 0 and st == 0
+
+
+@pytest.mark.parametrize("per_column", [False, True])
+def test_i8_matmul_requant_and_dequant_epilogues(ops, oracle, per_column):
+    M, K, N = 640, 256, 512
+    a, w, img = _i8_operands(ops, oracle, M, K, N, seed=77)
+    g = torch.Generator().manual_seed(78)
+    scale = (torch.rand(N if per_column else 1, generator=g) * (1e-3 - 1e-5) + 1e-5)
+    acc = a.int() @ w.int()
+    # the golden chain: matmul (int32) then requantization / dequantization of its result
+    zp = 3.0
+    want_q = torch.clamp(torch.round(acc.float() * scale + zp), -128, 127).to(torch.int8)
+    got_q = ops.i8_matmul(a.cuda(), img, N, scale=scale, zero_point=zp, out="int8").cpu()
+    assert torch.equal(got_q, want_q)
+    assert got_q.min() == -128 and got_q.max() == 127 and (got_q.abs() < 100).any()     # saturation and interior both exercised
+    want_f = (acc.float() - zp) * scale
+    got_f = ops.i8_matmul(a.cuda(), img, N, scale=scale, zero_point=zp, out="float32").cpu()
+    assert torch.equal(got_f, want_f)
+    assert np.array_equal(got_q.numpy(), oracle.i8_matmul(a.numpy(), img.cpu().numpy(), K, N, scale.numpy(), zp, 1))
+    assert np.array_equal(got_f.numpy(), oracle.i8_matmul(a.numpy(), img.cpu().numpy(), K, N, scale.numpy(), zp, 2))
+
+
+def test_i8_matmul_full_size_against_float_matmul(ops):
+    # 8192 x 4096 x 16384: partial sums stay far below 2^24, so a binary32 matmul of the same integers is exact
+    M, K, N = 8192, 4096, 16384
+    g = torch.Generator().manual_seed(5)
+    a = torch.randint(-128, 128, (M, K), generator=g, dtype=torch.int8).cuda()
+    w = torch.randint(-128, 128, (K, N), generator=g, dtype=torch.int8).cuda()
+    img = ops.tilize_pack(w.reshape(1, 1, K, N), ops.DF.Int8)
+    c = ops.i8_matmul(a, img, N)
+    rows = torch.arange(0, M, 61, device="cuda")
+    want = (a[rows].float() @ w.float()).int()
+    assert torch.equal(c[rows], want)
+    scale = torch.rand(N, generator=g).cuda() * 2e-5
+    q = ops.i8_matmul(a, img, N, scale=scale, zero_point=-2.0, out="int8")
+    want_q = torch.clamp(torch.round(want.float() * scale - 2.0), -128, 127).to(torch.int8)
+    assert torch.equal(q[rows], want_q)
+
+
+def test_i8_matmul_refuses_bad_arguments(ops):
+    a = torch.zeros(128, 96, dtype=torch.int8, device="cuda")
+    img = torch.zeros(3 * 8 * 1024, dtype=torch.uint8, device="cuda")
+    with pytest.raises(ops._cabi.BudaError, match="K % 128"):
+        ops.i8_matmul(a, img, 256)
+    a = torch.zeros(128, 128, dtype=torch.int8, device="cuda")
+    img = torch.zeros(4 * 8 * 1024, dtype=torch.uint8, device="cuda")
+    with pytest.raises(ops._cabi.BudaError, match="scale"):
+        ops.i8_matmul(a, img, 256, scale=torch.ones(7), out="int8")

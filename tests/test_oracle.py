@@ -8,6 +8,7 @@ import struct
 
 import numpy as np
 import pytest
+import torch
 
 
 # ------------------------------------------------------------------------------------------------
@@ -316,3 +317,23 @@ def test_bfp_a_tilize_round_trip(oracle):
         y32 = R.unpack_untilize(img, df, x.shape)
         assert np.array_equal(y16.astype(np.float32), y32)          # decoded values are exact in binary16
         assert np.array_equal(R.tilize_pack(y16, df), img)           # idempotent
+
+
+def test_i8_matmul_oracle_matches_the_golden_chain(oracle):
+    """int8 matmul -> int32 (op/eval/common.py:50-65), then requantization / dequantization of the result
+    (csrc/graph_lib/python_bindings.cpp:655-676, op/eval/buda/quantize.py:35-53), against torch."""
+    g = torch.Generator().manual_seed(9)
+    a = torch.randint(-128, 128, (96, 128), generator=g, dtype=torch.int8)
+    w = torch.randint(-128, 128, (128, 256), generator=g, dtype=torch.int8)
+    img = oracle.tilize_pack(w.reshape(1, 1, 128, 256).numpy(), oracle.Int8)
+    assert img.size == 4 * 8 * 1024                      # 32 Int8 tiles of 1024 bytes, no exponent sections
+    acc = a.int() @ w.int()
+    # the reference evaluates the matmul in float32: identical while the sums stay below 2^24
+    assert torch.equal((a.float() @ w.float()).to(torch.int32), acc)
+    assert np.array_equal(oracle.i8_matmul(a.numpy(), img, 128, 256), acc.numpy())
+    for scale in (torch.tensor([3e-4]), torch.rand(256, generator=g) * 1e-3 + 1e-5):
+        want_q = torch.clamp(torch.round(acc.float() * scale + 3.0), -128, 127).to(torch.int8)
+        assert np.array_equal(oracle.i8_matmul(a.numpy(), img, 128, 256, scale.numpy(), 3.0, 1), want_q.numpy())
+        want_f = (acc.float() - 3.0) * scale
+        assert np.array_equal(oracle.i8_matmul(a.numpy(), img, 128, 256, scale.numpy(), 3.0, 2), want_f.numpy())
+

@@ -26,6 +26,9 @@ cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, 
                               size_t err_len);
 
 int gemm_kernel_choice(int which);
+cudaError_t launch_i8_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W, int64_t N, const float *scale,
+                           int64_t scale_len, float zero_point, int out_mode, void *C, int64_t ldc, int sm_count, cudaStream_t stream,
+                           unsigned int *status, char *err, size_t err_len);
 
 // One status word per device that loads the library; kernels get its device address.
 __device__ unsigned int g_device_status = 0;
@@ -879,6 +882,20 @@ int buda_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void
     if (!C) return fail(BUDA_RUNTIME_ERROR, "null matrix pointer");
     void *dst[1] = {C};
     return buda_bfp8b_gemm_scatter(A, M, K, lda, W_tiles, N, dst, 1, ldc, stream);
+}
+
+int buda_i8_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N, const float *scale,
+                 int64_t scale_len, float zero_point, int out_mode, void *C, int64_t ldc, void *stream)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    if (!A || !W_tiles || !C) return fail(BUDA_RUNTIME_ERROR, "null matrix pointer");
+    char msg[256] = "";
+    cudaError_t e = launch_i8_gemm(A, M, K, lda, W_tiles, N, scale, scale_len, zero_point, out_mode, C, ldc, ctx->sm_count,
+                                   (cudaStream_t)stream, ctx->status, msg, sizeof(msg));
+    if (e != cudaSuccess) return msg[0] ? fail(BUDA_RUNTIME_ERROR, "%s", msg) : cuda_fail(e, "int8 gemm launch failed");
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return BUDA_SUCCESS;
 }
 
 int buda_gemm_select_kernel(int which) { return gemm_kernel_choice(which); }

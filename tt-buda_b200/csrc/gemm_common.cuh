@@ -209,14 +209,73 @@ __device__ __forceinline__ void store_row32(const uint32_t (&v)[32], uint16_t *c
     }
 }
 
+struct Params;
+__device__ __forceinline__ void store_row32_i8(const uint32_t (&v)[32], const Params &p, int64_t elem_offset, int col);
+
 struct Params {
-    const uint8_t *W;         // Bfp8_b image: record (kt, nt) at (kt * Nt + nt) * 1088
-    uint16_t *C[kMaxDst];     // bfloat16 destinations (this device first, then peers), row stride ldc
+    const uint8_t *W;         // weight image: record (kt, nt) at (kt * Nt + nt) * record bytes
+    uint16_t *C[kMaxDst];     // destinations (this device first, then peers), row stride ldc ELEMENTS of the output type
     int n_dst;
     int64_t M, N, K, ldc;
     uint32_t m_tiles, n_tiles, k_blocks, Nt;
     unsigned int *status;
+    // int8 kind only: what the epilogue does with the int32 accumulators
+    int out_mode;             // BUDA_I8_OUT_*
+    const float *scale;       // per column (scale_len == N) or one value (scale_len == 1); unused for int32 output
+    int64_t scale_len;
+    float zero_point, lo, hi;
 };
+
+// Epilogue of the int8 matmul for 32 consecutive columns of one row (first column `col`): the int32
+// accumulators as they are, requantised to int8, or dequantised to float32.  The arithmetic is the golden
+// evaluation's, operation by operation (separate multiply and add, round half to even, clamp, cast):
+//   requantise  clamp(round(float(acc) * scale + zero_point), lo, hi)      pybuda/pybuda/op/eval/buda/quantize.py:42-53
+//   dequantise  (float(acc) - zero_point) * scale                            pybuda/pybuda/op/eval/buda/quantize.py:35-40
+__device__ __forceinline__ void store_row32_i8(const uint32_t (&v)[32], const Params &p, int64_t elem_offset, int col)
+{
+    if (p.out_mode == BUDA_I8_OUT_INT32) {
+        uint32_t *out = reinterpret_cast<uint32_t *>(p.C[0]) + elem_offset;
+#pragma unroll
+        for (int q = 0; q < 8; q++)
+            reinterpret_cast<uint4 *>(out)[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        return;
+    }
+    const bool per_col = p.scale_len != 1;
+    const float s0 = __ldg(p.scale);
+    const float4 *scv = reinterpret_cast<const float4 *>(p.scale + (per_col ? col : 0));
+    if (p.out_mode == BUDA_I8_OUT_DEQUANT_F32) {
+        float *out = reinterpret_cast<float *>(p.C[0]) + elem_offset;
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            const float4 sc = per_col ? __ldg(scv + q) : make_float4(s0, s0, s0, s0);
+            float4 f;
+            f.x = __fmul_rn(__fsub_rn(__int2float_rn((int)v[4 * q]), p.zero_point), sc.x);
+            f.y = __fmul_rn(__fsub_rn(__int2float_rn((int)v[4 * q + 1]), p.zero_point), sc.y);
+            f.z = __fmul_rn(__fsub_rn(__int2float_rn((int)v[4 * q + 2]), p.zero_point), sc.z);
+            f.w = __fmul_rn(__fsub_rn(__int2float_rn((int)v[4 * q + 3]), p.zero_point), sc.w);
+            reinterpret_cast<float4 *>(out)[q] = f;
+        }
+        return;
+    }
+    uint32_t packed[8];
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+        const float4 sc = per_col ? __ldg(scv + q) : make_float4(s0, s0, s0, s0);
+        const float s4[4] = {sc.x, sc.y, sc.z, sc.w};
+        uint32_t w = 0;
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            float f = __fadd_rn(__fmul_rn(__int2float_rn((int)v[4 * q + b]), s4[b]), p.zero_point);
+            f = fminf(fmaxf(rintf(f), p.lo), p.hi);
+            f = (f != f) ? 0.0f : f;                      // NaN (e.g. 0 * inf) becomes 0, as in the stand-alone quantise kernels
+            w |= ((uint32_t)(__float2int_rn(f)) & 0xffu) << (8 * b);
+        }
+        packed[q] = w;
+    }
+    uint8_t *out = reinterpret_cast<uint8_t *>(p.C[0]) + elem_offset;
+    reinterpret_cast<uint4 *>(out)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    reinterpret_cast<uint4 *>(out)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+}
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,

@@ -1,17 +1,28 @@
-// K7, CTA-pair variant: C[M,N] (bfloat16) = A[M,K] (bfloat16) @ W[K,N], W stored as Bfp8_b tiles.
+// Tensor-core matmuls on CTA pairs (tcgen05.mma.cta_group::2), two operand kinds from one kernel template:
 //
-// The single-CTA kernel is bound by the integer work of turning Bfp8_b blocks into bfloat16 operands:
-// every CTA decodes a 256-column slab of W for 256 rows of A.  Here two CTAs on neighbouring SMs
-// (a cluster of 2) issue tcgen05.mma.cta_group::2: one instruction covers M = 256 (128 rows in each
-// CTA's tensor memory) x N = 256, and the hardware reads the weight operand half from each CTA's
-// shared memory.  So each CTA decodes only 128 columns per k-block while its tensor core still sees
-// all 256: half the decode work per flop, and half the decoded bytes written to shared memory.
+//   Bfp8 kind   C[M,N] (bfloat16) = A[M,K] (bfloat16) @ W[K,N], W stored as Bfp8_b tiles.
+//               Reference semantics: torch.matmul on the decoded operands
+//               (pybuda/pybuda/op/eval/pybuda/matmul.py:20-33; weight format rule pybuda/csrc/passes/dataformat.cpp:409-418).
+//   Int8 kind   acc[M,N] (int32) = A[M,K] (int8) @ W[K,N] (int8 tiles of an Int8 queue), then in the epilogue
+//               nothing / requantisation to int8 / dequantisation to float32.  Reference semantics: an int8 matmul
+//               yields int32 (pybuda/pybuda/op/eval/common.py:50-65) and a matmul carrying the "requant" attribute is
+//               followed by requantization of its result (pybuda/csrc/graph_lib/python_bindings.cpp:655-676):
+//               round(float(acc) * scale + zero_point) clamped to int8 (pybuda/pybuda/op/eval/buda/quantize.py:42-53);
+//               dequantization is (float(acc) - zero_point) * scale (quantize.py:35-40).
+//
+// Why pairs.  The single-CTA Bfp8 kernel is bound by the integer work of turning Bfp8_b blocks into bfloat16
+// operands: every CTA decodes a 256-column slab of W for 256 rows of A.  Here two CTAs on neighbouring SMs
+// issue one MMA that covers M = 256 (128 rows in each CTA's tensor memory) x N = 256, and the hardware reads
+// the weight operand half from each CTA's shared memory.  So each CTA prepares only 128 columns per k-block
+// while its tensor core still sees all 256: half the decode work per flop, and (for int8, whose tensor
+// throughput is twice that of bfloat16) half the weight bytes pulled from L2 per flop.
 //
 // Pair tile: 512 rows x 256 columns (two M = 256 accumulators, all 512 tensor-memory columns of both
-// SMs).  In each CTA (rank r = 0 leader, 1 peer):
-//   warp 8        producer: TMA-loads this CTA's two 128x64 activation boxes per k-block
-//   warps 10..17  decode this CTA's 128 weight columns (4 tile records x 2 k-tiles per k-block) into
-//                 the N-major swizzled operand stage, then arrive on the LEADER's full_b barrier
+// SMs); k-block = 128 bytes of K (64 bfloat16 / 128 int8).  In each CTA (rank r = 0 leader, 1 peer):
+//   warp 8        producer: TMA-loads this CTA's two 128-row activation boxes per k-block
+//   warps 10..17  weights: this CTA's 128 columns of the k-block, global -> registers -> N-major swizzled
+//                 operand stage (Bfp8: decoded to bfloat16; Int8: the 16-byte face rows are copied as they are),
+//                 then arrive on the LEADER's full_b barrier
 //   warp 9        leader: one thread issues the MMAs for the pair and commits completion to both
 //                 CTAs' barriers (multicast commit).  peer: relays "my activations landed" to the leader
 //   warps 0-7     epilogue for this CTA's 2 x 128 rows (two warps per tensor-memory lane quadrant, half
@@ -34,17 +45,13 @@ using namespace gemm;
 constexpr int kPairM = 512;        // rows of C per pair tile
 constexpr int kBN = 256;           // columns of C per pair tile
 constexpr int kHalfN = 128;        // weight columns decoded by one CTA
-constexpr int kBK = 64;            // k-block
-#ifndef PAIR_A_STAGES
-#define PAIR_A_STAGES 4
-#endif
+constexpr int kBKBytes = 128;      // k-block: one 128-byte swizzled row of K (64 bfloat16 / 128 int8)
 #ifndef PAIR_B_STAGES
 #define PAIR_B_STAGES 4
 #endif
-constexpr int kAStages = PAIR_A_STAGES;   // activation ring (per CTA: two 128x64 boxes per stage)
 constexpr int kBStages = PAIR_B_STAGES;   // decoded-weight ring (per CTA: 128 columns x 64 deep)
-constexpr int kABytes = 2 * 128 * kBK * 2;   // 32768
-constexpr int kBBytes = kHalfN * kBK * 2;    // 16384
+constexpr int kABytes = 2 * 128 * kBKBytes;  // 32768
+constexpr int kBBytes = kHalfN * kBKBytes;   // 16384
 constexpr int kDecodeWarps = 8;
 #ifndef GEMM_PREFETCH
 #define GEMM_PREFETCH 3
@@ -55,24 +62,66 @@ constexpr int kProducerWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1, kFirstDecodeW
 constexpr int kThreads = 32 * (kEpiWarps + 1 + 1 + kDecodeWarps);
 constexpr int kTmemCols = 512;
 
-constexpr int kSmemA = 0;
-constexpr int kSmemB = kSmemA + kAStages * kABytes;
-constexpr int kSmemBar = kSmemB + kBStages * kBBytes;
-constexpr int kNumBars = 3 * kAStages + 2 * kBStages + 2;
-constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 16 + 1024;
+constexpr int kEpiStageBytes = 32 * 128;           // per epilogue warp: 32 rows x 64 bfloat16 columns
 
-// instruction descriptor: D = F32, A = B = BF16, A K-major, B MN-major, N = 256, M = 256 (pair)
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) | ((uint32_t)(kBN >> 3) << 17) |
-                            ((uint32_t)(256 >> 4) << 24);
+// Shared-memory plan.  A launch that also writes peers' memory (kScatter) gives up one activation stage for the
+// epilogue's staging tiles; the plain launch keeps four activation stages and stores straight from registers.
+template <bool kScatter>
+struct Layout {
+    static constexpr int kAStages = kScatter ? 3 : 4;   // activation ring (per CTA: two 128-row boxes per stage)
+    static constexpr int kSmemA = 0;
+    static constexpr int kSmemB = kSmemA + kAStages * kABytes;
+    static constexpr int kSmemEpi = kSmemB + kBStages * kBBytes;
+    static constexpr int kSmemBar = kSmemEpi + (kScatter ? kEpiWarps * kEpiStageBytes : 0);
+    static constexpr int kNumBars = 3 * kAStages + 2 * kBStages + 2;
+    static constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 16 + 1024;
+};
 
-__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+enum : int { kKindBfp8 = 0, kKindI8 = 1 };
+
+template <int Kind>
+struct KindTraits;
+template <>
+struct KindTraits<kKindBfp8> {
+    static constexpr int kBK = 64;          // elements of K per k-block
+    static constexpr int kKTiles = 2;       // 32-deep tile rows per k-block
+    static constexpr int kRecordBytes = 1088;
+    // instruction descriptor: D = F32, A = B = BF16, A K-major, B MN-major, N = 256, M = 256 (pair)
+    static constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kBN >> 3) << 17) |
+                                       ((uint32_t)(256 >> 4) << 24);
+    // weight operand stage, N-major: 64-column atoms 1024 B apart, 8-deep k groups 2048 B apart
+    static constexpr uint32_t kBLbo = 1024, kBSbo = 2048;
+};
+template <>
+struct KindTraits<kKindI8> {
+    static constexpr int kBK = 128;
+    static constexpr int kKTiles = 4;
+    static constexpr int kRecordBytes = 1024;   // Int8 tile: four 16x16 faces, 16 bytes per face row, no exponents
+    // instruction descriptor: D = S32, A = B = S8, A K-major, B MN-major, N = 256, M = 256 (pair)
+    static constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(kBN >> 3) << 17) |
+                                       ((uint32_t)(256 >> 4) << 24);
+    // weight operand stage, N-major: one 128-column atom per 8-deep k group, groups 1024 B apart
+    static constexpr uint32_t kBLbo = 1024, kBSbo = 1024;
+};
+
+template <int Kind>
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
 {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
+    if constexpr (Kind == kKindBfp8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
 }
 
 // arrive on the barrier at this shared-memory offset in BOTH CTAs of the pair once every MMA issued so far is complete
@@ -84,14 +133,21 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t *bar)
                  : "memory");
 }
 
+template <int Kind, bool kScatter>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-bfp8b_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ Params p)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ Params p)
 {
+    using KT = KindTraits<Kind>;
+    using L = Layout<kScatter>;
+    constexpr int kBK = KT::kBK;
+    constexpr int kAStages = L::kAStages, kSmemA = L::kSmemA, kSmemB = L::kSmemB, kSmemEpi = L::kSmemEpi, kSmemBar = L::kSmemBar,
+                  kNumBars = L::kNumBars;
     extern __shared__ uint8_t smem_raw[];
     // identical carve-up in both CTAs: the MMA addresses the peer's operands by the leader's offsets
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *sA = smem + kSmemA;
     uint8_t *sB = smem + kSmemB;
+    uint8_t *sEpi = smem + kSmemEpi;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kSmemBar);
     uint64_t *full_a = bars;                    // [kAStages] this CTA's activations landed (TMA bytes)
     uint64_t *peer_a = full_a + kAStages;       // [kAStages] leader only: the peer's activations landed
@@ -199,13 +255,13 @@ bfp8b_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
 #pragma unroll
-                        for (int j = 0; j < kBK / 16; j++) {
+                        for (int j = 0; j < kBKBytes / 32; j++) {
                             // A: K-major, 8-row groups 1024 B apart, 32 B per 16-deep k-step inside the swizzled row
                             const uint64_t adesc = smem_desc(a_addr + h * (kABytes / 2) + j * 32, 16, 1024);
-                            // B (this CTA's 128 columns): 64-column atoms 1024 B apart, 8-deep k groups 2048 B apart
-                            const uint64_t bdesc = smem_desc(b_addr + j * 4096, 1024, 2048);
+                            // B (this CTA's 128 columns, N-major): 32 bytes of K = 4096 B of the stage per step
+                            const uint64_t bdesc = smem_desc(b_addr + j * 4096, KT::kBLbo, KT::kBSbo);
 #ifndef PAIR_EXP_NO_MMA
-                            umma_bf16_pair(tmem_base + h * kBN, adesc, bdesc, kIdesc, (kb > 0 || j > 0) ? 1u : 0u);
+                            umma_pair<Kind>(tmem_base + h * kBN, adesc, bdesc, KT::kIdesc, (kb > 0 || j > 0) ? 1u : 0u);
 #else
                             (void)adesc; (void)bdesc;
 #endif
@@ -233,9 +289,9 @@ bfp8b_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         }
         __syncwarp();
     } else if (warp >= kFirstDecodeWarp) {
-        // ------------------------------------------------------------------ decode warps (both CTAs)
-        // 16 units of 32 blocks per k-block: 8 records (2 k-tiles x 4 n-tiles) x two halves of their 64 blocks.
-        constexpr int kUnits = 16 / kDecodeWarps;
+        // ------------------------------------------------------------------ weight warps (both CTAs)
+        // Units of 32 face rows (16 values at fixed k): kKTiles x 4 tile records per k-block, two units per record.
+        constexpr int kUnits = KT::kKTiles * 4 * 2 / kDecodeWarps;
         const int dw = warp - kFirstDecodeWarp;
         // Raw records go global -> registers kPrefetch k-blocks ahead of their decode (a fetch cursor walks the
         // same (tile, k-block) sequence as the loop below), so the loop never waits for a load it just issued.
@@ -250,10 +306,15 @@ bfp8b_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                     const int u = it * kDecodeWarps + dw;
                     const int r = u >> 1;                           // record: k-tile r / 4, n-tile r % 4
                     const int blk = (u & 1) * 32 + lane;            // block = face * 16 + face row
-                    const uint8_t *rec =
-                        p.W + ((uint64_t)(f_kb * 2 + (r >> 2)) * p.Nt + (uint64_t)n_blk * 8 + rank * 4 + (r & 3)) * kRecord;
-                    m[it] = __ldg(reinterpret_cast<const uint4 *>(rec + 64 + blk * 16));
-                    e[it] = __ldg(rec + blk);
+                    const uint8_t *rec = p.W + ((uint64_t)(f_kb * KT::kKTiles + (r >> 2)) * p.Nt + (uint64_t)n_blk * 8 + rank * 4 +
+                                                (r & 3)) * KT::kRecordBytes;
+                    if constexpr (Kind == kKindBfp8) {
+                        m[it] = __ldg(reinterpret_cast<const uint4 *>(rec + 64 + blk * 16));
+                        e[it] = __ldg(rec + blk);
+                    } else {
+                        m[it] = __ldg(reinterpret_cast<const uint4 *>(rec + blk * 16));
+                        e[it] = 0u;
+                    }
                 }
                 if (++f_kb == p.k_blocks) {
                     f_kb = 0;
@@ -307,7 +368,13 @@ bfp8b_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                     const int blk = (u & 1) * 32 + lane;
                     const int k_local = (r >> 2) * 32 + (blk >> 5) * 16 + (blk & 15);
                     const int n_local = (r & 3) * 32 + ((blk >> 4) & 1) * 16;
-                    decode_block_to_operand<kHalfN / 64>(mant_cur[it], exp_cur[it], bst, k_local, n_local);
+                    if constexpr (Kind == kKindBfp8) {
+                        decode_block_to_operand<kHalfN / 64>(mant_cur[it], exp_cur[it], bst, k_local, n_local);
+                    } else {
+                        // 16 int8 values of one k: one 16-byte chunk of the 128-byte row k of its 8-deep group
+                        const int kr = k_local & 7;
+                        *reinterpret_cast<uint4 *>(bst + (k_local >> 3) * 1024 + kr * 128 + (((n_local >> 4) ^ kr) << 4)) = mant_cur[it];
+                    }
                 }
                 fence_async_smem();  // the tensor cores read shared memory through the async proxy
                 __syncwarp();
@@ -345,14 +412,57 @@ bfp8b_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                     tmem_ld32_issue(taddr + c * 64, v0);
                     tmem_ld32_issue(taddr + c * 64 + 32, v1);
                     tmem_ld_wait();
+                    if constexpr (Kind == kKindBfp8 && kScatter) {
+                        // Peers' copies go through shared memory, so that 8 lanes store one full 128-byte line of a
+                        // row: the lane that read row r writes its 64 bfloat16 values as row r of the warp's staging
+                        // tile (16-byte chunks XOR-swizzled by the row), then lanes re-read the tile four rows at a
+                        // time.  NVLink carries whole lines instead of 16-byte pieces (measured 3.5x faster).
+                        uint8_t *stg = sEpi + warp * kEpiStageBytes;
+#pragma unroll
+                        for (int q = 0; q < 8; q++) {
+                            const uint32_t(&v)[32] = q < 4 ? v0 : v1;
+                            const int b = (q & 3) * 8;
+                            uint4 o;
+                            o.x = pack_bf16x2(__uint_as_float(v[b]), __uint_as_float(v[b + 1]));
+                            o.y = pack_bf16x2(__uint_as_float(v[b + 2]), __uint_as_float(v[b + 3]));
+                            o.z = pack_bf16x2(__uint_as_float(v[b + 4]), __uint_as_float(v[b + 5]));
+                            o.w = pack_bf16x2(__uint_as_float(v[b + 6]), __uint_as_float(v[b + 7]));
+                            *reinterpret_cast<uint4 *>(stg + lane * 128 + ((q ^ (lane & 7)) << 4)) = o;
+                        }
+                        __syncwarp();
+                        const int64_t row_base = row - lane;
+                        const int ch = lane & 7;
+#pragma unroll
+                        for (int it = 0; it < 8; it++) {
+                            const int rr = it * 4 + (lane >> 3);
+                            const uint4 val = *reinterpret_cast<const uint4 *>(stg + rr * 128 + ((ch ^ (rr & 7)) << 4));
+#ifdef PAIR_EXP_NO_STORE
+                            if (row_base + rr < p.M && val.x == 0x7fc12345u)
+#else
+                            if (row_base + rr < p.M)
+#endif
+                            {
+                                const int64_t eo = (row_base + rr) * p.ldc + (int64_t)n_blk * kBN + col_half * (kBN / 2) + c * 64 + ch * 8;
+                                for (int d = 1; d < p.n_dst; d++) *reinterpret_cast<uint4 *>(p.C[d] + eo) = val;
+                            }
+                        }
+                        __syncwarp();
+                    }
 #ifdef PAIR_EXP_NO_STORE
                     if (row < p.M && v0[0] == 0x7fc12345u)
 #else
                     if (row < p.M)
 #endif
                     {
-                        store_row32(v0, p.C, p.n_dst, off + c * 64);
-                        store_row32(v1, p.C, p.n_dst, off + c * 64 + 32);
+                        if constexpr (Kind == kKindBfp8) {
+                            // this device's copy: straight from registers
+                            store_row32(v0, p.C, 1, off + c * 64);
+                            store_row32(v1, p.C, 1, off + c * 64 + 32);
+                        } else {
+                            const int col = (int)n_blk * kBN + col_half * (kBN / 2) + c * 64;
+                            store_row32_i8(v0, p, off + c * 64, col);
+                            store_row32_i8(v1, p, off + c * 64 + 32, col + 32);
+                        }
                     }
                 }
             }
@@ -372,17 +482,20 @@ bfp8b_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 
 }  // namespace gemm_pair
 
-// Launch of the CTA-pair kernel.  Same contract as the single-CTA launch; the caller has validated the shapes.
-cudaError_t launch_bfp8b_gemm_pair(const CUtensorMap &tmap, const gemm::Params &p_in, int sm_count, cudaStream_t stream)
+namespace {
+
+template <int Kind, bool kScatter>
+cudaError_t launch_pair(const CUtensorMap &tmap, const gemm::Params &p_in, int sm_count, cudaStream_t stream)
 {
     using namespace gemm_pair;
+    constexpr int kSmemBytes = Layout<kScatter>::kSmemBytes;
     static bool attr_done[64] = {};
     static int max_pairs[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     dev &= 63;
     if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(bfp8b_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<Kind, kScatter>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;
         // how many pairs the device can hold at once (SMs that cannot be paired inside their GPC stay idle)
         cudaLaunchConfig_t cfg = {};
@@ -397,22 +510,91 @@ cudaError_t launch_bfp8b_gemm_pair(const CUtensorMap &tmap, const gemm::Params &
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
         int n = 0;
-        e = cudaOccupancyMaxActiveClusters(&n, bfp8b_gemm_pair_kernel, &cfg);
+        e = cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<Kind, kScatter>, &cfg);
         if (e != cudaSuccess || n <= 0) {
             (void)cudaGetLastError();
             n = sm_count / 2;
         }
         max_pairs[dev] = n;
-        if (getenv("BUDA_GEMM_VERBOSE")) fprintf(stderr, "bfp8b gemm pair kernel: %d resident CTA pairs on %d SMs\n", n, sm_count);
+        if (getenv("BUDA_GEMM_VERBOSE")) fprintf(stderr, "gemm pair kernel (kind %d): %d resident CTA pairs on %d SMs\n", Kind, n, sm_count);
         attr_done[dev] = true;
     }
     gemm::Params p = p_in;
     p.m_tiles = (uint32_t)((p.M + kPairM - 1) / kPairM);
     p.n_tiles = (uint32_t)(p.N / kBN);
+    p.k_blocks = (uint32_t)(p.K / KindTraits<Kind>::kBK);
+    p.Nt = (uint32_t)(p.N / 32);
     uint32_t pairs = p.m_tiles * p.n_tiles;
     if (pairs > (uint32_t)max_pairs[dev]) pairs = (uint32_t)max_pairs[dev];
-    bfp8b_gemm_pair_kernel<<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap, p);
+    gemm_pair_kernel<Kind, kScatter><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap, p);
     return cudaGetLastError();
+}
+
+}  // namespace
+
+// Launch of the CTA-pair Bfp8 kernel.  Same contract as the single-CTA launch; the caller has validated the shapes.
+cudaError_t launch_bfp8b_gemm_pair(const CUtensorMap &tmap, const gemm::Params &p, int sm_count, cudaStream_t stream)
+{
+    if (p.n_dst > 1) return launch_pair<gemm_pair::kKindBfp8, true>(tmap, p, sm_count, stream);
+    return launch_pair<gemm_pair::kKindBfp8, false>(tmap, p, sm_count, stream);
+}
+
+// int8 x int8 -> int32 matmul with the requantise / dequantise epilogue (see the header of this file).
+cudaError_t launch_i8_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W, int64_t N, const float *scale,
+                           int64_t scale_len, float zero_point, int out_mode, void *C, int64_t ldc, int sm_count, cudaStream_t stream,
+                           unsigned int *status, char *err, size_t err_len)
+{
+    using namespace gemm;
+    if (M <= 0 || N <= 0 || K <= 0 || (N % 256) || (K % 128)) {
+        snprintf(err, err_len, "int8 gemm needs N %% 256 == 0 and K %% 128 == 0 (got M=%lld N=%lld K=%lld)", (long long)M, (long long)N,
+                 (long long)K);
+        return cudaErrorInvalidValue;
+    }
+    if (out_mode < BUDA_I8_OUT_INT32 || out_mode > BUDA_I8_OUT_DEQUANT_F32) {
+        snprintf(err, err_len, "int8 gemm: unknown output mode %d", out_mode);
+        return cudaErrorInvalidValue;
+    }
+    if (out_mode != BUDA_I8_OUT_INT32 && (!scale || (scale_len != 1 && scale_len != N))) {
+        snprintf(err, err_len, "int8 gemm: scale must hold 1 or N = %lld values (got %lld)", (long long)N, (long long)scale_len);
+        return cudaErrorInvalidValue;
+    }
+    const int out_elem = out_mode == BUDA_I8_OUT_REQUANT_I8 ? 1 : 4;
+    if (lda < K || ldc < N || (lda % 16) || ((ldc * out_elem) % 16) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+        (reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) ||
+        (scale_len > 1 && (reinterpret_cast<uintptr_t>(scale) & 15))) {
+        snprintf(err, err_len, "int8 gemm needs 16-byte aligned A, W, C, scale and row strides that are multiples of 16 bytes");
+        return cudaErrorInvalidValue;
+    }
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) {
+        snprintf(err, err_len, "cuTensorMapEncodeTiled is not available from this driver");
+        return cudaErrorNotSupported;
+    }
+    CUtensorMap tmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)lda};
+    const cuuint32_t box[2] = {128, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(A), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) {
+        snprintf(err, err_len, "cuTensorMapEncodeTiled failed with code %d", (int)cr);
+        return cudaErrorInvalidValue;
+    }
+    Params p = {};
+    p.W = static_cast<const uint8_t *>(W);
+    p.C[0] = static_cast<uint16_t *>(C);
+    p.n_dst = 1;
+    p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+    p.status = status;
+    p.out_mode = out_mode;
+    p.scale = scale;
+    p.scale_len = scale_len;
+    p.zero_point = zero_point;
+    p.lo = -128.0f;
+    p.hi = 127.0f;
+    return launch_pair<gemm_pair::kKindI8, false>(tmap, p, sm_count, stream);
 }
 
 }  // namespace buda

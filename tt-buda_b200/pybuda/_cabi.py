@@ -76,6 +76,7 @@ _SIGS = {
     "buda_requantize": (_i, [_vp, _i64, _vp, _vp, _i64, _i64, _f, _i, _f, _f, _vp, _vp]),
     "buda_bfp8b_gemm": (_i, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp]),
     "buda_bfp8b_gemm_scatter": (_i, [_vp, _i64, _i64, _i64, _vp, _i64, ctypes.POINTER(ctypes.c_void_p), _i, _i64, _vp]),
+    "buda_i8_gemm": (_i, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _f, _i, _vp, _i64, _vp]),
     "buda_gemm_select_kernel": (_i, [_i]),
     "buda_ipc_export": (_i, [_vp, ctypes.c_char_p]),
     "buda_ipc_open": (_i, [ctypes.c_char_p, _vpp]),

@@ -214,6 +214,24 @@ def bfp8b_matmul(a, w_image, n, out=None):
     return out
 
 
+def i8_matmul(a, w_image, n, scale=None, zero_point=0.0, out="int32"):
+    """int8 [M,K] @ W, W the tilized image of an Int8 queue holding a [K,N] tensor (tilize_pack(w_int8, DF.Int8)).
+    out = "int32": the accumulators; "int8": requantised, clamp(round(acc * scale + zero_point), -128, 127);
+    "float32": dequantised, (acc - zero_point) * scale.  scale: 1 value or N values (per output column)."""
+    _need_cuda(a, w_image)
+    assert a.dtype == torch.int8 and a.dim() == 2 and a.stride(1) == 1
+    m, k = a.shape
+    mode = {"int32": 0, "int8": 1, "float32": 2}[out]
+    c = torch.empty((m, n), dtype=[torch.int32, torch.int8, torch.float32][mode], device=a.device)
+    sc = None
+    if mode:
+        sc = scale.to(device=a.device, dtype=torch.float32).reshape(-1).contiguous()
+    with torch.cuda.device(a.device):
+        check(_cabi.lib.buda_i8_gemm(a.data_ptr(), m, k, a.stride(0), w_image.data_ptr(), n, sc.data_ptr() if mode else None,
+                                     sc.numel() if mode else 0, float(zero_point), mode, c.data_ptr(), c.stride(0), _stream()))
+    return c
+
+
 def select_gemm_kernel(which):
     """'auto' (default), 'single' or 'pair': which tensor-core kernel the matmul launches.  Returns the previous choice."""
     names = ["auto", "single", "pair"]
