@@ -54,6 +54,10 @@ typedef struct buda_queue_geom {
     uint32_t ublock_rt, ublock_ct;
     uint32_t t;
     uint32_t ublock_order; /* 0 = R (row-major scan of ublocks inside the mblock), 1 = C */
+    uint32_t tile_height;  /* 0 or 32: full tiles.  16, 8, 4, 2, 1: "tiny" tiles (TileDim, pybuda/csrc/lower_to_buda/
+                              common.hpp:80-90): a tile covers tile_height rows x 32 columns of the tensor, so
+                              R == grid_r*mblock_m*ublock_rt*tile_height; its record keeps the full size
+                              (balancer_utils.hpp:24-51 has no tile-dimension term) with rows >= tile_height zero. */
 } buda_queue_geom;
 
 /* ------------------------------------------------------------------ sizes (host only, no GPU) */

@@ -54,6 +54,10 @@ typedef struct {
     uint32_t ublock_rt, ublock_ct; /* micro-block, in tiles                              */
     uint32_t t;                    /* z dimension of one entry                           */
     uint32_t ublock_order;         /* 0 = row-major ublock scan (R), 1 = column-major (C)*/
+    uint32_t tile_height;          /* 0 or 32: full tiles; 16/8/4/2/1: tiny tiles (TileDim,
+                                      pybuda/csrc/lower_to_buda/common.hpp:80-90; tensor rows per tile as in
+                                      pybuda/pybuda/op/eval/buda/tilizer.py:40-52).  POLICY: the record keeps the
+                                      full-tile size (balancer_utils.hpp:24-51) and rows >= tile_height are zero */
 } ref_geom;
 
 int ref_threads(void)
@@ -343,6 +347,7 @@ static inline void store_from_f32(uint8_t *p, int df, float f)
 typedef struct {
     const ref_geom *g;
     uint32_t W, Z, R, C;       /* tensor dims; Z must equal g->t                */
+    uint32_t th;               /* tensor rows per tile                          */
     uint64_t tiles_per_entry;  /* per core buffer: t * mblock volume            */
     uint64_t tile_bytes;
     uint64_t buf_bytes;        /* one core's buffer: W entries                  */
@@ -353,9 +358,11 @@ static int make_ctx(layout_ctx *c, const ref_geom *g, const uint32_t shape[4], i
     long tb = ref_tile_bytes(df, with_header);
     if (tb < 0) return 1;
     c->g = g; c->W = shape[0]; c->Z = shape[1]; c->R = shape[2]; c->C = shape[3];
-    if (c->R % 32 || c->C % 32) return 1;
+    c->th = g->tile_height ? g->tile_height : 32;
+    if (c->th > 32 || (c->th & (c->th - 1))) return 1;
+    if (c->R % c->th || c->C % 32) return 1;
     if (g->t != c->Z) return 1;
-    if ((uint64_t)g->grid_r * g->mblock_m * g->ublock_rt * 32 != c->R) return 1;
+    if ((uint64_t)g->grid_r * g->mblock_m * g->ublock_rt * c->th != c->R) return 1;
     if ((uint64_t)g->grid_c * g->mblock_n * g->ublock_ct * 32 != c->C) return 1;
     c->tiles_per_entry = (uint64_t)g->t * g->mblock_m * g->mblock_n * g->ublock_rt * g->ublock_ct;
     c->tile_bytes = (uint64_t)tb;
@@ -401,9 +408,10 @@ int ref_tilize_pack(const void *src_, int src_df, const uint32_t shape[4], const
     } else {
         if (es == 0 || es != elem_bytes(dst_df)) return 1; /* layout-only: same element width */
     }
-    uint32_t Rt = c.R / 32, Ct = c.C / 32;
+    uint32_t Rt = c.R / c.th, Ct = c.C / 32;
     long hdr = with_header ? 32 : 0;
     long long ntiles = (long long)c.W * c.Z * Rt * Ct;
+    static const uint8_t zeros[16 * 4] = {0};
 #pragma omp parallel for schedule(static)
     for (long long ti = 0; ti < ntiles; ti++) {
         uint32_t ct = (uint32_t)(ti % Ct);
@@ -416,23 +424,26 @@ int ref_tilize_pack(const void *src_, int src_df, const uint32_t shape[4], const
         const uint8_t *base = src + (uint64_t)w * strides[0] + (uint64_t)z * strides[1];
         for (int face = 0; face < 4; face++) {
             for (int fr = 0; fr < 16; fr++) {
-                uint64_t r = (uint64_t)rt * 32 + (face >> 1) * 16 + fr;
+                uint32_t tr = (uint32_t)((face >> 1) * 16 + fr);   /* row inside the tile */
+                uint64_t r = (uint64_t)rt * c.th + tr;
                 uint64_t col0 = (uint64_t)ct * 32 + (face & 1) * 16;
                 const uint8_t *p = base + r * strides[2] + col0 * strides[3];
+                uint32_t estride = strides[3];
+                if (tr >= c.th) { p = zeros; estride = (uint32_t)es; }   /* rows a tiny tile does not hold */
                 int blk = face * 16 + fr;
                 if (m && is_bfp_a(dst_df)) {
                     uint16_t hv[16];
-                    for (int i = 0; i < 16; i++) memcpy(&hv[i], p + (uint64_t)i * strides[3], 2);
+                    for (int i = 0; i < 16; i++) memcpy(&hv[i], p + (uint64_t)i * estride, 2);
                     int bpb = 16 * (m + 1) / 8;
                     ref_bfp_a_pack_block(hv, m, rec + blk, rec + 64 + (long)blk * bpb);
                 } else if (m) {
                     uint32_t bits[16];
-                    for (int i = 0; i < 16; i++) bits[i] = load_as_f32_bits(p + (uint64_t)i * strides[3], src_df);
+                    for (int i = 0; i < 16; i++) bits[i] = load_as_f32_bits(p + (uint64_t)i * estride, src_df);
                     int bpb = 16 * (m + 1) / 8;
                     ref_bfp_pack_block(bits, m, rec + blk, rec + 64 + (long)blk * bpb);
                 } else {
                     for (int i = 0; i < 16; i++)
-                        memcpy(rec + ((long)blk * 16 + i) * es, p + (uint64_t)i * strides[3], es);
+                        memcpy(rec + ((long)blk * 16 + i) * es, p + (uint64_t)i * estride, es);
                 }
             }
         }
@@ -459,7 +470,7 @@ int ref_unpack_untilize(const void *src_, int src_df, int with_header, const ref
     } else {
         if (es == 0 || es != elem_bytes(src_df)) return 1;
     }
-    uint32_t Rt = c.R / 32, Ct = c.C / 32;
+    uint32_t Rt = c.R / c.th, Ct = c.C / 32;
     long hdr = with_header ? 32 : 0;
     long long ntiles = (long long)c.W * c.Z * Rt * Ct;
 #pragma omp parallel for schedule(static)
@@ -472,7 +483,9 @@ int ref_unpack_untilize(const void *src_, int src_df, int with_header, const ref
         uint8_t *base = dst + (uint64_t)w * strides[0] + (uint64_t)z * strides[1];
         for (int face = 0; face < 4; face++) {
             for (int fr = 0; fr < 16; fr++) {
-                uint64_t r = (uint64_t)rt * 32 + (face >> 1) * 16 + fr;
+                uint32_t tr = (uint32_t)((face >> 1) * 16 + fr);
+                if (tr >= c.th) continue;                      /* rows a tiny tile does not hold */
+                uint64_t r = (uint64_t)rt * c.th + tr;
                 uint64_t col0 = (uint64_t)ct * 32 + (face & 1) * 16;
                 uint8_t *p = base + r * strides[2] + col0 * strides[3];
                 int blk = face * 16 + fr;

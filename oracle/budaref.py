@@ -29,18 +29,18 @@ class Geom(ctypes.Structure):
         ("grid_r", ctypes.c_uint32), ("grid_c", ctypes.c_uint32),
         ("mblock_m", ctypes.c_uint32), ("mblock_n", ctypes.c_uint32),
         ("ublock_rt", ctypes.c_uint32), ("ublock_ct", ctypes.c_uint32),
-        ("t", ctypes.c_uint32), ("ublock_order", ctypes.c_uint32),
+        ("t", ctypes.c_uint32), ("ublock_order", ctypes.c_uint32), ("tile_height", ctypes.c_uint32),
     ]
 
     @classmethod
-    def for_shape(cls, shape, grid=(1, 1), ublock=(1, 1), ublock_order=0):
-        """Geometry covering a [w,z,R,C] tensor: R = grid_r*mblock_m*ublock_rt*32 and
+    def for_shape(cls, shape, grid=(1, 1), ublock=(1, 1), ublock_order=0, tile_height=32):
+        """Geometry covering a [w,z,R,C] tensor: R = grid_r*mblock_m*ublock_rt*tile_height and
         C = grid_c*mblock_n*ublock_ct*32 (pybuda/pybuda/tensor.py:1382-1404)."""
         _, z, r, c = shape
-        rt, ct = r // 32, c // 32
-        assert rt % (grid[0] * ublock[0]) == 0 and ct % (grid[1] * ublock[1]) == 0
+        rt, ct = r // tile_height, c // 32
+        assert r % tile_height == 0 and rt % (grid[0] * ublock[0]) == 0 and ct % (grid[1] * ublock[1]) == 0
         return cls(grid[0], grid[1], rt // (grid[0] * ublock[0]), ct // (grid[1] * ublock[1]),
-                   ublock[0], ublock[1], z, ublock_order)
+                   ublock[0], ublock[1], z, ublock_order, tile_height)
 
 
 def build(force=False):

@@ -337,3 +337,25 @@ def test_i8_matmul_oracle_matches_the_golden_chain(oracle):
         want_f = (acc.float() - 3.0) * scale
         assert np.array_equal(oracle.i8_matmul(a.numpy(), img, 128, 256, scale.numpy(), 3.0, 2), want_f.numpy())
 
+
+@pytest.mark.parametrize("th", [1, 2, 4, 8, 16])
+def test_tiny_tiles_equal_zero_padded_full_tiles(oracle, th):
+    """A tile of a tiny-tile queue (TileDim, csrc/lower_to_buda/common.hpp:80-90; rows per tile as in
+    op/eval/buda/tilizer.py:40-52) holds `th` tensor rows in a full-size record: the image equals that of the
+    tensor with every group of `th` rows padded with zero rows to 32."""
+    rng = np.random.default_rng(th)
+    rt = 3
+    x = rng.standard_normal((2, 2, rt * th, 96)).astype(np.float32)
+    g = oracle.Geom.for_shape(x.shape, tile_height=th)
+    xp = np.zeros((2, 2, rt * 32, 96), np.float32)
+    for r in range(rt):
+        xp[:, :, r * 32:r * 32 + th] = x[:, :, r * th:(r + 1) * th]
+    for df in (oracle.Bfp8_b, oracle.Bfp2_b, oracle.Float32):
+        img = oracle.tilize_pack(x, df, g)
+        assert img.size == 2 * 2 * rt * 3 * oracle.tile_bytes(df)
+        assert np.array_equal(img, oracle.tilize_pack(xp, df))
+        back = oracle.unpack_untilize(img, df, x.shape, geom=g)
+        full = oracle.unpack_untilize(img, df, xp.shape)
+        for r in range(rt):
+            assert np.array_equal(back[:, :, r * th:(r + 1) * th].view(np.uint32), full[:, :, r * 32:r * 32 + th].view(np.uint32))
+

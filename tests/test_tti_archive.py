@@ -90,7 +90,9 @@ def test_tbin_archive_packs_once_and_pushes_without_conversion(mods, oracle, tmp
           "attn.q": B.DramIODesc.for_tensor("attn.q", [1, 1, 1024, 1024], DF.Bfp4_b),
           "bias": B.DramIODesc.for_tensor("bias", [1, 1, 32, 1024], DF.Float16_b)}
     padded = dict(tensors)
-    padded["bias"] = T.pad_pytorch_tensor_to_buda(tensors["bias"], [])
+    # a plain-format queue takes the tensor in its own element type (the reference converts before tilizing:
+    # pybuda/pybuda/device_connector.py:177-201), and tile-aligned
+    padded["bias"] = T.pad_pytorch_tensor_to_buda(tensors["bias"], []).bfloat16()
     tti.save_tensor_archive(str(tmp_path), padded, F.BACKEND_TILIZED, qd)
     body = json.load(open(tmp_path / "device_image.json"))["tensors"]
     assert body["ffn.w1"]["format"] == "Bfp8_b" and body["ffn.w1"]["num_buffers"] == 8
@@ -116,6 +118,6 @@ def test_tbin_archive_packs_once_and_pushes_without_conversion(mods, oracle, tmp
         shape = (1, 1) + tuple(x.shape)
         geom = go if name == "ffn.w1" else None
         img = oracle.tilize_pack(x.reshape(shape).numpy(), fmt, geom) if geom else oracle.tilize_pack(x.reshape(shape).numpy(), fmt)
-        ref = oracle.unpack_untilize(img, fmt, shape, geom) if geom else oracle.unpack_untilize(img, fmt, shape)
+        ref = oracle.unpack_untilize(img, fmt, shape, geom=geom)
         assert np.array_equal(y.numpy().reshape(shape).view(np.uint32), ref.view(np.uint32))
     B.release_all_queues()

@@ -63,6 +63,7 @@ struct TileJob {
     // hstack / vstack host transforms place the t slices of a queue entry.  zn1 == 0: plain z * stride_z.
     uint32_t zn1, zn2;
     uint64_t stride_z_mid, stride_z_out;
+    uint32_t tile_h;                    // tensor rows per tile: 32, or 16 / 8 / 4 / 2 / 1 for tiny tiles (direct kernels only)
 };
 
 // byte offset of slice z on the row-major side

@@ -104,19 +104,23 @@ int make_job(const uint32_t shape[4], const uint64_t strides[4], const buda_queu
     if (tb < 0) return fail(BUDA_RUNTIME_ERROR, "unsupported queue data format %d", qdf);
     if (shape[2] == 0 || shape[3] == 0 || shape[0] == 0 || shape[1] == 0)
         return fail(BUDA_RUNTIME_ERROR, "empty tensor [%u,%u,%u,%u]", shape[0], shape[1], shape[2], shape[3]);
-    if (shape[2] % 32 || shape[3] % 32)
-        return fail(BUDA_RUNTIME_ERROR, "rows and columns must be multiples of the 32x32 tile, got [%u,%u]", shape[2],
+    const uint32_t th = g->tile_height ? g->tile_height : 32u;
+    if (th > 32u || (th & (th - 1u)))
+        return fail(BUDA_RUNTIME_ERROR, "tile height %u is not one of 32, 16, 8, 4, 2, 1", th);
+    if (shape[2] % th || shape[3] % 32)
+        return fail(BUDA_RUNTIME_ERROR, "rows and columns must be multiples of the %ux32 tile, got [%u,%u]", th, shape[2],
                     shape[3]);
     if (!g->grid_r || !g->grid_c || !g->mblock_m || !g->mblock_n || !g->ublock_rt || !g->ublock_ct || !g->t ||
         g->ublock_order > 1)
         return fail(BUDA_RUNTIME_ERROR, "invalid queue geometry");
     if (g->t != shape[1]) return fail(BUDA_RUNTIME_ERROR, "queue t=%u does not match tensor z=%u", g->t, shape[1]);
-    if ((uint64_t)g->grid_r * g->mblock_m * g->ublock_rt * 32u != shape[2] ||
+    if ((uint64_t)g->grid_r * g->mblock_m * g->ublock_rt * th != shape[2] ||
         (uint64_t)g->grid_c * g->mblock_n * g->ublock_ct * 32u != shape[3])
         return fail(BUDA_RUNTIME_ERROR, "queue geometry covers %llux%llu, tensor is %ux%u",
-                    (unsigned long long)g->grid_r * g->mblock_m * g->ublock_rt * 32u,
+                    (unsigned long long)g->grid_r * g->mblock_m * g->ublock_rt * th,
                     (unsigned long long)g->grid_c * g->mblock_n * g->ublock_ct * 32u, shape[2], shape[3]);
-    j.W = shape[0]; j.Z = shape[1]; j.Rt = shape[2] / 32; j.Ct = shape[3] / 32;
+    j.W = shape[0]; j.Z = shape[1]; j.Rt = shape[2] / th; j.Ct = shape[3] / 32;
+    j.tile_h = th;
     j.stride_w = strides[0]; j.stride_z = strides[1]; j.stride_r = strides[2];
     j.boxes_per_band = (j.Ct + kBoxTiles - 1) / kBoxTiles;
     const uint64_t items_per_tensor = (uint64_t)j.W * j.Z * j.Rt * j.boxes_per_band;
@@ -178,7 +182,7 @@ void pick_path(const TileJob &j, const PtrTable &p, int batch, int es, int &path
     const uint64_t valign = 4u * (uint64_t)es - 1u;
     uint64_t bits = j.stride_w | j.stride_z | j.stride_r;
     for (int b = 0; b < batch; b++) bits |= (uint64_t)p.src[b] | (uint64_t)p.dst[b];
-    path = (bits & 15u) == 0 ? 0 : 1;
+    path = ((bits & 15u) == 0 && j.tile_h == 32u) ? 0 : 1;   // tiny tiles: direct kernels only
     vec_ok = (bits & valign) == 0 ? 1 : 0;
 }
 
@@ -221,7 +225,7 @@ int tilize_device(int n, const void *const *srcs, int src_df, const uint32_t sha
         int path, vec_ok;
         pick_path(job, pt, nb, es, path, vec_ok);
         if (force_path >= 0) {
-            if (force_path == 0 && path != 0) return fail(BUDA_RUNTIME_ERROR, "staged path needs 16-byte aligned rows");
+            if (force_path == 0 && path != 0) return fail(BUDA_RUNTIME_ERROR, "staged path needs 16-byte aligned rows and 32-row tiles");
             path = force_path;
         }
         cudaError_t e = launch_tilize(job, pt, nb, mant, es, is_bfp_a(dst_df) ? 1 : 0, path, vec_ok, ctx->sm_count, stream, ctx->status);
@@ -259,7 +263,7 @@ int untilize_device(int n, const void *const *srcs, int src_df, int with_header,
         int path, vec_ok;
         pick_path(job, pt, nb, es, path, vec_ok);
         if (force_path >= 0) {
-            if (force_path == 0 && path != 0) return fail(BUDA_RUNTIME_ERROR, "staged path needs 16-byte aligned rows");
+            if (force_path == 0 && path != 0) return fail(BUDA_RUNTIME_ERROR, "staged path needs 16-byte aligned rows and 32-row tiles");
             path = force_path;
         }
         cudaError_t e = launch_untilize(job, pt, nb, mant, es, is_bfp_a(src_df) ? 1 : 0, path, vec_ok, ctx->sm_count, stream, ctx->status);

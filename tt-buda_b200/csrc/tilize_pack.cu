@@ -294,15 +294,16 @@ pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
         const uint32_t b = (uint32_t)(t / job.W);
         const uint32_t face = hf >> 1, half = hf & 1u;
         const uint32_t fr = half * 8u + (lane >> 2);
-        const uint64_t row = (uint64_t)rt * 32u + (face >> 1) * 16u + fr;
+        const uint32_t tr = (face >> 1) * 16u + fr;            // row inside the tile
+        const uint64_t row = (uint64_t)rt * job.tile_h + tr;  // tiny tiles hold tile_h tensor rows; the rest of the record is zero
         const uint64_t col = (uint64_t)ct * 32u + (face & 1u) * 16u + (lane & 3) * 4u;
         const uint8_t *p = ptrs.src[b] + (uint64_t)w * job.stride_w + rm_z_offset(job, z) + row * job.stride_r +
                            col * ES;
         uint8_t *r = ptrs.dst[b] + tile_record_offset(job, w, z, rt, ct);
         if (hdr && hf == 0 && lane < 8) reinterpret_cast<uint32_t *>(r)[lane] = 0;
         r += hdr;
-        uint32_t x[4];
-        load4<ES>(p, vec_ok != 0, x);
+        uint32_t x[4] = {0u, 0u, 0u, 0u};
+        if (tr < job.tile_h) load4<ES>(p, vec_ok != 0, x);
         const uint32_t blk = face * 16u + fr;
         if (M > 0) {
             constexpr int MM = M > 0 ? M : 7;

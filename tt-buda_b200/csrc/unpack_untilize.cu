@@ -223,7 +223,9 @@ unpack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant_
         const uint32_t b = (uint32_t)(t / job.W);
         const uint32_t face = hf >> 1, half = hf & 1u;
         const uint32_t fr = half * 8u + (lane >> 2);
-        const uint64_t row = (uint64_t)rt * 32u + (face >> 1) * 16u + fr;
+        const uint32_t tr = (face >> 1) * 16u + fr;            // row inside the tile
+        if (tr >= job.tile_h) continue;                       // tiny tiles: only tile_h rows of a record belong to the tensor
+        const uint64_t row = (uint64_t)rt * job.tile_h + tr;
         const uint64_t col = (uint64_t)ct * 32u + (face & 1u) * 16u + (lane & 3) * 4u;
         uint8_t *p = ptrs.dst[b] + (uint64_t)w * job.stride_w + rm_z_offset(job, z) + row * job.stride_r + col * ES;
         const uint8_t *r = ptrs.src[b] + tile_record_offset(job, w, z, rt, ct) + hdr;

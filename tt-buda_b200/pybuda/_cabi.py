@@ -24,17 +24,19 @@ class QueueGeom(ctypes.Structure):
         ("grid_r", ctypes.c_uint32), ("grid_c", ctypes.c_uint32),
         ("mblock_m", ctypes.c_uint32), ("mblock_n", ctypes.c_uint32),
         ("ublock_rt", ctypes.c_uint32), ("ublock_ct", ctypes.c_uint32),
-        ("t", ctypes.c_uint32), ("ublock_order", ctypes.c_uint32),
+        ("t", ctypes.c_uint32), ("ublock_order", ctypes.c_uint32), ("tile_height", ctypes.c_uint32),
     ]
 
     @classmethod
-    def for_shape(cls, shape, grid=(1, 1), ublock=(1, 1), ublock_order=0):
+    def for_shape(cls, shape, grid=(1, 1), ublock=(1, 1), ublock_order=0, tile_height=32):
         _, z, r, c = shape
-        rt, ct = r // 32, c // 32
+        if r % tile_height or c % 32:
+            raise ValueError(f"[{r},{c}] is not a whole number of {tile_height}x32 tiles")
+        rt, ct = r // tile_height, c // 32
         if rt % (grid[0] * ublock[0]) or ct % (grid[1] * ublock[1]):
             raise ValueError("grid x ublock does not divide the tensor's tile counts")
         return cls(grid[0], grid[1], rt // (grid[0] * ublock[0]), ct // (grid[1] * ublock[1]),
-                   ublock[0], ublock[1], z, ublock_order)
+                   ublock[0], ublock[1], z, ublock_order, tile_height)
 
 
 _vp, _i, _i64, _u64, _u32, _f = (ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_uint64, ctypes.c_uint32,

@@ -95,7 +95,8 @@ namespace backend
 tt_dram_io_desc make_queue_desc(const std::string &name, std::array<std::uint32_t, 4> shape, DataFormat df,
                                 std::pair<std::uint32_t, std::uint32_t> grid = {1, 1},
                                 std::pair<std::uint32_t, std::uint32_t> ublock = {1, 1}, std::uint32_t ublock_order = 0,
-                                std::uint32_t num_slots = 0, IO_TYPE io_type = IO_TYPE::Queue, bool tile_header = false);
+                                std::uint32_t num_slots = 0, IO_TYPE io_type = IO_TYPE::Queue, bool tile_header = false,
+                                std::uint32_t tile_height = 32);
 
 DEVICE_STATUS_CODE push_input(const tt_dram_io_desc &q, const tt_PytorchTensorDesc &tensor, const bool push_one,
                               const int timeout_in_seconds, const int ram_ptr);

@@ -74,16 +74,17 @@ void BackendModule(py::module &m_backend)
             "for_tensor",
             [](const std::string &name, std::array<std::uint32_t, 4> shape, tt::DataFormat df,
                std::pair<std::uint32_t, std::uint32_t> grid, std::pair<std::uint32_t, std::uint32_t> ublock,
-               const std::string &ublock_order, std::uint32_t num_slots, tt::IO_TYPE io_type, bool tile_header)
+               const std::string &ublock_order, std::uint32_t num_slots, tt::IO_TYPE io_type, bool tile_header,
+               std::uint32_t tile_height)
             {
                 if (ublock_order != "r" && ublock_order != "c")
                     throw std::runtime_error("ublock_order must be 'r' or 'c'");
                 return tt::backend::make_queue_desc(name, shape, df, grid, ublock, ublock_order == "c" ? 1 : 0, num_slots,
-                                                    io_type, tile_header);
+                                                    io_type, tile_header, tile_height);
             },
             py::arg("name"), py::arg("shape"), py::arg("data_format"), py::arg("grid") = std::make_pair(1u, 1u),
             py::arg("ublock") = std::make_pair(1u, 1u), py::arg("ublock_order") = "r", py::arg("num_slots") = 0,
-            py::arg("io_type") = tt::IO_TYPE::Queue, py::arg("tile_header") = false,
+            py::arg("io_type") = tt::IO_TYPE::Queue, py::arg("tile_header") = false, py::arg("tile_height") = 32,
             "Descriptor of a queue holding [w, z, R, C] tensors of the given format.  num_slots = 0 sizes the "
             "ring for two pushes of w entries.")
         .def_property_readonly("name", [](tt::tt_dram_io_desc &self) { return self.queue_name; })

@@ -45,7 +45,7 @@ DEVICE_STATUS_CODE from_cabi(int rc, const char *what)
 
 buda_queue_geom geom_of(const tt_dram_io_desc &q)
 {
-    buda_queue_geom g;
+    buda_queue_geom g = {};
     g.grid_r = q.bufq_grid_dim_r;
     g.grid_c = q.bufq_grid_dim_c;
     g.mblock_m = q.mblock_m;
@@ -54,6 +54,7 @@ buda_queue_geom geom_of(const tt_dram_io_desc &q)
     g.ublock_ct = q.ublock_ct;
     g.t = q.t;
     g.ublock_order = q.ublock_order;
+    g.tile_height = q.tile_height;
     return g;
 }
 
@@ -73,8 +74,8 @@ std::array<std::uint64_t, 4> strides64(const tt_PytorchTensorDesc &d)
 // A tensor covers the queue when its last two dims are the queue's rows and columns and its z is t.
 std::string check_tensor_fits(const tt_dram_io_desc &q, const tt_PytorchTensorDesc &d)
 {
-    if (q.tile_height != 32 || q.tile_width != 32)
-        return "only 32x32 tiles are supported";
+    if (q.tile_width != 32 || q.tile_height == 0 || q.tile_height > 32 || (q.tile_height & (q.tile_height - 1)))
+        return "tiles are 32 columns wide and 32, 16, 8, 4, 2 or 1 rows high";
     if (q.layout != IO_LAYOUT::Tilized)
         return "only tilized queues are supported";
     if (q.hstack_factor != 1 || q.vstack_factor != 1)
@@ -114,6 +115,7 @@ bool same_geometry(const tt_dram_io_desc &a, const tt_dram_io_desc &b)
     return a.bufq_grid_dim_r == b.bufq_grid_dim_r && a.bufq_grid_dim_c == b.bufq_grid_dim_c && a.mblock_m == b.mblock_m &&
            a.mblock_n == b.mblock_n && a.ublock_rt == b.ublock_rt && a.ublock_ct == b.ublock_ct && a.t == b.t &&
            a.ublock_order == b.ublock_order && a.bufq_target_format == b.bufq_target_format && a.tile_header == b.tile_header &&
+           a.tile_height == b.tile_height &&
            a.bufq_num_slots == b.bufq_num_slots;
 }
 
@@ -219,11 +221,14 @@ std::string last_error() { return t_last_error; }
 
 tt_dram_io_desc make_queue_desc(const std::string &name, std::array<std::uint32_t, 4> shape, DataFormat df,
                                 std::pair<std::uint32_t, std::uint32_t> grid, std::pair<std::uint32_t, std::uint32_t> ublock,
-                                std::uint32_t ublock_order, std::uint32_t num_slots, IO_TYPE io_type, bool tile_header)
+                                std::uint32_t ublock_order, std::uint32_t num_slots, IO_TYPE io_type, bool tile_header,
+                                std::uint32_t tile_height)
 {
-    if (shape[2] % 32 || shape[3] % 32)
-        throw std::runtime_error("queue rows and columns must be multiples of the 32x32 tile");
-    const std::uint32_t rt = shape[2] / 32, ct = shape[3] / 32;
+    if (tile_height == 0 || tile_height > 32 || (tile_height & (tile_height - 1)))
+        throw std::runtime_error("tile_height must be 32, 16, 8, 4, 2 or 1");
+    if (shape[2] % tile_height || shape[3] % 32)
+        throw std::runtime_error("queue rows and columns must be multiples of the tile (tile_height x 32)");
+    const std::uint32_t rt = shape[2] / tile_height, ct = shape[3] / 32;
     if (!grid.first || !grid.second || !ublock.first || !ublock.second || rt % (grid.first * ublock.first) ||
         ct % (grid.second * ublock.second))
         throw std::runtime_error("grid x ublock does not divide the tensor's tile counts");
@@ -243,6 +248,7 @@ tt_dram_io_desc make_queue_desc(const std::string &name, std::array<std::uint32_
     q.bufq_target_format = df;
     q.ublock_order = ublock_order;
     q.tile_header = tile_header;
+    q.tile_height = tile_height;
     q.io_type = io_type;
     q.bufq_entry_size = (std::uint32_t)(q.tiles_per_entry() * tile_size_bytes(df, tile_header));
     return q;
@@ -374,7 +380,8 @@ DEVICE_STATUS_CODE push_input(const tt_dram_io_desc &q, const tt_TilizedTensorDe
 DEVICE_STATUS_CODE get_output(const tt_dram_io_desc &q, tt_PytorchTensorDesc &out, const bool pop_one,
                               const int timeout_in_seconds, const int rd_ptr)
 {
-    if (q.tile_height != 32 || q.tile_width != 32 || q.layout != IO_LAYOUT::Tilized)
+    if (q.tile_width != 32 || q.tile_height == 0 || q.tile_height > 32 || (q.tile_height & (q.tile_height - 1)) ||
+        q.layout != IO_LAYOUT::Tilized)
         return fail(DEVICE_STATUS_CODE::RuntimeError, "get_output: only tilized queues of 32x32 tiles are supported");
     const std::uint32_t hs = std::max<std::uint32_t>(1, q.hstack_factor), vs = std::max<std::uint32_t>(1, q.vstack_factor);
     if (q.t % (hs * vs))

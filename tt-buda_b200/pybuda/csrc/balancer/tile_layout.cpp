@@ -7,7 +7,7 @@ namespace tt::balancer
 
 buda_queue_geom TileLayout::geom() const
 {
-    buda_queue_geom g;
+    buda_queue_geom g = {};
     g.grid_r = grid_shape.r;
     g.grid_c = grid_shape.c;
     g.mblock_m = block_shape.mblock_m;
