@@ -246,6 +246,15 @@ int buda_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void
 int buda_bfp8b_gemm_scatter(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N,
                             void *const *C_dsts, int n_dst, int64_t ldc, void *stream);
 
+/* Prestride transform of a convolution activation (device pointers): the [w, z, H, W] tensor, padded with
+ * zeros to multiples of `stride`, becomes [w, 1, n_offsets*z, ceil(H/stride)*ceil(W/stride)]:
+ *   dst[w, k*z + zc, hr*Ws + wc] = src[w, zc, hr*stride + y_k, wc*stride + x_k],  (x_k, y_k) = xy_offsets[2k], [2k+1]
+ * written dense into [w, dst_rows, dst_cols] with zeros outside.  It is what a queue whose descriptor carries
+ * a StrideDescriptor does to a pushed tensor before tilizing (pybuda/pybuda/tensor.py:1415-1422; golden
+ * pybuda/pybuda/op/eval/pybuda/tm.py:316-335).  xy_offsets is a HOST array of n_offsets (x, y) pairs. */
+int buda_prestride(const void *src, int elem_bytes, const uint32_t shape[4], const uint64_t strides_bytes[4], int stride,
+                   const int *xy_offsets, int n_offsets, void *dst, uint32_t dst_rows, uint32_t dst_cols, void *stream);
+
 /* acc[M,N] (int32) = A[M,K] (int8, row-major, row stride lda bytes) @ W[K,N], W the tilized image of an
  * Int8 queue (default geometry: 32x32 tiles row-major over [K/32][N/32], four 16x16 faces of 16-byte
  * rows, 1024 bytes per tile, no header) -- what buda_tilize_pack writes for a [1,1,K,N] int8 tensor.

@@ -287,3 +287,18 @@ def i8_matmul(a_i8, w_img, K, N, scale=None, zp=0.0, mode=0, geom=None):
                              out.ctypes.data)
     assert rc == 0
     return out
+
+
+def prestride_act(act, stride):
+    """Golden prestride of a [w, z, H, W] activation (pybuda/pybuda/op/eval/pybuda/tm.py:316-335): pad H and W with
+    zeros to multiples of the stride, take the stride x stride phase images act[:, :, y::s, x::s] (y outer, x inner),
+    stack them along z, flatten each image into one row -> [w, 1, z*s*s, (H/s)*(W/s)]."""
+    act = np.asarray(act)
+    w, z, h, wd = act.shape
+    hp, wp = -(-h // stride) * stride, -(-wd // stride) * stride
+    padded = np.zeros((w, z, hp, wp), dtype=act.dtype)
+    padded[:, :, :h, :wd] = act
+    phases = [padded[:, :, y::stride, x::stride] for y in range(stride) for x in range(stride)]
+    out = np.concatenate(phases, axis=-3)
+    return out.reshape(w, 1, out.shape[1], out.shape[2] * out.shape[3])
+

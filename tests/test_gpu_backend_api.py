@@ -234,3 +234,57 @@ def test_output_host_transforms(api, oracle, h, v, row_major, t):
             go = oracle.Geom.for_shape(shape, (1, 1), (2, 1), 0)
             want = torch.from_numpy(oracle.unpack_untilize(oracle.tilize_pack(x.numpy(), oracle.Bfp8_b, go), oracle.Bfp8_b, shape, geom=go))
         assert torch.equal(y, _golden_stack(want, h, v, row_major)), df_name
+
+
+def test_prestriding_queue_stores_the_prestrided_activation(api, oracle):
+    """push_input on a queue with a StrideDescriptor: the original [w, z, H, W] activation goes in, the queue holds
+    its prestrided form (golden op/eval/pybuda/tm.py:316-335), zero-padded to tiles."""
+    C, B, DF, T = api
+    g = torch.Generator().manual_seed(41)
+    x = torch.randn(2, 3, 30, 45, generator=g)                 # odd sizes: padding to the stride is exercised
+    for stride, fmt, tdtype in ((2, DF.Float32, torch.float32), (4, DF.Float16_b, torch.bfloat16), (2, DF.Bfp8_b, torch.float32)):
+        xs = x.to(tdtype)
+        gold = oracle.prestride_act(xs.float().numpy(), stride)            # [2, 1, 3*s*s, ceil(30/s)*ceil(45/s)]
+        rows, cols = T.align_up_tile(gold.shape[2]), T.align_up_tile(gold.shape[3])
+        q = B.DramIODesc.for_tensor(f"conv_act_{stride}_{int(fmt)}", [2, 1, rows, cols], fmt)
+        tr = T.RuntimeTensorTransform(T.RuntimeTensorTransformType.Prestride, stride_height=stride, stride_width=stride)
+        xs2, q = T.do_runtime_transform(tr, xs, q, [])
+        for src in (xs2, xs2.cuda()):                                       # host and device sources
+            _ok(B, B.push_input(q, T.pytorch_tensor_to_tensor_desc(src), False, 1, -1))
+            out = B.PytorchTensorDesc()
+            out.format = DF.Float32 if fmt != DF.Float16_b else DF.Float16_b
+            _ok(B, B.get_output(q, out, False, 1, -1))
+            y = T.tensor_desc_to_pytorch_tensor(out).clone().float()
+            _ok(B, B.pop_output(q, False, 1))
+            _ok(B, B.free_tensor(out))
+            want = np.zeros((2, 1, rows, cols), np.float32)
+            want[:, :, :gold.shape[2], :gold.shape[3]] = gold
+            if fmt == DF.Bfp8_b:
+                want = oracle.unpack_untilize(oracle.tilize_pack(want, oracle.Bfp8_b), oracle.Bfp8_b, want.shape)
+            assert np.array_equal(y.numpy().view(np.uint32), want.view(np.uint32))
+    # a descriptor that does not fit its queue is refused
+    small = B.DramIODesc.for_tensor("conv_act_small", [2, 1, 32, 32], DF.Float32)
+    _, small = T._prestride_shape(x, 2, 2, small)
+    assert B.push_input(small, T.pytorch_tensor_to_tensor_desc(x), False, 1, -1) == B.BackendStatusCode.RuntimeError
+    assert "does not fit" in B.last_error()
+
+
+@pytest.mark.parametrize("th", [1, 16])
+def test_tiny_tile_queue_round_trip(api, oracle, th):
+    C, B, DF, T = api
+    x = torch.randn(2, 1, th, 96, generator=torch.Generator().manual_seed(th))
+    q = B.DramIODesc.for_tensor(f"bias_th{th}", [2, 1, th, 96], DF.Bfp8_b, tile_height=th)
+    assert q.tile_height == th
+    _ok(B, B.push_input(q, T.pytorch_tensor_to_tensor_desc(x), False, 1, -1))
+    out = B.PytorchTensorDesc()
+    out.format = DF.Float32
+    _ok(B, B.get_output(q, out, False, 1, -1))
+    y = T.tensor_desc_to_pytorch_tensor(out).clone()
+    _ok(B, B.pop_output(q, False, 1))
+    _ok(B, B.free_tensor(out))
+    og = oracle.Geom.for_shape(x.shape, tile_height=th)
+    img = oracle.tilize_pack(x.numpy(), oracle.Bfp8_b, og)
+    assert img.size == 2 * 3 * 1088                                         # full-size records
+    want = oracle.unpack_untilize(img, oracle.Bfp8_b, x.shape, geom=og)
+    assert y.shape == x.shape and np.array_equal(y.numpy().view(np.uint32), want.view(np.uint32))
+

@@ -6,6 +6,7 @@ import os
 import pickle
 import re
 
+import numpy as np
 import pytest
 import torch
 
@@ -52,6 +53,7 @@ def test_cabi_sizes_match_oracle(oracle):
     # queues are sized with the 32-byte per-tile header, as the reference compiler sizes them
     assert _cabi.lib.buda_io_size_bytes(6, 0, 1, 1, 2, 4, 1, 2, 32, 32) == 16 * 1120
     assert _cabi.lib.buda_io_size_bytes(0, 1, 1, 1, 2, 4, 1, 2, 32, 32) == 16 * 4096
+    assert _cabi.lib.buda_io_size_bytes(6, 0, 1, 1, 2, 4, 1, 2, 4, 32) == 16 * 1120      # tiny tiles keep full-size records
 
 
 def test_cabi_tile_map_matches_oracle(oracle):
@@ -251,3 +253,62 @@ def test_tensor_wrappers(C, T):
     with pytest.raises(RuntimeError):
         back.to_buda_shape()
     assert T.to_pt_tensors([t, torch.zeros(1)])[0] is t.value()
+
+
+# ------------------------------------------------------------------------------------------------
+# runtime tensor transforms (reference: pybuda/pybuda/tensor.py:1382-1447)
+# ------------------------------------------------------------------------------------------------
+def test_runtime_transform_record_round_trips_through_json():
+    import json
+    from pybuda import tensor as T
+    tr = T.RuntimeTensorTransform(T.RuntimeTensorTransformType.Prestride, original_shape=(1, 3, 224, 224), stride_height=2,
+                                  stride_width=2, kernel_height=7, kernel_width=7)
+    back = T.RuntimeTensorTransform.from_json(json.loads(json.dumps(tr.to_json())))
+    assert back.to_json() == tr.to_json() and back.type is T.RuntimeTensorTransformType.Prestride
+
+
+def test_embedding_index_layout():
+    import pybuda._C as C
+    from pybuda import tensor as T
+    q = C.backend_api.DramIODesc.for_tensor("emb", [1, 1, 32, 64], C.DataFormat.RawUInt32)
+    idx = torch.arange(1100, dtype=torch.int32)
+    tr = T.RuntimeTensorTransform(T.RuntimeTensorTransformType.EmbeddingIndex, original_shape=(1100,))
+    t, q2 = T.do_runtime_transform(tr, idx.clone(), q, [])
+    assert t.shape == (1, 1, 32, 64) and q2 is q
+    # 1100 indices pad to 1120 = 35 rows of 32 with all-ones, rows pad to 64 with zeros; tile row j of 32 indices
+    # ends up as row j % 32 of the column block j // 32
+    flat = torch.full((1120,), -1, dtype=torch.int32)
+    flat[:1100] = idx
+    rows = torch.zeros(64, 32, dtype=torch.int32)
+    rows[:35] = flat.view(35, 32)
+    want = rows.view(2, 32, 32).transpose(0, 1).reshape(32, 64)
+    assert torch.equal(t[0, 0], want)
+
+
+def test_prestride_transform_sets_the_stride_descriptor(oracle):
+    import pybuda._C as C
+    from pybuda import tensor as T
+    q = C.backend_api.DramIODesc.for_tensor("conv_act", [1, 1, 32, 32], C.DataFormat.Float16_b)
+    x = torch.randn(1, 3, 8, 8)
+    y, q2 = T.eval_runtime_transform('{"type": "Prestride", "stride_height": 2, "stride_width": 2}', x, q, [])
+    assert y is x and q2.s_descriptor.stride == 2
+    assert q2.s_descriptor.xy_offsets == [(0, 0), (1, 0), (0, 1), (1, 1)]
+    # the oracle's restatement of the golden prestride against the golden's own torch formulation (tm.py:316-335)
+    a = torch.arange(2 * 3 * 5 * 7, dtype=torch.float32).reshape(2, 3, 5, 7)
+    act = torch.nn.functional.pad(a, (0, 1, 0, 1))
+    gold = torch.cat([act[:, :, yy::2, xx::2] for yy in range(2) for xx in range(2)], dim=-3)
+    gold = gold.view(2, 1, 12, 12)
+    assert np.array_equal(oracle.prestride_act(a.numpy(), 2), gold.numpy())
+    with pytest.raises(AssertionError):
+        T._prestride_shape(x, 2, 3, q)
+
+
+def test_reinterpret_shape_pads_to_the_queue_tiles():
+    import pybuda._C as C
+    from pybuda import tensor as T
+    q = C.backend_api.DramIODesc.for_tensor("r", [1, 1, 32, 64], C.DataFormat.Float32)
+    x = torch.arange(2 * 3 * 10, dtype=torch.float32).reshape(2, 30)
+    tr = T.RuntimeTensorTransform(T.RuntimeTensorTransformType.ReinterpretShape, reinterpreted_shape=(1, 1, 1, 60))
+    y, _ = T.do_runtime_transform(tr, x, q, [])
+    assert y.shape == (1, 1, 32, 64) and torch.equal(y[0, 0, 0, :60], x.reshape(-1)) and y[0, 0, 1:].abs().sum() == 0
+

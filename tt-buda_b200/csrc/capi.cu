@@ -26,6 +26,9 @@ cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, 
                               size_t err_len);
 
 int gemm_kernel_choice(int which);
+cudaError_t launch_prestride(const void *src, int elem_bytes, const uint32_t shape[4], const uint64_t strides[4], int stride,
+                             const int *xy_offsets, int n_offsets, void *dst, uint32_t dst_rows, uint32_t dst_cols, int sm_count,
+                             cudaStream_t stream);
 cudaError_t launch_i8_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W, int64_t N, const float *scale,
                            int64_t scale_len, float zero_point, int out_mode, void *C, int64_t ldc, int sm_count, cudaStream_t stream,
                            unsigned int *status, char *err, size_t err_len);
@@ -325,7 +328,7 @@ SlicePlan plan_slices(const TileJob &j, uint64_t row_bytes)
 {
     SlicePlan p{false, j.Rt, 1};
     if (!j.trivial_geom) return p;
-    const uint64_t band_bytes = 32ull * row_bytes;
+    const uint64_t band_bytes = (uint64_t)j.tile_h * row_bytes;
     uint64_t bps = kSliceTargetBytes / (band_bytes ? band_bytes : 1);
     if (bps < 1) bps = 1;
     if (bps > j.Rt) bps = j.Rt;
@@ -376,7 +379,7 @@ int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_
     std::lock_guard<std::mutex> lock(ctx->host_mu);
     // a slice on the device is always dense: [rows][row_bytes]
     const uint32_t slice_bands = plan.sliced ? plan.bands_per_slice : full.Rt;
-    const uint64_t slice_a = plan.sliced ? (uint64_t)slice_bands * 32u * row_bytes
+    const uint64_t slice_a = plan.sliced ? (uint64_t)slice_bands * full.tile_h * row_bytes
                                          : (uint64_t)shape[0] * shape[1] * shape[2] * row_bytes;
     const uint64_t slice_b = q_on_device ? 0 : (plan.sliced ? (uint64_t)slice_bands * full.Ct * full.tile_bytes : image_bytes);
     if (int rc = ensure_pipe(ctx, slice_a, slice_b)) return rc;
@@ -436,14 +439,14 @@ int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_
                 const int slot = (int)(k % kPipeDepth);
                 const uint32_t band0 = sl * plan.bands_per_slice;
                 const uint32_t nb = (full.Rt - band0 < plan.bands_per_slice) ? (full.Rt - band0) : plan.bands_per_slice;
-                const uint32_t sshape[4] = {1, 1, nb * 32u, shape[3]};
-                const uint64_t sstr[4] = {(uint64_t)nb * 32u * row_bytes, (uint64_t)nb * 32u * row_bytes, row_bytes,
+                const uint32_t sshape[4] = {1, 1, nb * full.tile_h, shape[3]};
+                const uint64_t sstr[4] = {(uint64_t)nb * full.tile_h * row_bytes, (uint64_t)nb * full.tile_h * row_bytes, row_bytes,
                                           (uint64_t)es};
                 buda_queue_geom sg = *geom;
                 sg.t = 1;
                 sg.mblock_m = nb;
                 uint8_t *a = ctx->stage_a[slot];
-                uint8_t *rm_ptr = rm_host + w * strides[0] + z * strides[1] + (uint64_t)band0 * 32u * strides[2];
+                uint8_t *rm_ptr = rm_host + w * strides[0] + z * strides[1] + (uint64_t)band0 * full.tile_h * strides[2];
                 uint8_t *q_ptr = q_mem + tile_record_offset(full, w, z, band0, 0);
                 uint8_t *b = q_on_device ? q_ptr : ctx->stage_b[slot];
                 const uint64_t q_len = (uint64_t)nb * full.Ct * full.tile_bytes;
@@ -455,7 +458,7 @@ int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_
                 }
                 cudaStream_t kernel_after = ctx->s_in;
                 if (direction == 0) {
-                    if ((e = copy_rows(a, rm_ptr, (uint64_t)nb * 32u, ctx->s_in, true)) != cudaSuccess)
+                    if ((e = copy_rows(a, rm_ptr, (uint64_t)nb * full.tile_h, ctx->s_in, true)) != cudaSuccess)
                         return cuda_fail(e, "host to device copy");
                 } else if (!q_on_device) {
                     if ((e = cudaMemcpyAsync(b, q_ptr, q_len, cudaMemcpyHostToDevice, ctx->s_in)) != cudaSuccess)
@@ -479,7 +482,7 @@ int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_
                     if (!q_on_device && (e = cudaMemcpyAsync(q_ptr, b, q_len, cudaMemcpyDeviceToHost, ctx->s_out)) != cudaSuccess)
                         return cuda_fail(e, "device to host copy");
                 } else {
-                    if ((e = copy_rows(a, rm_ptr, (uint64_t)nb * 32u, ctx->s_out, false)) != cudaSuccess)
+                    if ((e = copy_rows(a, rm_ptr, (uint64_t)nb * full.tile_h, ctx->s_out, false)) != cudaSuccess)
                         return cuda_fail(e, "device to host copy");
                 }
                 cudaEventRecord(ctx->ev_out[slot], ctx->s_out);
@@ -540,10 +543,10 @@ int64_t buda_io_size_bytes(int df, int untilized, uint32_t ublock_ct, uint32_t u
     }
     const int64_t tb = buda_tile_bytes(df, 1);
     if (tb < 0) return -1;
-    if (tile_height == 32 && tile_width == 32) return tiles * tb;
-    // smaller tiles keep the header and scale the payload
-    const int64_t payload = (tb - 32) * (int64_t)tile_height * tile_width / 1024;
-    return tiles * (payload + 32);
+    // Tiny tiles keep full-size records: the reference's tile size has no tile-dimension term
+    // (balancer_utils.hpp:24-51) and its allocator sizes every queue with the default tile dims
+    // (placer/allocator_utils.cpp:33-43), which is also what the pack kernels write.
+    return tiles * tb;
 }
 
 int64_t buda_tilized_bytes(const buda_queue_geom *geom, const uint32_t shape[4], int df, int with_header)
@@ -898,6 +901,30 @@ int buda_i8_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W
     cudaError_t e = launch_i8_gemm(A, M, K, lda, W_tiles, N, scale, scale_len, zero_point, out_mode, C, ldc, ctx->sm_count,
                                    (cudaStream_t)stream, ctx->status, msg, sizeof(msg));
     if (e != cudaSuccess) return msg[0] ? fail(BUDA_RUNTIME_ERROR, "%s", msg) : cuda_fail(e, "int8 gemm launch failed");
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return BUDA_SUCCESS;
+}
+
+int buda_prestride(const void *src, int elem_bytes, const uint32_t shape[4], const uint64_t strides_bytes[4], int stride,
+                   const int *xy_offsets, int n_offsets, void *dst, uint32_t dst_rows, uint32_t dst_cols, void *stream)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    if (!src || !dst || !shape || !strides_bytes || !xy_offsets) return fail(BUDA_RUNTIME_ERROR, "null argument");
+    if (elem_bytes != 1 && elem_bytes != 2 && elem_bytes != 4) return fail(BUDA_RUNTIME_ERROR, "element size %d is not 1, 2 or 4", elem_bytes);
+    if (stride < 1 || n_offsets < 1 || n_offsets > 64) return fail(BUDA_RUNTIME_ERROR, "stride %d with %d offsets is not supported", stride, n_offsets);
+    for (int k = 0; k < n_offsets; k++)
+        if (xy_offsets[2 * k] < 0 || xy_offsets[2 * k] >= stride || xy_offsets[2 * k + 1] < 0 || xy_offsets[2 * k + 1] >= stride)
+            return fail(BUDA_RUNTIME_ERROR, "offset %d = (%d, %d) lies outside the %dx%d stride window", k, xy_offsets[2 * k],
+                        xy_offsets[2 * k + 1], stride, stride);
+    if (strides_bytes[3] != (uint64_t)elem_bytes) return fail(BUDA_RUNTIME_ERROR, "innermost stride must equal the element size");
+    const uint64_t hs = (shape[2] + (uint32_t)stride - 1) / (uint32_t)stride, ws = (shape[3] + (uint32_t)stride - 1) / (uint32_t)stride;
+    if ((uint64_t)n_offsets * shape[1] > dst_rows || hs * ws > dst_cols)
+        return fail(BUDA_RUNTIME_ERROR, "prestrided tensor [%llu x %llu] does not fit the destination [%u x %u]",
+                    (unsigned long long)n_offsets * shape[1], (unsigned long long)(hs * ws), dst_rows, dst_cols);
+    cudaError_t e = launch_prestride(src, elem_bytes, shape, strides_bytes, stride, xy_offsets, n_offsets, dst, dst_rows, dst_cols,
+                                     ctx->sm_count, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "prestride launch failed");
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return BUDA_SUCCESS;
 }

@@ -257,9 +257,79 @@ tt_dram_io_desc make_queue_desc(const std::string &name, std::array<std::uint32_
 // ------------------------------------------------------------------------------------------------
 // push
 // ------------------------------------------------------------------------------------------------
+namespace
+{
+// Device memory freed when the scope ends.
+struct DeviceScratch
+{
+    void *p = nullptr;
+    ~DeviceScratch()
+    {
+        if (p)
+            buda_free(p);
+    }
+};
+
+// A queue whose descriptor carries a StrideDescriptor takes the ORIGINAL [w, z, H, W] activation and stores its
+// prestrided form [w, 1, z*s*s, (H/s)*(W/s)] (reference: the backend applies the descriptor inside push_input,
+// pybuda/pybuda/tensor.py:1415-1422; golden op/eval/pybuda/tm.py:316-335).
+DEVICE_STATUS_CODE push_prestrided(const tt_dram_io_desc &q, const tt_PytorchTensorDesc &tensor, const bool push_one,
+                                   const int timeout_in_seconds, const int ram_ptr)
+{
+    const Stride &sd = q.s_descriptor;
+    if (sd.xy_offsets.empty() || sd.xy_offsets.size() > 64)
+        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: stride descriptor needs 1..64 xy offsets");
+    if (tensor.ptr == nullptr)
+        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: tensor descriptor has a null pointer");
+    if (q.t != 1)
+        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: a prestriding queue has t == 1");
+    const std::uint32_t es = tensor.itemsize;
+    std::uint64_t expect = es;
+    for (int i = 3; i >= 0; i--)
+    {
+        if (tensor.shape[i] != 1 && tensor.strides[i] != expect)
+            return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: a prestrided push needs a dense row-major tensor");
+        expect *= tensor.shape[i];
+    }
+    const std::uint64_t src_bytes = tensor.numel() * es;
+    DeviceScratch staged, out;
+    const void *src = tensor.ptr;
+    if (!on_device(tensor.ptr))
+    {
+        if (buda_malloc(&staged.p, src_bytes) != BUDA_SUCCESS || buda_memcpy(staged.p, tensor.ptr, src_bytes, 0, nullptr) != BUDA_SUCCESS)
+            return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: " + cabi_error());
+        src = staged.p;
+    }
+    const std::uint32_t rows = q.rows(), cols = q.cols(), w = tensor.shape[0];
+    if (buda_malloc(&out.p, (std::uint64_t)w * rows * cols * es) != BUDA_SUCCESS)
+        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: " + cabi_error());
+    std::vector<int> xy;
+    for (const auto &o : sd.xy_offsets)
+    {
+        xy.push_back(o.first);
+        xy.push_back(o.second);
+    }
+    const std::uint64_t dense[4] = {(std::uint64_t)tensor.shape[1] * tensor.shape[2] * tensor.shape[3] * es,
+                                    (std::uint64_t)tensor.shape[2] * tensor.shape[3] * es, (std::uint64_t)tensor.shape[3] * es, es};
+    if (int rc = buda_prestride(src, (int)es, tensor.shape.data(), dense, sd.stride, xy.data(), (int)sd.xy_offsets.size(), out.p, rows,
+                                cols, nullptr);
+        rc != BUDA_SUCCESS)
+        return from_cabi(rc, "push_input (prestride)");
+    if ((std::uint64_t)rows * cols * es > 0xffffffffull)
+        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: prestrided entry exceeds the descriptor's 32-bit strides");
+    const std::uint32_t entry_bytes = (std::uint32_t)((std::uint64_t)rows * cols * es);
+    const tt_PytorchTensorDesc pre(out.p, es, tensor.format, {w, 1, rows, cols}, {entry_bytes, entry_bytes, cols * es, es}, 4);
+    tt_dram_io_desc plain = q;
+    plain.s_descriptor = Stride{};
+    return push_input(plain, pre, push_one, timeout_in_seconds, ram_ptr);
+}
+}  // namespace
+
 DEVICE_STATUS_CODE push_input(const tt_dram_io_desc &q, const tt_PytorchTensorDesc &tensor, const bool push_one,
                               const int timeout_in_seconds, const int ram_ptr)
 {
+    if (q.s_descriptor.stride > 1)
+        return push_prestrided(q, tensor, push_one, timeout_in_seconds, ram_ptr);
     const std::string why = check_tensor_fits(q, tensor);
     if (!why.empty())
         return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: " + why);

@@ -14,7 +14,7 @@ import torch
 
 from . import TILE_DIM
 from ._C import DataFormat
-from ._C.backend_api import PytorchTensorDesc, TilizedTensorDesc
+from ._C.backend_api import DramIODesc, PytorchTensorDesc, StrideDescriptor, TilizedTensorDesc
 
 SomeTensor = torch.Tensor
 
@@ -496,3 +496,122 @@ def to_pt_tensors(tensors, convert_format: bool = False) -> Tuple[torch.Tensor, 
 
 def to_buda_tensors(tensors) -> Tuple[Tensor, ...]:
     return tuple(t if isinstance(t, Tensor) else Tensor.create_from_torch(t) for t in tensors)
+
+
+# ------------------------------------------------------------------------------------------------
+# Runtime tensor transforms: what the host does to an input right before it is pushed
+# (reference: pybuda/pybuda/tensor.py:1382-1447; the transform record is bound from C++ at
+# pybuda/csrc/graph_lib/python_bindings.cpp:317-371 — the graph library is not part of this path, so the
+# record is a plain Python class with the same field names and JSON form).
+# ------------------------------------------------------------------------------------------------
+import json
+from enum import Enum
+
+
+def align_up(v: int, a: int) -> int:
+    return (v + a - 1) // a * a
+
+
+class RuntimeTensorTransformType(Enum):
+    NoTransform = 0
+    ReinterpretShape = 1
+    Prestride = 2
+    EmbeddingIndex = 3
+    ConstantInput = 4
+    Unpad = 5
+    Concatenate = 6
+
+
+class RuntimeTensorTransform:
+    def __init__(self, type=RuntimeTensorTransformType.NoTransform, original_shape=(), reinterpreted_shape=(), unpadded_shape=(),
+                 stride_height=1, stride_width=1, kernel_height=1, kernel_width=1):
+        self.type = type
+        self.original_shape = TensorShape(*original_shape)
+        self.reinterpreted_shape = TensorShape(*reinterpreted_shape)
+        self.unpadded_shape = TensorShape(*unpadded_shape)
+        self.stride_height, self.stride_width = stride_height, stride_width
+        self.kernel_height, self.kernel_width = kernel_height, kernel_width
+
+    def to_json(self):
+        return {"type": self.type.name, "original_shape": list(self.original_shape.dims),
+                "reinterpreted_shape": list(self.reinterpreted_shape.dims), "unpadded_shape": list(self.unpadded_shape.dims),
+                "stride_height": self.stride_height, "stride_width": self.stride_width,
+                "kernel_height": self.kernel_height, "kernel_width": self.kernel_width}
+
+    @classmethod
+    def from_json(cls, j):
+        return cls(RuntimeTensorTransformType[j["type"]], j.get("original_shape", ()), j.get("reinterpreted_shape", ()),
+                   j.get("unpadded_shape", ()), j.get("stride_height", 1), j.get("stride_width", 1), j.get("kernel_height", 1),
+                   j.get("kernel_width", 1))
+
+    def __repr__(self):
+        return f"RuntimeTensorTransform({self.to_json()})"
+
+
+def _embedding_index(tensor: torch.Tensor, original_shape: Tuple[int, ...], queue: DramIODesc):
+    """Lay a 1-D vector of row indices out the way an embedding op reads it: padded with all-ones (an invalid
+    index) to a whole number of 32x32 tiles, one tile row per 32 indices, transposed inside the tile rows
+    (reference tensor.py:1382-1413)."""
+    assert queue.data_format in [DataFormat.RawUInt8, DataFormat.RawUInt16, DataFormat.RawUInt32]
+    assert len(tensor.shape) <= 2, "Must be a 1d tensor"
+    assert len(original_shape) <= 1 or original_shape[-2] == 1, "Must be a 1d tensor"
+    assert len(original_shape) <= 2 or original_shape[-3] == 1, "Must be a 1d tensor"
+
+    q_rt = queue.bufq_grid_dim_r * queue.mblock_m * queue.ublock_rt
+    w = tensor.shape[0] if len(tensor.shape) > 1 else 1
+    pad = align_up(tensor.shape[-1], TILE_DIM) - tensor.shape[-1]
+    tensor = torch.nn.functional.pad(tensor, (0, pad))
+    tensor = tensor.reshape(w, 1, 1, tensor.shape[-1])
+    tensor[:, :, :, original_shape[-1]:] = ~torch.tensor(0, dtype=tensor.dtype)
+    tensor = tensor.view(w, q_rt, -1, TILE_DIM)
+    pad = align_up(tensor.shape[-2], TILE_DIM) - tensor.shape[-2]
+    tensor = torch.nn.functional.pad(tensor, (0, 0, 0, pad))
+    tensor = tensor.view(w, q_rt, -1, TILE_DIM, TILE_DIM)
+    tensor = tensor.transpose(2, 3).reshape(w, 1, q_rt * TILE_DIM, -1)
+
+    assert len(tensor.shape) == 4, "_embedding_index: rank changed"
+    assert tensor.shape[0] == w, "_embedding_index: w changed"
+    assert tensor.shape[1] == queue.t, "_embedding_index: t changed"
+    assert tensor.shape[2] == (queue.bufq_grid_dim_r * queue.mblock_m * queue.ublock_rt * TILE_DIM), "_embedding_index: tensor dims mismatch q dims"
+    assert tensor.shape[3] == (queue.bufq_grid_dim_c * queue.mblock_n * queue.ublock_ct * TILE_DIM), "_embedding_index: tensor dims mismatch q dims"
+    return tensor
+
+
+def _reinterpret_shape(tensor: torch.Tensor, shape: List[int], queue: DramIODesc, tile_bcast_dims: List[int]):
+    """View the tensor in the shape the compiled graph expects, then pad it to the queue's tiles (tensor.py:1407-1413)."""
+    tensor = tensor.contiguous().view(shape)
+    tensor = pad_pytorch_tensor_to_buda(tensor, tile_bcast_dims, squeeze=True, microbatch=queue.input_count,
+                                        tile_r=queue.tile_height, tile_c=queue.tile_width)
+    return tensor, queue
+
+
+def _prestride_shape(tensor: torch.Tensor, stride_height: int, stride_width: int, queue: DramIODesc):
+    """The tensor is pushed as it is; the queue's stride descriptor makes push_input store its prestrided form
+    (tensor.py:1415-1422)."""
+    assert stride_height == stride_width, "Backend supports only square strides for prestriding transform"
+    stride = stride_height
+    stride_desc = StrideDescriptor()
+    stride_desc.stride = stride
+    stride_desc.xy_offsets = [(x, y) for y in range(stride) for x in range(stride)]
+    queue.s_descriptor = stride_desc
+    return tensor, queue
+
+
+def do_runtime_transform(transform, tensor, q, tile_bcast_dims):
+    if transform.type == RuntimeTensorTransformType.EmbeddingIndex:
+        return _embedding_index(tensor, transform.original_shape.dims, q), q
+    elif transform.type == RuntimeTensorTransformType.ReinterpretShape:
+        return _reinterpret_shape(tensor, list(transform.reinterpreted_shape.dims), q, tile_bcast_dims)
+    elif transform.type == RuntimeTensorTransformType.NoTransform:
+        return tensor, q
+    elif transform.type == RuntimeTensorTransformType.Prestride:
+        return _prestride_shape(tensor, transform.stride_height, transform.stride_width, q)
+    else:
+        assert False, f"Unsupported runtime transform type: {transform.type}"
+
+
+def eval_runtime_transform(transform, inp, q, tile_bcast_dims):
+    if isinstance(transform, str):
+        transform = RuntimeTensorTransform.from_json(json.loads(transform))
+    return do_runtime_transform(transform, inp, q, tile_bcast_dims)
+
