@@ -366,11 +366,10 @@ cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, 
     }
     // Kernel choice: gemm_kernel_choice() (0 auto, 1 single-CTA, 2 CTA pair).  Auto gives the pair kernel every
     // problem with more than 256 rows (below that its 512-row tile would be mostly padding).
-    static int decode_warps = 0;
-    if (decode_warps == 0) {
+    static const int decode_warps = [] {
         const char *env = getenv("BUDA_GEMM_DECODE_WARPS");  // single-CTA kernel only: 8 (default, measured fastest) or 16
-        decode_warps = (env && atoi(env) == 16) ? 16 : 8;
-    }
+        return (env && atoi(env) == 16) ? 16 : 8;
+    }();
     const int forced = gemm_kernel_choice(-1);
     Params p;
     p.W = static_cast<const uint8_t *>(W);
@@ -385,16 +384,16 @@ cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, 
     const bool use_pair = forced == 2 || (forced == 0 && M > 256);
     if (use_pair) return launch_bfp8b_gemm_pair(tmap, p, sm_count, stream);
 
-    static bool attr_done[64] = {};
+    static std::atomic<bool> attr_done[64];
     int dev = 0;
     cudaGetDevice(&dev);
     dev &= 63;
-    if (!attr_done[dev]) {
+    if (!attr_done[dev].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(bfp8b_gemm_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(bfp8b_gemm_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;
-        attr_done[dev] = true;
+        attr_done[dev].store(true, std::memory_order_release);
     }
     uint32_t grid = p.m_tiles * p.n_tiles;
     if (grid > (uint32_t)sm_count) grid = (uint32_t)sm_count;

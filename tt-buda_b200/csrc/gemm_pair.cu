@@ -27,10 +27,12 @@
 //                 CTAs' barriers (multicast commit).  peer: relays "my activations landed" to the leader
 //   warps 0-7     epilogue for this CTA's 2 x 128 rows (two warps per tensor-memory lane quadrant, half
 //                 of the columns each); both CTAs' epilogues release the accumulators on the leader's
-//                 acc_empty barrier
+//                 acc_empty barrier.  In a launch that also feeds peer devices the same warps then forward
+//                 the piece they wrote to the peers' copies while the next tile's MMAs run
 // Every mbarrier wait is bounded; a wait that gives up raises the device status word, the CTA winds
 // down, its partner runs into its own limit, and both meet at the closing cluster barrier (tensor
 // memory is freed on every path).
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 
@@ -62,17 +64,15 @@ constexpr int kProducerWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1, kFirstDecodeW
 constexpr int kThreads = 32 * (kEpiWarps + 1 + 1 + kDecodeWarps);
 constexpr int kTmemCols = 512;
 
-constexpr int kEpiStageBytes = 32 * 128;           // per epilogue warp: 32 rows x 64 bfloat16 columns
 
-// Shared-memory plan.  A launch that also writes peers' memory (kScatter) gives up one activation stage for the
-// epilogue's staging tiles; the plain launch keeps four activation stages and stores straight from registers.
+// Shared-memory plan (the same for a launch that also writes peers' memory, kScatter).
 template <bool kScatter>
 struct Layout {
-    static constexpr int kAStages = kScatter ? 3 : 4;   // activation ring (per CTA: two 128-row boxes per stage)
+    static constexpr int kAStages = 4;                  // activation ring (per CTA: two 128-row boxes per stage)
     static constexpr int kSmemA = 0;
     static constexpr int kSmemB = kSmemA + kAStages * kABytes;
     static constexpr int kSmemEpi = kSmemB + kBStages * kBBytes;
-    static constexpr int kSmemBar = kSmemEpi + (kScatter ? kEpiWarps * kEpiStageBytes : 0);
+    static constexpr int kSmemBar = kSmemEpi;
     static constexpr int kNumBars = 3 * kAStages + 2 * kBStages + 2;
     static constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 16 + 1024;
 };
@@ -140,14 +140,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     using KT = KindTraits<Kind>;
     using L = Layout<kScatter>;
     constexpr int kBK = KT::kBK;
-    constexpr int kAStages = L::kAStages, kSmemA = L::kSmemA, kSmemB = L::kSmemB, kSmemEpi = L::kSmemEpi, kSmemBar = L::kSmemBar,
+    constexpr int kAStages = L::kAStages, kSmemA = L::kSmemA, kSmemB = L::kSmemB, kSmemBar = L::kSmemBar,
                   kNumBars = L::kNumBars;
     extern __shared__ uint8_t smem_raw[];
     // identical carve-up in both CTAs: the MMA addresses the peer's operands by the leader's offsets
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *sA = smem + kSmemA;
     uint8_t *sB = smem + kSmemB;
-    uint8_t *sEpi = smem + kSmemEpi;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kSmemBar);
     uint64_t *full_a = bars;                    // [kAStages] this CTA's activations landed (TMA bytes)
     uint64_t *peer_a = full_a + kAStages;       // [kAStages] leader only: the peer's activations landed
@@ -412,42 +411,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     tmem_ld32_issue(taddr + c * 64, v0);
                     tmem_ld32_issue(taddr + c * 64 + 32, v1);
                     tmem_ld_wait();
-                    if constexpr (Kind == kKindBfp8 && kScatter) {
-                        // Peers' copies go through shared memory, so that 8 lanes store one full 128-byte line of a
-                        // row: the lane that read row r writes its 64 bfloat16 values as row r of the warp's staging
-                        // tile (16-byte chunks XOR-swizzled by the row), then lanes re-read the tile four rows at a
-                        // time.  NVLink carries whole lines instead of 16-byte pieces (measured 3.5x faster).
-                        uint8_t *stg = sEpi + warp * kEpiStageBytes;
-#pragma unroll
-                        for (int q = 0; q < 8; q++) {
-                            const uint32_t(&v)[32] = q < 4 ? v0 : v1;
-                            const int b = (q & 3) * 8;
-                            uint4 o;
-                            o.x = pack_bf16x2(__uint_as_float(v[b]), __uint_as_float(v[b + 1]));
-                            o.y = pack_bf16x2(__uint_as_float(v[b + 2]), __uint_as_float(v[b + 3]));
-                            o.z = pack_bf16x2(__uint_as_float(v[b + 4]), __uint_as_float(v[b + 5]));
-                            o.w = pack_bf16x2(__uint_as_float(v[b + 6]), __uint_as_float(v[b + 7]));
-                            *reinterpret_cast<uint4 *>(stg + lane * 128 + ((q ^ (lane & 7)) << 4)) = o;
-                        }
-                        __syncwarp();
-                        const int64_t row_base = row - lane;
-                        const int ch = lane & 7;
-#pragma unroll
-                        for (int it = 0; it < 8; it++) {
-                            const int rr = it * 4 + (lane >> 3);
-                            const uint4 val = *reinterpret_cast<const uint4 *>(stg + rr * 128 + ((ch ^ (rr & 7)) << 4));
-#ifdef PAIR_EXP_NO_STORE
-                            if (row_base + rr < p.M && val.x == 0x7fc12345u)
-#else
-                            if (row_base + rr < p.M)
-#endif
-                            {
-                                const int64_t eo = (row_base + rr) * p.ldc + (int64_t)n_blk * kBN + col_half * (kBN / 2) + c * 64 + ch * 8;
-                                for (int d = 1; d < p.n_dst; d++) *reinterpret_cast<uint4 *>(p.C[d] + eo) = val;
-                            }
-                        }
-                        __syncwarp();
-                    }
 #ifdef PAIR_EXP_NO_STORE
                     if (row < p.M && v0[0] == 0x7fc12345u)
 #else
@@ -469,6 +432,30 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(acc_empty), 0));
+            if constexpr (Kind == kKindBfp8 && kScatter) {
+                // The accumulators are released: the next tile's MMAs run while this warp forwards the piece of the
+                // output it has just written (its own 32 rows x 128 columns of both halves) to the peers.  It
+                // re-reads the piece from this device's memory (L2) with lanes running along the row, so every
+                // store instruction carries two whole 256-byte row segments over NVLink instead of 32 fragments
+                // of 16 bytes; nothing is read from a peer.  __syncwarp orders the lanes' own stores before the
+                // re-read; ld.global.cg does not look in L1.
+                __syncwarp();
+                const int ch = lane & 15;
+#pragma unroll 1
+                for (int h = 0; h < 2; h++) {
+                    const int64_t row_base = (int64_t)m_blk * kPairM + h * 256 + rank * 128 + quad * 32;
+                    const int64_t col_base = (int64_t)n_blk * kBN + col_half * (kBN / 2) + ch * 8;
+#pragma unroll 4
+                    for (int it = 0; it < 16; it++) {
+                        const int64_t grow = row_base + it * 2 + (lane >> 4);
+                        if (grow < p.M) {
+                            const int64_t eo = grow * p.ldc + col_base;
+                            const uint4 val = __ldcg(reinterpret_cast<const uint4 *>(p.C[0] + eo));
+                            for (int d = 1; d < p.n_dst; d++) *reinterpret_cast<uint4 *>(p.C[d] + eo) = val;
+                        }
+                    }
+                }
+            }
         }
     }
 
@@ -489,12 +476,12 @@ cudaError_t launch_pair(const CUtensorMap &tmap, const gemm::Params &p_in, int s
 {
     using namespace gemm_pair;
     constexpr int kSmemBytes = Layout<kScatter>::kSmemBytes;
-    static bool attr_done[64] = {};
-    static int max_pairs[64] = {};
+    static std::atomic<int> max_pairs[64];   // 0 = this device has not been set up for this instantiation yet
     int dev = 0;
     cudaGetDevice(&dev);
     dev &= 63;
-    if (!attr_done[dev]) {
+    int resident = max_pairs[dev].load(std::memory_order_acquire);
+    if (resident == 0) {
         cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<Kind, kScatter>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;
         // how many pairs the device can hold at once (SMs that cannot be paired inside their GPC stay idle)
@@ -515,9 +502,9 @@ cudaError_t launch_pair(const CUtensorMap &tmap, const gemm::Params &p_in, int s
             (void)cudaGetLastError();
             n = sm_count / 2;
         }
-        max_pairs[dev] = n;
+        resident = n;
         if (getenv("BUDA_GEMM_VERBOSE")) fprintf(stderr, "gemm pair kernel (kind %d): %d resident CTA pairs on %d SMs\n", Kind, n, sm_count);
-        attr_done[dev] = true;
+        max_pairs[dev].store(n, std::memory_order_release);
     }
     gemm::Params p = p_in;
     p.m_tiles = (uint32_t)((p.M + kPairM - 1) / kPairM);
@@ -525,7 +512,7 @@ cudaError_t launch_pair(const CUtensorMap &tmap, const gemm::Params &p_in, int s
     p.k_blocks = (uint32_t)(p.K / KindTraits<Kind>::kBK);
     p.Nt = (uint32_t)(p.N / 32);
     uint32_t pairs = p.m_tiles * p.n_tiles;
-    if (pairs > (uint32_t)max_pairs[dev]) pairs = (uint32_t)max_pairs[dev];
+    if (pairs > (uint32_t)resident) pairs = (uint32_t)resident;
     gemm_pair_kernel<Kind, kScatter><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap, p);
     return cudaGetLastError();
 }

@@ -20,6 +20,8 @@
 //     exponent is a 4-lane-wide warp-shuffle maximum, and a warp covers 8 consecutive rows of one
 //     face so its stores form one contiguous run of the record.
 #include "bfp_codec.cuh"
+#include <atomic>
+
 #include "buda_common.cuh"
 
 namespace buda {
@@ -338,11 +340,12 @@ static cudaError_t launch_staged(const TileJob &job, const PtrTable &ptrs, int s
                                  unsigned int *status)
 {
     using Cfg = PackCfg<M, ES>;
-    static int per_sm_cache[64] = {};
+    static std::atomic<int> per_sm_cache[64];   // 0 = not yet looked up on this device (concurrent first calls store the same value)
     int dev = 0;
     cudaGetDevice(&dev);
     dev &= 63;
-    if (per_sm_cache[dev] == 0) {
+    int per_sm = per_sm_cache[dev].load(std::memory_order_acquire);
+    if (per_sm == 0) {
         cudaError_t e = cudaFuncSetAttribute(pack_staged_kernel<M, ES, AF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Cfg::smem_bytes);
         if (e != cudaSuccess) return e;
@@ -350,9 +353,10 @@ static cudaError_t launch_staged(const TileJob &job, const PtrTable &ptrs, int s
         e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, pack_staged_kernel<M, ES, AF>, kStagedThreads,
                                                           Cfg::smem_bytes);
         if (e != cudaSuccess) return e;
-        per_sm_cache[dev] = n < 1 ? 1 : (n > 4 ? 4 : n);
+        per_sm = n < 1 ? 1 : (n > 4 ? 4 : n);
+        per_sm_cache[dev].store(per_sm, std::memory_order_release);
     }
-    uint32_t grid = (uint32_t)(sm_count * per_sm_cache[dev]);
+    uint32_t grid = (uint32_t)(sm_count * per_sm);
     if (grid > job.total_items) grid = job.total_items;
     pack_staged_kernel<M, ES, AF><<<grid, kStagedThreads, Cfg::smem_bytes, stream>>>(job, ptrs, status);
     return cudaGetLastError();

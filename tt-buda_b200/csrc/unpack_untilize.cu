@@ -9,6 +9,8 @@
 // into a padded row-major band in shared memory, and the band leaves with one bulk async store
 // per row.  The direct kernel (any alignment) gives each block to four lanes.
 #include "bfp_codec.cuh"
+#include <atomic>
+
 #include "buda_common.cuh"
 
 namespace buda {
@@ -300,11 +302,12 @@ static cudaError_t launch_ustaged(const TileJob &job, const PtrTable &ptrs, int 
                                   unsigned int *status)
 {
     using Cfg = UnpackCfg<M, ES>;
-    static int per_sm_cache[64] = {};
+    static std::atomic<int> per_sm_cache[64];   // 0 = not yet looked up on this device (concurrent first calls store the same value)
     int dev = 0;
     cudaGetDevice(&dev);
     dev &= 63;
-    if (per_sm_cache[dev] == 0) {
+    int per_sm = per_sm_cache[dev].load(std::memory_order_acquire);
+    if (per_sm == 0) {
         cudaError_t e = cudaFuncSetAttribute(unpack_staged_kernel<M, ES, AF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Cfg::smem_bytes);
         if (e != cudaSuccess) return e;
@@ -312,9 +315,10 @@ static cudaError_t launch_ustaged(const TileJob &job, const PtrTable &ptrs, int 
         e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, unpack_staged_kernel<M, ES, AF>, kUStagedThreads,
                                                           Cfg::smem_bytes);
         if (e != cudaSuccess) return e;
-        per_sm_cache[dev] = n < 1 ? 1 : (n > 4 ? 4 : n);
+        per_sm = n < 1 ? 1 : (n > 4 ? 4 : n);
+        per_sm_cache[dev].store(per_sm, std::memory_order_release);
     }
-    uint32_t grid = (uint32_t)(sm_count * per_sm_cache[dev]);
+    uint32_t grid = (uint32_t)(sm_count * per_sm);
     if (grid > job.total_items) grid = job.total_items;
     unpack_staged_kernel<M, ES, AF><<<grid, kUStagedThreads, Cfg::smem_bytes, stream>>>(job, ptrs, status);
     return cudaGetLastError();
