@@ -6,8 +6,10 @@
 //
 // Mirror image of the pack kernels: the staged kernel brings whole tile records into shared
 // memory with bulk async copies (one per tile), a thread decodes one 16-value block and writes it
-// into a padded row-major band in shared memory, and the band leaves with one bulk async store
-// per row.  The direct kernel (any alignment) gives each block to four lanes.
+// into a padded row-major band in shared memory, and the band leaves with plain coalesced stores
+// (lanes along the row, 512 contiguous bytes per warp instruction; measured 11-15 % faster than one
+// bulk async store per row, whose completion the next band had to wait for).  The direct kernel
+// (any alignment) gives each block to four lanes.
 #include "bfp_codec.cuh"
 #include <atomic>
 
@@ -36,7 +38,12 @@ struct UnpackCfg {
 #else
     static constexpr int stages = 4;
 #endif
-    static constexpr int smem_bytes = stages * in_stage_bytes + 2 * out_buf_bytes + stages * (int)sizeof(UItemMeta) +
+#ifdef BUDA_UNPACK_OUTBUFS
+    static constexpr int out_bufs = BUDA_UNPACK_OUTBUFS;
+#else
+    static constexpr int out_bufs = 2;
+#endif
+    static constexpr int smem_bytes = stages * in_stage_bytes + out_bufs * out_buf_bytes + stages * (int)sizeof(UItemMeta) +
                                       2 * stages * 8 + 16;
 };
 
@@ -71,7 +78,7 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t *in_stage = smem;
     uint8_t *out_buf = smem + S * Cfg::in_stage_bytes;
-    UItemMeta *meta = reinterpret_cast<UItemMeta *>(out_buf + 2 * Cfg::out_buf_bytes);
+    UItemMeta *meta = reinterpret_cast<UItemMeta *>(out_buf + Cfg::out_bufs * Cfg::out_buf_bytes);
     uint64_t *full = reinterpret_cast<uint64_t *>(meta + S);
     uint64_t *empty = full + S;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + S);
@@ -131,7 +138,7 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
         const uint32_t ph = (it / S) & 1u;
         const bool ok = mbar_wait_bounded(&full[s], ph, abort_flag, status, BUDA_DEVSTAT_UNPACK_FULL_WAIT);
         const UItemMeta m = meta[s];
-        uint8_t *ob = out_buf + (it & 1u) * Cfg::out_buf_bytes;
+        uint8_t *ob = out_buf + (it % Cfg::out_bufs) * Cfg::out_buf_bytes;
         const uint8_t *stage = in_stage + s * Cfg::in_stage_bytes;
 
         if (!ok) {
@@ -188,8 +195,31 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
                 *reinterpret_cast<uint4 *>(ob + row * Cfg::pitch + t * 32 * ES + (f & 1) * 16 * ES + part * 16) = v;
             }
         }
+#ifndef BUDA_UNPACK_BULK_OUT
+        // Every block of the band is decoded: the band leaves with plain coalesced stores, four rows per warp,
+        // lanes along the row (one warp instruction = 512 contiguous bytes).  The next item decodes into the other
+        // band buffer; this one is overwritten two items later, after the next item's barrier, by which time every
+        // warp has finished copying it out.
+        if (named_bar_or(1, kUConsumerThreads, !ok)) break;
+        if (tid == 0) mbar_arrive(&empty[s]);
+        {
+            const int chunks = (int)m.ntiles * 2 * ES;   // 16-byte chunks per row piece
+            uint8_t *dst0 = ptrs.dst[m.b] + (uint64_t)m.w * job.stride_w + rm_z_offset(job, m.z) +
+                            (uint64_t)m.rt * 32u * job.stride_r + (uint64_t)m.ct0 * 32u * ES;
+#pragma unroll
+            for (int rr = 0; rr < 32 / kUConsumerWarps; rr++) {
+                const int row = warp * (32 / kUConsumerWarps) + rr;
+                const uint8_t *src = ob + row * Cfg::pitch;
+                uint8_t *dst = dst0 + (uint64_t)row * job.stride_r;
+                for (int c = lane; c < chunks; c += 32)
+                    __stcs(reinterpret_cast<uint4 *>(dst + c * 16), *reinterpret_cast<const uint4 *>(src + c * 16));
+            }
+        }
+    }
+#else
         fence_async_smem();
-        if (warp == 0) bulk_wait_read_all();  // the previous item's row stores have left shared memory
+        // the band the NEXT item will overwrite (out_bufs - 1 items back) must have left shared memory
+        if (warp == 0) bulk_wait_read<Cfg::out_bufs - 2>();
         if (named_bar_or(1, kUConsumerThreads, !ok)) break;
         if (tid == 0) mbar_arrive(&empty[s]);
         if (warp == 0) {
@@ -199,6 +229,7 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
             bulk_commit();
         }
     }
+#endif
     if (warp == 0) bulk_wait_all();
 }
 
