@@ -401,3 +401,35 @@ def test_tiny_tiles(ops, oracle, th, df_name, dtype):
     with pytest.raises(ops._cabi.BudaError, match="32-row tiles"):
         ops.tilize_pack(x.cuda(), df, geom, path=0)
 
+
+@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("df_name,m", [("Bfp8_b", 7), ("Bfp4_b", 3), ("Bfp2_b", 1)])
+def test_committed_known_answers_on_the_gpu(ops, df_name, m, path):
+    """The CUDA kernels against tests/golden/bfp_kat.npz (exact rational arithmetic; independent of the CPU oracle):
+    the 256 blocks become the face rows of four 32x32 tiles."""
+    import os
+    k = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "bfp_kat.npz"))
+    x = np.zeros((1, 1, 32, 128), np.uint32)
+    for b in range(256):
+        t, blk = divmod(b, 64)
+        face, fr = divmod(blk, 16)
+        r, c = (face >> 1) * 16 + fr, t * 32 + (face & 1) * 16
+        x[0, 0, r, c:c + 16] = k["x"][b]
+    xt = torch.from_numpy(x.view(np.float32)).cuda()
+    df = getattr(ops.DF, df_name)
+    img = ops.tilize_pack(xt, df, path=path).cpu().numpy()
+    rec = 64 + 2 * (m + 1) * 64
+    assert img.size == 4 * rec
+    for b in range(256):
+        t, blk = divmod(b, 64)
+        r0 = t * rec
+        assert img[r0 + blk] == k[f"E{m}"][b], (b, "exponent")
+        got = img[r0 + 64 + blk * 2 * (m + 1): r0 + 64 + (blk + 1) * 2 * (m + 1)]
+        assert np.array_equal(got, k[f"data{m}"][b]), (b, "datums")
+    back = ops.unpack_untilize(torch.from_numpy(img).cuda(), df, (1, 1, 32, 128), path=path).cpu().numpy().view(np.uint32)
+    for b in range(256):
+        t, blk = divmod(b, 64)
+        face, fr = divmod(blk, 16)
+        r, c = (face >> 1) * 16 + fr, t * 32 + (face & 1) * 16
+        assert np.array_equal(back[0, 0, r, c:c + 16], k[f"decoded{m}"][b]), (b, "decode")
+

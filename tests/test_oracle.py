@@ -359,3 +359,41 @@ def test_tiny_tiles_equal_zero_padded_full_tiles(oracle, th):
         for r in range(rt):
             assert np.array_equal(back[:, :, r * th:(r + 1) * th].view(np.uint32), full[:, :, r * 32:r * 32 + th].view(np.uint32))
 
+
+def _kat():
+    import os
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "bfp_kat.npz"))
+
+
+@pytest.mark.parametrize("m", [7, 3, 1])
+def test_oracle_matches_committed_known_answers(oracle, m):
+    """tests/golden/bfp_kat.npz was computed in exact rational arithmetic (tests/golden/bfp_spec.py), independently of
+    the C oracle: 256 blocks incl. ties, saturation, denormals, Inf / NaN and both ends of the exponent range."""
+    k = _kat()
+    assert int(k["spec_version"][0]) == 1
+    for i in range(k["x"].shape[0]):
+        E, d = oracle.bfp_pack_block(k["x"][i], m)
+        assert E == int(k[f"E{m}"][i]) and np.array_equal(d, k[f"data{m}"][i]), i
+        y = oracle.bfp_unpack_block(E, d, m)
+        assert np.array_equal(y.view(np.uint32), k[f"decoded{m}"][i]), i
+
+
+def test_known_answer_generator_is_reproducible():
+    """The committed fixture is what the committed generator writes."""
+    import importlib.util, os, sys
+    gdir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    sys.path.insert(0, gdir)
+    try:
+        spec = importlib.util.spec_from_file_location("gen_bfp_kat", os.path.join(gdir, "gen_bfp_kat.py"))
+        gen = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(gen)
+        blocks = gen.hand_picked() + gen.random_blocks(256 - len(gen.hand_picked()), seed=20240)
+        k = _kat()
+        assert np.array_equal(np.array(blocks, dtype=np.uint32), k["x"])
+        from bfp_spec import encode_block
+        for i in (0, 3, 5, 17, 100, 255):
+            E, data = encode_block(blocks[i], 7)
+            assert E == int(k["E7"][i]) and list(data) == list(k["data7"][i])
+    finally:
+        sys.path.remove(gdir)
+
