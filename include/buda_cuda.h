@@ -119,6 +119,14 @@ int buda_tilize_pack_host(const void *src_host, int src_df, const uint32_t shape
                           const uint64_t strides_bytes[4], const buda_queue_geom *geom, int dst_df,
                           int with_header, void *dst_host, uint64_t dst_bytes, void *stream);
 
+/* buda_tilize_pack_host over n tensors of one shape (HOST arrays of n host pointers): the caller loop of
+ * push_to_queues / push_constants_and_parameters / update_device_paramaters (pybuda/pybuda/backend.py:448-493),
+ * hoisted into one call so that the copy-in / kernel / copy-out pipeline runs across tensor boundaries and is
+ * drained once.  Returns when every image is complete. */
+int buda_tilize_pack_host_batch(int n, const void *const *srcs_host, int src_df, const uint32_t shape[4],
+                                const uint64_t strides_bytes[4], const buda_queue_geom *geom, int dst_df, int with_header,
+                                void *const *dsts_host, uint64_t dst_bytes_each, void *stream);
+
 /* buda_tilize_pack_host for callers that must not allocate.  It has no counterpart in the reference.
  * Same arguments and result, but the device staging for the tensor and its image is a fixed 8 MiB
  * array inside the library (held by every GPU that loads the library until the process exits)

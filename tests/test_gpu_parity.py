@@ -433,3 +433,26 @@ def test_committed_known_answers_on_the_gpu(ops, df_name, m, path):
         r, c = (face >> 1) * 16 + fr, t * 32 + (face & 1) * 16
         assert np.array_equal(back[0, 0, r, c:c + 16], k[f"decoded{m}"][b]), (b, "decode")
 
+
+def test_host_batch_pipeline_matches_single_calls(ops, oracle):
+    """buda_tilize_pack_host_batch: n host tensors through one pipeline run; same bytes as one call per tensor."""
+    import ctypes
+    from pybuda import _cabi
+    shape = (1, 2, 256, 4096)                      # 8 MiB per tensor: several pipeline slices each
+    g = torch.Generator().manual_seed(77)
+    xs = [torch.randn(shape, generator=g).pin_memory() for _ in range(5)]
+    geom = _cabi.QueueGeom.for_shape(shape)
+    nbytes = _cabi.tilized_bytes(geom, shape, int(ops.DF.Bfp8_b), False)
+    outs = [torch.empty(nbytes, dtype=torch.uint8).pin_memory() for _ in xs]
+    shape_c, strides_c = _cabi.u32x4(shape), _cabi.u64x4(_cabi.dense_strides(list(shape), 4))
+    _cabi.check(_cabi.lib.buda_tilize_pack_host_batch(len(xs), _cabi.ptr_array([x.data_ptr() for x in xs]), 0, shape_c, strides_c,
+                                                      ctypes.byref(geom), int(ops.DF.Bfp8_b), 0,
+                                                      _cabi.ptr_array([o.data_ptr() for o in outs]), nbytes, None))
+    for x, o in zip(xs, outs):
+        assert np.array_equal(o.numpy(), oracle.tilize_pack(x.numpy(), oracle.Bfp8_b))
+    # a null entry is refused before anything runs
+    rc = _cabi.lib.buda_tilize_pack_host_batch(2, _cabi.ptr_array([xs[0].data_ptr(), 0]), 0, shape_c, strides_c, ctypes.byref(geom),
+                                               int(ops.DF.Bfp8_b), 0, _cabi.ptr_array([outs[0].data_ptr(), outs[1].data_ptr()]),
+                                               nbytes, None)
+    assert rc == _cabi.RUNTIME_ERROR
+

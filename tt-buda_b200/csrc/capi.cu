@@ -354,15 +354,18 @@ int status_after_sync(DevCtx *ctx)
 // The row-major tensor is in HOST memory; the queue image is in host memory (q_on_device == 0) or
 // already in device memory, possibly as a ring of `slots` entries (q_on_device == 1).
 // direction 0: row-major -> queue image; 1: queue image -> row-major.
-int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_t shape[4], const uint64_t strides[4],
-                  const buda_queue_geom *geom, int q_df, int with_header, const void *q_c, uint64_t q_bytes, int q_on_device,
-                  uint32_t slots, uint32_t slot0)
+// n > 1: the same conversion for n tensors of one shape (rm_hosts[i] <-> q_ptrs[i]); the copy-in / kernel /
+// copy-out pipeline keeps running across tensor boundaries and is drained once, at the end.
+int host_pipeline_n(int direction, int n, const void *const *rm_hosts, int rm_df, const uint32_t shape[4], const uint64_t strides[4],
+                    const buda_queue_geom *geom, int q_df, int with_header, const void *const *q_ptrs, uint64_t q_bytes,
+                    int q_on_device, uint32_t slots, uint32_t slot0)
 {
     DevCtx *ctx;
     if (int rc = get_ctx(&ctx)) return rc;
-    if (!rm_host_c || !q_c) return fail(BUDA_RUNTIME_ERROR, "null buffer");
-    uint8_t *rm_host = (uint8_t *)rm_host_c;
-    uint8_t *q_mem = (uint8_t *)q_c;
+    if (n <= 0) return BUDA_SUCCESS;
+    if (!rm_hosts || !q_ptrs) return fail(BUDA_RUNTIME_ERROR, "null buffer table");
+    for (int i = 0; i < n; i++)
+        if (!rm_hosts[i] || !q_ptrs[i]) return fail(BUDA_RUNTIME_ERROR, "null buffer");
     int mant, es;
     if (int rc = classify(rm_df, q_df, mant, es, direction == 1)) return rc;
     TileJob full;
@@ -395,6 +398,9 @@ int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_
     };
 
     if (!plan.sliced) {
+      for (int bi = 0; bi < n; bi++) {
+        uint8_t *rm_host = (uint8_t *)rm_hosts[bi];
+        uint8_t *q_mem = (uint8_t *)q_ptrs[bi];
         // one shot: the whole tensor goes through slot 0
         uint8_t *a = ctx->stage_a[0];
         uint8_t *b = q_on_device ? q_mem : ctx->stage_b[0];
@@ -428,11 +434,15 @@ int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_
         if (e != cudaSuccess) return cuda_fail(e, "copy");
         e = cudaStreamSynchronize(ctx->s_comp);
         if (e != cudaSuccess) return cuda_fail(e, "synchronize");
-        return status_after_sync(ctx);
+      }
+      return status_after_sync(ctx);
     }
 
     // sliced: each slice is a [1,1,bands*32,C] tensor whose records are one contiguous run of the image
     uint64_t k = 0;
+    for (int bi = 0; bi < n; bi++) {
+    uint8_t *rm_host = (uint8_t *)rm_hosts[bi];
+    uint8_t *q_mem = (uint8_t *)q_ptrs[bi];
     for (uint32_t w = 0; w < shape[0]; w++) {
         for (uint32_t z = 0; z < shape[1]; z++) {
             for (uint32_t sl = 0; sl < plan.slices_per_plane; sl++, k++) {
@@ -489,10 +499,21 @@ int host_pipeline(int direction, const void *rm_host_c, int rm_df, const uint32_
             }
         }
     }
+    }
     if ((e = cudaStreamSynchronize(ctx->s_out)) != cudaSuccess) return cuda_fail(e, "synchronize");
     if ((e = cudaStreamSynchronize(ctx->s_comp)) != cudaSuccess) return cuda_fail(e, "synchronize");
     if ((e = cudaStreamSynchronize(ctx->s_in)) != cudaSuccess) return cuda_fail(e, "synchronize");
     return status_after_sync(ctx);
+}
+
+int host_pipeline(int direction, const void *rm_host, int rm_df, const uint32_t shape[4], const uint64_t strides[4],
+                  const buda_queue_geom *geom, int q_df, int with_header, const void *q, uint64_t q_bytes, int q_on_device,
+                  uint32_t slots, uint32_t slot0)
+{
+    if (!rm_host || !q) return fail(BUDA_RUNTIME_ERROR, "null buffer");
+    const void *rms[1] = {rm_host};
+    const void *qs[1] = {q};
+    return host_pipeline_n(direction, 1, rms, rm_df, shape, strides, geom, q_df, with_header, qs, q_bytes, q_on_device, slots, slot0);
 }
 
 }  // namespace
@@ -613,6 +634,14 @@ int buda_tilize_pack_host(const void *src_host, int src_df, const uint32_t shape
 {
     (void)stream;
     return host_pipeline(0, src_host, src_df, shape, strides_bytes, geom, dst_df, with_header, dst_host, dst_bytes, 0, 0, 0);
+}
+
+int buda_tilize_pack_host_batch(int n, const void *const *srcs_host, int src_df, const uint32_t shape[4],
+                                const uint64_t strides_bytes[4], const buda_queue_geom *geom, int dst_df, int with_header,
+                                void *const *dsts_host, uint64_t dst_bytes_each, void *stream)
+{
+    (void)stream;
+    return host_pipeline_n(0, n, srcs_host, src_df, shape, strides_bytes, geom, dst_df, with_header, dsts_host, dst_bytes_each, 0, 0, 0);
 }
 
 int buda_unpack_untilize(const void *src, int src_df, int with_header, const buda_queue_geom *geom, void *dst, int dst_df,

@@ -54,6 +54,7 @@ _SIGS = {
     "buda_tilize_pack_batch": (_i, [_i, _vpp, _i, _u32p, _u64p, _gp, _i, _i, _vpp, _u64, _vp]),
     "buda_tilize_pack_batch_path": (_i, [_i, _vpp, _i, _u32p, _u64p, _gp, _i, _i, _vpp, _u64, _vp, _i]),
     "buda_tilize_pack_host": (_i, [_vp, _i, _u32p, _u64p, _gp, _i, _i, _vp, _u64, _vp]),
+    "buda_tilize_pack_host_batch": (_i, [_i, _vpp, _i, _u32p, _u64p, _gp, _i, _i, _vpp, _u64, _vp]),
     "buda_tilize_pack_host_noalloc": (_i, [_vp, _i, _u32p, _u64p, _gp, _i, _i, _vp, _u64, _vp]),
     "buda_unpack_untilize": (_i, [_vp, _i, _i, _gp, _vp, _i, _u32p, _u64p, _vp]),
     "buda_unpack_untilize_batch": (_i, [_i, _vpp, _i, _i, _gp, _vpp, _i, _u32p, _u64p, _vp]),
