@@ -1,0 +1,88 @@
+"""Queue side of the reference's BackendAPI (pybuda/pybuda/backend.py:341-493): the class methods that push
+tensors into device queues, read them back and pop them.  Same names, arguments, retry and assertion behaviour.
+The compile / run side of that class (netlists, programs, device bring-up) is not part of this path."""
+from threading import Event
+from typing import Dict, List, Optional, Tuple, Union
+
+import torch
+
+from ._C.backend_api import (BackendStatusCode, DramIODesc, PytorchTensorDesc, TilizedTensorDesc, free_tensor, get_output,
+                             pop_output, push_input)
+from .tensor import (RuntimeTensorTransform, RuntimeTensorTransformType, Tensor, pytorch_tensor_to_tensor_desc)
+
+
+class BackendAPI:
+    @classmethod
+    def push_input(cls, queue_desc: DramIODesc, tensor_desc: Union[PytorchTensorDesc, TilizedTensorDesc], single_input: bool = True,
+                   timeout_secs: int = 1, ram_address: int = 0):
+        if isinstance(tensor_desc, TilizedTensorDesc):
+            assert push_input(queue_desc, tensor_desc, timeout_secs, ram_address) == BackendStatusCode.Success, \
+                "Error while pushing tilized inputs"
+        else:
+            assert push_input(queue_desc, tensor_desc, single_input, timeout_secs, ram_address) == BackendStatusCode.Success, \
+                "Error while pushing inputs"
+
+    @classmethod
+    def push_to_queues(cls, ordered_input_queues: List[DramIODesc], tensors: List[PytorchTensorDesc], single_input: bool):
+        assert len(tensors) == len(ordered_input_queues), (
+            f"Incorrect number of tensors provided on input: tensors:{len(tensors)} vs ordered_input_queues:{len(ordered_input_queues)}")
+        for i, inq in enumerate(ordered_input_queues):
+            BackendAPI.push_input(inq, tensors[i], single_input, 1, -1)
+
+    @classmethod
+    def read_queues(cls, queues: List[DramIODesc], original_shapes: List[Tuple[int, ...]],
+                    runtime_tensor_transforms: Optional[List[RuntimeTensorTransform]], requires_grad: List[bool],
+                    single_output: bool, rd_ptr: int = -1, shutdown_event: Optional[Event] = None, clone: bool = False,
+                    has_microbatch_dim: bool = True) -> List[Tensor]:
+        """get_output on every queue (a read that times out is retried up to 10 times, as in the reference), then the
+        tile padding is cut off.  clone=False returns views of backend-owned memory that stay valid until pop_queues."""
+        ret, tensors, out_descs = [], [], []
+        if runtime_tensor_transforms is None:
+            runtime_tensor_transforms = [None] * len(queues)
+        for outq in queues:
+            out_desc = PytorchTensorDesc()
+            retry_count, timeout = 10, 1
+            resp = BackendStatusCode.RuntimeError
+            for _ in range(retry_count):
+                resp = get_output(outq, out_desc, single_output, timeout, rd_ptr)
+                if resp != BackendStatusCode.TimeoutError:
+                    break
+                if shutdown_event and shutdown_event.is_set():
+                    break
+            if resp == BackendStatusCode.TimeoutError:
+                if shutdown_event:
+                    shutdown_event.set()
+                raise RuntimeError("Timeout while reading " + outq.name)
+            assert resp == BackendStatusCode.Success, "Error while reading output"
+            tensors.append(Tensor.create_from_tensor_descriptor(out_desc))
+            out_descs.append(out_desc)
+
+        assert len(original_shapes) == len(tensors)
+        assert len(requires_grad) == len(tensors)
+        for i, tensor in enumerate(tensors):
+            tr = runtime_tensor_transforms[i]
+            reinterpreted = list(tr.reinterpreted_shape.dims) if tr is not None and tr.reinterpreted_shape.dims else None
+            unpadded = list(tr.unpadded_shape.dims) if tr is not None and tr.unpadded_shape.dims else None
+            tensor = tensor.narrow_to_original_shape(tuple(original_shapes[i]), reinterpreted, has_microbatch_dim=has_microbatch_dim,
+                                                     unpadded_shape=unpadded)
+            if requires_grad[i]:
+                tensor = tensor.detach()
+                tensor.set_requires_grad(True)
+            if clone:
+                tensor = tensor.clone()
+                free_tensor(out_descs[i])
+            ret.append(tensor)
+        return ret
+
+    @classmethod
+    def pop_queues(cls, queues: List[DramIODesc], single_output: bool):
+        for outq in queues:
+            assert pop_output(outq, single_output, 1) == BackendStatusCode.Success, "Error while popping output"
+
+    @classmethod
+    def push_constants_and_parameters(cls, queues: Dict[str, DramIODesc], values: Dict[str, torch.Tensor]):
+        """The reference walks the compiled graph's constant and parameter names and pushes each value to its
+        RandomAccess queue at address 0 (backend.py:473-493); here the caller names the queues."""
+        for name, q in queues.items():
+            df = q.data_format if int(q.data_format) >= 0xF0 else None       # raw formats keep their integer bits
+            BackendAPI.push_input(q, pytorch_tensor_to_tensor_desc(values[name].contiguous(), df), True, 1, 0)
