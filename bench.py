@@ -479,6 +479,41 @@ def main():
             dt = time.perf_counter() - t0
             cpu = {"value": n_cpu * ELEMS * BYTES_PER_ELEM / dt / 1e9, "unit": "GB/s", "cores": R.threads(), "kind": "port",
                    "sample": f"first {n_cpu} of the 64 tensors, one pass, OpenMP over all host cores"}
+            # the same CPU arm for the secondary kernels, each on a bounded sample (seconds in total)
+            if not args.no_extras:
+                def cpu_timed(fn, work, unit, cores, sample):
+                    fn()
+                    t0 = time.perf_counter()
+                    fn()
+                    return {unit: round(work / (time.perf_counter() - t0), 2), "cores": cores, "sample": sample}
+
+                prev = R.set_threads(1)
+                cpu_other = {"pack_bfp8_b_single_thread": cpu_timed(lambda: R.tilize_pack(hs[0][:, :, :1024], R.Bfp8_b),
+                                                                    ELEMS / 4 * BYTES_PER_ELEM / 1e9, "GB/s", 1,
+                                                                    "a quarter of one tensor, CPU port, one thread")}
+                R.set_threads(prev)
+                img0 = R.tilize_pack(hs[0], R.Bfp8_b)
+                cpu_other["unpack_bfp8_b"] = cpu_timed(lambda: R.unpack_untilize(img0, R.Bfp8_b, SHAPE), ELEMS * BYTES_PER_ELEM / 1e9,
+                                                       "GB/s", R.threads(), "one tensor, CPU port, OpenMP over all host cores")
+                nthr = torch.get_num_threads()
+                xq = torch.rand(32, 1024, 1024) * 12 - 6
+                scq = torch.tensor([0.05])
+                # the golden evaluation's own torch expressions (op/eval/pybuda/quantize.py:56-66, 79-93, 95-110)
+                cpu_other["quantize"] = cpu_timed(lambda: torch.clamp(torch.round(xq / scq) + 3, -128, 127).to(torch.int8),
+                                                  xq.numel() * 5 / 1e9, "GB/s", nthr, "config-3 tensor, torch CPU")
+                qq = torch.clamp(torch.round(xq / scq) + 3, -128, 127).to(torch.int8)
+                cpu_other["dequantize"] = cpu_timed(lambda: (qq.float() - 3) * scq, xq.numel() * 5 / 1e9, "GB/s", nthr,
+                                                    "config-3 tensor, torch CPU")
+                accq = torch.randint(-2 ** 20, 2 ** 20, (32, 1024, 1024), dtype=torch.int32)
+                scs_cpu = torch.rand(1024) * (1e-2 - 1e-4) + 1e-4
+                cpu_other["requantize"] = cpu_timed(lambda: torch.clamp(torch.round(accq.float() * scs_cpu + 0.0), -128, 127).to(torch.int8),
+                                                    xq.numel() * 5 / 1e9, "GB/s", nthr, "config-3 tensor, torch CPU")
+                am = torch.randn(256, 4096)
+                wm = torch.randn(4096, 16384) * 0.02
+                cpu_other["matmul_fp32"] = cpu_timed(lambda: am @ wm, 2.0 * 256 * 4096 * 16384 / 1e12, "TFLOP/s", nthr,
+                                                     "256 of the 8192 activation rows, torch CPU matmul (the golden matmul)")
+                cpu["other_kernels"] = cpu_other
+                del xq, qq, accq, am, wm, img0
         except Exception as exc:
             cpu = {"value": None, "unit": "GB/s", "error": str(exc)}
 

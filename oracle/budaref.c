@@ -69,6 +69,19 @@ int ref_threads(void)
 #endif
 }
 
+/* limits the OpenMP team of the following calls (the single-thread CPU baseline); returns the previous limit */
+int ref_set_threads(int n)
+{
+#ifdef _OPENMP
+    int prev = omp_get_max_threads();
+    if (n > 0) omp_set_num_threads(n);
+    return prev;
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
 /* ---------------------------------------------------------------------------------------------
  * Sizes
  * ------------------------------------------------------------------------------------------- */

@@ -65,6 +65,8 @@ def lib():
         vp, i32, i64, u32p = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.POINTER(ctypes.c_uint32)
         gp = ctypes.POINTER(Geom)
         L.ref_threads.restype = i32
+        L.ref_set_threads.restype = i32
+        L.ref_set_threads.argtypes = [i32]
         L.ref_tile_bytes.restype = ctypes.c_long
         L.ref_tile_bytes.argtypes = [i32, i32]
         L.ref_data_format_byte_size.restype = ctypes.c_long
@@ -106,6 +108,11 @@ def lib():
 
 def threads():
     return lib().ref_threads()
+
+
+def set_threads(n):
+    """Limit the OpenMP team of the following calls; returns the previous limit."""
+    return lib().ref_set_threads(int(n))
 
 
 _NP_DF = {np.dtype(np.float32): Float32, np.dtype(np.int8): Int8, np.dtype(np.int32): Int32,
