@@ -303,13 +303,21 @@ size_t buda_last_error(char *buf, size_t buf_len);
  * gave up (see BUDA_DEVSTAT_*); the function then returns BUDA_TIMEOUT_ERROR. */
 int buda_device_status(int *status_out);
 
+/* Self-test of the failure path every kernel of the library shares: launches one CTA that waits, with the
+ * library's bounded mbarrier wait, for a barrier phase that nothing completes, for at most limit_ms
+ * (1..1000) milliseconds; the wait then gives up, records BUDA_DEVSTAT_SELFTEST_WAIT in the device status word
+ * and the kernel returns normally.  Nothing faults, traps or spins without a limit; the context stays usable.
+ * buda_device_status() afterwards returns BUDA_TIMEOUT_ERROR with that code, once. */
+int buda_selftest_bounded_wait(uint32_t limit_ms, void *stream);
+
 enum {
     BUDA_DEVSTAT_OK = 0,
     BUDA_DEVSTAT_PACK_FULL_WAIT = 1,   /* pack: consumer waited too long for a staged band     */
     BUDA_DEVSTAT_PACK_EMPTY_WAIT = 2,  /* pack: producer waited too long for a free stage      */
     BUDA_DEVSTAT_UNPACK_FULL_WAIT = 3,
     BUDA_DEVSTAT_UNPACK_EMPTY_WAIT = 4,
-    BUDA_DEVSTAT_GEMM_WAIT = 5
+    BUDA_DEVSTAT_GEMM_WAIT = 5,
+    BUDA_DEVSTAT_SELFTEST_WAIT = 6     /* buda_selftest_bounded_wait: the wait that nothing completes ran out */
 };
 
 /* Number of kernels this library has launched in this process (for launch accounting). */

@@ -456,3 +456,23 @@ def test_host_batch_pipeline_matches_single_calls(ops, oracle):
                                                nbytes, None)
     assert rc == _cabi.RUNTIME_ERROR
 
+
+
+def test_bounded_wait_gives_up_and_the_context_stays_usable(ops, oracle):
+    """The failure path all kernels share, exercised without any fault: a one-CTA self-test kernel waits (with the
+    library's bounded wait, 20 ms limit) for a barrier nothing completes; the wait gives up, the status word names
+    it, the kernel returns normally, and the next launches work."""
+    from pybuda import _cabi
+    torch.cuda.synchronize()
+    assert _cabi.device_status() == (0, 0)
+    _cabi.check(_cabi.lib.buda_selftest_bounded_wait(20, None))
+    rc, st = _cabi.device_status()
+    assert rc == _cabi.TIMEOUT_ERROR and st == 6                      # BUDA_DEVSTAT_SELFTEST_WAIT
+    assert "gave up" in _cabi.last_error()
+    assert _cabi.device_status() == (0, 0)                            # read once, then clear
+    x = torch.randn(1, 1, 64, 96, generator=torch.Generator().manual_seed(1))
+    img = ops.tilize_pack(x.cuda(), ops.DF.Bfp8_b)
+    assert np.array_equal(img.cpu().numpy(), oracle.tilize_pack(x.numpy(), oracle.Bfp8_b))
+    assert _cabi.device_status() == (0, 0)
+    assert _cabi.lib.buda_selftest_bounded_wait(0, None) == _cabi.RUNTIME_ERROR      # limits outside 1..1000 ms are refused
+    assert _cabi.lib.buda_selftest_bounded_wait(5000, None) == _cabi.RUNTIME_ERROR

@@ -180,7 +180,7 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // Bounded wait on an mbarrier phase.  Returns false if the wait gave up (after recording `code`
 // in the device status word and raising *abort_flag so every other wait in the CTA ends at once).
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
-                                                  unsigned int *status, unsigned int code)
+                                                  unsigned int *status, unsigned int code, uint64_t limit_ns = kWaitLimitNs)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
@@ -188,7 +188,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
         // parked for up to 20 us at a time: no spinning, and the abort flag / deadline are still looked at
         if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
         if (*abort_flag) return false;
-        if (global_timer_ns() - t0 > kWaitLimitNs) {
+        if (global_timer_ns() - t0 > limit_ns) {
             *abort_flag = 1;
             report_status(status, code);
             return false;

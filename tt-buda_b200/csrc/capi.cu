@@ -33,6 +33,23 @@ cudaError_t launch_i8_gemm(const void *A, int64_t M, int64_t K, int64_t lda, con
                            int64_t scale_len, float zero_point, int out_mode, void *C, int64_t ldc, int sm_count, cudaStream_t stream,
                            unsigned int *status, char *err, size_t err_len);
 
+// One CTA, one thread waiting: the barrier expects one arrival that never comes.  The other 31 lanes only take part in
+// the final warp convergence.  The wait is the product kernels' own mbar_wait_bounded with a caller-given limit.
+__global__ void selftest_wait_kernel(unsigned int *status, uint64_t limit_ns)
+{
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncwarp();
+    if (threadIdx.x == 0)
+        (void)mbar_wait_bounded(&bar, 0u, &abort_flag, status, BUDA_DEVSTAT_SELFTEST_WAIT, limit_ns);
+    __syncwarp();
+}
+
 // One status word per device that loads the library; kernels get its device address.
 __device__ unsigned int g_device_status = 0;
 }  // namespace buda
@@ -954,6 +971,18 @@ int buda_prestride(const void *src, int elem_bytes, const uint32_t shape[4], con
     cudaError_t e = launch_prestride(src, elem_bytes, shape, strides_bytes, stride, xy_offsets, n_offsets, dst, dst_rows, dst_cols,
                                      ctx->sm_count, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(e, "prestride launch failed");
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return BUDA_SUCCESS;
+}
+
+int buda_selftest_bounded_wait(uint32_t limit_ms, void *stream)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    if (limit_ms < 1 || limit_ms > 1000) return fail(BUDA_RUNTIME_ERROR, "limit of %u ms is outside 1..1000", limit_ms);
+    selftest_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ctx->status, (uint64_t)limit_ms * 1000000ull);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "self-test launch failed");
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return BUDA_SUCCESS;
 }
