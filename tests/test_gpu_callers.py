@@ -90,7 +90,6 @@ def test_threaded_pusher_reports_a_failed_push(mods):
         pusher.push([T.Tensor.create_from_torch(torch.randn(1, 32, 32))])   # the ring is full: the push times out
         with pytest.raises(AssertionError, match="Error while pushing inputs"):
             pusher.wait_for_pushes()
-        assert "stayed full" in B.last_error() or True                         # error text lives on the pusher thread
     finally:
         pusher.shutdown()
 
