@@ -382,6 +382,14 @@ def main():
             extras["pack_bfp8_b_direct_kernel"] = timed(
                 lambda: cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b, outs=outs, path=1), algo_bytes_step)
             nu = min(16, NT)
+            # bfloat16 source (2 + 1.0625 bytes per element) and bfloat16 destination
+            xb = [x.bfloat16() for x in xs[:nu]]
+            extras["pack_bfp8_b_from_bf16"] = timed(lambda: cuda_ops.tilize_pack_batch(xb, cuda_ops.DF.Bfp8_b, outs=outs[:nu]),
+                                                    nu * ELEMS * 3.0625)
+            extras["unpack_bfp8_b_to_bf16"] = timed(
+                lambda: cuda_ops.unpack_untilize_batch(outs[:nu], cuda_ops.DF.Bfp8_b, SHAPE, outs=xb), nu * ELEMS * 3.0625)
+            del xb
+            cuda_ops.tilize_pack_batch(xs[:nu], cuda_ops.DF.Bfp8_b, outs=outs[:nu])      # the images of the fp32 tensors again
             ys = [torch.empty(SHAPE, dtype=torch.float32, device=dev) for _ in range(nu)]
             extras["unpack_bfp8_b"] = timed(
                 lambda: cuda_ops.unpack_untilize_batch(outs[:nu], cuda_ops.DF.Bfp8_b, SHAPE, outs=ys), nu * ELEMS * BYTES_PER_ELEM)

@@ -43,12 +43,17 @@ constexpr int kMaxBatch = 64;    // tensors per launch (pointer table lives in k
 // A work item is a 32-row band of up to this many tiles.  8 (1 KiB row pieces per bulk copy) with two
 // stages and two resident CTAs per SM measured 6.26 TB/s on the Bfp8_b pack; 4 tiles with three stages 5.3.
 constexpr int kBoxTiles = BUDA_BOX_TILES;
+// Tiles per work item: what matters is the 1 KiB row piece, so a block-float conversion from / to 2-byte elements
+// takes twice as many tiles per band as one from / to 4-byte elements.  (Plain relayouts keep 8: their tile records
+// are as large as the rows, and 16 of them would leave room for one CTA per SM only.)
+__host__ __device__ constexpr int box_tiles_for(int es, bool block_float) { return (block_float && es < 4) ? 2 * kBoxTiles : kBoxTiles; }
 
 struct TileJob {
     // row-major side
     uint32_t W, Z, Rt, Ct;              // entries, t, tile rows, tile columns
     uint64_t stride_w, stride_z, stride_r;  // bytes
-    uint32_t boxes_per_band;            // ceil(Ct / kBoxTiles)
+    uint32_t box_tiles;                 // tiles per work item: box_tiles_for(row-major element size, block-float queue)
+    uint32_t boxes_per_band;            // ceil(Ct / box_tiles)
     uint32_t total_items;               // batch * W * Z * Rt * boxes_per_band  (< 2^31)
     uint32_t items_per_tensor;
     // queue side

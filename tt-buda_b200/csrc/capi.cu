@@ -142,7 +142,8 @@ int make_job(const uint32_t shape[4], const uint64_t strides[4], const buda_queu
     j.W = shape[0]; j.Z = shape[1]; j.Rt = shape[2] / th; j.Ct = shape[3] / 32;
     j.tile_h = th;
     j.stride_w = strides[0]; j.stride_z = strides[1]; j.stride_r = strides[2];
-    j.boxes_per_band = (j.Ct + kBoxTiles - 1) / kBoxTiles;
+    j.box_tiles = (uint32_t)box_tiles_for((int)strides[3], bfp_mant_bits(qdf) != 0);
+    j.boxes_per_band = (j.Ct + j.box_tiles - 1) / j.box_tiles;
     const uint64_t items_per_tensor = (uint64_t)j.W * j.Z * j.Rt * j.boxes_per_band;
     if (items_per_tensor * (uint64_t)batch >= (1ull << 31))
         return fail(BUDA_RUNTIME_ERROR, "too many tile bands in one launch (%llu); split the batch",

@@ -39,12 +39,13 @@ struct ItemMeta {
 
 template <int M, int ES>
 struct PackCfg {
-    static constexpr int row_bytes = kBoxTiles * 32 * ES;
+    static constexpr int box = box_tiles_for(ES, M > 0);
+    static constexpr int row_bytes = box * 32 * ES;
     static constexpr int pitch = row_bytes + 16;
     static constexpr int in_stage_bytes = 32 * pitch;
     static constexpr int payload = (M > 0) ? (64 + 1024 * (M + 1) / 8) : (1024 * ES);
     static constexpr int rec_max = payload + 32;
-    static constexpr int out_buf_bytes = kBoxTiles * rec_max;
+    static constexpr int out_buf_bytes = box * rec_max;
 #ifdef BUDA_PACK_STAGES
     static constexpr int stages = BUDA_PACK_STAGES;
 #else
@@ -64,8 +65,8 @@ __device__ __forceinline__ void decode_item(const TileJob &job, uint32_t item, I
     q /= job.Z;
     m.w = q % job.W;
     m.b = q / job.W;
-    m.ct0 = cb * kBoxTiles;
-    m.ntiles = min((uint32_t)kBoxTiles, job.Ct - m.ct0);
+    m.ct0 = cb * job.box_tiles;
+    m.ntiles = min(job.box_tiles, job.Ct - m.ct0);
 }
 
 template <int M, int ES, bool AF>
@@ -148,7 +149,7 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
             // fall through to the barrier below so the whole CTA leaves together
         } else if (M > 0) {
 #pragma unroll
-          for (int bc = warp; bc < 2 * kBoxTiles; bc += kConsumerWarps) {  // face column: tile bc/2, left/right face bc%2
+          for (int bc = warp; bc < 2 * Cfg::box; bc += kConsumerWarps) {  // face column: tile bc/2, left/right face bc%2
             const int tile_in_box = bc >> 1;
             const int face = ((lane >> 4) << 1) | (bc & 1);
             if ((uint32_t)tile_in_box < m.ntiles) {
@@ -205,7 +206,7 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
             }
         }
         fence_async_smem();
-        if (warp == 0 && lane < kBoxTiles) bulk_wait_read_all();  // the previous item's stores have left shared memory
+        if (warp == 0 && lane < Cfg::box) bulk_wait_read_all();  // the previous item's stores have left shared memory
         if (named_bar_or(1, kConsumerThreads, !ok)) break;
         if (tid == 0) mbar_arrive(&empty[s]);
         if (warp == 0 && (uint32_t)lane < m.ntiles) {
@@ -214,7 +215,7 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
             bulk_commit();
         }
     }
-    if (warp == 0 && lane < kBoxTiles) bulk_wait_all();
+    if (warp == 0 && lane < Cfg::box) bulk_wait_all();
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -27,16 +27,17 @@ struct UItemMeta {
 
 template <int M, int ES>
 struct UnpackCfg {
-    static constexpr int row_bytes = kBoxTiles * 32 * ES;
+    static constexpr int box = box_tiles_for(ES, M > 0);
+    static constexpr int row_bytes = box * 32 * ES;
     static constexpr int pitch = row_bytes + 16;
     static constexpr int out_buf_bytes = 32 * pitch;
     static constexpr int payload = (M > 0) ? (64 + 1024 * (M + 1) / 8) : (1024 * ES);
     static constexpr int rec_max = payload + 32;
-    static constexpr int in_stage_bytes = kBoxTiles * rec_max;
+    static constexpr int in_stage_bytes = box * rec_max;
 #ifdef BUDA_UNPACK_STAGES
     static constexpr int stages = BUDA_UNPACK_STAGES;
 #else
-    static constexpr int stages = 4;
+    static constexpr int stages = box > kBoxTiles ? 2 : 4;   // 16-tile items: two stages keep two CTAs per SM
 #endif
 #ifdef BUDA_UNPACK_OUTBUFS
     static constexpr int out_bufs = BUDA_UNPACK_OUTBUFS;
@@ -57,8 +58,8 @@ __device__ __forceinline__ void decode_uitem(const TileJob &job, uint32_t item, 
     q /= job.Z;
     m.w = q % job.W;
     m.b = q / job.W;
-    m.ct0 = cb * kBoxTiles;
-    m.ntiles = min((uint32_t)kBoxTiles, job.Ct - m.ct0);
+    m.ct0 = cb * job.box_tiles;
+    m.ntiles = min(job.box_tiles, job.Ct - m.ct0);
 }
 
 // In this file PtrTable.src is the queue image and PtrTable.dst the row-major tensor.
@@ -145,7 +146,7 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
             // fall through to the barrier below so the whole CTA leaves together
         } else if (M > 0) {
 #pragma unroll
-          for (int bc = warp; bc < 2 * kBoxTiles; bc += kUConsumerWarps) {  // face column: tile bc/2, left/right face bc%2
+          for (int bc = warp; bc < 2 * Cfg::box; bc += kUConsumerWarps) {  // face column: tile bc/2, left/right face bc%2
             const int tile_in_box = bc >> 1;
             const int face = ((lane >> 4) << 1) | (bc & 1);
             if ((uint32_t)tile_in_box < m.ntiles) {
