@@ -476,3 +476,39 @@ def test_bounded_wait_gives_up_and_the_context_stays_usable(ops, oracle):
     assert _cabi.device_status() == (0, 0)
     assert _cabi.lib.buda_selftest_bounded_wait(0, None) == _cabi.RUNTIME_ERROR      # limits outside 1..1000 ms are refused
     assert _cabi.lib.buda_selftest_bounded_wait(5000, None) == _cabi.RUNTIME_ERROR
+
+
+@pytest.mark.parametrize("scale", [0.05, 1.0 / 3.0, 0.1, 7.3e-3, 1e-5, 123.456, 1.0, 0.75, 2.0 ** -10, 3.0000002])
+def test_quantize_division_is_exact_at_rounding_boundaries(ops, scale):
+    """The quantise kernel may replace x / scale by x * (1 / scale) when it can show the rounded result is the same
+    (and redoes the chunk with the IEEE division otherwise).  Inputs sitting on and within a few ulps of every
+    rounding boundary (k + 1/2) * scale, plus ties, saturation edges, specials and a large random tensor, against the
+    golden expression evaluated by torch on the CPU (op/eval/pybuda/quantize.py:56-66)."""
+    s32 = np.float32(scale)
+    ks = np.arange(-140, 141, dtype=np.float64)
+    base = ((ks + 0.5) * np.float64(s32)).astype(np.float32)
+    cand = [base]
+    up, dn = base.copy(), base.copy()
+    for _ in range(4):
+        up = np.nextafter(up, np.float32(np.inf), dtype=np.float32)
+        dn = np.nextafter(dn, np.float32(-np.inf), dtype=np.float32)
+        cand += [up.copy(), dn.copy()]
+    ints = (ks * np.float64(s32)).astype(np.float32)                        # exact integers after the division
+    specials = np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1e-45, -1e-45, 3e38, -3e38, 1e-30, 127.5 * scale, -128.5 * scale],
+                        dtype=np.float32)
+    rng = np.random.default_rng(int(scale * 1e6) % 1000)
+    rand = (rng.standard_normal(1 << 20) * 40 * scale).astype(np.float32)
+    x = np.concatenate(cand + [ints, specials, rand])
+    x = np.concatenate([x, np.zeros((-x.size) % 16, np.float32)])
+    xt = torch.from_numpy(x)
+    st = torch.tensor([s32])
+    for zp in (0.0, 3.0, -7.0):
+        want = torch.clamp(torch.round(xt / st) + zp, -128, 127).to(torch.int8)
+        got = ops.quantize(xt.cuda(), st.cuda(), zp).cpu()
+        bad = (got != want).nonzero().flatten()
+        assert bad.numel() == 0, (scale, zp, x[bad[:5].numpy()], got[bad[:5]], want[bad[:5]])
+    # per-axis scales (hoisted when the grid stride is a multiple of the period) go through the same screen
+    scs = torch.from_numpy((rng.random(64).astype(np.float32) * 0.2 + 0.01) * s32)
+    x2 = torch.from_numpy((rng.standard_normal((4096, 64)) * 30).astype(np.float32)) * scs
+    want = torch.clamp(torch.round(x2 / scs) + 1.0, -128, 127).to(torch.int8)
+    assert torch.equal(ops.quantize(x2.cuda(), scs.cuda(), 1.0, axis=-1).cpu(), want)

@@ -115,16 +115,36 @@ __device__ __forceinline__ uint32_t pack_i8x4(uint32_t a, uint32_t b, uint32_t c
 // ------------------------------------------------------------------------------------------------
 // quantize: MODE 0 divides by the scale, MODE 1 multiplies by it
 // ------------------------------------------------------------------------------------------------
+// Division by a scale that a thread meets again in every sweep (hoisted scales) need not be a division
+// instruction sequence per element.  With r = RN(1 / s) (correctly rounded reciprocal), q' = RN(x * r) is within
+// 1.5 * 2^-23 |x / s| of the true quotient, and the golden result depends on the quotient only through
+// round-half-even(RN(x / s)).  So: round q' with the magic-number add; if q' lies farther than `screen` from every
+// half-integer, RN(x / s) rounds to the same integer (screen >= 3 * 2^-24 * (B + 2), B = largest magnitude that does
+// not saturate in the clamp; beyond B both saturate alike) and the cheap result stands; otherwise -- a few chunks in
+// a thousand -- the chunk is redone with the IEEE division.  Bit-identical to the division, at a third of its
+// instructions.  The host enables it (screen > 0) only for bounds and zero point within +-2^20, where values of
+// magnitude 2^22 and above saturate whatever their rounding.
 template <int MODE, int SM, bool VEC, bool FAST>
 __global__ void __launch_bounds__(256)
 quantize_kernel(const float *__restrict__ x, int64_t n, const float *__restrict__ scale, ScaleSel sel, float zp, float lo,
-                float hi, int8_t *__restrict__ out, int hoist)
+                float hi, int8_t *__restrict__ out, int hoist, float screen)
 {
     const int64_t chunks = (n + 15) >> 4;
     float s[16];
+    float r[16];
+    bool rcp_ok = false;
     // when the grid stride is a whole number of scale periods a thread meets the same 16 scales in
     // every sweep: fetch them once
     if (hoist) load_scales16<SM>(scale, sel, ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) << 4, 16, s);
+    if (MODE == 0 && FAST && hoist && screen > 0.0f) {
+        rcp_ok = true;
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+            r[k] = __frcp_rn(s[k]);
+            const float a = fabsf(s[k]);
+            rcp_ok = rcp_ok && (a >= 7.8886090522101181e-31f) && (a <= 1.2676506002282294e30f);   // 2^-100 .. 2^100; NaN fails
+        }
+    }
     for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * blockDim.x) {
         const int64_t i0 = c << 4;
         const int cnt = (n - i0 >= 16) ? 16 : (int)(n - i0);
@@ -142,9 +162,27 @@ quantize_kernel(const float *__restrict__ x, int64_t n, const float *__restrict_
         }
         if (!hoist) load_scales16<SM>(scale, sel, i0, cnt, s);
         uint32_t q[16];
+        bool rounded = false;
+        if (MODE == 0 && FAST && rcp_ok) {
+            float t[16];
+            bool risky = false;
 #pragma unroll
-        for (int k = 0; k < 16; k++) v[k] = (MODE == 0) ? __fdiv_rn(v[k], s[k]) : __fmul_rn(v[k], s[k]);
-        round_half_even16(v);
+            for (int k = 0; k < 16; k++) {
+                const float qa = __fmul_rn(v[k], r[k]);
+                t[k] = __fadd_rn(__fadd_rn(qa, 12582912.0f), -12582912.0f);
+                risky = risky || (fabsf(fabsf(__fsub_rn(qa, t[k])) - 0.5f) < screen);
+            }
+            if (!risky) {
+#pragma unroll
+                for (int k = 0; k < 16; k++) v[k] = t[k];
+                rounded = true;
+            }
+        }
+        if (!rounded) {
+#pragma unroll
+            for (int k = 0; k < 16; k++) v[k] = (MODE == 0) ? __fdiv_rn(v[k], s[k]) : __fmul_rn(v[k], s[k]);
+            round_half_even16(v);
+        }
 #pragma unroll
         for (int k = 0; k < 16; k++) q[k] = clamp_cast_i8<FAST>(__fadd_rn(v[k], zp), lo, hi);
         if (VEC && cnt == 16) {
@@ -334,15 +372,21 @@ cudaError_t launch_quantize(const float *x, int64_t n, const float *scale, int64
     const bool fast = lo >= -4194304.0f && hi <= 4194304.0f;
     // same scales in every sweep of the grid?  (per-tensor: trivially; last axis: stride a multiple of the period)
     const int hoist = (sm == kScalePerTensor || (sm == kScaleLastAxis16 && ((int64_t)grid * 256 * 16) % scale_len == 0)) ? 1 : 0;
+    // screened-reciprocal division (see quantize_kernel): only where magnitudes of 2^22 and above saturate for sure
+    float screen = 0.0f;
+    if (mode == 0 && lo >= -1048576.0f && hi <= 1048576.0f && fabsf(zp) <= 1048576.0f) {
+        const float B = fmaxf(fabsf(lo), fabsf(hi)) + fabsf(zp);
+        screen = (B + 2.0f) * 2.384185791015625e-07f;   // (B + 2) * 2^-22
+    }
 #define CALL(SMV)                                                                                                     \
     if (mode == 0) {                                                                                                  \
-        if (vec && fast) quantize_kernel<0, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist);   \
-        else if (vec) quantize_kernel<0, SMV, true, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist);     \
-        else quantize_kernel<0, SMV, false, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist);             \
+        if (vec && fast) quantize_kernel<0, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist, screen);   \
+        else if (vec) quantize_kernel<0, SMV, true, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist, screen);     \
+        else quantize_kernel<0, SMV, false, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist, screen);             \
     } else {                                                                                                          \
-        if (vec && fast) quantize_kernel<1, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist);   \
-        else if (vec) quantize_kernel<1, SMV, true, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist);     \
-        else quantize_kernel<1, SMV, false, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist);             \
+        if (vec && fast) quantize_kernel<1, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist, screen);   \
+        else if (vec) quantize_kernel<1, SMV, true, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist, screen);     \
+        else quantize_kernel<1, SMV, false, false><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist, screen);             \
     }
     BUDA_SM_SWITCH(sm, CALL)
 #undef CALL
