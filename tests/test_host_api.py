@@ -312,3 +312,23 @@ def test_reinterpret_shape_pads_to_the_queue_tiles():
     y, _ = T.do_runtime_transform(tr, x, q, [])
     assert y.shape == (1, 1, 32, 64) and torch.equal(y[0, 0, 0, :60], x.reshape(-1)) and y[0, 0, 1:].abs().sum() == 0
 
+
+
+def test_cpp_twins_of_the_torch_device_descriptor_helpers():
+    """to_pytorch_tensor_desc / pad_to_buda_shape of the reference's torch device plugin
+    (pybuda/csrc/tt_torch_device/tt_device.cpp:109-189), restated on (pointer, sizes, strides)."""
+    import pybuda._C as C
+    B, DF = C.backend_api, C.DataFormat
+    t = torch.zeros(3, 50, 70)
+    d = B.to_pytorch_tensor_desc(t.data_ptr(), 4, DF.Float32, list(t.shape), list(t.stride()))
+    # sizes right-aligned, r / c rounded UP to the tile, byte strides, the missing w stride copied from z
+    assert (list(d.shape), list(d.strides), d.dim, d.itemsize, d.format) == ([1, 3, 64, 96], [14000, 14000, 280, 4], 4, 4, DF.Float32)
+    v = torch.zeros(17, dtype=torch.bfloat16)
+    d = B.to_pytorch_tensor_desc(v.data_ptr(), 2, DF.Float16_b, [17], [1])
+    assert (list(d.shape), list(d.strides)) == ([1, 1, 32, 32], [64, 64, 64, 2])          # 1-D: one tile row per implied row
+    assert list(B.buda_padded_shape([3, 50, 70])) == [1, 3, 64, 96]
+    assert list(B.buda_padded_shape([5])) == [1, 1, 32, 32]
+    with pytest.raises(ValueError):
+        B.to_pytorch_tensor_desc(t.data_ptr(), 4, DF.Float32, [1, 2, 3, 4, 5], [1, 1, 1, 1, 1])
+    with pytest.raises(ValueError):
+        B.buda_padded_shape([1, 2, 3, 4, 5])

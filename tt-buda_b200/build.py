@@ -25,7 +25,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 
 HOST_DIR = os.path.join(HERE, "pybuda", "csrc")
 HOST_SOURCES = ["pybuda_bindings.cpp", "backend_api/backend_api.cpp", "backend_api/queue_store.cpp",
-                "lower_to_buda/common.cpp", "balancer/tile_layout.cpp"]
+                "lower_to_buda/common.cpp", "balancer/tile_layout.cpp", "tt_torch_device/tt_device.cpp"]
 
 
 def _nvcc():

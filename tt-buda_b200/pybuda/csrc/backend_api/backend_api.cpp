@@ -4,6 +4,7 @@
 // pybuda/csrc/backend_api/backend_api.cpp (descriptors 384-591, status enum 622-625, functions
 // 688-726).  What is new here: DramIODesc has a public factory (there is no netlist to read it
 // from), and a few helpers expose the device-resident queues.
+#include "tt_torch_device/tt_device.hpp"
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
@@ -276,6 +277,14 @@ void BackendModule(py::module &m_backend)
     m_backend.def("release_queue", &release_queue);
     m_backend.def("release_all_queues", &release_all_queues);
     m_backend.def("last_error", &last_error);
+    m_backend.def(
+        "to_pytorch_tensor_desc",
+        [](std::uintptr_t data, std::uint32_t element_size, tt::DataFormat format, const std::vector<std::int64_t> &sizes,
+           const std::vector<std::int64_t> &strides)
+        { return tt::to_pytorch_tensor_desc(reinterpret_cast<const void *>(data), element_size, format, sizes, strides); },
+        py::arg("data_ptr"), py::arg("element_size"), py::arg("format"), py::arg("sizes"), py::arg("strides"),
+        "Descriptor of a tensor of up to 4 dims by the rules of the reference's torch device plugin (borrowed pointer).");
+    m_backend.def("buda_padded_shape", &tt::buda_padded_shape, py::arg("sizes"));
     m_backend.def("matmul_bfp8b", &matmul_bfp8b, py::call_guard<py::gil_scoped_release>());
 }
 
