@@ -158,6 +158,14 @@ def profile_one(torch, cuda_ops, dev, name, reps=6):
         wimg = cuda_ops.tilize_pack(torch.randint(-128, 128, (1, 1, K, N), device=dev, dtype=torch.int8), cuda_ops.DF.Int8)
         sc = torch.rand(N, device=dev) * 2e-5
         fn, work, unit = (lambda: cuda_ops.i8_matmul(a, wimg, N, scale=sc, zero_point=0.0, out="int8")), 2.0 * M * N * K / 1e12, "TOP/s"
+    elif name in ("pack_bf16", "unpack_bf16"):
+        xs = [torch.randn(SHAPE, device=dev).bfloat16() for _ in range(8)]
+        imgs = cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b)
+        if name == "pack_bf16":
+            fn = lambda: cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b, outs=imgs)
+        else:
+            fn = lambda: cuda_ops.unpack_untilize_batch(imgs, cuda_ops.DF.Bfp8_b, SHAPE, outs=xs)
+        work, unit = 8 * ELEMS * 3.0625 / 1e9, "GB/s"
     elif name == "unpack":
         xs = [torch.randn(SHAPE, device=dev) for _ in range(8)]
         imgs = cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b)
@@ -238,7 +246,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (for profiler captures)")
     ap.add_argument("--tensors", type=int, default=N_TENSORS,
                     help="tensors per GPU batch; anything but 64 is a reduced case for profiler captures")
-    ap.add_argument("--profile-kernel", default=None, choices=["gemm", "i8gemm", "unpack", "quantize", "dequantize", "requantize"],
+    ap.add_argument("--profile-kernel", default=None, choices=["gemm", "i8gemm", "unpack", "pack_bf16", "unpack_bf16", "quantize", "dequantize", "requantize"],
                     help="run only this secondary kernel a few times and exit (small, self-ending case for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -512,3 +512,41 @@ def test_quantize_division_is_exact_at_rounding_boundaries(ops, scale):
     x2 = torch.from_numpy((rng.standard_normal((4096, 64)) * 30).astype(np.float32)) * scs
     want = torch.clamp(torch.round(x2 / scs) + 1.0, -128, 127).to(torch.int8)
     assert torch.equal(ops.quantize(x2.cuda(), scs.cuda(), 1.0, axis=-1).cpu(), want)
+
+
+@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("df_name,m", [("Bfp8_b", 7), ("Bfp4_b", 3), ("Bfp2_b", 1)])
+def test_bfloat16_sources_against_the_exact_arithmetic_spec(ops, df_name, m, path):
+    """bfloat16 sources take a packed-pair encoder of their own: the known-answer inputs truncated to bfloat16 (plus
+    blocks around the exponents where that encoder hands over to the general one), against the exact rational
+    restatement of the spec evaluated here."""
+    import os, sys
+    gdir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    sys.path.insert(0, gdir)
+    try:
+        from bfp_spec import encode_block
+    finally:
+        sys.path.remove(gdir)
+    k = np.load(os.path.join(gdir, "bfp_kat.npz"))
+    hb = (k["x"] >> 16).astype(np.uint16)                                   # [256, 16] bfloat16 bit patterns
+    rng = np.random.default_rng(5)
+    for i, e in enumerate([1, 6, 7, 15, 16, 17, 18, 126, 127, 252, 253, 254, 255]):   # block exponents around the hand-over points
+        mant = rng.integers(0, 128, 16).astype(np.uint16)
+        sign = (rng.integers(0, 2, 16) << 15).astype(np.uint16)
+        ex = np.minimum(e, np.maximum(0, e - rng.integers(0, 12, 16))).astype(np.uint16)
+        ex[0] = e
+        hb[240 + i] = sign | (ex << 7) | mant
+    x = np.zeros((1, 1, 32, 128), np.uint16)
+    for b in range(256):
+        t, blk = divmod(b, 64)
+        face, fr = divmod(blk, 16)
+        x[0, 0, (face >> 1) * 16 + fr, t * 32 + (face & 1) * 16: t * 32 + (face & 1) * 16 + 16] = hb[b]
+    xt = torch.from_numpy(x.view(np.int16)).view(torch.bfloat16).cuda()
+    img = ops.tilize_pack(xt, getattr(ops.DF, df_name), path=path).cpu().numpy()
+    rec = 64 + 2 * (m + 1) * 64
+    for b in range(256):
+        E, data = encode_block([int(v) << 16 for v in hb[b]], m)
+        t, blk = divmod(b, 64)
+        assert img[t * rec + blk] == E, (b, "exponent", img[t * rec + blk], E)
+        got = img[t * rec + 64 + blk * 2 * (m + 1): t * rec + 64 + (blk + 1) * 2 * (m + 1)]
+        assert got.tobytes() == data, (b, "datums", hb[b], got, list(data))

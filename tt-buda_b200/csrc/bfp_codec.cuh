@@ -128,6 +128,74 @@ __device__ __forceinline__ void bfp_encode16(const uint32_t (&x)[16], uint32_t &
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// bfloat16 sources, two values per 32-bit word.  The torch dtype that feeds a Bfp*_b queue is bfloat16
+// (pybuda/pybuda/tensor.py:602-632), so this is the common case for parameters; working on packed pairs
+// halves the integer work of the binary32 formulation above (which bounds that kernel: ALU pipe 64 %).
+//   |x| pairs: one AND; block maximum: max.u16x2; quantise: fma.rn.bf16x2(|x|, 2^(M-1+127-E), 128.0) -- a bfloat16
+//   in [128, 256) has ulp 1, so the single rounding of the fma IS round-to-nearest-even at integer granularity
+//   and q sits in the low 7 bits; a round-up to 256, Inf and NaN are caught by min.u16x2 against 128 + qmax.
+// Blocks with E < 17 (where a denormal input times the scale could still round to 1) or E > 253 (scale not a
+// normal bfloat16 for every M) return false: the caller widens the values and uses bfp_encode16.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b)
+{
+    uint32_t d;
+    asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t min_u16x2(uint32_t a, uint32_t b)
+{
+    uint32_t d;
+    asm("min.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+template <int M>
+__device__ __forceinline__ bool bfp_encode16_bf16(const uint32_t (&h)[8], uint32_t &E_out, uint32_t (&out)[BfpTraits<M>::words])
+{
+    constexpr uint32_t qmax = BfpTraits<M>::qmax;
+    uint32_t a[8];
+    uint32_t mx = 0;
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+        a[w] = h[w] & 0x7fff7fffu;
+        mx = max_u16x2(mx, a[w]);
+    }
+    const uint32_t E = max(mx & 0xffffu, mx >> 16) >> 7;
+    E_out = E;
+    if (E < 17u || E > 253u) return false;
+    const uint32_t S = ((uint32_t)(M + 253) - E) * 0x00800080u;      // 2^(M-1+127-E) as bfloat16, both halves
+    uint32_t d2[8];
+#pragma unroll
+    for (int w = 0; w < 8; w++) {
+        uint32_t r;
+        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a[w]), "r"(S), "r"(0x43004300u));
+        r = min_u16x2(r, 0x43004300u + qmax * 0x00010001u);
+        const uint32_t q2 = r & (qmax * 0x00010001u);
+        const uint32_t sign_bit = (qmax + 1u) * 0x00010001u;            // the datum's sign position in each half
+        const uint32_t sgn = (h[w] >> (15 - M)) & sign_bit;
+        const uint32_t nz = (q2 + qmax * 0x00010001u) & sign_bit;       // set iff q > 0: a zero magnitude keeps sign 0
+        d2[w] = q2 | (sgn & nz);
+    }
+    if (M == 7) {
+#pragma unroll
+        for (int k = 0; k < 4; k++) out[k % BfpTraits<M>::words] = __byte_perm(d2[2 * k], d2[2 * k + 1], 0x6420);
+    } else if (M == 3) {
+        uint32_t t[8];
+#pragma unroll
+        for (int w = 0; w < 8; w++) t[w] = d2[w] | (d2[w] >> 12);       // byte 0 = datum 2w | datum 2w+1 << 4
+        out[0] = __byte_perm(__byte_perm(t[0], t[1], 0x0040), __byte_perm(t[2], t[3], 0x0040), 0x5410);
+        out[1 % BfpTraits<M>::words] = __byte_perm(__byte_perm(t[4], t[5], 0x0040), __byte_perm(t[6], t[7], 0x0040), 0x5410);
+    } else {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int w = 0; w < 8; w++) acc |= ((d2[w] | (d2[w] >> 14)) & 0xfu) << (4 * w);   // datums 2w, 2w+1: 2 bits each
+        out[0] = acc;
+    }
+    return true;
+}
+
 // "a" formats (Bfp8 / Bfp4 / Bfp2): same datums, but the shared exponent is the 5-bit exponent of
 // binary16 (bias 15), stored in a byte.  The source is binary16; it is widened to binary32 bit patterns
 // so the encoder above can be reused: binary16 zeros / denormals become 0 (flush); Inf / NaN become the

@@ -155,6 +155,9 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
             if ((uint32_t)tile_in_box < m.ntiles) {
                 uint32_t x[16];
                 const uint8_t *p = stage + lane * Cfg::pitch + bc * 16 * ES;
+                constexpr int MM = M > 0 ? M : 7;
+                uint32_t E, d[BfpTraits<MM>::words];
+                bool encoded = false;
                 if (ES == 4) {
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
@@ -162,25 +165,23 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
                         x[4 * j] = v.x; x[4 * j + 1] = v.y; x[4 * j + 2] = v.z; x[4 * j + 3] = v.w;
                     }
                 } else {
+                    const uint4 v0 = *reinterpret_cast<const uint4 *>(p), v1 = *reinterpret_cast<const uint4 *>(p + 16);
+                    const uint32_t h[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                    if (!AF) encoded = bfp_encode16_bf16<MM>(h, E, d);   // packed-pair encoder; false at the ends of the exponent range
+                    if (!encoded) {
 #pragma unroll
-                    for (int j = 0; j < 2; j++) {
-                        uint4 v = *reinterpret_cast<const uint4 *>(p + 16 * j);
-                        const uint32_t h[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                        for (int k = 0; k < 4; k++) {
+                        for (int k = 0; k < 8; k++) {
                             if (AF) {  // binary16 source of the "a" formats
-                                x[8 * j + 2 * k] = half_bits_to_float_bits(h[k] & 0xffffu);
-                                x[8 * j + 2 * k + 1] = half_bits_to_float_bits(h[k] >> 16);
+                                x[2 * k] = half_bits_to_float_bits(h[k] & 0xffffu);
+                                x[2 * k + 1] = half_bits_to_float_bits(h[k] >> 16);
                             } else {   // bfloat16 widens exactly: it is the upper half
-                                x[8 * j + 2 * k] = h[k] << 16;
-                                x[8 * j + 2 * k + 1] = h[k] & 0xffff0000u;
+                                x[2 * k] = h[k] << 16;
+                                x[2 * k + 1] = h[k] & 0xffff0000u;
                             }
                         }
                     }
                 }
-                constexpr int MM = M > 0 ? M : 7;
-                uint32_t E, d[BfpTraits<MM>::words];
-                bfp_encode16<MM>(x, E, d);
+                if (!encoded) bfp_encode16<MM>(x, E, d);
                 uint8_t *r = ob + tile_in_box * rec + hdr;
                 const int blk = face * 16 + fr;
                 r[blk] = (uint8_t)(AF ? a_exponent_byte(E) : E);
