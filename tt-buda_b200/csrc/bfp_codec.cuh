@@ -262,4 +262,37 @@ __device__ __forceinline__ void bfp_decode16(uint32_t E, const uint32_t (&in)[Bf
     }
 }
 
+// Decode of one block straight to bfloat16 pairs (the default result type of a read from a Bfp*_b queue,
+// pybuda/pybuda/tensor.py:730-740): datum pair -> (2^M + q) as bfloat16 (q spliced into the top mantissa bits
+// under the exponent of 2^M), then one fma.rn.bf16x2 per pair: (2^M + q) * s - 2^M * s = q * s exactly, with
+// s = 2^(E-127-(M-1)); a zero magnitude gives +0.0 whatever its sign bit.  Half the work of decoding to binary32
+// and narrowing.  Returns false when s or 2^(M+1) * s is not a normal bfloat16 (E < M or E > 252): the caller uses
+// bfp_decode16.  o[p] holds values 2p (low half) and 2p + 1.
+template <int M>
+__device__ __forceinline__ bool bfp_decode16_bf16(uint32_t E, const uint32_t (&in)[BfpTraits<M>::words], uint32_t (&o)[8])
+{
+    if (E < (uint32_t)M || E > 252u) return false;
+    constexpr uint32_t qmax = BfpTraits<M>::qmax;
+    constexpr uint32_t base = ((uint32_t)(127 + M) << 7) * 0x00010001u;           // 2^M in both halves
+    const uint32_t sc = (E - (uint32_t)(M - 1)) * 0x00800080u;                      // s: exponent field E - (M-1)
+    const uint32_t off = ((E + 1u) * 0x00800080u) | 0x80008000u;                    // -(2^M * s): exponent field E + 1
+#pragma unroll
+    for (int p = 0; p < 8; p++) {
+        uint32_t pair;                                                              // datum 2p in bits 0.., datum 2p+1 in bits 16..
+        if (M == 7) {
+            pair = __byte_perm(in[(p / 2) % BfpTraits<M>::words], 0u, (p & 1) ? 0x4342 : 0x4140);
+        } else {
+            const uint32_t w = in[((2 * p) * (M + 1) / 32) % BfpTraits<M>::words] >> (((2 * p) * (M + 1)) % 32);
+            pair = (w & (2u * qmax + 1u)) | (((w >> (M + 1)) & (2u * qmax + 1u)) << 16);
+        }
+        const uint32_t q2 = pair & (qmax * 0x00010001u);
+        const uint32_t nz = ((q2 + qmax * 0x00010001u) >> M) & 0x00010001u;          // 1 per half iff q > 0
+        const uint32_t sgn = ((pair >> M) & nz) << 15;                              // sign bit, only beside a magnitude
+        uint32_t r;
+        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(base | (q2 << (7 - M))), "r"(sc), "r"(off));
+        o[p] = r | sgn;
+    }
+    return true;
+}
+
 }  // namespace buda

@@ -165,22 +165,28 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
                 } else {
                     d[0] = *reinterpret_cast<const uint32_t *>(q);
                 }
-                float v[16];
-                bfp_decode16<MM, AF>(E, d, v);
                 uint8_t *p = ob + lane * Cfg::pitch + bc * 16 * ES;
-                if (ES == 4) {
-#pragma unroll
-                    for (int j = 0; j < 4; j++)
-                        *reinterpret_cast<float4 *>(p + 16 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                } else {
-                    // at most 7 significant bits: the upper half of the binary32 is the exact bfloat16
-                    uint32_t h[8];
-#pragma unroll
-                    for (int j = 0; j < 8; j++)
-                        h[j] = AF ? pack_half2(v[2 * j], v[2 * j + 1])
-                                  : __byte_perm(__float_as_uint(v[2 * j]), __float_as_uint(v[2 * j + 1]), 0x7632);
+                uint32_t h[8];
+                if (ES == 2 && !AF && bfp_decode16_bf16<MM>(E, d, h)) {
+                    // bfloat16 destination: decoded as packed pairs (false at the ends of the exponent range)
                     *reinterpret_cast<uint4 *>(p) = make_uint4(h[0], h[1], h[2], h[3]);
                     *reinterpret_cast<uint4 *>(p + 16) = make_uint4(h[4], h[5], h[6], h[7]);
+                } else {
+                    float v[16];
+                    bfp_decode16<MM, AF>(E, d, v);
+                    if (ES == 4) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            *reinterpret_cast<float4 *>(p + 16 * j) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    } else {
+                        // at most 7 significant bits: the upper half of the binary32 is the exact bfloat16
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            h[j] = AF ? pack_half2(v[2 * j], v[2 * j + 1])
+                                      : __byte_perm(__float_as_uint(v[2 * j]), __float_as_uint(v[2 * j + 1]), 0x7632);
+                        *reinterpret_cast<uint4 *>(p) = make_uint4(h[0], h[1], h[2], h[3]);
+                        *reinterpret_cast<uint4 *>(p + 16) = make_uint4(h[4], h[5], h[6], h[7]);
+                    }
                 }
             }
           }
