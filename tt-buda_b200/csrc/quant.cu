@@ -341,14 +341,15 @@ static unsigned grid_for_tail(int64_t n)
     return (unsigned)blocks;
 }
 
-// Per-axis scales: one resident wave of blocks (8 x 256 threads per SM) sweeps the tensor, so a thread
-// does several sweeps and the scales it fetched once pay off.  Per-tensor scale: many short-lived blocks
-// measured faster.
+// One resident wave of blocks (8 x 256 threads per SM) sweeps the tensor, so a thread does several sweeps and what it
+// fetched or derived once (per-axis scales, the reciprocal of the scale) pays off.  Measured: per-axis always faster
+// this way; per-tensor 15 % faster at the 2^25-element size (30.3 vs 34.8 us), 1.4 % slower than many short-lived
+// blocks at 2^27, hence the switch.
 static unsigned grid_for(int64_t n, int sm_count, bool per_axis)
 {
     const int64_t chunks = (n + 15) >> 4;
     int64_t blocks = (chunks + 255) / 256;
-    const int64_t cap = (int64_t)sm_count * (per_axis ? 8 : 64);
+    const int64_t cap = (int64_t)sm_count * ((per_axis || n <= (int64_t(1) << 26)) ? 8 : 64);
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     return (unsigned)blocks;
