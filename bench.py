@@ -434,6 +434,45 @@ def main():
         except Exception as exc:
             extras["bfp8b_gemm_8192x4096x16384"] = {"error": str(exc)}
 
+    # ------------------------------------------------------------------ BERT-large weight set, layers dealt to the ranks
+    if not args.no_extras:
+        try:
+            from pybuda.sharding import units_of_rank
+
+            layers = units_of_rank(24, rank, world)        # layer l -> rank l % world (3 each at 8 GPUs)
+            groups = {}                                     # shape -> tensors: Q, K, V, O [1024,1024]; FFN [1024,4096], [4096,1024]
+            for l in layers:
+                for j, shp in enumerate([(1024, 1024)] * 4 + [(1024, 4096), (4096, 1024)]):
+                    g = torch.Generator(device=dev).manual_seed(2000 + 6 * l + j)
+                    groups.setdefault(shp, []).append(torch.randn((1, 1) + shp, generator=g, device=dev) * 0.02)
+            imgs = {shp: cuda_ops.tilize_pack_batch(ts, cuda_ops.DF.Bfp8_b) for shp, ts in groups.items()}
+            backs = {shp: [torch.empty_like(t) for t in ts] for shp, ts in groups.items()}
+
+            def round_trip():
+                for shp, ts in groups.items():
+                    cuda_ops.tilize_pack_batch(ts, cuda_ops.DF.Bfp8_b, outs=imgs[shp])
+                    cuda_ops.unpack_untilize_batch(imgs[shp], cuda_ops.DF.Bfp8_b, (1, 1) + shp, outs=backs[shp])
+
+            for _ in range(3):
+                round_trip()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                round_trip()
+            e1.record()
+            barrier()
+            ms = max_over_ranks(e0.elapsed_time(e1) / 10)
+            elems = 24 * (4 * 1024 * 1024 + 2 * 1024 * 4096)          # 301,989,888 over all ranks
+            extras["bert_large_weights_fp32_bfp8b_fp32"] = {
+                "GB/s": round(elems * 2 * BYTES_PER_ELEM / (ms * 1e-3) / 1e9, 1), "ms": round(ms, 4), "layers_per_rank": len(layers),
+                "frac_hbm_per_gpu": round(elems * 2 * BYTES_PER_ELEM / (ms * 1e-3) / 1e9 / world / hbm_peak, 3),
+                "note": "pack + unpack of this rank's layers, 6 launches per round trip; the set is 1.5 GB over all ranks, "
+                        "so at 8 GPUs a rank's share (191 MB) is near the size of L2"}
+            del groups, imgs, backs
+        except Exception as exc:
+            extras["bert_large_weights_fp32_bfp8b_fp32"] = {"error": str(exc)}
+
     # ------------------------------------------------------------------ column-parallel matmul over the ranks (N > 1)
     if world > 1 and not args.no_extras:
         try:
