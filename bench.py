@@ -11,7 +11,9 @@ tensor).  One step = one pass over the batch.  With N GPUs every rank packs its 
           inputs resident in HBM, one batched launch per step, timed with CUDA events.
   e2e   : the same metric through the host-buffer entry point (pinned host tensors in, host
           images out; copies inside the timed region).
-  roofline / cpu_baseline : see DESIGN.md.
+  roofline : algorithmic bytes per launch / mean CUDA-event launch time, against the measured copy bandwidth of
+          this pool's B200s; traffic = DRAM bytes of one launch from a profiler capture.
+  cpu_baseline : the CPU port of the same path on the box's host cores, on a bounded sample of the batch.
 
 --impl reference times the CPU implementation of the same path (the oracle port, OpenMP over all
 host cores) on the same workload and prints the same line with "impl": "reference".

@@ -65,7 +65,9 @@ def load_reference(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: gen_quant_golden.py <path of a tt-buda checkout>")
+    ref_root = sys.argv[1]
     py, bu = load_reference(ref_root)
     g = torch.Generator(device="cpu")
     out = {}
