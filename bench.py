@@ -169,10 +169,15 @@ def profile_one(torch, cuda_ops, dev, name, reps=6):
         else:
             fn = lambda: cuda_ops.unpack_untilize_batch(imgs, cuda_ops.DF.Bfp8_b, SHAPE, outs=xs)
         work, unit = 8 * ELEMS * 3.0625 / 1e9, "GB/s"
-    elif name == "unpack":
+    elif name in ("unpack", "pack_direct", "unpack_direct"):
         xs = [torch.randn(SHAPE, device=dev) for _ in range(8)]
         imgs = cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b)
-        fn, work, unit = (lambda: cuda_ops.unpack_untilize_batch(imgs, cuda_ops.DF.Bfp8_b, SHAPE, outs=xs)), 8 * ELEMS * BYTES_PER_ELEM / 1e9, "GB/s"
+        path = 1 if name.endswith("_direct") else None      # 1 = the kernels that unaligned tensors and tiny tiles take
+        if name == "pack_direct":
+            fn = lambda: cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b, outs=imgs, path=1)
+        else:
+            fn = lambda: cuda_ops.unpack_untilize_batch(imgs, cuda_ops.DF.Bfp8_b, SHAPE, outs=xs, path=path)
+        work, unit = 8 * ELEMS * BYTES_PER_ELEM / 1e9, "GB/s"
     else:
         n = 32 * 1024 * 1024 * 4  # 512 MiB of fp32: larger than L2
         sc = torch.tensor([0.05], device=dev)
@@ -249,7 +254,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (for profiler captures)")
     ap.add_argument("--tensors", type=int, default=N_TENSORS,
                     help="tensors per GPU batch; anything but 64 is a reduced case for profiler captures")
-    ap.add_argument("--profile-kernel", default=None, choices=["gemm", "i8gemm", "unpack", "pack_bf16", "unpack_bf16", "quantize", "dequantize", "requantize"],
+    ap.add_argument("--profile-kernel", default=None, choices=["gemm", "i8gemm", "unpack", "pack_direct", "unpack_direct", "pack_bf16", "unpack_bf16", "quantize", "dequantize", "requantize"],
                     help="run only this secondary kernel a few times and exit (small, self-ending case for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -404,6 +409,9 @@ def main():
             ys = [torch.empty(SHAPE, dtype=torch.float32, device=dev) for _ in range(nu)]
             extras["unpack_bfp8_b"] = timed(
                 lambda: cuda_ops.unpack_untilize_batch(outs[:nu], cuda_ops.DF.Bfp8_b, SHAPE, outs=ys), nu * ELEMS * BYTES_PER_ELEM)
+            extras["unpack_bfp8_b_direct_kernel"] = timed(
+                lambda: cuda_ops.unpack_untilize_batch(outs[:nu], cuda_ops.DF.Bfp8_b, SHAPE, outs=ys, path=1),
+                nu * ELEMS * BYTES_PER_ELEM)
             del ys
             n3 = 32 * 1024 * 1024
             # config-3 tensors are about the size of L2: every call takes the next of four copies of its input, so no

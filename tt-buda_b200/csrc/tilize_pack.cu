@@ -285,51 +285,59 @@ pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
     const int lane = threadIdx.x & 31;
     const uint64_t warps_total = (uint64_t)gridDim.x * (blockDim.x >> 5);
     const uint64_t warp_id = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const uint64_t tiles_per_tensor = (uint64_t)job.W * job.Z * job.Rt * job.Ct;
-    const uint64_t units = (uint64_t)batch * tiles_per_tensor * 8u;  // a unit is 8 rows of one face
+    const uint64_t tiles = (uint64_t)batch * job.W * job.Z * job.Rt * job.Ct;
     const uint32_t rec = job.tile_bytes, hdr = job.header_bytes;
-    for (uint64_t u = warp_id; u < units; u += warps_total) {
-        const uint32_t hf = (uint32_t)(u & 7u);
-        uint64_t t = u >> 3;
+    // A warp takes a whole tile per iteration: the tile's position is worked out once (the divisions by the run-time
+    // tensor dims were most of the instructions when a warp took an eighth of a tile), and the loads of all eight
+    // 8-row pieces (4 faces x 2 halves) are issued before the first is used.
+    for (uint64_t tt = warp_id; tt < tiles; tt += warps_total) {
+        uint64_t t = tt;
         const uint32_t ct = (uint32_t)(t % job.Ct); t /= job.Ct;
         const uint32_t rt = (uint32_t)(t % job.Rt); t /= job.Rt;
         const uint32_t z = (uint32_t)(t % job.Z); t /= job.Z;
         const uint32_t w = (uint32_t)(t % job.W);
         const uint32_t b = (uint32_t)(t / job.W);
-        const uint32_t face = hf >> 1, half = hf & 1u;
-        const uint32_t fr = half * 8u + (lane >> 2);
-        const uint32_t tr = (face >> 1) * 16u + fr;            // row inside the tile
-        const uint64_t row = (uint64_t)rt * job.tile_h + tr;  // tiny tiles hold tile_h tensor rows; the rest of the record is zero
-        const uint64_t col = (uint64_t)ct * 32u + (face & 1u) * 16u + (lane & 3) * 4u;
-        const uint8_t *p = ptrs.src[b] + (uint64_t)w * job.stride_w + rm_z_offset(job, z) + row * job.stride_r +
-                           col * ES;
+        const uint8_t *tile_src = ptrs.src[b] + (uint64_t)w * job.stride_w + rm_z_offset(job, z) +
+                                  (uint64_t)rt * job.tile_h * job.stride_r + ((uint64_t)ct * 32u + (lane & 3) * 4u) * ES;
         uint8_t *r = ptrs.dst[b] + tile_record_offset(job, w, z, rt, ct);
-        if (hdr && hf == 0 && lane < 8) reinterpret_cast<uint32_t *>(r)[lane] = 0;
+        if (hdr && lane < 8) reinterpret_cast<uint32_t *>(r)[lane] = 0;
         r += hdr;
-        uint32_t x[4] = {0u, 0u, 0u, 0u};
-        if (tr < job.tile_h) load4<ES>(p, vec_ok != 0, x);
-        const uint32_t blk = face * 16u + fr;
-        if (M > 0) {
-            constexpr int MM = M > 0 ? M : 7;
-            if (ES == 2) {
+        uint32_t xs[8][4];
 #pragma unroll
-                for (int i = 0; i < 4; i++) x[i] = AF ? half_bits_to_float_bits(x[i]) : (x[i] << 16);
+        for (int hf = 0; hf < 8; hf++) {
+            const uint32_t face = hf >> 1, half = hf & 1u;
+            const uint32_t tr = (face >> 1) * 16u + half * 8u + (lane >> 2);   // row inside the tile
+            xs[hf][0] = xs[hf][1] = xs[hf][2] = xs[hf][3] = 0u;               // tiny tiles: rows >= tile_h stay zero
+            if (tr < job.tile_h) load4<ES>(tile_src + (uint64_t)tr * job.stride_r + (face & 1u) * 16u * ES, vec_ok != 0, xs[hf]);
+        }
+#pragma unroll
+        for (int hf = 0; hf < 8; hf++) {
+            const uint32_t face = hf >> 1, half = hf & 1u;
+            const uint32_t fr = half * 8u + (lane >> 2);
+            uint32_t (&x)[4] = xs[hf];
+            const uint32_t blk = face * 16u + fr;
+            if (M > 0) {
+                constexpr int MM = M > 0 ? M : 7;
+                if (ES == 2) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) x[i] = AF ? half_bits_to_float_bits(x[i]) : (x[i] << 16);
+                }
+                uint32_t mx = max(max(x[0] & 0x7fffffffu, x[1] & 0x7fffffffu), max(x[2] & 0x7fffffffu, x[3] & 0x7fffffffu));
+                mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1, 4));
+                mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2, 4));
+                const uint32_t E = mx >> 23;
+                const uint32_t packed = encode4_shared_exp<MM>(x, E);
+                if ((lane & 3) == 0) r[blk] = (uint8_t)(AF ? a_exponent_byte(E) : E);
+                uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
+                if (MM == 7) reinterpret_cast<uint32_t *>(q)[lane & 3] = packed;
+                else if (MM == 3) reinterpret_cast<uint16_t *>(q)[lane & 3] = (uint16_t)packed;
+                else q[lane & 3] = (uint8_t)packed;
+            } else {
+                uint8_t *q = r + ((uint64_t)blk * 16u + (lane & 3) * 4u) * ES;
+                if (ES == 4) *reinterpret_cast<uint4 *>(q) = make_uint4(x[0], x[1], x[2], x[3]);
+                else if (ES == 2) *reinterpret_cast<uint2 *>(q) = make_uint2(x[0] | (x[1] << 16), x[2] | (x[3] << 16));
+                else *reinterpret_cast<uint32_t *>(q) = x[0] | (x[1] << 8) | (x[2] << 16) | (x[3] << 24);
             }
-            uint32_t mx = max(max(x[0] & 0x7fffffffu, x[1] & 0x7fffffffu), max(x[2] & 0x7fffffffu, x[3] & 0x7fffffffu));
-            mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1, 4));
-            mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2, 4));
-            const uint32_t E = mx >> 23;
-            const uint32_t packed = encode4_shared_exp<MM>(x, E);
-            if ((lane & 3) == 0) r[blk] = (uint8_t)(AF ? a_exponent_byte(E) : E);
-            uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
-            if (MM == 7) reinterpret_cast<uint32_t *>(q)[lane & 3] = packed;
-            else if (MM == 3) reinterpret_cast<uint16_t *>(q)[lane & 3] = (uint16_t)packed;
-            else q[lane & 3] = (uint8_t)packed;
-        } else {
-            uint8_t *q = r + ((uint64_t)blk * 16u + (lane & 3) * 4u) * ES;
-            if (ES == 4) *reinterpret_cast<uint4 *>(q) = make_uint4(x[0], x[1], x[2], x[3]);
-            else if (ES == 2) *reinterpret_cast<uint2 *>(q) = make_uint2(x[0] | (x[1] << 16), x[2] | (x[3] << 16));
-            else *reinterpret_cast<uint32_t *>(q) = x[0] | (x[1] << 8) | (x[2] << 16) | (x[3] << 24);
         }
     }
 }
@@ -368,8 +376,8 @@ template <int M, int ES, bool AF>
 static cudaError_t launch_direct(const TileJob &job, const PtrTable &ptrs, int batch, int vec_ok, int sm_count,
                                  cudaStream_t stream)
 {
-    const uint64_t units = (uint64_t)batch * job.W * job.Z * job.Rt * job.Ct * 8u;
-    uint64_t blocks = (units + 7) / 8;
+    const uint64_t tiles = (uint64_t)batch * job.W * job.Z * job.Rt * job.Ct;   // one warp iteration each
+    uint64_t blocks = (tiles + 7) / 8;
     const uint64_t cap = (uint64_t)sm_count * 32;
     if (blocks > cap) blocks = cap;
     pack_direct_kernel<M, ES, AF><<<(unsigned)blocks, 256, 0, stream>>>(job, ptrs, batch, vec_ok);

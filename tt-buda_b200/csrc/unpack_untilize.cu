@@ -250,84 +250,109 @@ unpack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant_
     const int lane = threadIdx.x & 31;
     const uint64_t warps_total = (uint64_t)gridDim.x * (blockDim.x >> 5);
     const uint64_t warp_id = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const uint64_t tiles_per_tensor = (uint64_t)job.W * job.Z * job.Rt * job.Ct;
-    const uint64_t units = (uint64_t)batch * tiles_per_tensor * 8u;
+    const uint64_t tiles = (uint64_t)batch * job.W * job.Z * job.Rt * job.Ct;
     const uint32_t hdr = job.header_bytes;
-    for (uint64_t u = warp_id; u < units; u += warps_total) {
-        const uint32_t hf = (uint32_t)(u & 7u);
-        uint64_t t = u >> 3;
+    // A warp takes a whole tile per iteration: the tile's position is worked out once, and the record reads of all
+    // eight 8-row pieces (4 faces x 2 halves) are issued before the first is decoded.
+    for (uint64_t tt = warp_id; tt < tiles; tt += warps_total) {
+        uint64_t t = tt;
         const uint32_t ct = (uint32_t)(t % job.Ct); t /= job.Ct;
         const uint32_t rt = (uint32_t)(t % job.Rt); t /= job.Rt;
         const uint32_t z = (uint32_t)(t % job.Z); t /= job.Z;
         const uint32_t w = (uint32_t)(t % job.W);
         const uint32_t b = (uint32_t)(t / job.W);
-        const uint32_t face = hf >> 1, half = hf & 1u;
-        const uint32_t fr = half * 8u + (lane >> 2);
-        const uint32_t tr = (face >> 1) * 16u + fr;            // row inside the tile
-        if (tr >= job.tile_h) continue;                       // tiny tiles: only tile_h rows of a record belong to the tensor
-        const uint64_t row = (uint64_t)rt * job.tile_h + tr;
-        const uint64_t col = (uint64_t)ct * 32u + (face & 1u) * 16u + (lane & 3) * 4u;
-        uint8_t *p = ptrs.dst[b] + (uint64_t)w * job.stride_w + rm_z_offset(job, z) + row * job.stride_r + col * ES;
+        uint8_t *tile_dst = ptrs.dst[b] + (uint64_t)w * job.stride_w + rm_z_offset(job, z) +
+                            (uint64_t)rt * job.tile_h * job.stride_r + ((uint64_t)ct * 32u + (lane & 3) * 4u) * ES;
         const uint8_t *r = ptrs.src[b] + tile_record_offset(job, w, z, rt, ct) + hdr;
-        const uint32_t blk = face * 16u + fr;
-        uint32_t x[4];
-        if (M > 0) {
-            constexpr int MM = M > 0 ? M : 7;
-            const uint32_t E = r[blk];
-            const uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
-            uint32_t packed;
-            if (MM == 7) packed = reinterpret_cast<const uint32_t *>(q)[lane & 3];
-            else if (MM == 3) packed = reinterpret_cast<const uint16_t *>(q)[lane & 3];
-            else packed = q[lane & 3];
-            float post = 1.0f;
-            const float sc = AF ? bfp_a_block_scale<MM>(E & 31u) : bfp_block_scale<MM>(E, post);
+        constexpr int MM = M > 0 ? M : 7;
+        constexpr int kRaw = (M == 0 && ES == 4) ? 4 : (M == 0 && ES == 2) ? 2 : 1;
+        uint32_t raw[8][kRaw];
+        uint32_t ex[8];
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const uint32_t d = packed >> (i * (MM + 1));
-                const uint32_t qb = kMagicBits | (d & BfpTraits<MM>::qmax);
-                const uint32_t signbit = (d << (31 - MM)) & 0x80000000u;
-                float mag = __fmul_rn(__fadd_rn(__uint_as_float(qb), -12582912.0f), sc);
-                if (MM == 1 && !AF) mag = __fmul_rn(mag, post);
-                const float val = __fadd_rn(__uint_as_float(__float_as_uint(mag) | signbit), 0.0f);
-                x[i] = __float_as_uint(val);
-                if (ES == 2) x[i] = AF ? (pack_half2(val, 0.0f) & 0xffffu) : (x[i] >> 16);
-            }
-        } else {
-            const uint8_t *q = r + ((uint64_t)blk * 16u + (lane & 3) * 4u) * ES;
-            if (ES == 4) {
-                uint4 v = *reinterpret_cast<const uint4 *>(q);
-                x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
-            } else if (ES == 2) {
-                uint2 v = *reinterpret_cast<const uint2 *>(q);
-                x[0] = v.x & 0xffffu; x[1] = v.x >> 16; x[2] = v.y & 0xffffu; x[3] = v.y >> 16;
+        for (int hf = 0; hf < 8; hf++) {
+            const uint32_t face = hf >> 1, half = hf & 1u;
+            const uint32_t fr = half * 8u + (lane >> 2);
+            const uint32_t tr = (face >> 1) * 16u + fr;            // row inside the tile
+            const uint32_t blk = face * 16u + fr;
+            ex[hf] = 0;
+#pragma unroll
+            for (int i = 0; i < kRaw; i++) raw[hf][i] = 0;
+            if (tr >= job.tile_h) continue;                       // tiny tiles: only tile_h rows of a record belong to the tensor
+            if (M > 0) {
+                ex[hf] = r[blk];
+                const uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
+                if (MM == 7) raw[hf][0] = reinterpret_cast<const uint32_t *>(q)[lane & 3];
+                else if (MM == 3) raw[hf][0] = reinterpret_cast<const uint16_t *>(q)[lane & 3];
+                else raw[hf][0] = q[lane & 3];
             } else {
-                uint32_t v = *reinterpret_cast<const uint32_t *>(q);
-                x[0] = v & 0xffu; x[1] = (v >> 8) & 0xffu; x[2] = (v >> 16) & 0xffu; x[3] = v >> 24;
+                const uint8_t *q = r + ((uint64_t)blk * 16u + (lane & 3) * 4u) * ES;
+                if (ES == 4) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(q);
+                    raw[hf][0] = v.x; raw[hf][kRaw > 1 ? 1 : 0] = v.y; raw[hf][kRaw > 2 ? 2 : 0] = v.z; raw[hf][kRaw > 3 ? 3 : 0] = v.w;
+                } else if (ES == 2) {
+                    const uint2 v = *reinterpret_cast<const uint2 *>(q);
+                    raw[hf][0] = v.x; raw[hf][kRaw > 1 ? 1 : 0] = v.y;
+                } else {
+                    raw[hf][0] = *reinterpret_cast<const uint32_t *>(q);
+                }
             }
         }
-        if (ES == 4) {
-            if (vec_ok) {
-                *reinterpret_cast<uint4 *>(p) = make_uint4(x[0], x[1], x[2], x[3]);
-            } else if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) {
 #pragma unroll
-                for (int i = 0; i < 4; i++) reinterpret_cast<uint32_t *>(p)[i] = x[i];
+        for (int hf = 0; hf < 8; hf++) {
+            const uint32_t face = hf >> 1, half = hf & 1u;
+            const uint32_t tr = (face >> 1) * 16u + half * 8u + (lane >> 2);
+            if (tr >= job.tile_h) continue;
+            uint8_t *p = tile_dst + (uint64_t)tr * job.stride_r + (face & 1u) * 16u * ES;
+            uint32_t x[4];
+            if (M > 0) {
+                const uint32_t E = ex[hf];
+                const uint32_t packed = raw[hf][0];
+                float post = 1.0f;
+                const float sc = AF ? bfp_a_block_scale<MM>(E & 31u) : bfp_block_scale<MM>(E, post);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t d = packed >> (i * (MM + 1));
+                    const uint32_t qb = kMagicBits | (d & BfpTraits<MM>::qmax);
+                    const uint32_t signbit = (d << (31 - MM)) & 0x80000000u;
+                    float mag = __fmul_rn(__fadd_rn(__uint_as_float(qb), -12582912.0f), sc);
+                    if (MM == 1 && !AF) mag = __fmul_rn(mag, post);
+                    const float val = __fadd_rn(__uint_as_float(__float_as_uint(mag) | signbit), 0.0f);
+                    x[i] = __float_as_uint(val);
+                    if (ES == 2) x[i] = AF ? (pack_half2(val, 0.0f) & 0xffffu) : (x[i] >> 16);
+                }
+            } else if (ES == 4) {
+                x[0] = raw[hf][0]; x[1] = raw[hf][kRaw > 1 ? 1 : 0]; x[2] = raw[hf][kRaw > 2 ? 2 : 0]; x[3] = raw[hf][kRaw > 3 ? 3 : 0];
+            } else if (ES == 2) {
+                const uint32_t v0 = raw[hf][0], v1 = raw[hf][kRaw > 1 ? 1 : 0];
+                x[0] = v0 & 0xffffu; x[1] = v0 >> 16; x[2] = v1 & 0xffffu; x[3] = v1 >> 16;
+            } else {
+                const uint32_t v = raw[hf][0];
+                x[0] = v & 0xffu; x[1] = (v >> 8) & 0xffu; x[2] = (v >> 16) & 0xffu; x[3] = v >> 24;
+            }
+            if (ES == 4) {
+                if (vec_ok) {
+                    *reinterpret_cast<uint4 *>(p) = make_uint4(x[0], x[1], x[2], x[3]);
+                } else if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) reinterpret_cast<uint32_t *>(p)[i] = x[i];
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; i++) p[i] = (uint8_t)(x[i >> 2] >> (8 * (i & 3)));
+                }
+            } else if (ES == 2) {
+                if (vec_ok) {
+                    *reinterpret_cast<uint2 *>(p) = make_uint2(x[0] | (x[1] << 16), x[2] | (x[3] << 16));
+                } else if ((reinterpret_cast<uintptr_t>(p) & 1u) == 0) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) reinterpret_cast<uint16_t *>(p)[i] = (uint16_t)x[i];
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) p[i] = (uint8_t)(x[i >> 1] >> (8 * (i & 1)));
+                }
             } else {
 #pragma unroll
-                for (int i = 0; i < 16; i++) p[i] = (uint8_t)(x[i >> 2] >> (8 * (i & 3)));
+                for (int i = 0; i < 4; i++) p[i] = (uint8_t)x[i];
             }
-        } else if (ES == 2) {
-            if (vec_ok) {
-                *reinterpret_cast<uint2 *>(p) = make_uint2(x[0] | (x[1] << 16), x[2] | (x[3] << 16));
-            } else if ((reinterpret_cast<uintptr_t>(p) & 1u) == 0) {
-#pragma unroll
-                for (int i = 0; i < 4; i++) reinterpret_cast<uint16_t *>(p)[i] = (uint16_t)x[i];
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; i++) p[i] = (uint8_t)(x[i >> 1] >> (8 * (i & 1)));
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 4; i++) p[i] = (uint8_t)x[i];
         }
     }
 }
@@ -366,8 +391,8 @@ template <int M, int ES, bool AF>
 static cudaError_t launch_udirect(const TileJob &job, const PtrTable &ptrs, int batch, int vec_ok, int sm_count,
                                   cudaStream_t stream)
 {
-    const uint64_t units = (uint64_t)batch * job.W * job.Z * job.Rt * job.Ct * 8u;
-    uint64_t blocks = (units + 7) / 8;
+    const uint64_t tiles = (uint64_t)batch * job.W * job.Z * job.Rt * job.Ct;   // one warp iteration each
+    uint64_t blocks = (tiles + 7) / 8;
     const uint64_t cap = (uint64_t)sm_count * 32;
     if (blocks > cap) blocks = cap;
     unpack_direct_kernel<M, ES, AF><<<(unsigned)blocks, 256, 0, stream>>>(job, ptrs, batch, vec_ok);
