@@ -222,27 +222,62 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
 // ------------------------------------------------------------------------------------------------
 // direct kernel: 4 lanes per block, warp-shuffle exponent reduction, any alignment
 // ------------------------------------------------------------------------------------------------
+// Bits of max(|a|, |b|, |c|, |d|) as floats; a NaN operand gives 0x7fffffff, so the exponent field is 255 for
+// NaN and Inf alike, as with an integer maximum of the magnitudes.  The absolute values fold into the
+// min/max instructions.
+__device__ __forceinline__ uint32_t absmax4_bits(const uint32_t (&x)[4])
+{
+    float m;
+    asm("{\n\t.reg .f32 a0, a1, a2, a3, m0;\n\t"
+        "abs.f32 a0, %1;\n\tabs.f32 a1, %2;\n\tabs.f32 a2, %3;\n\tabs.f32 a3, %4;\n\t"
+        "max.NaN.f32 m0, a0, a1, a2;\n\t"
+        "max.NaN.f32 %0, m0, a3;\n\t}"
+        : "=f"(m)
+        : "f"(__uint_as_float(x[0])), "f"(__uint_as_float(x[1])), "f"(__uint_as_float(x[2])), "f"(__uint_as_float(x[3])));
+    return __float_as_uint(m);
+}
+
+// The exponents next to 0 and 255, where the scale of the fast path is not a normal float: integer arithmetic,
+// kept out of line because almost no block takes it.
+__device__ __noinline__ uint32_t encode4_any_exp(uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3, uint32_t E, int m)
+{
+    return bfp_encode_datum_int(x0, E, m) | (bfp_encode_datum_int(x1, E, m) << (m + 1)) |
+           (bfp_encode_datum_int(x2, E, m) << (2 * (m + 1))) | (bfp_encode_datum_int(x3, E, m) << (3 * (m + 1)));
+}
+
+// Four data of one block, shared exponent E already known, packed at (M + 1) bits each.  In the usual exponent
+// range the magnitudes come out of one fused multiply-add each (round to nearest even into the low bits of
+// 1.5 * 2^23) and everything after it works on the four data at once, one byte each: saturation is per element,
+// then the sign bits are gathered with byte permutes and dropped where the magnitude is zero.
 template <int M>
 __device__ __forceinline__ uint32_t encode4_shared_exp(const uint32_t (&x)[4], uint32_t E)
 {
     constexpr uint32_t qmax = BfpTraits<M>::qmax;
-    uint32_t packed = 0;
     const bool fast = (E + 1u >= (uint32_t)M) && (E <= (uint32_t)(M + 252));
-    const float S = __uint_as_float((uint32_t)(M + 253 - (int)E) << 23);
+    if (fast) {
+        const float S = __uint_as_float((uint32_t)(M + 253 - (int)E) << 23);
+        uint32_t r[4];
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        uint32_t d;
-        if (fast) {
-            float r;
-            asm("fma.rn.ftz.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(__uint_as_float(x[i] & 0x7fffffffu)), "f"(S), "f"(12582912.0f));
-            uint32_t q = min(__float_as_uint(r), kMagicBits + qmax) - kMagicBits;
-            d = q ? (((x[i] >> 31) << M) | q) : 0u;
-        } else {
-            d = bfp_encode_datum_int(x[i], E, M);
+        for (int i = 0; i < 4; i++) {
+            float f;
+            asm("{\n\t.reg .f32 t;\n\tabs.ftz.f32 t, %1;\n\tfma.rn.ftz.f32 %0, t, %2, %3;\n\t}"
+                : "=f"(f) : "f"(__uint_as_float(x[i])), "f"(S), "f"(12582912.0f));
+            r[i] = min(__float_as_uint(f), kMagicBits + qmax);   // low byte = magnitude (the constant's low byte is 0)
         }
-        packed |= d << (i * (M + 1));
+        const uint32_t Q = __byte_perm(__byte_perm(r[0], r[1], 0x0040), __byte_perm(r[2], r[3], 0x0040), 0x5410);
+        const uint32_t SG = __byte_perm(__byte_perm(x[0], x[1], 0x0073), __byte_perm(x[2], x[3], 0x0073), 0x5410);
+        constexpr uint32_t kSignBit = 0x01010101u << M;
+        const uint32_t nz = Q + qmax * 0x01010101u;              // bit M of a byte is set where its magnitude is not 0
+        const uint32_t D = Q | ((SG >> (7 - M)) & nz & kSignBit);
+        if (M == 7) return D;
+        if (M == 3) {
+            const uint32_t t = D | (D >> 4);
+            return (t & 0xffu) | ((t >> 8) & 0xff00u);
+        }
+        const uint32_t t = D | (D >> 6);
+        return (t | (t >> 12)) & 0xffu;
     }
-    return packed;
+    return encode4_any_exp(x[0], x[1], x[2], x[3], E, M);
 }
 
 template <int ES>
@@ -278,6 +313,38 @@ __device__ __forceinline__ void load4(const uint8_t *p, bool vec, uint32_t (&x)[
     }
 }
 
+#ifndef PACK_DIRECT_GROUP
+#define PACK_DIRECT_GROUP 8
+#endif
+
+// Encode (or relayout) the four elements a lane holds of block `blk` and store them into tile record `r`.
+template <int M, int ES, bool AF>
+__device__ __forceinline__ void direct_encode_store(uint32_t (&x)[4], uint32_t blk, uint8_t *r, int lane)
+{
+    if (M > 0) {
+        constexpr int MM = M > 0 ? M : 7;
+        if (ES == 2) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) x[i] = AF ? half_bits_to_float_bits(x[i]) : (x[i] << 16);
+        }
+        uint32_t mx = absmax4_bits(x);
+        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1, 4));
+        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2, 4));
+        const uint32_t E = mx >> 23;
+        const uint32_t packed = encode4_shared_exp<MM>(x, E);
+        if ((lane & 3) == 0) r[blk] = (uint8_t)(AF ? a_exponent_byte(E) : E);
+        uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
+        if (MM == 7) reinterpret_cast<uint32_t *>(q)[lane & 3] = packed;
+        else if (MM == 3) reinterpret_cast<uint16_t *>(q)[lane & 3] = (uint16_t)packed;
+        else q[lane & 3] = (uint8_t)packed;
+    } else {
+        uint8_t *q = r + ((uint64_t)blk * 16u + (lane & 3) * 4u) * ES;
+        if (ES == 4) *reinterpret_cast<uint4 *>(q) = make_uint4(x[0], x[1], x[2], x[3]);
+        else if (ES == 2) *reinterpret_cast<uint2 *>(q) = make_uint2(x[0] | (x[1] << 16), x[2] | (x[3] << 16));
+        else *reinterpret_cast<uint32_t *>(q) = x[0] | (x[1] << 8) | (x[2] << 16) | (x[3] << 24);
+    }
+}
+
 template <int M, int ES, bool AF>
 __global__ void __launch_bounds__(256)
 pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ PtrTable ptrs, int batch, int vec_ok)
@@ -286,10 +353,13 @@ pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
     const uint64_t warps_total = (uint64_t)gridDim.x * (blockDim.x >> 5);
     const uint64_t warp_id = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const uint64_t tiles = (uint64_t)batch * job.W * job.Z * job.Rt * job.Ct;
-    const uint32_t rec = job.tile_bytes, hdr = job.header_bytes;
+    const uint32_t hdr = job.header_bytes;
+    constexpr int G = PACK_DIRECT_GROUP;
     // A warp takes a whole tile per iteration: the tile's position is worked out once (the divisions by the run-time
-    // tensor dims were most of the instructions when a warp took an eighth of a tile), and the loads of all eight
-    // 8-row pieces (4 faces x 2 halves) are issued before the first is used.
+    // tensor dims were most of the instructions when a warp took an eighth of a tile).  A tile is eight pieces of
+    // 8 rows of one face (piece = face * 2 + half); with rows that allow vector loads, the loads of G pieces are
+    // issued before the first is encoded.  The element-wise loads of unaligned rows stay a rolled loop: unrolled,
+    // their code no longer fits the instruction cache.
     for (uint64_t tt = warp_id; tt < tiles; tt += warps_total) {
         uint64_t t = tt;
         const uint32_t ct = (uint32_t)(t % job.Ct); t /= job.Ct;
@@ -302,41 +372,31 @@ pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
         uint8_t *r = ptrs.dst[b] + tile_record_offset(job, w, z, rt, ct);
         if (hdr && lane < 8) reinterpret_cast<uint32_t *>(r)[lane] = 0;
         r += hdr;
-        uint32_t xs[8][4];
+        if (vec_ok) {
+#pragma unroll 1
+            for (int g = 0; g < 8; g += G) {
+                uint32_t xs[G][4];
 #pragma unroll
-        for (int hf = 0; hf < 8; hf++) {
-            const uint32_t face = hf >> 1, half = hf & 1u;
-            const uint32_t tr = (face >> 1) * 16u + half * 8u + (lane >> 2);   // row inside the tile
-            xs[hf][0] = xs[hf][1] = xs[hf][2] = xs[hf][3] = 0u;               // tiny tiles: rows >= tile_h stay zero
-            if (tr < job.tile_h) load4<ES>(tile_src + (uint64_t)tr * job.stride_r + (face & 1u) * 16u * ES, vec_ok != 0, xs[hf]);
-        }
-#pragma unroll
-        for (int hf = 0; hf < 8; hf++) {
-            const uint32_t face = hf >> 1, half = hf & 1u;
-            const uint32_t fr = half * 8u + (lane >> 2);
-            uint32_t (&x)[4] = xs[hf];
-            const uint32_t blk = face * 16u + fr;
-            if (M > 0) {
-                constexpr int MM = M > 0 ? M : 7;
-                if (ES == 2) {
-#pragma unroll
-                    for (int i = 0; i < 4; i++) x[i] = AF ? half_bits_to_float_bits(x[i]) : (x[i] << 16);
+                for (int j = 0; j < G; j++) {
+                    const uint32_t face = (uint32_t)(g + j) >> 1, half = (uint32_t)(g + j) & 1u;
+                    const uint32_t tr = (face >> 1) * 16u + half * 8u + (lane >> 2);   // row inside the tile
+                    xs[j][0] = xs[j][1] = xs[j][2] = xs[j][3] = 0u;                    // tiny tiles: rows >= tile_h stay zero
+                    if (tr < job.tile_h) load4<ES>(tile_src + (uint64_t)tr * job.stride_r + (face & 1u) * 16u * ES, true, xs[j]);
                 }
-                uint32_t mx = max(max(x[0] & 0x7fffffffu, x[1] & 0x7fffffffu), max(x[2] & 0x7fffffffu, x[3] & 0x7fffffffu));
-                mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1, 4));
-                mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2, 4));
-                const uint32_t E = mx >> 23;
-                const uint32_t packed = encode4_shared_exp<MM>(x, E);
-                if ((lane & 3) == 0) r[blk] = (uint8_t)(AF ? a_exponent_byte(E) : E);
-                uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
-                if (MM == 7) reinterpret_cast<uint32_t *>(q)[lane & 3] = packed;
-                else if (MM == 3) reinterpret_cast<uint16_t *>(q)[lane & 3] = (uint16_t)packed;
-                else q[lane & 3] = (uint8_t)packed;
-            } else {
-                uint8_t *q = r + ((uint64_t)blk * 16u + (lane & 3) * 4u) * ES;
-                if (ES == 4) *reinterpret_cast<uint4 *>(q) = make_uint4(x[0], x[1], x[2], x[3]);
-                else if (ES == 2) *reinterpret_cast<uint2 *>(q) = make_uint2(x[0] | (x[1] << 16), x[2] | (x[3] << 16));
-                else *reinterpret_cast<uint32_t *>(q) = x[0] | (x[1] << 8) | (x[2] << 16) | (x[3] << 24);
+#pragma unroll
+                for (int j = 0; j < G; j++) {
+                    const uint32_t face = (uint32_t)(g + j) >> 1, half = (uint32_t)(g + j) & 1u;
+                    direct_encode_store<M, ES, AF>(xs[j], face * 16u + half * 8u + (lane >> 2), r, lane);
+                }
+            }
+        } else {
+#pragma unroll 1
+            for (uint32_t hf = 0; hf < 8; hf++) {
+                const uint32_t face = hf >> 1, half = hf & 1u;
+                const uint32_t tr = (face >> 1) * 16u + half * 8u + (lane >> 2);
+                uint32_t x[4] = {0u, 0u, 0u, 0u};
+                if (tr < job.tile_h) load4<ES>(tile_src + (uint64_t)tr * job.stride_r + (face & 1u) * 16u * ES, false, x);
+                direct_encode_store<M, ES, AF>(x, face * 16u + half * 8u + (lane >> 2), r, lane);
             }
         }
     }
