@@ -60,14 +60,25 @@ __device__ __forceinline__ void bfp_encode16(const uint32_t (&x)[16], uint32_t &
                                              uint32_t (&out)[BfpTraits<M>::words])
 {
     constexpr uint32_t qmax = BfpTraits<M>::qmax;
-    uint32_t a[16];
-    uint32_t maxa = 0;
-#pragma unroll
-    for (int i = 0; i < 16; i++) {
-        a[i] = x[i] & 0x7fffffffu;
-        maxa = max(maxa, a[i]);
-    }
-    const uint32_t E = maxa >> 23;  // the magnitude with the largest exponent also has the largest bits
+    // Maximum of the magnitudes as floats: the absolute values fold into the min/max instructions, three operands
+    // at a time.  A NaN operand gives 0x7fffffff, so NaN and Inf both end with exponent field 255, as an integer
+    // maximum of the magnitude bits would; for every other input the two maxima have the same exponent field.
+    float mf;
+    asm("{\n\t.reg .f32 a<16>, m<7>;\n\t"
+        "abs.f32 a0, %1;\n\tabs.f32 a1, %2;\n\tabs.f32 a2, %3;\n\tabs.f32 a3, %4;\n\t"
+        "abs.f32 a4, %5;\n\tabs.f32 a5, %6;\n\tabs.f32 a6, %7;\n\tabs.f32 a7, %8;\n\t"
+        "abs.f32 a8, %9;\n\tabs.f32 a9, %10;\n\tabs.f32 a10, %11;\n\tabs.f32 a11, %12;\n\t"
+        "abs.f32 a12, %13;\n\tabs.f32 a13, %14;\n\tabs.f32 a14, %15;\n\tabs.f32 a15, %16;\n\t"
+        "max.NaN.f32 m0, a0, a1, a2;\n\tmax.NaN.f32 m1, a3, a4, a5;\n\tmax.NaN.f32 m2, a6, a7, a8;\n\t"
+        "max.NaN.f32 m3, a9, a10, a11;\n\tmax.NaN.f32 m4, a12, a13, a14;\n\t"
+        "max.NaN.f32 m5, m0, m1, m2;\n\tmax.NaN.f32 m6, m3, m4, a15;\n\t"
+        "max.NaN.f32 %0, m5, m6;\n\t}"
+        : "=f"(mf)
+        : "f"(__uint_as_float(x[0])), "f"(__uint_as_float(x[1])), "f"(__uint_as_float(x[2])), "f"(__uint_as_float(x[3])),
+          "f"(__uint_as_float(x[4])), "f"(__uint_as_float(x[5])), "f"(__uint_as_float(x[6])), "f"(__uint_as_float(x[7])),
+          "f"(__uint_as_float(x[8])), "f"(__uint_as_float(x[9])), "f"(__uint_as_float(x[10])), "f"(__uint_as_float(x[11])),
+          "f"(__uint_as_float(x[12])), "f"(__uint_as_float(x[13])), "f"(__uint_as_float(x[14])), "f"(__uint_as_float(x[15])));
+    const uint32_t E = __float_as_uint(mf) >> 23;
     E_out = E;
 
     if (E + 1u >= (uint32_t)M && E <= (uint32_t)(M + 252)) {
@@ -76,7 +87,8 @@ __device__ __forceinline__ void bfp_encode16(const uint32_t (&x)[16], uint32_t &
 #pragma unroll
         for (int i = 0; i < 16; i++) {
             float r;
-            asm("fma.rn.ftz.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(__uint_as_float(a[i])), "f"(S), "f"(12582912.0f));
+            asm("{\n\t.reg .f32 t;\n\tabs.ftz.f32 t, %1;\n\tfma.rn.ftz.f32 %0, t, %2, %3;\n\t}"
+                : "=f"(r) : "f"(__uint_as_float(x[i])), "f"(S), "f"(12582912.0f));
             y[i] = min(__float_as_uint(r), kMagicBits + qmax);  // Inf / NaN and round-ups saturate here
         }
         uint32_t D[4];
