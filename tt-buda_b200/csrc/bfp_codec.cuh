@@ -167,13 +167,15 @@ template <int M>
 __device__ __forceinline__ bool bfp_encode16_bf16(const uint32_t (&h)[8], uint32_t &E_out, uint32_t (&out)[BfpTraits<M>::words])
 {
     constexpr uint32_t qmax = BfpTraits<M>::qmax;
-    uint32_t a[8];
-    uint32_t mx = 0;
-#pragma unroll
-    for (int w = 0; w < 8; w++) {
-        a[w] = h[w] & 0x7fff7fffu;
-        mx = max_u16x2(mx, a[w]);
-    }
+    uint32_t mx;
+    // block maximum of the magnitudes as bfloat16 pairs; a NaN gives 0x7fff, i.e. exponent field 255 like Inf
+    asm("{\n\t.reg .b32 a<8>, m<6>;\n\t"
+        "abs.bf16x2 a0, %1;\n\tabs.bf16x2 a1, %2;\n\tabs.bf16x2 a2, %3;\n\tabs.bf16x2 a3, %4;\n\t"
+        "abs.bf16x2 a4, %5;\n\tabs.bf16x2 a5, %6;\n\tabs.bf16x2 a6, %7;\n\tabs.bf16x2 a7, %8;\n\t"
+        "max.NaN.bf16x2 m0, a0, a1;\n\tmax.NaN.bf16x2 m1, a2, a3;\n\tmax.NaN.bf16x2 m2, a4, a5;\n\t"
+        "max.NaN.bf16x2 m3, a6, a7;\n\tmax.NaN.bf16x2 m4, m0, m1;\n\tmax.NaN.bf16x2 m5, m2, m3;\n\t"
+        "max.NaN.bf16x2 %0, m4, m5;\n\t}"
+        : "=r"(mx) : "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]));
     const uint32_t E = max(mx & 0xffffu, mx >> 16) >> 7;
     E_out = E;
     if (E < 17u || E > 253u) return false;
@@ -182,7 +184,7 @@ __device__ __forceinline__ bool bfp_encode16_bf16(const uint32_t (&h)[8], uint32
 #pragma unroll
     for (int w = 0; w < 8; w++) {
         uint32_t r;
-        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a[w]), "r"(S), "r"(0x43004300u));
+        asm("{\n\t.reg .b32 t;\n\tabs.bf16x2 t, %1;\n\tfma.rn.bf16x2 %0, t, %2, %3;\n\t}" : "=r"(r) : "r"(h[w]), "r"(S), "r"(0x43004300u));
         r = min_u16x2(r, 0x43004300u + qmax * 0x00010001u);
         const uint32_t q2 = r & (qmax * 0x00010001u);
         const uint32_t sign_bit = (qmax + 1u) * 0x00010001u;            // the datum's sign position in each half
@@ -284,25 +286,30 @@ template <int M>
 __device__ __forceinline__ bool bfp_decode16_bf16(uint32_t E, const uint32_t (&in)[BfpTraits<M>::words], uint32_t (&o)[8])
 {
     if (E < (uint32_t)M || E > 252u) return false;
-    constexpr uint32_t qmax = BfpTraits<M>::qmax;
     constexpr uint32_t base = ((uint32_t)(127 + M) << 7) * 0x00010001u;           // 2^M in both halves
     const uint32_t sc = (E - (uint32_t)(M - 1)) * 0x00800080u;                      // s: exponent field E - (M-1)
     const uint32_t off = ((E + 1u) * 0x00800080u) | 0x80008000u;                    // -(2^M * s): exponent field E + 1
+    // byte-aligned data: `lane[r]` holds, in byte j, datum (data per byte) * j + r shifted so that its sign is
+    // bit 7 and its magnitude starts at bit 6
+    constexpr int kPerByte = 8 / (M + 1);                                           // 1 / 2 / 4 data per byte
+    uint32_t lane[BfpTraits<M>::words][kPerByte];
+#pragma unroll
+    for (int w = 0; w < BfpTraits<M>::words; w++) {
+#pragma unroll
+        for (int r = 0; r < kPerByte; r++)
+            lane[w][r] = M == 7 ? in[w] : (in[w] << ((kPerByte - 1 - r) * (M + 1))) & ((0xffu << (7 - M)) & 0xffu) * 0x01010101u;
+    }
 #pragma unroll
     for (int p = 0; p < 8; p++) {
-        uint32_t pair;                                                              // datum 2p in bits 0.., datum 2p+1 in bits 16..
-        if (M == 7) {
-            pair = __byte_perm(in[(p / 2) % BfpTraits<M>::words], 0u, (p & 1) ? 0x4342 : 0x4140);
-        } else {
-            const uint32_t w = in[((2 * p) * (M + 1) / 32) % BfpTraits<M>::words] >> (((2 * p) * (M + 1)) % 32);
-            pair = (w & (2u * qmax + 1u)) | (((w >> (M + 1)) & (2u * qmax + 1u)) << 16);
-        }
-        const uint32_t q2 = pair & (qmax * 0x00010001u);
-        const uint32_t nz = ((q2 + qmax * 0x00010001u) >> M) & 0x00010001u;          // 1 per half iff q > 0
-        const uint32_t sgn = ((pair >> M) & nz) << 15;                              // sign bit, only beside a magnitude
-        uint32_t r;
-        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(base | (q2 << (7 - M))), "r"(sc), "r"(off));
-        o[p] = r | sgn;
+        // PP: datum 2p in bytes 0 and 1, datum 2p + 1 in bytes 2 and 3
+        const int d0 = 2 * p, d1 = 2 * p + 1;
+        const int w0 = d0 / (4 * kPerByte);                                         // both data sit in the same word
+        const int j0 = (d0 / kPerByte) % 4, j1 = (d1 / kPerByte) % 4;
+        const uint32_t A = lane[w0][d0 % kPerByte], B = lane[w0][d1 % kPerByte];
+        const uint32_t PP = __byte_perm(A, B, (uint32_t)(j0 | (j0 << 4) | ((4 + j1) << 8) | ((4 + j1) << 12)));
+        const uint32_t x = (PP & 0x807f807fu) | base;                                // +-(2^M + q)
+        const uint32_t o2 = off ^ (PP & 0x80008000u);                                // -+(2^M * s)
+        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(o[p]) : "r"(x), "r"(sc), "r"(o2));   // +-(q * s); +0 when q is 0
     }
     return true;
 }
