@@ -147,7 +147,7 @@ def make_batch(torch, device, seed0, n):
     return xs
 
 
-def profile_one(torch, cuda_ops, dev, name, reps=6):
+def profile_one(torch, cuda_ops, dev, name, reps=20, nt=8):
     """One secondary kernel on a case that ends by itself in milliseconds: for ncu captures."""
     if name == "gemm":
         M, K, N = 8192, 4096, 16384
@@ -162,22 +162,22 @@ def profile_one(torch, cuda_ops, dev, name, reps=6):
         sc = torch.rand(N, device=dev) * 2e-5
         fn, work, unit = (lambda: cuda_ops.i8_matmul(a, wimg, N, scale=sc, zero_point=0.0, out="int8")), 2.0 * M * N * K / 1e12, "TOP/s"
     elif name in ("pack_bf16", "unpack_bf16"):
-        xs = [torch.randn(SHAPE, device=dev).bfloat16() for _ in range(8)]
+        xs = [torch.randn(SHAPE, device=dev).bfloat16() for _ in range(nt)]
         imgs = cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b)
         if name == "pack_bf16":
             fn = lambda: cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b, outs=imgs)
         else:
             fn = lambda: cuda_ops.unpack_untilize_batch(imgs, cuda_ops.DF.Bfp8_b, SHAPE, outs=xs)
-        work, unit = 8 * ELEMS * 3.0625 / 1e9, "GB/s"
-    elif name in ("unpack", "pack_direct", "unpack_direct"):
-        xs = [torch.randn(SHAPE, device=dev) for _ in range(8)]
+        work, unit = nt * ELEMS * 3.0625 / 1e9, "GB/s"
+    elif name in ("pack", "unpack", "pack_direct", "unpack_direct"):
+        xs = [torch.randn(SHAPE, device=dev) for _ in range(nt)]
         imgs = cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b)
         path = 1 if name.endswith("_direct") else None      # 1 = the kernels that unaligned tensors and tiny tiles take
-        if name == "pack_direct":
-            fn = lambda: cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b, outs=imgs, path=1)
+        if name in ("pack", "pack_direct"):
+            fn = lambda: cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b, outs=imgs, path=1 if name == "pack_direct" else None)
         else:
             fn = lambda: cuda_ops.unpack_untilize_batch(imgs, cuda_ops.DF.Bfp8_b, SHAPE, outs=xs, path=path)
-        work, unit = 8 * ELEMS * BYTES_PER_ELEM / 1e9, "GB/s"
+        work, unit = nt * ELEMS * BYTES_PER_ELEM / 1e9, "GB/s"
     else:
         n = 32 * 1024 * 1024 * 4  # 512 MiB of fp32: larger than L2
         sc = torch.tensor([0.05], device=dev)
@@ -254,7 +254,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (for profiler captures)")
     ap.add_argument("--tensors", type=int, default=N_TENSORS,
                     help="tensors per GPU batch; anything but 64 is a reduced case for profiler captures")
-    ap.add_argument("--profile-kernel", default=None, choices=["gemm", "i8gemm", "unpack", "pack_direct", "unpack_direct", "pack_bf16", "unpack_bf16", "quantize", "dequantize", "requantize"],
+    ap.add_argument("--profile-kernel", default=None, choices=["gemm", "i8gemm", "pack", "unpack", "pack_direct", "unpack_direct", "pack_bf16", "unpack_bf16", "quantize", "dequantize", "requantize"],
                     help="run only this secondary kernel a few times and exit (small, self-ending case for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -294,7 +294,7 @@ def main():
 
     hbm_peak, peak_kind = peaks()
     if args.profile_kernel:
-        profile_one(torch, cuda_ops, dev, args.profile_kernel)
+        profile_one(torch, cuda_ops, dev, args.profile_kernel, nt=8 if args.tensors == N_TENSORS else args.tensors)
         return
     NT = args.tensors
     xs = make_batch(torch, dev, 1000 + N_TENSORS * rank, NT)

@@ -69,6 +69,7 @@ struct TileJob {
     uint32_t zn1, zn2;
     uint64_t stride_z_mid, stride_z_out;
     uint32_t tile_h;                    // tensor rows per tile: 32, or 16 / 8 / 4 / 2 / 1 for tiny tiles (direct kernels only)
+    uint32_t work_slot;                 // staged kernels: which work counter this launch draws its items from
 };
 
 // byte offset of slice z on the row-major side
@@ -78,6 +79,40 @@ __host__ __device__ inline uint64_t rm_z_offset(const TileJob &j, uint32_t z)
     return (uint64_t)(z % j.zn1) * j.stride_z + (uint64_t)((z / j.zn1) % j.zn2) * j.stride_z_mid +
            (uint64_t)(z / (j.zn1 * j.zn2)) * j.stride_z_out;
 }
+
+// Work items of a staged kernel are handed out in address order from a counter in device memory: a CTA that finishes
+// an item takes the next one, so the set of items in flight stays one compact, advancing window of the tensors.
+// With a fixed assignment (item = CTA + k * grid) the CTAs drift apart and the window spreads; on a stream that is
+// mostly stores that costs 15 % of the bandwidth (measured with a bare 1-byte-in / 4-bytes-out kernel on 32-row x
+// 1 KiB bands: 5.69 TB/s fixed, 6.63 TB/s from a counter, the same as one short-lived block per band).
+// A launch takes one of kWorkSlots counters round-robin and leaves it zeroed: the CTA that leaves last resets it.
+// Two launches share a counter only if kWorkSlots other launches were issued while the first still runs.
+struct WorkCounter {
+    unsigned int next, done;
+};
+constexpr int kWorkSlots = 1024;
+
+#ifdef __CUDACC__
+// Lane 0 asks for the next item; the answer is only waited for where work_fetch_get() uses it, so a producer warp
+// asks before it issues the current item's copies and reads the answer after them.
+__device__ __forceinline__ uint32_t work_fetch_issue(WorkCounter *wc, int lane)
+{
+    uint32_t v = 0;
+    if (lane == 0) v = atomicAdd(&wc->next, 1u);
+    return v;
+}
+__device__ __forceinline__ uint32_t work_fetch_get(uint32_t issued) { return __shfl_sync(0xffffffffu, issued, 0); }
+// one thread per CTA, after the CTA's last fetch, on every way out of the kernel
+__device__ __forceinline__ void work_leave(WorkCounter *wc)
+{
+    __threadfence();
+    if (atomicAdd(&wc->done, 1u) == gridDim.x - 1u) {
+        wc->next = 0u;
+        wc->done = 0u;
+        __threadfence();
+    }
+}
+#endif
 
 struct PtrTable {
     const uint8_t *src[kMaxBatch];

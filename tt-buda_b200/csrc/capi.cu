@@ -141,6 +141,7 @@ int make_job(const uint32_t shape[4], const uint64_t strides[4], const buda_queu
                     (unsigned long long)g->grid_c * g->mblock_n * g->ublock_ct * 32u, shape[2], shape[3]);
     j.W = shape[0]; j.Z = shape[1]; j.Rt = shape[2] / th; j.Ct = shape[3] / 32;
     j.tile_h = th;
+    j.work_slot = 0;                    // set per launch by the staged launchers
     j.stride_w = strides[0]; j.stride_z = strides[1]; j.stride_r = strides[2];
     j.box_tiles = (uint32_t)box_tiles_for((int)strides[3], bfp_mant_bits(qdf) != 0);
     j.boxes_per_band = (j.Ct + j.box_tiles - 1) / j.box_tiles;

@@ -327,7 +327,10 @@ static unsigned grid_for_groups(int64_t groups, int sm_count)
 {
     const int64_t per_block = (int64_t)(kThreadsPerBlock / 32) * 128;  // groups one block covers per sweep
     int64_t blocks = (groups + per_block - 1) / per_block;
-    const int64_t cap = (int64_t)sm_count * 64;
+    // No resident-wave cap here: this kernel is four fifths stores, and short-lived blocks handed out in address
+    // order ran 3.6 % faster than 64 blocks per SM striding over the tensor (6240 vs 6020 GB/s at 2^27 elements).
+    (void)sm_count;
+    const int64_t cap = 0x7fffffff;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     return (unsigned)blocks;

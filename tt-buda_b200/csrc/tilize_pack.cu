@@ -69,6 +69,9 @@ __device__ __forceinline__ void decode_item(const TileJob &job, uint32_t item, I
     m.ntiles = min(job.box_tiles, job.Ct - m.ct0);
 }
 
+static __device__ WorkCounter g_pack_work[kWorkSlots];
+static std::atomic<unsigned> g_next_work_slot{0};   // host side: the counter the next staged launch takes
+
 template <int M, int ES, bool AF>
 __global__ void __launch_bounds__(kStagedThreads)
 pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ PtrTable ptrs, unsigned int *status)
@@ -101,9 +104,12 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
 
     if (warp == kConsumerWarps) {
         // ---------------------------------------------------------------- producer warp
+        WorkCounter *wc = &g_pack_work[job.work_slot];
         uint32_t it = 0;
         bool ok = true;
-        for (uint32_t item = blockIdx.x; item < job.total_items; item += gridDim.x, ++it) {
+        uint32_t item = work_fetch_get(work_fetch_issue(wc, lane));
+        for (; item < job.total_items; ++it) {
+            const uint32_t next_issued = work_fetch_issue(wc, lane);   // asked for now, read after this item's copies are on their way
             const int s = it % S;
             const uint32_t ph = (it / S) & 1u;
             if (!mbar_wait_bounded(&empty[s], ph ^ 1u, abort_flag, status, BUDA_DEVSTAT_PACK_EMPTY_WAIT)) {
@@ -121,7 +127,21 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
             const uint8_t *src = ptrs.src[m.b] + (uint64_t)m.w * job.stride_w + rm_z_offset(job, m.z) +
                                  ((uint64_t)m.rt * 32u + lane) * job.stride_r + (uint64_t)m.ct0 * 32u * ES;
             bulk_g2s(in_stage + s * Cfg::in_stage_bytes + lane * Cfg::pitch, src, row_copy, &full[s]);
+            item = work_fetch_get(next_issued);
         }
+        if (ok) {
+            // no items left: an empty item in the next stage tells the consumer warps to leave
+            const int s = it % S;
+            if (mbar_wait_bounded(&empty[s], ((it / S) & 1u) ^ 1u, abort_flag, status, BUDA_DEVSTAT_PACK_EMPTY_WAIT)) {
+                if (lane == 0) {
+                    meta[s].ntiles = 0;
+                    mbar_arrive(&full[s]);
+                }
+            } else {
+                ok = false;
+            }
+        }
+        if (lane == 0) work_leave(wc);
         if (!ok || *abort_flag) {
             // gave up: let the copies already issued land before the CTA releases its shared memory
             const uint32_t back = it < (uint32_t)S ? it : (uint32_t)S;
@@ -137,11 +157,12 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
     // -------------------------------------------------------------------- consumer warps
     const int fr = lane & 15;
     uint32_t it = 0;
-    for (uint32_t item = blockIdx.x; item < job.total_items; item += gridDim.x, ++it) {
+    for (;; ++it) {
         const int s = it % S;
         const uint32_t ph = (it / S) & 1u;
         const bool ok = mbar_wait_bounded(&full[s], ph, abort_flag, status, BUDA_DEVSTAT_PACK_FULL_WAIT);
         const ItemMeta m = meta[s];
+        if (ok && m.ntiles == 0) break;   // the producer's end marker: the same for every consumer thread
         uint8_t *ob = out_buf + (it & 1u) * Cfg::out_buf_bytes;
         const uint8_t *stage = in_stage + s * Cfg::in_stage_bytes;
 
@@ -428,7 +449,9 @@ static cudaError_t launch_staged(const TileJob &job, const PtrTable &ptrs, int s
     }
     uint32_t grid = (uint32_t)(sm_count * per_sm);
     if (grid > job.total_items) grid = job.total_items;
-    pack_staged_kernel<M, ES, AF><<<grid, kStagedThreads, Cfg::smem_bytes, stream>>>(job, ptrs, status);
+    TileJob launch_job = job;
+    launch_job.work_slot = g_next_work_slot.fetch_add(1u, std::memory_order_relaxed) % kWorkSlots;
+    pack_staged_kernel<M, ES, AF><<<grid, kStagedThreads, Cfg::smem_bytes, stream>>>(launch_job, ptrs, status);
     return cudaGetLastError();
 }
 
