@@ -147,6 +147,27 @@ def make_batch(torch, device, seed0, n):
     return xs
 
 
+_RESULT_OUT = None
+
+
+def emit(text):
+    """Write a result line to the process's original standard output."""
+    out = _RESULT_OUT or sys.stdout
+    out.write(text + "\n")
+    out.flush()
+
+
+def keep_stdout_for_results():
+    """Point file descriptor 1 at standard error for everything else this process (and the libraries it loads: NCCL
+    prints a version banner on fd 1 when NCCL_DEBUG is set) may write, so that standard output carries the result
+    line and nothing else."""
+    global _RESULT_OUT
+    if _RESULT_OUT is None:
+        sys.stdout.flush()
+        _RESULT_OUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
 def profile_one(torch, cuda_ops, dev, name, reps=20, nt=8):
     """One secondary kernel on a case that ends by itself in milliseconds: for ncu captures."""
     if name == "gemm":
@@ -202,7 +223,7 @@ def profile_one(torch, cuda_ops, dev, name, reps=20, nt=8):
     a1.record()
     torch.cuda.synchronize()
     ms = a0.elapsed_time(a1) / reps
-    print(json.dumps({"kernel": name, "ms": ms, unit: work / (ms * 1e-3)}), flush=True)
+    emit(json.dumps({"kernel": name, "ms": ms, unit: work / (ms * 1e-3)}))
 
 
 def run_reference(args, rank, world):
@@ -239,10 +260,11 @@ def run_reference(args, rank, world):
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(json.dumps(line))
 
 
 def main():
+    keep_stdout_for_results()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -616,7 +638,7 @@ def main():
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
             "other_kernels": extras,
         }
-        print(json.dumps(line), flush=True)
+        emit(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
 
