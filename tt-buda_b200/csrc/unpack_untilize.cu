@@ -27,7 +27,7 @@ struct UItemMeta {
 
 template <int M, int ES>
 struct UnpackCfg {
-    static constexpr int box = box_tiles_for(ES, M > 0);
+    static constexpr int box = unpack_box_tiles_for(ES, M > 0);
     static constexpr int row_bytes = box * 32 * ES;
     static constexpr int pitch = row_bytes + 16;
     static constexpr int out_buf_bytes = 32 * pitch;
@@ -402,9 +402,10 @@ static cudaError_t launch_ustaged(const TileJob &job, const PtrTable &ptrs, int 
         per_sm = n < 1 ? 1 : (n > 4 ? 4 : n);
         per_sm_cache[dev].store(per_sm, std::memory_order_release);
     }
-    uint32_t grid = (uint32_t)(sm_count * per_sm);
-    if (grid > job.total_items) grid = job.total_items;
     TileJob launch_job = job;
+    if (!set_box_tiles(launch_job, Cfg::box)) return cudaErrorInvalidValue;   // more than 2^31 work items: split the batch
+    uint32_t grid = (uint32_t)(sm_count * per_sm);
+    if (grid > launch_job.total_items) grid = launch_job.total_items;
     launch_job.work_slot = g_next_work_slot.fetch_add(1u, std::memory_order_relaxed) % kWorkSlots;
     unpack_staged_kernel<M, ES, AF><<<grid, kUStagedThreads, Cfg::smem_bytes, stream>>>(launch_job, ptrs, status);
     return cudaGetLastError();
