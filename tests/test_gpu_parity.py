@@ -550,3 +550,38 @@ def test_bfloat16_sources_against_the_exact_arithmetic_spec(ops, df_name, m, pat
         assert img[t * rec + blk] == E, (b, "exponent", img[t * rec + blk], E)
         got = img[t * rec + 64 + blk * 2 * (m + 1): t * rec + 64 + (blk + 1) * 2 * (m + 1)]
         assert got.tobytes() == data, (b, "datums", hb[b], got, list(data))
+
+
+# ------------------------------------------------------------------------------------------------
+# The staged kernels draw their work items from a counter in device memory (one of 1024, taken round-robin per launch
+# and left zeroed by the launch).  More launches than counters, and launches that overlap on two streams.
+# ------------------------------------------------------------------------------------------------
+def test_work_counters_survive_reuse_and_concurrent_streams(ops, oracle):
+    g = torch.Generator().manual_seed(77)
+    small = torch.randn(1, 1, 64, 512, generator=g).cuda()
+    want_small = oracle.tilize_pack(small.cpu().numpy(), oracle.Bfp8_b)
+    img = ops.tilize_pack(small, ops.DF.Bfp8_b)
+    back = torch.empty_like(small)
+    for _ in range(1300):                                   # wraps the ring of counters, pack and unpack
+        ops.tilize_pack_batch([small], ops.DF.Bfp8_b, outs=[img])
+        ops.unpack_untilize_batch([img], ops.DF.Bfp8_b, tuple(small.shape), outs=[back])
+    assert np.array_equal(img.cpu().numpy(), want_small)
+    assert np.array_equal(_bits(back.cpu().numpy()),
+                          _bits(oracle.unpack_untilize(want_small, oracle.Bfp8_b, tuple(small.shape))))
+
+    # two streams, each packing its own 64 MiB tensor several times so that the launches overlap
+    xs = [torch.randn(1, 1, 4096, 4096, generator=g).cuda() for _ in range(2)]
+    outs = [ops.tilize_pack(x, ops.DF.Bfp8_b) for x in xs]
+    want = [o.clone() for o in outs]
+    for o in outs:
+        o.zero_()
+    streams = [torch.cuda.Stream() for _ in range(2)]
+    torch.cuda.synchronize()
+    for _ in range(6):
+        for x, o, st in zip(xs, outs, streams):
+            with torch.cuda.stream(st):
+                ops.tilize_pack_batch([x], ops.DF.Bfp8_b, outs=[o])
+    torch.cuda.synchronize()
+    for o, w in zip(outs, want):
+        assert torch.equal(o, w)
+    assert ops._cabi.device_status() == (0, 0)
