@@ -287,6 +287,19 @@ def test_quant_odd_sizes_and_axes(ops, oracle):
         s2 = torch.rand(shape[ax], generator=g) + 0.5
         rq = ops.requantize(acc.cuda(), (s * 1e-4).cuda(), s2.cuda(), -2, axis=axis)
         assert np.array_equal(rq.cpu().numpy(), oracle.requantize(acc.numpy(), (s * 1e-4).numpy(), s2.numpy(), -2, axis=axis))
+    # one scale for the whole tensor: a whole number of 16-element chunks takes the kernels without a loop, any other
+    # size the general ones; both requantise modes
+    for n in (4096 * 5, 4096 * 5 + 16, 4096 * 5 + 7):
+        x = (torch.randn(n, generator=g) * 40).view(-1)
+        s1 = torch.tensor([0.37])
+        for zp in (0, -5):
+            assert np.array_equal(ops.quantize(x.cuda(), s1.cuda(), zp).cpu().numpy(), oracle.quantize(x.numpy(), s1.numpy(), zp)), n
+        acc = torch.randint(-2 ** 22, 2 ** 22, (n,), generator=g, dtype=torch.int32)
+        sa, sb = torch.tensor([3.1e-5]), torch.tensor([0.73])
+        assert np.array_equal(ops.requantize(acc.cuda(), sa.cuda(), sb.cuda(), 4).cpu().numpy(),
+                              oracle.requantize(acc.numpy(), sa.numpy(), sb.numpy(), 4)), n
+        assert np.array_equal(ops.buda_requantize(acc.cuda(), sa.cuda(), -1).cpu().numpy(),
+                              oracle.buda_requantize(acc.numpy(), sa.numpy(), -1)), n
     # misaligned base pointers take the scalar path
     x = torch.randn(1001, generator=g).cuda()[1:]
     s = torch.tensor([0.1])

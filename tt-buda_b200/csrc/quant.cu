@@ -197,6 +197,56 @@ quantize_kernel(const float *__restrict__ x, int64_t n, const float *__restrict_
     }
 }
 
+// The same arithmetic for the commonest case (one scale for the tensor, aligned pointers, int8 bounds, a whole number
+// of chunks), one chunk per thread and no loop: the four data loads are issued first, so nothing waits for the scale
+// before them, and blocks that live for one sweep are handed out in address order by the hardware.
+template <int MODE>
+__global__ void __launch_bounds__(256)
+quantize_once_kernel(const float *__restrict__ x, int64_t chunks, const float *__restrict__ scale, float zp, float lo, float hi,
+                     int8_t *__restrict__ out, float screen)
+{
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= chunks) return;
+    const int64_t i0 = c << 4;
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float4 t = __ldcs(reinterpret_cast<const float4 *>(x + i0) + j);
+        v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+    }
+    const float sc = __ldg(scale);
+    bool rounded = false;
+    if (MODE == 0 && screen > 0.0f) {
+        const float a = fabsf(sc);
+        if (a >= 7.8886090522101181e-31f && a <= 1.2676506002282294e30f) {   // 2^-100 .. 2^100; NaN fails
+            const float r = __frcp_rn(sc);
+            float t[16];
+            bool risky = false;
+#pragma unroll
+            for (int k = 0; k < 16; k++) {
+                const float qa = __fmul_rn(v[k], r);
+                t[k] = __fadd_rn(__fadd_rn(qa, 12582912.0f), -12582912.0f);
+                risky = risky || (fabsf(fabsf(__fsub_rn(qa, t[k])) - 0.5f) < screen);
+            }
+            if (!risky) {
+#pragma unroll
+                for (int k = 0; k < 16; k++) v[k] = t[k];
+                rounded = true;
+            }
+        }
+    }
+    if (!rounded) {
+#pragma unroll
+        for (int k = 0; k < 16; k++) v[k] = (MODE == 0) ? __fdiv_rn(v[k], sc) : __fmul_rn(v[k], sc);
+        round_half_even16(v);
+    }
+    uint32_t q[16];
+#pragma unroll
+    for (int k = 0; k < 16; k++) q[k] = clamp_cast_i8<true>(__fadd_rn(v[k], zp), lo, hi);
+    __stcs(reinterpret_cast<uint4 *>(out + i0), make_uint4(pack_i8x4(q[0], q[1], q[2], q[3]), pack_i8x4(q[4], q[5], q[6], q[7]),
+                                                            pack_i8x4(q[8], q[9], q[10], q[11]), pack_i8x4(q[12], q[13], q[14], q[15])));
+}
+
 // ------------------------------------------------------------------------------------------------
 // dequantize
 // ------------------------------------------------------------------------------------------------
@@ -311,6 +361,41 @@ requantize_kernel(const int32_t *__restrict__ x, int64_t n, const float *__restr
     }
 }
 
+// One chunk per thread and no loop (see quantize_once_kernel): one scale for the tensor, aligned pointers, int8 bounds,
+// a whole number of chunks.
+template <int MODE, int SM>
+__global__ void __launch_bounds__(256)
+requantize_once_kernel(const int32_t *__restrict__ x, int64_t chunks, const float *__restrict__ scale_a,
+                       const float *__restrict__ scale_b, ScaleSel sel, float zp, float lo, float hi, int8_t *__restrict__ out)
+{
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= chunks) return;
+    const int64_t i0 = c << 4;
+    int xi[16];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int4 t = __ldcs(reinterpret_cast<const int4 *>(x + i0) + j);
+        xi[4 * j] = t.x; xi[4 * j + 1] = t.y; xi[4 * j + 2] = t.z; xi[4 * j + 3] = t.w;
+    }
+    float s[16];
+    load_scales16<SM>(scale_a, sel, i0, 16, s);
+    if (MODE == 0) {
+        float sb[16];
+        load_scales16<SM>(scale_b, sel, i0, 16, sb);
+#pragma unroll
+        for (int k = 0; k < 16; k++) s[k] = __fdiv_rn(s[k], sb[k]);
+    }
+    float pz[16];
+#pragma unroll
+    for (int k = 0; k < 16; k++) pz[k] = __fadd_rn(__fmul_rn(s[k], __int2float_rn(xi[k])), zp);
+    round_half_even16(pz);
+    uint32_t q[16];
+#pragma unroll
+    for (int k = 0; k < 16; k++) q[k] = clamp_cast_i8<true>(pz[k], lo, hi);
+    __stcs(reinterpret_cast<uint4 *>(out + i0), make_uint4(pack_i8x4(q[0], q[1], q[2], q[3]), pack_i8x4(q[4], q[5], q[6], q[7]),
+                                                            pack_i8x4(q[8], q[9], q[10], q[11]), pack_i8x4(q[12], q[13], q[14], q[15])));
+}
+
 // ------------------------------------------------------------------------------------------------
 // host launchers
 // ------------------------------------------------------------------------------------------------
@@ -382,6 +467,13 @@ cudaError_t launch_quantize(const float *x, int64_t n, const float *scale, int64
         const float B = fmaxf(fabsf(lo), fabsf(hi)) + fabsf(zp);
         screen = (B + 2.0f) * 2.384185791015625e-07f;   // (B + 2) * 2^-22
     }
+    if (vec && fast && sm == kScalePerTensor && (n & 15) == 0 && n > 0) {
+        const int64_t chunks = n >> 4;
+        const unsigned once_grid = (unsigned)((chunks + 255) / 256);
+        if (mode == 0) quantize_once_kernel<0><<<once_grid, 256, 0, stream>>>(x, chunks, scale, zp, lo, hi, out, screen);
+        else quantize_once_kernel<1><<<once_grid, 256, 0, stream>>>(x, chunks, scale, zp, lo, hi, out, screen);
+        return cudaGetLastError();
+    }
 #define CALL(SMV)                                                                                                     \
     if (mode == 0) {                                                                                                  \
         if (vec && fast) quantize_kernel<0, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale, sel, zp, lo, hi, out, hoist, screen);   \
@@ -435,6 +527,16 @@ cudaError_t launch_requantize(const int32_t *x, int64_t n, const float *scale_a,
     const bool fast = lo >= -4194304.0f && hi <= 4194304.0f;
     // same scales in every sweep of the grid?  (per-tensor: trivially; last axis: stride a multiple of the period)
     const int hoist = (sm == kScalePerTensor || (sm == kScaleLastAxis16 && ((int64_t)grid * 256 * 16) % scale_len == 0)) ? 1 : 0;
+    // (with scales along the last axis the resident blocks that fetch their 16 scales once stay faster: 6070 vs 5070 GB/s)
+    if (vec && fast && sm == kScalePerTensor && (n & 15) == 0 && n > 0) {
+        const int64_t chunks = n >> 4;
+        const unsigned once_grid = (unsigned)((chunks + 255) / 256);
+        if (mode == 0)
+            requantize_once_kernel<0, kScalePerTensor><<<once_grid, 256, 0, stream>>>(x, chunks, scale_a, scale_b, sel, zp, lo, hi, out);
+        else
+            requantize_once_kernel<1, kScalePerTensor><<<once_grid, 256, 0, stream>>>(x, chunks, scale_a, scale_b, sel, zp, lo, hi, out);
+        return cudaGetLastError();
+    }
 #define CALL(SMV)                                                                                                                 \
     if (mode == 0) {                                                                                                              \
         if (vec && fast) requantize_kernel<0, SMV, true, true><<<grid, 256, 0, stream>>>(x, n, scale_a, scale_b, sel, zp, lo, hi, out, hoist);  \
