@@ -634,6 +634,9 @@ def main():
                          # dram read+write per launch: ncu on an 8-tensor launch measured 82.57 MB per tensor
                          # (profiles/pack_staged_kernel_bfp8b_cfg2.md); traffic grows with the tensor count
                          "traffic": NT * 82.6e6, "traffic_unit": "bytes per launch, scaled from an 8-tensor ncu capture", "peak_kind": peak_kind, "kernel": "pack_staged_kernel<7,4>",
+                         # the peak is a 1:1 copy; this stream is 4/5 reads, for which a bare kernel (4 bytes in, 1 byte
+                         # out per element, same access shape) measured 7190 GB/s on this pool, read-only 7430
+                         "bare_kernel_same_mix_gbs": 7190.0,
                          "kernel_ms": kernel_ms},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
             "other_kernels": extras,
