@@ -170,6 +170,15 @@ def keep_stdout_for_results():
 
 def profile_one(torch, cuda_ops, dev, name, reps=20, nt=8):
     """One secondary kernel on a case that ends by itself in milliseconds: for ncu captures."""
+    if name == "bare_streams":
+        # every mix x schedule of the bare streaming kernels, 2^29 elements (2 GiB on the 4-byte side)
+        n_el = 1 << 29
+        out = {"elements": n_el, "unit": "GB/s"}
+        for mix, mname in ((0, "4_read_1_written"), (1, "1_read_4_written"), (2, "read_only"), (3, "write_only")):
+            out[mname] = {sname: round(cuda_ops.stream_probe(mix, sv, n_el), 1)
+                          for sname, sv in (("one_block_per_band", 0), ("resident_fixed_stride", 1), ("resident_device_counter", 2))}
+        emit(json.dumps({"kernel": name, **out}))
+        return
     if name == "gemm":
         M, K, N = 8192, 4096, 16384
         a = torch.randn(M, K, device=dev).bfloat16()
@@ -276,7 +285,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (for profiler captures)")
     ap.add_argument("--tensors", type=int, default=N_TENSORS,
                     help="tensors per GPU batch; anything but 64 is a reduced case for profiler captures")
-    ap.add_argument("--profile-kernel", default=None, choices=["gemm", "i8gemm", "pack", "unpack", "pack_direct", "unpack_direct", "pack_bf16", "unpack_bf16", "quantize", "dequantize", "requantize"],
+    ap.add_argument("--profile-kernel", default=None, choices=["bare_streams", "gemm", "i8gemm", "pack", "unpack", "pack_direct", "unpack_direct", "pack_bf16", "unpack_bf16", "quantize", "dequantize", "requantize"],
                     help="run only this secondary kernel a few times and exit (small, self-ending case for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -476,6 +485,24 @@ def main():
         except Exception as exc:
             extras["bfp8b_gemm_8192x4096x16384"] = {"error": str(exc)}
 
+    # ------------------------------------------------------------------ what the memory system gives a bare stream
+    # Kernels with the conversion kernels' access shape and no arithmetic (buda_stream_probe), on this GPU, now: the
+    # measured copy peak is a 1:1 stream, a pack reads 4 bytes per byte written and an unpack the reverse.
+    bare_pack_mix = None
+    if not args.no_extras:
+        try:
+            n_el = 1 << 28
+            sched = (("one_block_per_band", 0), ("resident_fixed_stride", 1), ("resident_device_counter", 2))
+            bare = {"elements": n_el, "unit": "GB/s",
+                    "pack_mix_4_read_1_written": {k: round(cuda_ops.stream_probe(0, v, n_el), 1) for k, v in sched},
+                    "unpack_mix_1_read_4_written": {k: round(cuda_ops.stream_probe(1, v, n_el), 1) for k, v in sched},
+                    "read_only": round(cuda_ops.stream_probe(2, 0, n_el), 1),
+                    "write_only": round(cuda_ops.stream_probe(3, 0, n_el), 1)}
+            bare_pack_mix = max(bare["pack_mix_4_read_1_written"].values())
+            extras["bare_streams"] = bare
+        except Exception as exc:
+            extras["bare_streams"] = {"error": str(exc)}
+
     # ------------------------------------------------------------------ BERT-large weight set, layers dealt to the ranks
     if not args.no_extras:
         try:
@@ -634,9 +661,10 @@ def main():
                          # dram read+write per launch: ncu on an 8-tensor launch measured 82.57 MB per tensor
                          # (profiles/pack_staged_kernel_bfp8b_cfg2.md); traffic grows with the tensor count
                          "traffic": NT * 82.6e6, "traffic_unit": "bytes per launch, scaled from an 8-tensor ncu capture", "peak_kind": peak_kind, "kernel": "pack_staged_kernel<7,4>",
-                         # the peak is a 1:1 copy; this stream is 4/5 reads, for which a bare kernel (4 bytes in, 1 byte
-                         # out per element, same access shape) measured 7190 GB/s on this pool, read-only 7430
-                         "bare_kernel_same_mix_gbs": 7190.0,
+                         # the peak is a 1:1 copy; this stream is 4/5 reads: a bare kernel with the same mix and access
+                         # shape, timed in this run (7190 GB/s in an earlier run on this pool if the extras are skipped)
+                         "bare_kernel_same_mix_gbs": bare_pack_mix if bare_pack_mix else 7190.0,
+                         "frac_of_bare_kernel": achieved / (bare_pack_mix if bare_pack_mix else 7190.0),
                          "kernel_ms": kernel_ms},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks.summary(),
             "other_kernels": extras,

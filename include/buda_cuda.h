@@ -310,6 +310,17 @@ int buda_device_status(int *status_out);
  * buda_device_status() afterwards returns BUDA_TIMEOUT_ERROR with that code, once. */
 int buda_selftest_bounded_wait(uint32_t limit_ms, void *stream);
 
+/* Measurement aid: times a bare streaming kernel that has the access shape of the conversion kernels and none of their
+ * arithmetic, to show what the memory system gives for a read : write mix (the roofline the real kernels are judged
+ * against; replaces nothing in the reference).  mix: 0 = 4 bytes read per byte written (tilize + pack, quantise),
+ * 1 = 1 byte read per 4 written (unpack + untilize, dequantise), 2 = reads only, 3 = writes only; the 4-byte side is
+ * touched in bands of 32 rows x 1 KiB inside rows of 16 KiB.  schedule: 0 = one short-lived block per band,
+ * 1 = resident blocks on a fixed stride, 2 = resident blocks that take bands in address order from a device counter.
+ * elements: a multiple of 131072, at most 2^30; the call allocates 5 bytes per element on the device and frees them.
+ * Runs 2 untimed and `reps` (1..1000) timed launches on `stream`, synchronises, and stores the mean milliseconds per
+ * launch in *ms_out. */
+int buda_stream_probe(int mix, int schedule, uint64_t elements, int reps, float *ms_out, void *stream);
+
 enum {
     BUDA_DEVSTAT_OK = 0,
     BUDA_DEVSTAT_PACK_FULL_WAIT = 1,   /* pack: consumer waited too long for a staged band     */

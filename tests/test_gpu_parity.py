@@ -598,3 +598,17 @@ def test_work_counters_survive_reuse_and_concurrent_streams(ops, oracle):
     for o, w in zip(outs, want):
         assert torch.equal(o, w)
     assert ops._cabi.device_status() == (0, 0)
+
+
+def test_stream_probe_runs_and_rejects_bad_arguments(ops):
+    """The bare streaming kernels behind the roofline figures: every mix and schedule runs on a small case and gives
+    a positive rate; sizes that are not whole row bands are refused with a status code."""
+    for mix in range(4):
+        for schedule in range(3):
+            assert ops.stream_probe(mix, schedule, elements=131072 * 64, reps=2) > 0.0
+    ms = ctypes.c_float(0.0)
+    lib = ops._cabi.lib
+    assert lib.buda_stream_probe(0, 0, 1000, 1, ctypes.byref(ms), None) == 1
+    assert lib.buda_stream_probe(5, 0, 131072, 1, ctypes.byref(ms), None) == 1
+    assert lib.buda_stream_probe(0, 0, 131072, 0, ctypes.byref(ms), None) == 1
+    assert ops._cabi.device_status() == (0, 0)

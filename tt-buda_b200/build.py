@@ -19,7 +19,7 @@ OBJ_DIR = os.path.join(CSRC, "build")
 CUDA_LIB = os.path.join(LIB_DIR, "libbuda_cuda.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
-CU_SOURCES = ["capi.cu", "tilize_pack.cu", "unpack_untilize.cu", "quant.cu", "bfp8_gemm.cu", "gemm_pair.cu", "prestride.cu"]
+CU_SOURCES = ["capi.cu", "tilize_pack.cu", "unpack_untilize.cu", "quant.cu", "bfp8_gemm.cu", "gemm_pair.cu", "prestride.cu", "stream_probe.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I", INCLUDE]
 

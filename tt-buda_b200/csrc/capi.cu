@@ -26,6 +26,7 @@ cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, 
                               size_t err_len);
 
 int gemm_kernel_choice(int which);
+cudaError_t run_stream_probe(int mix, int schedule, uint64_t elements, int reps, int sm_count, cudaStream_t stream, float *ms_out);
 cudaError_t launch_prestride(const void *src, int elem_bytes, const uint32_t shape[4], const uint64_t strides[4], int stride,
                              const int *xy_offsets, int n_offsets, void *dst, uint32_t dst_rows, uint32_t dst_cols, int sm_count,
                              cudaStream_t stream);
@@ -986,6 +987,21 @@ int buda_selftest_bounded_wait(uint32_t limit_ms, void *stream)
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "self-test launch failed");
     g_launches.fetch_add(1, std::memory_order_relaxed);
+    return BUDA_SUCCESS;
+}
+
+int buda_stream_probe(int mix, int schedule, uint64_t elements, int reps, float *ms_out, void *stream)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    if (!ms_out) return fail(BUDA_RUNTIME_ERROR, "null result pointer");
+    if (mix < 0 || mix > 3 || schedule < 0 || schedule > 2) return fail(BUDA_RUNTIME_ERROR, "mix %d / schedule %d out of range", mix, schedule);
+    if (reps < 1 || reps > 1000) return fail(BUDA_RUNTIME_ERROR, "%d repetitions is outside 1..1000", reps);
+    if (elements == 0 || elements % 131072u || elements > (1ull << 30))
+        return fail(BUDA_RUNTIME_ERROR, "element count %llu is not a multiple of 131072 up to 2^30", (unsigned long long)elements);
+    cudaError_t e = run_stream_probe(mix, schedule, elements, reps, ctx->sm_count, (cudaStream_t)stream, ms_out);
+    if (e != cudaSuccess) return cuda_fail(e, "stream probe failed");
+    g_launches.fetch_add((uint64_t)reps + 2, std::memory_order_relaxed);
     return BUDA_SUCCESS;
 }
 

@@ -83,6 +83,7 @@ _SIGS = {
     "buda_i8_gemm": (_i, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _f, _i, _vp, _i64, _vp]),
     "buda_gemm_select_kernel": (_i, [_i]),
     "buda_selftest_bounded_wait": (_i, [_u32, _vp]),
+    "buda_stream_probe": (_i, [_i, _i, _u64, _i, ctypes.POINTER(ctypes.c_float), _vp]),
     "buda_ipc_export": (_i, [_vp, ctypes.c_char_p]),
     "buda_ipc_open": (_i, [ctypes.c_char_p, _vpp]),
     "buda_ipc_close": (_i, [_vp]),

@@ -301,3 +301,12 @@ class SharedDeviceMatrix:
                 _cabi.lib.buda_free(self.ptr)
                 self.ptr = None
 
+
+def stream_probe(mix, schedule, elements=1 << 29, reps=10):
+    """GB/s of a bare streaming kernel with the conversion kernels' access shape (see buda_stream_probe):
+    mix 0 = 4 bytes read per byte written, 1 = the reverse, 2 = reads only, 3 = writes only;
+    schedule 0 = one block per band, 1 = resident blocks on a fixed stride, 2 = resident blocks on a device counter."""
+    ms = ctypes.c_float(0.0)
+    _cabi.check(_cabi.lib.buda_stream_probe(int(mix), int(schedule), int(elements), int(reps), ctypes.byref(ms), _stream()))
+    nbytes = elements * (5.0 if mix in (0, 1) else 4.0)
+    return nbytes / (ms.value * 1e-3) / 1e9
