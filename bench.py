@@ -134,6 +134,47 @@ class ClockSampler:
                 "samples": len(s), "source": "nvml" if self._nvml is not None else "nvidia-smi"}
 
 
+_PROBE = None
+
+
+def stream_probe(torch, mix, schedule, elements=1 << 29, reps=10):
+    """GB/s of a bare streaming kernel with the conversion kernels' access shape and none of their arithmetic
+    (tt-buda_b200/csrc/bench/stream_probe.cu, built into libbuda_probe.so, which only this benchmark loads).
+    mix 0 = 4 bytes read per byte written, 1 = the reverse, 2 = reads only, 3 = writes only; schedule 0 = one block
+    per band, 1 = resident blocks on a fixed stride, 2 = resident blocks on a device counter."""
+    global _PROBE
+    if _PROBE is None:
+        _PROBE = ctypes.CDLL(os.path.join(ROOT, "tt-buda_b200", "lib", "libbuda_probe.so"))
+        _PROBE.buda_probe_stream.restype = ctypes.c_int
+        _PROBE.buda_probe_stream.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_uint64, ctypes.c_int,
+                                             ctypes.POINTER(ctypes.c_float), ctypes.c_void_p]
+    ms = ctypes.c_float(0.0)
+    rc = _PROBE.buda_probe_stream(int(mix), int(schedule), int(elements), int(reps), ctypes.byref(ms),
+                                  ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    if rc != 0:
+        raise RuntimeError("stream probe failed")
+    nbytes = elements * (5.0 if mix in (0, 1) else 4.0)
+    return nbytes / (ms.value * 1e-3) / 1e9
+
+
+def host_cores():
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def gpu_numa_node(torch, index):
+    """NUMA node the GPU's PCIe slot hangs off (sysfs; None when it cannot be read)."""
+    try:
+        p = torch.cuda.get_device_properties(index)
+        bdf = "%04x:%02x:%02x.0" % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            return int(f.read().strip())
+    except Exception:
+        return None
+
+
 def make_batch(torch, device, seed0, n):
     """Synthetic batch with the value distribution of the config (generated on the device)."""
     xs = []
@@ -175,7 +216,7 @@ def profile_one(torch, cuda_ops, dev, name, reps=20, nt=8):
         n_el = 1 << 29
         out = {"elements": n_el, "unit": "GB/s"}
         for mix, mname in ((0, "4_read_1_written"), (1, "1_read_4_written"), (2, "read_only"), (3, "write_only")):
-            out[mname] = {sname: round(cuda_ops.stream_probe(mix, sv, n_el), 1)
+            out[mname] = {sname: round(stream_probe(torch, mix, sv, n_el), 1)
                           for sname, sv in (("one_block_per_band", 0), ("resident_fixed_stride", 1), ("resident_device_counter", 2))}
         emit(json.dumps({"kernel": name, **out}))
         return
@@ -243,6 +284,8 @@ def run_reference(args, rank, world):
     from oracle import budaref as R
 
     R.build()
+    # torchrun exports OMP_NUM_THREADS=1 to its workers: give the CPU arm the host's cores back
+    R.set_threads(host_cores())
     n_sample = 4  # tensors per step: a bounded sample of the 64-tensor batch
     rng = np.random.default_rng(1000)
     xs = []
@@ -360,6 +403,44 @@ def main():
     value = world * args.steps * algo_bytes_step / (total_ms * 1e-3) / 1e9
     achieved = algo_bytes_step / (kernel_ms * 1e-3) / 1e9
 
+    # ------------------------------------------------------------------ the bytes that were timed, against the oracle
+    parity_sample = None
+    if rank == 0 and not args.no_cpu:
+        try:
+            from oracle import budaref as R
+
+            R.build()
+            R.set_threads(host_cores())
+            parity_sample = bool((outs[0].cpu().numpy() == R.tilize_pack(xs[0].cpu().numpy(), R.Bfp8_b)).all())
+        except Exception as exc:
+            parity_sample = f"not checked: {exc}"
+
+    # ------------------------------------------------------------------ strong scaling: the config's 64 tensors dealt to the ranks
+    # tensor i -> GPU i mod g: a rank packs 64 / g tensors in one launch per step (8 at 8 GPUs, a ~95 us launch)
+    strong = None
+    try:
+        from pybuda.sharding import units_of_rank
+
+        mine = len(units_of_rank(N_TENSORS, rank, world)) if NT == N_TENSORS else max(1, NT // world)
+        sx, so = xs[:mine], outs[:mine]
+        for _ in range(args.warmup):
+            cuda_ops.tilize_pack_batch(sx, cuda_ops.DF.Bfp8_b, outs=so)
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(args.steps):
+            cuda_ops.tilize_pack_batch(sx, cuda_ops.DF.Bfp8_b, outs=so)
+        s1.record()
+        barrier()
+        s_ms = max_over_ranks(s0.elapsed_time(s1)) / args.steps
+        total_tensors = N_TENSORS if NT == N_TENSORS else mine * world
+        s_gbs = total_tensors * ELEMS * BYTES_PER_ELEM / (s_ms * 1e-3) / 1e9
+        strong = {"value": s_gbs, "unit": "GB/s", "tensors_total": total_tensors, "tensors_per_gpu": mine, "ms_per_step": s_ms,
+                  "launches_per_step_per_gpu": 1, "frac_hbm_per_gpu": s_gbs / world / hbm_peak,
+                  "note": "the batch of 64 shared out (tensor i -> GPU i mod g); time = slowest rank's launch"}
+    except Exception as exc:
+        strong = {"value": None, "error": str(exc)}
+
     # ------------------------------------------------------------------ e2e: host buffers in and out
     e2e = None
     try:
@@ -400,6 +481,11 @@ def main():
                "h2d_bytes_per_step": NT * ELEMS * 4, "d2h_bytes_per_step": NT * IMAGE_BYTES,
                "steps": args.e2e_steps, "api": "buda_tilize_pack_host_batch (pinned host tensors, one call per step)",
                "matches_device_path": same,
+               "h2d_gbs_per_gpu": NT * ELEMS * 4 * args.e2e_steps / e2e_s / 1e9,
+               "d2h_gbs_per_gpu": NT * IMAGE_BYTES * args.e2e_steps / e2e_s / 1e9,
+               "gpu_numa_node": gpu_numa_node(torch, local_rank), "host_cores": host_cores(),
+               "limiter": "host-to-device copy over PCIe (4 of every 5.06 bytes moved); with several GPUs behind one "
+                          "NUMA node the ranks also share that node's memory bandwidth",
                "one_call_per_tensor": {"value": world * algo_bytes_step / per_tensor_s / 1e9, "api": "buda_tilize_pack_host x 64"}}
         del hx, himg
     except Exception as exc:  # report, never hide
@@ -444,6 +530,16 @@ def main():
                 lambda: cuda_ops.unpack_untilize_batch(outs[:nu], cuda_ops.DF.Bfp8_b, SHAPE, outs=ys, path=1),
                 nu * ELEMS * BYTES_PER_ELEM)
             del ys
+            # plain relayout (tilize / untilize without a format change): 2 x element size per element
+            for tname, tdt, tdf, tes in (("fp32", torch.float32, cuda_ops.DF.Float32, 4), ("bf16", torch.bfloat16, cuda_ops.DF.Float16_b, 2),
+                                         ("int8", torch.int8, cuda_ops.DF.Int8, 1)):
+                xr = [(torch.randint(-128, 128, SHAPE, device=dev, dtype=torch.int8) if tdt == torch.int8 else x.to(tdt))
+                      for x in xs[:nu]]
+                ir = cuda_ops.tilize_pack_batch(xr, tdf)
+                extras[f"relayout_{tname}_tilize"] = timed(lambda: cuda_ops.tilize_pack_batch(xr, tdf, outs=ir), nu * ELEMS * 2 * tes)
+                extras[f"relayout_{tname}_untilize"] = timed(
+                    lambda: cuda_ops.unpack_untilize_batch(ir, tdf, SHAPE, outs=xr), nu * ELEMS * 2 * tes)
+                del xr, ir
             n3 = 32 * 1024 * 1024
             # config-3 tensors are about the size of L2: every call takes the next of four copies of its input, so no
             # call finds its input (or the previous call's output) still in the cache
@@ -494,10 +590,10 @@ def main():
             n_el = 1 << 28
             sched = (("one_block_per_band", 0), ("resident_fixed_stride", 1), ("resident_device_counter", 2))
             bare = {"elements": n_el, "unit": "GB/s",
-                    "pack_mix_4_read_1_written": {k: round(cuda_ops.stream_probe(0, v, n_el), 1) for k, v in sched},
-                    "unpack_mix_1_read_4_written": {k: round(cuda_ops.stream_probe(1, v, n_el), 1) for k, v in sched},
-                    "read_only": round(cuda_ops.stream_probe(2, 0, n_el), 1),
-                    "write_only": round(cuda_ops.stream_probe(3, 0, n_el), 1)}
+                    "pack_mix_4_read_1_written": {k: round(stream_probe(torch, 0, v, n_el), 1) for k, v in sched},
+                    "unpack_mix_1_read_4_written": {k: round(stream_probe(torch, 1, v, n_el), 1) for k, v in sched},
+                    "read_only": round(stream_probe(torch, 2, 0, n_el), 1),
+                    "write_only": round(stream_probe(torch, 3, 0, n_el), 1)}
             bare_pack_mix = max(bare["pack_mix_4_read_1_written"].values())
             extras["bare_streams"] = bare
         except Exception as exc:
@@ -509,19 +605,22 @@ def main():
             from pybuda.sharding import units_of_rank
 
             layers = units_of_rank(24, rank, world)        # layer l -> rank l % world (3 each at 8 GPUs)
-            groups = {}                                     # shape -> tensors: Q, K, V, O [1024,1024]; FFN [1024,4096], [4096,1024]
+            ws = []                                         # Q, K, V, O [1024,1024]; FFN [1024,4096], [4096,1024]
             for l in layers:
                 for j, shp in enumerate([(1024, 1024)] * 4 + [(1024, 4096), (4096, 1024)]):
                     g = torch.Generator(device=dev).manual_seed(2000 + 6 * l + j)
-                    groups.setdefault(shp, []).append(torch.randn((1, 1) + shp, generator=g, device=dev) * 0.02)
-            imgs = {shp: cuda_ops.tilize_pack_batch(ts, cuda_ops.DF.Bfp8_b) for shp, ts in groups.items()}
-            backs = {shp: [torch.empty_like(t) for t in ts] for shp, ts in groups.items()}
+                    ws.append(torch.randn((1, 1) + shp, generator=g, device=dev) * 0.02)
+            imgs = cuda_ops.tilize_pack_jobs(ws, cuda_ops.DF.Bfp8_b)
+            backs = [torch.empty_like(t) for t in ws]
+            lc0 = _cabi.launch_count()
 
             def round_trip():
-                for shp, ts in groups.items():
-                    cuda_ops.tilize_pack_batch(ts, cuda_ops.DF.Bfp8_b, outs=imgs[shp])
-                    cuda_ops.unpack_untilize_batch(imgs[shp], cuda_ops.DF.Bfp8_b, (1, 1) + shp, outs=backs[shp])
+                # the whole set, whatever its shapes: one pack launch and one unpack launch
+                cuda_ops.tilize_pack_jobs(ws, cuda_ops.DF.Bfp8_b, outs=imgs)
+                cuda_ops.unpack_untilize_jobs(imgs, cuda_ops.DF.Bfp8_b, backs)
 
+            round_trip()
+            launches_rt = _cabi.launch_count() - lc0
             for _ in range(3):
                 round_trip()
             barrier()
@@ -536,9 +635,10 @@ def main():
             extras["bert_large_weights_fp32_bfp8b_fp32"] = {
                 "GB/s": round(elems * 2 * BYTES_PER_ELEM / (ms * 1e-3) / 1e9, 1), "ms": round(ms, 4), "layers_per_rank": len(layers),
                 "frac_hbm_per_gpu": round(elems * 2 * BYTES_PER_ELEM / (ms * 1e-3) / 1e9 / world / hbm_peak, 3),
-                "note": "pack + unpack of this rank's layers, 6 launches per round trip; the set is 1.5 GB over all ranks, "
-                        "so at 8 GPUs a rank's share (191 MB) is near the size of L2"}
-            del groups, imgs, backs
+                "launches_per_round_trip": int(launches_rt),
+                "note": "pack + unpack of this rank's layers through the job-table entry points (all shapes in one launch "
+                        "each way); the set is 1.5 GB over all ranks, so at 8 GPUs a rank's share (191 MB) is near the size of L2"}
+            del ws, imgs, backs
         except Exception as exc:
             extras["bert_large_weights_fp32_bfp8b_fp32"] = {"error": str(exc)}
 
@@ -548,9 +648,11 @@ def main():
             from pybuda.parallel_matmul import ColumnParallelBfp8Matmul
 
             M, K, N = 8192, 4096, 16384
-            a = torch.randn(M, K, device=dev).bfloat16()
+            gmm = torch.Generator(device=dev).manual_seed(6)       # the same activations and weight on every rank
+            a = torch.randn(M, K, device=dev, generator=gmm).bfloat16()
+            w_full = torch.randn(1, 1, K, N, device=dev, generator=gmm) * 0.02
             op = ColumnParallelBfp8Matmul(K, N, bands=8)
-            op.load_weight_shard(torch.randn(1, 1, K, op.n_local, device=dev) * 0.02, already_sharded=True)
+            op.load_weight_shard(w_full)
             cfull = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
 
             def run(gather):
@@ -568,8 +670,10 @@ def main():
             ms_local, ms_gather = run(False), run(True)
 
             # the exchange fused into the kernel: the epilogue stores each tile into every rank's output
-            # through peer-mapped memory (timed with the closing barrier that makes the result readable)
-            op.enable_fused_scatter(M)
+            # through peer-mapped memory.  Five launches, then a stream-ordered all-reduce: the closing event is
+            # recorded when every rank's kernels (and with them their stores into this rank's matrix) are done.
+            fused_out = op.enable_fused_scatter(M)
+            flag = torch.zeros(1, device=dev)
             for _ in range(2):
                 op.fused(a)
             barrier()
@@ -577,9 +681,20 @@ def main():
             e0.record()
             for _ in range(5):
                 op.fused(a, sync=False)
+            dist.all_reduce(flag)
             e1.record()
             barrier()
             ms_fused = max_over_ranks(e0.elapsed_time(e1) / 5)
+            # correctness on every rank, outside the timed loops: fused == all-gather variant == one-GPU product
+            op(a, out=cfull, gather=True)
+            w_img_full = cuda_ops.tilize_pack(w_full, cuda_ops.DF.Bfp8_b)
+            c_single = cuda_ops.bfp8b_matmul(a, w_img_full, N)
+            torch.cuda.synchronize()
+            ok_local = float(torch.equal(fused_out, c_single) and torch.equal(cfull, c_single))
+            ok_t = torch.tensor([ok_local], device=dev)
+            dist.all_reduce(ok_t, op=dist.ReduceOp.MIN)
+            fused_matches = bool(ok_t.item() == 1.0)
+            del w_img_full, c_single, w_full
             op.disable_fused_scatter()
             # what bounds the fused kernel: the tensor cores, or this rank's stores leaving over NVLink
             flops_rank = 2.0 * M * (N / world) * K
@@ -589,6 +704,8 @@ def main():
                 "TFLOP/s_without_gather": round(2.0 * M * N * K / (ms_local * 1e-3) / 1e12, 1), "ms_without_gather": round(ms_local, 4),
                 "TFLOP/s_with_all_gather": round(2.0 * M * N * K / (ms_gather * 1e-3) / 1e12, 1), "ms_with_all_gather": round(ms_gather, 4),
                 "TFLOP/s_fused_scatter": round(2.0 * M * N * K / (ms_fused * 1e-3) / 1e12, 1), "ms_fused_scatter": round(ms_fused, 4),
+                "fused_matches": fused_matches,
+                "nvlink_store_gbs_per_gpu": round(link_bytes / (ms_fused * 1e-3) / 1e9, 1),
                 "fused_scatter_floor_ms": round(t_floor * 1e3, 4), "fused_scatter_frac_of_floor": round(t_floor * 1e3 / ms_fused, 3),
                 "floor": "max(flops / measured bf16 burst peak, bytes leaving this GPU / 770 GB/s measured peer copy)",
                 "bands": 8}
@@ -654,13 +771,19 @@ def main():
         line = {
             "metric": "bfp8b_tilize_pack_throughput", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "value_is": "weak scaling: every GPU packs its own batch of 64 tensors; the config's own 64 tensors shared out "
+                        "over the GPUs are in `strong`",
+            "strong": strong, "parity_sample": parity_sample,
             "vs_baseline": None, "dtype": "u8", "data": "synthetic",
             "config": {"workload": WORKLOAD if NT == N_TENSORS else WORKLOAD + f" (REDUCED to {NT} tensors)", "per_gpu_batch": NT, "l2": "inputs (4 GiB per step) larger than L2",
                        "launches_per_step": 1},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                         # dram read+write per launch: ncu on an 8-tensor launch measured 82.57 MB per tensor
-                         # (profiles/pack_staged_kernel_bfp8b_cfg2.md); traffic grows with the tensor count
-                         "traffic": NT * 82.6e6, "traffic_unit": "bytes per launch, scaled from an 8-tensor ncu capture", "peak_kind": peak_kind, "kernel": "pack_staged_kernel<7,4>",
+                         # dram read + write per launch: a constant, not read live -- an ncu capture of an 8-tensor
+                         # launch measured 82.57 MB per tensor, and traffic grows with the tensor count
+                         "traffic": NT * 82.6e6, "traffic_unit": "bytes per launch", "traffic_source": "constant: 82.57 MB per tensor "
+                         "from an ncu capture of an 8-tensor launch, scaled by the tensor count",
+                         "peak_kind": peak_kind, "peak_note": "the peak is a 1:1 copy; for a stream that is 4/5 reads the memory system "
+                         "gives more (bare_kernel_same_mix_gbs), so frac can exceed 1", "kernel": "pack_staged_kernel<7,4>",
                          # the peak is a 1:1 copy; this stream is 4/5 reads: a bare kernel with the same mix and access
                          # shape, timed in this run (7190 GB/s in an earlier run on this pool if the extras are skipped)
                          "bare_kernel_same_mix_gbs": bare_pack_mix if bare_pack_mix else 7190.0,

@@ -60,6 +60,50 @@ typedef struct buda_queue_geom {
                               (balancer_utils.hpp:24-51 has no tile-dimension term) with rows >= tile_height zero. */
 } buda_queue_geom;
 
+/* One tensor of a call that converts many tensors of different shapes (buda_*_jobs below).  `tensor` is the
+ * row-major side, `image` the queue image; which one is read depends on the direction of the call.
+ * band_count > 0 converts only the tile rows band_first + k * band_step, k < band_count (a tile row = 32 tensor rows
+ * across the whole width): every record still lands where the full tensor's image has it, so the GPUs of a box can
+ * each convert their share of one tensor's tile rows (band b -> GPU b mod g) into one image.  When the queue grid is
+ * 1x1 a tile row's records are one contiguous slice of the image (TileLayout::map,
+ * pybuda/csrc/balancer/types.cpp:629-648).  band_count == 0: the whole tensor. */
+typedef struct buda_tensor_job {
+    const void *tensor;
+    void *image;
+    uint64_t image_bytes;          /* capacity of the image buffer (all grid buffers) */
+    uint32_t shape[4];
+    uint64_t strides_bytes[4];
+    buda_queue_geom geom;
+    uint32_t band_first, band_step, band_count;
+    uint32_t slots, first_slot;    /* image is a ring of `slots` entries per grid core (0: dense image), see the queue section */
+} buda_tensor_job;
+
+/* The choices of the block-float byte layout that the reference's published description leaves open
+ * (docs/public/dataformats.rst:74-83: "Truncate bits to fit in the BFP format mantissa size, optionally round before
+ * truncation"; the drawings docs/public/images/bfp{8,4,2}_blocks.png show 32-bit rows without saying which end holds
+ * exponent 0 / datum 0).  The converter that fixes them is not part of the reference checkout, so each is a switch:
+ * when real tile bytes of that converter become available, set the combination that reproduces them.  All zero
+ * (face_order {0,1,2,3}) is this library's default and the only layout the matmul kernels read. */
+enum { BUDA_BFP_ROUND_NEAREST_EVEN = 0, BUDA_BFP_ROUND_TRUNCATE = 1 };
+enum { BUDA_BFP_OVERFLOW_SATURATE = 0, BUDA_BFP_OVERFLOW_BUMP_EXPONENT = 1 };
+enum { BUDA_BFP_ORDER_LITTLE = 0, BUDA_BFP_ORDER_BIG = 1 };
+typedef struct buda_bfp_policy {
+    uint32_t rounding;        /* of the dropped mantissa bits */
+    uint32_t overflow;        /* a magnitude that rounds up past 2^m - 1: saturate, or raise the block's shared exponent by
+                                 one and encode the whole block against it */
+    uint8_t face_order[4];    /* which 16x16 face is stored first, second, ... (0 = rows 0-15 x cols 0-15, 1 = rows 0-15 x
+                                 cols 16-31, 2 = rows 16-31 x cols 0-15, 3 = rows 16-31 x cols 16-31); applies to every format */
+    uint32_t exponent_order;  /* LITTLE: exponent of block k in byte k of the exponent section; BIG: in byte k ^ 3
+                                 (first exponent in the top byte of each 32-bit word) */
+    uint32_t datum_order;     /* LITTLE: datum i of a block in bits [i(m+1), (i+1)(m+1)) of the block's bytes read as
+                                 little-endian words; BIG: the datum fields of each 32-bit word in reverse order */
+} buda_bfp_policy;
+
+/* Process-wide; takes effect for calls that start afterwards.  NULL restores the default.  Replaces nothing in the
+ * reference (there the behaviour is fixed inside the absent converter). */
+int buda_set_bfp_policy(const buda_bfp_policy *policy);
+int buda_get_bfp_policy(buda_bfp_policy *policy_out);
+
 /* ------------------------------------------------------------------ sizes (host only, no GPU) */
 
 /* Bytes of one 32x32 tile record; with_header adds the 32-byte header/pad.
@@ -103,14 +147,12 @@ int buda_tilize_pack_batch(int n, const void *const *srcs_host, int src_df, cons
                            const uint64_t strides_bytes[4], const buda_queue_geom *geom, int dst_df,
                            int with_header, void *const *dsts_host, uint64_t dst_bytes_each, void *stream);
 
-/* buda_tilize_pack_batch with the kernel chosen by the caller: path 0 = staged (shared-memory
- * staging by bulk async copies; needs 16-byte aligned rows), 1 = direct (4 lanes per block, warp
- * shuffle exponent reduction; any alignment).  For tests and for measuring one kernel against the
- * other; no counterpart in the reference. */
-int buda_tilize_pack_batch_path(int n, const void *const *srcs_host, int src_df, const uint32_t shape[4],
-                                const uint64_t strides_bytes[4], const buda_queue_geom *geom, int dst_df,
-                                int with_header, void *const *dsts_host, uint64_t dst_bytes_each, void *stream,
-                                int path);
+/* Tensors of DIFFERENT shapes, strides and queue geometries (one src_df -> dst_df conversion) in as few launches as
+ * possible: the caller loop of push_constants_and_parameters / update_device_paramaters
+ * (pybuda/pybuda/backend.py:458-517), which walks every constant and parameter of a graph, hoisted into the kernel.
+ * Up to 192 tensors share one launch; work is still handed out in address order across them.  jobs_host is a HOST
+ * array; tensor and image are device pointers. */
+int buda_tilize_pack_jobs(int n, const buda_tensor_job *jobs_host, int src_df, int dst_df, int with_header, void *stream);
 
 /* Host-buffer form: copies the tensor to the device, converts, and copies the image back to
  * dst_host (what tt::backend::tilize_tensor returns to tti/archive.py:133).  Chunked so the two
@@ -127,6 +169,12 @@ int buda_tilize_pack_host_batch(int n, const void *const *srcs_host, int src_df,
                                 const uint64_t strides_bytes[4], const buda_queue_geom *geom, int dst_df, int with_header,
                                 void *const *dsts_host, uint64_t dst_bytes_each, void *stream);
 
+/* The same for tensors of different shapes: job.tensor is a HOST pointer; job.image is a host pointer
+ * (image_on_device == 0) or a device pointer, e.g. the queues the parameters live in (image_on_device != 0; slots /
+ * first_slot then apply).  One pipeline over all tensors, drained once. */
+int buda_tilize_pack_host_jobs(int n, const buda_tensor_job *jobs_host, int src_df, int dst_df, int with_header,
+                               int image_on_device, void *stream);
+
 /* buda_tilize_pack_host for callers that must not allocate.  It has no counterpart in the reference.
  * Same arguments and result, but the device staging for the tensor and its image is a fixed 8 MiB
  * array inside the library (held by every GPU that loads the library until the process exits)
@@ -138,6 +186,7 @@ int buda_tilize_pack_host_batch(int n, const void *const *srcs_host, int src_df,
  * anything larger is refused with BUDA_RUNTIME_ERROR and a message naming the limit.
  * The first call on a device also looks up the array's device address (cudaGetSymbolAddress) and
  * sets kernel attributes; make that first call before any stream capture begins.
+ * `stream` must belong to the device that is current when the call is made: the array address used is that device's.
  * All calls on a device share the one array, which keeps the previous call's bytes.  The library
  * lets one host thread at a time through per device; GPU work of two calls that still overlapped
  * (e.g. issued around that lock from forked copies of a context) would race on the array.
@@ -158,14 +207,15 @@ int buda_unpack_untilize_batch(int n, const void *const *srcs_host, int src_df, 
                                const buda_queue_geom *geom, void *const *dsts_host, int dst_df,
                                const uint32_t shape[4], const uint64_t strides_bytes[4], void *stream);
 
-int buda_unpack_untilize_batch_path(int n, const void *const *srcs_host, int src_df, int with_header,
-                                    const buda_queue_geom *geom, void *const *dsts_host, int dst_df,
-                                    const uint32_t shape[4], const uint64_t strides_bytes[4], void *stream,
-                                    int path);
+/* Inverse of buda_tilize_pack_jobs: job.image is read, job.tensor written. */
+int buda_unpack_untilize_jobs(int n, const buda_tensor_job *jobs_host, int src_df, int with_header, int dst_df, void *stream);
 
 int buda_unpack_untilize_host(const void *src_host, int src_df, int with_header, const buda_queue_geom *geom,
                               void *dst_host, int dst_df, const uint32_t shape[4],
                               const uint64_t strides_bytes[4], void *stream);
+
+int buda_unpack_untilize_host_jobs(int n, const buda_tensor_job *jobs_host, int src_df, int with_header, int dst_df,
+                                   int image_on_device, void *stream);
 
 /* ------------------------------------------------------------------ device-resident queues
  * A queue is a ring of `slots` entries per grid core in device memory: core buffers of
@@ -281,11 +331,6 @@ int buda_prestride(const void *src, int elem_bytes, const uint32_t shape[4], con
 int buda_i8_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N, const float *scale,
                  int64_t scale_len, float zero_point, int out_mode, void *C, int64_t ldc, void *stream);
 
-/* Which tensor-core kernel buda_bfp8b_gemm* launches: 0 = automatic (CTA-pair kernel for M > 256, single-CTA
- * kernel otherwise), 1 = single-CTA, 2 = CTA pair.  Process-wide; a negative value only reads.  Returns the
- * previous setting.  Results are identical bit for bit; the knob exists for measurement. */
-int buda_gemm_select_kernel(int which);
-
 /* Inter-process handles for device memory from buda_malloc, so that one process per GPU can hand its
  * output matrix to its peers.  export: 64-byte handle of an allocation's base pointer.  open: maps a
  * peer's allocation into this process (peer access is enabled on demand).  close: unmaps it. */
@@ -303,24 +348,6 @@ size_t buda_last_error(char *buf, size_t buf_len);
  * gave up (see BUDA_DEVSTAT_*); the function then returns BUDA_TIMEOUT_ERROR. */
 int buda_device_status(int *status_out);
 
-/* Self-test of the failure path every kernel of the library shares: launches one CTA that waits, with the
- * library's bounded mbarrier wait, for a barrier phase that nothing completes, for at most limit_ms
- * (1..1000) milliseconds; the wait then gives up, records BUDA_DEVSTAT_SELFTEST_WAIT in the device status word
- * and the kernel returns normally.  Nothing faults, traps or spins without a limit; the context stays usable.
- * buda_device_status() afterwards returns BUDA_TIMEOUT_ERROR with that code, once. */
-int buda_selftest_bounded_wait(uint32_t limit_ms, void *stream);
-
-/* Measurement aid: times a bare streaming kernel that has the access shape of the conversion kernels and none of their
- * arithmetic, to show what the memory system gives for a read : write mix (the roofline the real kernels are judged
- * against; replaces nothing in the reference).  mix: 0 = 4 bytes read per byte written (tilize + pack, quantise),
- * 1 = 1 byte read per 4 written (unpack + untilize, dequantise), 2 = reads only, 3 = writes only; the 4-byte side is
- * touched in bands of 32 rows x 1 KiB inside rows of 16 KiB.  schedule: 0 = one short-lived block per band,
- * 1 = resident blocks on a fixed stride, 2 = resident blocks that take bands in address order from a device counter.
- * elements: a multiple of 131072, at most 2^30; the call allocates 5 bytes per element on the device and frees them.
- * Runs 2 untimed and `reps` (1..1000) timed launches on `stream`, synchronises, and stores the mean milliseconds per
- * launch in *ms_out. */
-int buda_stream_probe(int mix, int schedule, uint64_t elements, int reps, float *ms_out, void *stream);
-
 enum {
     BUDA_DEVSTAT_OK = 0,
     BUDA_DEVSTAT_PACK_FULL_WAIT = 1,   /* pack: consumer waited too long for a staged band     */
@@ -328,7 +355,7 @@ enum {
     BUDA_DEVSTAT_UNPACK_FULL_WAIT = 3,
     BUDA_DEVSTAT_UNPACK_EMPTY_WAIT = 4,
     BUDA_DEVSTAT_GEMM_WAIT = 5,
-    BUDA_DEVSTAT_SELFTEST_WAIT = 6     /* buda_selftest_bounded_wait: the wait that nothing completes ran out */
+    BUDA_DEVSTAT_SELFTEST_WAIT = 6     /* buda_selftest_bounded_wait (buda_cuda_testing.h): the wait that nothing completes ran out */
 };
 
 /* Number of kernels this library has launched in this process (for launch accounting). */

@@ -21,7 +21,9 @@
  *     third_party/budabackend, branch main, no pinned commit, directory empty in the reference
  *     checkout).  The restatement follows the published description
  *     (docs/public/dataformats.rst:59-89 and docs/public/images/bfp{8,4,2}_blocks.png) and freezes
- *     every choice the description leaves open; each such choice is marked "POLICY" below.
+ *     every choice the description leaves open; each such choice is marked "POLICY" below, and the ones that
+ *     change bytes (rounding, overflow, face / exponent / datum order) are switches (ref_set_bfp_policy) so that a
+ *     real converter's bytes can be adopted by setting them.
  *
  * The Bfp encoder here works in integers (shift / mask / explicit round-to-nearest-even) on
  * purpose: the CUDA kernels use a floating-point formulation of the same arithmetic, so agreement
@@ -81,6 +83,60 @@ int ref_set_threads(int n)
     return 1;
 #endif
 }
+
+/* ---------------------------------------------------------------------------------------------
+ * POLICY switches: every choice the published description leaves open for the block-float bytes, as one
+ * process-wide record (default: all zero, faces in order 0 1 2 3).  "Truncate bits to fit in the BFP format mantissa
+ * size, optionally round before truncation" (docs/public/dataformats.rst:80-81) names both roundings; the drawings
+ * docs/public/images/bfp{8,4,2}_blocks.png show 32-bit rows without saying which end holds the first exponent /
+ * datum.  When real tile bytes of the reference's converter are available, the combination that reproduces them
+ * is set here and, identically, in the CUDA library.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+    uint32_t rounding;       /* 0 nearest even, 1 truncate */
+    uint32_t overflow;       /* 0 saturate, 1 raise the block exponent by one and re-encode the block */
+    uint8_t face_order[4];   /* face stored at position p of the record */
+    uint32_t exponent_order; /* 0: exponent of block k in byte k; 1: in byte k ^ 3 (big-endian 32-bit words) */
+    uint32_t datum_order;    /* 0: datum i in bits [i w, (i+1) w) of the block; 1: fields of each 32-bit word reversed */
+} ref_bfp_policy;
+
+static ref_bfp_policy g_pol = {0, 0, {0, 1, 2, 3}, 0, 0};
+
+int ref_set_bfp_policy(const ref_bfp_policy *p)
+{
+    static const ref_bfp_policy def = {0, 0, {0, 1, 2, 3}, 0, 0};
+    if (!p) { g_pol = def; return 0; }
+    int seen = 0;
+    for (int i = 0; i < 4; i++) {
+        if (p->face_order[i] > 3) return 1;
+        seen |= 1 << p->face_order[i];
+    }
+    if (seen != 15 || p->rounding > 1 || p->overflow > 1 || p->exponent_order > 1 || p->datum_order > 1) return 1;
+    g_pol = *p;
+    return 0;
+}
+
+/* bit offset of datum i (w bits wide) inside its block's bytes, read as little-endian 32-bit words */
+static inline int datum_bit_offset(int i, int w)
+{
+    int per_word = 32 / w, word = i / per_word, field = i % per_word;
+    if (g_pol.datum_order) field = per_word - 1 - field;
+    return word * 32 + field * w;
+}
+
+static inline void put_datum(uint8_t *out, int i, int w, uint32_t d)
+{
+    int bit = datum_bit_offset(i, w);
+    out[bit >> 3] |= (uint8_t)(d << (bit & 7));
+}
+
+static inline uint32_t get_datum(const uint8_t *in, int i, int w)
+{
+    int bit = datum_bit_offset(i, w);
+    return ((uint32_t)in[bit >> 3] >> (bit & 7)) & ((1u << w) - 1u);
+}
+
+static inline int exponent_byte_index(int blk) { return g_pol.exponent_order ? (blk ^ 3) : blk; }
 
 /* ---------------------------------------------------------------------------------------------
  * Sizes
@@ -182,8 +238,9 @@ void ref_tile_unmap(const ref_geom *g, uint32_t core_r, uint32_t core_c, uint64_
  * itself).  Each datum is sign + m magnitude bits, m = 7 / 3 / 1, with NO implied one.
  * ------------------------------------------------------------------------------------------- */
 
-/* Encode one value against the block exponent.  bits: IEEE-754 binary32 pattern. */
-static inline uint32_t bfp_encode_datum(uint32_t bits, uint32_t block_exp, int m)
+/* Encode one value against the block exponent.  bits: IEEE-754 binary32 pattern.  *over is set when a finite value's
+ * magnitude comes out above the largest one. */
+static inline uint32_t bfp_encode_datum(uint32_t bits, uint32_t block_exp, int m, int *over)
 {
     uint32_t sign = bits >> 31;
     uint32_t e = (bits >> 23) & 0xffu;
@@ -201,13 +258,15 @@ static inline uint32_t bfp_encode_datum(uint32_t bits, uint32_t block_exp, int m
         if (shift > 25) {
             q = 0; /* less than half of the last kept bit: rounds to zero */
         } else {
-            /* POLICY: round to nearest, ties to even, on the dropped bits ("optionally round") */
+            /* POLICY (rounding): to nearest, ties to even, on the dropped bits ("optionally round"), or plain
+             * truncation */
             uint32_t kept = sig >> shift;
             uint32_t rem = sig & ((1u << shift) - 1u);
             uint32_t half = 1u << (shift - 1);
-            if (rem > half || (rem == half && (kept & 1u))) kept++;
-            /* POLICY: a round-up past the largest magnitude saturates; the block exponent is
-             * not bumped */
+            if (!g_pol.rounding && (rem > half || (rem == half && (kept & 1u)))) kept++;
+            /* POLICY (overflow): a round-up past the largest magnitude saturates here; under the other policy the
+             * caller raises the block exponent and encodes the block again */
+            if (kept > qmax) *over = 1;
             q = kept > qmax ? qmax : kept;
         }
     }
@@ -216,7 +275,7 @@ static inline uint32_t bfp_encode_datum(uint32_t bits, uint32_t block_exp, int m
 }
 
 /* Encode one 16-value block.  out receives 16/8/4 bytes for m = 7/3/1.
- * POLICY (sub-byte order): datum i of the block occupies the lower-numbered bits first, i.e.
+ * POLICY (datum order, default): datum i of the block occupies the lower-numbered bits first, i.e.
  * Bfp4 datum i -> bits [4(i&1)+3 : 4(i&1)] of byte i/2, Bfp2 datum i -> bits [2(i&3)+1 : 2(i&3)]
  * of byte i/4 (little-endian inside the 32-bit rows drawn in bfp4_blocks.png / bfp2_blocks.png). */
 void ref_bfp_pack_block(const uint32_t bits[16], int m, uint8_t *exp_out, uint8_t *out)
@@ -226,14 +285,17 @@ void ref_bfp_pack_block(const uint32_t bits[16], int m, uint8_t *exp_out, uint8_
         uint32_t e = (bits[i] >> 23) & 0xffu; /* step 3: maximum exponent of the block */
         if (e > block_exp) block_exp = e;
     }
-    *exp_out = (uint8_t)block_exp;
     int w = m + 1;             /* datum width in bits: 8, 4, 2 */
-    int per_byte = 8 / w;      /* 1, 2, 4 */
-    memset(out, 0, 16 / per_byte);
-    for (int i = 0; i < 16; i++) {
-        uint32_t d = bfp_encode_datum(bits[i], block_exp, m);
-        out[i / per_byte] |= (uint8_t)(d << (w * (i % per_byte)));
+    uint32_t d[16];
+    int over = 0;
+    for (int i = 0; i < 16; i++) d[i] = bfp_encode_datum(bits[i], block_exp, m, &over);
+    if (g_pol.overflow && over && block_exp < 255) {
+        block_exp++;
+        for (int i = 0; i < 16; i++) d[i] = bfp_encode_datum(bits[i], block_exp, m, &over);
     }
+    *exp_out = (uint8_t)block_exp;
+    memset(out, 0, 16 * w / 8);
+    for (int i = 0; i < 16; i++) put_datum(out, i, w, d[i]);
 }
 
 /* Decode: value = (-1)^s * q * 2^(E - 127 - (m-1)), rounded to binary32 (exact unless it
@@ -250,11 +312,8 @@ static inline float bfp_decode_datum(uint32_t d, uint32_t block_exp, int m)
 
 void ref_bfp_unpack_block(uint8_t exp_in, const uint8_t *in, int m, float out[16])
 {
-    int w = m + 1, per_byte = 8 / w;
-    for (int i = 0; i < 16; i++) {
-        uint32_t d = (in[i / per_byte] >> (w * (i % per_byte))) & ((1u << w) - 1u);
-        out[i] = bfp_decode_datum(d, exp_in, m);
-    }
+    int w = m + 1;
+    for (int i = 0; i < 16; i++) out[i] = bfp_decode_datum(get_datum(in, i, w), exp_in, m);
 }
 
 /* ---------------------------------------------------------------------------------------------
@@ -264,7 +323,7 @@ void ref_bfp_unpack_block(uint8_t exp_in, const uint8_t *in, int m, float out[16
  * 11-bit significand, zero / denormal -> 0, Inf / NaN (e == 31) -> largest magnitude.
  * decode: (-1)^s * q * 2^(E - 15 - (m-1)).   PARITY UNPINNED like the "b" encoding.
  * ------------------------------------------------------------------------------------------- */
-static inline uint32_t bfp_a_encode_datum(uint16_t h, uint32_t block_exp, int m)
+static inline uint32_t bfp_a_encode_datum(uint16_t h, uint32_t block_exp, int m, int *over)
 {
     uint32_t sign = h >> 15, e = (h >> 10) & 31u, qmax = (1u << m) - 1u, q;
     if (e == 0) {
@@ -278,7 +337,8 @@ static inline uint32_t bfp_a_encode_datum(uint16_t h, uint32_t block_exp, int m)
             q = 0;
         } else {
             uint32_t kept = sig >> shift, rem = sig & ((1u << shift) - 1u), half = 1u << (shift - 1);
-            if (rem > half || (rem == half && (kept & 1u))) kept++;
+            if (!g_pol.rounding && (rem > half || (rem == half && (kept & 1u)))) kept++;
+            if (kept > qmax) *over = 1;
             q = kept > qmax ? qmax : kept;
         }
     }
@@ -293,17 +353,25 @@ void ref_bfp_a_pack_block(const uint16_t h[16], int m, uint8_t *exp_out, uint8_t
         uint32_t e = (h[i] >> 10) & 31u;
         if (e > block_exp) block_exp = e;
     }
+    int w = m + 1;
+    uint32_t d[16];
+    int over = 0;
+    for (int i = 0; i < 16; i++) d[i] = bfp_a_encode_datum(h[i], block_exp, m, &over);
+    /* an all-Inf/NaN-free block whose exponent is 30 may be raised to 31 */
+    if (g_pol.overflow && over && block_exp < 31) {
+        block_exp++;
+        for (int i = 0; i < 16; i++) d[i] = bfp_a_encode_datum(h[i], block_exp, m, &over);
+    }
     *exp_out = (uint8_t)block_exp;
-    int w = m + 1, per_byte = 8 / w;
-    memset(out, 0, 16 / per_byte);
-    for (int i = 0; i < 16; i++) out[i / per_byte] |= (uint8_t)(bfp_a_encode_datum(h[i], block_exp, m) << (w * (i % per_byte)));
+    memset(out, 0, 16 * w / 8);
+    for (int i = 0; i < 16; i++) put_datum(out, i, w, d[i]);
 }
 
 void ref_bfp_a_unpack_block(uint8_t exp_in, const uint8_t *in, int m, float out[16])
 {
-    int w = m + 1, per_byte = 8 / w;
+    int w = m + 1;
     for (int i = 0; i < 16; i++) {
-        uint32_t d = (in[i / per_byte] >> (w * (i % per_byte))) & ((1u << w) - 1u);
+        uint32_t d = get_datum(in, i, w);
         uint32_t q = d & ((1u << m) - 1u), sign = (d >> m) & 1u;
         float f = q ? (float)ldexp((double)q, (int)(exp_in & 31u) - 15 - (m - 1)) : 0.0f;
         out[i] = (sign && q) ? -f : f;
@@ -435,7 +503,8 @@ int ref_tilize_pack(const void *src_, int src_df, const uint32_t shape[4], const
         if (hdr) memset(rec, 0, 32);
         rec += hdr;
         const uint8_t *base = src + (uint64_t)w * strides[0] + (uint64_t)z * strides[1];
-        for (int face = 0; face < 4; face++) {
+        for (int pos = 0; pos < 4; pos++) {
+            int face = g_pol.face_order[pos];                      /* POLICY (face order): the face stored at this position */
             for (int fr = 0; fr < 16; fr++) {
                 uint32_t tr = (uint32_t)((face >> 1) * 16 + fr);   /* row inside the tile */
                 uint64_t r = (uint64_t)rt * c.th + tr;
@@ -443,17 +512,17 @@ int ref_tilize_pack(const void *src_, int src_df, const uint32_t shape[4], const
                 const uint8_t *p = base + r * strides[2] + col0 * strides[3];
                 uint32_t estride = strides[3];
                 if (tr >= c.th) { p = zeros; estride = (uint32_t)es; }   /* rows a tiny tile does not hold */
-                int blk = face * 16 + fr;
+                int blk = pos * 16 + fr;
                 if (m && is_bfp_a(dst_df)) {
                     uint16_t hv[16];
                     for (int i = 0; i < 16; i++) memcpy(&hv[i], p + (uint64_t)i * estride, 2);
                     int bpb = 16 * (m + 1) / 8;
-                    ref_bfp_a_pack_block(hv, m, rec + blk, rec + 64 + (long)blk * bpb);
+                    ref_bfp_a_pack_block(hv, m, rec + exponent_byte_index(blk), rec + 64 + (long)blk * bpb);
                 } else if (m) {
                     uint32_t bits[16];
                     for (int i = 0; i < 16; i++) bits[i] = load_as_f32_bits(p + (uint64_t)i * estride, src_df);
                     int bpb = 16 * (m + 1) / 8;
-                    ref_bfp_pack_block(bits, m, rec + blk, rec + 64 + (long)blk * bpb);
+                    ref_bfp_pack_block(bits, m, rec + exponent_byte_index(blk), rec + 64 + (long)blk * bpb);
                 } else {
                     for (int i = 0; i < 16; i++)
                         memcpy(rec + ((long)blk * 16 + i) * es, p + (uint64_t)i * estride, es);
@@ -494,18 +563,19 @@ int ref_unpack_untilize(const void *src_, int src_df, int with_header, const ref
         uint32_t w = (uint32_t)(ti / ((long long)Ct * Rt * c.Z));
         const uint8_t *rec = src + tile_offset(&c, w, z, rt, ct) + hdr;
         uint8_t *base = dst + (uint64_t)w * strides[0] + (uint64_t)z * strides[1];
-        for (int face = 0; face < 4; face++) {
+        for (int pos = 0; pos < 4; pos++) {
+            int face = g_pol.face_order[pos];
             for (int fr = 0; fr < 16; fr++) {
                 uint32_t tr = (uint32_t)((face >> 1) * 16 + fr);
                 if (tr >= c.th) continue;                      /* rows a tiny tile does not hold */
                 uint64_t r = (uint64_t)rt * c.th + tr;
                 uint64_t col0 = (uint64_t)ct * 32 + (face & 1) * 16;
                 uint8_t *p = base + r * strides[2] + col0 * strides[3];
-                int blk = face * 16 + fr;
+                int blk = pos * 16 + fr;
                 if (m && is_bfp_a(src_df)) {
                     float vals[16];
                     int bpb = 16 * (m + 1) / 8;
-                    ref_bfp_a_unpack_block(rec[blk], rec + 64 + (long)blk * bpb, m, vals);
+                    ref_bfp_a_unpack_block(rec[exponent_byte_index(blk)], rec + 64 + (long)blk * bpb, m, vals);
                     for (int i = 0; i < 16; i++) {
                         if (dst_df == DF_Float32) {
                             memcpy(p + (uint64_t)i * strides[3], &vals[i], 4);
@@ -517,7 +587,7 @@ int ref_unpack_untilize(const void *src_, int src_df, int with_header, const ref
                 } else if (m) {
                     float vals[16];
                     int bpb = 16 * (m + 1) / 8;
-                    ref_bfp_unpack_block(rec[blk], rec + 64 + (long)blk * bpb, m, vals);
+                    ref_bfp_unpack_block(rec[exponent_byte_index(blk)], rec + 64 + (long)blk * bpb, m, vals);
                     for (int i = 0; i < 16; i++) store_from_f32(p + (uint64_t)i * strides[3], dst_df, vals[i]);
                 } else {
                     for (int i = 0; i < 16; i++)

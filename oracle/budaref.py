@@ -43,6 +43,25 @@ class Geom(ctypes.Structure):
                    ublock[0], ublock[1], z, ublock_order, tile_height)
 
 
+class BfpPolicy(ctypes.Structure):
+    """ref_bfp_policy; the default constructor is the default layout."""
+
+    _fields_ = [
+        ("rounding", ctypes.c_uint32), ("overflow", ctypes.c_uint32), ("face_order", ctypes.c_uint8 * 4),
+        ("exponent_order", ctypes.c_uint32), ("datum_order", ctypes.c_uint32),
+    ]
+
+    def __init__(self, rounding=0, overflow=0, face_order=(0, 1, 2, 3), exponent_order=0, datum_order=0):
+        super().__init__(rounding, overflow, (ctypes.c_uint8 * 4)(*face_order), exponent_order, datum_order)
+
+
+def set_bfp_policy(policy=None):
+    """Process-wide layout policy of the oracle (None: the default)."""
+    rc = lib().ref_set_bfp_policy(ctypes.byref(policy) if policy is not None else None)
+    if rc:
+        raise ValueError("invalid block-float policy")
+
+
 def build(force=False):
     """Compile libbudaref.so with the committed Makefile (building the checker is not using it)."""
     if force or not os.path.exists(_LIB_PATH) or (
@@ -67,6 +86,8 @@ def lib():
         L.ref_threads.restype = i32
         L.ref_set_threads.restype = i32
         L.ref_set_threads.argtypes = [i32]
+        L.ref_set_bfp_policy.restype = i32
+        L.ref_set_bfp_policy.argtypes = [ctypes.POINTER(BfpPolicy)]
         L.ref_tile_bytes.restype = ctypes.c_long
         L.ref_tile_bytes.argtypes = [i32, i32]
         L.ref_data_format_byte_size.restype = ctypes.c_long

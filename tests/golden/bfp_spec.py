@@ -7,6 +7,10 @@ of the 16 values; sign + 7 / 3 / 1 magnitude bits without an implied one).  Froz
 ties to even; a round-up past the largest magnitude saturates; zero / denormal inputs encode as 0; Inf / NaN
 encode the largest magnitude; a zero magnitude is stored with sign 0; datum i occupies bits [i*(m+1), (i+1)*(m+1))
 of the block's little-endian bit string; decode (-1)^s * q * 2^(E-127-(m-1)), q = 0 -> +0.0.
+
+The choices that change bytes are also available the other way round (Policy): truncation instead of rounding, a
+shared exponent raised by one instead of saturation, another face order, and exponents / datums counted from the top
+end of each 32-bit word.  The default Policy() is the frozen spec above.
 """
 import math
 import struct
@@ -15,45 +19,96 @@ from fractions import Fraction
 SPEC_VERSION = 1
 
 
+class Policy:
+    def __init__(self, rounding=0, overflow=0, face_order=(0, 1, 2, 3), exponent_order=0, datum_order=0):
+        self.rounding = rounding              # 0 nearest even, 1 truncate
+        self.overflow = overflow              # 0 saturate, 1 raise the shared exponent by one
+        self.face_order = tuple(face_order)   # face stored first, second, third, fourth
+        self.exponent_order = exponent_order  # 0: exponent of block k in byte k, 1: in byte k ^ 3
+        self.datum_order = datum_order        # 0: datum i in the i-th field from the bottom, 1: fields of each 32-bit word from the top
+
+    def as_tuple(self):
+        return (self.rounding, self.overflow) + self.face_order + (self.exponent_order, self.datum_order)
+
+
+DEFAULT = Policy()
+
+
 def f2b(x: float) -> int:
     return struct.unpack("<I", struct.pack("<f", x))[0]
 
 
-def encode_block(bits16, m):
-    """16 binary32 bit patterns -> (shared exponent byte, bytes of the 16 datums)."""
-    exps = [(b >> 23) & 0xFF for b in bits16]
-    E = max(exps)
-    qmax = (1 << m) - 1
-    datums = []
+def _quantise(bits16, exps, E, m, policy):
+    """Magnitudes of the block against shared exponent E, before saturation (None marks Inf / NaN)."""
+    qs = []
     for b, e in zip(bits16, exps):
-        sign = b >> 31
         if e == 0:
-            q = 0
+            qs.append(0)
         elif e == 255:
-            q = qmax
+            qs.append(None)
         else:
             mag = Fraction((b & 0x7FFFFF) | 0x800000, 1 << 23) * Fraction(2) ** (e - 127)
             v = mag * Fraction(2) ** (m - 1) / Fraction(2) ** (E - 127)
             fl = math.floor(v)
             rem = v - fl
-            if rem > Fraction(1, 2) or (rem == Fraction(1, 2) and fl % 2 == 1):
+            if policy.rounding == 0 and (rem > Fraction(1, 2) or (rem == Fraction(1, 2) and fl % 2 == 1)):
                 fl += 1
-            q = min(fl, qmax)
-        datums.append(((sign << m) | q) if q else 0)
+            qs.append(fl)
+    return qs
+
+
+def _field_position(i, w, policy):
+    """Bit offset of datum i in the block's bytes read as little-endian 32-bit words."""
+    per_word = 32 // w
+    word, field = divmod(i, per_word)
+    if policy.datum_order:
+        field = per_word - 1 - field
+    return word * 32 + field * w
+
+
+def encode_block(bits16, m, policy=DEFAULT):
+    """16 binary32 bit patterns -> (shared exponent byte, bytes of the 16 datums)."""
+    exps = [(b >> 23) & 0xFF for b in bits16]
+    E = max(exps)
+    qmax = (1 << m) - 1
+    qs = _quantise(bits16, exps, E, m, policy)
+    if policy.overflow and E < 255 and any(q is not None and q > qmax for q in qs):
+        E += 1
+        qs = _quantise(bits16, exps, E, m, policy)
+    datums = []
+    for b, q in zip(bits16, qs):
+        q = qmax if q is None else min(q, qmax)
+        datums.append((((b >> 31) << m) | q) if q else 0)
     w = m + 1
     bitstring = 0
     for i, d in enumerate(datums):
-        bitstring |= d << (w * i)
+        bitstring |= d << _field_position(i, w, policy)
     return E, bitstring.to_bytes(2 * w, "little")
 
 
-def decode_block(E, data: bytes, m):
+def encode_tile(bits32x32, m, policy=DEFAULT):
+    """One 32x32 tile (rows of binary32 bit patterns) -> its record: 64 exponent bytes, then the datum bytes of the
+    64 blocks; block k = the face at position k // 16, face row k % 16."""
+    w = m + 1
+    exps = bytearray(64)
+    data = bytearray(64 * 2 * w)
+    for pos, face in enumerate(policy.face_order):
+        for fr in range(16):
+            r, c = (face >> 1) * 16 + fr, (face & 1) * 16
+            E, d = encode_block([int(v) for v in bits32x32[r][c:c + 16]], m, policy)
+            k = pos * 16 + fr
+            exps[k ^ 3 if policy.exponent_order else k] = E
+            data[k * 2 * w:(k + 1) * 2 * w] = d
+    return bytes(exps) + bytes(data)
+
+
+def decode_block(E, data: bytes, m, policy=DEFAULT):
     """-> 16 binary32 bit patterns (overflow gives infinity, as the conversion to binary32 does)."""
     w = m + 1
     word = int.from_bytes(data, "little")
     out = []
     for i in range(16):
-        dat = (word >> (w * i)) & ((1 << w) - 1)
+        dat = (word >> _field_position(i, w, policy)) & ((1 << w) - 1)
         q, s = dat & ((1 << m) - 1), dat >> m
         if q == 0:
             out.append(0)

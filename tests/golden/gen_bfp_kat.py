@@ -1,5 +1,6 @@
 """Writes tests/golden/bfp_kat.npz: known-answer vectors of the frozen block-float spec, computed by the
-exact-arithmetic restatement in bfp_spec.py (not by the C oracle, not by the CUDA kernels).
+exact-arithmetic restatement in bfp_spec.py (not by the C oracle, not by the CUDA kernels), and
+tests/golden/bfp_kat_policies.npz: the tile records of the same values under each of the other layout policies.
 
     python tests/golden/gen_bfp_kat.py
 
@@ -12,7 +13,7 @@ import random
 
 import numpy as np
 
-from bfp_spec import SPEC_VERSION, decode_block, encode_block, f2b
+from bfp_spec import SPEC_VERSION, Policy, decode_block, encode_block, encode_tile, f2b
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
@@ -85,6 +86,40 @@ def main():
         arrays[f"decoded{m}"] = np.array(decs, dtype=np.uint32)
     np.savez_compressed(os.path.join(HERE, "bfp_kat.npz"), **arrays)
     print(f"{len(blocks)} blocks written")
+    write_policy_vectors(blocks)
+
+
+# every switch on its own, then combinations; the columns are (rounding, overflow, face order x4, exponent order, datum order)
+POLICIES = [
+    Policy(rounding=1),
+    Policy(overflow=1),
+    Policy(datum_order=1),
+    Policy(exponent_order=1),
+    Policy(face_order=(0, 2, 1, 3)),
+    Policy(rounding=1, overflow=1, face_order=(3, 1, 2, 0), exponent_order=1, datum_order=1),
+    Policy(rounding=0, overflow=1, face_order=(1, 0, 3, 2), exponent_order=1, datum_order=1),
+]
+
+
+def tiles_of(blocks):
+    """The 256 blocks as the face rows of four 32x32 tiles, faces in the natural order (as the tests lay them out)."""
+    tiles = np.zeros((4, 32, 32), dtype=np.uint32)
+    for b, vals in enumerate(blocks):
+        t, blk = divmod(b, 64)
+        face, fr = divmod(blk, 16)
+        tiles[t, (face >> 1) * 16 + fr, (face & 1) * 16:(face & 1) * 16 + 16] = vals
+    return tiles
+
+
+def write_policy_vectors(blocks):
+    tiles = tiles_of(blocks)
+    arrays = {"spec_version": np.array([SPEC_VERSION]),
+              "policies": np.array([p.as_tuple() for p in POLICIES], dtype=np.uint8)}
+    for m in (7, 3, 1):
+        recs = [[list(encode_tile(tiles[t].tolist(), m, p)) for t in range(4)] for p in POLICIES]
+        arrays[f"records{m}"] = np.array(recs, dtype=np.uint8)       # [policy, tile, record bytes]
+    np.savez_compressed(os.path.join(HERE, "bfp_kat_policies.npz"), **arrays)
+    print(f"{len(POLICIES)} policies x 3 formats x 4 tiles written")
 
 
 if __name__ == "__main__":

@@ -59,7 +59,24 @@ def _worker(rank, world, port, results):
         fused_equal = torch.equal(cf, single)
         ok = ok and fused_equal
         op.disable_fused_scatter()
-        results[rank] = (bool(ok), rel, bool(fused_equal))
+        # tile-row bands of ONE tensor dealt to the ranks (band b -> rank b % world): every rank packs its bands into
+        # its own copy of the image; merged by ownership on rank 0 they are the oracle's image of the whole tensor
+        from pybuda.sharding import band_record_slice, bands_of_rank
+        x1 = torch.randn(1, 1, 1024, 1024, generator=torch.Generator().manual_seed(0))
+        ref1 = R.tilize_pack(x1.numpy(), R.Bfp8_b)
+        mine = torch.full((ref1.size,), 0xAB, dtype=torch.uint8, device="cuda")
+        cuda_ops.tilize_pack_jobs([x1.cuda()], cuda_ops.DF.Bfp8_b, outs=[mine], bands=[bands_of_rank(32, rank, world)])
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        merged = np.empty(ref1.size, np.uint8)
+        for b in range(32):
+            off, nb = band_record_slice(b, 32, 32, 1088)
+            merged[off:off + nb] = gathered[b % world][off:off + nb].cpu().numpy()
+            other = gathered[(b + 1) % world][off:off + nb].cpu().numpy()
+            ok = ok and bool((other == 0xAB).all())               # nobody touches a band it does not own
+        bands_equal = bool(np.array_equal(merged, ref1))
+        ok = ok and bands_equal
+        results[rank] = (bool(ok), rel, bool(fused_equal), bands_equal)
     finally:
         dist.destroy_process_group()
 

@@ -600,15 +600,20 @@ def test_work_counters_survive_reuse_and_concurrent_streams(ops, oracle):
     assert ops._cabi.device_status() == (0, 0)
 
 
-def test_stream_probe_runs_and_rejects_bad_arguments(ops):
-    """The bare streaming kernels behind the roofline figures: every mix and schedule runs on a small case and gives
-    a positive rate; sizes that are not whole row bands are refused with a status code."""
+def test_stream_probe_library_runs_and_rejects_bad_arguments(ops):
+    """The bare streaming kernels behind the roofline figures live in their own small library that only the benchmark
+    loads: every mix and schedule runs on a small case; sizes that are not whole row bands are refused."""
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib = ctypes.CDLL(os.path.join(root, "tt-buda_b200", "lib", "libbuda_probe.so"))
+    lib.buda_probe_stream.restype = ctypes.c_int
+    lib.buda_probe_stream.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_uint64, ctypes.c_int, ctypes.POINTER(ctypes.c_float),
+                                      ctypes.c_void_p]
+    ms = ctypes.c_float(0.0)
     for mix in range(4):
         for schedule in range(3):
-            assert ops.stream_probe(mix, schedule, elements=131072 * 64, reps=2) > 0.0
-    ms = ctypes.c_float(0.0)
-    lib = ops._cabi.lib
-    assert lib.buda_stream_probe(0, 0, 1000, 1, ctypes.byref(ms), None) == 1
-    assert lib.buda_stream_probe(5, 0, 131072, 1, ctypes.byref(ms), None) == 1
-    assert lib.buda_stream_probe(0, 0, 131072, 0, ctypes.byref(ms), None) == 1
+            assert lib.buda_probe_stream(mix, schedule, 131072 * 64, 2, ctypes.byref(ms), None) == 0 and ms.value > 0.0
+    assert lib.buda_probe_stream(0, 0, 1000, 1, ctypes.byref(ms), None) == 1
+    assert lib.buda_probe_stream(5, 0, 131072, 1, ctypes.byref(ms), None) == 1
+    assert lib.buda_probe_stream(0, 0, 131072, 0, ctypes.byref(ms), None) == 1
     assert ops._cabi.device_status() == (0, 0)

@@ -397,3 +397,119 @@ def test_known_answer_generator_is_reproducible():
     finally:
         sys.path.remove(gdir)
 
+
+
+# ------------------------------------------------------------------------------------------------
+# Layout policies: the switches for what the published format description leaves open
+# ------------------------------------------------------------------------------------------------
+def _policy_kat():
+    import os
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "bfp_kat_policies.npz"))
+
+
+def _kat_tiles():
+    """The 256 known-answer blocks laid out as the face rows of four 32x32 tiles side by side: [1,1,32,128]."""
+    k = _kat()
+    x = np.zeros((1, 1, 32, 128), np.uint32)
+    for b in range(256):
+        t, blk = divmod(b, 64)
+        face, fr = divmod(blk, 16)
+        x[0, 0, (face >> 1) * 16 + fr, t * 32 + (face & 1) * 16: t * 32 + (face & 1) * 16 + 16] = k["x"][b]
+    return x
+
+
+def _spec_decode_tiles(records, m, policy_row):
+    """What the exact-arithmetic spec decodes from four tile records laid side by side: [1,1,32,128] bit patterns."""
+    import os, sys
+    gdir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    sys.path.insert(0, gdir)
+    try:
+        from bfp_spec import Policy, decode_block
+    finally:
+        sys.path.remove(gdir)
+    pol = Policy(int(policy_row[0]), int(policy_row[1]), tuple(int(v) for v in policy_row[2:6]), int(policy_row[6]), int(policy_row[7]))
+    w = m + 1
+    rec = 64 + 64 * 2 * w
+    out = np.zeros((1, 1, 32, 128), np.uint32)
+    records = np.asarray(records, np.uint8).reshape(4, rec)
+    for t in range(4):
+        for pos, face in enumerate(pol.face_order):
+            for fr in range(16):
+                k = pos * 16 + fr
+                E = int(records[t, k ^ 3 if pol.exponent_order else k])
+                data = records[t, 64 + k * 2 * w: 64 + (k + 1) * 2 * w].tobytes()
+                r, c = (face >> 1) * 16 + fr, t * 32 + (face & 1) * 16
+                out[0, 0, r, c:c + 16] = decode_block(E, data, m, pol)
+    return out
+
+
+@pytest.mark.parametrize("df_name,m", [("Bfp8_b", 7), ("Bfp4_b", 3), ("Bfp2_b", 1)])
+def test_oracle_matches_known_answers_of_every_policy(oracle, df_name, m):
+    """tests/golden/bfp_kat_policies.npz holds the tile records of the known-answer values under each non-default
+    policy, computed by the exact-arithmetic spec; the C oracle with the same switches must write the same bytes,
+    and read them back to what the spec decodes."""
+    kp = _policy_kat()
+    x = _kat_tiles().view(np.float32)
+    try:
+        for pi, row in enumerate(kp["policies"]):
+            pol = oracle.BfpPolicy(int(row[0]), int(row[1]), tuple(int(v) for v in row[2:6]), int(row[6]), int(row[7]))
+            oracle.set_bfp_policy(pol)
+            img = oracle.tilize_pack(x, getattr(oracle, df_name))
+            want = kp[f"records{m}"][pi].reshape(-1)
+            assert np.array_equal(img, want), (pi, row.tolist(), int(np.argmax(img != want)))
+            back = oracle.unpack_untilize(img, getattr(oracle, df_name), x.shape).view(np.uint32)
+            assert np.array_equal(back, _spec_decode_tiles(want, m, row)), (pi, "decode")
+    finally:
+        oracle.set_bfp_policy(None)
+
+
+def test_policy_switches_one_by_one(oracle):
+    """Each switch does what its name says, on hand-worked blocks."""
+    from oracle import budaref as R
+    f = lambda v: np.array([v], np.float32).view(np.uint32)[0]
+    try:
+        # rounding: 1.9921875 = 255/128 -> 7-bit magnitude 127.5: nearest-even saturates at 127, truncation gives 127;
+        # 1.0234375 = 65.5/64 -> nearest even 66 (65.5 -> 66), truncation 65
+        blk = np.zeros(16, np.uint32)
+        blk[0], blk[1] = f(1.0), f(1.0234375)
+        E, d = R.bfp_pack_block(blk, 7)
+        assert (E, d[0], d[1]) == (127, 64, 66)
+        R.set_bfp_policy(R.BfpPolicy(rounding=1))
+        E, d = R.bfp_pack_block(blk, 7)
+        assert (E, d[0], d[1]) == (127, 64, 65)
+        # overflow: 1.99609375 rounds up to 128 > 127: saturate keeps E, bump raises E and halves every magnitude
+        blk[:] = 0
+        blk[0], blk[1] = f(1.99609375), f(-1.0)
+        R.set_bfp_policy(None)
+        E, d = R.bfp_pack_block(blk, 7)
+        assert (E, d[0], d[1]) == (127, 127, 0x80 | 64)
+        R.set_bfp_policy(R.BfpPolicy(overflow=1))
+        E, d = R.bfp_pack_block(blk, 7)
+        assert (E, d[0], d[1]) == (128, 64, 0x80 | 32)
+        # truncation never overflows, so the two switches together leave E alone
+        R.set_bfp_policy(R.BfpPolicy(rounding=1, overflow=1))
+        E, d = R.bfp_pack_block(blk, 7)
+        assert (E, d[0], d[1]) == (127, 127, 0x80 | 64)
+        # datum order: Bfp4 datums 0..7 share the first 32-bit word; big order puts datum 0 in the top nibble of byte 3
+        blk[:] = 0
+        blk[0] = f(1.0)      # 3-bit magnitude 4
+        R.set_bfp_policy(None)
+        _, d = R.bfp_pack_block(blk, 3)
+        assert d[0] == 0x04 and not d[1:].any()
+        R.set_bfp_policy(R.BfpPolicy(datum_order=1))
+        _, d = R.bfp_pack_block(blk, 3)
+        assert d[3] == 0x40 and not d[:3].any() and not d[4:].any()
+        # face order and exponent order on one tile: a single 2.0 in face 2 (row 16, column 0)
+        x = np.zeros((1, 1, 32, 32), np.float32)
+        x[0, 0, 16, 0] = 2.0
+        R.set_bfp_policy(None)
+        img = R.tilize_pack(x, R.Bfp8_b)
+        assert img[32] == 128 and img[64 + 32 * 16] == 64
+        R.set_bfp_policy(R.BfpPolicy(face_order=(2, 0, 1, 3), exponent_order=1))
+        img = R.tilize_pack(x, R.Bfp8_b)
+        assert img[0 ^ 3] == 128 and img[64] == 64           # face 2 is stored first; its exponent sits in byte 3 of word 0
+        assert np.array_equal(R.unpack_untilize(img, R.Bfp8_b, x.shape), x)
+        with pytest.raises(ValueError):
+            R.set_bfp_policy(R.BfpPolicy(face_order=(0, 0, 1, 2)))
+    finally:
+        R.set_bfp_policy(None)

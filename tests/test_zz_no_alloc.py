@@ -6,7 +6,8 @@ loop that must not pay the device-wide synchronisation an allocation implies.  F
 buda_tilize_pack_host_noalloc stages through a fixed 8 MiB array inside the library.  This test
 calls it through the C ABI twice in a row (second call with another shape and format, so bytes left
 in the shared array by the first call would show) and compares every output byte with the ordinary
-host-buffer entry point; it also checks that an oversize request is refused with a clear message."""
+host-buffer entry point and with the CPU oracle; it also checks that an oversize request is refused with a
+clear message."""
 import ctypes
 
 import pytest
@@ -29,9 +30,18 @@ def _both(cabi, x, dst_df, with_header, geom):
     return got, ref
 
 
-def test_no_alloc_entry_point_matches_host_entry_point_on_two_calls():
+def _oracle_image(oracle, x, df, with_header, grid=(1, 1), ublock=(1, 1), order=0):
+    import numpy as np
+    geom = oracle.Geom.for_shape(list(x.shape), grid, ublock, order)
+    if x.dtype == torch.bfloat16:
+        return oracle.tilize_pack(x.view(torch.int16).numpy().view(np.uint16), df, geom, with_header, src_df=oracle.Float16_b)
+    return oracle.tilize_pack(x.numpy(), df, geom, with_header)
+
+
+def test_no_alloc_entry_point_matches_host_entry_point_on_two_calls(oracle):
     if not torch.cuda.is_available():
         pytest.fail("this test needs a CUDA device; there is no CPU fallback to test")
+    import numpy as np
     from pybuda import _cabi as cabi
 
     g = torch.Generator().manual_seed(123)
@@ -39,10 +49,12 @@ def test_no_alloc_entry_point_matches_host_entry_point_on_two_calls():
     x1 = torch.randn(1, 1, 1024, 1024, generator=g)
     got1, ref1 = _both(cabi, x1, 6, False, cabi.QueueGeom.for_shape(list(x1.shape)))
     assert torch.equal(got1, ref1)
+    assert np.array_equal(got1.numpy(), _oracle_image(oracle, x1, oracle.Bfp8_b, False))
     # call 2, straight after: smaller tensor, other format, tile headers, another queue geometry
     x2 = (torch.randn(2, 3, 128, 160, generator=g) * 100).bfloat16()
     got2, ref2 = _both(cabi, x2, 7, True, cabi.QueueGeom.for_shape(list(x2.shape), (2, 1), (1, 5), 1))
     assert torch.equal(got2, ref2)
+    assert np.array_equal(got2.numpy(), _oracle_image(oracle, x2, oracle.Bfp4_b, True, (2, 1), (1, 5), 1))
     # and the first input once more gives the first answer
     got3, _ = _both(cabi, x1, 6, False, cabi.QueueGeom.for_shape(list(x1.shape)))
     assert torch.equal(got3, ref1)

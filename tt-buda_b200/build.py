@@ -1,5 +1,6 @@
-"""In-tree build of the native parts: libbuda_cuda.so (CUDA kernels + C ABI, sm_100a only) and
-the pybind11 module pybuda._C (C++ host layer that calls the C ABI).
+"""In-tree build of the native parts: libbuda_cuda.so (CUDA kernels + C ABI, sm_100a only), the
+pybind11 module pybuda._C (C++ host layer that calls the C ABI), and libbuda_probe.so (bare streaming
+kernels that only the benchmark loads).
 
     python tt-buda_b200/build.py [--force]
 
@@ -19,7 +20,8 @@ OBJ_DIR = os.path.join(CSRC, "build")
 CUDA_LIB = os.path.join(LIB_DIR, "libbuda_cuda.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
-CU_SOURCES = ["capi.cu", "tilize_pack.cu", "unpack_untilize.cu", "quant.cu", "bfp8_gemm.cu", "gemm_pair.cu", "prestride.cu", "stream_probe.cu"]
+PROBE_LIB = os.path.join(LIB_DIR, "libbuda_probe.so")
+CU_SOURCES = ["capi.cu", "tilize_pack.cu", "unpack_untilize.cu", "quant.cu", "bfp8_gemm.cu", "gemm_pair.cu", "prestride.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I", INCLUDE]
 
@@ -56,7 +58,7 @@ def _run(cmd):
 def build_cuda(force=False, verbose=False):
     os.makedirs(LIB_DIR, exist_ok=True)
     os.makedirs(OBJ_DIR, exist_ok=True)
-    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h", ".hpp"))]
     headers.append(os.path.join(INCLUDE, "buda_cuda.h"))
     jobs = []
     for src in CU_SOURCES:
@@ -71,6 +73,9 @@ def build_cuda(force=False, verbose=False):
     objs = [os.path.join(OBJ_DIR, s[:-3] + ".o") for s in CU_SOURCES]
     if force or jobs or _newer(CUDA_LIB, objs):
         _run([_nvcc(), "-shared", "-o", CUDA_LIB] + objs + ["-Xcompiler", "-fPIC"])
+    probe_src = os.path.join(CSRC, "bench", "stream_probe.cu")
+    if force or _newer(PROBE_LIB, [probe_src]):
+        _run([_nvcc()] + NVCC_FLAGS + ["-shared", "-o", PROBE_LIB, probe_src])
     return CUDA_LIB
 
 

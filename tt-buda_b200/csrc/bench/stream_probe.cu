@@ -5,7 +5,11 @@
 // A band is 32 rows x 1 KiB inside rows of 16 KiB (what a staged work item touches on the row-major side); the other
 // side of a band is contiguous.  A block of 256 threads moves one band at a time: 8 warps x 4 rows, a warp
 // instruction covers 512 contiguous bytes of a row.
-#include "buda_common.cuh"
+//
+// Built into its own small library (libbuda_probe.so) that only bench.py loads: a measurement aid, not part of the
+// conversion library or its interface.
+#include <cuda_runtime.h>
+#include <stdint.h>
 
 namespace buda {
 
@@ -143,3 +147,19 @@ cudaError_t run_stream_probe(int mix, int schedule, uint64_t elements, int reps,
 }
 
 }  // namespace buda
+
+// mix: 0 = 4 bytes read per byte written (tilize + pack, quantise), 1 = 1 byte read per 4 written (unpack + untilize,
+// dequantise), 2 = reads only, 3 = writes only.  schedule: 0 = one short-lived block per band, 1 = resident blocks on
+// a fixed stride, 2 = resident blocks that take bands in address order from a device counter.  elements: a multiple
+// of 131072, at most 2^30; 5 bytes per element are allocated on the current device for the run and freed.  Runs 2
+// untimed and `reps` (1..1000) timed launches on `stream`, synchronises, and stores the mean milliseconds per launch
+// in *ms_out.  Returns 0, or 1 for bad arguments / a CUDA error.
+extern "C" int buda_probe_stream(int mix, int schedule, uint64_t elements, int reps, float *ms_out, void *stream)
+{
+    if (!ms_out || mix < 0 || mix > 3 || schedule < 0 || schedule > 2 || reps < 1 || reps > 1000) return 1;
+    if (elements == 0 || elements % 131072u || elements > (1ull << 30)) return 1;
+    int dev = 0, sm_count = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 1;
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 1;
+    return buda::run_stream_probe(mix, schedule, elements, reps, sm_count, (cudaStream_t)stream, ms_out) == cudaSuccess ? 0 : 1;
+}

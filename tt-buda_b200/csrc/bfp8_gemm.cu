@@ -124,13 +124,9 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                         ok = false;
                         break;
                     }
-#ifndef GEMM_EXP_NO_A
                     mbar_arrive_expect_tx(&full_a[s], kABytes);
                     tma_load_2d(sA + s * kABytes, &tmap_a, (int)(kb * kBK), (int)(m_blk * kBM), &full_a[s]);
                     tma_load_2d(sA + s * kABytes + kABytes / 2, &tmap_a, (int)(kb * kBK), (int)(m_blk * kBM + 128), &full_a[s]);
-#else
-                    mbar_arrive(&full_a[s]);
-#endif
                 }
             }
             if (!ok || *abort_flag) {
@@ -173,11 +169,7 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                             const uint64_t adesc = smem_desc(a_addr + h * (kABytes / 2) + j * 32, 16, 1024);
                             // B: N-major, 64-column atoms 1024 B apart, 8-deep k groups 4096 B apart
                             const uint64_t bdesc = smem_desc(b_addr + j * 8192, 1024, 4096);
-#ifndef GEMM_EXP_NO_MMA
                             umma_bf16(tmem_base + h * kBN, adesc, bdesc, kIdesc, (kb > 0 || j > 0) ? 1u : 0u);
-#else
-                            (void)adesc; (void)bdesc;
-#endif
                         }
                     }
                     umma_commit(&empty_a[s]);
@@ -250,10 +242,6 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                     break;
                 }
                 uint8_t *bst = sB + t * kBBytes;
-#ifdef GEMM_EXP_NO_DECODE
-                if (exp_cur[0] == 0x12345u) bst[lane] = (uint8_t)mant_cur[0].x;
-                if (false)
-#endif
 #pragma unroll
                 for (int it = 0; it < kUnits; it++) {
                     const int u = it * kDecodeWarps + dw;
@@ -284,11 +272,7 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                 for (int c = 0; c < kBN / 32; c++) {
                     uint32_t v[32];
                     tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(h * kBN + c * 32), v);
-#ifdef GEMM_EXP_NO_STORE
-                    if (row < p.M && v[0] == 0x7fc12345u)
-#else
                     if (row < p.M)
-#endif
                         store_row32(v, p.C, p.n_dst, off + c * 32);
                 }
             }
@@ -308,18 +292,12 @@ bfp8b_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
 }  // namespace gemm
 
-// Process-wide choice of matmul kernel: 0 auto, 1 single-CTA, 2 CTA pair.  which < 0 only reads.  The
-// environment variable BUDA_GEMM_KERNEL (single | pair) sets the initial value.  Returns the previous value.
+// Process-wide choice of matmul kernel: 0 auto, 1 single-CTA, 2 CTA pair.  which < 0 only reads.
+// Returns the previous value.
 int gemm_kernel_choice(int which)
 {
-    static std::atomic<int> choice{-1};
-    int cur = choice.load();
-    if (cur < 0) {
-        const char *k = getenv("BUDA_GEMM_KERNEL");
-        int init = (k && k[0] == 's') ? 1 : (k && k[0] == 'p') ? 2 : 0;
-        choice.compare_exchange_strong(cur, init);
-        cur = choice.load();
-    }
+    static std::atomic<int> choice{0};
+    const int cur = choice.load();
     if (which >= 0 && which <= 2) choice.store(which);
     return cur;
 }
@@ -366,10 +344,6 @@ cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, 
     }
     // Kernel choice: gemm_kernel_choice() (0 auto, 1 single-CTA, 2 CTA pair).  Auto gives the pair kernel every
     // problem with more than 256 rows (below that its 512-row tile would be mostly padding).
-    static const int decode_warps = [] {
-        const char *env = getenv("BUDA_GEMM_DECODE_WARPS");  // single-CTA kernel only: 8 (default, measured fastest) or 16
-        return (env && atoi(env) == 16) ? 16 : 8;
-    }();
     const int forced = gemm_kernel_choice(-1);
     Params p;
     p.W = static_cast<const uint8_t *>(W);
@@ -390,17 +364,12 @@ cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, 
     dev &= 63;
     if (!attr_done[dev].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(bfp8b_gemm_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(bfp8b_gemm_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;
         attr_done[dev].store(true, std::memory_order_release);
     }
     uint32_t grid = p.m_tiles * p.n_tiles;
     if (grid > (uint32_t)sm_count) grid = (uint32_t)sm_count;
-    if (decode_warps == 8)
-        bfp8b_gemm_kernel<8><<<grid, threads_for<8>(), kSmemBytes, stream>>>(tmap, p);
-    else
-        bfp8b_gemm_kernel<16><<<grid, threads_for<16>(), kSmemBytes, stream>>>(tmap, p);
+    bfp8b_gemm_kernel<8><<<grid, threads_for<8>(), kSmemBytes, stream>>>(tmap, p);   // 8 decode warps measured faster than 16
     return cudaGetLastError();
 }
 

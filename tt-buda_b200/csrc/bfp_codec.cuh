@@ -19,6 +19,8 @@
 
 #include <stdint.h>
 
+#include "buda_common.cuh"
+
 namespace buda {
 
 constexpr uint32_t kMagicBits = 0x4b400000u;  // 1.5 * 2^23: ulp 1, even
@@ -30,8 +32,10 @@ struct BfpTraits {
     static constexpr int bytes = 16 * (M + 1) / 8;   // 16 / 8 / 4
 };
 
-// Integer encoder of one value (used for blocks at the ends of the exponent range).
-__device__ __forceinline__ uint32_t bfp_encode_datum_int(uint32_t bits, uint32_t E, int m)
+// Integer encoder of one value (used for blocks at the ends of the exponent range, and by the general
+// kernel flavour after a shared exponent was raised).  trunc: drop the low bits instead of rounding to
+// nearest even.  *over is set when the magnitude of a finite value came out above the largest one.
+__device__ __forceinline__ uint32_t bfp_encode_datum_int(uint32_t bits, uint32_t E, int m, bool trunc = false, bool *over = nullptr)
 {
     const uint32_t qmax = (1u << m) - 1u;
     uint32_t e = (bits >> 23) & 0xffu, q;
@@ -46,23 +50,33 @@ __device__ __forceinline__ uint32_t bfp_encode_datum_int(uint32_t bits, uint32_t
             q = 0;
         } else {
             uint32_t kept = sig >> shift, rem = sig & ((1u << shift) - 1u), half = 1u << (shift - 1u);
-            kept += (rem > half || (rem == half && (kept & 1u))) ? 1u : 0u;
+            kept += (!trunc && (rem > half || (rem == half && (kept & 1u)))) ? 1u : 0u;
+            if (over && kept > qmax) *over = true;
             q = kept < qmax ? kept : qmax;
         }
     }
     return q ? (((bits >> 31) << m) | q) : 0u;
 }
 
-// Encode one block.  x: the 16 values as binary32 bit patterns.  Returns the shared exponent and
-// the packed datums (out[0] holds datums 0.., little-endian).
+// Reverses the order of the (M + 1)-bit datum fields inside one 32-bit word (its own inverse).
 template <int M>
-__device__ __forceinline__ void bfp_encode16(const uint32_t (&x)[16], uint32_t &E_out,
-                                             uint32_t (&out)[BfpTraits<M>::words])
+__device__ __forceinline__ uint32_t reverse_datum_fields(uint32_t w)
 {
-    constexpr uint32_t qmax = BfpTraits<M>::qmax;
-    // Maximum of the magnitudes as floats: the absolute values fold into the min/max instructions, three operands
-    // at a time.  A NaN operand gives 0x7fffffff, so NaN and Inf both end with exponent field 255, as an integer
-    // maximum of the magnitude bits would; for every other input the two maxima have the same exponent field.
+    if (M == 7) return __byte_perm(w, 0u, 0x0123);
+    if (M == 3) {
+        const uint32_t r = __byte_perm(w, 0u, 0x0123);
+        return ((r & 0x0f0f0f0fu) << 4) | ((r >> 4) & 0x0f0f0f0fu);
+    }
+    const uint32_t r = __brev(w);
+    return ((r & 0x55555555u) << 1) | ((r >> 1) & 0x55555555u);
+}
+
+// Largest biased binary32 exponent of the 16 values.  The maximum of the magnitudes is taken as floats: the absolute
+// values fold into the min/max instructions, three operands at a time.  A NaN operand gives 0x7fffffff, so NaN and
+// Inf both end with exponent field 255, as an integer maximum of the magnitude bits would; for every other input
+// the two maxima have the same exponent field.
+__device__ __forceinline__ uint32_t bfp_block_exponent(const uint32_t (&x)[16])
+{
     float mf;
     asm("{\n\t.reg .f32 a<16>, m<7>;\n\t"
         "abs.f32 a0, %1;\n\tabs.f32 a1, %2;\n\tabs.f32 a2, %3;\n\tabs.f32 a3, %4;\n\t"
@@ -78,65 +92,151 @@ __device__ __forceinline__ void bfp_encode16(const uint32_t (&x)[16], uint32_t &
           "f"(__uint_as_float(x[4])), "f"(__uint_as_float(x[5])), "f"(__uint_as_float(x[6])), "f"(__uint_as_float(x[7])),
           "f"(__uint_as_float(x[8])), "f"(__uint_as_float(x[9])), "f"(__uint_as_float(x[10])), "f"(__uint_as_float(x[11])),
           "f"(__uint_as_float(x[12])), "f"(__uint_as_float(x[13])), "f"(__uint_as_float(x[14])), "f"(__uint_as_float(x[15])));
-    const uint32_t E = __float_as_uint(mf) >> 23;
+    return __float_as_uint(mf) >> 23;
+}
+
+// |x| * S + 1.5 * 2^23 in one fused multiply-add: rounded to nearest even, or toward zero (= truncation of the
+// magnitude, every operand being non-negative).  The magnitude sits in the low bits of the result, unsaturated.
+template <bool RZ>
+__device__ __forceinline__ uint32_t bfp_quantise_bits(uint32_t xbits, float S)
+{
+    float r;
+    if (RZ)
+        asm("{\n\t.reg .f32 t;\n\tabs.ftz.f32 t, %1;\n\tfma.rz.ftz.f32 %0, t, %2, %3;\n\t}"
+            : "=f"(r) : "f"(__uint_as_float(xbits)), "f"(S), "f"(12582912.0f));
+    else
+        asm("{\n\t.reg .f32 t;\n\tabs.ftz.f32 t, %1;\n\tfma.rn.ftz.f32 %0, t, %2, %3;\n\t}"
+            : "=f"(r) : "f"(__uint_as_float(xbits)), "f"(S), "f"(12582912.0f));
+    return __float_as_uint(r);
+}
+
+// Signs and saturated magnitudes (y: magic constant + q, one per value) -> the packed datums of the block.
+template <int M>
+__device__ __forceinline__ void bfp_pack_datums(const uint32_t (&x)[16], const uint32_t (&y)[16], uint32_t (&out)[BfpTraits<M>::words])
+{
+    uint32_t D[4];
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+        // Q: the four magnitudes, one per byte.  T: the four sign-carrying top bytes.
+        uint32_t Q = __byte_perm(__byte_perm(y[4 * w], y[4 * w + 1], 0x0040),
+                                 __byte_perm(y[4 * w + 2], y[4 * w + 3], 0x0040), 0x5410);
+        uint32_t T = __byte_perm(__byte_perm(x[4 * w], x[4 * w + 1], 0x0073),
+                                 __byte_perm(x[4 * w + 2], x[4 * w + 3], 0x0073), 0x5410);
+        if (M == 7) {
+            uint32_t nz = (Q + 0x7f7f7f7fu) & 0x80808080u;  // bit 7 of a byte set iff its q > 0
+            D[w] = Q | (T & nz);
+        } else if (M == 3) {
+            uint32_t nz = (Q + 0x07070707u) & 0x08080808u;
+            D[w] = Q | ((T >> 4) & nz);
+        } else {
+            uint32_t nz = (Q + 0x01010101u) & 0x02020202u;
+            D[w] = Q | ((T >> 6) & nz);
+        }
+    }
+    if (M == 7) {
+#pragma unroll
+        for (int w = 0; w < 4; w++) out[w % BfpTraits<M>::words] = D[w];
+    } else if (M == 3) {
+        // two 4-bit datums per byte: bytes 0 and 2 of (D | D >> 4)
+        uint32_t t0 = D[0] | (D[0] >> 4), t1 = D[1] | (D[1] >> 4);
+        uint32_t t2 = D[2] | (D[2] >> 4), t3 = D[3] | (D[3] >> 4);
+        out[0] = __byte_perm(t0, t1, 0x6420);
+        out[1 % BfpTraits<M>::words] = __byte_perm(t2, t3, 0x6420);
+    } else {
+        // four 2-bit datums per byte: byte 0 of u, u = t | t >> 12, t = D | D >> 6
+        uint32_t u[4];
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            uint32_t t = D[w] | (D[w] >> 6);
+            u[w] = t | (t >> 12);
+        }
+        out[0] = __byte_perm(__byte_perm(u[0], u[1], 0x0040), __byte_perm(u[2], u[3], 0x0040), 0x5410);
+    }
+}
+
+// One block through the integer encoder.  Returns true when a finite magnitude rounded up past the largest one.
+template <int M>
+__device__ __forceinline__ bool bfp_encode16_int(const uint32_t (&x)[16], uint32_t E, bool trunc, uint32_t (&out)[BfpTraits<M>::words])
+{
+    bool over = false;
+#pragma unroll
+    for (int w = 0; w < BfpTraits<M>::words; w++) out[w] = 0;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        uint32_t d = bfp_encode_datum_int(x[i], E, M, trunc, &over);
+        out[(i * (M + 1)) / 32] |= d << ((i * (M + 1)) % 32);
+    }
+    return over;
+}
+
+// Encode one block.  x: the 16 values as binary32 bit patterns.  Returns the shared exponent and
+// the packed datums (out[0] holds datums 0.., little-endian).
+template <int M>
+__device__ __forceinline__ void bfp_encode16(const uint32_t (&x)[16], uint32_t &E_out,
+                                             uint32_t (&out)[BfpTraits<M>::words])
+{
+    constexpr uint32_t qmax = BfpTraits<M>::qmax;
+    const uint32_t E = bfp_block_exponent(x);
     E_out = E;
 
     if (E + 1u >= (uint32_t)M && E <= (uint32_t)(M + 252)) {
         const float S = __uint_as_float((uint32_t)(M + 253 - (int)E) << 23);  // 2^(M-1+127-E)
         uint32_t y[16];
 #pragma unroll
-        for (int i = 0; i < 16; i++) {
-            float r;
-            asm("{\n\t.reg .f32 t;\n\tabs.ftz.f32 t, %1;\n\tfma.rn.ftz.f32 %0, t, %2, %3;\n\t}"
-                : "=f"(r) : "f"(__uint_as_float(x[i])), "f"(S), "f"(12582912.0f));
-            y[i] = min(__float_as_uint(r), kMagicBits + qmax);  // Inf / NaN and round-ups saturate here
-        }
-        uint32_t D[4];
-#pragma unroll
-        for (int w = 0; w < 4; w++) {
-            // Q: the four magnitudes, one per byte.  T: the four sign-carrying top bytes.
-            uint32_t Q = __byte_perm(__byte_perm(y[4 * w], y[4 * w + 1], 0x0040),
-                                     __byte_perm(y[4 * w + 2], y[4 * w + 3], 0x0040), 0x5410);
-            uint32_t T = __byte_perm(__byte_perm(x[4 * w], x[4 * w + 1], 0x0073),
-                                     __byte_perm(x[4 * w + 2], x[4 * w + 3], 0x0073), 0x5410);
-            if (M == 7) {
-                uint32_t nz = (Q + 0x7f7f7f7fu) & 0x80808080u;  // bit 7 of a byte set iff its q > 0
-                D[w] = Q | (T & nz);
-            } else if (M == 3) {
-                uint32_t nz = (Q + 0x07070707u) & 0x08080808u;
-                D[w] = Q | ((T >> 4) & nz);
-            } else {
-                uint32_t nz = (Q + 0x01010101u) & 0x02020202u;
-                D[w] = Q | ((T >> 6) & nz);
-            }
-        }
-        if (M == 7) {
-#pragma unroll
-            for (int w = 0; w < 4; w++) out[w % BfpTraits<M>::words] = D[w];
-        } else if (M == 3) {
-            // two 4-bit datums per byte: bytes 0 and 2 of (D | D >> 4)
-            uint32_t t0 = D[0] | (D[0] >> 4), t1 = D[1] | (D[1] >> 4);
-            uint32_t t2 = D[2] | (D[2] >> 4), t3 = D[3] | (D[3] >> 4);
-            out[0] = __byte_perm(t0, t1, 0x6420);
-            out[1 % BfpTraits<M>::words] = __byte_perm(t2, t3, 0x6420);
-        } else {
-            // four 2-bit datums per byte: byte 0 of u, u = t | t >> 12, t = D | D >> 6
-            uint32_t u[4];
-#pragma unroll
-            for (int w = 0; w < 4; w++) {
-                uint32_t t = D[w] | (D[w] >> 6);
-                u[w] = t | (t >> 12);
-            }
-            out[0] = __byte_perm(__byte_perm(u[0], u[1], 0x0040), __byte_perm(u[2], u[3], 0x0040), 0x5410);
-        }
+        for (int i = 0; i < 16; i++) y[i] = min(bfp_quantise_bits<false>(x[i], S), kMagicBits + qmax);  // Inf / NaN and round-ups saturate here
+        bfp_pack_datums<M>(x, y, out);
     } else {
+        (void)bfp_encode16_int<M>(x, E, false, out);
+    }
+}
+
+// The same under a layout policy (general kernel flavour): truncation instead of rounding, a shared exponent that
+// is raised by one when a magnitude rounds up past the largest one (every value of the block is then encoded
+// against the raised exponent), and the datum fields of each 32-bit word in reverse order.
+template <int M>
+__device__ __noinline__ void bfp_encode16_raised(const uint32_t (&x)[16], uint32_t E, bool trunc, uint32_t (&out)[BfpTraits<M>::words])
+{
+    (void)bfp_encode16_int<M>(x, E, trunc, out);
+}
+
+// raise_limit: the shared exponent may be raised while it is below this (255; 143 = 31 + 112 for the widened
+// binary16 values of the "a" formats, whose exponent byte has 5 bits).
+template <int M>
+__device__ __forceinline__ void bfp_encode16_policy(const uint32_t (&x)[16], uint32_t &E_out, uint32_t (&out)[BfpTraits<M>::words],
+                                                    const BfpPolicy &pol, uint32_t raise_limit)
+{
+    constexpr uint32_t qmax = BfpTraits<M>::qmax;
+    uint32_t E = bfp_block_exponent(x);
+    bool over = false;
+    if (E + 1u >= (uint32_t)M && E <= (uint32_t)(M + 252)) {
+        const float S = __uint_as_float((uint32_t)(M + 253 - (int)E) << 23);
+        uint32_t y[16];
+        if (pol.trunc) {
 #pragma unroll
-        for (int w = 0; w < BfpTraits<M>::words; w++) out[w] = 0;
+            for (int i = 0; i < 16; i++) y[i] = bfp_quantise_bits<true>(x[i], S);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; i++) y[i] = bfp_quantise_bits<false>(x[i], S);
+        }
+        uint32_t top = 0;
 #pragma unroll
         for (int i = 0; i < 16; i++) {
-            uint32_t d = bfp_encode_datum_int(x[i], E, M);
-            out[(i * (M + 1)) / 32] |= d << ((i * (M + 1)) % 32);
+            top = max(top, y[i]);
+            y[i] = min(y[i], kMagicBits + qmax);
         }
+        over = top > kMagicBits + qmax;     // below the limit every value of the block is finite
+        bfp_pack_datums<M>(x, y, out);
+    } else {
+        over = bfp_encode16_int<M>(x, E, pol.trunc != 0, out);
+    }
+    if (pol.bump && over && E < raise_limit) {
+        E += 1u;
+        bfp_encode16_raised<M>(x, E, pol.trunc != 0, out);
+    }
+    E_out = E;
+    if (pol.datum_be) {
+#pragma unroll
+        for (int w = 0; w < BfpTraits<M>::words; w++) out[w] = reverse_datum_fields<M>(out[w]);
     }
 }
 

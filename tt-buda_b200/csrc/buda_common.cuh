@@ -37,12 +37,9 @@ __host__ __device__ inline int plain_elem_bytes(int df)
 // Launch-time description of one tilize/untilize job (uniform over a batch of tensors)
 // ------------------------------------------------------------------------------------------------
 constexpr int kMaxBatch = 64;    // tensors per launch (pointer table lives in kernel parameters)
-#ifndef BUDA_BOX_TILES
-#define BUDA_BOX_TILES 8
-#endif
 // A work item is a 32-row band of up to this many tiles.  8 (1 KiB row pieces per bulk copy) with two
 // stages and two resident CTAs per SM measured 6.26 TB/s on the Bfp8_b pack; 4 tiles with three stages 5.3.
-constexpr int kBoxTiles = BUDA_BOX_TILES;
+constexpr int kBoxTiles = 8;
 // Tiles per work item of the staged kernels.  Unpack: what matters is the 1 KiB row piece it writes, so a block-float
 // conversion to 2-byte elements takes twice as many tiles per band as one to 4-byte elements.  (Plain relayouts keep 8:
 // their tile records are as large as the rows, and 16 of them would leave room for one CTA per SM only.)  Pack: since
@@ -55,6 +52,29 @@ __host__ __device__ constexpr int pack_box_tiles_for(int es, int mant_bits)
     return mant_bits == 7 ? unpack_box_tiles_for(es, true) / 2 : unpack_box_tiles_for(es, mant_bits > 0);
 }
 __host__ __device__ constexpr int box_tiles_for(int es, bool block_float) { return unpack_box_tiles_for(es, block_float); }
+
+// The choices of the block-float byte layout that the published format description leaves open
+// (docs/public/dataformats.rst:59-89 of the reference: "truncate bits ..., optionally round before truncation";
+// the drawings docs/public/images/bfp{8,4,2}_blocks.png do not say which end of a 32-bit word holds datum 0).
+// All zero = the layout this library writes by default.  Only the general kernel flavour reads it.
+struct BfpPolicy {
+    uint8_t trunc;        // rounding of the dropped mantissa bits: 0 nearest even, 1 truncate
+    uint8_t bump;         // a round-up past the largest magnitude: 0 saturates, 1 raises the shared exponent by one
+    uint8_t exp_be;       // exponent section: 0 block k in byte k, 1 big-endian inside each 32-bit word (byte k ^ 3)
+    uint8_t datum_be;     // mantissa section: 0 datum i in bits [i(m+1), (i+1)(m+1)) of the block, 1 the fields of each 32-bit word reversed
+    uint8_t face_pos[4];  // where face f (0 = top left, 1 = top right, 2 = bottom left, 3 = bottom right) sits in the record
+    uint8_t face_at[4];   // the inverse: which face sits at position p
+};
+__host__ __device__ inline BfpPolicy default_policy()
+{
+    BfpPolicy p = {0, 0, 0, 0, {0, 1, 2, 3}, {0, 1, 2, 3}};
+    return p;
+}
+__host__ __device__ inline bool policy_is_default(const BfpPolicy &p)
+{
+    return !p.trunc && !p.bump && !p.exp_be && !p.datum_be && p.face_pos[0] == 0 && p.face_pos[1] == 1 && p.face_pos[2] == 2 &&
+           p.face_pos[3] == 3;
+}
 
 struct TileJob {
     // row-major side
@@ -78,6 +98,7 @@ struct TileJob {
     uint64_t stride_z_mid, stride_z_out;
     uint32_t tile_h;                    // tensor rows per tile: 32, or 16 / 8 / 4 / 2 / 1 for tiny tiles (direct kernels only)
     uint32_t work_slot;                 // staged kernels: which work counter this launch draws its items from
+    BfpPolicy pol;                      // general kernel flavour only
 };
 
 // Re-derives the work-item fields of a job for `box` tiles per item; false when the launch would have 2^31 items or more.
@@ -139,6 +160,66 @@ struct PtrTable {
     const uint8_t *src[kMaxBatch];
     uint8_t *dst[kMaxBatch];
 };
+
+// ------------------------------------------------------------------------------------------------
+// Job table of the general kernel flavour: every tensor of a launch has its own shape, strides, queue
+// geometry and (optionally) its own selection of tile rows, so a whole set of differently shaped
+// parameters is ONE launch, and so is the share of one tensor's tile-row bands that a GPU owns.
+// Work items are numbered tensor after tensor (item_start), so they are still started in address order.
+// The table travels in the kernel parameters.
+// ------------------------------------------------------------------------------------------------
+constexpr int kMaxGen = 192;
+struct GenEntry {
+    const uint8_t *rm;                  // row-major tensor
+    uint8_t *q;                         // queue image (pack writes it, unpack reads it)
+    uint64_t stride_w, stride_z, stride_r;
+    uint32_t W, Z, Rt, Ct;              // entries, t, tile rows, tile columns of the whole tensor
+    uint32_t item_start;                // first work item of this tensor
+    uint32_t boxes_per_band;
+    uint32_t band_first, band_step, bands;   // tile rows taken: band_first + k * band_step, k < bands
+    uint32_t slots, slot0;
+    uint16_t grid_r, grid_c, mblock_m, mblock_n, ublock_rt, ublock_ct;
+    uint8_t ublock_order, trivial_geom, pad0, pad1;
+};
+struct GenTable {
+    uint32_t n, pad;
+    GenEntry e[kMaxGen];
+};
+
+// Numbers the work items of a table for `box` tiles per item; false when the launch would have 2^31 items or more.
+inline bool finalize_table(GenTable &t, TileJob &common, uint32_t box)
+{
+    uint64_t items = 0;
+    common.box_tiles = box;
+    for (uint32_t i = 0; i < t.n; i++) {
+        GenEntry &e = t.e[i];
+        e.boxes_per_band = (e.Ct + box - 1) / box;
+        e.item_start = (uint32_t)items;
+        items += (uint64_t)e.W * e.Z * e.bands * e.boxes_per_band;
+        if (items >= (1ull << 31)) return false;
+    }
+    common.total_items = (uint32_t)items;
+    return true;
+}
+
+// The TileJob view of one table entry (only the fields the kernels' address arithmetic reads).
+__host__ __device__ inline void job_of_entry(const TileJob &common, const GenEntry &e, TileJob &j)
+{
+    j.W = e.W; j.Z = e.Z; j.Rt = e.Rt; j.Ct = e.Ct;
+    j.stride_w = e.stride_w; j.stride_z = e.stride_z; j.stride_r = e.stride_r;
+    j.box_tiles = common.box_tiles;
+    j.boxes_per_band = e.boxes_per_band;
+    j.g.grid_r = e.grid_r; j.g.grid_c = e.grid_c; j.g.mblock_m = e.mblock_m; j.g.mblock_n = e.mblock_n;
+    j.g.ublock_rt = e.ublock_rt; j.g.ublock_ct = e.ublock_ct; j.g.t = e.Z; j.g.ublock_order = e.ublock_order;
+    j.tile_bytes = common.tile_bytes;
+    j.header_bytes = common.header_bytes;
+    j.tiles_per_entry = (uint64_t)e.Z * e.mblock_m * e.mblock_n * e.ublock_rt * e.ublock_ct;
+    j.slots = e.slots; j.slot0 = e.slot0;
+    j.buf_bytes = (uint64_t)(e.slots ? e.slots : e.W) * j.tiles_per_entry * common.tile_bytes;
+    j.trivial_geom = e.trivial_geom;
+    j.zn1 = j.zn2 = 0;
+    j.tile_h = 32;
+}
 
 // Tile (z, rt, ct) of entry w -> byte offset of its record inside the queue image.
 // Restates TileLayout::map (pybuda/csrc/balancer/types.cpp:629-648): the grid core owning the

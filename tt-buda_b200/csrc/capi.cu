@@ -14,6 +14,14 @@ cudaError_t launch_tilize(const TileJob &job, const PtrTable &ptrs, int batch, i
                           int vec_ok, int sm_count, cudaStream_t stream, unsigned int *status);
 cudaError_t launch_untilize(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int a_format, int path,
                             int vec_ok, int sm_count, cudaStream_t stream, unsigned int *status);
+cudaError_t launch_tilize_table(const TileJob &job, const GenTable &table, int mant_bits, int es, int a_format, int sm_count,
+                                cudaStream_t stream, unsigned int *status);
+cudaError_t launch_tilize_direct_policy(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int a_format,
+                                        int vec_ok, int sm_count, cudaStream_t stream);
+cudaError_t launch_untilize_table(const TileJob &job, const GenTable &table, int mant_bits, int es, int a_format, int sm_count,
+                                  cudaStream_t stream, unsigned int *status);
+cudaError_t launch_untilize_direct_policy(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int a_format,
+                                          int vec_ok, int sm_count, cudaStream_t stream);
 cudaError_t launch_quantize(const float *x, int64_t n, const float *scale, int64_t scale_len, int64_t inner, float zp,
                             int mode, float lo, float hi, int8_t *out, int sm_count, cudaStream_t stream);
 cudaError_t launch_dequantize(const int8_t *x, int64_t n, const float *scale, int64_t scale_len, int64_t inner, float zp,
@@ -26,7 +34,6 @@ cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, 
                               size_t err_len);
 
 int gemm_kernel_choice(int which);
-cudaError_t run_stream_probe(int mix, int schedule, uint64_t elements, int reps, int sm_count, cudaStream_t stream, float *ms_out);
 cudaError_t launch_prestride(const void *src, int elem_bytes, const uint32_t shape[4], const uint64_t strides[4], int stride,
                              const int *xy_offsets, int n_offsets, void *dst, uint32_t dst_rows, uint32_t dst_cols, int sm_count,
                              cudaStream_t stream);
@@ -78,6 +85,17 @@ int cuda_fail(cudaError_t e, const char *what)
 
 constexpr int kMaxDevices = 64;
 constexpr int kPipeDepth = 4;
+
+// The process-wide byte-layout policy (buda_set_bfp_policy).  Read once per call.
+std::mutex g_policy_mu;
+BfpPolicy g_policy = default_policy();
+buda_bfp_policy g_policy_public = {0, 0, {0, 1, 2, 3}, 0, 0};
+
+BfpPolicy current_policy()
+{
+    std::lock_guard<std::mutex> lock(g_policy_mu);
+    return g_policy;
+}
 
 struct DevCtx {
     std::once_flag once;
@@ -142,6 +160,7 @@ int make_job(const uint32_t shape[4], const uint64_t strides[4], const buda_queu
                     (unsigned long long)g->grid_c * g->mblock_n * g->ublock_ct * 32u, shape[2], shape[3]);
     j.W = shape[0]; j.Z = shape[1]; j.Rt = shape[2] / th; j.Ct = shape[3] / 32;
     j.tile_h = th;
+    j.pol = default_policy();           // the callers that honour a policy overwrite it
     j.work_slot = 0;                    // set per launch by the staged launchers
     j.stride_w = strides[0]; j.stride_z = strides[1]; j.stride_r = strides[2];
     j.box_tiles = (uint32_t)box_tiles_for((int)strides[3], bfp_mant_bits(qdf) != 0);
@@ -216,6 +235,70 @@ int check_queue_ptrs_aligned(const void *const *q, int n)
     return BUDA_SUCCESS;
 }
 
+// Table entry of the general kernel flavour for one tensor whose job has been validated by make_job.
+// band_count == 0 takes every tile row.
+int fill_entry(const TileJob &j, const void *rm, void *q, uint32_t band_first, uint32_t band_step, uint32_t band_count, GenEntry &e)
+{
+    const buda_queue_geom &g = j.g;
+    if ((g.grid_r | g.grid_c | g.mblock_m | g.mblock_n | g.ublock_rt | g.ublock_ct) > 0xffffu)
+        return fail(BUDA_RUNTIME_ERROR, "queue geometry terms above 65535 are not supported in a job table");
+    if (band_count == 0) {
+        band_first = 0; band_step = 1; band_count = j.Rt;
+    }
+    if (band_step == 0 || (uint64_t)band_first + (uint64_t)(band_count - 1) * band_step >= j.Rt)
+        return fail(BUDA_RUNTIME_ERROR, "tile rows %u + k*%u, k < %u, reach past the tensor's %u tile rows", band_first, band_step,
+                    band_count, j.Rt);
+    memset(&e, 0, sizeof(e));
+    e.rm = (const uint8_t *)rm;
+    e.q = (uint8_t *)q;
+    e.stride_w = j.stride_w; e.stride_z = j.stride_z; e.stride_r = j.stride_r;
+    e.W = j.W; e.Z = j.Z; e.Rt = j.Rt; e.Ct = j.Ct;
+    e.band_first = band_first; e.band_step = band_step; e.bands = band_count;
+    e.slots = j.slots; e.slot0 = j.slot0;
+    e.grid_r = (uint16_t)g.grid_r; e.grid_c = (uint16_t)g.grid_c; e.mblock_m = (uint16_t)g.mblock_m; e.mblock_n = (uint16_t)g.mblock_n;
+    e.ublock_rt = (uint16_t)g.ublock_rt; e.ublock_ct = (uint16_t)g.ublock_ct;
+    e.ublock_order = (uint8_t)g.ublock_order;
+    e.trivial_geom = (uint8_t)j.trivial_geom;
+    return BUDA_SUCCESS;
+}
+
+// One launch of a uniform batch through the kernel the alignment allows, in the flavour the policy asks for.
+// direction 0 = tilize + pack (pt.src row-major, pt.dst image), 1 = unpack + untilize (pt.src image, pt.dst row-major).
+int launch_uniform(int direction, DevCtx *ctx, TileJob &job, const PtrTable &pt, int nb, int mant, int es, int a_format, int path,
+                   int vec_ok, cudaStream_t stream)
+{
+    const BfpPolicy pol = current_policy();
+    cudaError_t e;
+    if (policy_is_default(pol)) {
+        e = direction == 0 ? launch_tilize(job, pt, nb, mant, es, a_format, path, vec_ok, ctx->sm_count, stream, ctx->status)
+                           : launch_untilize(job, pt, nb, mant, es, a_format, path, vec_ok, ctx->sm_count, stream, ctx->status);
+    } else {
+        job.pol = pol;
+        if (path == 0 && job.zn1 == 0) {
+            GenTable *tab = new GenTable;   // ~20 KB: kept off the stack of whatever thread calls in
+            tab->n = (uint32_t)nb;
+            tab->pad = 0;
+            int rc = BUDA_SUCCESS;
+            for (int b = 0; b < nb && rc == BUDA_SUCCESS; b++)
+                rc = direction == 0 ? fill_entry(job, pt.src[b], pt.dst[b], 0, 1, 0, tab->e[b])
+                                    : fill_entry(job, pt.dst[b], const_cast<uint8_t *>(pt.src[b]), 0, 1, 0, tab->e[b]);
+            if (rc != BUDA_SUCCESS) {
+                delete tab;
+                return rc;
+            }
+            e = direction == 0 ? launch_tilize_table(job, *tab, mant, es, a_format, ctx->sm_count, stream, ctx->status)
+                               : launch_untilize_table(job, *tab, mant, es, a_format, ctx->sm_count, stream, ctx->status);
+            delete tab;
+        } else {
+            e = direction == 0 ? launch_tilize_direct_policy(job, pt, nb, mant, es, a_format, vec_ok, ctx->sm_count, stream)
+                               : launch_untilize_direct_policy(job, pt, nb, mant, es, a_format, vec_ok, ctx->sm_count, stream);
+        }
+    }
+    if (e != cudaSuccess) return cuda_fail(e, direction == 0 ? "tilize launch failed" : "untilize launch failed");
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return BUDA_SUCCESS;
+}
+
 int tilize_device(int n, const void *const *srcs, int src_df, const uint32_t shape[4], const uint64_t strides[4],
                   const buda_queue_geom *geom, int dst_df, int with_header, void *const *dsts, uint64_t dst_bytes_each,
                   cudaStream_t stream, int force_path, uint32_t slots = 0, uint32_t slot0 = 0)
@@ -251,9 +334,7 @@ int tilize_device(int n, const void *const *srcs, int src_df, const uint32_t sha
             if (force_path == 0 && path != 0) return fail(BUDA_RUNTIME_ERROR, "staged path needs 16-byte aligned rows and 32-row tiles");
             path = force_path;
         }
-        cudaError_t e = launch_tilize(job, pt, nb, mant, es, is_bfp_a(dst_df) ? 1 : 0, path, vec_ok, ctx->sm_count, stream, ctx->status);
-        if (e != cudaSuccess) return cuda_fail(e, "tilize launch failed");
-        g_launches.fetch_add(1, std::memory_order_relaxed);
+        if (int rc = launch_uniform(0, ctx, job, pt, nb, mant, es, is_bfp_a(dst_df) ? 1 : 0, path, vec_ok, stream)) return rc;
     }
     return BUDA_SUCCESS;
 }
@@ -289,9 +370,7 @@ int untilize_device(int n, const void *const *srcs, int src_df, int with_header,
             if (force_path == 0 && path != 0) return fail(BUDA_RUNTIME_ERROR, "staged path needs 16-byte aligned rows and 32-row tiles");
             path = force_path;
         }
-        cudaError_t e = launch_untilize(job, pt, nb, mant, es, is_bfp_a(src_df) ? 1 : 0, path, vec_ok, ctx->sm_count, stream, ctx->status);
-        if (e != cudaSuccess) return cuda_fail(e, "untilize launch failed");
-        g_launches.fetch_add(1, std::memory_order_relaxed);
+        if (int rc = launch_uniform(1, ctx, job, pt, nb, mant, es, is_bfp_a(src_df) ? 1 : 0, path, vec_ok, stream)) return rc;
     }
     return BUDA_SUCCESS;
 }
@@ -371,159 +450,208 @@ int status_after_sync(DevCtx *ctx)
     return BUDA_SUCCESS;
 }
 
-// The row-major tensor is in HOST memory; the queue image is in host memory (q_on_device == 0) or
-// already in device memory, possibly as a ring of `slots` entries (q_on_device == 1).
+// One tensor of a host-buffer conversion: the row-major tensor is in HOST memory; the queue image is in host
+// memory or already in device memory (possibly a ring of `slots` entries), the same for every item of a call.
+struct HostItem {
+    const void *rm_host;
+    const void *q_ptr;
+    const uint32_t *shape;
+    const uint64_t *strides;
+    const buda_queue_geom *geom;
+    uint64_t q_bytes;
+    uint32_t slots, slot0;
+};
+
 // direction 0: row-major -> queue image; 1: queue image -> row-major.
-// n > 1: the same conversion for n tensors of one shape (rm_hosts[i] <-> q_ptrs[i]); the copy-in / kernel /
-// copy-out pipeline keeps running across tensor boundaries and is drained once, at the end.
-int host_pipeline_n(int direction, int n, const void *const *rm_hosts, int rm_df, const uint32_t shape[4], const uint64_t strides[4],
-                    const buda_queue_geom *geom, int q_df, int with_header, const void *const *q_ptrs, uint64_t q_bytes,
-                    int q_on_device, uint32_t slots, uint32_t slot0)
+// The copy-in / kernel / copy-out pipeline keeps running across tensor boundaries and is drained once, at the end.
+// Whatever the outcome, nothing of this call is still in flight on the staging slots when the lock is released.
+int host_pipeline_items(int direction, int n, const HostItem *items, int rm_df, int q_df, int with_header, int q_on_device)
 {
     DevCtx *ctx;
     if (int rc = get_ctx(&ctx)) return rc;
     if (n <= 0) return BUDA_SUCCESS;
-    if (!rm_hosts || !q_ptrs) return fail(BUDA_RUNTIME_ERROR, "null buffer table");
-    for (int i = 0; i < n; i++)
-        if (!rm_hosts[i] || !q_ptrs[i]) return fail(BUDA_RUNTIME_ERROR, "null buffer");
+    if (!items) return fail(BUDA_RUNTIME_ERROR, "null buffer table");
     int mant, es;
     if (int rc = classify(rm_df, q_df, mant, es, direction == 1)) return rc;
-    TileJob full;
-    if (int rc = make_job(shape, strides, geom, q_df, with_header, 1, full, slots, slot0)) return rc;
-    if (strides[3] != (uint64_t)es) return fail(BUDA_RUNTIME_ERROR, "innermost stride must equal the element size");
-    const uint64_t image_bytes = full.buf_bytes * geom->grid_r * geom->grid_c;
-    if (q_bytes < image_bytes)
-        return fail(BUDA_RUNTIME_ERROR, "queue image buffer holds %llu bytes, needs %llu", (unsigned long long)q_bytes,
-                    (unsigned long long)image_bytes);
-    const uint64_t row_bytes = (uint64_t)shape[3] * es;
-    if (strides[2] < row_bytes) return fail(BUDA_RUNTIME_ERROR, "row stride smaller than a row");
-    const SlicePlan plan = plan_slices(full, row_bytes);
 
-    std::lock_guard<std::mutex> lock(ctx->host_mu);
-    // a slice on the device is always dense: [rows][row_bytes]
-    const uint32_t slice_bands = plan.sliced ? plan.bands_per_slice : full.Rt;
-    const uint64_t slice_a = plan.sliced ? (uint64_t)slice_bands * full.tile_h * row_bytes
-                                         : (uint64_t)shape[0] * shape[1] * shape[2] * row_bytes;
-    const uint64_t slice_b = q_on_device ? 0 : (plan.sliced ? (uint64_t)slice_bands * full.Ct * full.tile_bytes : image_bytes);
-    if (int rc = ensure_pipe(ctx, slice_a, slice_b)) return rc;
-
-    cudaError_t e = cudaSuccess;
-    auto copy_rows = [&](uint8_t *dev, uint8_t *host, uint64_t rows, cudaStream_t s, bool to_dev) -> cudaError_t {
-        // rows of `row_bytes` at pitch strides[2] on the host, dense on the device
-        if (strides[2] == row_bytes)
-            return cudaMemcpyAsync(to_dev ? (void *)dev : (void *)host, to_dev ? (void *)host : (void *)dev,
-                                   rows * row_bytes, to_dev ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, s);
-        return to_dev ? cudaMemcpy2DAsync(dev, row_bytes, host, strides[2], row_bytes, rows, cudaMemcpyHostToDevice, s)
-                      : cudaMemcpy2DAsync(host, strides[2], dev, row_bytes, row_bytes, rows, cudaMemcpyDeviceToHost, s);
+    // validate everything and size the staging slots before anything is enqueued
+    struct Plan {
+        TileJob full;
+        SlicePlan plan;
+        uint64_t row_bytes, image_bytes;
     };
-
-    if (!plan.sliced) {
-      for (int bi = 0; bi < n; bi++) {
-        uint8_t *rm_host = (uint8_t *)rm_hosts[bi];
-        uint8_t *q_mem = (uint8_t *)q_ptrs[bi];
-        // one shot: the whole tensor goes through slot 0
-        uint8_t *a = ctx->stage_a[0];
-        uint8_t *b = q_on_device ? q_mem : ctx->stage_b[0];
-        const uint64_t dense[4] = {(uint64_t)shape[1] * shape[2] * row_bytes, (uint64_t)shape[2] * row_bytes, row_bytes,
-                                   (uint64_t)es};
-        const void *srcs[1];
-        void *dsts[1];
-        if (direction == 0) {
-            for (uint32_t w = 0; w < shape[0] && e == cudaSuccess; w++)
-                for (uint32_t z = 0; z < shape[1] && e == cudaSuccess; z++)
-                    e = copy_rows(a + w * dense[0] + z * dense[1], rm_host + w * strides[0] + z * strides[1], shape[2],
-                                  ctx->s_comp, true);
-            if (e != cudaSuccess) return cuda_fail(e, "host to device copy");
-            srcs[0] = a; dsts[0] = b;
-            if (int rc = tilize_device(1, srcs, rm_df, shape, dense, geom, q_df, with_header, dsts, image_bytes, ctx->s_comp, -1,
-                                       q_on_device ? slots : 0, q_on_device ? slot0 : 0))
-                return rc;
-            if (!q_on_device) e = cudaMemcpyAsync(q_mem, b, image_bytes, cudaMemcpyDeviceToHost, ctx->s_comp);
-        } else {
-            if (!q_on_device) e = cudaMemcpyAsync(b, q_mem, image_bytes, cudaMemcpyHostToDevice, ctx->s_comp);
-            if (e != cudaSuccess) return cuda_fail(e, "host to device copy");
-            srcs[0] = b; dsts[0] = a;
-            if (int rc = untilize_device(1, srcs, q_df, with_header, geom, dsts, rm_df, shape, dense, ctx->s_comp, -1,
-                                         q_on_device ? slots : 0, q_on_device ? slot0 : 0))
-                return rc;
-            for (uint32_t w = 0; w < shape[0] && e == cudaSuccess; w++)
-                for (uint32_t z = 0; z < shape[1] && e == cudaSuccess; z++)
-                    e = copy_rows(a + w * dense[0] + z * dense[1], rm_host + w * strides[0] + z * strides[1], shape[2],
-                                  ctx->s_comp, false);
-        }
-        if (e != cudaSuccess) return cuda_fail(e, "copy");
-        e = cudaStreamSynchronize(ctx->s_comp);
-        if (e != cudaSuccess) return cuda_fail(e, "synchronize");
-      }
-      return status_after_sync(ctx);
+    std::vector<Plan> plans((size_t)n);
+    uint64_t need_a = 0, need_b = 0;
+    for (int i = 0; i < n; i++) {
+        const HostItem &it = items[i];
+        if (!it.rm_host || !it.q_ptr) return fail(BUDA_RUNTIME_ERROR, "null buffer");
+        Plan &pl = plans[(size_t)i];
+        if (int rc = make_job(it.shape, it.strides, it.geom, q_df, with_header, 1, pl.full, it.slots, it.slot0)) return rc;
+        if (it.strides[3] != (uint64_t)es) return fail(BUDA_RUNTIME_ERROR, "innermost stride must equal the element size");
+        pl.image_bytes = pl.full.buf_bytes * it.geom->grid_r * it.geom->grid_c;
+        if (it.q_bytes < pl.image_bytes)
+            return fail(BUDA_RUNTIME_ERROR, "queue image buffer holds %llu bytes, needs %llu", (unsigned long long)it.q_bytes,
+                        (unsigned long long)pl.image_bytes);
+        pl.row_bytes = (uint64_t)it.shape[3] * es;
+        if (it.strides[2] < pl.row_bytes) return fail(BUDA_RUNTIME_ERROR, "row stride smaller than a row");
+        pl.plan = plan_slices(pl.full, pl.row_bytes);
+        const uint64_t slice_a = pl.plan.sliced ? (uint64_t)pl.plan.bands_per_slice * pl.full.tile_h * pl.row_bytes
+                                                : (uint64_t)it.shape[0] * it.shape[1] * it.shape[2] * pl.row_bytes;
+        const uint64_t slice_b = q_on_device ? 0
+                                             : (pl.plan.sliced ? (uint64_t)pl.plan.bands_per_slice * pl.full.Ct * pl.full.tile_bytes
+                                                               : pl.image_bytes);
+        if (slice_a > need_a) need_a = slice_a;
+        if (slice_b > need_b) need_b = slice_b;
     }
 
-    // sliced: each slice is a [1,1,bands*32,C] tensor whose records are one contiguous run of the image
-    uint64_t k = 0;
+    std::lock_guard<std::mutex> lock(ctx->host_mu);
+    if (int rc = ensure_pipe(ctx, need_a, need_b)) return rc;
+
+    auto drain = [&]() -> cudaError_t {
+        cudaError_t first = cudaSuccess, e;
+        if ((e = cudaStreamSynchronize(ctx->s_in)) != cudaSuccess && first == cudaSuccess) first = e;
+        if ((e = cudaStreamSynchronize(ctx->s_comp)) != cudaSuccess && first == cudaSuccess) first = e;
+        if ((e = cudaStreamSynchronize(ctx->s_out)) != cudaSuccess && first == cudaSuccess) first = e;
+        return first;
+    };
+    // leaves with the pipeline drained (best effort) so that the next caller never meets this call's work
+    auto bail = [&](int rc) -> int {
+        (void)drain();
+        return rc;
+    };
+
+    uint64_t k = 0;   // slices issued so far
     for (int bi = 0; bi < n; bi++) {
-    uint8_t *rm_host = (uint8_t *)rm_hosts[bi];
-    uint8_t *q_mem = (uint8_t *)q_ptrs[bi];
-    for (uint32_t w = 0; w < shape[0]; w++) {
-        for (uint32_t z = 0; z < shape[1]; z++) {
-            for (uint32_t sl = 0; sl < plan.slices_per_plane; sl++, k++) {
-                const int slot = (int)(k % kPipeDepth);
-                const uint32_t band0 = sl * plan.bands_per_slice;
-                const uint32_t nb = (full.Rt - band0 < plan.bands_per_slice) ? (full.Rt - band0) : plan.bands_per_slice;
-                const uint32_t sshape[4] = {1, 1, nb * full.tile_h, shape[3]};
-                const uint64_t sstr[4] = {(uint64_t)nb * full.tile_h * row_bytes, (uint64_t)nb * full.tile_h * row_bytes, row_bytes,
-                                          (uint64_t)es};
-                buda_queue_geom sg = *geom;
-                sg.t = 1;
-                sg.mblock_m = nb;
-                uint8_t *a = ctx->stage_a[slot];
-                uint8_t *rm_ptr = rm_host + w * strides[0] + z * strides[1] + (uint64_t)band0 * full.tile_h * strides[2];
-                uint8_t *q_ptr = q_mem + tile_record_offset(full, w, z, band0, 0);
-                uint8_t *b = q_on_device ? q_ptr : ctx->stage_b[slot];
-                const uint64_t q_len = (uint64_t)nb * full.Ct * full.tile_bytes;
-                const void *srcs[1];
-                void *dsts[1];
-                // the staging slot is free once the last stream that used it has passed ev_out
-                if (k >= (uint64_t)kPipeDepth) {
-                    if ((e = cudaStreamWaitEvent(ctx->s_in, ctx->ev_out[slot], 0)) != cudaSuccess) return cuda_fail(e, "wait");
+        const HostItem &it = items[bi];
+        const Plan &pl = plans[(size_t)bi];
+        const TileJob &full = pl.full;
+        const uint32_t *shape = it.shape;
+        const uint64_t *strides = it.strides;
+        const uint64_t row_bytes = pl.row_bytes;
+        uint8_t *rm_host = (uint8_t *)it.rm_host;
+        uint8_t *q_mem = (uint8_t *)it.q_ptr;
+        cudaError_t e = cudaSuccess;
+        auto copy_rows = [&](uint8_t *dev, uint8_t *host, uint64_t rows, cudaStream_t s, bool to_dev) -> cudaError_t {
+            // rows of `row_bytes` at pitch strides[2] on the host, dense on the device
+            if (strides[2] == row_bytes)
+                return cudaMemcpyAsync(to_dev ? (void *)dev : (void *)host, to_dev ? (void *)host : (void *)dev,
+                                       rows * row_bytes, to_dev ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, s);
+            return to_dev ? cudaMemcpy2DAsync(dev, row_bytes, host, strides[2], row_bytes, rows, cudaMemcpyHostToDevice, s)
+                          : cudaMemcpy2DAsync(host, strides[2], dev, row_bytes, row_bytes, rows, cudaMemcpyDeviceToHost, s);
+        };
+
+        if (!pl.plan.sliced) {
+            // one shot: the whole tensor goes through slot 0, after everything issued so far has left the slots
+            if (k > 0) {
+                if ((e = drain()) != cudaSuccess) return cuda_fail(e, "synchronize");
+                k = 0;
+            }
+            uint8_t *a = ctx->stage_a[0];
+            uint8_t *b = q_on_device ? q_mem : ctx->stage_b[0];
+            const uint64_t dense[4] = {(uint64_t)shape[1] * shape[2] * row_bytes, (uint64_t)shape[2] * row_bytes, row_bytes,
+                                       (uint64_t)es};
+            const void *srcs[1];
+            void *dsts[1];
+            if (direction == 0) {
+                for (uint32_t w = 0; w < shape[0] && e == cudaSuccess; w++)
+                    for (uint32_t z = 0; z < shape[1] && e == cudaSuccess; z++)
+                        e = copy_rows(a + w * dense[0] + z * dense[1], rm_host + w * strides[0] + z * strides[1], shape[2],
+                                      ctx->s_comp, true);
+                if (e != cudaSuccess) return bail(cuda_fail(e, "host to device copy"));
+                srcs[0] = a; dsts[0] = b;
+                if (int rc = tilize_device(1, srcs, rm_df, shape, dense, it.geom, q_df, with_header, dsts, pl.image_bytes, ctx->s_comp, -1,
+                                           q_on_device ? it.slots : 0, q_on_device ? it.slot0 : 0))
+                    return bail(rc);
+                if (!q_on_device) e = cudaMemcpyAsync(q_mem, b, pl.image_bytes, cudaMemcpyDeviceToHost, ctx->s_comp);
+            } else {
+                if (!q_on_device) e = cudaMemcpyAsync(b, q_mem, pl.image_bytes, cudaMemcpyHostToDevice, ctx->s_comp);
+                if (e != cudaSuccess) return bail(cuda_fail(e, "host to device copy"));
+                srcs[0] = b; dsts[0] = a;
+                if (int rc = untilize_device(1, srcs, q_df, with_header, it.geom, dsts, rm_df, shape, dense, ctx->s_comp, -1,
+                                             q_on_device ? it.slots : 0, q_on_device ? it.slot0 : 0))
+                    return bail(rc);
+                for (uint32_t w = 0; w < shape[0] && e == cudaSuccess; w++)
+                    for (uint32_t z = 0; z < shape[1] && e == cudaSuccess; z++)
+                        e = copy_rows(a + w * dense[0] + z * dense[1], rm_host + w * strides[0] + z * strides[1], shape[2],
+                                      ctx->s_comp, false);
+            }
+            if (e != cudaSuccess) return bail(cuda_fail(e, "copy"));
+            if ((e = cudaStreamSynchronize(ctx->s_comp)) != cudaSuccess) return bail(cuda_fail(e, "synchronize"));
+            continue;
+        }
+
+        // sliced: each slice is a [1,1,bands*32,C] tensor whose records are one contiguous run of the image
+        const SlicePlan &plan = pl.plan;
+        for (uint32_t w = 0; w < shape[0]; w++) {
+            for (uint32_t z = 0; z < shape[1]; z++) {
+                for (uint32_t sl = 0; sl < plan.slices_per_plane; sl++, k++) {
+                    const int slot = (int)(k % kPipeDepth);
+                    const uint32_t band0 = sl * plan.bands_per_slice;
+                    const uint32_t nb = (full.Rt - band0 < plan.bands_per_slice) ? (full.Rt - band0) : plan.bands_per_slice;
+                    const uint32_t sshape[4] = {1, 1, nb * full.tile_h, shape[3]};
+                    const uint64_t sstr[4] = {(uint64_t)nb * full.tile_h * row_bytes, (uint64_t)nb * full.tile_h * row_bytes, row_bytes,
+                                              (uint64_t)es};
+                    buda_queue_geom sg = *it.geom;
+                    sg.t = 1;
+                    sg.mblock_m = nb;
+                    uint8_t *a = ctx->stage_a[slot];
+                    uint8_t *rm_ptr = rm_host + w * strides[0] + z * strides[1] + (uint64_t)band0 * full.tile_h * strides[2];
+                    uint8_t *q_ptr = q_mem + tile_record_offset(full, w, z, band0, 0);
+                    uint8_t *b = q_on_device ? q_ptr : ctx->stage_b[slot];
+                    const uint64_t q_len = (uint64_t)nb * full.Ct * full.tile_bytes;
+                    const void *srcs[1];
+                    void *dsts[1];
+                    // the staging slot is free once the last stream that used it has passed ev_out
+                    if (k >= (uint64_t)kPipeDepth) {
+                        if ((e = cudaStreamWaitEvent(ctx->s_in, ctx->ev_out[slot], 0)) != cudaSuccess) return bail(cuda_fail(e, "wait"));
+                    }
+                    if (direction == 0) {
+                        if ((e = copy_rows(a, rm_ptr, (uint64_t)nb * full.tile_h, ctx->s_in, true)) != cudaSuccess)
+                            return bail(cuda_fail(e, "host to device copy"));
+                    } else if (!q_on_device) {
+                        if ((e = cudaMemcpyAsync(b, q_ptr, q_len, cudaMemcpyHostToDevice, ctx->s_in)) != cudaSuccess)
+                            return bail(cuda_fail(e, "host to device copy"));
+                    }
+                    cudaEventRecord(ctx->ev_in[slot], ctx->s_in);
+                    cudaStreamWaitEvent(ctx->s_comp, ctx->ev_in[slot], 0);
+                    if (direction == 0) {
+                        srcs[0] = a; dsts[0] = b;
+                        if (int rc = tilize_device(1, srcs, rm_df, sshape, sstr, &sg, q_df, with_header, dsts, q_len, ctx->s_comp, -1))
+                            return bail(rc);
+                    } else {
+                        srcs[0] = b; dsts[0] = a;
+                        if (int rc = untilize_device(1, srcs, q_df, with_header, &sg, dsts, rm_df, sshape, sstr, ctx->s_comp, -1))
+                            return bail(rc);
+                    }
+                    cudaEventRecord(ctx->ev_comp[slot], ctx->s_comp);
+                    cudaStreamWaitEvent(ctx->s_out, ctx->ev_comp[slot], 0);
+                    if (direction == 0) {
+                        if (!q_on_device && (e = cudaMemcpyAsync(q_ptr, b, q_len, cudaMemcpyDeviceToHost, ctx->s_out)) != cudaSuccess)
+                            return bail(cuda_fail(e, "device to host copy"));
+                    } else {
+                        if ((e = copy_rows(a, rm_ptr, (uint64_t)nb * full.tile_h, ctx->s_out, false)) != cudaSuccess)
+                            return bail(cuda_fail(e, "device to host copy"));
+                    }
+                    cudaEventRecord(ctx->ev_out[slot], ctx->s_out);
                 }
-                cudaStream_t kernel_after = ctx->s_in;
-                if (direction == 0) {
-                    if ((e = copy_rows(a, rm_ptr, (uint64_t)nb * full.tile_h, ctx->s_in, true)) != cudaSuccess)
-                        return cuda_fail(e, "host to device copy");
-                } else if (!q_on_device) {
-                    if ((e = cudaMemcpyAsync(b, q_ptr, q_len, cudaMemcpyHostToDevice, ctx->s_in)) != cudaSuccess)
-                        return cuda_fail(e, "host to device copy");
-                }
-                (void)kernel_after;
-                cudaEventRecord(ctx->ev_in[slot], ctx->s_in);
-                cudaStreamWaitEvent(ctx->s_comp, ctx->ev_in[slot], 0);
-                if (direction == 0) {
-                    srcs[0] = a; dsts[0] = b;
-                    if (int rc = tilize_device(1, srcs, rm_df, sshape, sstr, &sg, q_df, with_header, dsts, q_len, ctx->s_comp, -1))
-                        return rc;
-                } else {
-                    srcs[0] = b; dsts[0] = a;
-                    if (int rc = untilize_device(1, srcs, q_df, with_header, &sg, dsts, rm_df, sshape, sstr, ctx->s_comp, -1))
-                        return rc;
-                }
-                cudaEventRecord(ctx->ev_comp[slot], ctx->s_comp);
-                cudaStreamWaitEvent(ctx->s_out, ctx->ev_comp[slot], 0);
-                if (direction == 0) {
-                    if (!q_on_device && (e = cudaMemcpyAsync(q_ptr, b, q_len, cudaMemcpyDeviceToHost, ctx->s_out)) != cudaSuccess)
-                        return cuda_fail(e, "device to host copy");
-                } else {
-                    if ((e = copy_rows(a, rm_ptr, (uint64_t)nb * full.tile_h, ctx->s_out, false)) != cudaSuccess)
-                        return cuda_fail(e, "device to host copy");
-                }
-                cudaEventRecord(ctx->ev_out[slot], ctx->s_out);
             }
         }
     }
-    }
-    if ((e = cudaStreamSynchronize(ctx->s_out)) != cudaSuccess) return cuda_fail(e, "synchronize");
-    if ((e = cudaStreamSynchronize(ctx->s_comp)) != cudaSuccess) return cuda_fail(e, "synchronize");
-    if ((e = cudaStreamSynchronize(ctx->s_in)) != cudaSuccess) return cuda_fail(e, "synchronize");
+    if (cudaError_t e = drain()) return cuda_fail(e, "synchronize");
     return status_after_sync(ctx);
+}
+
+// n tensors of one shape and geometry (rm_hosts[i] <-> q_ptrs[i])
+int host_pipeline_n(int direction, int n, const void *const *rm_hosts, int rm_df, const uint32_t shape[4], const uint64_t strides[4],
+                    const buda_queue_geom *geom, int q_df, int with_header, const void *const *q_ptrs, uint64_t q_bytes,
+                    int q_on_device, uint32_t slots, uint32_t slot0)
+{
+    if (n <= 0) return BUDA_SUCCESS;
+    if (!rm_hosts || !q_ptrs) return fail(BUDA_RUNTIME_ERROR, "null buffer table");
+    if (!shape || !strides || !geom) return fail(BUDA_RUNTIME_ERROR, "null shape / strides / geometry");
+    std::vector<HostItem> items((size_t)n);
+    for (int i = 0; i < n; i++) items[(size_t)i] = HostItem{rm_hosts[i], q_ptrs[i], shape, strides, geom, q_bytes, slots, slot0};
+    return host_pipeline_items(direction, n, items.data(), rm_df, q_df, with_header, q_on_device);
 }
 
 int host_pipeline(int direction, const void *rm_host, int rm_df, const uint32_t shape[4], const uint64_t strides[4],
@@ -534,6 +662,67 @@ int host_pipeline(int direction, const void *rm_host, int rm_df, const uint32_t 
     const void *rms[1] = {rm_host};
     const void *qs[1] = {q};
     return host_pipeline_n(direction, 1, rms, rm_df, shape, strides, geom, q_df, with_header, qs, q_bytes, q_on_device, slots, slot0);
+}
+
+// n tensors with their own shapes through the general kernel flavour: aligned ones share launches of up to kMaxGen
+// table entries; a tensor whose rows are not 16-byte aligned (or that has tiny tiles) gets a launch of the direct kernel.
+int jobs_device(int direction, int n, const buda_tensor_job *jobs, int rm_df, int q_df, int with_header, cudaStream_t stream)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    if (n <= 0) return BUDA_SUCCESS;
+    if (!jobs) return fail(BUDA_RUNTIME_ERROR, "null job table");
+    int mant, es;
+    if (int rc = classify(rm_df, q_df, mant, es, direction == 1)) return rc;
+    const int a_format = is_bfp_a(q_df) ? 1 : 0;
+    const BfpPolicy pol = current_policy();
+    GenTable *tab = new GenTable;
+    tab->n = 0;
+    tab->pad = 0;
+    TileJob common;
+    memset(&common, 0, sizeof(common));
+    int rc = BUDA_SUCCESS;
+    auto flush = [&]() -> int {
+        if (tab->n == 0) return BUDA_SUCCESS;
+        cudaError_t e = direction == 0 ? launch_tilize_table(common, *tab, mant, es, a_format, ctx->sm_count, stream, ctx->status)
+                                       : launch_untilize_table(common, *tab, mant, es, a_format, ctx->sm_count, stream, ctx->status);
+        tab->n = 0;
+        if (e != cudaSuccess) return cuda_fail(e, "job table launch failed");
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return BUDA_SUCCESS;
+    };
+    for (int i = 0; i < n && rc == BUDA_SUCCESS; i++) {
+        const buda_tensor_job &jb = jobs[i];
+        if (!jb.tensor || !jb.image) { rc = fail(BUDA_RUNTIME_ERROR, "null tensor pointer in job %d", i); break; }
+        TileJob j;
+        if ((rc = make_job(jb.shape, jb.strides_bytes, &jb.geom, q_df, with_header, 1, j, jb.slots, jb.first_slot))) break;
+        if (jb.strides_bytes[3] != (uint64_t)es) { rc = fail(BUDA_RUNTIME_ERROR, "innermost stride must equal the element size (%d)", es); break; }
+        const uint64_t need = j.buf_bytes * jb.geom.grid_r * jb.geom.grid_c;
+        if (jb.image_bytes < need) {
+            rc = fail(BUDA_RUNTIME_ERROR, "job %d: image buffer holds %llu bytes, the queue image needs %llu", i,
+                      (unsigned long long)jb.image_bytes, (unsigned long long)need);
+            break;
+        }
+        if (!aligned16((uint64_t)jb.image)) { rc = fail(BUDA_RUNTIME_ERROR, "queue image pointers must be 16-byte aligned"); break; }
+        PtrTable pt;
+        memset(&pt, 0, sizeof(pt));
+        pt.src[0] = (const uint8_t *)(direction == 0 ? jb.tensor : jb.image);
+        pt.dst[0] = (uint8_t *)(direction == 0 ? jb.image : const_cast<void *>(jb.tensor));
+        int path, vec_ok;
+        pick_path(j, pt, 1, es, path, vec_ok);
+        if (path == 0) {
+            common = j;
+            common.pol = pol;
+            if ((rc = fill_entry(j, jb.tensor, jb.image, jb.band_first, jb.band_step, jb.band_count, tab->e[tab->n]))) break;
+            if (++tab->n == (uint32_t)kMaxGen) rc = flush();
+        } else {
+            if (jb.band_count != 0) { rc = fail(BUDA_RUNTIME_ERROR, "job %d: a selection of tile rows needs 16-byte aligned rows and 32-row tiles", i); break; }
+            rc = launch_uniform(direction, ctx, j, pt, 1, mant, es, a_format, 1, vec_ok, stream);
+        }
+    }
+    if (rc == BUDA_SUCCESS) rc = flush();
+    delete tab;
+    return rc;
 }
 
 }  // namespace
@@ -775,9 +964,76 @@ int buda_queue_read_stacked(const void *queue_base, int src_df, int with_header,
     int path, vec_ok;
     pick_path(job, pt, 1, es, path, vec_ok);
     if (((job.stride_z | job.stride_z_mid | job.stride_z_out) & 15u) != 0) path = 1, vec_ok = 0;
-    cudaError_t e = launch_untilize(job, pt, 1, mant, es, is_bfp_a(src_df) ? 1 : 0, path, vec_ok, ctx->sm_count, (cudaStream_t)stream, ctx->status);
-    if (e != cudaSuccess) return cuda_fail(e, "untilize launch failed");
-    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return launch_uniform(1, ctx, job, pt, 1, mant, es, is_bfp_a(src_df) ? 1 : 0, path, vec_ok, (cudaStream_t)stream);
+}
+
+int buda_tilize_pack_jobs(int n, const buda_tensor_job *jobs_host, int src_df, int dst_df, int with_header, void *stream)
+{
+    return jobs_device(0, n, jobs_host, src_df, dst_df, with_header, (cudaStream_t)stream);
+}
+
+int buda_unpack_untilize_jobs(int n, const buda_tensor_job *jobs_host, int src_df, int with_header, int dst_df, void *stream)
+{
+    return jobs_device(1, n, jobs_host, dst_df, src_df, with_header, (cudaStream_t)stream);
+}
+
+static int host_jobs(int direction, int n, const buda_tensor_job *jobs, int rm_df, int q_df, int with_header, int image_on_device)
+{
+    if (n <= 0) return BUDA_SUCCESS;
+    if (!jobs) return fail(BUDA_RUNTIME_ERROR, "null job table");
+    std::vector<HostItem> items((size_t)n);
+    for (int i = 0; i < n; i++) {
+        if (jobs[i].band_count != 0) return fail(BUDA_RUNTIME_ERROR, "job %d: the host-buffer entry points convert whole tensors", i);
+        items[(size_t)i] = HostItem{jobs[i].tensor, jobs[i].image, jobs[i].shape, jobs[i].strides_bytes, &jobs[i].geom,
+                                    jobs[i].image_bytes, image_on_device ? jobs[i].slots : 0u, image_on_device ? jobs[i].first_slot : 0u};
+    }
+    return host_pipeline_items(direction, n, items.data(), rm_df, q_df, with_header, image_on_device ? 1 : 0);
+}
+
+int buda_tilize_pack_host_jobs(int n, const buda_tensor_job *jobs_host, int src_df, int dst_df, int with_header, int image_on_device,
+                               void *stream)
+{
+    (void)stream;
+    return host_jobs(0, n, jobs_host, src_df, dst_df, with_header, image_on_device);
+}
+
+int buda_unpack_untilize_host_jobs(int n, const buda_tensor_job *jobs_host, int src_df, int with_header, int dst_df,
+                                   int image_on_device, void *stream)
+{
+    (void)stream;
+    return host_jobs(1, n, jobs_host, dst_df, src_df, with_header, image_on_device);
+}
+
+int buda_set_bfp_policy(const buda_bfp_policy *policy)
+{
+    buda_bfp_policy pub = {0, 0, {0, 1, 2, 3}, 0, 0};
+    if (policy) pub = *policy;
+    if (pub.rounding > 1 || pub.overflow > 1 || pub.exponent_order > 1 || pub.datum_order > 1)
+        return fail(BUDA_RUNTIME_ERROR, "unknown block-float policy value");
+    BfpPolicy p = default_policy();
+    bool seen[4] = {false, false, false, false};
+    for (int pos = 0; pos < 4; pos++) {
+        const unsigned f = pub.face_order[pos];
+        if (f > 3 || seen[f]) return fail(BUDA_RUNTIME_ERROR, "face_order must be a permutation of 0, 1, 2, 3");
+        seen[f] = true;
+        p.face_at[pos] = (uint8_t)f;
+        p.face_pos[f] = (uint8_t)pos;
+    }
+    p.trunc = (uint8_t)pub.rounding;
+    p.bump = (uint8_t)pub.overflow;
+    p.exp_be = (uint8_t)pub.exponent_order;
+    p.datum_be = (uint8_t)pub.datum_order;
+    std::lock_guard<std::mutex> lock(g_policy_mu);
+    g_policy = p;
+    g_policy_public = pub;
+    return BUDA_SUCCESS;
+}
+
+int buda_get_bfp_policy(buda_bfp_policy *policy_out)
+{
+    if (!policy_out) return fail(BUDA_RUNTIME_ERROR, "null argument");
+    std::lock_guard<std::mutex> lock(g_policy_mu);
+    *policy_out = g_policy_public;
     return BUDA_SUCCESS;
 }
 
@@ -922,6 +1178,13 @@ int buda_bfp8b_gemm_scatter(const void *A, int64_t M, int64_t K, int64_t lda, co
     DevCtx *ctx;
     if (int rc = get_ctx(&ctx)) return rc;
     if (!A || !W_tiles || !C_dsts) return fail(BUDA_RUNTIME_ERROR, "null matrix pointer");
+    {
+        const BfpPolicy pol = current_policy();
+        BfpPolicy layout = pol;
+        layout.trunc = layout.bump = 0;   // rounding and overflow do not change how bytes are read back
+        if (!policy_is_default(layout))
+            return fail(BUDA_RUNTIME_ERROR, "the matmul reads weight images in the default byte layout; the current block-float policy changes it");
+    }
     for (int d = 0; d < n_dst && d < 8; d++)
         if (!C_dsts[d]) return fail(BUDA_RUNTIME_ERROR, "null destination %d", d);
     char msg[256] = "";
@@ -946,6 +1209,8 @@ int buda_i8_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W
     DevCtx *ctx;
     if (int rc = get_ctx(&ctx)) return rc;
     if (!A || !W_tiles || !C) return fail(BUDA_RUNTIME_ERROR, "null matrix pointer");
+    if (current_policy().face_pos[1] != 1 || current_policy().face_pos[2] != 2)
+        return fail(BUDA_RUNTIME_ERROR, "the matmul reads weight images in the default face order; the current policy changes it");
     char msg[256] = "";
     cudaError_t e = launch_i8_gemm(A, M, K, lda, W_tiles, N, scale, scale_len, zero_point, out_mode, C, ldc, ctx->sm_count,
                                    (cudaStream_t)stream, ctx->status, msg, sizeof(msg));
@@ -987,21 +1252,6 @@ int buda_selftest_bounded_wait(uint32_t limit_ms, void *stream)
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "self-test launch failed");
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    return BUDA_SUCCESS;
-}
-
-int buda_stream_probe(int mix, int schedule, uint64_t elements, int reps, float *ms_out, void *stream)
-{
-    DevCtx *ctx;
-    if (int rc = get_ctx(&ctx)) return rc;
-    if (!ms_out) return fail(BUDA_RUNTIME_ERROR, "null result pointer");
-    if (mix < 0 || mix > 3 || schedule < 0 || schedule > 2) return fail(BUDA_RUNTIME_ERROR, "mix %d / schedule %d out of range", mix, schedule);
-    if (reps < 1 || reps > 1000) return fail(BUDA_RUNTIME_ERROR, "%d repetitions is outside 1..1000", reps);
-    if (elements == 0 || elements % 131072u || elements > (1ull << 30))
-        return fail(BUDA_RUNTIME_ERROR, "element count %llu is not a multiple of 131072 up to 2^30", (unsigned long long)elements);
-    cudaError_t e = run_stream_probe(mix, schedule, elements, reps, ctx->sm_count, (cudaStream_t)stream, ms_out);
-    if (e != cudaSuccess) return cuda_fail(e, "stream probe failed");
-    g_launches.fetch_add((uint64_t)reps + 2, std::memory_order_relaxed);
     return BUDA_SUCCESS;
 }
 
@@ -1148,14 +1398,23 @@ extern "C" int buda_tilize_pack_host_noalloc(const void *src_host, int src_df, c
                     : cudaMemcpy2DAsync(d, row_bytes, h, strides_bytes[2], row_bytes, shape[2], cudaMemcpyHostToDevice, s);
         }
     }
-    if (e != cudaSuccess) return cuda_fail(e, "host to device copy");
+    // From here on work may be in flight on the shared array: every way out waits for the stream first, so the next
+    // caller (possibly on another stream) never meets it.
+    if (e != cudaSuccess) {
+        (void)cudaStreamSynchronize(s);
+        return cuda_fail(e, "host to device copy");
+    }
     // the kernel writes every byte of every tile record (header included), so nothing left in the
     // array by an earlier call can show through and nothing has to be cleared first
     const void *srcs[1] = {d_src};
     void *dsts[1] = {d_img};
-    if (int rc = tilize_device(1, srcs, src_df, shape, dense, geom, dst_df, with_header, dsts, image_bytes, s, -1)) return rc;
-    if ((e = cudaMemcpyAsync(dst_host, d_img, image_bytes, cudaMemcpyDeviceToHost, s)) != cudaSuccess)
-        return cuda_fail(e, "device to host copy");
-    if ((e = cudaStreamSynchronize(s)) != cudaSuccess) return cuda_fail(e, "synchronize");
+    if (int rc = tilize_device(1, srcs, src_df, shape, dense, geom, dst_df, with_header, dsts, image_bytes, s, -1)) {
+        (void)cudaStreamSynchronize(s);
+        return rc;
+    }
+    e = cudaMemcpyAsync(dst_host, d_img, image_bytes, cudaMemcpyDeviceToHost, s);
+    const cudaError_t es2 = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return cuda_fail(e, "device to host copy");
+    if (es2 != cudaSuccess) return cuda_fail(es2, "synchronize");
     return status_after_sync(ctx);
 }

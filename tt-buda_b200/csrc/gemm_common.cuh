@@ -117,37 +117,19 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t ran
 // measured to add roughly 0.4 us to every k-block of the pair kernel's issue loop.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
 {
-#ifdef PAIR_STRICT_SCOPE
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-#else
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-#endif
 }
 
 __device__ __forceinline__ bool mbar_try_wait_parked_cluster(uint64_t *bar, uint32_t parity, uint32_t hint_ns)
 {
-#ifdef PAIR_STRICT_SCOPE
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
-        : "memory");
-    return ok != 0;
-#else
     return mbar_try_wait_parked(bar, parity, hint_ns);
-#endif
 }
 
 // Bounded wait on a barrier whose arrivals come from both CTAs of a pair.
 __device__ __forceinline__ bool mbar_wait_bounded_cluster(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
                                                           unsigned int *status, unsigned int code)
 {
-#ifndef PAIR_STRICT_SCOPE
     if (mbar_try_wait(bar, parity)) return true;
-#endif
     const uint64_t t0 = global_timer_ns();
     while (true) {
         if (mbar_try_wait_parked_cluster(bar, parity, 20000u)) return true;

@@ -48,17 +48,11 @@ constexpr int kPairM = 512;        // rows of C per pair tile
 constexpr int kBN = 256;           // columns of C per pair tile
 constexpr int kHalfN = 128;        // weight columns decoded by one CTA
 constexpr int kBKBytes = 128;      // k-block: one 128-byte swizzled row of K (64 bfloat16 / 128 int8)
-#ifndef PAIR_B_STAGES
-#define PAIR_B_STAGES 4
-#endif
-constexpr int kBStages = PAIR_B_STAGES;   // decoded-weight ring (per CTA: 128 columns x 64 deep)
+constexpr int kBStages = 4;   // decoded-weight ring (per CTA: 128 columns x 64 deep)
 constexpr int kABytes = 2 * 128 * kBKBytes;  // 32768
 constexpr int kBBytes = kHalfN * kBKBytes;   // 16384
 constexpr int kDecodeWarps = 8;
-#ifndef GEMM_PREFETCH
-#define GEMM_PREFETCH 3
-#endif
-constexpr int kPrefetch = GEMM_PREFETCH;   // k-blocks of raw weight records in flight per decode thread
+constexpr int kPrefetch = 3;   // k-blocks of raw weight records in flight per decode thread
 constexpr int kEpiWarps = 8;        // two per tensor-memory lane quadrant: each takes half of the columns
 constexpr int kProducerWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1, kFirstDecodeWarp = kEpiWarps + 2;
 constexpr int kThreads = 32 * (kEpiWarps + 1 + 1 + kDecodeWarps);
@@ -204,13 +198,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         ok = false;
                         break;
                     }
-#ifndef GEMM_EXP_NO_A
                     mbar_arrive_expect_tx(&full_a[s], kABytes);
                     tma_load_2d(sA + s * kABytes, &tmap_a, (int)(kb * kBK), row0, &full_a[s]);
                     tma_load_2d(sA + s * kABytes + kABytes / 2, &tmap_a, (int)(kb * kBK), row0 + 256, &full_a[s]);
-#else
-                    mbar_arrive(&full_a[s]);
-#endif
                 }
             }
             const uint32_t back = i < (uint32_t)kAStages ? i : (uint32_t)kAStages;
@@ -259,11 +249,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                             const uint64_t adesc = smem_desc(a_addr + h * (kABytes / 2) + j * 32, 16, 1024);
                             // B (this CTA's 128 columns, N-major): 32 bytes of K = 4096 B of the stage per step
                             const uint64_t bdesc = smem_desc(b_addr + j * 4096, KT::kBLbo, KT::kBSbo);
-#ifndef PAIR_EXP_NO_MMA
                             umma_pair<Kind>(tmem_base + h * kBN, adesc, bdesc, KT::kIdesc, (kb > 0 || j > 0) ? 1u : 0u);
-#else
-                            (void)adesc; (void)bdesc;
-#endif
                         }
                     }
                     umma_commit_pair(&empty_a[s]);
@@ -356,10 +342,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     break;
                 }
                 uint8_t *bst = sB + t * kBBytes;
-#ifdef PAIR_EXP_NO_DECODE
-                if (exp_cur[0] == 0x12345u) bst[lane] = (uint8_t)mant_cur[0].x;
-                if (false)
-#endif
 #pragma unroll
                 for (int it = 0; it < kUnits; it++) {
                     const int u = it * kDecodeWarps + dw;
@@ -411,11 +393,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     tmem_ld32_issue(taddr + c * 64, v0);
                     tmem_ld32_issue(taddr + c * 64 + 32, v1);
                     tmem_ld_wait();
-#ifdef PAIR_EXP_NO_STORE
-                    if (row < p.M && v0[0] == 0x7fc12345u)
-#else
                     if (row < p.M)
-#endif
                     {
                         if constexpr (Kind == kKindBfp8) {
                             // this device's copy: straight from registers
@@ -503,7 +481,6 @@ cudaError_t launch_pair(const CUtensorMap &tmap, const gemm::Params &p_in, int s
             n = sm_count / 2;
         }
         resident = n;
-        if (getenv("BUDA_GEMM_VERBOSE")) fprintf(stderr, "gemm pair kernel (kind %d): %d resident CTA pairs on %d SMs\n", Kind, n, sm_count);
         max_pairs[dev].store(n, std::memory_order_release);
     }
     gemm::Params p = p_in;

@@ -19,10 +19,14 @@
 //     Four lanes own one block: each loads 4 values (one 128-bit load when aligned), the shared
 //     exponent is a 4-lane-wide warp-shuffle maximum, and a warp covers 8 consecutive rows of one
 //     face so its stores form one contiguous run of the record.
+// Each kernel exists in two flavours (template flag G).  The plain one serves a batch of tensors of one shape with the
+// default byte layout.  The general one takes a table with one entry per tensor (own shape, strides, queue geometry,
+// selection of tile rows) and honours a layout policy (rounding, overflow, face / exponent / datum order).
 #include "bfp_codec.cuh"
 #include <atomic>
 
 #include "buda_common.cuh"
+#include "work_slots_cuda.cuh"
 
 namespace buda {
 
@@ -46,11 +50,7 @@ struct PackCfg {
     static constexpr int payload = (M > 0) ? (64 + 1024 * (M + 1) / 8) : (1024 * ES);
     static constexpr int rec_max = payload + 32;
     static constexpr int out_buf_bytes = box * rec_max;
-#ifdef BUDA_PACK_STAGES
-    static constexpr int stages = BUDA_PACK_STAGES;
-#else
     static constexpr int stages = 2;  // depth comes from the CTAs resident per SM, not from stages per CTA
-#endif
     static constexpr int smem_bytes = stages * in_stage_bytes + 2 * out_buf_bytes + stages * (int)sizeof(ItemMeta) +
                                       2 * stages * 8 + 16;
 };
@@ -69,12 +69,33 @@ __device__ __forceinline__ void decode_item(const TileJob &job, uint32_t item, I
     m.ntiles = min(job.box_tiles, job.Ct - m.ct0);
 }
 
-static __device__ WorkCounter g_pack_work[kWorkSlots];
-static std::atomic<unsigned> g_next_work_slot{0};   // host side: the counter the next staged launch takes
+// General flavour: work item -> table entry (cursor `cur` only moves forward: a CTA's items come in increasing order),
+// then the position inside that tensor's selection of tile rows.
+__device__ __forceinline__ void decode_item_gen(const GenTable &tab, const TileJob &common, uint32_t item, uint32_t &cur, ItemMeta &m)
+{
+    while (cur + 1u < tab.n && item >= tab.e[cur + 1u].item_start) cur++;
+    const GenEntry &e = tab.e[cur];
+    uint32_t q = item - e.item_start;
+    const uint32_t cb = q % e.boxes_per_band;
+    q /= e.boxes_per_band;
+    const uint32_t k = q % e.bands;
+    q /= e.bands;
+    m.rt = e.band_first + k * e.band_step;
+    m.z = q % e.Z;
+    m.w = q / e.Z;
+    m.b = cur;
+    m.ct0 = cb * common.box_tiles;
+    m.ntiles = min(common.box_tiles, e.Ct - m.ct0);
+}
 
-template <int M, int ES, bool AF>
+static __device__ WorkCounter g_pack_work[kWorkSlots];
+
+template <bool G> struct TableOf { using type = PtrTable; };
+template <> struct TableOf<true> { using type = GenTable; };
+
+template <int M, int ES, bool AF, bool G>
 __global__ void __launch_bounds__(kStagedThreads)
-pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ PtrTable ptrs, unsigned int *status)
+pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ typename TableOf<G>::type ptrs, unsigned int *status)
 {
     using Cfg = PackCfg<M, ES>;
     constexpr int S = Cfg::stages;
@@ -105,7 +126,7 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
     if (warp == kConsumerWarps) {
         // ---------------------------------------------------------------- producer warp
         WorkCounter *wc = &g_pack_work[job.work_slot];
-        uint32_t it = 0;
+        uint32_t it = 0, cur = 0;
         bool ok = true;
         uint32_t item = work_fetch_get(work_fetch_issue(wc, lane));
         for (; item < job.total_items; ++it) {
@@ -117,15 +138,23 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
                 break;
             }
             ItemMeta m;
-            decode_item(job, item, m);
+            const uint8_t *src;
+            if constexpr (G) {
+                decode_item_gen(ptrs, job, item, cur, m);
+                const GenEntry &e = ptrs.e[m.b];
+                src = e.rm + (uint64_t)m.w * e.stride_w + (uint64_t)m.z * e.stride_z + ((uint64_t)m.rt * 32u + lane) * e.stride_r +
+                      (uint64_t)m.ct0 * 32u * ES;
+            } else {
+                decode_item(job, item, m);
+                src = ptrs.src[m.b] + (uint64_t)m.w * job.stride_w + rm_z_offset(job, m.z) +
+                      ((uint64_t)m.rt * 32u + lane) * job.stride_r + (uint64_t)m.ct0 * 32u * ES;
+            }
             const uint32_t row_copy = m.ntiles * 32u * ES;
             if (lane == 0) {
                 meta[s] = m;
                 mbar_arrive_expect_tx(&full[s], 32u * row_copy);
             }
             __syncwarp();
-            const uint8_t *src = ptrs.src[m.b] + (uint64_t)m.w * job.stride_w + rm_z_offset(job, m.z) +
-                                 ((uint64_t)m.rt * 32u + lane) * job.stride_r + (uint64_t)m.ct0 * 32u * ES;
             bulk_g2s(in_stage + s * Cfg::in_stage_bytes + lane * Cfg::pitch, src, row_copy, &full[s]);
             item = work_fetch_get(next_issued);
         }
@@ -188,7 +217,14 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
                 } else {
                     const uint4 v0 = *reinterpret_cast<const uint4 *>(p), v1 = *reinterpret_cast<const uint4 *>(p + 16);
                     const uint32_t h[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-                    if (!AF) encoded = bfp_encode16_bf16<MM>(h, E, d);   // packed-pair encoder; false at the ends of the exponent range
+                    // packed-pair encoder; false at the ends of the exponent range
+                    if (!AF && (!G || !(job.pol.trunc | job.pol.bump))) {
+                        encoded = bfp_encode16_bf16<MM>(h, E, d);
+                        if (G && encoded && job.pol.datum_be) {
+#pragma unroll
+                            for (int w = 0; w < BfpTraits<MM>::words; w++) d[w] = reverse_datum_fields<MM>(d[w]);
+                        }
+                    }
                     if (!encoded) {
 #pragma unroll
                         for (int k = 0; k < 8; k++) {
@@ -202,10 +238,13 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
                         }
                     }
                 }
-                if (!encoded) bfp_encode16<MM>(x, E, d);
+                if (!encoded) {
+                    if constexpr (G) bfp_encode16_policy<MM>(x, E, d, job.pol, AF ? 143u : 255u);
+                    else bfp_encode16<MM>(x, E, d);
+                }
                 uint8_t *r = ob + tile_in_box * rec + hdr;
-                const int blk = face * 16 + fr;
-                r[blk] = (uint8_t)(AF ? a_exponent_byte(E) : E);
+                const int blk = (G ? (int)job.pol.face_pos[face] : face) * 16 + fr;
+                r[(G && job.pol.exp_be) ? (blk ^ 3) : blk] = (uint8_t)(AF ? a_exponent_byte(E) : E);
                 uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
                 if (MM == 7) *reinterpret_cast<uint4 *>(q) = make_uint4(d[0], d[1 % BfpTraits<MM>::words], d[2 % BfpTraits<MM>::words], d[3 % BfpTraits<MM>::words]);
                 else if (MM == 3) *reinterpret_cast<uint2 *>(q) = make_uint2(d[0], d[1 % BfpTraits<MM>::words]);
@@ -220,7 +259,8 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
             const int nchunks = (int)m.ntiles * chunks_per_tile;
             for (int c = tid; c < nchunks; c += kConsumerThreads) {
                 const int t = c / chunks_per_tile, k = c % chunks_per_tile;
-                const int f = k / (16 * cpr), r16 = (k / cpr) % 16, part = k % cpr;
+                const int r16 = (k / cpr) % 16, part = k % cpr;
+                const int f = G ? (int)job.pol.face_at[k / (16 * cpr)] : k / (16 * cpr);   // the face stored at this position
                 const int row = (f >> 1) * 16 + r16;
                 const uint4 v = *reinterpret_cast<const uint4 *>(stage + row * Cfg::pitch + t * 32 * ES +
                                                                  (f & 1) * 16 * ES + part * 16);
@@ -232,7 +272,14 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
         if (named_bar_or(1, kConsumerThreads, !ok)) break;
         if (tid == 0) mbar_arrive(&empty[s]);
         if (warp == 0 && (uint32_t)lane < m.ntiles) {
-            uint8_t *dst = ptrs.dst[m.b] + tile_record_offset(job, m.w, m.z, m.rt, m.ct0 + lane);
+            uint8_t *dst;
+            if constexpr (G) {
+                TileJob ej;
+                job_of_entry(job, ptrs.e[m.b], ej);
+                dst = ptrs.e[m.b].q + tile_record_offset(ej, m.w, m.z, m.rt, m.ct0 + lane);
+            } else {
+                dst = ptrs.dst[m.b] + tile_record_offset(job, m.w, m.z, m.rt, m.ct0 + lane);
+            }
             bulk_s2g(dst, ob + lane * rec, rec);
             bulk_commit();
         }
@@ -260,18 +307,20 @@ __device__ __forceinline__ uint32_t absmax4_bits(const uint32_t (&x)[4])
 
 // The exponents next to 0 and 255, where the scale of the fast path is not a normal float: integer arithmetic,
 // kept out of line because almost no block takes it.
-__device__ __noinline__ uint32_t encode4_any_exp(uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3, uint32_t E, int m)
+__device__ __noinline__ uint32_t encode4_any_exp(uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3, uint32_t E, int m,
+                                                 bool trunc = false, bool *over = nullptr)
 {
-    return bfp_encode_datum_int(x0, E, m) | (bfp_encode_datum_int(x1, E, m) << (m + 1)) |
-           (bfp_encode_datum_int(x2, E, m) << (2 * (m + 1))) | (bfp_encode_datum_int(x3, E, m) << (3 * (m + 1)));
+    return bfp_encode_datum_int(x0, E, m, trunc, over) | (bfp_encode_datum_int(x1, E, m, trunc, over) << (m + 1)) |
+           (bfp_encode_datum_int(x2, E, m, trunc, over) << (2 * (m + 1))) | (bfp_encode_datum_int(x3, E, m, trunc, over) << (3 * (m + 1)));
 }
 
 // Four data of one block, shared exponent E already known, packed at (M + 1) bits each.  In the usual exponent
 // range the magnitudes come out of one fused multiply-add each (round to nearest even into the low bits of
 // 1.5 * 2^23) and everything after it works on the four data at once, one byte each: saturation is per element,
 // then the sign bits are gathered with byte permutes and dropped where the magnitude is zero.
+// trunc / over: general flavour only (truncation instead of rounding; *over reports a finite magnitude above the largest).
 template <int M>
-__device__ __forceinline__ uint32_t encode4_shared_exp(const uint32_t (&x)[4], uint32_t E)
+__device__ __forceinline__ uint32_t encode4_shared_exp(const uint32_t (&x)[4], uint32_t E, bool trunc = false, bool *over = nullptr)
 {
     constexpr uint32_t qmax = BfpTraits<M>::qmax;
     const bool fast = (E + 1u >= (uint32_t)M) && (E <= (uint32_t)(M + 252));
@@ -280,10 +329,9 @@ __device__ __forceinline__ uint32_t encode4_shared_exp(const uint32_t (&x)[4], u
         uint32_t r[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            float f;
-            asm("{\n\t.reg .f32 t;\n\tabs.ftz.f32 t, %1;\n\tfma.rn.ftz.f32 %0, t, %2, %3;\n\t}"
-                : "=f"(f) : "f"(__uint_as_float(x[i])), "f"(S), "f"(12582912.0f));
-            r[i] = min(__float_as_uint(f), kMagicBits + qmax);   // low byte = magnitude (the constant's low byte is 0)
+            const uint32_t y = trunc ? bfp_quantise_bits<true>(x[i], S) : bfp_quantise_bits<false>(x[i], S);
+            if (over && y > kMagicBits + qmax) *over = true;
+            r[i] = min(y, kMagicBits + qmax);   // low byte = magnitude (the constant's low byte is 0)
         }
         const uint32_t Q = __byte_perm(__byte_perm(r[0], r[1], 0x0040), __byte_perm(r[2], r[3], 0x0040), 0x5410);
         const uint32_t SG = __byte_perm(__byte_perm(x[0], x[1], 0x0073), __byte_perm(x[2], x[3], 0x0073), 0x5410);
@@ -298,7 +346,7 @@ __device__ __forceinline__ uint32_t encode4_shared_exp(const uint32_t (&x)[4], u
         const uint32_t t = D | (D >> 6);
         return (t | (t >> 12)) & 0xffu;
     }
-    return encode4_any_exp(x[0], x[1], x[2], x[3], E, M);
+    return encode4_any_exp(x[0], x[1], x[2], x[3], E, M, trunc, over);
 }
 
 template <int ES>
@@ -334,13 +382,10 @@ __device__ __forceinline__ void load4(const uint8_t *p, bool vec, uint32_t (&x)[
     }
 }
 
-#ifndef PACK_DIRECT_GROUP
-#define PACK_DIRECT_GROUP 8
-#endif
-
 // Encode (or relayout) the four elements a lane holds of block `blk` and store them into tile record `r`.
-template <int M, int ES, bool AF>
-__device__ __forceinline__ void direct_encode_store(uint32_t (&x)[4], uint32_t blk, uint8_t *r, int lane)
+// blk is the block's position in the record (face position * 16 + face row).
+template <int M, int ES, bool AF, bool G>
+__device__ __forceinline__ void direct_encode_store(uint32_t (&x)[4], uint32_t blk, uint8_t *r, int lane, const BfpPolicy &pol)
 {
     if (M > 0) {
         constexpr int MM = M > 0 ? M : 7;
@@ -351,13 +396,36 @@ __device__ __forceinline__ void direct_encode_store(uint32_t (&x)[4], uint32_t b
         uint32_t mx = absmax4_bits(x);
         mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 1, 4));
         mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 2, 4));
-        const uint32_t E = mx >> 23;
-        const uint32_t packed = encode4_shared_exp<MM>(x, E);
-        if ((lane & 3) == 0) r[blk] = (uint8_t)(AF ? a_exponent_byte(E) : E);
+        uint32_t E = mx >> 23;
+        uint32_t packed;
+        if constexpr (G) {
+            bool over = false;
+            packed = encode4_shared_exp<MM>(x, E, pol.trunc != 0, &over);
+            // the block spans four lanes: any of them rounding up raises the exponent for all
+            uint32_t ov = over ? 1u : 0u;
+            ov |= __shfl_xor_sync(0xffffffffu, ov, 1, 4);
+            ov |= __shfl_xor_sync(0xffffffffu, ov, 2, 4);
+            if (pol.bump && ov && E < (AF ? 143u : 255u)) {
+                E += 1u;
+                packed = encode4_any_exp(x[0], x[1], x[2], x[3], E, MM, pol.trunc != 0);
+            }
+        } else {
+            packed = encode4_shared_exp<MM>(x, E);
+        }
+        int part = lane & 3;
+        if (G && pol.datum_be) {
+            // the lane's four datums in reverse order; which quarter of which word they land in is reversed as well
+            if (MM == 7) packed = __byte_perm(packed, 0u, 0x0123);
+            else if (MM == 3) packed = ((packed & 0xfu) << 12) | ((packed & 0xf0u) << 4) | ((packed >> 4) & 0xf0u) | ((packed >> 12) & 0xfu);
+            else packed = ((packed & 3u) << 6) | ((packed & 0xcu) << 2) | ((packed >> 2) & 0xcu) | ((packed >> 6) & 3u);
+            if (MM == 3) part ^= 1;        // two lanes share a 32-bit word
+            else if (MM == 1) part ^= 3;   // four lanes share a 32-bit word
+        }
+        if ((lane & 3) == 0) r[(G && pol.exp_be) ? (blk ^ 3u) : blk] = (uint8_t)(AF ? a_exponent_byte(E) : E);
         uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
-        if (MM == 7) reinterpret_cast<uint32_t *>(q)[lane & 3] = packed;
-        else if (MM == 3) reinterpret_cast<uint16_t *>(q)[lane & 3] = (uint16_t)packed;
-        else q[lane & 3] = (uint8_t)packed;
+        if (MM == 7) reinterpret_cast<uint32_t *>(q)[part] = packed;
+        else if (MM == 3) reinterpret_cast<uint16_t *>(q)[part] = (uint16_t)packed;
+        else q[part] = (uint8_t)packed;
     } else {
         uint8_t *q = r + ((uint64_t)blk * 16u + (lane & 3) * 4u) * ES;
         if (ES == 4) *reinterpret_cast<uint4 *>(q) = make_uint4(x[0], x[1], x[2], x[3]);
@@ -366,7 +434,7 @@ __device__ __forceinline__ void direct_encode_store(uint32_t (&x)[4], uint32_t b
     }
 }
 
-template <int M, int ES, bool AF>
+template <int M, int ES, bool AF, bool G>
 __global__ void __launch_bounds__(256)
 pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ PtrTable ptrs, int batch, int vec_ok)
 {
@@ -375,7 +443,7 @@ pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
     const uint64_t warp_id = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const uint64_t tiles = (uint64_t)batch * job.W * job.Z * job.Rt * job.Ct;
     const uint32_t hdr = job.header_bytes;
-    constexpr int G = PACK_DIRECT_GROUP;
+    constexpr int GR = 8;   // pieces whose loads are issued before the first is encoded
     // A warp takes a whole tile per iteration: the tile's position is worked out once (the divisions by the run-time
     // tensor dims were most of the instructions when a warp took an eighth of a tile).  A tile is eight pieces of
     // 8 rows of one face (piece = face * 2 + half); with rows that allow vector loads, the loads of G pieces are
@@ -395,19 +463,20 @@ pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
         r += hdr;
         if (vec_ok) {
 #pragma unroll 1
-            for (int g = 0; g < 8; g += G) {
-                uint32_t xs[G][4];
+            for (int g = 0; g < 8; g += GR) {
+                uint32_t xs[GR][4];
 #pragma unroll
-                for (int j = 0; j < G; j++) {
+                for (int j = 0; j < GR; j++) {
                     const uint32_t face = (uint32_t)(g + j) >> 1, half = (uint32_t)(g + j) & 1u;
                     const uint32_t tr = (face >> 1) * 16u + half * 8u + (lane >> 2);   // row inside the tile
                     xs[j][0] = xs[j][1] = xs[j][2] = xs[j][3] = 0u;                    // tiny tiles: rows >= tile_h stay zero
                     if (tr < job.tile_h) load4<ES>(tile_src + (uint64_t)tr * job.stride_r + (face & 1u) * 16u * ES, true, xs[j]);
                 }
 #pragma unroll
-                for (int j = 0; j < G; j++) {
+                for (int j = 0; j < GR; j++) {
                     const uint32_t face = (uint32_t)(g + j) >> 1, half = (uint32_t)(g + j) & 1u;
-                    direct_encode_store<M, ES, AF>(xs[j], face * 16u + half * 8u + (lane >> 2), r, lane);
+                    const uint32_t pos = G ? (uint32_t)job.pol.face_pos[face] : face;
+                    direct_encode_store<M, ES, AF, G>(xs[j], pos * 16u + half * 8u + (lane >> 2), r, lane, job.pol);
                 }
             }
         } else {
@@ -417,7 +486,8 @@ pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
                 const uint32_t tr = (face >> 1) * 16u + half * 8u + (lane >> 2);
                 uint32_t x[4] = {0u, 0u, 0u, 0u};
                 if (tr < job.tile_h) load4<ES>(tile_src + (uint64_t)tr * job.stride_r + (face & 1u) * 16u * ES, false, x);
-                direct_encode_store<M, ES, AF>(x, face * 16u + half * 8u + (lane >> 2), r, lane);
+                const uint32_t pos = G ? (uint32_t)job.pol.face_pos[face] : face;
+                direct_encode_store<M, ES, AF, G>(x, pos * 16u + half * 8u + (lane >> 2), r, lane, job.pol);
             }
         }
     }
@@ -426,8 +496,10 @@ pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
 // ------------------------------------------------------------------------------------------------
 // host launchers
 // ------------------------------------------------------------------------------------------------
-template <int M, int ES, bool AF>
-static cudaError_t launch_staged(const TileJob &job, const PtrTable &ptrs, int sm_count, cudaStream_t stream,
+static DeviceWorkSlots g_pack_slots[64];   // per device: which work counter the next staged launch takes
+
+template <int M, int ES, bool AF, bool G>
+static cudaError_t launch_staged(const TileJob &job, const typename TableOf<G>::type &table, int sm_count, cudaStream_t stream,
                                  unsigned int *status)
 {
     using Cfg = PackCfg<M, ES>;
@@ -437,26 +509,37 @@ static cudaError_t launch_staged(const TileJob &job, const PtrTable &ptrs, int s
     dev &= 63;
     int per_sm = per_sm_cache[dev].load(std::memory_order_acquire);
     if (per_sm == 0) {
-        cudaError_t e = cudaFuncSetAttribute(pack_staged_kernel<M, ES, AF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(pack_staged_kernel<M, ES, AF, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Cfg::smem_bytes);
         if (e != cudaSuccess) return e;
         int n = 0;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, pack_staged_kernel<M, ES, AF>, kStagedThreads,
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, pack_staged_kernel<M, ES, AF, G>, kStagedThreads,
                                                           Cfg::smem_bytes);
         if (e != cudaSuccess) return e;
         per_sm = n < 1 ? 1 : (n > 5 ? 5 : n);
         per_sm_cache[dev].store(per_sm, std::memory_order_release);
     }
     TileJob launch_job = job;
-    if (!set_box_tiles(launch_job, Cfg::box)) return cudaErrorInvalidValue;   // more than 2^31 work items: split the batch
+    typename TableOf<G>::type launch_table = table;
+    if constexpr (G) {
+        if (!finalize_table(launch_table, launch_job, Cfg::box)) return cudaErrorInvalidValue;
+    } else {
+        if (!set_box_tiles(launch_job, Cfg::box)) return cudaErrorInvalidValue;   // more than 2^31 work items: split the batch
+    }
+    if (launch_job.total_items == 0) return cudaSuccess;
     uint32_t grid = (uint32_t)(sm_count * per_sm);
     if (grid > launch_job.total_items) grid = launch_job.total_items;
-    launch_job.work_slot = g_next_work_slot.fetch_add(1u, std::memory_order_relaxed) % kWorkSlots;
-    pack_staged_kernel<M, ES, AF><<<grid, kStagedThreads, Cfg::smem_bytes, stream>>>(launch_job, ptrs, status);
-    return cudaGetLastError();
+    bool tracked = false;
+    const int slot = take_work_slot(g_pack_slots[dev], stream, &tracked);
+    if (slot < 0) return cudaErrorLaunchOutOfResources;   // the counters reserved for graph capture are used up
+    launch_job.work_slot = (uint32_t)slot;
+    pack_staged_kernel<M, ES, AF, G><<<grid, kStagedThreads, Cfg::smem_bytes, stream>>>(launch_job, launch_table, status);
+    const cudaError_t e = cudaGetLastError();
+    work_slot_launched(g_pack_slots[dev], slot, stream, tracked);
+    return e;
 }
 
-template <int M, int ES, bool AF>
+template <int M, int ES, bool AF, bool G>
 static cudaError_t launch_direct(const TileJob &job, const PtrTable &ptrs, int batch, int vec_ok, int sm_count,
                                  cudaStream_t stream)
 {
@@ -464,31 +547,48 @@ static cudaError_t launch_direct(const TileJob &job, const PtrTable &ptrs, int b
     uint64_t blocks = (tiles + 7) / 8;
     const uint64_t cap = (uint64_t)sm_count * 32;
     if (blocks > cap) blocks = cap;
-    pack_direct_kernel<M, ES, AF><<<(unsigned)blocks, 256, 0, stream>>>(job, ptrs, batch, vec_ok);
+    pack_direct_kernel<M, ES, AF, G><<<(unsigned)blocks, 256, 0, stream>>>(job, ptrs, batch, vec_ok);
     return cudaGetLastError();
 }
 
+#define BUDA_FOR_EACH_PACK_KIND(X) \
+    X(7, 4, false) X(3, 4, false) X(1, 4, false) X(7, 2, false) X(3, 2, false) X(1, 2, false) \
+    X(7, 2, true) X(3, 2, true) X(1, 2, true) X(0, 4, false) X(0, 2, false) X(0, 1, false)
+
 // mant_bits 7/3/1 = Bfp pack, 0 = plain relayout; es = source element bytes; a_format: 5-bit shared
 // exponent with a binary16 source.  path: 0 = staged (needs 16-byte aligned rows), 1 = direct.
+// Plain flavour: a batch of tensors of one shape, default byte layout.
 cudaError_t launch_tilize(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int a_format, int path,
                           int vec_ok, int sm_count, cudaStream_t stream, unsigned int *status)
 {
-#define BUDA_DISPATCH(MM, EE, AA)                                                                  \
-    if (mant_bits == MM && es == EE && (a_format != 0) == AA)                                      \
-        return path == 0 ? launch_staged<MM, EE, AA>(job, ptrs, sm_count, stream, status)          \
-                         : launch_direct<MM, EE, AA>(job, ptrs, batch, vec_ok, sm_count, stream);
-    BUDA_DISPATCH(7, 4, false)
-    BUDA_DISPATCH(3, 4, false)
-    BUDA_DISPATCH(1, 4, false)
-    BUDA_DISPATCH(7, 2, false)
-    BUDA_DISPATCH(3, 2, false)
-    BUDA_DISPATCH(1, 2, false)
-    BUDA_DISPATCH(7, 2, true)
-    BUDA_DISPATCH(3, 2, true)
-    BUDA_DISPATCH(1, 2, true)
-    BUDA_DISPATCH(0, 4, false)
-    BUDA_DISPATCH(0, 2, false)
-    BUDA_DISPATCH(0, 1, false)
+#define BUDA_DISPATCH(MM, EE, AA)                                                                         \
+    if (mant_bits == MM && es == EE && (a_format != 0) == AA)                                             \
+        return path == 0 ? launch_staged<MM, EE, AA, false>(job, ptrs, sm_count, stream, status)          \
+                         : launch_direct<MM, EE, AA, false>(job, ptrs, batch, vec_ok, sm_count, stream);
+    BUDA_FOR_EACH_PACK_KIND(BUDA_DISPATCH)
+#undef BUDA_DISPATCH
+    return cudaErrorInvalidValue;
+}
+
+// General flavour, staged kernel: one table entry per tensor; job carries what the entries share (record size,
+// header, layout policy).
+cudaError_t launch_tilize_table(const TileJob &job, const GenTable &table, int mant_bits, int es, int a_format, int sm_count,
+                                cudaStream_t stream, unsigned int *status)
+{
+#define BUDA_DISPATCH(MM, EE, AA) \
+    if (mant_bits == MM && es == EE && (a_format != 0) == AA) return launch_staged<MM, EE, AA, true>(job, table, sm_count, stream, status);
+    BUDA_FOR_EACH_PACK_KIND(BUDA_DISPATCH)
+#undef BUDA_DISPATCH
+    return cudaErrorInvalidValue;
+}
+
+// General flavour, direct kernel: a batch of one shape under job.pol.
+cudaError_t launch_tilize_direct_policy(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int a_format,
+                                        int vec_ok, int sm_count, cudaStream_t stream)
+{
+#define BUDA_DISPATCH(MM, EE, AA) \
+    if (mant_bits == MM && es == EE && (a_format != 0) == AA) return launch_direct<MM, EE, AA, true>(job, ptrs, batch, vec_ok, sm_count, stream);
+    BUDA_FOR_EACH_PACK_KIND(BUDA_DISPATCH)
 #undef BUDA_DISPATCH
     return cudaErrorInvalidValue;
 }

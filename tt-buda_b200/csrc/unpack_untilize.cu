@@ -10,10 +10,13 @@
 // (lanes along the row, 512 contiguous bytes per warp instruction; measured 11-15 % faster than one
 // bulk async store per row, whose completion the next band had to wait for).  The direct kernel
 // (any alignment) gives each block to four lanes.
+// As on the pack side every kernel has a plain flavour (a batch of tensors of one shape, default byte layout) and a
+// general one (template flag G: a table with one entry per tensor, and the layout policy's face / exponent / datum order).
 #include "bfp_codec.cuh"
 #include <atomic>
 
 #include "buda_common.cuh"
+#include "work_slots_cuda.cuh"
 
 namespace buda {
 
@@ -34,16 +37,8 @@ struct UnpackCfg {
     static constexpr int payload = (M > 0) ? (64 + 1024 * (M + 1) / 8) : (1024 * ES);
     static constexpr int rec_max = payload + 32;
     static constexpr int in_stage_bytes = box * rec_max;
-#ifdef BUDA_UNPACK_STAGES
-    static constexpr int stages = BUDA_UNPACK_STAGES;
-#else
     static constexpr int stages = box > kBoxTiles ? 2 : 4;   // 16-tile items: two stages keep two CTAs per SM
-#endif
-#ifdef BUDA_UNPACK_OUTBUFS
-    static constexpr int out_bufs = BUDA_UNPACK_OUTBUFS;
-#else
     static constexpr int out_bufs = 2;
-#endif
     static constexpr int smem_bytes = stages * in_stage_bytes + out_bufs * out_buf_bytes + stages * (int)sizeof(UItemMeta) +
                                       2 * stages * 8 + 16;
 };
@@ -70,12 +65,33 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi)
     return d;
 }
 
-static __device__ WorkCounter g_unpack_work[kWorkSlots];
-static std::atomic<unsigned> g_next_work_slot{0};   // host side: the counter the next staged launch takes
+// General flavour: work item -> table entry (the cursor only moves forward), then the position inside that tensor's
+// selection of tile rows.
+__device__ __forceinline__ void decode_uitem_gen(const GenTable &tab, const TileJob &common, uint32_t item, uint32_t &cur, UItemMeta &m)
+{
+    while (cur + 1u < tab.n && item >= tab.e[cur + 1u].item_start) cur++;
+    const GenEntry &e = tab.e[cur];
+    uint32_t q = item - e.item_start;
+    const uint32_t cb = q % e.boxes_per_band;
+    q /= e.boxes_per_band;
+    const uint32_t k = q % e.bands;
+    q /= e.bands;
+    m.rt = e.band_first + k * e.band_step;
+    m.z = q % e.Z;
+    m.w = q / e.Z;
+    m.b = cur;
+    m.ct0 = cb * common.box_tiles;
+    m.ntiles = min(common.box_tiles, e.Ct - m.ct0);
+}
 
-template <int M, int ES, bool AF>
+static __device__ WorkCounter g_unpack_work[kWorkSlots];
+
+template <bool G> struct UTableOf { using type = PtrTable; };
+template <> struct UTableOf<true> { using type = GenTable; };
+
+template <int M, int ES, bool AF, bool G>
 __global__ void __launch_bounds__(kUStagedThreads)
-unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ PtrTable ptrs, unsigned int *status)
+unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ typename UTableOf<G>::type ptrs, unsigned int *status)
 {
     using Cfg = UnpackCfg<M, ES>;
     constexpr int S = Cfg::stages;
@@ -103,7 +119,7 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
     if (warp == kUConsumerWarps) {
         // ---------------------------------------------------------------- producer warp
         WorkCounter *wc = &g_unpack_work[job.work_slot];
-        uint32_t it = 0;
+        uint32_t it = 0, cur = 0;
         bool ok = true;
         uint32_t item = work_fetch_get(work_fetch_issue(wc, lane));
         for (; item < job.total_items; ++it) {
@@ -115,14 +131,22 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
                 break;
             }
             UItemMeta m;
-            decode_uitem(job, item, m);
+            if constexpr (G) decode_uitem_gen(ptrs, job, item, cur, m);
+            else decode_uitem(job, item, m);
             if (lane == 0) {
                 meta[s] = m;
                 mbar_arrive_expect_tx(&full[s], m.ntiles * rec);
             }
             __syncwarp();
             if ((uint32_t)lane < m.ntiles) {
-                const uint8_t *src = ptrs.src[m.b] + tile_record_offset(job, m.w, m.z, m.rt, m.ct0 + lane);
+                const uint8_t *src;
+                if constexpr (G) {
+                    TileJob ej;
+                    job_of_entry(job, ptrs.e[m.b], ej);
+                    src = ptrs.e[m.b].q + tile_record_offset(ej, m.w, m.z, m.rt, m.ct0 + lane);
+                } else {
+                    src = ptrs.src[m.b] + tile_record_offset(job, m.w, m.z, m.rt, m.ct0 + lane);
+                }
                 bulk_g2s(in_stage + s * Cfg::in_stage_bytes + lane * rec, src, rec, &full[s]);
             }
             item = work_fetch_get(next_issued);
@@ -173,8 +197,8 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
             if ((uint32_t)tile_in_box < m.ntiles) {
                 constexpr int MM = M > 0 ? M : 7;
                 const uint8_t *r = stage + tile_in_box * rec + hdr;
-                const int blk = face * 16 + fr;
-                const uint32_t E = r[blk];
+                const int blk = (G ? (int)job.pol.face_pos[face] : face) * 16 + fr;
+                const uint32_t E = r[(G && job.pol.exp_be) ? (blk ^ 3) : blk];
                 const uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
                 uint32_t d[BfpTraits<MM>::words];
                 if (MM == 7) {
@@ -185,6 +209,10 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
                     d[0] = t.x; d[1 % BfpTraits<MM>::words] = t.y;
                 } else {
                     d[0] = *reinterpret_cast<const uint32_t *>(q);
+                }
+                if (G && job.pol.datum_be) {
+#pragma unroll
+                    for (int w = 0; w < BfpTraits<MM>::words; w++) d[w] = reverse_datum_fields<MM>(d[w]);
                 }
                 uint8_t *p = ob + lane * Cfg::pitch + bc * 16 * ES;
                 uint32_t h[8];
@@ -217,13 +245,13 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
             const int nchunks = (int)m.ntiles * chunks_per_tile;
             for (int c = tid; c < nchunks; c += kUConsumerThreads) {
                 const int t = c / chunks_per_tile, k = c % chunks_per_tile;
-                const int f = k / (16 * cpr), r16 = (k / cpr) % 16, part = k % cpr;
+                const int r16 = (k / cpr) % 16, part = k % cpr;
+                const int f = G ? (int)job.pol.face_at[k / (16 * cpr)] : k / (16 * cpr);   // the face stored at this position
                 const int row = (f >> 1) * 16 + r16;
                 const uint4 v = *reinterpret_cast<const uint4 *>(stage + t * rec + hdr + k * 16);
                 *reinterpret_cast<uint4 *>(ob + row * Cfg::pitch + t * 32 * ES + (f & 1) * 16 * ES + part * 16) = v;
             }
         }
-#ifndef BUDA_UNPACK_BULK_OUT
         // Every block of the band is decoded: the band leaves with plain coalesced stores, four rows per warp,
         // lanes along the row (one warp instruction = 512 contiguous bytes).  The next item decodes into the other
         // band buffer; this one is overwritten two items later, after the next item's barrier, by which time every
@@ -232,39 +260,34 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
         if (tid == 0) mbar_arrive(&empty[s]);
         {
             const int chunks = (int)m.ntiles * 2 * ES;   // 16-byte chunks per row piece
-            uint8_t *dst0 = ptrs.dst[m.b] + (uint64_t)m.w * job.stride_w + rm_z_offset(job, m.z) +
-                            (uint64_t)m.rt * 32u * job.stride_r + (uint64_t)m.ct0 * 32u * ES;
+            uint8_t *dst0;
+            uint64_t stride_r;
+            if constexpr (G) {
+                const GenEntry &e = ptrs.e[m.b];
+                stride_r = e.stride_r;
+                dst0 = const_cast<uint8_t *>(e.rm) + (uint64_t)m.w * e.stride_w + (uint64_t)m.z * e.stride_z +
+                       (uint64_t)m.rt * 32u * stride_r + (uint64_t)m.ct0 * 32u * ES;
+            } else {
+                stride_r = job.stride_r;
+                dst0 = ptrs.dst[m.b] + (uint64_t)m.w * job.stride_w + rm_z_offset(job, m.z) +
+                       (uint64_t)m.rt * 32u * stride_r + (uint64_t)m.ct0 * 32u * ES;
+            }
 #pragma unroll
             for (int rr = 0; rr < 32 / kUConsumerWarps; rr++) {
                 const int row = warp * (32 / kUConsumerWarps) + rr;
                 const uint8_t *src = ob + row * Cfg::pitch;
-                uint8_t *dst = dst0 + (uint64_t)row * job.stride_r;
+                uint8_t *dst = dst0 + (uint64_t)row * stride_r;
                 for (int c = lane; c < chunks; c += 32)
                     __stcs(reinterpret_cast<uint4 *>(dst + c * 16), *reinterpret_cast<const uint4 *>(src + c * 16));
             }
         }
     }
-#else
-        fence_async_smem();
-        // the band the NEXT item will overwrite (out_bufs - 1 items back) must have left shared memory
-        if (warp == 0) bulk_wait_read<Cfg::out_bufs - 2>();
-        if (named_bar_or(1, kUConsumerThreads, !ok)) break;
-        if (tid == 0) mbar_arrive(&empty[s]);
-        if (warp == 0) {
-            uint8_t *dst = ptrs.dst[m.b] + (uint64_t)m.w * job.stride_w + rm_z_offset(job, m.z) +
-                           ((uint64_t)m.rt * 32u + lane) * job.stride_r + (uint64_t)m.ct0 * 32u * ES;
-            bulk_s2g(dst, ob + lane * Cfg::pitch, m.ntiles * 32u * ES);
-            bulk_commit();
-        }
-    }
-#endif
-    if (warp == 0) bulk_wait_all();
 }
 
 // ------------------------------------------------------------------------------------------------
 // direct kernel
 // ------------------------------------------------------------------------------------------------
-template <int M, int ES, bool AF>
+template <int M, int ES, bool AF, bool G>
 __global__ void __launch_bounds__(256)
 unpack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ PtrTable ptrs, int batch, int vec_ok)
 {
@@ -294,17 +317,26 @@ unpack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant_
             const uint32_t face = hf >> 1, half = hf & 1u;
             const uint32_t fr = half * 8u + (lane >> 2);
             const uint32_t tr = (face >> 1) * 16u + fr;            // row inside the tile
-            const uint32_t blk = face * 16u + fr;
+            const uint32_t blk = (G ? (uint32_t)job.pol.face_pos[face] : face) * 16u + fr;   // position in the record
             ex[hf] = 0;
 #pragma unroll
             for (int i = 0; i < kRaw; i++) raw[hf][i] = 0;
             if (tr >= job.tile_h) continue;                       // tiny tiles: only tile_h rows of a record belong to the tensor
             if (M > 0) {
-                ex[hf] = r[blk];
+                ex[hf] = r[(G && job.pol.exp_be) ? (blk ^ 3u) : blk];
                 const uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
-                if (MM == 7) raw[hf][0] = reinterpret_cast<const uint32_t *>(q)[lane & 3];
-                else if (MM == 3) raw[hf][0] = reinterpret_cast<const uint16_t *>(q)[lane & 3];
-                else raw[hf][0] = q[lane & 3];
+                int part = lane & 3;
+                if (G && job.pol.datum_be) part ^= (MM == 3) ? 1 : (MM == 1) ? 3 : 0;   // reversed fields: see the pack kernel
+                uint32_t pk;
+                if (MM == 7) pk = reinterpret_cast<const uint32_t *>(q)[part];
+                else if (MM == 3) pk = reinterpret_cast<const uint16_t *>(q)[part];
+                else pk = q[part];
+                if (G && job.pol.datum_be) {
+                    if (MM == 7) pk = __byte_perm(pk, 0u, 0x0123);
+                    else if (MM == 3) pk = ((pk & 0xfu) << 12) | ((pk & 0xf0u) << 4) | ((pk >> 4) & 0xf0u) | ((pk >> 12) & 0xfu);
+                    else pk = ((pk & 3u) << 6) | ((pk & 0xcu) << 2) | ((pk >> 2) & 0xcu) | ((pk >> 6) & 3u);
+                }
+                raw[hf][0] = pk;
             } else {
                 const uint8_t *q = r + ((uint64_t)blk * 16u + (lane & 3) * 4u) * ES;
                 if (ES == 4) {
@@ -381,8 +413,10 @@ unpack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant_
 // ------------------------------------------------------------------------------------------------
 // host launchers
 // ------------------------------------------------------------------------------------------------
-template <int M, int ES, bool AF>
-static cudaError_t launch_ustaged(const TileJob &job, const PtrTable &ptrs, int sm_count, cudaStream_t stream,
+static DeviceWorkSlots g_unpack_slots[64];   // per device: which work counter the next staged launch takes
+
+template <int M, int ES, bool AF, bool G>
+static cudaError_t launch_ustaged(const TileJob &job, const typename UTableOf<G>::type &table, int sm_count, cudaStream_t stream,
                                   unsigned int *status)
 {
     using Cfg = UnpackCfg<M, ES>;
@@ -392,26 +426,37 @@ static cudaError_t launch_ustaged(const TileJob &job, const PtrTable &ptrs, int 
     dev &= 63;
     int per_sm = per_sm_cache[dev].load(std::memory_order_acquire);
     if (per_sm == 0) {
-        cudaError_t e = cudaFuncSetAttribute(unpack_staged_kernel<M, ES, AF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(unpack_staged_kernel<M, ES, AF, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Cfg::smem_bytes);
         if (e != cudaSuccess) return e;
         int n = 0;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, unpack_staged_kernel<M, ES, AF>, kUStagedThreads,
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, unpack_staged_kernel<M, ES, AF, G>, kUStagedThreads,
                                                           Cfg::smem_bytes);
         if (e != cudaSuccess) return e;
         per_sm = n < 1 ? 1 : (n > 4 ? 4 : n);
         per_sm_cache[dev].store(per_sm, std::memory_order_release);
     }
     TileJob launch_job = job;
-    if (!set_box_tiles(launch_job, Cfg::box)) return cudaErrorInvalidValue;   // more than 2^31 work items: split the batch
+    typename UTableOf<G>::type launch_table = table;
+    if constexpr (G) {
+        if (!finalize_table(launch_table, launch_job, Cfg::box)) return cudaErrorInvalidValue;
+    } else {
+        if (!set_box_tiles(launch_job, Cfg::box)) return cudaErrorInvalidValue;   // more than 2^31 work items: split the batch
+    }
+    if (launch_job.total_items == 0) return cudaSuccess;
     uint32_t grid = (uint32_t)(sm_count * per_sm);
     if (grid > launch_job.total_items) grid = launch_job.total_items;
-    launch_job.work_slot = g_next_work_slot.fetch_add(1u, std::memory_order_relaxed) % kWorkSlots;
-    unpack_staged_kernel<M, ES, AF><<<grid, kUStagedThreads, Cfg::smem_bytes, stream>>>(launch_job, ptrs, status);
-    return cudaGetLastError();
+    bool tracked = false;
+    const int slot = take_work_slot(g_unpack_slots[dev], stream, &tracked);
+    if (slot < 0) return cudaErrorLaunchOutOfResources;   // the counters reserved for graph capture are used up
+    launch_job.work_slot = (uint32_t)slot;
+    unpack_staged_kernel<M, ES, AF, G><<<grid, kUStagedThreads, Cfg::smem_bytes, stream>>>(launch_job, launch_table, status);
+    const cudaError_t e = cudaGetLastError();
+    work_slot_launched(g_unpack_slots[dev], slot, stream, tracked);
+    return e;
 }
 
-template <int M, int ES, bool AF>
+template <int M, int ES, bool AF, bool G>
 static cudaError_t launch_udirect(const TileJob &job, const PtrTable &ptrs, int batch, int vec_ok, int sm_count,
                                   cudaStream_t stream)
 {
@@ -419,34 +464,47 @@ static cudaError_t launch_udirect(const TileJob &job, const PtrTable &ptrs, int 
     uint64_t blocks = (tiles + 7) / 8;
     const uint64_t cap = (uint64_t)sm_count * 32;
     if (blocks > cap) blocks = cap;
-    unpack_direct_kernel<M, ES, AF><<<(unsigned)blocks, 256, 0, stream>>>(job, ptrs, batch, vec_ok);
+    unpack_direct_kernel<M, ES, AF, G><<<(unsigned)blocks, 256, 0, stream>>>(job, ptrs, batch, vec_ok);
     return cudaGetLastError();
 }
 
+#define BUDA_FOR_EACH_UNPACK_KIND(X) \
+    X(7, 4, false) X(3, 4, false) X(1, 4, false) X(7, 2, false) X(3, 2, false) X(1, 2, false) \
+    X(7, 4, true) X(3, 4, true) X(1, 4, true) X(7, 2, true) X(3, 2, true) X(1, 2, true)       \
+    X(0, 4, false) X(0, 2, false) X(0, 1, false)
+
 // mant_bits 7/3/1 = Bfp decode, 0 = plain relayout; es = destination element bytes; a_format: 5-bit
-// shared exponent (destination binary16 when es == 2).
+// shared exponent (destination binary16 when es == 2).  Plain flavour.
 cudaError_t launch_untilize(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int a_format, int path,
                             int vec_ok, int sm_count, cudaStream_t stream, unsigned int *status)
 {
-#define BUDA_DISPATCH(MM, EE, AA)                                                                   \
-    if (mant_bits == MM && es == EE && (a_format != 0) == AA)                                       \
-        return path == 0 ? launch_ustaged<MM, EE, AA>(job, ptrs, sm_count, stream, status)          \
-                         : launch_udirect<MM, EE, AA>(job, ptrs, batch, vec_ok, sm_count, stream);
-    BUDA_DISPATCH(7, 4, false)
-    BUDA_DISPATCH(3, 4, false)
-    BUDA_DISPATCH(1, 4, false)
-    BUDA_DISPATCH(7, 2, false)
-    BUDA_DISPATCH(3, 2, false)
-    BUDA_DISPATCH(1, 2, false)
-    BUDA_DISPATCH(7, 4, true)
-    BUDA_DISPATCH(3, 4, true)
-    BUDA_DISPATCH(1, 4, true)
-    BUDA_DISPATCH(7, 2, true)
-    BUDA_DISPATCH(3, 2, true)
-    BUDA_DISPATCH(1, 2, true)
-    BUDA_DISPATCH(0, 4, false)
-    BUDA_DISPATCH(0, 2, false)
-    BUDA_DISPATCH(0, 1, false)
+#define BUDA_DISPATCH(MM, EE, AA)                                                                          \
+    if (mant_bits == MM && es == EE && (a_format != 0) == AA)                                              \
+        return path == 0 ? launch_ustaged<MM, EE, AA, false>(job, ptrs, sm_count, stream, status)          \
+                         : launch_udirect<MM, EE, AA, false>(job, ptrs, batch, vec_ok, sm_count, stream);
+    BUDA_FOR_EACH_UNPACK_KIND(BUDA_DISPATCH)
+#undef BUDA_DISPATCH
+    return cudaErrorInvalidValue;
+}
+
+// General flavour, staged kernel: one table entry per tensor.
+cudaError_t launch_untilize_table(const TileJob &job, const GenTable &table, int mant_bits, int es, int a_format, int sm_count,
+                                  cudaStream_t stream, unsigned int *status)
+{
+#define BUDA_DISPATCH(MM, EE, AA) \
+    if (mant_bits == MM && es == EE && (a_format != 0) == AA) return launch_ustaged<MM, EE, AA, true>(job, table, sm_count, stream, status);
+    BUDA_FOR_EACH_UNPACK_KIND(BUDA_DISPATCH)
+#undef BUDA_DISPATCH
+    return cudaErrorInvalidValue;
+}
+
+// General flavour, direct kernel: a batch of one shape under job.pol.
+cudaError_t launch_untilize_direct_policy(const TileJob &job, const PtrTable &ptrs, int batch, int mant_bits, int es, int a_format,
+                                          int vec_ok, int sm_count, cudaStream_t stream)
+{
+#define BUDA_DISPATCH(MM, EE, AA) \
+    if (mant_bits == MM && es == EE && (a_format != 0) == AA) return launch_udirect<MM, EE, AA, true>(job, ptrs, batch, vec_ok, sm_count, stream);
+    BUDA_FOR_EACH_UNPACK_KIND(BUDA_DISPATCH)
 #undef BUDA_DISPATCH
     return cudaErrorInvalidValue;
 }

@@ -1,13 +1,11 @@
-"""ctypes view of libbuda_cuda.so (include/buda_cuda.h) for callers that already hold device
+"""ctypes view of libbuda_cuda.so (include/buda_cuda.h, include/buda_cuda_testing.h) for callers that already hold device
 pointers, e.g. CUDA torch tensors.  There is no fallback: if the library is missing this module
 raises at import, and every compute call needs a CUDA device.
 """
 import ctypes
 import os
 
-# BUDA_CUDA_LIB points at another build of the same library (e.g. one compiled with tuning macros)
-_LIB_PATH = os.environ.get("BUDA_CUDA_LIB") or os.path.join(
-    os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libbuda_cuda.so")
+_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libbuda_cuda.so")
 if not os.path.exists(_LIB_PATH):
     raise ImportError(
         f"{_LIB_PATH} is missing: build it with `python tt-buda_b200/build.py` (there is no CPU fallback)")
@@ -39,8 +37,32 @@ class QueueGeom(ctypes.Structure):
                    ublock[0], ublock[1], z, ublock_order, tile_height)
 
 
+class TensorJob(ctypes.Structure):
+    """buda_tensor_job"""
+
+    _fields_ = [
+        ("tensor", ctypes.c_void_p), ("image", ctypes.c_void_p), ("image_bytes", ctypes.c_uint64),
+        ("shape", ctypes.c_uint32 * 4), ("strides_bytes", ctypes.c_uint64 * 4), ("geom", QueueGeom),
+        ("band_first", ctypes.c_uint32), ("band_step", ctypes.c_uint32), ("band_count", ctypes.c_uint32),
+        ("slots", ctypes.c_uint32), ("first_slot", ctypes.c_uint32),
+    ]
+
+
+class BfpPolicy(ctypes.Structure):
+    """buda_bfp_policy; the default constructor gives the library's default layout"""
+
+    _fields_ = [
+        ("rounding", ctypes.c_uint32), ("overflow", ctypes.c_uint32), ("face_order", ctypes.c_uint8 * 4),
+        ("exponent_order", ctypes.c_uint32), ("datum_order", ctypes.c_uint32),
+    ]
+
+    def __init__(self, rounding=0, overflow=0, face_order=(0, 1, 2, 3), exponent_order=0, datum_order=0):
+        super().__init__(rounding, overflow, (ctypes.c_uint8 * 4)(*face_order), exponent_order, datum_order)
+
+
 _vp, _i, _i64, _u64, _u32, _f = (ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_uint64, ctypes.c_uint32,
                                  ctypes.c_float)
+_jp, _pp = ctypes.POINTER(TensorJob), ctypes.POINTER(BfpPolicy)
 _u32p, _u64p, _gp, _vpp = (ctypes.POINTER(ctypes.c_uint32), ctypes.POINTER(ctypes.c_uint64),
                            ctypes.POINTER(QueueGeom), ctypes.POINTER(ctypes.c_void_p))
 
@@ -56,6 +78,12 @@ _SIGS = {
     "buda_tilize_pack_host": (_i, [_vp, _i, _u32p, _u64p, _gp, _i, _i, _vp, _u64, _vp]),
     "buda_tilize_pack_host_batch": (_i, [_i, _vpp, _i, _u32p, _u64p, _gp, _i, _i, _vpp, _u64, _vp]),
     "buda_tilize_pack_host_noalloc": (_i, [_vp, _i, _u32p, _u64p, _gp, _i, _i, _vp, _u64, _vp]),
+    "buda_tilize_pack_jobs": (_i, [_i, _jp, _i, _i, _i, _vp]),
+    "buda_tilize_pack_host_jobs": (_i, [_i, _jp, _i, _i, _i, _i, _vp]),
+    "buda_unpack_untilize_jobs": (_i, [_i, _jp, _i, _i, _i, _vp]),
+    "buda_unpack_untilize_host_jobs": (_i, [_i, _jp, _i, _i, _i, _i, _vp]),
+    "buda_set_bfp_policy": (_i, [_pp]),
+    "buda_get_bfp_policy": (_i, [_pp]),
     "buda_unpack_untilize": (_i, [_vp, _i, _i, _gp, _vp, _i, _u32p, _u64p, _vp]),
     "buda_unpack_untilize_batch": (_i, [_i, _vpp, _i, _i, _gp, _vpp, _i, _u32p, _u64p, _vp]),
     "buda_unpack_untilize_batch_path": (_i, [_i, _vpp, _i, _i, _gp, _vpp, _i, _u32p, _u64p, _vp, _i]),
@@ -83,7 +111,6 @@ _SIGS = {
     "buda_i8_gemm": (_i, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _f, _i, _vp, _i64, _vp]),
     "buda_gemm_select_kernel": (_i, [_i]),
     "buda_selftest_bounded_wait": (_i, [_u32, _vp]),
-    "buda_stream_probe": (_i, [_i, _i, _u64, _i, ctypes.POINTER(ctypes.c_float), _vp]),
     "buda_ipc_export": (_i, [_vp, ctypes.c_char_p]),
     "buda_ipc_open": (_i, [ctypes.c_char_p, _vpp]),
     "buda_ipc_close": (_i, [_vp]),

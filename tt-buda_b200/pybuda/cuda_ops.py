@@ -302,11 +302,57 @@ class SharedDeviceMatrix:
                 self.ptr = None
 
 
-def stream_probe(mix, schedule, elements=1 << 29, reps=10):
-    """GB/s of a bare streaming kernel with the conversion kernels' access shape (see buda_stream_probe):
-    mix 0 = 4 bytes read per byte written, 1 = the reverse, 2 = reads only, 3 = writes only;
-    schedule 0 = one block per band, 1 = resident blocks on a fixed stride, 2 = resident blocks on a device counter."""
-    ms = ctypes.c_float(0.0)
-    _cabi.check(_cabi.lib.buda_stream_probe(int(mix), int(schedule), int(elements), int(reps), ctypes.byref(ms), _stream()))
-    nbytes = elements * (5.0 if mix in (0, 1) else 4.0)
-    return nbytes / (ms.value * 1e-3) / 1e9
+def set_bfp_policy(policy=None):
+    """Process-wide block-float layout policy (a _cabi.BfpPolicy; None restores the default)."""
+    check(_cabi.lib.buda_set_bfp_policy(ctypes.byref(policy) if policy is not None else None))
+
+
+def get_bfp_policy():
+    p = _cabi.BfpPolicy()
+    check(_cabi.lib.buda_get_bfp_policy(ctypes.byref(p)))
+    return p
+
+
+def _job_table(tensors, images, q_df, geoms, with_header, bands):
+    jobs = (_cabi.TensorJob * len(tensors))()
+    for i, (t, im) in enumerate(zip(tensors, images)):
+        shape, strides = _desc(t)
+        g = geoms[i] if geoms is not None and geoms[i] is not None else QueueGeom.for_shape(shape)
+        j = jobs[i]
+        j.tensor, j.image = t.data_ptr(), im.data_ptr()
+        j.image_bytes = im.numel() * im.element_size()
+        j.shape = _cabi.u32x4(shape)
+        j.strides_bytes = _cabi.u64x4(strides)
+        j.geom = g
+        if bands is not None and bands[i] is not None:
+            j.band_first, j.band_step, j.band_count = bands[i]
+    return jobs
+
+
+def tilize_pack_jobs(tensors, dst_df, geoms=None, with_header=False, outs=None, bands=None):
+    """Tilize (and block-float pack) CUDA tensors of DIFFERENT shapes (one dtype) in as few launches as possible.
+    geoms: per-tensor QueueGeom or None; bands: per-tensor (first, step, count) selection of tile rows or None.
+    Returns the list of uint8 image tensors."""
+    _need_cuda(*tensors)
+    src_df = _TORCH_TO_DF[tensors[0].dtype]
+    if outs is None:
+        outs = []
+        for i, t in enumerate(tensors):
+            shape, _ = _desc(t)
+            g = geoms[i] if geoms is not None and geoms[i] is not None else QueueGeom.for_shape(shape)
+            outs.append(torch.empty(_cabi.tilized_bytes(g, shape, int(dst_df), with_header), dtype=torch.uint8, device=t.device))
+    jobs = _job_table(tensors, outs, dst_df, geoms, with_header, bands)
+    with torch.cuda.device(tensors[0].device):
+        check(_cabi.lib.buda_tilize_pack_jobs(len(tensors), jobs, int(src_df), int(dst_df), int(with_header), _stream()))
+    return outs
+
+
+def unpack_untilize_jobs(images, src_df, outs, geoms=None, with_header=False, bands=None):
+    """Inverse of tilize_pack_jobs: images[i] -> outs[i] (CUDA tensors of one dtype, any shapes)."""
+    _need_cuda(*images)
+    _need_cuda(*outs)
+    dst_df = _TORCH_TO_DF[outs[0].dtype]
+    jobs = _job_table(outs, images, src_df, geoms, with_header, bands)
+    with torch.cuda.device(outs[0].device):
+        check(_cabi.lib.buda_unpack_untilize_jobs(len(outs), jobs, int(src_df), int(with_header), int(dst_df), _stream()))
+    return outs

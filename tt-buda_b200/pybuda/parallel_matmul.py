@@ -22,9 +22,12 @@ from .sharding import band_slices, column_shard, gather_layout_to_row_major
 
 class ColumnParallelBfp8Matmul:
     def __init__(self, k: int, n: int, group=None, bands: int = 8,
-                 local_matmul: Optional[Callable[[torch.Tensor, torch.Tensor, int, torch.Tensor], torch.Tensor]] = None):
+                 local_matmul: Optional[Callable[[torch.Tensor, torch.Tensor, int, torch.Tensor], torch.Tensor]] = None,
+                 scatter: Optional[Callable[[torch.Tensor], None]] = None, wait_local: Optional[Callable[[], None]] = None):
         """local_matmul(a, weight_image, n_local, out) -> out.  The default is the CUDA kernel; tests of the
-        exchange logic on CPU ranks (gloo) pass a stand-in."""
+        exchange logic on CPU ranks (gloo) pass a stand-in.  scatter(a) starts this rank's stores into every rank's
+        output and wait_local() returns when they are done (defaults: the fused kernel on the current CUDA stream and
+        a synchronisation of that stream)."""
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -39,6 +42,8 @@ class ColumnParallelBfp8Matmul:
         self.weight_image = None
         self._shared = None        # SharedDeviceMatrix: this rank's full output, mapped by the peers
         self._dst_ptrs = None
+        self._scatter = scatter if scatter is not None else self._scatter_kernel
+        self._wait_local = wait_local if wait_local is not None else (lambda: torch.cuda.current_stream().synchronize())
 
     def enable_fused_scatter(self, m: int):
         """Allocate this rank's full [m, n] output where the peers can map it, exchange the handles and map
@@ -68,19 +73,31 @@ class ColumnParallelBfp8Matmul:
             self._shared.close()
             self._shared, self._dst_ptrs = None, None
 
-    def fused(self, a: torch.Tensor, sync: bool = True) -> torch.Tensor:
-        """One kernel: this rank's column block, written into every rank's output.  With sync (default) a
-        barrier follows, after which the returned [m, n] matrix is complete on every rank."""
+    def _scatter_kernel(self, a: torch.Tensor):
         from . import cuda_ops
 
+        cuda_ops.bfp8b_matmul_scatter(a, self.weight_image, self.n_local, self._dst_ptrs, self.n)
+
+    def fused(self, a: torch.Tensor, sync: bool = True) -> torch.Tensor:
+        """One kernel: this rank's column block, written into every rank's output.  With sync (default) the call
+        returns when the [m, n] matrix is complete on every rank; with sync=False it only enqueues this rank's
+        kernel, and complete() has to follow before anybody reads."""
         if self._shared is None or a.shape[0] != self._shared.rows:
             raise RuntimeError("enable_fused_scatter(m) first, with m = a.shape[0]")
         if self.weight_image is None:
             raise RuntimeError("load_weight_shard() first")
-        cuda_ops.bfp8b_matmul_scatter(a, self.weight_image, self.n_local, self._dst_ptrs, self.n)
-        if sync and self.world > 1:
-            dist.barrier(group=self.group)
+        self._scatter(a)
+        if sync:
+            self.complete()
         return self._shared.tensor
+
+    def complete(self):
+        """Makes the scattered result readable everywhere.  A rank may pass the barrier only when its OWN stores into
+        the peers are done, so it first waits for its kernel -- whatever backend the group uses and whatever stream
+        the kernel ran on; a barrier alone orders nothing that is still in flight on a device."""
+        self._wait_local()
+        if self.world > 1:
+            dist.barrier(group=self.group)
 
     def load_weight_shard(self, w_full_or_shard: torch.Tensor, already_sharded: bool = False):
         """Pack this rank's columns of a [K, N] float weight to a Bfp8_b queue image on its device."""

@@ -12,6 +12,27 @@ def units_of_rank(n_units: int, rank: int, world: int) -> List[int]:
     return list(range(rank, n_units, world))
 
 
+def bands_of_rank(tile_rows: int, rank: int, world: int) -> Tuple[int, int, int]:
+    """Tile-row bands of ONE tensor dealt over the GPUs: band b (32 tensor rows across the whole width) belongs to
+    rank b % world.  Returns (first, step, count), the selection the job-table entry points take
+    (buda_tensor_job.band_first / band_step / band_count); count is 0 for a rank that gets nothing."""
+    if not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside a world of {world}")
+    return rank, world, len(range(rank, tile_rows, world))
+
+
+def band_record_slice(band: int, tile_rows: int, tile_cols: int, tile_bytes: int, z: int = 0, entry: int = 0,
+                      t: int = 1) -> Tuple[int, int]:
+    """(offset, length) in bytes of the records of tile row `band` of slice z of entry `entry` inside the queue image,
+    for a 1x1 grid with 1x1 ublocks scanned row-major: there a band's records are one contiguous run -- tile (z, r, c)
+    sits at address z * rows * cols + r * cols + c (TileLayout::map, pybuda/csrc/balancer/types.cpp:629-648).  With
+    any other geometry a band is scattered over the image and the kernels place each record themselves."""
+    if not (0 <= band < tile_rows and 0 <= z < t):
+        raise ValueError("band or slice outside the tensor")
+    first_tile = (entry * t + z) * tile_rows * tile_cols + band * tile_cols
+    return first_tile * tile_bytes, tile_cols * tile_bytes
+
+
 def band_slices(rows: int, bands: int, multiple: int = 32) -> List[Tuple[int, int]]:
     """Split `rows` into at most `bands` contiguous (start, stop) row ranges whose sizes are multiples of
     `multiple` (the last one takes the remainder)."""
