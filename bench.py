@@ -240,6 +240,13 @@ def profile_one(torch, cuda_ops, dev, name, reps=20, nt=8):
         else:
             fn = lambda: cuda_ops.unpack_untilize_batch(imgs, cuda_ops.DF.Bfp8_b, SHAPE, outs=xs)
         work, unit = nt * ELEMS * 3.0625 / 1e9, "GB/s"
+    elif name in ("pack_jobs", "unpack_jobs"):
+        # the general kernel flavour (job table) on a uniform batch
+        xs = [torch.randn(SHAPE, device=dev) for _ in range(nt)]
+        tj = cuda_ops.TensorJobs(xs, cuda_ops.DF.Bfp8_b)
+        tj.pack()
+        fn = tj.pack if name == "pack_jobs" else tj.unpack
+        work, unit = nt * ELEMS * BYTES_PER_ELEM / 1e9, "GB/s"
     elif name in ("pack", "unpack", "pack_direct", "unpack_direct"):
         xs = [torch.randn(SHAPE, device=dev) for _ in range(nt)]
         imgs = cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b)
@@ -328,7 +335,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (for profiler captures)")
     ap.add_argument("--tensors", type=int, default=N_TENSORS,
                     help="tensors per GPU batch; anything but 64 is a reduced case for profiler captures")
-    ap.add_argument("--profile-kernel", default=None, choices=["bare_streams", "gemm", "i8gemm", "pack", "unpack", "pack_direct", "unpack_direct", "pack_bf16", "unpack_bf16", "quantize", "dequantize", "requantize"],
+    ap.add_argument("--profile-kernel", default=None, choices=["bare_streams", "gemm", "i8gemm", "pack_jobs", "unpack_jobs", "pack", "unpack", "pack_direct", "unpack_direct", "pack_bf16", "unpack_bf16", "quantize", "dequantize", "requantize"],
                     help="run only this secondary kernel a few times and exit (small, self-ending case for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -514,6 +521,10 @@ def main():
                 extras[name] = timed(lambda: cuda_ops.tilize_pack_batch(xs, df, outs=o2), NT * (ELEMS * 4 + ib))
             extras["pack_bfp8_b_direct_kernel"] = timed(
                 lambda: cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Bfp8_b, outs=outs, path=1), algo_bytes_step)
+            # the general kernel flavour (job table) on the same uniform batch: what the table look-ups cost by themselves
+            tj = cuda_ops.TensorJobs(xs, cuda_ops.DF.Bfp8_b, images=outs)
+            extras["pack_bfp8_b_job_table_flavour"] = timed(tj.pack, algo_bytes_step)
+            del tj
             nu = min(16, NT)
             # bfloat16 source (2 + 1.0625 bytes per element) and bfloat16 destination
             xb = [x.bfloat16() for x in xs[:nu]]
@@ -610,14 +621,16 @@ def main():
                 for j, shp in enumerate([(1024, 1024)] * 4 + [(1024, 4096), (4096, 1024)]):
                     g = torch.Generator(device=dev).manual_seed(2000 + 6 * l + j)
                     ws.append(torch.randn((1, 1) + shp, generator=g, device=dev) * 0.02)
-            imgs = cuda_ops.tilize_pack_jobs(ws, cuda_ops.DF.Bfp8_b)
+            fwd = cuda_ops.TensorJobs(ws, cuda_ops.DF.Bfp8_b)                      # job tables prepared once
+            imgs = fwd.pack()
             backs = [torch.empty_like(t) for t in ws]
+            bwd = cuda_ops.TensorJobs(backs, cuda_ops.DF.Bfp8_b, images=imgs)
             lc0 = _cabi.launch_count()
 
             def round_trip():
                 # the whole set, whatever its shapes: one pack launch and one unpack launch
-                cuda_ops.tilize_pack_jobs(ws, cuda_ops.DF.Bfp8_b, outs=imgs)
-                cuda_ops.unpack_untilize_jobs(imgs, cuda_ops.DF.Bfp8_b, backs)
+                fwd.pack()
+                bwd.unpack()
 
             round_trip()
             launches_rt = _cabi.launch_count() - lc0
@@ -638,7 +651,7 @@ def main():
                 "launches_per_round_trip": int(launches_rt),
                 "note": "pack + unpack of this rank's layers through the job-table entry points (all shapes in one launch "
                         "each way); the set is 1.5 GB over all ranks, so at 8 GPUs a rank's share (191 MB) is near the size of L2"}
-            del ws, imgs, backs
+            del ws, imgs, backs, fwd, bwd
         except Exception as exc:
             extras["bert_large_weights_fp32_bfp8b_fp32"] = {"error": str(exc)}
 

@@ -236,6 +236,35 @@ int buda_queue_read(const void *queue_base, int src_df, int with_header, const b
                     uint32_t first_slot, void *dst, int dst_is_host, int dst_df, const uint32_t shape[4],
                     const uint64_t strides_bytes[4], void *stream);
 
+/* A tensor pushed through one of the reference's runtime tensor transforms, converted in ONE kernel: the kernel's
+ * index arithmetic reads the source the way the transform would have rewritten it, so no padded / gathered copy of
+ * the tensor is ever made.  `shape` is the tile-aligned [w, t, R, C] the queue covers; the view says where element
+ * (w, z, r, c) of that shape comes from:
+ *   BUDA_SRC_PADDED           the tensor [w, t, valid_r, valid_c] (its own strides in strides_bytes), zero outside:
+ *                             the tile padding of pad_pytorch_tensor_to_buda (pybuda/pybuda/tensor.py:805-877; a
+ *                             tile-broadcast dim is a stride of 0) applied to a ReinterpretShape view (tensor.py:1407-1413)
+ *   BUDA_SRC_EMBEDDING_INDEX  a vector of `emb_count` row indices per entry (entry stride strides_bytes[0]) laid out
+ *                             for an embedding op (_embedding_index, pybuda/pybuda/tensor.py:1382-1405): each 32x32
+ *                             tile is 1024 consecutive indices, emb_group indices per queue tile row, all ones past
+ *                             the last index, zero past the group; t == 1
+ *   BUDA_SRC_PRESTRIDE        a convolution activation [w, ps_z, ps_h, ps_w] (strides_bytes) cut into its stride phases:
+ *                             row k * ps_z + zc, column hr * ceil(ps_w / s) + wc  <-  act[w, zc, hr * s + y_k, wc * s + x_k]
+ *                             (pybuda/pybuda/tensor.py:1415-1422, golden pybuda/pybuda/op/eval/pybuda/tm.py:316-335); t == 1
+ * src is a DEVICE pointer.  queue_base / slots / first_slot as in buda_queue_write (slots == 0: a dense image). */
+enum { BUDA_SRC_DENSE = 0, BUDA_SRC_PADDED = 1, BUDA_SRC_EMBEDDING_INDEX = 2, BUDA_SRC_PRESTRIDE = 3 };
+typedef struct buda_source_view {
+    uint32_t mode;
+    uint32_t valid_r, valid_c;
+    uint64_t emb_count, emb_group;
+    uint32_t ps_stride, ps_z, ps_h, ps_w;
+    uint32_t ps_n_offsets;          /* 1..64 */
+    int32_t ps_xy[128];             /* (x, y) pairs, each inside the stride window */
+} buda_source_view;
+
+int buda_queue_write_view(const void *src, int src_df, const uint32_t shape[4], const uint64_t strides_bytes[4],
+                          const buda_source_view *view, const buda_queue_geom *geom, int dst_df, int with_header,
+                          void *queue_base, uint64_t queue_bytes, uint32_t slots, uint32_t first_slot, void *stream);
+
 /* Read `entries` entries and apply the output host transforms on the way: the t slices of an
  * entry are laid side by side, hstack across (columns) and vstack down (rows), giving a dense
  * [entries, t/(hstack*vstack), R*vstack, C*hstack] device tensor.  stack_row_major != 0: slice z sits

@@ -144,13 +144,13 @@ def test_policies_cover_plain_formats_a_formats_headers_and_geometry(ops, oracle
 def test_matmul_refuses_a_layout_it_cannot_read(ops):
     from pybuda import _cabi
     a = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
-    w = ops.tilize_pack(torch.zeros(1, 1, 64, 128, device="cuda"), ops.DF.Bfp8_b)
+    w = ops.tilize_pack(torch.zeros(1, 1, 64, 256, device="cuda"), ops.DF.Bfp8_b)
     try:
         ops.set_bfp_policy(_cabi.BfpPolicy(rounding=1, overflow=1))       # rounding / overflow do not change how bytes are read
-        ops.bfp8b_matmul(a, w, 128)
+        ops.bfp8b_matmul(a, w, 256)
         ops.set_bfp_policy(_cabi.BfpPolicy(datum_order=1))
         with pytest.raises(_cabi.BudaError):
-            ops.bfp8b_matmul(a, w, 128)
+            ops.bfp8b_matmul(a, w, 256)
         with pytest.raises(_cabi.BudaError):
             ops.set_bfp_policy(_cabi.BfpPolicy(face_order=(0, 1, 1, 3)))
     finally:

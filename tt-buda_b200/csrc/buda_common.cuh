@@ -76,6 +76,26 @@ __host__ __device__ inline bool policy_is_default(const BfpPolicy &p)
            p.face_pos[3] == 3;
 }
 
+// How the general flavour of the direct pack kernel reads the row-major side when that is not a dense tensor of whole
+// tiles: the runtime tensor transforms of the reference's push path, done in the kernel's index arithmetic instead
+// of as separate passes over the data.  Element (w, z, r, c) of the tile-aligned shape the queue covers comes from
+//   kSrcPadded     the tensor itself where r < valid_r and c < valid_c, zero elsewhere (tile padding of
+//                  pad_pytorch_tensor_to_buda, pybuda/pybuda/tensor.py:805-877)
+//   kSrcEmbedding  a vector of row indices laid out for an embedding op (pybuda/pybuda/tensor.py:1382-1405): with
+//                  group = indices per queue tile row, a = (c / 32) * 32 + r % 32 and flat = (r / 32) * group + a * 32 +
+//                  c % 32: zero where a >= group / 32, all ones where flat >= count, else indices[w][flat]
+//   kSrcPrestride  a convolution activation [w, ps_z, ps_h, ps_w] cut into its stride phases
+//                  (pybuda/pybuda/op/eval/pybuda/tm.py:316-335): r = k * ps_z + zc, c = hr * ps_ws + wc ->
+//                  act[w, zc, hr * s + y_k, wc * s + x_k], zero outside the activation or past the last phase / pixel
+enum : uint32_t { kSrcDense = 0, kSrcPadded = 1, kSrcEmbedding = 2, kSrcPrestride = 3 };
+struct SourceView {
+    uint32_t mode;
+    uint32_t valid_r, valid_c;
+    uint64_t emb_count, emb_group;
+    uint32_t ps_stride, ps_noff, ps_z, ps_h, ps_w, ps_hs, ps_ws;
+    int8_t ps_x[64], ps_y[64];
+};
+
 struct TileJob {
     // row-major side
     uint32_t W, Z, Rt, Ct;              // entries, t, tile rows, tile columns
@@ -99,6 +119,7 @@ struct TileJob {
     uint32_t tile_h;                    // tensor rows per tile: 32, or 16 / 8 / 4 / 2 / 1 for tiny tiles (direct kernels only)
     uint32_t work_slot;                 // staged kernels: which work counter this launch draws its items from
     BfpPolicy pol;                      // general kernel flavour only
+    SourceView view;                    // general flavour of the direct pack kernel only
 };
 
 // Re-derives the work-item fields of a job for `box` tiles per item; false when the launch would have 2^31 items or more.
@@ -173,18 +194,36 @@ struct GenEntry {
     const uint8_t *rm;                  // row-major tensor
     uint8_t *q;                         // queue image (pack writes it, unpack reads it)
     uint64_t stride_w, stride_z, stride_r;
+    uint64_t tiles_per_entry;           // per grid core: t * macro-block volume
+    uint64_t buf_bytes;                 // one grid core's buffer
     uint32_t W, Z, Rt, Ct;              // entries, t, tile rows, tile columns of the whole tensor
     uint32_t item_start;                // first work item of this tensor
     uint32_t boxes_per_band;
     uint32_t band_first, band_step, bands;   // tile rows taken: band_first + k * band_step, k < bands
     uint32_t slots, slot0;
+    uint32_t bpb_magic, bands_magic;    // n / boxes_per_band and n / bands as a multiply and a shift (n < 2^31)
     uint16_t grid_r, grid_c, mblock_m, mblock_n, ublock_rt, ublock_ct;
-    uint8_t ublock_order, trivial_geom, pad0, pad1;
+    uint8_t ublock_order, trivial_geom, bpb_shift, bands_shift;
 };
+static_assert(sizeof(GenEntry) == 128, "one 32-bit word per lane when a warp copies an entry");
 struct GenTable {
     uint32_t n, pad;
     GenEntry e[kMaxGen];
 };
+
+// floor(n / d) for n < 2^31 as (n * magic) >> shift: magic = ceil(2^(31+s) / d) with s = ceil(log2 d) fits 32 bits.
+inline void fast_div_setup(uint32_t d, uint32_t &magic, uint8_t &shift)
+{
+    uint32_t sft = 0;
+    while ((1ull << sft) < d) sft++;
+    const uint64_t num = 1ull << (31 + sft);
+    magic = (uint32_t)((num + d - 1) / d);
+    shift = (uint8_t)(31 + sft);
+}
+__host__ __device__ inline uint32_t fast_div(uint32_t n, uint32_t magic, uint32_t shift)
+{
+    return (uint32_t)(((uint64_t)n * magic) >> shift);
+}
 
 // Numbers the work items of a table for `box` tiles per item; false when the launch would have 2^31 items or more.
 inline bool finalize_table(GenTable &t, TileJob &common, uint32_t box)
@@ -194,6 +233,8 @@ inline bool finalize_table(GenTable &t, TileJob &common, uint32_t box)
     for (uint32_t i = 0; i < t.n; i++) {
         GenEntry &e = t.e[i];
         e.boxes_per_band = (e.Ct + box - 1) / box;
+        fast_div_setup(e.boxes_per_band, e.bpb_magic, e.bpb_shift);
+        fast_div_setup(e.bands, e.bands_magic, e.bands_shift);
         e.item_start = (uint32_t)items;
         items += (uint64_t)e.W * e.Z * e.bands * e.boxes_per_band;
         if (items >= (1ull << 31)) return false;
@@ -213,9 +254,9 @@ __host__ __device__ inline void job_of_entry(const TileJob &common, const GenEnt
     j.g.ublock_rt = e.ublock_rt; j.g.ublock_ct = e.ublock_ct; j.g.t = e.Z; j.g.ublock_order = e.ublock_order;
     j.tile_bytes = common.tile_bytes;
     j.header_bytes = common.header_bytes;
-    j.tiles_per_entry = (uint64_t)e.Z * e.mblock_m * e.mblock_n * e.ublock_rt * e.ublock_ct;
+    j.tiles_per_entry = e.tiles_per_entry;
     j.slots = e.slots; j.slot0 = e.slot0;
-    j.buf_bytes = (uint64_t)(e.slots ? e.slots : e.W) * j.tiles_per_entry * common.tile_bytes;
+    j.buf_bytes = e.buf_bytes;
     j.trivial_geom = e.trivial_geom;
     j.zn1 = j.zn2 = 0;
     j.tile_h = 32;

@@ -161,6 +161,7 @@ int make_job(const uint32_t shape[4], const uint64_t strides[4], const buda_queu
     j.W = shape[0]; j.Z = shape[1]; j.Rt = shape[2] / th; j.Ct = shape[3] / 32;
     j.tile_h = th;
     j.pol = default_policy();           // the callers that honour a policy overwrite it
+    memset(&j.view, 0, sizeof(j.view)); // dense source unless buda_queue_write_view says otherwise
     j.work_slot = 0;                    // set per launch by the staged launchers
     j.stride_w = strides[0]; j.stride_z = strides[1]; j.stride_r = strides[2];
     j.box_tiles = (uint32_t)box_tiles_for((int)strides[3], bfp_mant_bits(qdf) != 0);
@@ -255,6 +256,8 @@ int fill_entry(const TileJob &j, const void *rm, void *q, uint32_t band_first, u
     e.W = j.W; e.Z = j.Z; e.Rt = j.Rt; e.Ct = j.Ct;
     e.band_first = band_first; e.band_step = band_step; e.bands = band_count;
     e.slots = j.slots; e.slot0 = j.slot0;
+    e.tiles_per_entry = j.tiles_per_entry;
+    e.buf_bytes = j.buf_bytes;
     e.grid_r = (uint16_t)g.grid_r; e.grid_c = (uint16_t)g.grid_c; e.mblock_m = (uint16_t)g.mblock_m; e.mblock_n = (uint16_t)g.mblock_n;
     e.ublock_rt = (uint16_t)g.ublock_rt; e.ublock_ct = (uint16_t)g.ublock_ct;
     e.ublock_order = (uint8_t)g.ublock_order;
@@ -910,6 +913,84 @@ int buda_queue_write(const void *src, int src_is_host, int src_df, const uint32_
     void *dsts[1] = {queue_base};
     return tilize_device(1, srcs, src_df, shape, strides_bytes, geom, dst_df, with_header, dsts, (uint64_t)qb,
                          (cudaStream_t)stream, -1, slots, first_slot);
+}
+
+int buda_queue_write_view(const void *src, int src_df, const uint32_t shape[4], const uint64_t strides_bytes[4],
+                          const buda_source_view *view, const buda_queue_geom *geom, int dst_df, int with_header, void *queue_base,
+                          uint64_t queue_bytes, uint32_t slots, uint32_t first_slot, void *stream)
+{
+    DevCtx *ctx;
+    if (int rc = get_ctx(&ctx)) return rc;
+    if (!src || !queue_base || !view || !geom || !shape || !strides_bytes) return fail(BUDA_RUNTIME_ERROR, "null argument");
+    int mant, es;
+    if (int rc = classify(src_df, dst_df, mant, es)) return rc;
+    if (strides_bytes[3] != (uint64_t)es) return fail(BUDA_RUNTIME_ERROR, "innermost stride must equal the element size (%d)", es);
+    if (geom->tile_height != 0 && geom->tile_height != 32) return fail(BUDA_RUNTIME_ERROR, "source views need 32-row tiles");
+    TileJob job;
+    if (int rc = make_job(shape, strides_bytes, geom, dst_df, with_header, 1, job, slots, first_slot)) return rc;
+    const uint64_t need = job.buf_bytes * geom->grid_r * geom->grid_c;
+    if (queue_bytes < need)
+        return fail(BUDA_RUNTIME_ERROR, "destination holds %llu bytes, the queue image needs %llu", (unsigned long long)queue_bytes,
+                    (unsigned long long)need);
+    if (!aligned16((uint64_t)queue_base)) return fail(BUDA_RUNTIME_ERROR, "queue image pointers must be 16-byte aligned");
+    SourceView &v = job.view;
+    memset(&v, 0, sizeof(v));
+    switch (view->mode) {
+        case BUDA_SRC_PADDED:
+            if (view->valid_r == 0 || view->valid_c == 0 || view->valid_r > shape[2] || view->valid_c > shape[3])
+                return fail(BUDA_RUNTIME_ERROR, "padded view: valid extent %ux%u outside the %ux%u the queue covers", view->valid_r,
+                            view->valid_c, shape[2], shape[3]);
+            v.mode = kSrcPadded;
+            v.valid_r = view->valid_r;
+            v.valid_c = view->valid_c;
+            break;
+        case BUDA_SRC_EMBEDDING_INDEX:
+            if (shape[1] != 1) return fail(BUDA_RUNTIME_ERROR, "embedding-index view: t must be 1");
+            if (mant != 0) return fail(BUDA_RUNTIME_ERROR, "embedding-index view: indices go to a raw / integer queue");
+            if (view->emb_group == 0 || view->emb_group % 32 || view->emb_group > (uint64_t)shape[3] * 32u)
+                return fail(BUDA_RUNTIME_ERROR, "embedding-index view: %llu indices per tile row do not fit %u columns",
+                            (unsigned long long)view->emb_group, shape[3]);
+            if (view->emb_count > (uint64_t)(shape[2] / 32u) * view->emb_group)
+                return fail(BUDA_RUNTIME_ERROR, "embedding-index view: %llu indices do not fit the queue", (unsigned long long)view->emb_count);
+            v.mode = kSrcEmbedding;
+            v.emb_count = view->emb_count;
+            v.emb_group = view->emb_group;
+            break;
+        case BUDA_SRC_PRESTRIDE: {
+            if (shape[1] != 1) return fail(BUDA_RUNTIME_ERROR, "prestride view: t must be 1");
+            const uint32_t sdv = view->ps_stride;
+            if (sdv < 1 || sdv > 127 || view->ps_n_offsets < 1 || view->ps_n_offsets > 64 || !view->ps_z || !view->ps_h || !view->ps_w)
+                return fail(BUDA_RUNTIME_ERROR, "prestride view: stride %u with %u offsets is not supported", sdv, view->ps_n_offsets);
+            v.mode = kSrcPrestride;
+            v.ps_stride = sdv;
+            v.ps_noff = view->ps_n_offsets;
+            v.ps_z = view->ps_z; v.ps_h = view->ps_h; v.ps_w = view->ps_w;
+            v.ps_hs = (view->ps_h + sdv - 1) / sdv;
+            v.ps_ws = (view->ps_w + sdv - 1) / sdv;
+            for (uint32_t k = 0; k < view->ps_n_offsets; k++) {
+                const int32_t x = view->ps_xy[2 * k], y = view->ps_xy[2 * k + 1];
+                if (x < 0 || y < 0 || x >= (int32_t)sdv || y >= (int32_t)sdv)
+                    return fail(BUDA_RUNTIME_ERROR, "prestride view: offset %u = (%d, %d) lies outside the %ux%u stride window", k, x, y, sdv, sdv);
+                v.ps_x[k] = (int8_t)x;
+                v.ps_y[k] = (int8_t)y;
+            }
+            if ((uint64_t)v.ps_noff * v.ps_z > shape[2] || (uint64_t)v.ps_hs * v.ps_ws > shape[3])
+                return fail(BUDA_RUNTIME_ERROR, "prestride view: [%llu x %llu] does not fit the queue's %ux%u",
+                            (unsigned long long)v.ps_noff * v.ps_z, (unsigned long long)v.ps_hs * v.ps_ws, shape[2], shape[3]);
+            break;
+        }
+        default:
+            return fail(BUDA_RUNTIME_ERROR, "unknown source view mode %u", view->mode);
+    }
+    job.pol = current_policy();
+    PtrTable pt;
+    memset(&pt, 0, sizeof(pt));
+    pt.src[0] = (const uint8_t *)src;
+    pt.dst[0] = (uint8_t *)queue_base;
+    cudaError_t e = launch_tilize_direct_policy(job, pt, 1, mant, es, is_bfp_a(dst_df) ? 1 : 0, 0, ctx->sm_count, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "tilize launch failed");
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return BUDA_SUCCESS;
 }
 
 int buda_queue_read(const void *queue_base, int src_df, int with_header, const buda_queue_geom *geom, uint32_t slots,

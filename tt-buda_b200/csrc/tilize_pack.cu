@@ -53,6 +53,11 @@ struct PackCfg {
     static constexpr int stages = 2;  // depth comes from the CTAs resident per SM, not from stages per CTA
     static constexpr int smem_bytes = stages * in_stage_bytes + 2 * out_buf_bytes + stages * (int)sizeof(ItemMeta) +
                                       2 * stages * 8 + 16;
+    // general flavour: a copy of the table entry in use, the first work item of every entry, and per stage the
+    // destination of each tile of the item (worked out by the producer, which holds the entry)
+    static constexpr int gen_extra_bytes = 136 + (kMaxGen + 1) * 4 + 4 + stages * 16 * 8;
+    template <bool G>
+    static constexpr int smem_for() { return smem_bytes + (G ? gen_extra_bytes : 0); }
 };
 
 __device__ __forceinline__ void decode_item(const TileJob &job, uint32_t item, ItemMeta &m)
@@ -69,21 +74,56 @@ __device__ __forceinline__ void decode_item(const TileJob &job, uint32_t item, I
     m.ntiles = min(job.box_tiles, job.Ct - m.ct0);
 }
 
-// General flavour: work item -> table entry (cursor `cur` only moves forward: a CTA's items come in increasing order),
-// then the position inside that tensor's selection of tile rows.
-__device__ __forceinline__ void decode_item_gen(const GenTable &tab, const TileJob &common, uint32_t item, uint32_t &cur, ItemMeta &m)
+// General flavour.  Kernel parameters are slow to read with a run-time index, so the table is touched as little as
+// possible: every entry's first work item is copied to shared memory once per CTA, the entry a work item belongs to is
+// found there by bisection, and the entry itself is copied to shared memory when the producer moves on to it.
+struct GenCache {
+    GenEntry e;                       // 128 bytes
+    uint32_t loaded, pad;             // index of the entry held in e
+};
+static_assert(sizeof(GenCache) == 136, "shared-memory plan of the general flavour");
+
+__device__ __forceinline__ void gen_load_starts(const GenTable &tab, uint32_t total_items, uint32_t *starts, int tid, int nthreads)
 {
-    while (cur + 1u < tab.n && item >= tab.e[cur + 1u].item_start) cur++;
-    const GenEntry &e = tab.e[cur];
-    uint32_t q = item - e.item_start;
-    const uint32_t cb = q % e.boxes_per_band;
-    q /= e.boxes_per_band;
-    const uint32_t k = q % e.bands;
-    q /= e.bands;
+    for (uint32_t i = (uint32_t)tid; i <= tab.n; i += (uint32_t)nthreads) starts[i] = i < tab.n ? tab.e[i].item_start : total_items;
+}
+
+// whole producer warp; returns with *cache holding the entry of `item`
+__device__ __forceinline__ void gen_find_entry(const GenTable &tab, const uint32_t *starts, uint32_t item, GenCache *cache, int lane)
+{
+    uint32_t idx = cache->loaded;
+    if (idx >= tab.n || item < starts[idx] || item >= starts[idx + 1u]) {
+        uint32_t lo = 0, hi = tab.n;          // largest idx with starts[idx] <= item
+        while (hi - lo > 1u) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if (starts[mid] <= item) lo = mid; else hi = mid;
+        }
+        __syncwarp();
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(&tab.e[lo]);
+        reinterpret_cast<uint32_t *>(&cache->e)[lane] = src[lane];   // 32 lanes x 4 bytes = the entry
+        if (lane == 31) cache->loaded = lo;
+        __syncwarp();
+    }
+}
+
+__device__ __forceinline__ void decode_item_gen(const GenCache *cache, const TileJob &common, uint32_t item, ItemMeta &m)
+{
+    const GenEntry &e = cache->e;
+    // divisions by this entry's own numbers as multiply-and-shift; one slice and one entry (the usual case) need none
+    const uint32_t q0 = item - e.item_start;
+    const uint32_t q1 = fast_div(q0, e.bpb_magic, e.bpb_shift);
+    const uint32_t cb = q0 - q1 * e.boxes_per_band;
+    const uint32_t q2 = fast_div(q1, e.bands_magic, e.bands_shift);
+    const uint32_t k = q1 - q2 * e.bands;
     m.rt = e.band_first + k * e.band_step;
-    m.z = q % e.Z;
-    m.w = q / e.Z;
-    m.b = cur;
+    if (e.Z == 1u) {
+        m.z = 0;
+        m.w = q2;
+    } else {
+        m.w = q2 / e.Z;
+        m.z = q2 - m.w * e.Z;
+    }
+    m.b = cache->loaded;
     m.ct0 = cb * common.box_tiles;
     m.ntiles = min(common.box_tiles, e.Ct - m.ct0);
 }
@@ -93,8 +133,10 @@ static __device__ WorkCounter g_pack_work[kWorkSlots];
 template <bool G> struct TableOf { using type = PtrTable; };
 template <> struct TableOf<true> { using type = GenTable; };
 
+// The general flavour is held to the register budget of the plain one (five CTAs of 288 threads per SM for the 8-bit
+// formats): what it spills sits on the policy-only paths.
 template <int M, int ES, bool AF, bool G>
-__global__ void __launch_bounds__(kStagedThreads)
+__global__ void __launch_bounds__(kStagedThreads, (G && M == 7 && ES == 4) ? 5 : 0)
 pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ typename TableOf<G>::type ptrs, unsigned int *status)
 {
     using Cfg = PackCfg<M, ES>;
@@ -106,6 +148,10 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
     uint64_t *full = reinterpret_cast<uint64_t *>(meta + S);
     uint64_t *empty = full + S;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + S);
+    // general flavour only (see PackCfg::gen_extra_bytes)
+    GenCache *gcache = reinterpret_cast<GenCache *>(reinterpret_cast<uint8_t *>(empty + S) + 16);
+    uint32_t *gstarts = reinterpret_cast<uint32_t *>(gcache + 1);
+    uint64_t *gdst = reinterpret_cast<uint64_t *>(gstarts + kMaxGen + 2);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rec = job.tile_bytes, hdr = job.header_bytes;
@@ -116,8 +162,10 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
             mbar_init(&empty[s], 1);
         }
         *abort_flag = 0;
+        if constexpr (G) gcache->loaded = 0xffffffffu;
         mbar_fence_init();
     }
+    if constexpr (G) gen_load_starts(ptrs, job.total_items, gstarts, tid, kStagedThreads);
     // header bytes of the staged records are written once: they stay zero for every item
     for (int i = tid; i < 2 * Cfg::out_buf_bytes / 4; i += kStagedThreads) reinterpret_cast<uint32_t *>(out_buf)[i] = 0;
     fence_async_smem();
@@ -126,25 +174,37 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
     if (warp == kConsumerWarps) {
         // ---------------------------------------------------------------- producer warp
         WorkCounter *wc = &g_pack_work[job.work_slot];
-        uint32_t it = 0, cur = 0;
+        uint32_t it = 0;
         bool ok = true;
         uint32_t item = work_fetch_get(work_fetch_issue(wc, lane));
         for (; item < job.total_items; ++it) {
             const uint32_t next_issued = work_fetch_issue(wc, lane);   // asked for now, read after this item's copies are on their way
             const int s = it % S;
             const uint32_t ph = (it / S) & 1u;
+            ItemMeta m;
+            const uint8_t *src;
+            uint8_t *tile_dst = nullptr;
+            if constexpr (G) {
+                // table look-up and index arithmetic first: they hide behind the wait for a free stage
+                gen_find_entry(ptrs, gstarts, item, gcache, lane);
+                decode_item_gen(gcache, job, item, m);
+                const GenEntry &e = gcache->e;
+                src = e.rm + (uint64_t)m.w * e.stride_w + (uint64_t)m.z * e.stride_z + ((uint64_t)m.rt * 32u + lane) * e.stride_r +
+                      (uint64_t)m.ct0 * 32u * ES;
+                if ((uint32_t)lane < m.ntiles) {
+                    TileJob ej;
+                    job_of_entry(job, e, ej);
+                    tile_dst = e.q + tile_record_offset(ej, m.w, m.z, m.rt, m.ct0 + lane);
+                }
+            }
             if (!mbar_wait_bounded(&empty[s], ph ^ 1u, abort_flag, status, BUDA_DEVSTAT_PACK_EMPTY_WAIT)) {
                 ok = false;
                 break;
             }
-            ItemMeta m;
-            const uint8_t *src;
             if constexpr (G) {
-                decode_item_gen(ptrs, job, item, cur, m);
-                const GenEntry &e = ptrs.e[m.b];
-                src = e.rm + (uint64_t)m.w * e.stride_w + (uint64_t)m.z * e.stride_z + ((uint64_t)m.rt * 32u + lane) * e.stride_r +
-                      (uint64_t)m.ct0 * 32u * ES;
-            } else {
+                if ((uint32_t)lane < m.ntiles) gdst[s * 16 + lane] = reinterpret_cast<uint64_t>(tile_dst);
+            }
+            if constexpr (!G) {
                 decode_item(job, item, m);
                 src = ptrs.src[m.b] + (uint64_t)m.w * job.stride_w + rm_z_offset(job, m.z) +
                       ((uint64_t)m.rt * 32u + lane) * job.stride_r + (uint64_t)m.ct0 * 32u * ES;
@@ -185,6 +245,13 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
 
     // -------------------------------------------------------------------- consumer warps
     const int fr = lane & 15;
+    // A thread always meets the same face: the face column bc advances by the (even) number of consumer warps, so
+    // bc % 2 stays warp % 2.  Its block's place in the record is therefore fixed for the whole launch.
+    const int my_face = ((lane >> 4) << 1) | (warp & 1);
+    const int blk = (G ? (int)job.pol.face_pos[my_face] : my_face) * 16 + fr;
+    const int exp_idx = (G && job.pol.exp_be) ? (blk ^ 3) : blk;
+    // general flavour: the policy's arithmetic only where the policy asks for it (uniform over the launch)
+    const bool plain_codec = !G || !(job.pol.trunc | job.pol.bump | job.pol.datum_be);
     uint32_t it = 0;
     for (;; ++it) {
         const int s = it % S;
@@ -192,6 +259,10 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
         const bool ok = mbar_wait_bounded(&full[s], ph, abort_flag, status, BUDA_DEVSTAT_PACK_FULL_WAIT);
         const ItemMeta m = meta[s];
         if (ok && m.ntiles == 0) break;   // the producer's end marker: the same for every consumer thread
+        uint64_t my_dst = 0;              // general flavour: where this lane's tile record goes (read while the stage is still ours)
+        if constexpr (G) {
+            if (ok && warp == 0 && (uint32_t)lane < m.ntiles) my_dst = gdst[s * 16 + lane];
+        }
         uint8_t *ob = out_buf + (it & 1u) * Cfg::out_buf_bytes;
         const uint8_t *stage = in_stage + s * Cfg::in_stage_bytes;
 
@@ -201,7 +272,6 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
 #pragma unroll
           for (int bc = warp; bc < 2 * Cfg::box; bc += kConsumerWarps) {  // face column: tile bc/2, left/right face bc%2
             const int tile_in_box = bc >> 1;
-            const int face = ((lane >> 4) << 1) | (bc & 1);
             if ((uint32_t)tile_in_box < m.ntiles) {
                 uint32_t x[16];
                 const uint8_t *p = stage + lane * Cfg::pitch + bc * 16 * ES;
@@ -218,13 +288,7 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
                     const uint4 v0 = *reinterpret_cast<const uint4 *>(p), v1 = *reinterpret_cast<const uint4 *>(p + 16);
                     const uint32_t h[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
                     // packed-pair encoder; false at the ends of the exponent range
-                    if (!AF && (!G || !(job.pol.trunc | job.pol.bump))) {
-                        encoded = bfp_encode16_bf16<MM>(h, E, d);
-                        if (G && encoded && job.pol.datum_be) {
-#pragma unroll
-                            for (int w = 0; w < BfpTraits<MM>::words; w++) d[w] = reverse_datum_fields<MM>(d[w]);
-                        }
-                    }
+                    if (!AF && plain_codec) encoded = bfp_encode16_bf16<MM>(h, E, d);
                     if (!encoded) {
 #pragma unroll
                         for (int k = 0; k < 8; k++) {
@@ -239,12 +303,11 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
                     }
                 }
                 if (!encoded) {
-                    if constexpr (G) bfp_encode16_policy<MM>(x, E, d, job.pol, AF ? 143u : 255u);
-                    else bfp_encode16<MM>(x, E, d);
+                    if (plain_codec) bfp_encode16<MM>(x, E, d);
+                    else bfp_encode16_policy<MM>(x, E, d, job.pol, AF ? 143u : 255u);
                 }
                 uint8_t *r = ob + tile_in_box * rec + hdr;
-                const int blk = (G ? (int)job.pol.face_pos[face] : face) * 16 + fr;
-                r[(G && job.pol.exp_be) ? (blk ^ 3) : blk] = (uint8_t)(AF ? a_exponent_byte(E) : E);
+                r[exp_idx] = (uint8_t)(AF ? a_exponent_byte(E) : E);
                 uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
                 if (MM == 7) *reinterpret_cast<uint4 *>(q) = make_uint4(d[0], d[1 % BfpTraits<MM>::words], d[2 % BfpTraits<MM>::words], d[3 % BfpTraits<MM>::words]);
                 else if (MM == 3) *reinterpret_cast<uint2 *>(q) = make_uint2(d[0], d[1 % BfpTraits<MM>::words]);
@@ -273,13 +336,8 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
         if (tid == 0) mbar_arrive(&empty[s]);
         if (warp == 0 && (uint32_t)lane < m.ntiles) {
             uint8_t *dst;
-            if constexpr (G) {
-                TileJob ej;
-                job_of_entry(job, ptrs.e[m.b], ej);
-                dst = ptrs.e[m.b].q + tile_record_offset(ej, m.w, m.z, m.rt, m.ct0 + lane);
-            } else {
-                dst = ptrs.dst[m.b] + tile_record_offset(job, m.w, m.z, m.rt, m.ct0 + lane);
-            }
+            if constexpr (G) dst = reinterpret_cast<uint8_t *>(my_dst);
+            else dst = ptrs.dst[m.b] + tile_record_offset(job, m.w, m.z, m.rt, m.ct0 + lane);
             bulk_s2g(dst, ob + lane * rec, rec);
             bulk_commit();
         }
@@ -382,6 +440,41 @@ __device__ __forceinline__ void load4(const uint8_t *p, bool vec, uint32_t (&x)[
     }
 }
 
+// One element of the row-major side under a source view (see SourceView); r, c are coordinates in the tile-aligned
+// shape the queue covers.  base is the tensor's first byte.
+template <int ES>
+__device__ __forceinline__ uint32_t fetch_view_elem(const TileJob &j, const uint8_t *base, uint32_t w, uint32_t z, uint32_t r, uint32_t c)
+{
+    const SourceView &v = j.view;
+    const uint8_t *p;
+    if (v.mode == kSrcPadded) {
+        if (r >= v.valid_r || c >= v.valid_c) return 0u;
+        p = base + (uint64_t)w * j.stride_w + rm_z_offset(j, z) + (uint64_t)r * j.stride_r + (uint64_t)c * ES;
+    } else if (v.mode == kSrcEmbedding) {
+        const uint64_t a = (uint64_t)(c >> 5) * 32u + (r & 31u);
+        if (a * 32u >= v.emb_group) return 0u;
+        const uint64_t flat = (uint64_t)(r >> 5) * v.emb_group + a * 32u + (c & 31u);
+        if (flat >= v.emb_count) return ES == 4 ? 0xffffffffu : ES == 2 ? 0xffffu : 0xffu;
+        p = base + (uint64_t)w * j.stride_w + flat * ES;
+    } else {
+        if (r >= v.ps_noff * v.ps_z || c >= v.ps_hs * v.ps_ws) return 0u;
+        const uint32_t k = r / v.ps_z, zc = r - k * v.ps_z;
+        const uint32_t hr = c / v.ps_ws, wc = c - hr * v.ps_ws;
+        const uint32_t y = hr * v.ps_stride + (uint32_t)v.ps_y[k], x = wc * v.ps_stride + (uint32_t)v.ps_x[k];
+        if (y >= v.ps_h || x >= v.ps_w) return 0u;
+        p = base + (uint64_t)w * j.stride_w + (uint64_t)zc * j.stride_z + (uint64_t)y * j.stride_r + (uint64_t)x * ES;
+    }
+    if (ES == 4) {
+        if ((reinterpret_cast<uintptr_t>(p) & 3u) == 0) return *reinterpret_cast<const uint32_t *>(p);
+        return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
+    }
+    if (ES == 2) {
+        if ((reinterpret_cast<uintptr_t>(p) & 1u) == 0) return *reinterpret_cast<const uint16_t *>(p);
+        return (uint32_t)p[0] | ((uint32_t)p[1] << 8);
+    }
+    return p[0];
+}
+
 // Encode (or relayout) the four elements a lane holds of block `blk` and store them into tile record `r`.
 // blk is the block's position in the record (face position * 16 + face row).
 template <int M, int ES, bool AF, bool G>
@@ -461,7 +554,20 @@ pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
         uint8_t *r = ptrs.dst[b] + tile_record_offset(job, w, z, rt, ct);
         if (hdr && lane < 8) reinterpret_cast<uint32_t *>(r)[lane] = 0;
         r += hdr;
-        if (vec_ok) {
+        if (G && job.view.mode != kSrcDense) {
+            // the source is read through a view: element by element, each with its own address or fill value
+#pragma unroll 1
+            for (uint32_t hf = 0; hf < 8; hf++) {
+                const uint32_t face = hf >> 1, half = hf & 1u;
+                const uint32_t tr = (face >> 1) * 16u + half * 8u + (lane >> 2);
+                const uint32_t c0 = ct * 32u + (face & 1u) * 16u + (lane & 3) * 4u;
+                uint32_t x[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) x[i] = fetch_view_elem<ES>(job, ptrs.src[b], w, z, rt * 32u + tr, c0 + i);
+                const uint32_t pos = (uint32_t)job.pol.face_pos[face];
+                direct_encode_store<M, ES, AF, G>(x, pos * 16u + half * 8u + (lane >> 2), r, lane, job.pol);
+            }
+        } else if (vec_ok) {
 #pragma unroll 1
             for (int g = 0; g < 8; g += GR) {
                 uint32_t xs[GR][4];
@@ -510,11 +616,11 @@ static cudaError_t launch_staged(const TileJob &job, const typename TableOf<G>::
     int per_sm = per_sm_cache[dev].load(std::memory_order_acquire);
     if (per_sm == 0) {
         cudaError_t e = cudaFuncSetAttribute(pack_staged_kernel<M, ES, AF, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             Cfg::smem_bytes);
+                                             Cfg::template smem_for<G>());
         if (e != cudaSuccess) return e;
         int n = 0;
         e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, pack_staged_kernel<M, ES, AF, G>, kStagedThreads,
-                                                          Cfg::smem_bytes);
+                                                          Cfg::template smem_for<G>());
         if (e != cudaSuccess) return e;
         per_sm = n < 1 ? 1 : (n > 5 ? 5 : n);
         per_sm_cache[dev].store(per_sm, std::memory_order_release);
@@ -533,7 +639,7 @@ static cudaError_t launch_staged(const TileJob &job, const typename TableOf<G>::
     const int slot = take_work_slot(g_pack_slots[dev], stream, &tracked);
     if (slot < 0) return cudaErrorLaunchOutOfResources;   // the counters reserved for graph capture are used up
     launch_job.work_slot = (uint32_t)slot;
-    pack_staged_kernel<M, ES, AF, G><<<grid, kStagedThreads, Cfg::smem_bytes, stream>>>(launch_job, launch_table, status);
+    pack_staged_kernel<M, ES, AF, G><<<grid, kStagedThreads, Cfg::template smem_for<G>(), stream>>>(launch_job, launch_table, status);
     const cudaError_t e = cudaGetLastError();
     work_slot_launched(g_pack_slots[dev], slot, stream, tracked);
     return e;

@@ -41,6 +41,11 @@ struct UnpackCfg {
     static constexpr int out_bufs = 2;
     static constexpr int smem_bytes = stages * in_stage_bytes + out_bufs * out_buf_bytes + stages * (int)sizeof(UItemMeta) +
                                       2 * stages * 8 + 16;
+    // general flavour: a copy of the table entry in use, the first work item of every entry, and per stage where the
+    // item's band starts in the row-major tensor and its row stride (worked out by the producer, which holds the entry)
+    static constexpr int gen_extra_bytes = 136 + (kMaxGen + 1) * 4 + 4 + stages * 2 * 8;
+    template <bool G>
+    static constexpr int smem_for() { return smem_bytes + (G ? gen_extra_bytes : 0); }
 };
 
 __device__ __forceinline__ void decode_uitem(const TileJob &job, uint32_t item, UItemMeta &m)
@@ -65,21 +70,56 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi)
     return d;
 }
 
-// General flavour: work item -> table entry (the cursor only moves forward), then the position inside that tensor's
-// selection of tile rows.
-__device__ __forceinline__ void decode_uitem_gen(const GenTable &tab, const TileJob &common, uint32_t item, uint32_t &cur, UItemMeta &m)
+// General flavour.  Kernel parameters are slow to read with a run-time index, so the table is touched as little as
+// possible: every entry's first work item is copied to shared memory once per CTA, the entry a work item belongs to is
+// found there by bisection, and the entry itself is copied to shared memory when the producer moves on to it.
+struct UGenCache {
+    GenEntry e;                       // 128 bytes
+    uint32_t loaded, pad;             // index of the entry held in e
+};
+static_assert(sizeof(UGenCache) == 136, "shared-memory plan of the general flavour");
+
+__device__ __forceinline__ void ugen_load_starts(const GenTable &tab, uint32_t total_items, uint32_t *starts, int tid, int nthreads)
 {
-    while (cur + 1u < tab.n && item >= tab.e[cur + 1u].item_start) cur++;
-    const GenEntry &e = tab.e[cur];
-    uint32_t q = item - e.item_start;
-    const uint32_t cb = q % e.boxes_per_band;
-    q /= e.boxes_per_band;
-    const uint32_t k = q % e.bands;
-    q /= e.bands;
+    for (uint32_t i = (uint32_t)tid; i <= tab.n; i += (uint32_t)nthreads) starts[i] = i < tab.n ? tab.e[i].item_start : total_items;
+}
+
+// whole producer warp; returns with *cache holding the entry of `item`
+__device__ __forceinline__ void ugen_find_entry(const GenTable &tab, const uint32_t *starts, uint32_t item, UGenCache *cache, int lane)
+{
+    const uint32_t idx = cache->loaded;
+    if (idx >= tab.n || item < starts[idx] || item >= starts[idx + 1u]) {
+        uint32_t lo = 0, hi = tab.n;          // largest index with starts[index] <= item
+        while (hi - lo > 1u) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if (starts[mid] <= item) lo = mid; else hi = mid;
+        }
+        __syncwarp();
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(&tab.e[lo]);
+        reinterpret_cast<uint32_t *>(&cache->e)[lane] = src[lane];   // 32 lanes x 4 bytes = the entry
+        if (lane == 31) cache->loaded = lo;
+        __syncwarp();
+    }
+}
+
+__device__ __forceinline__ void decode_uitem_gen(const UGenCache *cache, const TileJob &common, uint32_t item, UItemMeta &m)
+{
+    const GenEntry &e = cache->e;
+    // divisions by this entry's own numbers as multiply-and-shift; one slice and one entry (the usual case) need none
+    const uint32_t q0 = item - e.item_start;
+    const uint32_t q1 = fast_div(q0, e.bpb_magic, e.bpb_shift);
+    const uint32_t cb = q0 - q1 * e.boxes_per_band;
+    const uint32_t q2 = fast_div(q1, e.bands_magic, e.bands_shift);
+    const uint32_t k = q1 - q2 * e.bands;
     m.rt = e.band_first + k * e.band_step;
-    m.z = q % e.Z;
-    m.w = q / e.Z;
-    m.b = cur;
+    if (e.Z == 1u) {
+        m.z = 0;
+        m.w = q2;
+    } else {
+        m.w = q2 / e.Z;
+        m.z = q2 - m.w * e.Z;
+    }
+    m.b = cache->loaded;
     m.ct0 = cb * common.box_tiles;
     m.ntiles = min(common.box_tiles, e.Ct - m.ct0);
 }
@@ -102,6 +142,10 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
     uint64_t *full = reinterpret_cast<uint64_t *>(meta + S);
     uint64_t *empty = full + S;
     volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + S);
+    // general flavour only (see UnpackCfg::gen_extra_bytes)
+    UGenCache *gcache = reinterpret_cast<UGenCache *>(reinterpret_cast<uint8_t *>(empty + S) + 16);
+    uint32_t *gstarts = reinterpret_cast<uint32_t *>(gcache + 1);
+    uint64_t *gband = reinterpret_cast<uint64_t *>(gstarts + kMaxGen + 2);   // [stage][band start, row stride]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rec = job.tile_bytes, hdr = job.header_bytes;
@@ -112,43 +156,59 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
             mbar_init(&empty[s], 1);
         }
         *abort_flag = 0;
+        if constexpr (G) gcache->loaded = 0xffffffffu;
         mbar_fence_init();
     }
+    if constexpr (G) ugen_load_starts(ptrs, job.total_items, gstarts, tid, kUStagedThreads);
     __syncthreads();
 
     if (warp == kUConsumerWarps) {
         // ---------------------------------------------------------------- producer warp
         WorkCounter *wc = &g_unpack_work[job.work_slot];
-        uint32_t it = 0, cur = 0;
+        uint32_t it = 0;
         bool ok = true;
         uint32_t item = work_fetch_get(work_fetch_issue(wc, lane));
         for (; item < job.total_items; ++it) {
             const uint32_t next_issued = work_fetch_issue(wc, lane);   // asked for now, read after this item's copies are on their way
             const int s = it % S;
             const uint32_t ph = (it / S) & 1u;
+            UItemMeta m;
+            const uint8_t *src = nullptr;
+            uint64_t band_start = 0, band_stride = 0;
+            if constexpr (G) {
+                // table look-up and address arithmetic first: they hide behind the wait for a free stage
+                ugen_find_entry(ptrs, gstarts, item, gcache, lane);
+                decode_uitem_gen(gcache, job, item, m);
+                const GenEntry &e = gcache->e;
+                if ((uint32_t)lane < m.ntiles) {
+                    TileJob ej;
+                    job_of_entry(job, e, ej);
+                    src = e.q + tile_record_offset(ej, m.w, m.z, m.rt, m.ct0 + lane);
+                }
+                band_stride = e.stride_r;
+                band_start = reinterpret_cast<uint64_t>(e.rm) + (uint64_t)m.w * e.stride_w + (uint64_t)m.z * e.stride_z +
+                             (uint64_t)m.rt * 32u * e.stride_r + (uint64_t)m.ct0 * 32u * ES;
+            }
             if (!mbar_wait_bounded(&empty[s], ph ^ 1u, abort_flag, status, BUDA_DEVSTAT_UNPACK_EMPTY_WAIT)) {
                 ok = false;
                 break;
             }
-            UItemMeta m;
-            if constexpr (G) decode_uitem_gen(ptrs, job, item, cur, m);
-            else decode_uitem(job, item, m);
+            if constexpr (G) {
+                if (lane == 0) {
+                    gband[2 * s] = band_start;
+                    gband[2 * s + 1] = band_stride;
+                }
+            }
+            if constexpr (!G) {
+                decode_uitem(job, item, m);
+                if ((uint32_t)lane < m.ntiles) src = ptrs.src[m.b] + tile_record_offset(job, m.w, m.z, m.rt, m.ct0 + lane);
+            }
             if (lane == 0) {
                 meta[s] = m;
                 mbar_arrive_expect_tx(&full[s], m.ntiles * rec);
             }
             __syncwarp();
-            if ((uint32_t)lane < m.ntiles) {
-                const uint8_t *src;
-                if constexpr (G) {
-                    TileJob ej;
-                    job_of_entry(job, ptrs.e[m.b], ej);
-                    src = ptrs.e[m.b].q + tile_record_offset(ej, m.w, m.z, m.rt, m.ct0 + lane);
-                } else {
-                    src = ptrs.src[m.b] + tile_record_offset(job, m.w, m.z, m.rt, m.ct0 + lane);
-                }
-                bulk_g2s(in_stage + s * Cfg::in_stage_bytes + lane * rec, src, rec, &full[s]);
-            }
+            if ((uint32_t)lane < m.ntiles) bulk_g2s(in_stage + s * Cfg::in_stage_bytes + lane * rec, src, rec, &full[s]);
             item = work_fetch_get(next_issued);
         }
         if (ok) {
@@ -184,6 +244,13 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
         const bool ok = mbar_wait_bounded(&full[s], ph, abort_flag, status, BUDA_DEVSTAT_UNPACK_FULL_WAIT);
         const UItemMeta m = meta[s];
         if (ok && m.ntiles == 0) break;   // the producer's end marker: the same for every consumer thread
+        uint64_t g_start = 0, g_stride = 0;   // general flavour: read while the stage is still ours
+        if constexpr (G) {
+            if (ok) {
+                g_start = gband[2 * s];
+                g_stride = gband[2 * s + 1];
+            }
+        }
         uint8_t *ob = out_buf + (it % Cfg::out_bufs) * Cfg::out_buf_bytes;
         const uint8_t *stage = in_stage + s * Cfg::in_stage_bytes;
 
@@ -263,10 +330,8 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
             uint8_t *dst0;
             uint64_t stride_r;
             if constexpr (G) {
-                const GenEntry &e = ptrs.e[m.b];
-                stride_r = e.stride_r;
-                dst0 = const_cast<uint8_t *>(e.rm) + (uint64_t)m.w * e.stride_w + (uint64_t)m.z * e.stride_z +
-                       (uint64_t)m.rt * 32u * stride_r + (uint64_t)m.ct0 * 32u * ES;
+                stride_r = g_stride;
+                dst0 = reinterpret_cast<uint8_t *>(g_start);
             } else {
                 stride_r = job.stride_r;
                 dst0 = ptrs.dst[m.b] + (uint64_t)m.w * job.stride_w + rm_z_offset(job, m.z) +
@@ -427,11 +492,11 @@ static cudaError_t launch_ustaged(const TileJob &job, const typename UTableOf<G>
     int per_sm = per_sm_cache[dev].load(std::memory_order_acquire);
     if (per_sm == 0) {
         cudaError_t e = cudaFuncSetAttribute(unpack_staged_kernel<M, ES, AF, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             Cfg::smem_bytes);
+                                             Cfg::template smem_for<G>());
         if (e != cudaSuccess) return e;
         int n = 0;
         e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, unpack_staged_kernel<M, ES, AF, G>, kUStagedThreads,
-                                                          Cfg::smem_bytes);
+                                                          Cfg::template smem_for<G>());
         if (e != cudaSuccess) return e;
         per_sm = n < 1 ? 1 : (n > 4 ? 4 : n);
         per_sm_cache[dev].store(per_sm, std::memory_order_release);
@@ -450,7 +515,7 @@ static cudaError_t launch_ustaged(const TileJob &job, const typename UTableOf<G>
     const int slot = take_work_slot(g_unpack_slots[dev], stream, &tracked);
     if (slot < 0) return cudaErrorLaunchOutOfResources;   // the counters reserved for graph capture are used up
     launch_job.work_slot = (uint32_t)slot;
-    unpack_staged_kernel<M, ES, AF, G><<<grid, kUStagedThreads, Cfg::smem_bytes, stream>>>(launch_job, launch_table, status);
+    unpack_staged_kernel<M, ES, AF, G><<<grid, kUStagedThreads, Cfg::template smem_for<G>(), stream>>>(launch_job, launch_table, status);
     const cudaError_t e = cudaGetLastError();
     work_slot_launched(g_unpack_slots[dev], slot, stream, tracked);
     return e;

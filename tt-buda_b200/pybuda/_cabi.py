@@ -60,6 +60,17 @@ class BfpPolicy(ctypes.Structure):
         super().__init__(rounding, overflow, (ctypes.c_uint8 * 4)(*face_order), exponent_order, datum_order)
 
 
+class SourceView(ctypes.Structure):
+    """buda_source_view"""
+
+    _fields_ = [
+        ("mode", ctypes.c_uint32), ("valid_r", ctypes.c_uint32), ("valid_c", ctypes.c_uint32),
+        ("emb_count", ctypes.c_uint64), ("emb_group", ctypes.c_uint64),
+        ("ps_stride", ctypes.c_uint32), ("ps_z", ctypes.c_uint32), ("ps_h", ctypes.c_uint32), ("ps_w", ctypes.c_uint32),
+        ("ps_n_offsets", ctypes.c_uint32), ("ps_xy", ctypes.c_int32 * 128),
+    ]
+
+
 _vp, _i, _i64, _u64, _u32, _f = (ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_uint64, ctypes.c_uint32,
                                  ctypes.c_float)
 _jp, _pp = ctypes.POINTER(TensorJob), ctypes.POINTER(BfpPolicy)
@@ -90,6 +101,7 @@ _SIGS = {
     "buda_unpack_untilize_host": (_i, [_vp, _i, _i, _gp, _vp, _i, _u32p, _u64p, _vp]),
     "buda_queue_bytes": (_i64, [_gp, _i, _i, _u32]),
     "buda_queue_write": (_i, [_vp, _i, _i, _u32p, _u64p, _gp, _i, _i, _vp, _u32, _u32, _vp]),
+    "buda_queue_write_view": (_i, [_vp, _i, _u32p, _u64p, ctypes.POINTER(SourceView), _gp, _i, _i, _vp, _u64, _u32, _u32, _vp]),
     "buda_queue_read": (_i, [_vp, _i, _i, _gp, _u32, _u32, _vp, _i, _i, _u32p, _u64p, _vp]),
     "buda_queue_read_stacked": (_i, [_vp, _i, _i, _gp, _u32, _u32, _u32, _u32, _u32, _i, _vp, _i, _vp]),
     "buda_malloc": (_i, [_vpp, _u64]),

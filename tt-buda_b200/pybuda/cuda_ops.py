@@ -329,30 +329,48 @@ def _job_table(tensors, images, q_df, geoms, with_header, bands):
     return jobs
 
 
+class TensorJobs:
+    """A prepared job table: n CUDA tensors of one dtype but any shapes, their queue images, geometries and
+    (optionally) selections of tile rows.  Building the table costs a few microseconds of Python per tensor, so a
+    caller that converts the same set repeatedly (a parameter set every step) prepares it once; pack() and unpack()
+    are then one C call each."""
+
+    def __init__(self, tensors, q_df, images=None, geoms=None, with_header=False, bands=None):
+        _need_cuda(*tensors)
+        self.tensors = list(tensors)
+        self.q_df, self.with_header = int(q_df), bool(with_header)
+        self.rm_df = int(_TORCH_TO_DF[tensors[0].dtype])
+        if images is None:
+            images = []
+            for i, t in enumerate(tensors):
+                shape, _ = _desc(t)
+                g = geoms[i] if geoms is not None and geoms[i] is not None else QueueGeom.for_shape(shape)
+                images.append(torch.empty(_cabi.tilized_bytes(g, shape, self.q_df, with_header), dtype=torch.uint8, device=t.device))
+        _need_cuda(*images)
+        self.images = list(images)
+        self._jobs = _job_table(self.tensors, self.images, q_df, geoms, with_header, bands)
+        self._n = len(self.tensors)
+
+    def pack(self):
+        """tensors -> images"""
+        with torch.cuda.device(self.tensors[0].device):
+            check(_cabi.lib.buda_tilize_pack_jobs(self._n, self._jobs, self.rm_df, self.q_df, int(self.with_header), _stream()))
+        return self.images
+
+    def unpack(self):
+        """images -> tensors"""
+        with torch.cuda.device(self.tensors[0].device):
+            check(_cabi.lib.buda_unpack_untilize_jobs(self._n, self._jobs, self.q_df, int(self.with_header), self.rm_df, _stream()))
+        return self.tensors
+
+
 def tilize_pack_jobs(tensors, dst_df, geoms=None, with_header=False, outs=None, bands=None):
     """Tilize (and block-float pack) CUDA tensors of DIFFERENT shapes (one dtype) in as few launches as possible.
     geoms: per-tensor QueueGeom or None; bands: per-tensor (first, step, count) selection of tile rows or None.
     Returns the list of uint8 image tensors."""
-    _need_cuda(*tensors)
-    src_df = _TORCH_TO_DF[tensors[0].dtype]
-    if outs is None:
-        outs = []
-        for i, t in enumerate(tensors):
-            shape, _ = _desc(t)
-            g = geoms[i] if geoms is not None and geoms[i] is not None else QueueGeom.for_shape(shape)
-            outs.append(torch.empty(_cabi.tilized_bytes(g, shape, int(dst_df), with_header), dtype=torch.uint8, device=t.device))
-    jobs = _job_table(tensors, outs, dst_df, geoms, with_header, bands)
-    with torch.cuda.device(tensors[0].device):
-        check(_cabi.lib.buda_tilize_pack_jobs(len(tensors), jobs, int(src_df), int(dst_df), int(with_header), _stream()))
-    return outs
+    return TensorJobs(tensors, dst_df, outs, geoms, with_header, bands).pack()
 
 
 def unpack_untilize_jobs(images, src_df, outs, geoms=None, with_header=False, bands=None):
     """Inverse of tilize_pack_jobs: images[i] -> outs[i] (CUDA tensors of one dtype, any shapes)."""
-    _need_cuda(*images)
-    _need_cuda(*outs)
-    dst_df = _TORCH_TO_DF[outs[0].dtype]
-    jobs = _job_table(outs, images, src_df, geoms, with_header, bands)
-    with torch.cuda.device(outs[0].device):
-        check(_cabi.lib.buda_unpack_untilize_jobs(len(outs), jobs, int(src_df), int(with_header), int(dst_df), _stream()))
-    return outs
+    return TensorJobs(outs, src_df, images, geoms, with_header, bands).unpack()
