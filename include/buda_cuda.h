@@ -242,7 +242,8 @@ int buda_queue_read(const void *queue_base, int src_df, int with_header, const b
  * (w, z, r, c) of that shape comes from:
  *   BUDA_SRC_PADDED           the tensor [w, t, valid_r, valid_c] (its own strides in strides_bytes), zero outside:
  *                             the tile padding of pad_pytorch_tensor_to_buda (pybuda/pybuda/tensor.py:805-877; a
- *                             tile-broadcast dim is a stride of 0) applied to a ReinterpretShape view (tensor.py:1407-1413)
+ *                             tile-broadcast dim, of size 1, stands for its whole tile: bcast_r / bcast_c) applied to a
+ *                             ReinterpretShape view (tensor.py:1407-1413)
  *   BUDA_SRC_EMBEDDING_INDEX  a vector of `emb_count` row indices per entry (entry stride strides_bytes[0]) laid out
  *                             for an embedding op (_embedding_index, pybuda/pybuda/tensor.py:1382-1405): each 32x32
  *                             tile is 1024 consecutive indices, emb_group indices per queue tile row, all ones past
@@ -255,6 +256,7 @@ enum { BUDA_SRC_DENSE = 0, BUDA_SRC_PADDED = 1, BUDA_SRC_EMBEDDING_INDEX = 2, BU
 typedef struct buda_source_view {
     uint32_t mode;
     uint32_t valid_r, valid_c;
+    uint32_t bcast_r, bcast_c;      /* BUDA_SRC_PADDED: rows / columns all read row 0 / column 0 (valid_r / valid_c == 1) */
     uint64_t emb_count, emb_group;
     uint32_t ps_stride, ps_z, ps_h, ps_w;
     uint32_t ps_n_offsets;          /* 1..64 */

@@ -330,3 +330,63 @@ def prestride_act(act, stride):
     out = np.concatenate(phases, axis=-3)
     return out.reshape(w, 1, out.shape[1], out.shape[2] * out.shape[3])
 
+
+
+# ------------------------------------------------------------------------------------------------
+# Runtime tensor transforms of the push path, restated in numpy (checker for the kernels' source views).
+# Pinned by tests/golden/transform_golden.npz, which the reference's own functions produced.
+# ------------------------------------------------------------------------------------------------
+def _align32(v):
+    return (v + 31) // 32 * 32
+
+
+def embedding_index(indices, count, q_rt):
+    """Row indices laid out for an embedding op (pybuda/pybuda/tensor.py:1382-1405): padded to whole tiles with
+    all-ones from position `count` on, cut into q_rt groups (one per queue tile row), every 32 consecutive indices a
+    row, rows zero-padded to a multiple of 32, and each 32x32 block of rows transposed into place so that a tile holds
+    1024 consecutive indices.  Returns [w, 1, q_rt * 32, columns]."""
+    idx = np.atleast_2d(np.asarray(indices))
+    w, n = idx.shape
+    n_pad = _align32(n)
+    flat = np.zeros((w, n_pad), dtype=idx.dtype)
+    flat[:, :n] = idx
+    flat[:, count:] = ~np.zeros((), dtype=idx.dtype)
+    assert n_pad % (q_rt * 32) == 0, "the padded index count must split evenly over the queue's tile rows"
+    rows = n_pad // q_rt // 32
+    p_rows = _align32(rows)
+    t = np.zeros((w, q_rt, p_rows, 32), dtype=idx.dtype)
+    t[:, :, :rows, :] = flat.reshape(w, q_rt, rows, 32)
+    t = t.reshape(w, q_rt, p_rows // 32, 32, 32).transpose(0, 1, 3, 2, 4)
+    return np.ascontiguousarray(t).reshape(w, 1, q_rt * 32, p_rows)
+
+
+def prestride_act(act, stride, xy_offsets=None):
+    """Convolution activation cut into its stride phases (golden pybuda/pybuda/op/eval/pybuda/tm.py:316-335; the
+    offsets are the queue's StrideDescriptor, pybuda/pybuda/tensor.py:1415-1422): [w, z, H, W], zero-padded to
+    multiples of the stride -> [w, 1, n_offsets * z, ceil(H/s) * ceil(W/s)]."""
+    act = np.asarray(act)
+    w, z, h, wd = act.shape
+    if xy_offsets is None:
+        xy_offsets = [(x, y) for y in range(stride) for x in range(stride)]
+    hp, wp = -(-h // stride) * stride, -(-wd // stride) * stride
+    padded = np.zeros((w, z, hp, wp), dtype=act.dtype)
+    padded[:, :, :h, :wd] = act
+    phases = [padded[:, :, y::stride, x::stride] for (x, y) in xy_offsets]
+    out = np.concatenate(phases, axis=1)
+    return np.ascontiguousarray(out).reshape(w, 1, out.shape[1], out.shape[2] * out.shape[3])
+
+
+def pad_to_tiles(x, replicate_rows=False, replicate_cols=False):
+    """Rows and columns of a 4-D tensor rounded up to whole 32x32 tiles: zeros, or the single row / column repeated
+    for a tile-broadcast dim (pad_pytorch_tensor_to_buda, pybuda/pybuda/tensor.py:805-877)."""
+    x = np.asarray(x)
+    w, z, r, c = x.shape
+    out = np.zeros((w, z, _align32(r), _align32(c)), dtype=x.dtype)
+    out[:, :, :r, :c] = x
+    if replicate_cols:
+        assert c == 1
+        out[:, :, :r, :] = x
+    if replicate_rows:
+        assert r == 1
+        out[:, :, :, :] = out[:, :, :1, :]
+    return out

@@ -513,3 +513,37 @@ def test_policy_switches_one_by_one(oracle):
             R.set_bfp_policy(R.BfpPolicy(face_order=(0, 0, 1, 2)))
     finally:
         R.set_bfp_policy(None)
+
+
+# ------------------------------------------------------------------------------------------------
+# Runtime tensor transforms: the numpy restatements against vectors the reference's own functions produced
+# ------------------------------------------------------------------------------------------------
+def _transform_golden():
+    import os
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "transform_golden.npz"))
+
+
+def test_transform_restatements_match_the_reference_vectors(oracle):
+    g = _transform_golden()
+    k = 0
+    while f"emb{k}_in" in g.files:
+        n, w, q_rt, q_ct = (int(v) for v in g[f"emb{k}_meta"])
+        got = oracle.embedding_index(g[f"emb{k}_in"], n, q_rt)
+        assert got.shape == g[f"emb{k}_out"].shape == (w, 1, q_rt * 32, q_ct * 32)
+        assert np.array_equal(got, g[f"emb{k}_out"]), ("embedding index", k)
+        k += 1
+    assert k == 5
+    k = 0
+    while f"pre{k}_in" in g.files:
+        got = oracle.prestride_act(g[f"pre{k}_in"], int(g[f"pre{k}_stride"][0]))
+        assert np.array_equal(got, g[f"pre{k}_out"]), ("prestride", k)
+        k += 1
+    assert k == 4
+    k = 0
+    while f"pad{k}_in" in g.files:
+        x, bc, want = g[f"pad{k}_in"], list(g[f"pad{k}_bcast"]), g[f"pad{k}_out"]
+        x4 = x.reshape((1,) * (4 - x.ndim) + x.shape)
+        got = oracle.pad_to_tiles(x4, replicate_rows=(2 in bc or -2 in bc), replicate_cols=(3 in bc or -1 in bc))
+        assert np.array_equal(got.reshape(want.shape), want), ("pad", k)
+        k += 1
+    assert k == 5

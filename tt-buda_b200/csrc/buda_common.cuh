@@ -80,7 +80,8 @@ __host__ __device__ inline bool policy_is_default(const BfpPolicy &p)
 // tiles: the runtime tensor transforms of the reference's push path, done in the kernel's index arithmetic instead
 // of as separate passes over the data.  Element (w, z, r, c) of the tile-aligned shape the queue covers comes from
 //   kSrcPadded     the tensor itself where r < valid_r and c < valid_c, zero elsewhere (tile padding of
-//                  pad_pytorch_tensor_to_buda, pybuda/pybuda/tensor.py:805-877)
+//                  pad_pytorch_tensor_to_buda, pybuda/pybuda/tensor.py:805-877); with bcast_r / bcast_c the single row /
+//                  column of a tile-broadcast dimension stands for every row / column of its tile
 //   kSrcEmbedding  a vector of row indices laid out for an embedding op (pybuda/pybuda/tensor.py:1382-1405): with
 //                  group = indices per queue tile row, a = (c / 32) * 32 + r % 32 and flat = (r / 32) * group + a * 32 +
 //                  c % 32: zero where a >= group / 32, all ones where flat >= count, else indices[w][flat]
@@ -91,6 +92,7 @@ enum : uint32_t { kSrcDense = 0, kSrcPadded = 1, kSrcEmbedding = 2, kSrcPrestrid
 struct SourceView {
     uint32_t mode;
     uint32_t valid_r, valid_c;
+    uint32_t bcast_r, bcast_c;
     uint64_t emb_count, emb_group;
     uint32_t ps_stride, ps_noff, ps_z, ps_h, ps_w, ps_hs, ps_ws;
     int8_t ps_x[64], ps_y[64];

@@ -940,9 +940,13 @@ int buda_queue_write_view(const void *src, int src_df, const uint32_t shape[4], 
             if (view->valid_r == 0 || view->valid_c == 0 || view->valid_r > shape[2] || view->valid_c > shape[3])
                 return fail(BUDA_RUNTIME_ERROR, "padded view: valid extent %ux%u outside the %ux%u the queue covers", view->valid_r,
                             view->valid_c, shape[2], shape[3]);
+            if ((view->bcast_r && view->valid_r != 1) || (view->bcast_c && view->valid_c != 1))
+                return fail(BUDA_RUNTIME_ERROR, "padded view: only a dimension of size 1 is broadcast across its tile");
             v.mode = kSrcPadded;
             v.valid_r = view->valid_r;
             v.valid_c = view->valid_c;
+            v.bcast_r = view->bcast_r ? 1u : 0u;
+            v.bcast_c = view->bcast_c ? 1u : 0u;
             break;
         case BUDA_SRC_EMBEDDING_INDEX:
             if (shape[1] != 1) return fail(BUDA_RUNTIME_ERROR, "embedding-index view: t must be 1");

@@ -448,6 +448,8 @@ __device__ __forceinline__ uint32_t fetch_view_elem(const TileJob &j, const uint
     const SourceView &v = j.view;
     const uint8_t *p;
     if (v.mode == kSrcPadded) {
+        if (v.bcast_r) r = 0;
+        if (v.bcast_c) c = 0;
         if (r >= v.valid_r || c >= v.valid_c) return 0u;
         p = base + (uint64_t)w * j.stride_w + rm_z_offset(j, z) + (uint64_t)r * j.stride_r + (uint64_t)c * ES;
     } else if (v.mode == kSrcEmbedding) {

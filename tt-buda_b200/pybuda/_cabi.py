@@ -65,6 +65,7 @@ class SourceView(ctypes.Structure):
 
     _fields_ = [
         ("mode", ctypes.c_uint32), ("valid_r", ctypes.c_uint32), ("valid_c", ctypes.c_uint32),
+        ("bcast_r", ctypes.c_uint32), ("bcast_c", ctypes.c_uint32),
         ("emb_count", ctypes.c_uint64), ("emb_group", ctypes.c_uint64),
         ("ps_stride", ctypes.c_uint32), ("ps_z", ctypes.c_uint32), ("ps_h", ctypes.c_uint32), ("ps_w", ctypes.c_uint32),
         ("ps_n_offsets", ctypes.c_uint32), ("ps_xy", ctypes.c_int32 * 128),

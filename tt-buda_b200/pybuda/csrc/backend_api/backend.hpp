@@ -55,6 +55,22 @@ struct Stride
     int stride = -1;
 };
 
+// How a pushed tensor is read when a runtime tensor transform stands between it and the queue (push_input_view).
+enum class SOURCE_VIEW : std::uint32_t
+{
+    Padded = 1,          // zero padding up to the queue's tiles; a size-1 row dimension may be broadcast across its tile
+    EmbeddingIndex = 2,  // a vector of row indices laid out for an embedding op
+    Prestride = 3        // a convolution activation cut into its stride phases
+};
+
+struct tt_SourceView
+{
+    SOURCE_VIEW mode = SOURCE_VIEW::Padded;
+    bool broadcast_rows = false, broadcast_cols = false;  // Padded
+    std::uint64_t count = 0, group = 0;                   // EmbeddingIndex: indices per entry; indices per queue tile row
+    Stride stride;                                        // Prestride
+};
+
 // Queue descriptor: field names of the reference's DramIODesc (backend_api.cpp:409-487).
 struct tt_dram_io_desc
 {
@@ -102,6 +118,11 @@ DEVICE_STATUS_CODE push_input(const tt_dram_io_desc &q, const tt_PytorchTensorDe
                               const int timeout_in_seconds, const int ram_ptr);
 DEVICE_STATUS_CODE push_input(const tt_dram_io_desc &q, const tt_TilizedTensorDesc &tensor, const int timeout_in_seconds,
                               const int ram_ptr);
+// ---- not in the reference: a whole set of tensors in one call, and pushes through a runtime transform in one kernel
+DEVICE_STATUS_CODE push_input_batch(const std::vector<tt_dram_io_desc> &queues, const std::vector<tt_PytorchTensorDesc> &tensors,
+                                    const bool push_one, const int timeout_in_seconds, const std::vector<int> &ram_ptrs);
+DEVICE_STATUS_CODE push_input_view(const tt_dram_io_desc &q, const tt_PytorchTensorDesc &tensor, const tt_SourceView &view,
+                                   const bool push_one, const int timeout_in_seconds, const int ram_ptr);
 DEVICE_STATUS_CODE get_output(const tt_dram_io_desc &q, tt_PytorchTensorDesc &out, const bool pop_one,
                               const int timeout_in_seconds, const int rd_ptr);
 DEVICE_STATUS_CODE pop_output(const tt_dram_io_desc &q, const bool pop_one, const int timeout_in_seconds);

@@ -253,6 +253,24 @@ void BackendModule(py::module &m_backend)
                   py::overload_cast<const tt::tt_dram_io_desc &, const tt::tt_TilizedTensorDesc &, const int, const int>(
                       &push_input),
                   py::call_guard<py::gil_scoped_release>());
+    py::enum_<tt::SOURCE_VIEW>(m_backend, "SourceViewMode")
+        .value("Padded", tt::SOURCE_VIEW::Padded)
+        .value("EmbeddingIndex", tt::SOURCE_VIEW::EmbeddingIndex)
+        .value("Prestride", tt::SOURCE_VIEW::Prestride);
+    py::class_<tt::tt_SourceView>(m_backend, "SourceView")
+        .def(py::init<>())
+        .def_readwrite("mode", &tt::tt_SourceView::mode)
+        .def_readwrite("broadcast_rows", &tt::tt_SourceView::broadcast_rows)
+        .def_readwrite("broadcast_cols", &tt::tt_SourceView::broadcast_cols)
+        .def_readwrite("count", &tt::tt_SourceView::count)
+        .def_readwrite("group", &tt::tt_SourceView::group)
+        .def_readwrite("stride", &tt::tt_SourceView::stride);
+    m_backend.def("push_input_view", &push_input_view, py::call_guard<py::gil_scoped_release>(), py::arg("queue"), py::arg("tensor"),
+                  py::arg("view"), py::arg("push_one"), py::arg("timeout_in_seconds"), py::arg("ram_ptr"),
+                  "push_input of a tensor that a runtime tensor transform stands in front of: the pack kernel reads it through the view");
+    m_backend.def("push_input_batch", &push_input_batch, py::call_guard<py::gil_scoped_release>(), py::arg("queues"), py::arg("tensors"),
+                  py::arg("push_one"), py::arg("timeout_in_seconds"), py::arg("ram_ptrs") = std::vector<int>{},
+                  "push_input for a whole set of (queue, tensor) pairs: one conversion launch per format combination");
     m_backend.def("pop_output", &pop_output, py::call_guard<py::gil_scoped_release>());
     m_backend.def("get_output", &get_output, py::call_guard<py::gil_scoped_release>());
     m_backend.def("free_tensor", py::overload_cast<tt::tt_PytorchTensorDesc &>(&free_tensor));

@@ -270,113 +270,269 @@ struct DeviceScratch
     }
 };
 
-// A queue whose descriptor carries a StrideDescriptor takes the ORIGINAL [w, z, H, W] activation and stores its
-// prestrided form [w, 1, z*s*s, (H/s)*(W/s)] (reference: the backend applies the descriptor inside push_input,
-// pybuda/pybuda/tensor.py:1415-1422; golden op/eval/pybuda/tm.py:316-335).
-DEVICE_STATUS_CODE push_prestrided(const tt_dram_io_desc &q, const tt_PytorchTensorDesc &tensor, const bool push_one,
-                                   const int timeout_in_seconds, const int ram_ptr)
+// Slots of a queue held for one push: taken under the queue's lock (a ring queue waits, up to its timeout, until the
+// entries fit; a RandomAccess queue writes where ram_ptr says), released by commit() once the data is in place.
+struct SlotClaim
 {
-    const Stride &sd = q.s_descriptor;
-    if (sd.xy_offsets.empty() || sd.xy_offsets.size() > 64)
-        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: stride descriptor needs 1..64 xy offsets");
-    if (tensor.ptr == nullptr)
-        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: tensor descriptor has a null pointer");
-    if (q.t != 1)
-        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: a prestriding queue has t == 1");
-    const std::uint32_t es = tensor.itemsize;
-    std::uint64_t expect = es;
-    for (int i = 3; i >= 0; i--)
+    std::shared_ptr<QueueState> st;
+    std::unique_lock<std::mutex> lock;
+    std::uint32_t first_slot = 0, entries = 0;
+    bool ring = false;
+
+    DEVICE_STATUS_CODE take(const tt_dram_io_desc &q, std::uint32_t n, int timeout_in_seconds, int ram_ptr)
     {
-        if (tensor.shape[i] != 1 && tensor.strides[i] != expect)
-            return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: a prestrided push needs a dense row-major tensor");
-        expect *= tensor.shape[i];
+        if (auto rc = get_queue(q, true, st); rc != DEVICE_STATUS_CODE::Success)
+            return rc;
+        if (n > st->slots)
+            return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: more entries than the queue has slots");
+        entries = n;
+        ring = q.io_type != IO_TYPE::RandomAccess;
+        lock = std::unique_lock<std::mutex>(st->mu);
+        if (!ring)
+        {
+            if (ram_ptr < 0 || (std::uint32_t)ram_ptr + n > st->slots)
+                return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: ram_ptr outside the queue");
+            first_slot = (std::uint32_t)ram_ptr;
+            return DEVICE_STATUS_CODE::Success;
+        }
+        const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(std::max(0, timeout_in_seconds));
+        if (!st->cv.wait_until(lock, deadline, [&] { return st->occupancy + n <= st->slots; }))
+            return fail(DEVICE_STATUS_CODE::TimeoutError, "push_input: queue '" + q.queue_name + "' stayed full");
+        first_slot = st->wr;
+        return DEVICE_STATUS_CODE::Success;
     }
-    const std::uint64_t src_bytes = tensor.numel() * es;
-    DeviceScratch staged, out;
-    const void *src = tensor.ptr;
-    if (!on_device(tensor.ptr))
+
+    void commit()
     {
-        if (buda_malloc(&staged.p, src_bytes) != BUDA_SUCCESS || buda_memcpy(staged.p, tensor.ptr, src_bytes, 0, nullptr) != BUDA_SUCCESS)
-            return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: " + cabi_error());
-        src = staged.p;
+        if (ring)
+        {
+            st->wr = (st->wr + entries) % st->slots;
+            st->occupancy += entries;
+        }
+        else
+        {
+            st->occupancy = std::max(st->occupancy, first_slot + entries);
+        }
+        lock.unlock();
+        st->cv.notify_all();
     }
-    const std::uint32_t rows = q.rows(), cols = q.cols(), w = tensor.shape[0];
-    if (buda_malloc(&out.p, (std::uint64_t)w * rows * cols * es) != BUDA_SUCCESS)
+};
+
+std::string check_queue_tiles(const tt_dram_io_desc &q)
+{
+    if (q.tile_width != 32 || q.tile_height == 0 || q.tile_height > 32 || (q.tile_height & (q.tile_height - 1)))
+        return "tiles are 32 columns wide and 32, 16, 8, 4, 2 or 1 rows high";
+    if (q.layout != IO_LAYOUT::Tilized)
+        return "only tilized queues are supported";
+    if (q.hstack_factor != 1 || q.vstack_factor != 1)
+        return "hstack / vstack host transforms are not supported";
+    return "";
+}
+
+// The tensor on the device: itself when it already lives there, otherwise a scratch copy of its `bytes` bytes.
+DEVICE_STATUS_CODE device_copy_of(const void *ptr, std::uint64_t bytes, DeviceScratch &scratch, const void *&dev)
+{
+    dev = ptr;
+    if (on_device(ptr))
+        return DEVICE_STATUS_CODE::Success;
+    if (buda_malloc(&scratch.p, bytes) != BUDA_SUCCESS || buda_memcpy(scratch.p, ptr, bytes, 0, nullptr) != BUDA_SUCCESS)
         return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: " + cabi_error());
-    std::vector<int> xy;
-    for (const auto &o : sd.xy_offsets)
-    {
-        xy.push_back(o.first);
-        xy.push_back(o.second);
-    }
-    const std::uint64_t dense[4] = {(std::uint64_t)tensor.shape[1] * tensor.shape[2] * tensor.shape[3] * es,
-                                    (std::uint64_t)tensor.shape[2] * tensor.shape[3] * es, (std::uint64_t)tensor.shape[3] * es, es};
-    if (int rc = buda_prestride(src, (int)es, tensor.shape.data(), dense, sd.stride, xy.data(), (int)sd.xy_offsets.size(), out.p, rows,
-                                cols, nullptr);
-        rc != BUDA_SUCCESS)
-        return from_cabi(rc, "push_input (prestride)");
-    if ((std::uint64_t)rows * cols * es > 0xffffffffull)
-        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: prestrided entry exceeds the descriptor's 32-bit strides");
-    const std::uint32_t entry_bytes = (std::uint32_t)((std::uint64_t)rows * cols * es);
-    const tt_PytorchTensorDesc pre(out.p, es, tensor.format, {w, 1, rows, cols}, {entry_bytes, entry_bytes, cols * es, es}, 4);
-    tt_dram_io_desc plain = q;
-    plain.s_descriptor = Stride{};
-    return push_input(plain, pre, push_one, timeout_in_seconds, ram_ptr);
+    dev = scratch.p;
+    return DEVICE_STATUS_CODE::Success;
+}
+
+// bytes a strided [w,z,r,c] tensor spans from its first to its last element
+std::uint64_t span_bytes(const tt_PytorchTensorDesc &t)
+{
+    std::uint64_t last = 0;
+    for (int i = 0; i < 4; i++)
+        last += (std::uint64_t)(t.shape[i] ? t.shape[i] - 1 : 0) * t.strides[i];
+    return last + t.itemsize;
 }
 }  // namespace
+
+// A tensor pushed through a source view (see buda_source_view): one kernel reads it the way the runtime transform
+// would have rewritten it and writes the queue's tiles.  `tensor` describes the SOURCE (its own shape and strides).
+DEVICE_STATUS_CODE push_input_view(const tt_dram_io_desc &q, const tt_PytorchTensorDesc &tensor, const tt_SourceView &view,
+                                   const bool push_one, const int timeout_in_seconds, const int ram_ptr)
+{
+    if (const std::string why = check_queue_tiles(q); !why.empty())
+        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: " + why);
+    if (q.tile_height != 32)
+        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: a transformed push needs 32-row tiles");
+    if (tensor.ptr == nullptr)
+        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: tensor descriptor has a null pointer");
+    const std::uint32_t entries = tensor.shape[0];
+    if (push_one && entries != 1)
+        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: a single-entry push needs a tensor with w == 1");
+    buda_source_view v = {};
+    v.mode = (std::uint32_t)view.mode;
+    const std::uint32_t es = tensor.itemsize;
+    std::uint64_t strides[4] = {tensor.strides[0], tensor.strides[1], tensor.strides[2], es};
+    switch (view.mode)
+    {
+        case SOURCE_VIEW::Padded:
+            if (tensor.shape[1] != q.t || tensor.shape[2] > q.rows() || tensor.shape[3] > q.cols())
+                return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: the tensor is larger than the queue's entries");
+            if ((view.broadcast_rows && tensor.shape[2] != 1) || (view.broadcast_cols && tensor.shape[3] != 1))
+                return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: only a dimension of size 1 is broadcast across its tile");
+            v.valid_r = tensor.shape[2];
+            v.valid_c = tensor.shape[3];
+            v.bcast_r = view.broadcast_rows ? 1 : 0;
+            v.bcast_c = view.broadcast_cols ? 1 : 0;
+            break;
+        case SOURCE_VIEW::EmbeddingIndex:
+            v.emb_count = view.count;
+            v.emb_group = view.group;
+            strides[1] = strides[2] = 0;
+            break;
+        case SOURCE_VIEW::Prestride:
+        {
+            const Stride &sd = view.stride;
+            if (sd.xy_offsets.empty() || sd.xy_offsets.size() > 64)
+                return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: stride descriptor needs 1..64 xy offsets");
+            v.ps_stride = (std::uint32_t)sd.stride;
+            v.ps_z = tensor.shape[1];
+            v.ps_h = tensor.shape[2];
+            v.ps_w = tensor.shape[3];
+            v.ps_n_offsets = (std::uint32_t)sd.xy_offsets.size();
+            for (std::size_t k = 0; k < sd.xy_offsets.size(); k++)
+            {
+                v.ps_xy[2 * k] = sd.xy_offsets[k].first;
+                v.ps_xy[2 * k + 1] = sd.xy_offsets[k].second;
+            }
+            break;
+        }
+        default: return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: unknown source view");
+    }
+    if (tensor.strides[3] != es)
+        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: a transformed push needs unit-stride rows");
+    DeviceScratch staged;
+    const void *src = nullptr;
+    if (auto rc = device_copy_of(tensor.ptr, span_bytes(tensor), staged, src); rc != DEVICE_STATUS_CODE::Success)
+        return rc;
+    SlotClaim claim;
+    if (auto rc = claim.take(q, entries, timeout_in_seconds, ram_ptr); rc != DEVICE_STATUS_CODE::Success)
+        return rc;
+    const buda_queue_geom g = geom_of(q);
+    const std::uint32_t qshape[4] = {entries, q.t, q.rows(), q.cols()};
+    int rc = buda_queue_write_view(src, (int)tensor.format, qshape, strides, &v, &g, (int)q.bufq_target_format, q.tile_header ? 1 : 0,
+                                   claim.st->base, claim.st->bytes, claim.st->slots, claim.first_slot, nullptr);
+    if (rc == BUDA_SUCCESS)
+        rc = buda_stream_synchronize(nullptr);  // the caller (or the scratch copy) may go away as soon as we return
+    if (rc != BUDA_SUCCESS)
+        return from_cabi(rc, "push_input");
+    claim.commit();
+    return DEVICE_STATUS_CODE::Success;
+}
 
 DEVICE_STATUS_CODE push_input(const tt_dram_io_desc &q, const tt_PytorchTensorDesc &tensor, const bool push_one,
                               const int timeout_in_seconds, const int ram_ptr)
 {
     if (q.s_descriptor.stride > 1)
-        return push_prestrided(q, tensor, push_one, timeout_in_seconds, ram_ptr);
+    {
+        // A queue whose descriptor carries a StrideDescriptor takes the ORIGINAL [w, z, H, W] activation and stores its
+        // prestrided form (the reference's backend applies the descriptor inside push_input,
+        // pybuda/pybuda/tensor.py:1415-1422): here the pack kernel gathers it while it tilizes.
+        if (q.t != 1)
+            return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: a prestriding queue has t == 1");
+        tt_SourceView view;
+        view.mode = SOURCE_VIEW::Prestride;
+        view.stride = q.s_descriptor;
+        return push_input_view(q, tensor, view, push_one, timeout_in_seconds, ram_ptr);
+    }
     const std::string why = check_tensor_fits(q, tensor);
     if (!why.empty())
         return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: " + why);
     if (push_one && tensor.shape[0] != 1)
         return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: a single-entry push needs a tensor with w == 1");
-    const std::uint32_t entries = tensor.shape[0];
-    std::shared_ptr<QueueState> st;
-    if (auto rc = get_queue(q, true, st); rc != DEVICE_STATUS_CODE::Success)
+    SlotClaim claim;
+    if (auto rc = claim.take(q, tensor.shape[0], timeout_in_seconds, ram_ptr); rc != DEVICE_STATUS_CODE::Success)
         return rc;
-    if (entries > st->slots)
-        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: more entries than the queue has slots");
-
-    std::unique_lock<std::mutex> lock(st->mu);
-    std::uint32_t first_slot;
-    if (q.io_type == IO_TYPE::RandomAccess)
-    {
-        if (ram_ptr < 0 || (std::uint32_t)ram_ptr + entries > st->slots)
-            return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: ram_ptr outside the queue");
-        first_slot = (std::uint32_t)ram_ptr;
-    }
-    else
-    {
-        const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(std::max(0, timeout_in_seconds));
-        if (!st->cv.wait_until(lock, deadline, [&] { return st->occupancy + entries <= st->slots; }))
-            return fail(DEVICE_STATUS_CODE::TimeoutError, "push_input: queue '" + q.queue_name + "' stayed full");
-        first_slot = st->wr;
-    }
     const buda_queue_geom g = geom_of(q);
     const bool host = !on_device(tensor.ptr);
     const auto st64 = strides64(tensor);
     int rc = buda_queue_write(tensor.ptr, host ? 1 : 0, (int)tensor.format, tensor.shape.data(), st64.data(), &g,
-                              (int)q.bufq_target_format, q.tile_header ? 1 : 0, st->base, st->slots, first_slot, nullptr);
+                              (int)q.bufq_target_format, q.tile_header ? 1 : 0, claim.st->base, claim.st->slots, claim.first_slot,
+                              nullptr);
     if (rc == BUDA_SUCCESS && !host)
         rc = buda_stream_synchronize(nullptr);  // the caller may free the source as soon as we return
     if (rc != BUDA_SUCCESS)
         return from_cabi(rc, "push_input");
-    if (q.io_type != IO_TYPE::RandomAccess)
+    claim.commit();
+    return DEVICE_STATUS_CODE::Success;
+}
+
+// Many tensors to many queues in one go: what the reference's parameter loop does one push_input at a time
+// (pybuda/pybuda/backend.py:458-517).  Slots are claimed in every queue first, then all conversions that share a
+// (source format, queue format, header) combination run as ONE job table -- one launch for up to 192 device-resident
+// tensors, or one copy / convert pipeline over all host tensors -- and the queues' pointers move when everything is in.
+DEVICE_STATUS_CODE push_input_batch(const std::vector<tt_dram_io_desc> &queues, const std::vector<tt_PytorchTensorDesc> &tensors,
+                                    const bool push_one, const int timeout_in_seconds, const std::vector<int> &ram_ptrs)
+{
+    const std::size_t n = queues.size();
+    if (tensors.size() != n || (!ram_ptrs.empty() && ram_ptrs.size() != n))
+        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input_batch: queues, tensors and ram pointers differ in number");
+    std::vector<SlotClaim> claims(n);
+    std::vector<buda_tensor_job> jobs(n);
+    std::vector<bool> host(n);
+    for (std::size_t i = 0; i < n; i++)
     {
-        st->wr = (st->wr + entries) % st->slots;
-        st->occupancy += entries;
+        const tt_dram_io_desc &q = queues[i];
+        const tt_PytorchTensorDesc &t = tensors[i];
+        if (q.s_descriptor.stride > 1)
+            return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input_batch: prestriding queues take push_input");
+        if (const std::string why = check_tensor_fits(q, t); !why.empty())
+            return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input_batch: " + why);
+        if (push_one && t.shape[0] != 1)
+            return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input_batch: a single-entry push needs tensors with w == 1");
+        for (std::size_t k = 0; k < i; k++)
+            if (queues[k].key() == q.key())
+                return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input_batch: queue '" + q.queue_name + "' appears twice");
+        if (auto rc = claims[i].take(q, t.shape[0], timeout_in_seconds, ram_ptrs.empty() ? -1 : ram_ptrs[i]);
+            rc != DEVICE_STATUS_CODE::Success)
+            return rc;   // claims taken so far release their locks as they go out of scope; nothing was written
+        buda_tensor_job &j = jobs[i];
+        memset(&j, 0, sizeof(j));
+        j.tensor = t.ptr;
+        j.image = claims[i].st->base;
+        j.image_bytes = claims[i].st->bytes;
+        for (int d = 0; d < 4; d++)
+        {
+            j.shape[d] = t.shape[d];
+            j.strides_bytes[d] = t.strides[d];
+        }
+        j.geom = geom_of(q);
+        j.slots = claims[i].st->slots;
+        j.first_slot = claims[i].first_slot;
+        host[i] = !on_device(t.ptr);
     }
-    else
+    // one call per (source format, queue format, header, host / device) combination
+    std::vector<bool> done(n, false);
+    for (std::size_t i = 0; i < n; i++)
     {
-        st->occupancy = std::max(st->occupancy, first_slot + entries);
+        if (done[i])
+            continue;
+        std::vector<buda_tensor_job> group;
+        for (std::size_t k = i; k < n; k++)
+        {
+            if (!done[k] && tensors[k].format == tensors[i].format && queues[k].bufq_target_format == queues[i].bufq_target_format &&
+                queues[k].tile_header == queues[i].tile_header && host[k] == host[i])
+            {
+                group.push_back(jobs[k]);
+                done[k] = true;
+            }
+        }
+        const int src_df = (int)tensors[i].format, dst_df = (int)queues[i].bufq_target_format, hdr = queues[i].tile_header ? 1 : 0;
+        int rc = host[i] ? buda_tilize_pack_host_jobs((int)group.size(), group.data(), src_df, dst_df, hdr, 1, nullptr)
+                         : buda_tilize_pack_jobs((int)group.size(), group.data(), src_df, dst_df, hdr, nullptr);
+        if (rc != BUDA_SUCCESS)
+            return from_cabi(rc, "push_input_batch");
     }
-    lock.unlock();
-    st->cv.notify_all();
+    if (int rc = buda_stream_synchronize(nullptr); rc != BUDA_SUCCESS)   // the callers may free their tensors once we return
+        return from_cabi(rc, "push_input_batch");
+    for (auto &c : claims)
+        c.commit();
     return DEVICE_STATUS_CODE::Success;
 }
 
@@ -391,26 +547,11 @@ DEVICE_STATUS_CODE push_input(const tt_dram_io_desc &q, const tt_TilizedTensorDe
     if (tensor.num_buffers != cores || q.bufq_entry_size == 0 || tensor.buf_size_bytes % q.bufq_entry_size)
         return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: tilized tensor does not match the queue's buffers");
     const std::uint32_t entries = tensor.buf_size_bytes / q.bufq_entry_size;
-    std::shared_ptr<QueueState> st;
-    if (auto rc = get_queue(q, true, st); rc != DEVICE_STATUS_CODE::Success)
+    SlotClaim claim;
+    if (auto rc = claim.take(q, entries, timeout_in_seconds, ram_ptr); rc != DEVICE_STATUS_CODE::Success)
         return rc;
-    if (entries > st->slots)
-        return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: more entries than the queue has slots");
-    std::unique_lock<std::mutex> lock(st->mu);
-    std::uint32_t first_slot;
-    if (q.io_type == IO_TYPE::RandomAccess)
-    {
-        if (ram_ptr < 0 || (std::uint32_t)ram_ptr + entries > st->slots)
-            return fail(DEVICE_STATUS_CODE::RuntimeError, "push_input: ram_ptr outside the queue");
-        first_slot = (std::uint32_t)ram_ptr;
-    }
-    else
-    {
-        const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(std::max(0, timeout_in_seconds));
-        if (!st->cv.wait_until(lock, deadline, [&] { return st->occupancy + entries <= st->slots; }))
-            return fail(DEVICE_STATUS_CODE::TimeoutError, "push_input: queue '" + q.queue_name + "' stayed full");
-        first_slot = st->wr;
-    }
+    QueueState *st = claim.st.get();
+    const std::uint32_t first_slot = claim.first_slot;
     // the image is already in queue order: copy entry by entry into the ring of each grid buffer
     const std::uint64_t entry = q.bufq_entry_size;
     const std::uint64_t core_stride = (std::uint64_t)st->slots * entry;
@@ -430,17 +571,7 @@ DEVICE_STATUS_CODE push_input(const tt_dram_io_desc &q, const tt_TilizedTensorDe
             done += run;
         }
     }
-    if (q.io_type != IO_TYPE::RandomAccess)
-    {
-        st->wr = (st->wr + entries) % st->slots;
-        st->occupancy += entries;
-    }
-    else
-    {
-        st->occupancy = std::max(st->occupancy, first_slot + entries);
-    }
-    lock.unlock();
-    st->cv.notify_all();
+    claim.commit();
     return DEVICE_STATUS_CODE::Success;
 }
 

@@ -374,3 +374,23 @@ def tilize_pack_jobs(tensors, dst_df, geoms=None, with_header=False, outs=None, 
 def unpack_untilize_jobs(images, src_df, outs, geoms=None, with_header=False, bands=None):
     """Inverse of tilize_pack_jobs: images[i] -> outs[i] (CUDA tensors of one dtype, any shapes)."""
     return TensorJobs(outs, src_df, images, geoms, with_header, bands).unpack()
+
+
+def tilize_pack_view(src, dst_df, queue_shape, view, geom=None, with_header=False, out=None, strides_bytes=None):
+    """Tilize a CUDA tensor that is read through a source view (_cabi.SourceView: tile padding / broadcast, an
+    embedding-index vector, a prestrided convolution activation) straight into the queue image of `queue_shape`
+    ([w, t, R, C], whole tiles): one kernel, no intermediate tensor."""
+    _need_cuda(src)
+    qshape = _cabi.shape4(queue_shape)
+    if geom is None:
+        geom = QueueGeom.for_shape(qshape)
+    nbytes = _cabi.tilized_bytes(geom, qshape, int(dst_df), with_header)
+    if out is None:
+        out = torch.empty(nbytes, dtype=torch.uint8, device=src.device)
+    if strides_bytes is None:
+        _, strides_bytes = _desc(src)
+    with torch.cuda.device(src.device):
+        check(_cabi.lib.buda_queue_write_view(src.data_ptr(), int(_TORCH_TO_DF[src.dtype]), _cabi.u32x4(qshape), _cabi.u64x4(strides_bytes),
+                                              ctypes.byref(view), ctypes.byref(geom), int(dst_df), int(with_header), out.data_ptr(),
+                                              out.numel(), 0, 0, _stream()))
+    return out
