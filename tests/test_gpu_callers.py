@@ -127,3 +127,86 @@ def test_parameters_pushed_to_random_access_queues(mods, oracle):
     assert B.get_output(queues["lut"], out, True, 1, 0) == B.BackendStatusCode.Success, B.last_error()
     assert torch.equal(T.tensor_desc_to_pytorch_tensor(out).reshape(64, 32), table)
     B.free_tensor(out)
+
+
+def test_parameter_set_goes_down_in_one_launch_per_format(mods, oracle):
+    """push_constants_and_parameters / update_device_paramaters: a model's whole parameter set -- different shapes,
+    queue geometries and formats -- in one backend call; tensors that share a (source, queue) format pair share a
+    conversion launch.  Device-resident and host values alike."""
+    B, DF, T, backend, dc, parameter = mods
+    from pybuda import _cabi
+    g = torch.Generator().manual_seed(12)
+    shapes = {"q": (1024, 1024), "k": (1024, 1024), "ffn1": (1024, 4096), "ffn2": (4096, 1024), "ln": (32, 1024), "emb": (64, 32)}
+    for where in ("host", "device"):
+        values, queues = {}, {}
+        for i, (name, shp) in enumerate(shapes.items()):
+            v = torch.randn(shp, generator=g) * 0.02
+            if name == "emb":
+                v = torch.randint(0, 1000, shp, generator=g, dtype=torch.int32)
+            values[name] = v.cuda() if where == "device" else v
+            fmt = DF.RawUInt32 if name == "emb" else (DF.Bfp4_b if name == "ln" else DF.Bfp8_b)
+            grid = (2, 2) if name == "ffn1" else (1, 1)
+            queues[name] = B.DramIODesc.for_tensor(f"{where}_{name}", [1, 1, *shp], fmt, grid=grid, io_type=B.IOType.RandomAccess, num_slots=1)
+        n0 = _cabi.launch_count()
+        backend.BackendAPI.push_constants_and_parameters(queues, values)
+        launches = _cabi.launch_count() - n0
+        if where == "device":
+            assert launches == 3, launches          # fp32 -> Bfp8_b (4 tensors), fp32 -> Bfp4_b, int32 -> RawUInt32
+        for name, shp in shapes.items():
+            out = B.PytorchTensorDesc()
+            if name != "emb":
+                out.format = DF.Float32
+            assert B.get_output(queues[name], out, True, 1, 0) == B.BackendStatusCode.Success, B.last_error()
+            got = T.tensor_desc_to_pytorch_tensor(out).clone().reshape(shp)
+            B.free_tensor(out)
+            if name == "emb":
+                assert torch.equal(got, values[name].cpu())
+            else:
+                fmt = oracle.Bfp4_b if name == "ln" else oracle.Bfp8_b
+                want = _quantised(oracle, values[name].cpu().numpy().reshape(1, 1, *shp), fmt).reshape(shp)
+                assert np.array_equal(got.numpy().view(np.uint32), want.view(np.uint32)), (where, name)
+        # new values for two of them, into the same addresses
+        upd = {"q": values["q"] * 2, "ln": values["ln"] + 1}
+        backend.BackendAPI.update_device_paramaters(queues, upd)
+        out = B.PytorchTensorDesc()
+        out.format = DF.Float32
+        assert B.get_output(queues["q"], out, True, 1, 0) == B.BackendStatusCode.Success
+        want = _quantised(oracle, upd["q"].cpu().numpy().reshape(1, 1, 1024, 1024), oracle.Bfp8_b).reshape(1024, 1024)
+        assert np.array_equal(T.tensor_desc_to_pytorch_tensor(out).numpy().reshape(1024, 1024).view(np.uint32), want.view(np.uint32))
+        B.free_tensor(out)
+    # the same queue twice in one call is refused
+    q = queues["q"]
+    d = T.pytorch_tensor_to_tensor_desc(torch.zeros(1, 1, 1024, 1024))
+    assert B.push_input_batch([q, q], [d, d], True, 1, [0, 0]) == B.BackendStatusCode.RuntimeError
+    assert "twice" in B.last_error()
+
+
+def test_connector_pushes_reinterpreted_and_prestrided_inputs(mods, oracle):
+    """ReinterpretShape (the tensor's elements read in another shape, then padded by the kernel) and Prestride (the queue
+    carries a stride descriptor; the kernel gathers the phases) through the connector."""
+    B, DF, T, backend, dc, _ = mods
+    g = torch.Generator().manual_seed(13)
+    flat = torch.randn(1, 2 * 45 * 50, generator=g)                       # reinterpreted as [1, 2, 45, 50] -> queue [1, 2, 64, 64]
+    act = torch.randn(1, 3, 10, 12, generator=g)                          # stride 2 -> [1, 1, 12, 30] -> queue [1, 1, 32, 32]
+    q0 = B.DramIODesc.for_tensor("reint", [1, 2, 64, 64], DF.Float32)
+    q1 = B.DramIODesc.for_tensor("prestr", [1, 1, 32, 32], DF.Float32)
+    tr0 = T.RuntimeTensorTransform(T.RuntimeTensorTransformType.ReinterpretShape, original_shape=tuple(flat.shape), reinterpreted_shape=(1, 2, 45, 50))
+    tr1 = T.RuntimeTensorTransform(T.RuntimeTensorTransformType.Prestride, stride_height=2, stride_width=2)
+    _, q1 = T.eval_runtime_transform(tr1, act, q1, [])                    # attaches the stride descriptor to the queue
+    pusher = dc.DirectPusherDeviceConnector(threading.Event(), sequential=True)
+    pusher.set_dram_io_push_queues([q0, q1], [[], []], [tr0, tr1])
+    for dev in ("cpu", "cuda"):
+        pusher.push([flat.to(dev), act.to(dev)])
+        out = B.PytorchTensorDesc()
+        assert B.get_output(q0, out, True, 1, -1) == B.BackendStatusCode.Success, B.last_error()
+        got = T.tensor_desc_to_pytorch_tensor(out).clone()
+        B.free_tensor(out)
+        B.pop_output(q0, True, 1)
+        want = oracle.pad_to_tiles(flat.numpy().reshape(1, 2, 45, 50))
+        assert np.array_equal(got.numpy(), want), dev
+        out = B.PytorchTensorDesc()
+        assert B.get_output(q1, out, True, 1, -1) == B.BackendStatusCode.Success, B.last_error()
+        got = T.tensor_desc_to_pytorch_tensor(out).clone()
+        B.free_tensor(out)
+        B.pop_output(q1, True, 1)
+        assert np.array_equal(got.numpy(), oracle.pad_to_tiles(oracle.prestride_act(act.numpy(), 2))), dev

@@ -7,7 +7,7 @@ from typing import Dict, List, Optional, Tuple, Union
 import torch
 
 from ._C.backend_api import (BackendStatusCode, DramIODesc, PytorchTensorDesc, TilizedTensorDesc, free_tensor, get_output,
-                             pop_output, push_input)
+                             pop_output, push_input, push_input_batch, push_input_view)
 from .tensor import (RuntimeTensorTransform, RuntimeTensorTransformType, Tensor, pytorch_tensor_to_tensor_desc)
 
 
@@ -28,6 +28,28 @@ class BackendAPI:
             f"Incorrect number of tensors provided on input: tensors:{len(tensors)} vs ordered_input_queues:{len(ordered_input_queues)}")
         for i, inq in enumerate(ordered_input_queues):
             BackendAPI.push_input(inq, tensors[i], single_input, 1, -1)
+
+    @classmethod
+    def push_staged(cls, queues: List[DramIODesc], staged: List[Tuple[PytorchTensorDesc, object]], single_input: bool,
+                    ram_addresses: Optional[List[int]] = None):
+        """(descriptor, source view or None) pairs to their queues.  Descriptors without a view travel together in one
+        push_input_batch call (one conversion launch per format combination instead of one per tensor); a descriptor
+        with a view, or one for a prestriding queue, is pushed by itself."""
+        assert len(staged) == len(queues), f"{len(staged)} tensors staged for {len(queues)} queues"
+        ram = list(ram_addresses) if ram_addresses is not None else [-1] * len(queues)
+        together = []
+        for i, (q, (desc, view)) in enumerate(zip(queues, staged)):
+            if view is not None:
+                rc = push_input_view(q, desc, view, single_input, 1, ram[i])
+                assert rc == BackendStatusCode.Success, "Error while pushing inputs"
+            elif isinstance(desc, TilizedTensorDesc) or q.s_descriptor.stride > 1:
+                BackendAPI.push_input(q, desc, single_input, 1, ram[i])
+            else:
+                together.append(i)
+        if together:
+            rc = push_input_batch([queues[i] for i in together], [staged[i][0] for i in together], single_input, 1,
+                                  [ram[i] for i in together])
+            assert rc == BackendStatusCode.Success, "Error while pushing inputs"
 
     @classmethod
     def read_queues(cls, queues: List[DramIODesc], original_shapes: List[Tuple[int, ...]],
@@ -81,8 +103,19 @@ class BackendAPI:
 
     @classmethod
     def push_constants_and_parameters(cls, queues: Dict[str, DramIODesc], values: Dict[str, torch.Tensor]):
-        """The reference walks the compiled graph's constant and parameter names and pushes each value to its
-        RandomAccess queue at address 0 (backend.py:473-493); here the caller names the queues."""
-        for name, q in queues.items():
+        """Every constant and parameter of a model to its RandomAccess queue at address 0.  The reference walks the
+        compiled graph's names and pushes them one by one (backend.py:458-493); here the caller names the queues and the
+        whole set goes down in ONE backend call: tensors of different shapes share a conversion launch."""
+        names = list(queues)
+        descs = []
+        for name in names:
+            q = queues[name]
             df = q.data_format if int(q.data_format) >= 0xF0 else None       # raw formats keep their integer bits
-            BackendAPI.push_input(q, pytorch_tensor_to_tensor_desc(values[name].contiguous(), df), True, 1, 0)
+            descs.append((pytorch_tensor_to_tensor_desc(values[name].contiguous(), df), None))
+        BackendAPI.push_staged([queues[n] for n in names], descs, True, ram_addresses=[0] * len(names))
+
+    @classmethod
+    def update_device_paramaters(cls, queues: Dict[str, DramIODesc], values: Dict[str, torch.Tensor]):
+        """New values for parameters that already live on the device (name as the reference spells it,
+        backend.py:495-517): the same batched push, into the same addresses."""
+        BackendAPI.push_constants_and_parameters({n: queues[n] for n in values}, values)

@@ -1,7 +1,8 @@
 """Direct device connectors (reference: pybuda/pybuda/device_connector.py:131-375): the objects through which a
 host process pushes a set of tensors into a device's input queues and reads / pops its output queues.  The
-pusher converts each tensor to a type the queue's converter accepts, applies the runtime tensor transform, pads to
-tiles and calls BackendAPI.push_to_queues — on the caller's thread (sequential) or on a pusher thread fed through a
+pusher converts each tensor to a type the queue's converter accepts, describes the runtime tensor transform and the tile
+padding to the pack kernel as a source view (the data itself is not rewritten on the host) and pushes the whole set in
+one backend call — on the caller's thread (sequential) or on a pusher thread fed through a
 bounded command queue, as in the reference.  Inter-process transports (multiprocessing queues, torch queues) of
 the reference are not part of this path."""
 import queue
@@ -12,10 +13,10 @@ import torch
 
 from . import TILE_DIM
 from ._C import DataFormat
-from ._C.backend_api import DramIODesc, PytorchTensorDesc
+from ._C.backend_api import DramIODesc, PytorchTensorDesc, SourceView, SourceViewMode
 from .backend import BackendAPI
-from .tensor import (RuntimeTensorTransform, RuntimeTensorTransformType, Tensor, _embedding_index, is_equivalent_data_format,
-                     pad_pytorch_tensor_to_buda, pytorch_tensor_to_tensor_desc)
+from .tensor import (RuntimeTensorTransform, RuntimeTensorTransformType, Tensor, TilePadding, embedding_index_layout,
+                     is_equivalent_data_format, pytorch_tensor_to_tensor_desc)
 
 
 class DirectPusherDeviceConnector:
@@ -74,78 +75,86 @@ class DirectPusherDeviceConnector:
             err, self.push_error = self.push_error, None
             raise err
 
+    # Which torch dtypes a queue's converter takes as they are, and what everything else is cast to first.
+    _FLOAT_FAMILIES = (
+        ((DataFormat.Float16, DataFormat.Bfp8, DataFormat.Bfp4, DataFormat.Bfp2), (torch.float16,), DataFormat.Float16),
+        ((DataFormat.Float16_b, DataFormat.Bfp8_b, DataFormat.Bfp4_b, DataFormat.Bfp2_b), (torch.float32, torch.bfloat16),
+         DataFormat.Float16_b),
+    )
+
     def _convert_tensor_for_tilize(self, tensor: Tensor, q: DramIODesc) -> Tensor:
-        """Convert formats to the closest format the queue's converter takes."""
-        if is_equivalent_data_format(tensor.pt_data_format, q.data_format):
+        """The tensor in a torch dtype the queue's converter accepts: the 5-bit-exponent family takes float16, the
+        8-bit-exponent family float32 or bfloat16, integers are cast to the queue's own type; anything the table does
+        not know is left for the converter to judge."""
+        have = tensor.pt_data_format
+        if is_equivalent_data_format(have, q.data_format):
             return tensor
-        pt_format = tensor.value().dtype
         if not tensor.value().is_floating_point():
             return tensor.to_format(q.data_format)
-        if q.data_format in [DataFormat.Float16, DataFormat.Bfp8, DataFormat.Bfp4, DataFormat.Bfp2]:
-            if pt_format != torch.float16:          # tensor has to be float16
-                return tensor.to_format(DataFormat.Float16)
-            return tensor
-        if q.data_format in [DataFormat.Float16_b, DataFormat.Bfp8_b, DataFormat.Bfp4_b, DataFormat.Bfp2_b]:
-            if pt_format not in [torch.float32, torch.bfloat16]:   # tensor can be bfloat or fp32
-                return tensor.to_format(DataFormat.Float16_b)
-            return tensor
+        for family, accepted, fallback in self._FLOAT_FAMILIES:
+            if q.data_format in family:
+                return tensor if have in accepted else tensor.to_format(fallback)
         return tensor
 
+    def _tile_dims(self, slot: int) -> Tuple[int, int]:
+        return tuple(self.tile_dims[slot]) if self.tile_dims is not None else (TILE_DIM, TILE_DIM)
+
+    def _stage(self, slot: int, item: Union[Tensor, torch.Tensor]):
+        """One pushed tensor -> (torch value to keep alive, descriptor, source view or None).  Padding, tile broadcast
+        and the embedding-index layout are not applied to the data here: they are handed to the pack kernel as a
+        source view, which reads the tensor accordingly while it writes the queue's tiles."""
+        q = self.direct_push_queues[slot]
+        transform = self.runtime_tensor_transforms[slot]
+        kind = transform.type
+        if kind == RuntimeTensorTransformType.ConstantInput:
+            assert self.constant_tensors[slot] is not None, "a constant input needs its tensor"
+            item, kind = self.constant_tensors[slot], RuntimeTensorTransformType.NoTransform
+        if isinstance(item, Tensor):
+            item = self._convert_tensor_for_tilize(item, q)
+        value = item.value() if isinstance(item, Tensor) else item
+        df = item.data_format if isinstance(item, Tensor) and int(item.data_format) >= 0xF0 else None
+
+        if kind == RuntimeTensorTransformType.EmbeddingIndex:
+            count = transform.original_shape.dims[-1]
+            idx = value.reshape(-1, value.shape[-1]).to(torch.int32).contiguous()
+            q_rt = q.bufq_grid_dim_r * q.mblock_m * q.ublock_rt
+            view = SourceView()
+            view.mode = SourceViewMode.EmbeddingIndex
+            view.count = count
+            view.group, _ = embedding_index_layout(count, idx.shape[-1], q_rt)
+            return idx, pytorch_tensor_to_tensor_desc(idx.view(idx.shape[0], 1, 1, idx.shape[1]), df=DataFormat.RawUInt32), view
+        if kind == RuntimeTensorTransformType.Prestride:
+            return value, pytorch_tensor_to_tensor_desc(value, df=df), None          # the queue's stride descriptor does the rest
+        if kind == RuntimeTensorTransformType.ReinterpretShape:
+            dims = list(transform.reinterpreted_shape.dims)
+            if isinstance(item, Tensor) and dims[0] == 1:
+                dims[0] = self.microbatch
+            value = value.contiguous().view(dims)
+        elif kind != RuntimeTensorTransformType.NoTransform:
+            raise AssertionError(f"Unsupported runtime transform type: {kind}")
+
+        tile_r, tile_c = self._tile_dims(slot)
+        plan = TilePadding(value, self.tile_broadcast_dims[slot], True, self.microbatch, tile_r, tile_c)
+        if plan.aligned:
+            return plan.view, pytorch_tensor_to_tensor_desc(plan.view, df=df), None
+        if plan.view.dim() != 4 or tile_r != TILE_DIM or tile_c != TILE_DIM or plan.view.stride(-1) != 1:
+            padded = plan.materialise()                                               # tiny tiles and odd layouts: pad on the host
+            return padded, pytorch_tensor_to_tensor_desc(padded, df=df), None
+        view = SourceView()
+        view.mode = SourceViewMode.Padded
+        view.broadcast_rows, view.broadcast_cols = plan.rep_r, plan.rep_c
+        src = plan.view.contiguous()
+        return src, pytorch_tensor_to_tensor_desc(src, df=df), view
+
     def _internal_push(self, tensors: List[Union[Tensor, torch.Tensor]]):
-        assert self.direct_push_queues, "Direct push queues have not been set"
-        assert self.tile_broadcast_dims is not None
-        assert len(tensors) == len(self.direct_push_queues), (
-            f"Incorrect number of tensors provided on input: {len(tensors)} vs {len(self.direct_push_queues)}")
-        assert self.runtime_tensor_transforms, "Runtime tensor transforms have not been set"
-        assert len(tensors) == len(self.runtime_tensor_transforms)
-        tensors = list(tensors)
-        tensor_dtypes = [None] * len(tensors)
-
-        for i, t in enumerate(tensors):
-            if isinstance(t, Tensor):
-                tensors[i] = self._convert_tensor_for_tilize(t, self.direct_push_queues[i])
-
-        for i, t in enumerate(tensors):
-            transform = self.runtime_tensor_transforms[i]
-            if transform.type == RuntimeTensorTransformType.EmbeddingIndex:
-                if isinstance(t, Tensor):
-                    t = t.value()
-                t = _embedding_index(t, transform.original_shape.dims, self.direct_push_queues[i])
-                tensors[i] = t
-                tensor_dtypes[i] = DataFormat.RawUInt32
-                continue
-            elif transform.type == RuntimeTensorTransformType.ConstantInput:
-                assert self.constant_tensors[i] is not None
-                tensors[i] = self.constant_tensors[i]
-                t = tensors[i]
-
-            if isinstance(tensors[i], torch.Tensor):
-                if transform.type == RuntimeTensorTransformType.ReinterpretShape:
-                    t = t.contiguous().view(list(transform.reinterpreted_shape.dims))
-                elif transform.type == RuntimeTensorTransformType.Prestride:
-                    continue
-                tile_r = self.tile_dims[i][0] if self.tile_dims is not None else TILE_DIM
-                tile_c = self.tile_dims[i][1] if self.tile_dims is not None else TILE_DIM
-                tensors[i] = pad_pytorch_tensor_to_buda(t, self.tile_broadcast_dims[i], squeeze=True, microbatch=self.microbatch,
-                                                        tile_r=tile_r, tile_c=tile_c)
-            else:
-                if transform.type == RuntimeTensorTransformType.ReinterpretShape:
-                    tensors[i] = t.to_buda_shape(self.tile_broadcast_dims[i], reinterpret_shape=list(transform.reinterpreted_shape.dims),
-                                                 clone=False, squeeze=True, microbatch=self.microbatch)
-                elif transform.type == RuntimeTensorTransformType.Prestride:
-                    pass
-                elif transform.type == RuntimeTensorTransformType.NoTransform:
-                    tensors[i] = t.to_buda_shape(self.tile_broadcast_dims[i], reinterpret_shape=None, clone=False, squeeze=True,
-                                                 microbatch=self.microbatch)
-
-        def to_tensor_desc(t: Union[Tensor, torch.Tensor], df: Optional[DataFormat]) -> PytorchTensorDesc:
-            if isinstance(t, Tensor):
-                return t.to_tensor_desc()
-            return pytorch_tensor_to_tensor_desc(t, df=df)
-
-        BackendAPI.push_to_queues(self.direct_push_queues, [to_tensor_desc(t, df) for t, df in zip(tensors, tensor_dtypes)],
-                                  single_input=False)
-        self.save_tensors = tensors
+        queues = self.direct_push_queues
+        assert queues, "set_dram_io_push_queues() has not been called"
+        assert self.tile_broadcast_dims is not None and self.runtime_tensor_transforms, "push queues were set without their transforms"
+        assert len(tensors) == len(queues) == len(self.runtime_tensor_transforms), (
+            f"{len(tensors)} tensors pushed to {len(queues)} queues")
+        staged = [self._stage(slot, item) for slot, item in enumerate(tensors)]
+        BackendAPI.push_staged(queues, [(desc, view) for _, desc, view in staged], single_input=False)
+        self.save_tensors = [value for value, _, _ in staged]
 
     def push(self, tensors: List[Tensor]):
         if not self.sequential:

@@ -233,50 +233,72 @@ def is_buda_shape(tensor: torch.Tensor, min_dim=-1) -> bool:
     return tensor.shape[-1] % TILE_DIM == 0 and tensor.shape[-2] % TILE_DIM == 0
 
 
+class TilePadding:
+    """What stands between a torch tensor and the 4-D tile-aligned shape a queue takes: the tensor viewed in 4-D (with
+    the microbatch dimension broadcast if it was missing), how many rows / columns of padding the last two dims need,
+    and whether that padding repeats the single row / column (a tile-broadcast dim) instead of being zero.  The host
+    path materialises it (pad_pytorch_tensor_to_buda); a push to a device queue hands it to the pack kernel instead,
+    which pads while it reads."""
+
+    __slots__ = ("view", "pad_r", "pad_c", "rep_r", "rep_c")
+
+    def __init__(self, tensor: torch.Tensor, tile_broadcast_dims, squeeze: bool, microbatch: int, tile_r: int, tile_c: int):
+        if tensor.dim() == 0:
+            tensor = tensor.reshape(1)                      # a scalar pads like a one-element vector
+        rank = 2 if (squeeze and tensor.dim() > 2 and tensor.shape[0] != microbatch) else 4
+        if is_buda_shape(tensor, rank):
+            self.view, self.pad_r, self.pad_c, self.rep_r, self.rep_c = tensor, 0, 0, False, False
+            return
+        v = tensor
+        while v.dim() < rank:
+            v = v.unsqueeze(1 if v.shape[0] == microbatch else 0)
+        while v.dim() > 5:
+            assert v.shape[0] == 1, "only leading dimensions of size 1 can be dropped"
+            v = v.squeeze(0)
+        if v.shape[0] < microbatch:
+            v = v.broadcast_to([microbatch, *v.shape[1:]])
+        self.view = v
+        dims = set(d % 4 for d in tile_broadcast_dims) if tile_broadcast_dims else set()
+        self.rep_r, self.rep_c = 2 in dims, 3 in dims
+        if self.rep_r:
+            assert v.shape[-2] == 1, "a tile-broadcast dimension must have size 1"
+        if self.rep_c:
+            assert v.shape[-1] == 1, "a tile-broadcast dimension must have size 1"
+        self.pad_r, self.pad_c = (-v.shape[-2]) % tile_r, (-v.shape[-1]) % tile_c
+
+    @property
+    def aligned(self) -> bool:
+        return self.pad_r == 0 and self.pad_c == 0
+
+    def padded_shape(self):
+        return (*self.view.shape[:-2], self.view.shape[-2] + self.pad_r, self.view.shape[-1] + self.pad_c)
+
+    def materialise(self) -> torch.Tensor:
+        v = self.view
+        if self.aligned:
+            return v.detach().contiguous()
+        out = torch.zeros(self.padded_shape(), dtype=v.dtype, device=v.device)
+        rows, cols = v.shape[-2], v.shape[-1]
+        # columns first, then rows: a repeated row carries the (zero or repeated) column padding with it
+        out[..., :rows, :cols] = v.detach()
+        if self.rep_c:
+            out[..., :rows, :] = v.detach()
+        if self.rep_r:
+            out[..., :, :] = out[..., :1, :].clone()
+        return out
+
+
 def pad_pytorch_tensor_to_buda(tensor: torch.Tensor, tile_broadcast_dims: List[int], squeeze: bool = False, microbatch=1,
                                tile_r=TILE_DIM, tile_c=TILE_DIM) -> torch.Tensor:
     """Pad a torch tensor to 4-D with rows / columns rounded up to the tile.  Dims listed in
     tile_broadcast_dims (size 1) are replicated across the tile instead of zero padded."""
-    if tensor.dim() == 0:
-        tensor = tensor.reshape(1)  # a scalar pads like a one-element vector
-    min_dim = 2 if (squeeze and tensor.shape[0] != microbatch and len(tensor.shape) > 2) else 4
-    if is_buda_shape(tensor, min_dim):
+    plan = TilePadding(tensor, tile_broadcast_dims, squeeze, microbatch, tile_r, tile_c)
+    if plan.view is tensor and plan.aligned:
         return tensor
-    out = tensor
-    while out.dim() < min_dim:
-        out = out.unsqueeze(1 if out.shape[0] == microbatch else 0)
-    while out.dim() > 5:
-        assert out.shape[0] == 1, "Invalid dimension size above dim 5"
-        out = out.squeeze(0)
-    if out.shape[0] < microbatch:
-        out = out.broadcast_to([microbatch, *out.shape[1:]]).contiguous()
-    if is_buda_shape(out):
-        return out.detach().contiguous()
-
-    rows, cols = out.shape[-2], out.shape[-1]
-    pad_c = (-cols) % tile_c
-    pad_r = (-rows) % tile_r
-    rep_c = -1 in tile_broadcast_dims or 3 in tile_broadcast_dims
-    rep_r = -2 in tile_broadcast_dims or 2 in tile_broadcast_dims
-    if rep_c:
-        assert cols == 1, "Trying to broadcast to tile dim a dimension that's not 1"
-    if rep_r:
-        assert rows == 1, "Trying to broadcast to tile dim a dimension that's not 1"
-
-    # torch pads floating 3-D+ tensors only
-    dtype, ndim = out.dtype, out.dim()
-    work = out if dtype == torch.float32 else out.type(torch.float32)
-    while work.dim() < 3:
-        work = work.unsqueeze(0)
-    work = torch.nn.functional.pad(work, (0, pad_c, 0, 0), mode="replicate" if rep_c else "constant")
-    work = torch.nn.functional.pad(work, (0, 0, 0, pad_r), mode="replicate" if rep_r else "constant")
-    while work.dim() > ndim:
-        work = work.squeeze(0)
-    if work.dtype != dtype:
-        work = work.type(dtype)
-    work = work.detach()
-    work.requires_grad = tensor.requires_grad
-    return work
+    out = plan.materialise()
+    if out.is_floating_point():
+        out.requires_grad = tensor.requires_grad
+    return out
 
 
 def narrow_buda_tensor_to_pytorch(tensor: torch.Tensor, shape: List[int], has_microbatch_dim: bool = False) -> torch.Tensor:
@@ -355,15 +377,14 @@ class Tensor:
 
 
 class TensorFromPytorch(Tensor):
-    """Tensor wrapper around a concrete torch tensor."""
+    """A torch value tagged with the device data format it is meant for."""
 
     def __init__(self, torch_tensor: torch.Tensor, dev_data_format: Optional[DataFormat], constant: bool):
         super().__init__()
-        self._value = torch_tensor
-        self._data_format = dev_data_format if dev_data_format is not None else pytorch_dtype_to_buda_dataformat(
-            torch_tensor.dtype)
-        self._constant = constant
+        self._value, self._constant = torch_tensor, bool(constant)
+        self._data_format = pytorch_dtype_to_buda_dataformat(torch_tensor.dtype) if dev_data_format is None else dev_data_format
 
+    # --- what it holds
     def has_value(self) -> bool:
         return True
 
@@ -373,51 +394,44 @@ class TensorFromPytorch(Tensor):
     def is_constant(self) -> bool:
         return self._constant
 
-    @property
-    def requires_grad(self) -> bool:
-        return self._value.requires_grad
+    shape = property(lambda self: TensorShape(*self._value.shape))
+    pt_data_format = property(lambda self: self._value.dtype)
+    data_format = property(lambda self: self._data_format)
+    requires_grad = property(lambda self: self._value.requires_grad)
 
     def set_requires_grad(self, requires_grad: bool):
         self._value.requires_grad = requires_grad
 
-    def to_buda_shape(self, tile_broadcast_dims: List[int], reinterpret_shape: Optional[List[int]] = None, clone: bool = False,
-                      squeeze: bool = False, microbatch=1, tile_r=TILE_DIM, tile_c=TILE_DIM) -> "Tensor":
-        """This tensor padded to the 4-D tile-aligned shape the queues take."""
-        value = self._value.clone() if clone else self._value
-        if not clone and reinterpret_shape is None and is_buda_shape(value):
-            return self
-        if reinterpret_shape is not None:
-            if reinterpret_shape[0] == 1:
-                reinterpret_shape[0] = microbatch
-            value = value.view(reinterpret_shape)
-        return Tensor.create_from_torch(pad_pytorch_tensor_to_buda(value, tile_broadcast_dims, squeeze, microbatch, tile_r, tile_c))
+    # --- copies
+    def _like(self, value: torch.Tensor, data_format: Optional[DataFormat] = None) -> "Tensor":
+        return Tensor.create_from_torch(value, dev_data_format=data_format)
 
+    def clone(self) -> Tensor:
+        return self._like(self._value.clone())
+
+    def detach(self) -> Tensor:
+        return self._like(self._value.detach())
+
+    def to_format(self, data_format: DataFormat) -> "Tensor":
+        """The same values in the torch dtype that `data_format` travels as (bfloat16 for the Bfp*_b formats), tagged
+        with it.  Nothing is packed here: tile bytes only come into being when the tensor is pushed."""
+        return self._like(self._value.to(buda_dataformat_to_pytorch_dtype(data_format)), data_format)
+
+    # --- on the way to a queue
     def to_tensor_desc(self) -> "PytorchTensorDesc":
         return pytorch_tensor_to_tensor_desc(self._value)
 
-    @property
-    def pt_data_format(self) -> torch.dtype:
-        return self._value.dtype
-
-    @property
-    def data_format(self) -> DataFormat:
-        return self._data_format
-
-    def to_format(self, data_format: DataFormat) -> "Tensor":
-        """Tag the tensor with a device format and cast the torch value to the dtype that format
-        travels as (Bfp*_b -> bfloat16).  No packing happens here: bytes are produced at push time."""
-        return Tensor.create_from_torch(self._value.type(buda_dataformat_to_pytorch_dtype(data_format)),
-                                        dev_data_format=data_format)
-
-    @property
-    def shape(self):
-        return TensorShape(*self._value.shape)
-
-    def clone(self) -> Tensor:
-        return Tensor.create_from_torch(self._value.clone())
-
-    def detach(self) -> Tensor:
-        return Tensor.create_from_torch(self._value.detach())
+    def to_buda_shape(self, tile_broadcast_dims: List[int], reinterpret_shape: Optional[List[int]] = None, clone: bool = False,
+                      squeeze: bool = False, microbatch=1, tile_r=TILE_DIM, tile_c=TILE_DIM) -> "Tensor":
+        """This tensor in the 4-D tile-aligned shape the queues take (itself when it already has it)."""
+        if reinterpret_shape is None and not clone and is_buda_shape(self._value):
+            return self
+        value = self._value.clone() if clone else self._value
+        if reinterpret_shape is not None:
+            dims = list(reinterpret_shape)
+            dims[0] = microbatch if dims[0] == 1 else dims[0]
+            value = value.view(dims)
+        return self._like(pad_pytorch_tensor_to_buda(value, tile_broadcast_dims, squeeze, microbatch, tile_r, tile_c))
 
 
 class TensorFromDescriptor(Tensor):
@@ -548,70 +562,73 @@ class RuntimeTensorTransform:
         return f"RuntimeTensorTransform({self.to_json()})"
 
 
+def embedding_index_layout(count: int, length: int, queue_tile_rows: int):
+    """Geometry of an embedding-index push: `length` indices per entry (of which the first `count` are real), dealt
+    evenly over the queue's tile rows.  Returns (indices per tile row, tile columns): every 32x32 tile holds 1024
+    consecutive indices, so a tile row needs ceil(group / 1024) tile columns."""
+    padded = align_up(length, TILE_DIM)
+    assert padded % (queue_tile_rows * TILE_DIM) == 0, "the padded index vector must split evenly over the queue's tile rows"
+    group = padded // queue_tile_rows
+    return group, align_up(group // TILE_DIM, TILE_DIM) // TILE_DIM
+
+
 def _embedding_index(tensor: torch.Tensor, original_shape: Tuple[int, ...], queue: DramIODesc):
-    """Lay a 1-D vector of row indices out the way an embedding op reads it: padded with all-ones (an invalid
-    index) to a whole number of 32x32 tiles, one tile row per 32 indices, transposed inside the tile rows
-    (reference tensor.py:1382-1413)."""
-    assert queue.data_format in [DataFormat.RawUInt8, DataFormat.RawUInt16, DataFormat.RawUInt32]
-    assert len(tensor.shape) <= 2, "Must be a 1d tensor"
-    assert len(original_shape) <= 1 or original_shape[-2] == 1, "Must be a 1d tensor"
-    assert len(original_shape) <= 2 or original_shape[-3] == 1, "Must be a 1d tensor"
-
+    """Host form of the embedding-index transform (what the pack kernel's embedding view produces on the device):
+    out[w, 0, g*32 + i, j*32 + k] = index[w, g*group + (j*32 + i)*32 + k]; all ones from position original_shape[-1]
+    on, zero where (j*32 + i)*32 reaches past the group."""
+    assert queue.data_format in (DataFormat.RawUInt8, DataFormat.RawUInt16, DataFormat.RawUInt32), "indices travel in a raw integer queue"
+    assert tensor.dim() <= 2 and all(d == 1 for d in tuple(original_shape)[:-1][-2:]), "embedding indices form a vector"
+    idx = tensor.reshape(-1, tensor.shape[-1])
+    w, length = idx.shape
     q_rt = queue.bufq_grid_dim_r * queue.mblock_m * queue.ublock_rt
-    w = tensor.shape[0] if len(tensor.shape) > 1 else 1
-    pad = align_up(tensor.shape[-1], TILE_DIM) - tensor.shape[-1]
-    tensor = torch.nn.functional.pad(tensor, (0, pad))
-    tensor = tensor.reshape(w, 1, 1, tensor.shape[-1])
-    tensor[:, :, :, original_shape[-1]:] = ~torch.tensor(0, dtype=tensor.dtype)
-    tensor = tensor.view(w, q_rt, -1, TILE_DIM)
-    pad = align_up(tensor.shape[-2], TILE_DIM) - tensor.shape[-2]
-    tensor = torch.nn.functional.pad(tensor, (0, 0, 0, pad))
-    tensor = tensor.view(w, q_rt, -1, TILE_DIM, TILE_DIM)
-    tensor = tensor.transpose(2, 3).reshape(w, 1, q_rt * TILE_DIM, -1)
-
-    assert len(tensor.shape) == 4, "_embedding_index: rank changed"
-    assert tensor.shape[0] == w, "_embedding_index: w changed"
-    assert tensor.shape[1] == queue.t, "_embedding_index: t changed"
-    assert tensor.shape[2] == (queue.bufq_grid_dim_r * queue.mblock_m * queue.ublock_rt * TILE_DIM), "_embedding_index: tensor dims mismatch q dims"
-    assert tensor.shape[3] == (queue.bufq_grid_dim_c * queue.mblock_n * queue.ublock_ct * TILE_DIM), "_embedding_index: tensor dims mismatch q dims"
-    return tensor
+    group, ct = embedding_index_layout(original_shape[-1], length, q_rt)
+    r = torch.arange(q_rt * TILE_DIM).unsqueeze(1)
+    c = torch.arange(ct * TILE_DIM).unsqueeze(0)
+    a = (c // TILE_DIM) * TILE_DIM + r % TILE_DIM
+    flat = (r // TILE_DIM) * group + a * TILE_DIM + c % TILE_DIM
+    ones = torch.tensor(-1, dtype=idx.dtype)
+    src = torch.cat([idx, torch.zeros(w, 1, dtype=idx.dtype)], dim=1)                 # one spare slot to gather from
+    out = src[:, flat.clamp(max=length - 1)]
+    out = torch.where(flat >= original_shape[-1], ones, out)
+    out = torch.where(a * TILE_DIM >= group, torch.zeros((), dtype=idx.dtype), out)
+    out = out.reshape(w, 1, q_rt * TILE_DIM, ct * TILE_DIM)
+    assert out.shape[1] == queue.t and out.shape[3] == queue.bufq_grid_dim_c * queue.mblock_n * queue.ublock_ct * TILE_DIM, \
+        "the index layout does not match the queue's geometry"
+    return out
 
 
 def _reinterpret_shape(tensor: torch.Tensor, shape: List[int], queue: DramIODesc, tile_bcast_dims: List[int]):
-    """View the tensor in the shape the compiled graph expects, then pad it to the queue's tiles (tensor.py:1407-1413)."""
-    tensor = tensor.contiguous().view(shape)
-    tensor = pad_pytorch_tensor_to_buda(tensor, tile_bcast_dims, squeeze=True, microbatch=queue.input_count,
-                                        tile_r=queue.tile_height, tile_c=queue.tile_width)
-    return tensor, queue
+    """The tensor's elements read in the shape the compiled graph expects, padded to the queue's tiles."""
+    reshaped = tensor.contiguous().view(shape)
+    return pad_pytorch_tensor_to_buda(reshaped, tile_bcast_dims, squeeze=True, microbatch=queue.input_count,
+                                      tile_r=queue.tile_height, tile_c=queue.tile_width), queue
 
 
 def _prestride_shape(tensor: torch.Tensor, stride_height: int, stride_width: int, queue: DramIODesc):
-    """The tensor is pushed as it is; the queue's stride descriptor makes push_input store its prestrided form
-    (tensor.py:1415-1422)."""
-    assert stride_height == stride_width, "Backend supports only square strides for prestriding transform"
-    stride = stride_height
-    stride_desc = StrideDescriptor()
-    stride_desc.stride = stride
-    stride_desc.xy_offsets = [(x, y) for y in range(stride) for x in range(stride)]
-    queue.s_descriptor = stride_desc
+    """Nothing happens to the tensor here: the queue gets a stride descriptor (all stride x stride phase offsets, row
+    by row) and push_input stores the activation in its prestrided form."""
+    assert stride_height == stride_width, "prestriding works with square strides only"
+    desc = StrideDescriptor()
+    desc.stride = stride_height
+    desc.xy_offsets = [(k % stride_width, k // stride_width) for k in range(stride_height * stride_width)]
+    queue.s_descriptor = desc
     return tensor, queue
 
 
 def do_runtime_transform(transform, tensor, q, tile_bcast_dims):
-    if transform.type == RuntimeTensorTransformType.EmbeddingIndex:
-        return _embedding_index(tensor, transform.original_shape.dims, q), q
-    elif transform.type == RuntimeTensorTransformType.ReinterpretShape:
-        return _reinterpret_shape(tensor, list(transform.reinterpreted_shape.dims), q, tile_bcast_dims)
-    elif transform.type == RuntimeTensorTransformType.NoTransform:
+    kind = transform.type
+    if kind == RuntimeTensorTransformType.NoTransform:
         return tensor, q
-    elif transform.type == RuntimeTensorTransformType.Prestride:
+    if kind == RuntimeTensorTransformType.EmbeddingIndex:
+        return _embedding_index(tensor, transform.original_shape.dims, q), q
+    if kind == RuntimeTensorTransformType.ReinterpretShape:
+        return _reinterpret_shape(tensor, list(transform.reinterpreted_shape.dims), q, tile_bcast_dims)
+    if kind == RuntimeTensorTransformType.Prestride:
         return _prestride_shape(tensor, transform.stride_height, transform.stride_width, q)
-    else:
-        assert False, f"Unsupported runtime transform type: {transform.type}"
+    raise AssertionError(f"Unsupported runtime transform type: {kind}")
 
 
 def eval_runtime_transform(transform, inp, q, tile_bcast_dims):
     if isinstance(transform, str):
         transform = RuntimeTensorTransform.from_json(json.loads(transform))
     return do_runtime_transform(transform, inp, q, tile_bcast_dims)
-
