@@ -58,43 +58,40 @@ class BackendAPI:
                     has_microbatch_dim: bool = True) -> List[Tensor]:
         """get_output on every queue (a read that times out is retried up to 10 times, as in the reference), then the
         tile padding is cut off.  clone=False returns views of backend-owned memory that stay valid until pop_queues."""
-        ret, tensors, out_descs = [], [], []
-        if runtime_tensor_transforms is None:
-            runtime_tensor_transforms = [None] * len(queues)
-        for outq in queues:
-            out_desc = PytorchTensorDesc()
-            retry_count, timeout = 10, 1
-            resp = BackendStatusCode.RuntimeError
-            for _ in range(retry_count):
-                resp = get_output(outq, out_desc, single_output, timeout, rd_ptr)
-                if resp != BackendStatusCode.TimeoutError:
-                    break
-                if shutdown_event and shutdown_event.is_set():
-                    break
-            if resp == BackendStatusCode.TimeoutError:
-                if shutdown_event:
-                    shutdown_event.set()
-                raise RuntimeError("Timeout while reading " + outq.name)
-            assert resp == BackendStatusCode.Success, "Error while reading output"
-            tensors.append(Tensor.create_from_tensor_descriptor(out_desc))
-            out_descs.append(out_desc)
+        count = len(queues)
+        assert len(original_shapes) == count and len(requires_grad) == count, "one original shape and one requires_grad flag per queue"
+        transforms = runtime_tensor_transforms if runtime_tensor_transforms is not None else [None] * count
 
-        assert len(original_shapes) == len(tensors)
-        assert len(requires_grad) == len(tensors)
-        for i, tensor in enumerate(tensors):
-            tr = runtime_tensor_transforms[i]
-            reinterpreted = list(tr.reinterpreted_shape.dims) if tr is not None and tr.reinterpreted_shape.dims else None
-            unpadded = list(tr.unpadded_shape.dims) if tr is not None and tr.unpadded_shape.dims else None
-            tensor = tensor.narrow_to_original_shape(tuple(original_shapes[i]), reinterpreted, has_microbatch_dim=has_microbatch_dim,
-                                                     unpadded_shape=unpadded)
-            if requires_grad[i]:
-                tensor = tensor.detach()
-                tensor.set_requires_grad(True)
+        def fetch(q: DramIODesc) -> PytorchTensorDesc:
+            desc, status = PytorchTensorDesc(), BackendStatusCode.TimeoutError
+            for _attempt in range(10):                      # one-second reads, so a shutdown request is noticed between them
+                status = get_output(q, desc, single_output, 1, rd_ptr)
+                if status != BackendStatusCode.TimeoutError or (shutdown_event is not None and shutdown_event.is_set()):
+                    break
+            if status == BackendStatusCode.TimeoutError:
+                if shutdown_event is not None:
+                    shutdown_event.set()                    # whoever else waits on this device should give up too
+                raise RuntimeError("Timeout while reading " + q.name)
+            assert status == BackendStatusCode.Success, "Error while reading output"
+            return desc
+
+        def dims_of(shape_field) -> Optional[list]:
+            return list(shape_field.dims) if shape_field is not None and shape_field.dims else None
+
+        descs = [fetch(q) for q in queues]
+        results = []
+        for desc, shape, tr, grad in zip(descs, original_shapes, transforms, requires_grad):
+            t = Tensor.create_from_tensor_descriptor(desc).narrow_to_original_shape(
+                tuple(shape), dims_of(tr.reinterpreted_shape) if tr is not None else None, has_microbatch_dim=has_microbatch_dim,
+                unpadded_shape=dims_of(tr.unpadded_shape) if tr is not None else None)
+            if grad:
+                t = t.detach()
+                t.set_requires_grad(True)
             if clone:
-                tensor = tensor.clone()
-                free_tensor(out_descs[i])
-            ret.append(tensor)
-        return ret
+                t = t.clone()
+                free_tensor(desc)
+            results.append(t)
+        return results
 
     @classmethod
     def pop_queues(cls, queues: List[DramIODesc], single_output: bool):

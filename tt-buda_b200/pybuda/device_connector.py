@@ -35,37 +35,39 @@ class DirectPusherDeviceConnector:
         self.pusher_thread_queue = None
         self.push_error = None
 
+    _QUIT = "quit"
+
     def pusher_thread_main(self, cmdqueue: queue.Queue):
-        while True:
-            while True:
-                try:
-                    cmd = cmdqueue.get(timeout=0.1)
-                    break
-                except queue.Empty:
-                    if self.shutdown_event is not None and self.shutdown_event.is_set():
-                        return
-                    continue
-            if cmd == "quit":
-                return
+        """Body of the pusher thread: sets of tensors arrive through the command queue and are pushed in order.  The
+        thread wakes ten times a second to see whether the process is shutting down."""
+        stop = self.shutdown_event
+        while stop is None or not stop.is_set():
             try:
-                self._internal_push(cmd)
-            except Exception as exc:  # noqa: BLE001  surfaced to the caller by wait_for_pushes()
+                work = cmdqueue.get(timeout=0.1)
+            except queue.Empty:
+                continue
+            try:
+                if isinstance(work, str) and work == self._QUIT:
+                    return
+                self._internal_push(work)
+            except Exception as exc:  # noqa: BLE001  handed to the caller by wait_for_pushes()
                 self.push_error = exc
             finally:
                 cmdqueue.task_done()
 
     def shutdown(self):
-        if self.pusher_thread:
-            self.pusher_thread_queue.put("quit")
-            self.pusher_thread.join(timeout=10)
-            self.pusher_thread = None
+        thread, self.pusher_thread = self.pusher_thread, None
+        if thread is not None:
+            self.pusher_thread_queue.put(self._QUIT)
+            thread.join(timeout=10)
 
     def initialize(self):
-        if not self.sequential and not self.pusher_thread:
-            # don't allow pushes to go too far ahead, or we'll run out of memory
-            self.pusher_thread_queue = queue.Queue(maxsize=3)
-            self.pusher_thread = threading.Thread(target=self.pusher_thread_main, args=(self.pusher_thread_queue,), daemon=True)
-            self.pusher_thread.start()
+        if self.sequential or self.pusher_thread is not None:
+            return
+        # a short command queue: pushes must not run far ahead of the device, their tensors are kept alive meanwhile
+        self.pusher_thread_queue = queue.Queue(maxsize=3)
+        self.pusher_thread = threading.Thread(target=self.pusher_thread_main, args=(self.pusher_thread_queue,), daemon=True)
+        self.pusher_thread.start()
 
     def wait_for_pushes(self):
         """Blocks until the pusher thread has drained its command queue; re-raises a push that failed there."""
@@ -157,11 +159,11 @@ class DirectPusherDeviceConnector:
         self.save_tensors = [value for value, _, _ in staged]
 
     def push(self, tensors: List[Tensor]):
-        if not self.sequential:
-            assert self.pusher_thread is not None, "initialize() starts the pusher thread"
-            self.pusher_thread_queue.put(tensors)
-        else:
+        if self.sequential:
             self._internal_push(tensors)
+            return
+        assert self.pusher_thread is not None, "initialize() starts the pusher thread"
+        self.pusher_thread_queue.put(tensors)
 
     def set_dram_io_push_queues(self, direct_push_queues: List[DramIODesc], tile_broadcast_dims: List[List[int]],
                                 runtime_tensor_transforms: Optional[List[RuntimeTensorTransform]],
@@ -184,20 +186,22 @@ class DirectPopperDeviceConnector:
         self.requires_grad = None
         self.runtime_tensor_transforms = None
 
+    def _queues(self) -> List[DramIODesc]:
+        assert self.direct_pop_queues is not None, "set_dram_io_pop_queues() has not been called"
+        return self.direct_pop_queues
+
     def read(self) -> List[Tensor]:
-        assert self.direct_pop_queues is not None, "Direct pop queues have not been set"
-        if len(self.direct_pop_queues) == 0:
+        queues = self._queues()
+        if not queues:
             return []
-        assert self.original_shapes is not None
-        return BackendAPI.read_queues(self.direct_pop_queues, self.original_shapes, self.runtime_tensor_transforms,
-                                      requires_grad=self.requires_grad, single_output=False, shutdown_event=self.shutdown_event,
-                                      clone=False)
+        assert self.original_shapes is not None, "pop queues were set without the tensors' original shapes"
+        return BackendAPI.read_queues(queues, self.original_shapes, self.runtime_tensor_transforms, requires_grad=self.requires_grad,
+                                      single_output=False, shutdown_event=self.shutdown_event, clone=False)
 
     def pop(self):
-        assert self.direct_pop_queues is not None, "Direct pop queues have not been set"
-        if len(self.direct_pop_queues) == 0:
-            return
-        BackendAPI.pop_queues(self.direct_pop_queues, single_output=False)
+        queues = self._queues()
+        if queues:
+            BackendAPI.pop_queues(queues, single_output=False)
 
     def set_dram_io_pop_queues(self, direct_pop_queues: List[DramIODesc], original_shapes: List[Tuple[int, ...]],
                                requires_grad: List[bool], runtime_tensor_transforms: Optional[List[RuntimeTensorTransform]]):
