@@ -524,6 +524,15 @@ def main():
             # the general kernel flavour (job table) on the same uniform batch: what the table look-ups cost by themselves
             tj = cuda_ops.TensorJobs(xs, cuda_ops.DF.Bfp8_b, images=outs)
             extras["pack_bfp8_b_job_table_flavour"] = timed(tj.pack, algo_bytes_step)
+            # the same flavour under a non-default layout policy (truncation instead of rounding; then every switch flipped)
+            try:
+                cuda_ops.set_bfp_policy(_cabi.BfpPolicy(rounding=1))
+                extras["pack_bfp8_b_truncate_policy"] = timed(tj.pack, algo_bytes_step)
+                cuda_ops.set_bfp_policy(_cabi.BfpPolicy(rounding=0, overflow=1, face_order=(1, 0, 3, 2), exponent_order=1, datum_order=1))
+                extras["pack_bfp8_b_all_switches_policy"] = timed(tj.pack, algo_bytes_step)
+            finally:
+                cuda_ops.set_bfp_policy(None)
+            tj.pack()                                       # the images in the default layout again
             del tj
             nu = min(16, NT)
             # bfloat16 source (2 + 1.0625 bytes per element) and bfloat16 destination
@@ -685,19 +694,27 @@ def main():
             # the exchange fused into the kernel: the epilogue stores each tile into every rank's output
             # through peer-mapped memory.  Five launches, then a stream-ordered all-reduce: the closing event is
             # recorded when every rank's kernels (and with them their stores into this rank's matrix) are done.
-            fused_out = op.enable_fused_scatter(M)
             flag = torch.zeros(1, device=dev)
-            for _ in range(2):
-                op.fused(a)
-            barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(5):
-                op.fused(a, sync=False)
-            dist.all_reduce(flag)
-            e1.record()
-            barrier()
-            ms_fused = max_over_ranks(e0.elapsed_time(e1) / 5)
+
+            def time_fused():
+                for _ in range(2):
+                    op.fused(a)
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(5):
+                    op.fused(a, sync=False)
+                dist.all_reduce(flag)
+                e1.record()
+                barrier()
+                return max_over_ranks(e0.elapsed_time(e1) / 5)
+
+            # first with one plain store per peer, then through the switch's multicast where the system has one
+            op.enable_fused_scatter(M, multicast=False)
+            ms_peer_stores = time_fused()
+            fused_out = op.enable_fused_scatter(M)
+            route = op.exchange
+            ms_fused = time_fused() if route == "multicast" else ms_peer_stores
             # correctness on every rank, outside the timed loops: fused == all-gather variant == one-GPU product
             op(a, out=cfull, gather=True)
             w_img_full = cuda_ops.tilize_pack(w_full, cuda_ops.DF.Bfp8_b)
@@ -717,7 +734,7 @@ def main():
                 "TFLOP/s_without_gather": round(2.0 * M * N * K / (ms_local * 1e-3) / 1e12, 1), "ms_without_gather": round(ms_local, 4),
                 "TFLOP/s_with_all_gather": round(2.0 * M * N * K / (ms_gather * 1e-3) / 1e12, 1), "ms_with_all_gather": round(ms_gather, 4),
                 "TFLOP/s_fused_scatter": round(2.0 * M * N * K / (ms_fused * 1e-3) / 1e12, 1), "ms_fused_scatter": round(ms_fused, 4),
-                "fused_matches": fused_matches,
+                "fused_matches": fused_matches, "fused_route": route, "ms_fused_peer_stores": round(ms_peer_stores, 4),
                 "nvlink_store_gbs_per_gpu": round(link_bytes / (ms_fused * 1e-3) / 1e9, 1),
                 "fused_scatter_floor_ms": round(t_floor * 1e3, 4), "fused_scatter_frac_of_floor": round(t_floor * 1e3 / ms_fused, 3),
                 "floor": "max(flops / measured bf16 burst peak, bytes leaving this GPU / 770 GB/s measured peer copy)",

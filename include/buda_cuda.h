@@ -335,6 +335,14 @@ int buda_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void
 int buda_bfp8b_gemm_scatter(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N,
                             void *const *C_dsts, int n_dst, int64_t ldc, void *stream);
 
+/* The same exchange through the NVSwitch: C_multicast is the multicast address of the [M, N] matrix that every device of
+ * the group has bound to one multicast object (cuMulticast*; torch's symmetric memory hands it out), already pointing at
+ * the column block this device owns, as C_local does in this device's own copy.  The epilogue writes the tile to
+ * C_local and then issues ONE multimem store per 16 bytes, which the switch replicates to every device: a device sends
+ * its block once instead of once per peer.  Same completion rule as above.  M > 256. */
+int buda_bfp8b_gemm_multicast(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N, void *C_local,
+                              void *C_multicast, int64_t ldc, void *stream);
+
 /* Prestride transform of a convolution activation (device pointers): the [w, z, H, W] tensor, padded with
  * zeros to multiples of `stride`, becomes [w, 1, n_offsets*z, ceil(H/stride)*ceil(W/stride)]:
  *   dst[w, k*z + zc, hr*Ws + wc] = src[w, zc, hr*stride + y_k, wc*stride + x_k],  (x_k, y_k) = xy_offsets[2k], [2k+1]

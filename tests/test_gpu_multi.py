@@ -49,16 +49,19 @@ def _worker(rank, world, port, results):
         ok = ok and torch.equal(single, c)            # same kernel, same k order: identical bits
         # the same product with the exchange fused into the kernel: each rank's epilogue stores its column
         # block into every rank's output through peer-mapped memory
-        out = op.enable_fused_scatter(m)
-        out.zero_()
-        torch.cuda.synchronize()
-        dist.barrier()
-        for _ in range(2):
-            cf = op.fused(a)
-        torch.cuda.synchronize()
-        fused_equal = torch.equal(cf, single)
-        ok = ok and fused_equal
-        op.disable_fused_scatter()
+        fused_equal, routes = True, []
+        for multicast in (False, None):                 # one store per peer; then the switch's multicast where there is one
+            out = op.enable_fused_scatter(m, multicast=multicast)
+            routes.append(op.exchange)
+            out.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            for _ in range(2):
+                cf = op.fused(a)
+            torch.cuda.synchronize()
+            fused_equal = fused_equal and torch.equal(cf, single)
+            op.disable_fused_scatter()
+        ok = ok and fused_equal and routes[0] == "peer stores"
         # tile-row bands of ONE tensor dealt to the ranks (band b -> rank b % world): every rank packs its bands into
         # its own copy of the image; merged by ownership on rank 0 they are the oracle's image of the whole tensor
         from pybuda.sharding import band_record_slice, bands_of_rank
@@ -76,7 +79,7 @@ def _worker(rank, world, port, results):
             ok = ok and bool((other == 0xAB).all())               # nobody touches a band it does not own
         bands_equal = bool(np.array_equal(merged, ref1))
         ok = ok and bands_equal
-        results[rank] = (bool(ok), rel, bool(fused_equal), bands_equal)
+        results[rank] = (bool(ok), rel, bool(fused_equal), bands_equal, routes)
     finally:
         dist.destroy_process_group()
 

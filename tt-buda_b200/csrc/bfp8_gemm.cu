@@ -306,8 +306,11 @@ cudaError_t launch_bfp8b_gemm_pair(const CUtensorMap &tmap, const gemm::Params &
 
 // C[d] (d < n_dst) all receive the product: C[0] on this device, the rest may be peers' memory mapped into
 // this process (plain stores from the epilogue; nothing is read from a peer).
+// C_mc (may be null): the multicast address of the same matrix on every device of an NVSwitch group; the pair
+// kernel's epilogue then issues one multimem store per 16 bytes instead of one store per peer.
 cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W, int64_t N, void *const *C, int n_dst,
-                              int64_t ldc, int sm_count, cudaStream_t stream, unsigned int *status, char *err, size_t err_len)
+                              void *C_mc, int64_t ldc, int sm_count, cudaStream_t stream, unsigned int *status, char *err,
+                              size_t err_len)
 {
     using namespace gemm;
     if (M <= 0 || N <= 0 || K <= 0 || (N % kBN) || (K % kBK)) {
@@ -349,13 +352,18 @@ cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, 
     p.W = static_cast<const uint8_t *>(W);
     for (int d = 0; d < kMaxDst; d++) p.C[d] = d < n_dst ? static_cast<uint16_t *>(C[d]) : nullptr;
     p.n_dst = n_dst;
+    p.C_mc = static_cast<uint16_t *>(C_mc);
+    if (C_mc && (reinterpret_cast<uintptr_t>(C_mc) & 15)) {
+        snprintf(err, err_len, "bfp8b gemm needs a 16-byte aligned multicast address");
+        return cudaErrorInvalidValue;
+    }
     p.M = M; p.N = N; p.K = K; p.ldc = ldc;
     p.m_tiles = (uint32_t)((M + kBM - 1) / kBM);
     p.n_tiles = (uint32_t)(N / kBN);
     p.k_blocks = (uint32_t)(K / kBK);
     p.Nt = (uint32_t)(N / 32);
     p.status = status;
-    const bool use_pair = forced == 2 || (forced == 0 && M > 256);
+    const bool use_pair = forced == 2 || (forced == 0 && M > 256) || C_mc != nullptr;   // only the pair kernel forwards
     if (use_pair) return launch_bfp8b_gemm_pair(tmap, p, sm_count, stream);
 
     static std::atomic<bool> attr_done[64];

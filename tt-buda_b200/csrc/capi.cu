@@ -30,7 +30,7 @@ cudaError_t launch_requantize(const int32_t *x, int64_t n, const float *scale_a,
                               int64_t inner, float zp, int mode, float lo, float hi, int8_t *out, int sm_count,
                               cudaStream_t stream);
 cudaError_t launch_bfp8b_gemm(const void *A, int64_t M, int64_t K, int64_t lda, const void *W, int64_t N, void *const *C,
-                              int n_dst, int64_t ldc, int sm_count, cudaStream_t stream, unsigned int *status, char *err,
+                              int n_dst, void *C_mc, int64_t ldc, int sm_count, cudaStream_t stream, unsigned int *status, char *err,
                               size_t err_len);
 
 int gemm_kernel_choice(int which);
@@ -1257,8 +1257,25 @@ int buda_requantize(const int32_t *x, int64_t n, const float *inp_scale, const f
     return BUDA_SUCCESS;
 }
 
+static int gemm_scatter_impl(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N, void *const *C_dsts,
+                             int n_dst, void *C_mc, int64_t ldc, void *stream);
+
 int buda_bfp8b_gemm_scatter(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N, void *const *C_dsts,
                             int n_dst, int64_t ldc, void *stream)
+{
+    return gemm_scatter_impl(A, M, K, lda, W_tiles, N, C_dsts, n_dst, nullptr, ldc, stream);
+}
+
+int buda_bfp8b_gemm_multicast(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N, void *C_local,
+                              void *C_multicast, int64_t ldc, void *stream)
+{
+    if (!C_local || !C_multicast) return fail(BUDA_RUNTIME_ERROR, "null matrix pointer");
+    void *dst[1] = {C_local};
+    return gemm_scatter_impl(A, M, K, lda, W_tiles, N, dst, 1, C_multicast, ldc, stream);
+}
+
+static int gemm_scatter_impl(const void *A, int64_t M, int64_t K, int64_t lda, const void *W_tiles, int64_t N, void *const *C_dsts,
+                             int n_dst, void *C_mc, int64_t ldc, void *stream)
 {
     DevCtx *ctx;
     if (int rc = get_ctx(&ctx)) return rc;
@@ -1273,7 +1290,7 @@ int buda_bfp8b_gemm_scatter(const void *A, int64_t M, int64_t K, int64_t lda, co
     for (int d = 0; d < n_dst && d < 8; d++)
         if (!C_dsts[d]) return fail(BUDA_RUNTIME_ERROR, "null destination %d", d);
     char msg[256] = "";
-    cudaError_t e = launch_bfp8b_gemm(A, M, K, lda, W_tiles, N, C_dsts, n_dst, ldc, ctx->sm_count, (cudaStream_t)stream,
+    cudaError_t e = launch_bfp8b_gemm(A, M, K, lda, W_tiles, N, C_dsts, n_dst, C_mc, ldc, ctx->sm_count, (cudaStream_t)stream,
                                       ctx->status, msg, sizeof(msg));
     if (e != cudaSuccess) return msg[0] ? fail(BUDA_RUNTIME_ERROR, "%s", msg) : cuda_fail(e, "gemm launch failed");
     g_launches.fetch_add(1, std::memory_order_relaxed);

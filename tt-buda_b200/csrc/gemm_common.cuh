@@ -198,6 +198,8 @@ struct Params {
     const uint8_t *W;         // weight image: record (kt, nt) at (kt * Nt + nt) * record bytes
     uint16_t *C[kMaxDst];     // destinations (this device first, then peers), row stride ldc ELEMENTS of the output type
     int n_dst;
+    uint16_t *C_mc;           // multicast address of the same matrix on every device of the group (NVSwitch replicates
+                              // one store to all of them), or null
     int64_t M, N, K, ldc;
     uint32_t m_tiles, n_tiles, k_blocks, Nt;
     unsigned int *status;

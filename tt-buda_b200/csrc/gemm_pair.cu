@@ -28,7 +28,9 @@
 //   warps 0-7     epilogue for this CTA's 2 x 128 rows (two warps per tensor-memory lane quadrant, half
 //                 of the columns each); both CTAs' epilogues release the accumulators on the leader's
 //                 acc_empty barrier.  In a launch that also feeds peer devices the same warps then forward
-//                 the piece they wrote to the peers' copies while the next tile's MMAs run
+//                 the piece they wrote to the peers' copies while the next tile's MMAs run: one plain store per
+//                 peer, or ONE multimem store to the multicast address of the matrix, which the NVSwitch
+//                 replicates to every device of the group
 // Every mbarrier wait is bounded; a wait that gives up raises the device status word, the CTA winds
 // down, its partner runs into its own limit, and both meet at the closing cluster barrier (tensor
 // memory is freed on every path).
@@ -124,6 +126,14 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t *bar)
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
                      smem_u32(bar)),
                  "h"((uint16_t)3)
+                 : "memory");
+}
+
+// one 16-byte store that the switch delivers to every device bound to the multicast address
+__device__ __forceinline__ void multimem_st_16(void *mc_addr, const uint4 v)
+{
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+                 "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
                  : "memory");
 }
 
@@ -429,7 +439,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         if (grow < p.M) {
                             const int64_t eo = grow * p.ldc + col_base;
                             const uint4 val = __ldcg(reinterpret_cast<const uint4 *>(p.C[0] + eo));
-                            for (int d = 1; d < p.n_dst; d++) *reinterpret_cast<uint4 *>(p.C[d] + eo) = val;
+                            if (p.C_mc) multimem_st_16(p.C_mc + eo, val);   // every device of the group, this one included
+                            else
+                                for (int d = 1; d < p.n_dst; d++) *reinterpret_cast<uint4 *>(p.C[d] + eo) = val;
                         }
                     }
                 }
@@ -499,7 +511,7 @@ cudaError_t launch_pair(const CUtensorMap &tmap, const gemm::Params &p_in, int s
 // Launch of the CTA-pair Bfp8 kernel.  Same contract as the single-CTA launch; the caller has validated the shapes.
 cudaError_t launch_bfp8b_gemm_pair(const CUtensorMap &tmap, const gemm::Params &p, int sm_count, cudaStream_t stream)
 {
-    if (p.n_dst > 1) return launch_pair<gemm_pair::kKindBfp8, true>(tmap, p, sm_count, stream);
+    if (p.n_dst > 1 || p.C_mc) return launch_pair<gemm_pair::kKindBfp8, true>(tmap, p, sm_count, stream);
     return launch_pair<gemm_pair::kKindBfp8, false>(tmap, p, sm_count, stream);
 }
 
@@ -550,6 +562,7 @@ cudaError_t launch_i8_gemm(const void *A, int64_t M, int64_t K, int64_t lda, con
     p.W = static_cast<const uint8_t *>(W);
     p.C[0] = static_cast<uint16_t *>(C);
     p.n_dst = 1;
+    p.C_mc = nullptr;
     p.M = M; p.N = N; p.K = K; p.ldc = ldc;
     p.status = status;
     p.out_mode = out_mode;

@@ -120,6 +120,7 @@ _SIGS = {
     "buda_requantize": (_i, [_vp, _i64, _vp, _vp, _i64, _i64, _f, _i, _f, _f, _vp, _vp]),
     "buda_bfp8b_gemm": (_i, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp]),
     "buda_bfp8b_gemm_scatter": (_i, [_vp, _i64, _i64, _i64, _vp, _i64, ctypes.POINTER(ctypes.c_void_p), _i, _i64, _vp]),
+    "buda_bfp8b_gemm_multicast": (_i, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _vp, _i64, _vp]),
     "buda_prestride": (_i, [_vp, _i, _u32p, _u64p, _i, ctypes.POINTER(ctypes.c_int), _i, _vp, _u32, _u32, _vp]),
     "buda_i8_gemm": (_i, [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _f, _i, _vp, _i64, _vp]),
     "buda_gemm_select_kernel": (_i, [_i]),

@@ -249,6 +249,17 @@ def bfp8b_matmul_scatter(a, w_image, n, dst_ptrs, ldc):
                                                 _cabi.ptr_array(dst_ptrs), len(dst_ptrs), ldc, _stream()))
 
 
+def bfp8b_matmul_multicast(a, w_image, n, local_ptr, multicast_ptr, ldc):
+    """The same product stored to this device's copy (local_ptr) and, through one multimem store per 16 bytes, to
+    every device bound to the multicast address (multicast_ptr); both already point at this device's column block."""
+    _need_cuda(a, w_image)
+    assert a.dtype == torch.bfloat16 and a.dim() == 2 and a.stride(1) == 1
+    m, k = a.shape
+    with torch.cuda.device(a.device):
+        check(_cabi.lib.buda_bfp8b_gemm_multicast(a.data_ptr(), m, k, a.stride(0), w_image.data_ptr(), n, local_ptr, multicast_ptr,
+                                                  ldc, _stream()))
+
+
 class _RawCudaBuffer:
     """Lets torch view memory it did not allocate (buda_malloc / a mapped peer allocation)."""
 

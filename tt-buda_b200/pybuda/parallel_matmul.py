@@ -5,10 +5,11 @@ activations; it computes its [M, N/g] slice with the tcgen05 kernel, and the sli
 in one of two ways:
 
   * fused (`enable_fused_scatter`, the fast path on GPUs): every rank keeps the full [M, N] output in
-    device memory its peers have mapped, and the matmul kernel's epilogue stores each finished tile
-    into its own copy AND straight into every peer's copy over NVLink, while the tensor cores work on
-    the next tile.  No all-gather, no staging, no permute pass: a barrier after the kernel is the only
-    host-visible exchange step.
+    device memory its peers can reach, and the matmul kernel's epilogue stores each finished tile
+    into its own copy AND into every peer's copy over NVLink, while the tensor cores work on
+    the next tile -- through the NVSwitch's multicast where the system offers it (one multimem store
+    per value, replicated by the switch), else with one plain store per peer.  No all-gather, no
+    staging, no permute pass: a barrier after the kernel is the only host-visible exchange step.
   * library all-gather (the baseline, and what CPU ranks test): the rows are cut into bands and band k
     is gathered with NCCL on a side stream while band k+1 is computed.
 """
@@ -40,17 +41,28 @@ class ColumnParallelBfp8Matmul:
             local_matmul = lambda a, w, nl, out: cuda_ops.bfp8b_matmul(a, w, nl, out=out)
         self._mm = local_matmul
         self.weight_image = None
-        self._shared = None        # SharedDeviceMatrix: this rank's full output, mapped by the peers
+        self._shared = None        # this rank's full output where the peers can reach it
         self._dst_ptrs = None
+        self._mc = None            # set when the output lives in symmetric memory with a multicast mapping
         self._scatter = scatter if scatter is not None else self._scatter_kernel
         self._wait_local = wait_local if wait_local is not None else (lambda: torch.cuda.current_stream().synchronize())
 
-    def enable_fused_scatter(self, m: int):
-        """Allocate this rank's full [m, n] output where the peers can map it, exchange the handles and map
-        theirs.  Collective: every rank of the group calls it with the same m."""
+    def enable_fused_scatter(self, m: int, multicast: Optional[bool] = None):
+        """Allocate this rank's full [m, n] output where the peers can reach it.  Collective: every rank of the group
+        calls it with the same arguments.  multicast=None tries the NVSwitch route first (the matrix in symmetric
+        memory bound to one multicast object, so a rank's epilogue sends each value once and the switch replicates it)
+        and falls back to peer-mapped memory with one store per peer; True / False force one or the other."""
         from . import cuda_ops
 
         self.disable_fused_scatter()
+        self._mc = None
+        if multicast is not False and self.world > 1:
+            self._mc = self._try_multicast(m)
+            if self._mc is None and multicast:
+                raise RuntimeError("no multicast (NVSwitch) mapping of symmetric memory on this system")
+        if self._mc is not None:
+            self._shared = self._mc
+            return self._shared.tensor
         self._shared = cuda_ops.SharedDeviceMatrix(m, self.n)
         handles = [None] * self.world
         if self.world > 1:
@@ -65,18 +77,51 @@ class ColumnParallelBfp8Matmul:
             dist.barrier(group=self.group)
         return self._shared.tensor
 
+    def _try_multicast(self, m: int):
+        """The [m, n] output in torch's symmetric memory with a multicast mapping, or None when the system has none
+        (every rank answers alike: the decision is agreed on with an all-reduce)."""
+        from types import SimpleNamespace
+
+        hdl = tensor = None
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            tensor = symm_mem.empty((m, self.n), dtype=torch.bfloat16, device=torch.device("cuda", torch.cuda.current_device()))
+            hdl = symm_mem.rendezvous(tensor, self.group if self.group is not None else dist.group.WORLD)
+            ok = int(hdl.multicast_ptr != 0)
+        except Exception:   # noqa: BLE001  no symmetric memory / no fabric: the peer-mapped route still works
+            ok = 0
+        agreed = torch.tensor([ok], device="cuda")
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=self.group)
+        if int(agreed.item()) == 0:
+            return None
+        return SimpleNamespace(rows=m, tensor=tensor, handle=hdl, local_ptr=tensor.data_ptr(), mc_ptr=int(hdl.multicast_ptr),
+                               close=lambda: None)
+
     def disable_fused_scatter(self):
         if self._shared is not None:
             torch.cuda.synchronize()
             if self.world > 1:
                 dist.barrier(group=self.group)   # nobody unmaps while a peer may still be storing
             self._shared.close()
-            self._shared, self._dst_ptrs = None, None
+            self._shared, self._dst_ptrs, self._mc = None, None, None
+
+    @property
+    def exchange(self) -> str:
+        """How fused() reaches the peers: "multicast" (NVSwitch replication), "peer stores" or "off"."""
+        if self._shared is None:
+            return "off"
+        return "multicast" if getattr(self, "_mc", None) is not None else "peer stores"
 
     def _scatter_kernel(self, a: torch.Tensor):
         from . import cuda_ops
 
-        cuda_ops.bfp8b_matmul_scatter(a, self.weight_image, self.n_local, self._dst_ptrs, self.n)
+        if getattr(self, "_mc", None) is not None:
+            col_bytes = self.col0 * 2
+            cuda_ops.bfp8b_matmul_multicast(a, self.weight_image, self.n_local, self._mc.local_ptr + col_bytes,
+                                            self._mc.mc_ptr + col_bytes, self.n)
+        else:
+            cuda_ops.bfp8b_matmul_scatter(a, self.weight_image, self.n_local, self._dst_ptrs, self.n)
 
     def fused(self, a: torch.Tensor, sync: bool = True) -> torch.Tensor:
         """One kernel: this rank's column block, written into every rank's output.  With sync (default) the call
