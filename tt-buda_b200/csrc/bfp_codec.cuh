@@ -170,8 +170,9 @@ __device__ __forceinline__ bool bfp_encode16_int(const uint32_t (&x)[16], uint32
 }
 
 // Encode one block.  x: the 16 values as binary32 bit patterns.  Returns the shared exponent and
-// the packed datums (out[0] holds datums 0.., little-endian).
-template <int M>
+// the packed datums (out[0] holds datums 0.., little-endian).  RZ: truncate instead of rounding to nearest even (the
+// same instruction count: only the rounding mode of the multiply-add differs).
+template <int M, bool RZ = false>
 __device__ __forceinline__ void bfp_encode16(const uint32_t (&x)[16], uint32_t &E_out,
                                              uint32_t (&out)[BfpTraits<M>::words])
 {
@@ -183,10 +184,10 @@ __device__ __forceinline__ void bfp_encode16(const uint32_t (&x)[16], uint32_t &
         const float S = __uint_as_float((uint32_t)(M + 253 - (int)E) << 23);  // 2^(M-1+127-E)
         uint32_t y[16];
 #pragma unroll
-        for (int i = 0; i < 16; i++) y[i] = min(bfp_quantise_bits<false>(x[i], S), kMagicBits + qmax);  // Inf / NaN and round-ups saturate here
+        for (int i = 0; i < 16; i++) y[i] = min(bfp_quantise_bits<RZ>(x[i], S), kMagicBits + qmax);  // Inf / NaN and round-ups saturate here
         bfp_pack_datums<M>(x, y, out);
     } else {
-        (void)bfp_encode16_int<M>(x, E, false, out);
+        (void)bfp_encode16_int<M>(x, E, RZ, out);
     }
 }
 

@@ -202,6 +202,7 @@ struct Params {
                               // one store to all of them), or null
     int64_t M, N, K, ldc;
     uint32_t m_tiles, n_tiles, k_blocks, Nt;
+    uint32_t raster_m;        // pair kernel: output tiles are walked in groups of this many tile rows (see tile_coords)
     unsigned int *status;
     // int8 kind only: what the epilogue does with the int32 accumulators
     int out_mode;             // BUDA_I8_OUT_*
@@ -209,6 +210,19 @@ struct Params {
     int64_t scale_len;
     float zero_point, lo, hi;
 };
+
+// Which output tile the t-th work unit is.  Tiles are walked in groups of raster_m tile rows: down the rows of a group,
+// then along the columns, then the next group.  The pairs that run at the same time then share a few tile rows of the
+// activations, which stay in L2 for the whole sweep over the columns, instead of streaming all of A once per wave.
+__device__ __forceinline__ void tile_coords(const Params &p, uint32_t t, uint32_t &m_blk, uint32_t &n_blk)
+{
+    const uint32_t per_group = p.raster_m * p.n_tiles;
+    const uint32_t group = t / per_group, within = t - group * per_group;
+    const uint32_t m0 = group * p.raster_m;
+    const uint32_t rows = min(p.raster_m, p.m_tiles - m0);      // the last group may be shorter
+    n_blk = within / rows;
+    m_blk = m0 + (within - n_blk * rows);
+}
 
 // Epilogue of the int8 matmul for 32 consecutive columns of one row (first column `col`): the int32
 // accumulators as they are, requantised to int8, or dequantised to float32.  The arithmetic is the golden

@@ -396,53 +396,6 @@ requantize_once_kernel(const int32_t *__restrict__ x, int64_t chunks, const floa
                                                             pack_i8x4(q[8], q[9], q[10], q[11]), pack_i8x4(q[12], q[13], q[14], q[15])));
 }
 
-// Scales along the last axis, short-lived blocks in address order: a block takes R consecutive runs of 256 chunks; when
-// the scale period divides 256 chunks, a thread's R chunks all sit in the same 16 columns, so it fetches its 16 scales
-// once and all of its data loads (4 R x 128 bit) are in flight before the first is used.  Between the one-chunk form
-// (address order, but 16 scales re-fetched per chunk: 5070 GB/s) and the resident grid (scales fetched once, but every
-// block strides over the whole tensor: 6070 GB/s at 2^27 elements, 0.74-0.83 of the copy peak at the 2^25 of config 3).
-template <int MODE, int R>
-__global__ void __launch_bounds__(256)
-requantize_rows_kernel(const int32_t *__restrict__ x, int64_t chunks, const float *__restrict__ scale_a,
-                       const float *__restrict__ scale_b, ScaleSel sel, float zp, float lo, float hi, int8_t *__restrict__ out)
-{
-    const int64_t c0 = (int64_t)blockIdx.x * (256 * R) + threadIdx.x;
-    int xi[R][16];
-#pragma unroll
-    for (int j = 0; j < R; j++) {
-        const int64_t c = c0 + j * 256;
-        if (c < chunks) {
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-                const int4 t = __ldcs(reinterpret_cast<const int4 *>(x + (c << 4)) + q);
-                xi[j][4 * q] = t.x; xi[j][4 * q + 1] = t.y; xi[j][4 * q + 2] = t.z; xi[j][4 * q + 3] = t.w;
-            }
-        }
-    }
-    float s[16];
-    load_scales16<kScaleLastAxis16>(scale_a, sel, c0 << 4, 16, s);
-    if (MODE == 0) {
-        float sb[16];
-        load_scales16<kScaleLastAxis16>(scale_b, sel, c0 << 4, 16, sb);
-#pragma unroll
-        for (int k = 0; k < 16; k++) s[k] = __fdiv_rn(s[k], sb[k]);
-    }
-#pragma unroll
-    for (int j = 0; j < R; j++) {
-        const int64_t c = c0 + j * 256;
-        if (c >= chunks) break;
-        float pz[16];
-#pragma unroll
-        for (int k = 0; k < 16; k++) pz[k] = __fadd_rn(__fmul_rn(s[k], __int2float_rn(xi[j][k])), zp);
-        round_half_even16(pz);
-        uint32_t q[16];
-#pragma unroll
-        for (int k = 0; k < 16; k++) q[k] = clamp_cast_i8<true>(pz[k], lo, hi);
-        __stcs(reinterpret_cast<uint4 *>(out + (c << 4)), make_uint4(pack_i8x4(q[0], q[1], q[2], q[3]), pack_i8x4(q[4], q[5], q[6], q[7]),
-                                                                    pack_i8x4(q[8], q[9], q[10], q[11]), pack_i8x4(q[12], q[13], q[14], q[15])));
-    }
-}
-
 // ------------------------------------------------------------------------------------------------
 // host launchers
 // ------------------------------------------------------------------------------------------------
@@ -574,7 +527,9 @@ cudaError_t launch_requantize(const int32_t *x, int64_t n, const float *scale_a,
     const bool fast = lo >= -4194304.0f && hi <= 4194304.0f;
     // same scales in every sweep of the grid?  (per-tensor: trivially; last axis: stride a multiple of the period)
     const int hoist = (sm == kScalePerTensor || (sm == kScaleLastAxis16 && ((int64_t)grid * 256 * 16) % scale_len == 0)) ? 1 : 0;
-    // (with scales along the last axis the resident blocks that fetch their 16 scales once stay faster: 6070 vs 5070 GB/s)
+    // (with scales along the last axis the resident blocks that fetch their 16 scales once stay faster: 6070 vs 5070 GB/s for
+    // one chunk per short-lived thread, and 3840 GB/s at the 2^25-element size for short-lived blocks of four runs of 256
+    // chunks whose threads fetch their scales once -- at ~100 registers only two such blocks fit an SM)
     if (vec && fast && sm == kScalePerTensor && (n & 15) == 0 && n > 0) {
         const int64_t chunks = n >> 4;
         const unsigned once_grid = (unsigned)((chunks + 255) / 256);
@@ -582,15 +537,6 @@ cudaError_t launch_requantize(const int32_t *x, int64_t n, const float *scale_a,
             requantize_once_kernel<0, kScalePerTensor><<<once_grid, 256, 0, stream>>>(x, chunks, scale_a, scale_b, sel, zp, lo, hi, out);
         else
             requantize_once_kernel<1, kScalePerTensor><<<once_grid, 256, 0, stream>>>(x, chunks, scale_a, scale_b, sel, zp, lo, hi, out);
-        return cudaGetLastError();
-    }
-    // scales along the last axis whose period divides a block's 256 chunks: R runs of 256 chunks per short-lived block
-    if (vec && fast && sm == kScaleLastAxis16 && (n & 15) == 0 && n > 0 && (256 * 16) % scale_len == 0) {
-        constexpr int R = 4;
-        const int64_t chunks = n >> 4;
-        const unsigned rows_grid = (unsigned)((chunks + 256 * R - 1) / (256 * R));
-        if (mode == 0) requantize_rows_kernel<0, R><<<rows_grid, 256, 0, stream>>>(x, chunks, scale_a, scale_b, sel, zp, lo, hi, out);
-        else requantize_rows_kernel<1, R><<<rows_grid, 256, 0, stream>>>(x, chunks, scale_a, scale_b, sel, zp, lo, hi, out);
         return cudaGetLastError();
     }
 #define CALL(SMV)                                                                                                                 \

@@ -47,18 +47,19 @@ class ColumnParallelBfp8Matmul:
         self._scatter = scatter if scatter is not None else self._scatter_kernel
         self._wait_local = wait_local if wait_local is not None else (lambda: torch.cuda.current_stream().synchronize())
 
-    def enable_fused_scatter(self, m: int, multicast: Optional[bool] = None):
+    def enable_fused_scatter(self, m: int, multicast: bool = False):
         """Allocate this rank's full [m, n] output where the peers can reach it.  Collective: every rank of the group
-        calls it with the same arguments.  multicast=None tries the NVSwitch route first (the matrix in symmetric
-        memory bound to one multicast object, so a rank's epilogue sends each value once and the switch replicates it)
-        and falls back to peer-mapped memory with one store per peer; True / False force one or the other."""
+        calls it with the same arguments.  Default: peer-mapped memory, one store per peer.  multicast=True puts the
+        matrix in symmetric memory bound to one NVSwitch multicast object instead, so a rank's epilogue sends each
+        value once and the switch replicates it (measured slower than the peer stores on 2 and 4 B200s, where every
+        GPU also receives its own block back through the switch; kept as an option)."""
         from . import cuda_ops
 
         self.disable_fused_scatter()
         self._mc = None
-        if multicast is not False and self.world > 1:
+        if multicast and self.world > 1:
             self._mc = self._try_multicast(m)
-            if self._mc is None and multicast:
+            if self._mc is None:
                 raise RuntimeError("no multicast (NVSwitch) mapping of symmetric memory on this system")
         if self._mc is not None:
             self._shared = self._mc
