@@ -132,8 +132,11 @@ int buda_tile_map(const buda_queue_geom *geom, uint32_t t, uint32_t r, uint32_t 
 
 /* Row-major tensor -> queue image, converting to dst_df on the way.
  * src_df Float32 or Float16_b -> dst_df Bfp8_b / Bfp4_b / Bfp2_b (block-float pack), or
+ * src_df Float16 -> Bfp8 / Bfp4 / Bfp2 (5-bit shared exponent), or
+ * src_df Float32 / Float16_b / Float16 -> Lf8 (one 1-5-2 float per element, docs/public/dataformats.rst:24:
+ * IEEE-style with subnormals, infinities and NaNs, round to nearest even), or
  * src_df == dst_df of a plain format (Float32, Float16, Float16_b, Int8, Int32, UInt16, Lf8,
- * RawUInt8/16/32): layout only.
+ * RawUInt8/16/32; any pair of equal element width): layout only.
  * Replaces the conversion half of tt::backend::tilize_tensor / push_input
  * (bound at backend_api.cpp:688-704). */
 int buda_tilize_pack(const void *src, int src_df, const uint32_t shape[4], const uint64_t strides_bytes[4],

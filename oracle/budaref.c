@@ -398,6 +398,53 @@ static inline uint16_t float_to_half_bits(float f)
 static int is_bfp_a(int df) { return df == DF_Bfp8 || df == DF_Bfp4 || df == DF_Bfp2; }
 
 /* ---------------------------------------------------------------------------------------------
+ * Lf8: "1-bit sign, 5-bit exponent, 2-bit mantissa, no shared exponent, floating point"
+ * (docs/public/dataformats.rst:24).  The reference has no host conversion for it and no torch dtype
+ * (pybuda/pybuda/tensor.py:563-632 raise), so this is a reading of the format table, PARITY UNPINNED:
+ * the IEEE-754 rules for those field widths (bias 15, subnormals, infinities, NaNs), round to nearest
+ * even.  Written on values (frexp / ldexp), not on bit patterns, so that it is independent of the
+ * device code it checks.
+ * ------------------------------------------------------------------------------------------- */
+uint8_t ref_lf8_encode(double v)
+{
+    uint8_t sign = signbit(v) ? 0x80u : 0u;
+    if (v != v) return (uint8_t)(sign | 0x7fu);
+    double a = fabs(v);
+    if (isinf(a)) return (uint8_t)(sign | 0x7cu);
+    if (a < ldexp(1.0, -14)) return (uint8_t)(sign | (uint8_t)nearbyint(ldexp(a, 16)));  /* multiples of 2^-16; 4 = 2^-14 */
+    int e;
+    double m = frexp(a, &e);            /* a = m * 2^e, 0.5 <= m < 1 */
+    int q = (int)nearbyint(ldexp(m, 3)) - 4;   /* (2m - 1) * 4 rounded to nearest even: 0..4 */
+    e -= 1;
+    if (q == 4) { q = 0; e += 1; }
+    if (e > 15) return (uint8_t)(sign | 0x7cu);  /* past the largest finite value 1.75 * 2^15 */
+    return (uint8_t)(sign | ((e + 15) << 2) | q);
+}
+
+double ref_lf8_decode(uint8_t c)
+{
+    int e = (c >> 2) & 31, m = c & 3;
+    double a;
+    if (e == 31) a = m ? NAN : INFINITY;
+    else if (e == 0) a = ldexp((double)m, -16);
+    else a = ldexp(1.0 + m / 4.0, e - 15);
+    return (c & 0x80u) ? -a : a;
+}
+
+/* binary16 bit pattern -> value (exact) */
+static inline double half_bits_to_double(uint16_t h)
+{
+    int e = (h >> 10) & 31, m = h & 0x3ff;
+    double a;
+    if (e == 31) a = m ? NAN : INFINITY;
+    else if (e == 0) a = ldexp((double)m, -24);
+    else a = ldexp(1.0 + m / 1024.0, e - 15);
+    return (h & 0x8000u) ? -a : a;
+}
+
+static int is_lf8_float_side(int df) { return df == DF_Float32 || df == DF_Float16_b || df == DF_Float16; }
+
+/* ---------------------------------------------------------------------------------------------
  * Element access helpers
  * ------------------------------------------------------------------------------------------- */
 static inline uint32_t load_as_f32_bits(const uint8_t *p, int df)
@@ -481,7 +528,10 @@ int ref_tilize_pack(const void *src_, int src_df, const uint32_t shape[4], const
     if (make_ctx(&c, g, shape, dst_df, with_header)) return 1;
     int m = bfp_mant_bits(dst_df);
     int es = elem_bytes(src_df);
-    if (m && is_bfp_a(dst_df)) {
+    int lf8 = (dst_df == DF_Lf8 && is_lf8_float_side(src_df));   /* element-wise conversion; Lf8 -> Lf8 is a relayout */
+    if (lf8) {
+        /* nothing more to check */
+    } else if (m && is_bfp_a(dst_df)) {
         if (src_df != DF_Float16) return 1;
     } else if (m) {
         if (!(dst_df == DF_Bfp8_b || dst_df == DF_Bfp4_b || dst_df == DF_Bfp2_b)) return 1;
@@ -513,7 +563,15 @@ int ref_tilize_pack(const void *src_, int src_df, const uint32_t shape[4], const
                 uint32_t estride = strides[3];
                 if (tr >= c.th) { p = zeros; estride = (uint32_t)es; }   /* rows a tiny tile does not hold */
                 int blk = pos * 16 + fr;
-                if (m && is_bfp_a(dst_df)) {
+                if (lf8) {
+                    for (int i = 0; i < 16; i++) {
+                        const uint8_t *q = p + (uint64_t)i * estride;
+                        double v;
+                        if (src_df == DF_Float16) { uint16_t h; memcpy(&h, q, 2); v = half_bits_to_double(h); }
+                        else { uint32_t b = load_as_f32_bits(q, src_df); float f; memcpy(&f, &b, 4); v = (double)f; }
+                        rec[(long)blk * 16 + i] = ref_lf8_encode(v);
+                    }
+                } else if (m && is_bfp_a(dst_df)) {
                     uint16_t hv[16];
                     for (int i = 0; i < 16; i++) memcpy(&hv[i], p + (uint64_t)i * estride, 2);
                     int bpb = 16 * (m + 1) / 8;
@@ -544,7 +602,10 @@ int ref_unpack_untilize(const void *src_, int src_df, int with_header, const ref
     if (make_ctx(&c, g, shape, src_df, with_header)) return 1;
     int m = bfp_mant_bits(src_df);
     int es = elem_bytes(dst_df);
-    if (m && is_bfp_a(src_df)) {
+    int lf8 = (src_df == DF_Lf8 && is_lf8_float_side(dst_df));
+    if (lf8) {
+        /* nothing more to check */
+    } else if (m && is_bfp_a(src_df)) {
         if (!(dst_df == DF_Float32 || dst_df == DF_Float16)) return 1;
     } else if (m) {
         if (!(src_df == DF_Bfp8_b || src_df == DF_Bfp4_b || src_df == DF_Bfp2_b)) return 1;
@@ -572,7 +633,23 @@ int ref_unpack_untilize(const void *src_, int src_df, int with_header, const ref
                 uint64_t col0 = (uint64_t)ct * 32 + (face & 1) * 16;
                 uint8_t *p = base + r * strides[2] + col0 * strides[3];
                 int blk = pos * 16 + fr;
-                if (m && is_bfp_a(src_df)) {
+                if (lf8) {
+                    for (int i = 0; i < 16; i++) {
+                        uint8_t code = rec[(long)blk * 16 + i];
+                        uint8_t *q = p + (uint64_t)i * strides[3];
+                        if (dst_df == DF_Float16) {
+                            uint16_t h = (uint16_t)(code << 8);   /* the code is the upper byte of the binary16 of the same value */
+                            memcpy(q, &h, 2);
+                        } else {
+                            float f = (float)ref_lf8_decode(code);   /* exact */
+                            if ((code & 0x7cu) == 0x7cu && (code & 3u)) {   /* NaN: the two mantissa bits go to the top of the wider mantissa */
+                                uint32_t b = ((uint32_t)(code & 0x80u) << 24) | 0x7f800000u | ((uint32_t)(code & 3u) << 21);
+                                memcpy(&f, &b, 4);
+                            }
+                            store_from_f32(q, dst_df, f);
+                        }
+                    }
+                } else if (m && is_bfp_a(src_df)) {
                     float vals[16];
                     int bpb = 16 * (m + 1) / 8;
                     ref_bfp_a_unpack_block(rec[exponent_byte_index(blk)], rec + 64 + (long)blk * bpb, m, vals);

@@ -103,6 +103,10 @@ def lib():
         L.ref_tilize_pack.argtypes = [vp, i32, u32p, u32p, gp, i32, i32, vp]
         L.ref_unpack_untilize.restype = i32
         L.ref_unpack_untilize.argtypes = [vp, i32, i32, gp, vp, i32, u32p, u32p]
+        L.ref_lf8_encode.restype = ctypes.c_uint8
+        L.ref_lf8_encode.argtypes = [ctypes.c_double]
+        L.ref_lf8_decode.restype = ctypes.c_double
+        L.ref_lf8_decode.argtypes = [ctypes.c_uint8]
         L.ref_bfp_pack_block.restype = None
         L.ref_bfp_pack_block.argtypes = [vp, i32, vp, vp]
         L.ref_bfp_unpack_block.restype = None
@@ -206,6 +210,15 @@ def unpack_untilize(img, src_df, shape, dst_dtype=np.float32, geom=None, with_he
                                    dst_df, _u32x4(shape4), _u32x4(_strides4(shape4, out.itemsize)))
     assert rc == 0, "ref_unpack_untilize rejected its arguments"
     return out.reshape(shape)
+
+
+def lf8_encode(v):
+    """One value -> its Lf8 code (1-5-2 float, round to nearest even)."""
+    return int(lib().ref_lf8_encode(float(v)))
+
+
+def lf8_decode(code):
+    return float(lib().ref_lf8_decode(int(code)))
 
 
 def bfp_pack_block(bits16, mant_bits):

@@ -126,3 +126,51 @@ def decode_block(E, data: bytes, m, policy=DEFAULT):
             assert shift >= 0, "a decoded value is never below the smallest subnormal"
         out.append(bits | (s << 31))
     return out
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# Lf8: 1 sign, 5 exponent, 2 mantissa bits per element, no shared exponent (docs/public/dataformats.rst:24 of the
+# reference).  Frozen reading (the reference has no host conversion to compare with): the IEEE-754 rules for those
+# field widths -- bias 15, subnormals, code 0x7c = infinity, 0x7d-0x7f = NaN -- and round to nearest, ties to the
+# even code.  Stated here as "the nearest representable value", by exact comparison against the whole value table.
+# ------------------------------------------------------------------------------------------------------------------
+def lf8_value(code: int) -> Fraction:
+    """Exact value of a finite, non-negative code (0 .. 0x7b)."""
+    e, m = (code >> 2) & 31, code & 3
+    assert code < 0x7C
+    if e == 0:
+        return Fraction(m, 4) * Fraction(2) ** (-14)
+    return (1 + Fraction(m, 4)) * Fraction(2) ** (e - 15)
+
+
+_LF8_TABLE = [lf8_value(c) for c in range(0x7C)]
+# the value code 0x7c would have if the exponent range went on: deciding between the largest finite value and infinity
+_LF8_NEXT = Fraction(2) ** 16
+
+
+def lf8_encode_bits(b: int) -> int:
+    """binary32 bit pattern -> Lf8 code."""
+    sign = (b >> 24) & 0x80
+    e, frac = (b >> 23) & 0xFF, b & 0x7FFFFF
+    if e == 255:
+        return sign | (0x7F if frac else 0x7C)
+    mag = Fraction(frac, 1 << 23) * Fraction(2) ** (-126) if e == 0 else Fraction(frac | 0x800000, 1 << 23) * Fraction(2) ** (e - 127)
+    table = _LF8_TABLE + [_LF8_NEXT]
+    lo = max(c for c in range(len(table)) if table[c] <= mag) if mag >= 0 else 0
+    if lo == len(table) - 1:
+        return sign | 0x7C
+    down, up = mag - table[lo], table[lo + 1] - mag
+    code = lo if down < up else lo + 1 if up < down else (lo if lo % 2 == 0 else lo + 1)
+    return sign | code
+
+
+def lf8_decode_bits(code: int) -> int:
+    """Lf8 code -> binary32 bit pattern of the same value (exact; NaN keeps its two mantissa bits on top)."""
+    sign = (code & 0x80) << 24
+    c = code & 0x7F
+    if c >= 0x7C:
+        return sign | 0x7F800000 | ((c & 3) << 21)
+    v = lf8_value(c)
+    if v == 0:
+        return sign
+    return sign | f2b(float(v))

@@ -4,6 +4,7 @@ unpinned Bfp encoding) against hand-worked blocks and an independent pure-Python
 frozen spec."""
 import itertools
 import math
+import os
 import struct
 
 import numpy as np
@@ -547,3 +548,65 @@ def test_transform_restatements_match_the_reference_vectors(oracle):
         assert np.array_equal(got.reshape(want.shape), want), ("pad", k)
         k += 1
     assert k == 5
+
+
+# ------------------------------------------------------------------------------------------------
+# Lf8 (1-5-2 float per element).  Parity unpinned: the reference documents the field widths only
+# (docs/public/dataformats.rst:24).  The oracle is checked against the exact-arithmetic spec's committed
+# vectors and against an independent implementation of the same IEEE-style format (torch.float8_e5m2).
+# ------------------------------------------------------------------------------------------------
+def _lf8_kat():
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "lf8_kat.npz"))
+
+
+def test_lf8_oracle_matches_committed_known_answers(oracle):
+    kat = _lf8_kat()
+    vals = kat["bits"].view(np.float32)
+    got = np.array([oracle.lf8_encode(v) for v in vals.astype(np.float64)], dtype=np.uint8)
+    nan = np.isnan(vals)
+    assert np.array_equal(got[~nan], kat["codes"][~nan])
+    assert np.all((got[nan] & 0x7F) == 0x7F)
+    for c in range(256):
+        want = np.array([kat["decode"][c]], dtype=np.uint32).view(np.float32)[0]
+        have = np.float32(oracle.lf8_decode(c))
+        assert (np.isnan(want) and np.isnan(have)) or want.view(np.uint32) == have.view(np.uint32), c
+
+
+def test_lf8_spec_vectors_are_reproducible():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bfp_spec_lf8", os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "bfp_spec.py"))
+    S = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(S)
+    kat = _lf8_kat()
+    for i in list(range(0, 60)) + list(range(60, len(kat["bits"]), 211)):
+        assert S.lf8_encode_bits(int(kat["bits"][i])) == int(kat["codes"][i])
+
+
+def test_lf8_oracle_agrees_with_an_independent_e5m2_conversion(oracle):
+    if not hasattr(torch, "float8_e5m2"):
+        pytest.skip("this torch has no float8_e5m2")
+    bits = (np.arange(65536, dtype=np.uint32) << 16)          # every bfloat16 pattern, widened
+    rng = np.random.default_rng(5)
+    more = (rng.standard_normal(65536) * np.exp(rng.uniform(-14, 12, 65536))).astype(np.float32).view(np.uint32)
+    x = np.concatenate([bits, more]).view(np.float32).reshape(1, 1, 128, 1024)
+    img = oracle.tilize_pack(x, oracle.Lf8)
+    assert img.size == x.size
+    codes = oracle.unpack_untilize(img, oracle.Lf8, x.shape, np.uint8, dst_df=oracle.Lf8)   # relayout back to row-major
+    t8 = torch.from_numpy(x.copy()).to(torch.float8_e5m2)
+    nan = np.isnan(x)
+    assert np.array_equal(codes[~nan], t8.view(torch.uint8).numpy()[~nan])
+    back = oracle.unpack_untilize(img, oracle.Lf8, x.shape, np.float32)
+    assert np.array_equal(back.view(np.uint32)[~nan], t8.to(torch.float32).numpy().view(np.uint32)[~nan])
+    assert np.all(np.isnan(back[nan]))
+    # bfloat16 and binary16 sources and destinations
+    xb = (x.view(np.uint32) >> 16).astype(np.uint16)          # truncated to bfloat16: compare with its own widening
+    img_of_widened = oracle.tilize_pack((xb.astype(np.uint32) << 16).view(np.float32), oracle.Lf8)
+    assert np.array_equal(oracle.tilize_pack(xb, oracle.Lf8, src_df=oracle.Float16_b), img_of_widened)
+    xh = x.astype(np.float16)
+    imgh = oracle.tilize_pack(xh, oracle.Lf8)
+    th8 = torch.from_numpy(xh.copy()).to(torch.float8_e5m2)
+    nanh = np.isnan(xh)
+    codesh = oracle.unpack_untilize(imgh, oracle.Lf8, x.shape, np.uint8, dst_df=oracle.Lf8)
+    assert np.array_equal(codesh[~nanh], th8.view(torch.uint8).numpy()[~nanh])
+    backh = oracle.unpack_untilize(imgh, oracle.Lf8, x.shape, np.float16)
+    assert np.array_equal(backh.view(np.uint16), (codesh.astype(np.uint16) << 8))

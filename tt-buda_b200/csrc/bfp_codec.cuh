@@ -328,6 +328,46 @@ __device__ __forceinline__ uint32_t half_bits_to_float_bits(uint32_t h)
     return a | ((h & 0x8000u) << 16);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Lf8: a float of 1 sign, 5 exponent and 2 mantissa bits per element, no shared exponent
+// (docs/public/dataformats.rst:24 of the reference).  The reference has no host-side conversion for it, so the
+// arithmetic is this library's reading: the IEEE-754 rules of a binary format with those field widths (bias 15,
+// subnormals, infinities and NaNs), rounding to nearest even -- the upper byte of a binary16.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t lf8_encode_float_bits(uint32_t u)
+{
+    const uint32_t a = u & 0x7fffffffu;
+    uint32_t c;
+    if (a > 0x7f800000u) {
+        c = 0x7fu;                                   // NaN
+    } else if (a >= (113u << 23)) {                  // 2^-14 and above: a normal result, or past the largest one
+        // exponent field and two mantissa bits, rounded to nearest even; a carry out of the mantissa moves up the exponent
+        const uint32_t r = (a + 0x000fffffu + ((a >> 21) & 1u)) >> 21;
+        c = min(r - (112u << 2), 0x7cu);             // 0x7c = infinity
+    } else {
+        c = (uint32_t)__float2int_rn(__uint_as_float(a) * 65536.0f);   // multiples of 2^-16: 0 .. 4 (4 = the smallest normal)
+    }
+    return c | ((u >> 24) & 0x80u);
+}
+
+__device__ __forceinline__ uint32_t lf8_encode_half_bits(uint32_t h)
+{
+    const uint32_t a = h & 0x7fffu;
+    const uint32_t c = a > 0x7c00u ? 0x7fu : (a + 0x7fu + ((a >> 8) & 1u)) >> 8;   // the same rounding on the binary16 bit pattern
+    return c | ((h >> 8) & 0x80u);
+}
+
+// exact: every Lf8 value is a binary32 (and a bfloat16: upper half of the result; and a binary16: code << 8)
+__device__ __forceinline__ uint32_t lf8_decode_float_bits(uint32_t c)
+{
+    const uint32_t e = (c >> 2) & 31u, m = c & 3u;
+    uint32_t a;
+    if (e == 0u) a = __float_as_uint((float)m * 1.52587890625e-05f);
+    else if (e == 31u) a = 0x7f800000u | (m << 21);
+    else a = ((e + 112u) << 23) | (m << 21);
+    return a | ((c & 0x80u) << 24);
+}
+
 // binary32 block exponent of widened binary16 data -> the 5-bit exponent byte
 __device__ __forceinline__ uint32_t a_exponent_byte(uint32_t e32) { return e32 > 112u ? e32 - 112u : 0u; }
 

@@ -23,6 +23,10 @@ __host__ __device__ inline int bfp_mant_bits(int df)
     }
 }
 
+// Value of the kernels' mantissa-bits parameter that selects the element-wise conversion to / from Lf8 (7 / 3 / 1 are
+// the block-float formats, 0 a relayout that keeps the element bytes).
+constexpr int kLf8 = 8;
+
 __host__ __device__ inline int plain_elem_bytes(int df)
 {
     switch (df) {

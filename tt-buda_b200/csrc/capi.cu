@@ -208,6 +208,12 @@ int classify(int rm_df, int q_df, int &mant, int &es, bool unpacking = false)
         es = rm_df == BUDA_DF_Float32 ? 4 : 2;
         return BUDA_SUCCESS;
     }
+    if (q_df == BUDA_DF_Lf8 && (rm_df == BUDA_DF_Float32 || rm_df == BUDA_DF_Float16_b || rm_df == BUDA_DF_Float16)) {
+        // element-wise conversion to / from the 1-5-2 float (direct kernels only); an Lf8 row-major side is a relayout
+        mant = kLf8;
+        es = rm_df == BUDA_DF_Float32 ? 4 : 2;
+        return BUDA_SUCCESS;
+    }
     es = plain_elem_bytes(q_df);
     if (es == 0) return fail(BUDA_RUNTIME_ERROR, "unsupported queue data format %d", q_df);
     if (plain_elem_bytes(rm_df) != es)
@@ -216,16 +222,20 @@ int classify(int rm_df, int q_df, int &mant, int &es, bool unpacking = false)
     return BUDA_SUCCESS;
 }
 
+// The kernels' flag for a binary16 row-major side: the "a" block-float formats travel as binary16, and Lf8 converts
+// from / to it as well as from / to the 8-bit-exponent floats.
+inline int half_side(int rm_df, int q_df) { return (is_bfp_a(q_df) || (q_df == BUDA_DF_Lf8 && rm_df == BUDA_DF_Float16)) ? 1 : 0; }
+
 inline bool aligned16(uint64_t v) { return (v & 15u) == 0; }
 
 // The staged (bulk-copy) kernels need every row start 16-byte aligned on both sides; the direct
 // kernels use 4-element vector accesses when rows are aligned to 4 elements.
-void pick_path(const TileJob &j, const PtrTable &p, int batch, int es, int &path, int &vec_ok)
+void pick_path(const TileJob &j, const PtrTable &p, int batch, int es, int &path, int &vec_ok, int mant = 0)
 {
     const uint64_t valign = 4u * (uint64_t)es - 1u;
     uint64_t bits = j.stride_w | j.stride_z | j.stride_r;
     for (int b = 0; b < batch; b++) bits |= (uint64_t)p.src[b] | (uint64_t)p.dst[b];
-    path = ((bits & 15u) == 0 && j.tile_h == 32u) ? 0 : 1;   // tiny tiles: direct kernels only
+    path = ((bits & 15u) == 0 && j.tile_h == 32u && mant != kLf8) ? 0 : 1;   // tiny tiles and Lf8 conversions: direct kernels only
     vec_ok = (bits & valign) == 0 ? 1 : 0;
 }
 
@@ -332,12 +342,12 @@ int tilize_device(int n, const void *const *srcs, int src_df, const uint32_t sha
             pt.dst[b] = (uint8_t *)dsts[b0 + b];
         }
         int path, vec_ok;
-        pick_path(job, pt, nb, es, path, vec_ok);
+        pick_path(job, pt, nb, es, path, vec_ok, mant);
         if (force_path >= 0) {
             if (force_path == 0 && path != 0) return fail(BUDA_RUNTIME_ERROR, "staged path needs 16-byte aligned rows and 32-row tiles");
             path = force_path;
         }
-        if (int rc = launch_uniform(0, ctx, job, pt, nb, mant, es, is_bfp_a(dst_df) ? 1 : 0, path, vec_ok, stream)) return rc;
+        if (int rc = launch_uniform(0, ctx, job, pt, nb, mant, es, half_side(src_df, dst_df), path, vec_ok, stream)) return rc;
     }
     return BUDA_SUCCESS;
 }
@@ -368,12 +378,12 @@ int untilize_device(int n, const void *const *srcs, int src_df, int with_header,
             pt.dst[b] = (uint8_t *)dsts[b0 + b];
         }
         int path, vec_ok;
-        pick_path(job, pt, nb, es, path, vec_ok);
+        pick_path(job, pt, nb, es, path, vec_ok, mant);
         if (force_path >= 0) {
             if (force_path == 0 && path != 0) return fail(BUDA_RUNTIME_ERROR, "staged path needs 16-byte aligned rows and 32-row tiles");
             path = force_path;
         }
-        if (int rc = launch_uniform(1, ctx, job, pt, nb, mant, es, is_bfp_a(src_df) ? 1 : 0, path, vec_ok, stream)) return rc;
+        if (int rc = launch_uniform(1, ctx, job, pt, nb, mant, es, half_side(dst_df, src_df), path, vec_ok, stream)) return rc;
     }
     return BUDA_SUCCESS;
 }
@@ -677,7 +687,7 @@ int jobs_device(int direction, int n, const buda_tensor_job *jobs, int rm_df, in
     if (!jobs) return fail(BUDA_RUNTIME_ERROR, "null job table");
     int mant, es;
     if (int rc = classify(rm_df, q_df, mant, es, direction == 1)) return rc;
-    const int a_format = is_bfp_a(q_df) ? 1 : 0;
+    const int a_format = half_side(rm_df, q_df);
     const BfpPolicy pol = current_policy();
     GenTable *tab = new GenTable;
     tab->n = 0;
@@ -712,7 +722,7 @@ int jobs_device(int direction, int n, const buda_tensor_job *jobs, int rm_df, in
         pt.src[0] = (const uint8_t *)(direction == 0 ? jb.tensor : jb.image);
         pt.dst[0] = (uint8_t *)(direction == 0 ? jb.image : const_cast<void *>(jb.tensor));
         int path, vec_ok;
-        pick_path(j, pt, 1, es, path, vec_ok);
+        pick_path(j, pt, 1, es, path, vec_ok, mant);
         if (path == 0) {
             common = j;
             common.pol = pol;
@@ -991,7 +1001,7 @@ int buda_queue_write_view(const void *src, int src_df, const uint32_t shape[4], 
     memset(&pt, 0, sizeof(pt));
     pt.src[0] = (const uint8_t *)src;
     pt.dst[0] = (uint8_t *)queue_base;
-    cudaError_t e = launch_tilize_direct_policy(job, pt, 1, mant, es, is_bfp_a(dst_df) ? 1 : 0, 0, ctx->sm_count, (cudaStream_t)stream);
+    cudaError_t e = launch_tilize_direct_policy(job, pt, 1, mant, es, half_side(src_df, dst_df), 0, ctx->sm_count, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(e, "tilize launch failed");
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return BUDA_SUCCESS;
@@ -1047,9 +1057,9 @@ int buda_queue_read_stacked(const void *queue_base, int src_df, int with_header,
     pt.src[0] = (const uint8_t *)queue_base;
     pt.dst[0] = (uint8_t *)dst;
     int path, vec_ok;
-    pick_path(job, pt, 1, es, path, vec_ok);
+    pick_path(job, pt, 1, es, path, vec_ok, mant);
     if (((job.stride_z | job.stride_z_mid | job.stride_z_out) & 15u) != 0) path = 1, vec_ok = 0;
-    return launch_uniform(1, ctx, job, pt, 1, mant, es, is_bfp_a(src_df) ? 1 : 0, path, vec_ok, (cudaStream_t)stream);
+    return launch_uniform(1, ctx, job, pt, 1, mant, es, half_side(dst_df, src_df), path, vec_ok, (cudaStream_t)stream);
 }
 
 int buda_tilize_pack_jobs(int n, const buda_tensor_job *jobs_host, int src_df, int dst_df, int with_header, void *stream)

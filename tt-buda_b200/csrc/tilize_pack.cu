@@ -489,8 +489,15 @@ __device__ __forceinline__ uint32_t fetch_view_elem(const TileJob &j, const uint
 template <int M, int ES, bool AF, bool G>
 __device__ __forceinline__ void direct_encode_store(uint32_t (&x)[4], uint32_t blk, uint8_t *r, int lane, const BfpPolicy &pol)
 {
-    if (M > 0) {
-        constexpr int MM = M > 0 ? M : 7;
+    if constexpr (M == kLf8) {
+        // element-wise 1-5-2 float: no exponent section, one byte per element; AF marks a binary16 source
+        uint32_t c[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            c[i] = (ES == 2 && AF) ? lf8_encode_half_bits(x[i]) : lf8_encode_float_bits(ES == 2 ? (x[i] << 16) : x[i]);
+        reinterpret_cast<uint32_t *>(r + blk * 16u)[lane & 3] = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
+    } else if (M > 0) {
+        constexpr int MM = (M > 0 && M < kLf8) ? M : 7;
         if (ES == 2) {
 #pragma unroll
             for (int i = 0; i < 4; i++) x[i] = AF ? half_bits_to_float_bits(x[i]) : (x[i] << 16);
@@ -671,6 +678,8 @@ static cudaError_t launch_direct(const TileJob &job, const PtrTable &ptrs, int b
 #define BUDA_FOR_EACH_PACK_KIND(X) \
     X(7, 4, false) X(3, 4, false) X(1, 4, false) X(7, 2, false) X(3, 2, false) X(1, 2, false) \
     X(7, 2, true) X(3, 2, true) X(1, 2, true) X(0, 4, false) X(0, 2, false) X(0, 1, false)
+// conversions only the direct kernel performs (Lf8 from binary32, bfloat16 and binary16)
+#define BUDA_FOR_EACH_DIRECT_ONLY_PACK_KIND(X) X(kLf8, 4, false) X(kLf8, 2, false) X(kLf8, 2, true)
 
 // mant_bits 7/3/1 = Bfp pack, 0 = plain relayout; es = source element bytes; a_format: 5-bit shared
 // exponent with a binary16 source.  path: 0 = staged (needs 16-byte aligned rows), 1 = direct.
@@ -683,6 +692,11 @@ cudaError_t launch_tilize(const TileJob &job, const PtrTable &ptrs, int batch, i
         return path == 0 ? launch_staged<MM, EE, AA, false>(job, ptrs, sm_count, stream, status)          \
                          : launch_direct<MM, EE, AA, false>(job, ptrs, batch, vec_ok, sm_count, stream);
     BUDA_FOR_EACH_PACK_KIND(BUDA_DISPATCH)
+#undef BUDA_DISPATCH
+#define BUDA_DISPATCH(MM, EE, AA) \
+    if (mant_bits == MM && es == EE && (a_format != 0) == AA && path != 0) \
+        return launch_direct<MM, EE, AA, false>(job, ptrs, batch, vec_ok, sm_count, stream);
+    BUDA_FOR_EACH_DIRECT_ONLY_PACK_KIND(BUDA_DISPATCH)
 #undef BUDA_DISPATCH
     return cudaErrorInvalidValue;
 }
@@ -706,6 +720,7 @@ cudaError_t launch_tilize_direct_policy(const TileJob &job, const PtrTable &ptrs
 #define BUDA_DISPATCH(MM, EE, AA) \
     if (mant_bits == MM && es == EE && (a_format != 0) == AA) return launch_direct<MM, EE, AA, true>(job, ptrs, batch, vec_ok, sm_count, stream);
     BUDA_FOR_EACH_PACK_KIND(BUDA_DISPATCH)
+    BUDA_FOR_EACH_DIRECT_ONLY_PACK_KIND(BUDA_DISPATCH)
 #undef BUDA_DISPATCH
     return cudaErrorInvalidValue;
 }

@@ -373,7 +373,7 @@ unpack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant_
         uint8_t *tile_dst = ptrs.dst[b] + (uint64_t)w * job.stride_w + rm_z_offset(job, z) +
                             (uint64_t)rt * job.tile_h * job.stride_r + ((uint64_t)ct * 32u + (lane & 3) * 4u) * ES;
         const uint8_t *r = ptrs.src[b] + tile_record_offset(job, w, z, rt, ct) + hdr;
-        constexpr int MM = M > 0 ? M : 7;
+        constexpr int MM = (M > 0 && M < kLf8) ? M : 7;
         constexpr int kRaw = (M == 0 && ES == 4) ? 4 : (M == 0 && ES == 2) ? 2 : 1;
         uint32_t raw[8][kRaw];
         uint32_t ex[8];
@@ -387,7 +387,9 @@ unpack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < kRaw; i++) raw[hf][i] = 0;
             if (tr >= job.tile_h) continue;                       // tiny tiles: only tile_h rows of a record belong to the tensor
-            if (M > 0) {
+            if (M == kLf8) {
+                raw[hf][0] = reinterpret_cast<const uint32_t *>(r + blk * 16u)[lane & 3];   // four 1-5-2 floats, no exponent section
+            } else if (M > 0) {
                 ex[hf] = r[(G && job.pol.exp_be) ? (blk ^ 3u) : blk];
                 const uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
                 int part = lane & 3;
@@ -422,7 +424,14 @@ unpack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant_
             if (tr >= job.tile_h) continue;
             uint8_t *p = tile_dst + (uint64_t)tr * job.stride_r + (face & 1u) * 16u * ES;
             uint32_t x[4];
-            if (M > 0) {
+            if (M == kLf8) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t c = (raw[hf][0] >> (8 * i)) & 0xffu;
+                    // exact in every destination: binary16 holds the code as its upper byte, bfloat16 is the upper half of the binary32
+                    x[i] = (ES == 2 && AF) ? (c << 8) : (ES == 2 ? lf8_decode_float_bits(c) >> 16 : lf8_decode_float_bits(c));
+                }
+            } else if (M > 0) {
                 const uint32_t E = ex[hf];
                 const uint32_t packed = raw[hf][0];
                 float post = 1.0f;
@@ -539,6 +548,8 @@ static cudaError_t launch_udirect(const TileJob &job, const PtrTable &ptrs, int 
     X(7, 4, false) X(3, 4, false) X(1, 4, false) X(7, 2, false) X(3, 2, false) X(1, 2, false) \
     X(7, 4, true) X(3, 4, true) X(1, 4, true) X(7, 2, true) X(3, 2, true) X(1, 2, true)       \
     X(0, 4, false) X(0, 2, false) X(0, 1, false)
+// conversions only the direct kernel performs (Lf8 to binary32, bfloat16 and binary16)
+#define BUDA_FOR_EACH_DIRECT_ONLY_UNPACK_KIND(X) X(kLf8, 4, false) X(kLf8, 2, false) X(kLf8, 2, true)
 
 // mant_bits 7/3/1 = Bfp decode, 0 = plain relayout; es = destination element bytes; a_format: 5-bit
 // shared exponent (destination binary16 when es == 2).  Plain flavour.
@@ -550,6 +561,11 @@ cudaError_t launch_untilize(const TileJob &job, const PtrTable &ptrs, int batch,
         return path == 0 ? launch_ustaged<MM, EE, AA, false>(job, ptrs, sm_count, stream, status)          \
                          : launch_udirect<MM, EE, AA, false>(job, ptrs, batch, vec_ok, sm_count, stream);
     BUDA_FOR_EACH_UNPACK_KIND(BUDA_DISPATCH)
+#undef BUDA_DISPATCH
+#define BUDA_DISPATCH(MM, EE, AA) \
+    if (mant_bits == MM && es == EE && (a_format != 0) == AA && path != 0) \
+        return launch_udirect<MM, EE, AA, false>(job, ptrs, batch, vec_ok, sm_count, stream);
+    BUDA_FOR_EACH_DIRECT_ONLY_UNPACK_KIND(BUDA_DISPATCH)
 #undef BUDA_DISPATCH
     return cudaErrorInvalidValue;
 }
@@ -572,6 +588,7 @@ cudaError_t launch_untilize_direct_policy(const TileJob &job, const PtrTable &pt
 #define BUDA_DISPATCH(MM, EE, AA) \
     if (mant_bits == MM && es == EE && (a_format != 0) == AA) return launch_udirect<MM, EE, AA, true>(job, ptrs, batch, vec_ok, sm_count, stream);
     BUDA_FOR_EACH_UNPACK_KIND(BUDA_DISPATCH)
+    BUDA_FOR_EACH_DIRECT_ONLY_UNPACK_KIND(BUDA_DISPATCH)
 #undef BUDA_DISPATCH
     return cudaErrorInvalidValue;
 }

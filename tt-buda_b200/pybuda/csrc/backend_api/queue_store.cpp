@@ -617,6 +617,11 @@ DEVICE_STATUS_CODE get_output(const tt_dram_io_desc &q, tt_PytorchTensorDesc &ou
         if (fmt != DataFormat::Float32 && fmt != DataFormat::Float16_b)
             fmt = default_output_format(q.bufq_target_format);
     }
+    else if (q.bufq_target_format == DataFormat::Lf8 &&
+             (fmt == DataFormat::Float32 || fmt == DataFormat::Float16_b || fmt == DataFormat::Float16))
+    {
+        // an Lf8 queue decodes to the float the caller names; with no request its bytes come back as they are
+    }
     else
     {
         fmt = q.bufq_target_format;
