@@ -596,7 +596,18 @@ def main():
             wi = cuda_ops.tilize_pack(torch.randint(-128, 128, (1, 1, K, N), device=dev, dtype=torch.int8), cuda_ops.DF.Int8)
             sci = torch.rand(N, device=dev) * 2e-5
             r = timed(lambda: cuda_ops.i8_matmul(ai, wi, N, scale=sci, zero_point=0.0, out="int8"), 0, reps=5)
-            extras["i8_gemm_requant_8192x4096x16384"] = {"TOP/s": round(2.0 * M * N * K / (r["ms"] * 1e-3) / 1e12, 1), "ms": r["ms"]}
+            i8 = {"TOP/s": round(2.0 * M * N * K / (r["ms"] * 1e-3) / 1e12, 1), "ms": r["ms"]}
+            try:
+                # the denominator: the library's int8 matmul of the same size on this GPU, now (int32 out, no requantisation)
+                bi = torch.randint(-128, 128, (K, N), device=dev, dtype=torch.int8)
+                rl = timed(lambda: torch._int_mm(ai, bi), 0, reps=5)
+                i8["library_int8_matmul_TOP/s"] = round(2.0 * M * N * K / (rl["ms"] * 1e-3) / 1e12, 1)
+                i8["frac_of_library_int8_matmul"] = round(rl["ms"] / r["ms"], 3)
+                del bi
+            except Exception as exc:
+                i8["library_int8_matmul_TOP/s"] = None
+                i8["library_note"] = str(exc)[:120]
+            extras["i8_gemm_requant_8192x4096x16384"] = i8
             del ai, wi
         except Exception as exc:
             extras["bfp8b_gemm_8192x4096x16384"] = {"error": str(exc)}
