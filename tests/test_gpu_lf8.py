@@ -146,8 +146,8 @@ def test_lf8_queue_through_the_backend_api(oracle):
     from pybuda import tensor as T
     B, DF = C.backend_api, C.DataFormat
     try:
-        x = _values((2, 1, 64, 96), 31, torch.float32)
-        q = B.DramIODesc.for_tensor("lf8_q", [2, 1, 64, 96], DF.Lf8)
+        x = _values((1, 2, 64, 96), 31, torch.float32)
+        q = B.DramIODesc.for_tensor("lf8_q", [1, 2, 64, 96], DF.Lf8)
         assert B.push_input(q, T.pytorch_tensor_to_tensor_desc(x), True, 1, -1) == B.BackendStatusCode.Success, B.last_error()
         out = B.PytorchTensorDesc()
         out.format = DF.Float32

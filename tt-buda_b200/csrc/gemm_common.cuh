@@ -29,6 +29,21 @@ __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *t
         : "memory");
 }
 
+// One tile of shared memory (laid out as the tensor map's box, 128-byte swizzle) to global memory, this device's or a
+// peer's; completion is tracked by the issuing thread's bulk group.  x * element size is a multiple of 16 bytes at every
+// call site, and no coordinate is negative.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *tmap, const void *smem_src, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(reinterpret_cast<uint64_t>(tmap)),
+                 "r"(x), "r"(y), "r"(smem_u32(smem_src))
+                 : "memory");
+}
+
+// Tensor maps of the output matrix on every destination (this device first, then peers)
+struct alignas(64) OutMaps {
+    CUtensorMap m[kMaxDst];
+};
+
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
 {
     asm volatile(
@@ -203,6 +218,7 @@ struct Params {
     int64_t M, N, K, ldc;
     uint32_t m_tiles, n_tiles, k_blocks, Nt;
     uint32_t raster_m;        // pair kernel: output tiles are walked in groups of this many tile rows (see tile_coords)
+    int tma_epilogue;         // pair kernel, Bfp8 kind: output tiles leave through shared memory and bulk tensor stores
     unsigned int *status;
     // int8 kind only: what the epilogue does with the int32 accumulators
     int out_mode;             // BUDA_I8_OUT_*
@@ -222,6 +238,32 @@ __device__ __forceinline__ void tile_coords(const Params &p, uint32_t t, uint32_
     const uint32_t rows = min(p.raster_m, p.m_tiles - m0);      // the last group may be shorter
     n_blk = within / rows;
     m_blk = m0 + (within - n_blk * rows);
+}
+
+// Requantisation of 32 consecutive columns of one row (first column `col`) to int8, four values per word.
+__device__ __forceinline__ void requant_row32(const uint32_t (&v)[32], const Params &p, int col, uint32_t (&packed)[8])
+{
+    const bool per_col = p.scale_len != 1;
+    const float s0 = __ldg(p.scale);
+    const float4 *scv = reinterpret_cast<const float4 *>(p.scale + (per_col ? col : 0));
+    // clamp, then round: the bounds are integers and rounding is monotone, so this equals the golden
+    // round-then-clamp; after the clamp |c| <= 128, where adding 1.5 * 2^23 rounds half to even and leaves the
+    // two's-complement result in the low byte of the sum's bits -- no round or float->int conversion instruction
+    // (those run at a quarter of the rate and were the epilogue's bottleneck: 0.124 ms of a 0.468 ms launch).
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+        const float4 sc = per_col ? __ldg(scv + q) : make_float4(s0, s0, s0, s0);
+        const float s4[4] = {sc.x, sc.y, sc.z, sc.w};
+        uint32_t b4[4];
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            const float f = __fadd_rn(__fmul_rn(__int2float_rn((int)v[4 * q + b]), s4[b]), p.zero_point);
+            float c = fminf(fmaxf(f, p.lo), p.hi);
+            c = (f != f) ? 0.0f : c;                      // NaN (e.g. 0 * inf) becomes 0, as in the stand-alone quantise kernels
+            b4[b] = __float_as_uint(__fadd_rn(c, 12582912.0f));
+        }
+        packed[q] = __byte_perm(__byte_perm(b4[0], b4[1], 0x0040), __byte_perm(b4[2], b4[3], 0x0040), 0x5410);
+    }
 }
 
 // Epilogue of the int8 matmul for 32 consecutive columns of one row (first column `col`): the int32
@@ -255,25 +297,8 @@ __device__ __forceinline__ void store_row32_i8(const uint32_t (&v)[32], const Pa
         }
         return;
     }
-    // clamp, then round: the bounds are integers and rounding is monotone, so this equals the golden
-    // round-then-clamp; after the clamp |c| <= 128, where adding 1.5 * 2^23 rounds half to even and leaves the
-    // two's-complement result in the low byte of the sum's bits -- no round or float->int conversion instruction
-    // (those run at a quarter of the rate and were the epilogue's bottleneck: 0.124 ms of a 0.468 ms launch).
     uint32_t packed[8];
-#pragma unroll
-    for (int q = 0; q < 8; q++) {
-        const float4 sc = per_col ? __ldg(scv + q) : make_float4(s0, s0, s0, s0);
-        const float s4[4] = {sc.x, sc.y, sc.z, sc.w};
-        uint32_t b4[4];
-#pragma unroll
-        for (int b = 0; b < 4; b++) {
-            const float f = __fadd_rn(__fmul_rn(__int2float_rn((int)v[4 * q + b]), s4[b]), p.zero_point);
-            float c = fminf(fmaxf(f, p.lo), p.hi);
-            c = (f != f) ? 0.0f : c;                      // NaN (e.g. 0 * inf) becomes 0, as in the stand-alone quantise kernels
-            b4[b] = __float_as_uint(__fadd_rn(c, 12582912.0f));
-        }
-        packed[q] = __byte_perm(__byte_perm(b4[0], b4[1], 0x0040), __byte_perm(b4[2], b4[3], 0x0040), 0x5410);
-    }
+    requant_row32(v, p, col, packed);
     uint8_t *out = reinterpret_cast<uint8_t *>(p.C[0]) + elem_offset;
     reinterpret_cast<uint4 *>(out)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
     reinterpret_cast<uint4 *>(out)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);

@@ -59,6 +59,7 @@ constexpr int kEpiWarps = 8;        // two per tensor-memory lane quadrant: each
 constexpr int kProducerWarp = kEpiWarps, kMmaWarp = kEpiWarps + 1, kFirstDecodeWarp = kEpiWarps + 2;
 constexpr int kThreads = 32 * (kEpiWarps + 1 + 1 + kDecodeWarps);
 constexpr int kTmemCols = 512;
+constexpr int kEpiStageBytes = 32 * 128;   // what one epilogue warp hands to one bulk tensor store
 
 
 // Shared-memory plan (the same for a launch that also writes peers' memory, kScatter).
@@ -67,8 +68,8 @@ struct Layout {
     static constexpr int kAStages = 4;                  // activation ring (per CTA: two 128-row boxes per stage)
     static constexpr int kSmemA = 0;
     static constexpr int kSmemB = kSmemA + kAStages * kABytes;
-    static constexpr int kSmemEpi = kSmemB + kBStages * kBBytes;
-    static constexpr int kSmemBar = kSmemEpi;
+    static constexpr int kSmemEpi = kSmemB + kBStages * kBBytes;      // per epilogue warp: 32 rows x 64 bfloat16 columns, 128-byte swizzle
+    static constexpr int kSmemBar = kSmemEpi + kEpiWarps * kEpiStageBytes;
     static constexpr int kNumBars = 3 * kAStages + 2 * kBStages + 2;
     static constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 16 + 1024;
 };
@@ -139,7 +140,7 @@ __device__ __forceinline__ void multimem_st_16(void *mc_addr, const uint4 v)
 
 template <int Kind, bool kScatter>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ Params p)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ Params p, const __grid_constant__ OutMaps out_maps)
 {
     using KT = KindTraits<Kind>;
     using L = Layout<kScatter>;
@@ -395,6 +396,92 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const bool got = mbar_wait_bounded(acc_full, tile_iter & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT);
             if (!__all_sync(0xffffffffu, got)) break;  // the whole warp leaves together
             tc_fence_after();
+            if (Kind == kKindBfp8 && p.tma_epilogue) {
+                // The warp's 32 rows x 64 columns go to shared memory as bfloat16 (lane = row; the 16-byte chunks of a row
+                // are permuted by the row number so that the lanes' stores do not meet in a bank -- the 128-byte swizzle
+                // of the tensor map undoes it), and one elected lane hands the piece to the copy engine: one bulk tensor
+                // store per destination, this device's matrix and every peer's alike.  The warp neither issues 32
+                // separate lines per store instruction nor waits for NVLink; rows past M are clipped by the tensor map.
+                uint8_t *stage = smem + L::kSmemEpi + warp * kEpiStageBytes;
+#pragma unroll 1
+                for (int h = 0; h < 2; h++) {
+                    const int y = (int)(m_blk * kPairM) + h * 256 + (int)rank * 128 + quad * 32;
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(h * kBN + col_half * (kBN / 2));
+#pragma unroll 1
+                    for (int c = 0; c < kBN / 2 / 64; c++) {
+                        uint32_t v0[32], v1[32];
+                        tmem_ld32_issue(taddr + c * 64, v0);
+                        tmem_ld32_issue(taddr + c * 64 + 32, v1);
+                        tmem_ld_wait();
+                        uint4 o[8];
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            o[q].x = pack_bf16x2(__uint_as_float(v0[8 * q]), __uint_as_float(v0[8 * q + 1]));
+                            o[q].y = pack_bf16x2(__uint_as_float(v0[8 * q + 2]), __uint_as_float(v0[8 * q + 3]));
+                            o[q].z = pack_bf16x2(__uint_as_float(v0[8 * q + 4]), __uint_as_float(v0[8 * q + 5]));
+                            o[q].w = pack_bf16x2(__uint_as_float(v0[8 * q + 6]), __uint_as_float(v0[8 * q + 7]));
+                            o[q + 4].x = pack_bf16x2(__uint_as_float(v1[8 * q]), __uint_as_float(v1[8 * q + 1]));
+                            o[q + 4].y = pack_bf16x2(__uint_as_float(v1[8 * q + 2]), __uint_as_float(v1[8 * q + 3]));
+                            o[q + 4].z = pack_bf16x2(__uint_as_float(v1[8 * q + 4]), __uint_as_float(v1[8 * q + 5]));
+                            o[q + 4].w = pack_bf16x2(__uint_as_float(v1[8 * q + 6]), __uint_as_float(v1[8 * q + 7]));
+                        }
+                        if (lane == 0) bulk_wait_read_all();   // the previous piece has been read out of the stage
+                        __syncwarp();
+                        uint8_t *rowp = stage + lane * 128;
+#pragma unroll
+                        for (int q = 0; q < 8; q++) *reinterpret_cast<uint4 *>(rowp + ((q ^ (lane & 7)) << 4)) = o[q];
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            const int x = (int)(n_blk * kBN) + col_half * (kBN / 2) + c * 64;
+                            for (int d = 0; d < p.n_dst; d++) tma_store_2d(&out_maps.m[d], stage, x, y);
+                            bulk_commit();
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(acc_empty), 0));
+                continue;
+            }
+            if (Kind == kKindI8 && p.tma_epilogue) {
+                // The same for the requantised int8 output: 32 rows x 64 bytes per piece, 64-byte swizzle.
+                uint8_t *stage = smem + L::kSmemEpi + warp * kEpiStageBytes;
+#pragma unroll 1
+                for (int h = 0; h < 2; h++) {
+                    const int y = (int)(m_blk * kPairM) + h * 256 + (int)rank * 128 + quad * 32;
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(h * kBN + col_half * (kBN / 2));
+#pragma unroll 1
+                    for (int c = 0; c < kBN / 2 / 64; c++) {
+                        uint32_t v0[32], v1[32];
+                        tmem_ld32_issue(taddr + c * 64, v0);
+                        tmem_ld32_issue(taddr + c * 64 + 32, v1);
+                        tmem_ld_wait();
+                        const int x = (int)(n_blk * kBN) + col_half * (kBN / 2) + c * 64;
+                        uint32_t w0[8], w1[8];
+                        requant_row32(v0, p, x, w0);
+                        requant_row32(v1, p, x + 32, w1);
+                        if (lane == 0) bulk_wait_read_all();   // the previous piece has been read out of the stage
+                        __syncwarp();
+                        uint8_t *rowp = stage + lane * 64;
+                        const int sw = (lane >> 1) & 3;
+                        *reinterpret_cast<uint4 *>(rowp + ((0 ^ sw) << 4)) = make_uint4(w0[0], w0[1], w0[2], w0[3]);
+                        *reinterpret_cast<uint4 *>(rowp + ((1 ^ sw) << 4)) = make_uint4(w0[4], w0[5], w0[6], w0[7]);
+                        *reinterpret_cast<uint4 *>(rowp + ((2 ^ sw) << 4)) = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+                        *reinterpret_cast<uint4 *>(rowp + ((3 ^ sw) << 4)) = make_uint4(w1[4], w1[5], w1[6], w1[7]);
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&out_maps.m[0], stage, x, y);
+                            bulk_commit();
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(acc_empty), 0));
+                continue;
+            }
 #pragma unroll 1
             for (int h = 0; h < 2; h++) {
                 const int64_t row = (int64_t)m_blk * kPairM + h * 256 + rank * 128 + quad * 32 + lane;
@@ -452,6 +539,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
     }
 
+    // the bulk tensor stores of the epilogue are complete before the kernel is (only the lanes that issued any hold a group)
+    if (warp < kEpiWarps && lane == 0) bulk_wait_all();
     // every path ends here: neither CTA leaves while its partner may still touch its shared memory or barriers
     tc_fence_before();
     cluster_sync_all();
@@ -462,10 +551,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
 }  // namespace gemm_pair
 
+int gemm_kernel_choice(int which);
+
 namespace {
 
 template <int Kind, bool kScatter>
-cudaError_t launch_pair(const CUtensorMap &tmap, const gemm::Params &p_in, int sm_count, cudaStream_t stream)
+cudaError_t launch_pair(const CUtensorMap &tmap, const gemm::Params &p_in, const gemm::OutMaps &out_maps, int sm_count, cudaStream_t stream)
 {
     using namespace gemm_pair;
     constexpr int kSmemBytes = Layout<kScatter>::kSmemBytes;
@@ -507,19 +598,28 @@ cudaError_t launch_pair(const CUtensorMap &tmap, const gemm::Params &p_in, int s
     p.n_tiles = (uint32_t)(p.N / kBN);
     p.k_blocks = (uint32_t)(p.K / KindTraits<Kind>::kBK);
     p.Nt = (uint32_t)(p.N / 32);
-    uint32_t pairs = p.m_tiles * p.n_tiles;
+    const uint32_t tiles = p.m_tiles * p.n_tiles;
+    uint32_t pairs = tiles;
     if (pairs > (uint32_t)resident) pairs = (uint32_t)resident;
-    gemm_pair_kernel<Kind, kScatter><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap, p);
+    if constexpr (kScatter) {
+        // A launch that also feeds the peers is bound by what each pair sends after each of its tiles, so every pair
+        // should send the same amount: the fewest pairs that still finish in the same number of rounds (256 tiles on
+        // 74 pairs are 4 rounds with 34 pairs sending in the last one; on 64 pairs they are 4 rounds of 64).
+        const uint32_t rounds = (tiles + pairs - 1u) / pairs;
+        pairs = (tiles + rounds - 1u) / rounds;
+    }
+    gemm_pair_kernel<Kind, kScatter><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tmap, p, out_maps);
     return cudaGetLastError();
 }
 
 }  // namespace
 
 // Launch of the CTA-pair Bfp8 kernel.  Same contract as the single-CTA launch; the caller has validated the shapes.
-cudaError_t launch_bfp8b_gemm_pair(const CUtensorMap &tmap, const gemm::Params &p, int sm_count, cudaStream_t stream)
+cudaError_t launch_bfp8b_gemm_pair(const CUtensorMap &tmap, const gemm::Params &p, const gemm::OutMaps &out_maps, int sm_count,
+                                   cudaStream_t stream)
 {
-    if (p.n_dst > 1 || p.C_mc) return launch_pair<gemm_pair::kKindBfp8, true>(tmap, p, sm_count, stream);
-    return launch_pair<gemm_pair::kKindBfp8, false>(tmap, p, sm_count, stream);
+    if (p.n_dst > 1 || p.C_mc) return launch_pair<gemm_pair::kKindBfp8, true>(tmap, p, out_maps, sm_count, stream);
+    return launch_pair<gemm_pair::kKindBfp8, false>(tmap, p, out_maps, sm_count, stream);
 }
 
 // int8 x int8 -> int32 matmul with the requantise / dequantise epilogue (see the header of this file).
@@ -578,7 +678,21 @@ cudaError_t launch_i8_gemm(const void *A, int64_t M, int64_t K, int64_t lda, con
     p.zero_point = zero_point;
     p.lo = -128.0f;
     p.hi = 127.0f;
-    return launch_pair<gemm_pair::kKindI8, false>(tmap, p, sm_count, stream);
+    // the requantised int8 output leaves as bulk tensor stores (see the Bfp8 kind); 4-byte outputs store from registers
+    OutMaps out_maps = {};
+    p.tma_epilogue = (out_mode == BUDA_I8_OUT_REQUANT_I8 && gemm_kernel_choice(-1) != 3) ? 1 : 0;
+    if (p.tma_epilogue) {
+        const cuuint64_t cdims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+        const cuuint64_t cstrides[1] = {(cuuint64_t)ldc};
+        const cuuint32_t cbox[2] = {64, 32};
+        cr = encode(&out_maps.m[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, C, cdims, cstrides, cbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) {
+            snprintf(err, err_len, "cuTensorMapEncodeTiled failed for the output with code %d", (int)cr);
+            return cudaErrorInvalidValue;
+        }
+    }
+    return launch_pair<gemm_pair::kKindI8, false>(tmap, p, out_maps, sm_count, stream);
 }
 
 }  // namespace buda
