@@ -26,8 +26,9 @@ int buda_unpack_untilize_batch_path(int n, const void *const *srcs_host, int src
                                     int path);
 
 /* Which tensor-core kernel buda_bfp8b_gemm* launches: 0 = automatic (CTA-pair kernel for M > 256, single-CTA
- * kernel otherwise), 1 = single-CTA, 2 = CTA pair.  Process-wide; a negative value only reads.  Returns the
- * previous setting.  The two kernels give identical bits; the tests check that. */
+ * kernel otherwise), 1 = single-CTA, 2 = CTA pair, 3 = CTA pair with the epilogue that stores from registers
+ * instead of through bulk tensor stores (also honoured by buda_i8_gemm).  Process-wide; a negative value only
+ * reads.  Returns the previous setting.  All of them give identical bits; the tests check that. */
 int buda_gemm_select_kernel(int which);
 
 /* Self-test of the failure path every kernel of the library shares: launches one CTA that waits, with the

@@ -56,9 +56,9 @@ def test_one_hot_rows_copy_decoded_weights_exactly(ops, oracle):
                     f"got {c[tuple(bad[0])].item()} want {want[tuple(bad[0])].item()}")
 
 
-@pytest.fixture(params=["single", "pair"])
+@pytest.fixture(params=["single", "pair", "pair_register_epilogue"])
 def kernel(request, ops):
-    """Both tensor-core kernels (one CTA per tile; a CTA pair per tile) run every shape."""
+    """Both tensor-core kernels (one CTA per tile; a CTA pair per tile, with either epilogue) run every shape."""
     prev = ops.select_gemm_kernel(request.param)
     yield request.param
     ops.select_gemm_kernel(prev)
@@ -86,9 +86,18 @@ def test_pair_and_single_kernels_agree_bit_for_bit(ops, oracle):
         c1 = ops.bfp8b_matmul(a, img, N)
         ops.select_gemm_kernel("pair")
         c2 = ops.bfp8b_matmul(a, img, N)
+        ops.select_gemm_kernel("pair_register_epilogue")
+        c3 = ops.bfp8b_matmul(a, img, N)
+        # rows past M are clipped by the bulk tensor store, and a wider output keeps its other columns
+        wide = torch.full((M - 37 + 5, N + 64), 7.0, dtype=torch.bfloat16, device="cuda")
+        ops.select_gemm_kernel("pair")
+        ops.bfp8b_matmul(a[: M - 37], img, N, out=wide[: M - 37, :N])
     finally:
         ops.select_gemm_kernel(prev)
     assert torch.equal(c1, c2)    # same k order, same binary32 accumulation
+    assert torch.equal(c2, c3)
+    assert torch.equal(wide[: M - 37, :N], c2[: M - 37])
+    assert torch.all(wide[M - 37:] == 7.0) and torch.all(wide[:, N:] == 7.0)
     rc, st = ops._cabi.device_status()
     assert rc == 0 and st == 0
 
@@ -229,7 +238,9 @@ def test_i8_matmul_accumulators_exact(ops, oracle, M, K, N):
 
 
 @pytest.mark.parametrize("per_column", [False, True])
-def test_i8_matmul_requant_and_dequant_epilogues(ops, oracle, per_column):
+def test_i8_matmul_requant_and_dequant_epilogues(ops, oracle, per_column, kernel):
+    if kernel == "single":
+        pytest.skip("the int8 matmul has the pair kernel only")
     M, K, N = 640, 256, 512
     a, w, img = _i8_operands(ops, oracle, M, K, N, seed=77)
     g = torch.Generator().manual_seed(78)

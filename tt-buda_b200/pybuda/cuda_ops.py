@@ -233,8 +233,9 @@ def i8_matmul(a, w_image, n, scale=None, zero_point=0.0, out="int32"):
 
 
 def select_gemm_kernel(which):
-    """'auto' (default), 'single' or 'pair': which tensor-core kernel the matmul launches.  Returns the previous choice."""
-    names = ["auto", "single", "pair"]
+    """'auto' (default), 'single', 'pair' or 'pair_register_epilogue': which tensor-core kernel the matmul launches.
+    Returns the previous choice."""
+    names = ["auto", "single", "pair", "pair_register_epilogue"]
     return names[_cabi.lib.buda_gemm_select_kernel(names.index(which))]
 
 
