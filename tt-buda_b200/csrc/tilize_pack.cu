@@ -135,7 +135,9 @@ template <> struct TableOf<true> { using type = GenTable; };
 
 // The general flavour is held to the register budget of the plain one (five CTAs of 288 threads per SM for the 8-bit
 // formats): what it spills sits on the policy-only paths.
-template <int M, int ES, bool AF, bool G>
+// P: the launch honours a non-default layout policy (general flavour only).  A job table under the default policy -- the
+// usual case: parameter sets, layers of a model -- runs the plain flavour's consumer code.
+template <int M, int ES, bool AF, bool G, bool P>
 __global__ void __launch_bounds__(kStagedThreads, (G && M == 7 && ES == 4) ? 5 : 0)
 pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ typename TableOf<G>::type ptrs, unsigned int *status)
 {
@@ -248,12 +250,12 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
     // A thread always meets the same face: the face column bc advances by the (even) number of consumer warps, so
     // bc % 2 stays warp % 2.  Its block's place in the record is therefore fixed for the whole launch.
     const int my_face = ((lane >> 4) << 1) | (warp & 1);
-    const int blk = (G ? (int)job.pol.face_pos[my_face] : my_face) * 16 + fr;
-    const int exp_idx = (G && job.pol.exp_be) ? (blk ^ 3) : blk;
+    const int blk = (P ? (int)job.pol.face_pos[my_face] : my_face) * 16 + fr;
+    const int exp_idx = (P && job.pol.exp_be) ? (blk ^ 3) : blk;
     // general flavour (all uniform over the launch): only a raised exponent needs the policy encoder; truncation is the
     // plain encoder with another rounding mode, a reversed datum order one permute per word afterwards
-    const bool plain_codec = !G || !job.pol.bump;
-    const bool trunc = G && job.pol.trunc, datum_be = G && job.pol.datum_be;
+    const bool plain_codec = !P || !job.pol.bump;
+    const bool trunc = P && job.pol.trunc, datum_be = P && job.pol.datum_be;
     uint32_t it = 0;
     for (;; ++it) {
         const int s = it % S;
@@ -330,7 +332,7 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
             for (int c = tid; c < nchunks; c += kConsumerThreads) {
                 const int t = c / chunks_per_tile, k = c % chunks_per_tile;
                 const int r16 = (k / cpr) % 16, part = k % cpr;
-                const int f = G ? (int)job.pol.face_at[k / (16 * cpr)] : k / (16 * cpr);   // the face stored at this position
+                const int f = P ? (int)job.pol.face_at[k / (16 * cpr)] : k / (16 * cpr);   // the face stored at this position
                 const int row = (f >> 1) * 16 + r16;
                 const uint4 v = *reinterpret_cast<const uint4 *>(stage + row * Cfg::pitch + t * 32 * ES +
                                                                  (f & 1) * 16 * ES + part * 16);
@@ -620,7 +622,7 @@ pack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
 // ------------------------------------------------------------------------------------------------
 static DeviceWorkSlots g_pack_slots[64];   // per device: which work counter the next staged launch takes
 
-template <int M, int ES, bool AF, bool G>
+template <int M, int ES, bool AF, bool G, bool P = false>
 static cudaError_t launch_staged(const TileJob &job, const typename TableOf<G>::type &table, int sm_count, cudaStream_t stream,
                                  unsigned int *status)
 {
@@ -631,11 +633,11 @@ static cudaError_t launch_staged(const TileJob &job, const typename TableOf<G>::
     dev &= 63;
     int per_sm = per_sm_cache[dev].load(std::memory_order_acquire);
     if (per_sm == 0) {
-        cudaError_t e = cudaFuncSetAttribute(pack_staged_kernel<M, ES, AF, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(pack_staged_kernel<M, ES, AF, G, P>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Cfg::template smem_for<G>());
         if (e != cudaSuccess) return e;
         int n = 0;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, pack_staged_kernel<M, ES, AF, G>, kStagedThreads,
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, pack_staged_kernel<M, ES, AF, G, P>, kStagedThreads,
                                                           Cfg::template smem_for<G>());
         if (e != cudaSuccess) return e;
         per_sm = n < 1 ? 1 : (n > 5 ? 5 : n);
@@ -657,7 +659,7 @@ static cudaError_t launch_staged(const TileJob &job, const typename TableOf<G>::
     launch_job.work_slot = (uint32_t)slot;
     // (A programmatic dependent launch -- the next conversion's CTAs becoming resident and running their prologue while
     // this one drains -- was measured on back-to-back launches of the 64-tensor batch: 6.5 % slower, not kept.)
-    pack_staged_kernel<M, ES, AF, G><<<grid, kStagedThreads, Cfg::template smem_for<G>(), stream>>>(launch_job, launch_table, status);
+    pack_staged_kernel<M, ES, AF, G, P><<<grid, kStagedThreads, Cfg::template smem_for<G>(), stream>>>(launch_job, launch_table, status);
     const cudaError_t e = cudaGetLastError();
     work_slot_launched(g_pack_slots[dev], slot, stream, tracked);
     return e;
@@ -707,7 +709,9 @@ cudaError_t launch_tilize_table(const TileJob &job, const GenTable &table, int m
                                 cudaStream_t stream, unsigned int *status)
 {
 #define BUDA_DISPATCH(MM, EE, AA) \
-    if (mant_bits == MM && es == EE && (a_format != 0) == AA) return launch_staged<MM, EE, AA, true>(job, table, sm_count, stream, status);
+    if (mant_bits == MM && es == EE && (a_format != 0) == AA)                                                           \
+        return policy_is_default(job.pol) ? launch_staged<MM, EE, AA, true, false>(job, table, sm_count, stream, status) \
+                                          : launch_staged<MM, EE, AA, true, true>(job, table, sm_count, stream, status);
     BUDA_FOR_EACH_PACK_KIND(BUDA_DISPATCH)
 #undef BUDA_DISPATCH
     return cudaErrorInvalidValue;

@@ -129,7 +129,8 @@ static __device__ WorkCounter g_unpack_work[kWorkSlots];
 template <bool G> struct UTableOf { using type = PtrTable; };
 template <> struct UTableOf<true> { using type = GenTable; };
 
-template <int M, int ES, bool AF, bool G>
+// P: the launch honours a non-default layout policy (see the pack kernel)
+template <int M, int ES, bool AF, bool G, bool P>
 __global__ void __launch_bounds__(kUStagedThreads)
 unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ typename UTableOf<G>::type ptrs, unsigned int *status)
 {
@@ -264,8 +265,8 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
             if ((uint32_t)tile_in_box < m.ntiles) {
                 constexpr int MM = M > 0 ? M : 7;
                 const uint8_t *r = stage + tile_in_box * rec + hdr;
-                const int blk = (G ? (int)job.pol.face_pos[face] : face) * 16 + fr;
-                const uint32_t E = r[(G && job.pol.exp_be) ? (blk ^ 3) : blk];
+                const int blk = (P ? (int)job.pol.face_pos[face] : face) * 16 + fr;
+                const uint32_t E = r[(P && job.pol.exp_be) ? (blk ^ 3) : blk];
                 const uint8_t *q = r + 64 + blk * BfpTraits<MM>::bytes;
                 uint32_t d[BfpTraits<MM>::words];
                 if (MM == 7) {
@@ -277,7 +278,7 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
                 } else {
                     d[0] = *reinterpret_cast<const uint32_t *>(q);
                 }
-                if (G && job.pol.datum_be) {
+                if (P && job.pol.datum_be) {
 #pragma unroll
                     for (int w = 0; w < BfpTraits<MM>::words; w++) d[w] = reverse_datum_fields<MM>(d[w]);
                 }
@@ -313,7 +314,7 @@ unpack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant_
             for (int c = tid; c < nchunks; c += kUConsumerThreads) {
                 const int t = c / chunks_per_tile, k = c % chunks_per_tile;
                 const int r16 = (k / cpr) % 16, part = k % cpr;
-                const int f = G ? (int)job.pol.face_at[k / (16 * cpr)] : k / (16 * cpr);   // the face stored at this position
+                const int f = P ? (int)job.pol.face_at[k / (16 * cpr)] : k / (16 * cpr);   // the face stored at this position
                 const int row = (f >> 1) * 16 + r16;
                 const uint4 v = *reinterpret_cast<const uint4 *>(stage + t * rec + hdr + k * 16);
                 *reinterpret_cast<uint4 *>(ob + row * Cfg::pitch + t * 32 * ES + (f & 1) * 16 * ES + part * 16) = v;
@@ -489,7 +490,7 @@ unpack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant_
 // ------------------------------------------------------------------------------------------------
 static DeviceWorkSlots g_unpack_slots[64];   // per device: which work counter the next staged launch takes
 
-template <int M, int ES, bool AF, bool G>
+template <int M, int ES, bool AF, bool G, bool P = false>
 static cudaError_t launch_ustaged(const TileJob &job, const typename UTableOf<G>::type &table, int sm_count, cudaStream_t stream,
                                   unsigned int *status)
 {
@@ -500,11 +501,11 @@ static cudaError_t launch_ustaged(const TileJob &job, const typename UTableOf<G>
     dev &= 63;
     int per_sm = per_sm_cache[dev].load(std::memory_order_acquire);
     if (per_sm == 0) {
-        cudaError_t e = cudaFuncSetAttribute(unpack_staged_kernel<M, ES, AF, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(unpack_staged_kernel<M, ES, AF, G, P>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              Cfg::template smem_for<G>());
         if (e != cudaSuccess) return e;
         int n = 0;
-        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, unpack_staged_kernel<M, ES, AF, G>, kUStagedThreads,
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, unpack_staged_kernel<M, ES, AF, G, P>, kUStagedThreads,
                                                           Cfg::template smem_for<G>());
         if (e != cudaSuccess) return e;
         per_sm = n < 1 ? 1 : (n > 4 ? 4 : n);
@@ -526,7 +527,7 @@ static cudaError_t launch_ustaged(const TileJob &job, const typename UTableOf<G>
     launch_job.work_slot = (uint32_t)slot;
     // (A programmatic dependent launch -- the next conversion's CTAs becoming resident and running their prologue while
     // this one drains -- was measured on back-to-back launches of the 64-tensor batch: 6.5 % slower, not kept.)
-    unpack_staged_kernel<M, ES, AF, G><<<grid, kUStagedThreads, Cfg::template smem_for<G>(), stream>>>(launch_job, launch_table, status);
+    unpack_staged_kernel<M, ES, AF, G, P><<<grid, kUStagedThreads, Cfg::template smem_for<G>(), stream>>>(launch_job, launch_table, status);
     const cudaError_t e = cudaGetLastError();
     work_slot_launched(g_unpack_slots[dev], slot, stream, tracked);
     return e;
@@ -575,7 +576,9 @@ cudaError_t launch_untilize_table(const TileJob &job, const GenTable &table, int
                                   cudaStream_t stream, unsigned int *status)
 {
 #define BUDA_DISPATCH(MM, EE, AA) \
-    if (mant_bits == MM && es == EE && (a_format != 0) == AA) return launch_ustaged<MM, EE, AA, true>(job, table, sm_count, stream, status);
+    if (mant_bits == MM && es == EE && (a_format != 0) == AA)                                                            \
+        return policy_is_default(job.pol) ? launch_ustaged<MM, EE, AA, true, false>(job, table, sm_count, stream, status) \
+                                          : launch_ustaged<MM, EE, AA, true, true>(job, table, sm_count, stream, status);
     BUDA_FOR_EACH_UNPACK_KIND(BUDA_DISPATCH)
 #undef BUDA_DISPATCH
     return cudaErrorInvalidValue;
