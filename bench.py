@@ -137,19 +137,26 @@ class ClockSampler:
 _PROBE = None
 
 
-def stream_probe(torch, mix, schedule, elements=1 << 29, reps=10):
-    """GB/s of a bare streaming kernel with the conversion kernels' access shape and none of their arithmetic
-    (tt-buda_b200/csrc/bench/stream_probe.cu, built into libbuda_probe.so, which only this benchmark loads).
-    mix 0 = 4 bytes read per byte written, 1 = the reverse, 2 = reads only, 3 = writes only; schedule 0 = one block
-    per band, 1 = resident blocks on a fixed stride, 2 = resident blocks on a device counter."""
+def probe_lib():
     global _PROBE
     if _PROBE is None:
         _PROBE = ctypes.CDLL(os.path.join(ROOT, "tt-buda_b200", "lib", "libbuda_probe.so"))
         _PROBE.buda_probe_stream.restype = ctypes.c_int
         _PROBE.buda_probe_stream.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_uint64, ctypes.c_int,
                                              ctypes.POINTER(ctypes.c_float), ctypes.c_void_p]
+        _PROBE.buda_probe_peer_stores.restype = ctypes.c_int
+        _PROBE.buda_probe_peer_stores.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_uint32,
+                                                  ctypes.c_uint32, ctypes.c_uint64, ctypes.c_void_p]
+    return _PROBE
+
+
+def stream_probe(torch, mix, schedule, elements=1 << 29, reps=10):
+    """GB/s of a bare streaming kernel with the conversion kernels' access shape and none of their arithmetic
+    (tt-buda_b200/csrc/bench/stream_probe.cu, built into libbuda_probe.so, which only this benchmark loads).
+    mix 0 = 4 bytes read per byte written, 1 = the reverse, 2 = reads only, 3 = writes only; schedule 0 = one block
+    per band, 1 = resident blocks on a fixed stride, 2 = resident blocks on a device counter."""
     ms = ctypes.c_float(0.0)
-    rc = _PROBE.buda_probe_stream(int(mix), int(schedule), int(elements), int(reps), ctypes.byref(ms),
+    rc = probe_lib().buda_probe_stream(int(mix), int(schedule), int(elements), int(reps), ctypes.byref(ms),
                                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     if rc != 0:
         raise RuntimeError("stream probe failed")
@@ -560,6 +567,12 @@ def main():
                 extras[f"relayout_{tname}_untilize"] = timed(
                     lambda: cuda_ops.unpack_untilize_batch(ir, tdf, SHAPE, outs=xr), nu * ELEMS * 2 * tes)
                 del xr, ir
+            # Lf8 (one 1-5-2 float per element): conversions of the direct kernels, 5 bytes per element
+            il = cuda_ops.tilize_pack_batch(xs[:nu], cuda_ops.DF.Lf8)
+            extras["pack_lf8_from_fp32"] = timed(lambda: cuda_ops.tilize_pack_batch(xs[:nu], cuda_ops.DF.Lf8, outs=il), nu * ELEMS * 5)
+            yl = [torch.empty(SHAPE, dtype=torch.float32, device=dev) for _ in range(nu)]
+            extras["unpack_lf8_to_fp32"] = timed(lambda: cuda_ops.unpack_untilize_batch(il, cuda_ops.DF.Lf8, SHAPE, outs=yl), nu * ELEMS * 5)
+            del il, yl
             n3 = 32 * 1024 * 1024
             # config-3 tensors are about the size of L2: every call takes the next of four copies of its input, so no
             # call finds its input (or the previous call's output) still in the cache
@@ -733,6 +746,37 @@ def main():
             fused_out = op.enable_fused_scatter(M)
             route = op.exchange
             ms_fused = time_fused()
+            # what NVLink gives bare stores of the same shape: every rank copies its block of columns into the peers'
+            # matrices with a kernel that does nothing else (libbuda_probe.so), all ranks at once, timed the same way
+            ms_bare = None
+            try:
+                op.enable_fused_scatter(M, multicast=False)
+                probe = probe_lib()
+                ptrs = op.block_pointers
+                arr = (ctypes.c_void_p * (len(ptrs) - 1))(*[ctypes.c_void_p(p) for p in ptrs[1:]])
+                stream_h = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+                def bare():
+                    if probe.buda_probe_peer_stores(ctypes.c_void_p(ptrs[0]), arr, len(ptrs) - 1, M, (N // world) * 2, N * 2, stream_h):
+                        raise RuntimeError("peer-store probe refused its arguments")
+
+                for _ in range(2):
+                    bare()
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(5):
+                    bare()
+                dist.all_reduce(flag)
+                e1.record()
+                barrier()
+                ms_bare = max_over_ranks(e0.elapsed_time(e1) / 5)
+                fused_out = op.enable_fused_scatter(M)
+                op.fused(a)
+            except Exception as exc:  # report, never hide
+                extras["peer_store_probe_error"] = str(exc)[:200]
+                fused_out = op.enable_fused_scatter(M)
+                op.fused(a)
             # correctness on every rank, outside the timed loops: fused == all-gather variant == one-GPU product
             op(a, out=cfull, gather=True)
             w_img_full = cuda_ops.tilize_pack(w_full, cuda_ops.DF.Bfp8_b)
@@ -756,6 +800,9 @@ def main():
                 "ms_fused_peer_store_route": round(ms_peer, 4),
                 "ms_fused_multicast_route": round(ms_multicast, 4) if ms_multicast is not None else None,
                 "nvlink_store_gbs_per_gpu": round(link_bytes / (ms_fused * 1e-3) / 1e9, 1),
+                "bare_peer_stores_ms": round(ms_bare, 4) if ms_bare else None,
+                "bare_peer_stores_gbs_per_gpu": round(link_bytes / (ms_bare * 1e-3) / 1e9, 1) if ms_bare else None,
+                "fused_scatter_vs_matmul_plus_bare_stores": round(ms_fused / (ms_local + ms_bare), 3) if ms_bare else None,
                 "fused_scatter_floor_ms": round(t_floor * 1e3, 4), "fused_scatter_frac_of_floor": round(t_floor * 1e3 / ms_fused, 3),
                 "floor": "max(flops / measured bf16 burst peak, bytes leaving this GPU / 770 GB/s measured peer copy)",
                 "bands": 8}

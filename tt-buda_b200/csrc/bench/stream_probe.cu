@@ -146,7 +146,52 @@ cudaError_t run_stream_probe(int mix, int schedule, uint64_t elements, int reps,
     return e;
 }
 
+// A block of `rows` rows x row_bytes (a multiple of 512) read from src and stored to the same place in up to 7 other
+// matrices of the same pitch (peers' memory mapped into this process): the traffic of the column-parallel matmul's
+// exchange with none of its arithmetic.  A warp instruction covers 512 contiguous bytes of a row; nothing is read from a peer.
+struct PeerDsts {
+    uint8_t *p[7];
+    int n;
+};
+
+__global__ void __launch_bounds__(256)
+peer_store_probe_kernel(const uint8_t *__restrict__ src, PeerDsts dsts, uint32_t rows, uint32_t row_bytes, uint64_t pitch)
+{
+    const uint32_t pieces_per_row = row_bytes / 512u;
+    const uint64_t pieces = (uint64_t)rows * pieces_per_row;
+    const int lane = threadIdx.x & 31;
+    const uint64_t warps = (uint64_t)gridDim.x * 8u;
+    for (uint64_t w = (uint64_t)blockIdx.x * 8u + (threadIdx.x >> 5); w < pieces; w += warps) {
+        const uint64_t off = (w / pieces_per_row) * pitch + (w % pieces_per_row) * 512u + (uint64_t)lane * 16u;
+        const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(src + off));
+        for (int d = 0; d < dsts.n; d++) *reinterpret_cast<uint4 *>(dsts.p[d] + off) = v;
+    }
+}
+
 }  // namespace buda
+
+// One launch of the peer-store probe on `stream` (no synchronisation: the caller times a series of launches with its own
+// events, on every rank at once).  src and every dsts[i] are 16-byte aligned device addresses valid in this process;
+// row_bytes is a multiple of 512, pitch_bytes of 16.  Returns 0, or 1 for bad arguments / a launch error.
+extern "C" int buda_probe_peer_stores(const void *src, void *const *dsts, int n_dsts, uint32_t rows, uint32_t row_bytes,
+                                      uint64_t pitch_bytes, void *stream)
+{
+    if (!src || !dsts || n_dsts < 1 || n_dsts > 7 || rows == 0 || row_bytes == 0 || row_bytes % 512u || pitch_bytes % 16u ||
+        pitch_bytes < row_bytes || ((uintptr_t)src & 15u))
+        return 1;
+    buda::PeerDsts d = {};
+    d.n = n_dsts;
+    for (int i = 0; i < n_dsts; i++) {
+        if (!dsts[i] || ((uintptr_t)dsts[i] & 15u)) return 1;
+        d.p[i] = static_cast<uint8_t *>(dsts[i]);
+    }
+    int dev = 0, sm_count = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 1;
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 1;
+    buda::peer_store_probe_kernel<<<(unsigned)(sm_count * 8), 256, 0, (cudaStream_t)stream>>>(static_cast<const uint8_t *>(src), d, rows,
+                                                                                              row_bytes, pitch_bytes);
+    return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
 
 // mix: 0 = 4 bytes read per byte written (tilize + pack, quantise), 1 = 1 byte read per 4 written (unpack + untilize,
 // dequantise), 2 = reads only, 3 = writes only.  schedule: 0 = one short-lived block per band, 1 = resident blocks on

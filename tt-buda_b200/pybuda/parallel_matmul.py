@@ -102,6 +102,12 @@ class ColumnParallelBfp8Matmul:
         return SimpleNamespace(rows=m, tensor=tensor, handle=hdl, local_ptr=tensor.data_ptr(), mc_ptr=int(hdl.multicast_ptr),
                                close=lambda: None)
 
+    @property
+    def block_pointers(self):
+        """Device addresses of this rank's block of columns in every copy of the output (this rank's own first), as the
+        peer-store route uses them; None under the multicast route or before enable_fused_scatter."""
+        return None if self._dst_ptrs is None else list(self._dst_ptrs)
+
     def disable_fused_scatter(self):
         if self._shared is not None:
             torch.cuda.synchronize()
