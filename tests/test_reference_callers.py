@@ -1,7 +1,7 @@
 """The reference's OWN caller code driving this repository's pybuda._C.
 
-Runs where a checkout of the reference is present (the path in REFERENCE_ROOT, default /root/reference) and is skipped
-elsewhere.  The reference's Python package cannot be imported (tensorflow, jax, its unbuilt C++ module), so the
+Runs where a checkout of the reference is present (the path in REFERENCE_ROOT, else a directory `reference` beside this
+repository) and is skipped elsewhere.  The reference's Python package cannot be imported (tensorflow, jax, its unbuilt C++ module), so the
 functions under test are taken out of its source files by name -- pybuda/pybuda/tensor.py:
 pytorch_tensor_to_tensor_desc, tensor_desc_to_pytorch_tensor, pad_pytorch_tensor_to_buda, narrow_buda_tensor_to_pytorch,
 is_equivalent_data_format, the dtype maps; pybuda/pybuda/device_connector.py: DirectPusherDeviceConnector;
@@ -20,7 +20,8 @@ import numpy as np
 import pytest
 import torch
 
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 pytestmark = pytest.mark.skipif(not os.path.isfile(os.path.join(REF, "pybuda/pybuda/tensor.py")),
                                 reason="needs a checkout of the reference")
 
