@@ -337,16 +337,15 @@ __device__ __forceinline__ uint32_t half_bits_to_float_bits(uint32_t h)
 __device__ __forceinline__ uint32_t lf8_encode_float_bits(uint32_t u)
 {
     const uint32_t a = u & 0x7fffffffu;
-    uint32_t c;
-    if (a > 0x7f800000u) {
-        c = 0x7fu;                                   // NaN
-    } else if (a >= (113u << 23)) {                  // 2^-14 and above: a normal result, or past the largest one
-        // exponent field and two mantissa bits, rounded to nearest even; a carry out of the mantissa moves up the exponent
-        const uint32_t r = (a + 0x000fffffu + ((a >> 21) & 1u)) >> 21;
-        c = min(r - (112u << 2), 0x7cu);             // 0x7c = infinity
-    } else {
-        c = (uint32_t)__float2int_rn(__uint_as_float(a) * 65536.0f);   // multiples of 2^-16: 0 .. 4 (4 = the smallest normal)
-    }
+    // 2^-14 and above: exponent field and two mantissa bits, rounded to nearest even; a carry out of the mantissa moves
+    // up the exponent; past the largest finite value the result is 0x7c = infinity
+    const uint32_t r = (a + 0x000fffffu + ((a >> 21) & 1u)) >> 21;
+    const uint32_t normal = min(r - (112u << 2), 0x7cu);
+    // below 2^-14: multiples of 2^-16, 0 .. 4 (4 = the smallest normal)
+    // (one multiply-add into the low bits of 1.5 * 2^23 rounds to nearest even without a conversion instruction)
+    const uint32_t subnormal = __float_as_uint(__fmaf_rn(__uint_as_float(min(a, 113u << 23)), 65536.0f, 12582912.0f)) & 7u;
+    uint32_t c = a >= (113u << 23) ? normal : subnormal;   // both computed, one selected: no divergence inside a warp
+    c = a > 0x7f800000u ? 0x7fu : c;                      // NaN
     return c | ((u >> 24) & 0x80u);
 }
 
@@ -360,12 +359,29 @@ __device__ __forceinline__ uint32_t lf8_encode_half_bits(uint32_t h)
 // exact: every Lf8 value is a binary32 (and a bfloat16: upper half of the result; and a binary16: code << 8)
 __device__ __forceinline__ uint32_t lf8_decode_float_bits(uint32_t c)
 {
-    const uint32_t e = (c >> 2) & 31u, m = c & 3u;
-    uint32_t a;
-    if (e == 0u) a = __float_as_uint((float)m * 1.52587890625e-05f);
-    else if (e == 31u) a = 0x7f800000u | (m << 21);
-    else a = ((e + 112u) << 23) | (m << 21);
+    const uint32_t x = (c & 0x7fu) << 21;                         // exponent and mantissa fields where binary32 has them
+    uint32_t a = x + (112u << 23);                                // normal: re-bias by 127 - 15
+    a += x >= (0x7cu << 21) ? (112u << 23) : 0u;                  // exponent 31: infinity / NaN (the mantissa bits stay on top)
+    // exponent 0: m * 2^-16, m = 0 .. 3
+    const uint32_t sub = __float_as_uint(__fmul_rn(__fadd_rn(__uint_as_float(0x4b000000u | (c & 3u)), -8388608.0f), 1.52587890625e-05f));
+    a = x < (4u << 21) ? sub : a;
     return a | ((c & 0x80u) << 24);
+}
+
+// Two binary32 values -> two Lf8 codes (first value in the low byte) with the hardware's e5m2 conversion, which rounds to
+// nearest even and handles subnormals but saturates to the largest finite value; values that round to infinity under the
+// IEEE rule (magnitude >= 61440, the midpoint above the largest finite value) and infinities themselves are set right
+// afterwards, as are NaNs (0x7f with the sign of the input).
+__device__ __forceinline__ uint32_t lf8_encode_float_bits_x2(uint32_t u0, uint32_t u1)
+{
+    uint16_t d;
+    asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(d) : "f"(__uint_as_float(u1)), "f"(__uint_as_float(u0)));
+    uint32_t c = d;
+    const uint32_t a0 = u0 & 0x7fffffffu, a1 = u1 & 0x7fffffffu;
+    // 0x47700000 = 61440.0f: from there on infinity, and NaN (sign kept) above the infinity pattern
+    if (a0 >= 0x47700000u) c = (c & 0xff00u) | ((u0 >> 24) & 0x80u) | (a0 > 0x7f800000u ? 0x7fu : 0x7cu);
+    if (a1 >= 0x47700000u) c = (c & 0x00ffu) | ((((u1 >> 24) & 0x80u) | (a1 > 0x7f800000u ? 0x7fu : 0x7cu)) << 8);
+    return c;
 }
 
 // binary32 block exponent of widened binary16 data -> the 5-bit exponent byte

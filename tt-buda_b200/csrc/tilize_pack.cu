@@ -493,11 +493,18 @@ __device__ __forceinline__ void direct_encode_store(uint32_t (&x)[4], uint32_t b
 {
     if constexpr (M == kLf8) {
         // element-wise 1-5-2 float: no exponent section, one byte per element; AF marks a binary16 source
-        uint32_t c[4];
+        uint32_t packed;
+        if (ES == 2 && AF) {
+            packed = lf8_encode_half_bits(x[0]) | (lf8_encode_half_bits(x[1]) << 8) | (lf8_encode_half_bits(x[2]) << 16) |
+                     (lf8_encode_half_bits(x[3]) << 24);
+        } else {
+            if (ES == 2) {
 #pragma unroll
-        for (int i = 0; i < 4; i++)
-            c[i] = (ES == 2 && AF) ? lf8_encode_half_bits(x[i]) : lf8_encode_float_bits(ES == 2 ? (x[i] << 16) : x[i]);
-        reinterpret_cast<uint32_t *>(r + blk * 16u)[lane & 3] = c[0] | (c[1] << 8) | (c[2] << 16) | (c[3] << 24);
+                for (int i = 0; i < 4; i++) x[i] <<= 16;   // bfloat16 widens exactly
+            }
+            packed = lf8_encode_float_bits_x2(x[0], x[1]) | (lf8_encode_float_bits_x2(x[2], x[3]) << 16);
+        }
+        reinterpret_cast<uint32_t *>(r + blk * 16u)[lane & 3] = packed;
     } else if (M > 0) {
         constexpr int MM = (M > 0 && M < kLf8) ? M : 7;
         if (ES == 2) {
