@@ -509,6 +509,10 @@ def main():
     extras = {}
     if not args.no_extras:
         def timed(fn, nbytes, reps=10):
+            # each secondary figure is a kernel timed by itself: a short rest first, so that it does not inherit the
+            # power state of the loop before it (the same kernel measured 0.91 and 1.01 of the copy peak without one)
+            torch.cuda.synchronize()
+            time.sleep(0.25)
             for _ in range(3):
                 fn()
             torch.cuda.synchronize()
