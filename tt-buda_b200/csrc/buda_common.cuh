@@ -50,10 +50,16 @@ constexpr int kBoxTiles = 8;
 // work items are started in address order, neighbouring 512-byte row pieces are fetched at about the same time anyway,
 // and for the 8-bit formats half-size items with five CTAs per SM instead of two are 3.4 % faster (7050 vs 6818 GB/s on
 // 32 fp32 tensors); the 4- and 2-bit formats, whose records are smaller, lose 7-14 % that way and keep the full size.
-__host__ __device__ constexpr int unpack_box_tiles_for(int es, bool block_float) { return (block_float && es < 4) ? 2 * kBoxTiles : kBoxTiles; }
+// Plain relayouts: 4-byte elements take half-size items in the pack direction (8 of their 4 KiB records per stage leave
+// room for one CTA per SM only), 1-byte elements take double-size items both ways (a row piece of 8 tiles is 256 bytes).
+__host__ __device__ constexpr int unpack_box_tiles_for(int es, bool block_float)
+{
+    return ((block_float && es < 4) || (!block_float && es == 1)) ? 2 * kBoxTiles : kBoxTiles;
+}
 __host__ __device__ constexpr int pack_box_tiles_for(int es, int mant_bits)
 {
-    return mant_bits == 7 ? unpack_box_tiles_for(es, true) / 2 : unpack_box_tiles_for(es, mant_bits > 0);
+    return mant_bits == 7 ? unpack_box_tiles_for(es, true) / 2
+                          : (mant_bits == 0 && es == 4) ? kBoxTiles / 2 : unpack_box_tiles_for(es, mant_bits > 0);
 }
 __host__ __device__ constexpr int box_tiles_for(int es, bool block_float) { return unpack_box_tiles_for(es, block_float); }
 
