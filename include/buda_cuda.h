@@ -84,7 +84,8 @@ typedef struct buda_tensor_job {
  * exponent 0 / datum 0).  The converter that fixes them is not part of the reference checkout, so each is a switch:
  * when real tile bytes of that converter become available, set the combination that reproduces them.  All zero
  * (face_order {0,1,2,3}) is this library's default and the only layout the matmul kernels read. */
-enum { BUDA_BFP_ROUND_NEAREST_EVEN = 0, BUDA_BFP_ROUND_TRUNCATE = 1 };
+enum { BUDA_BFP_ROUND_NEAREST_EVEN = 0, BUDA_BFP_ROUND_TRUNCATE = 1,
+       BUDA_BFP_ROUND_HALF_THEN_TRUNCATE = 2 /* half an ulp of the kept width added before the truncation: nearest, ties away from zero */ };
 enum { BUDA_BFP_OVERFLOW_SATURATE = 0, BUDA_BFP_OVERFLOW_BUMP_EXPONENT = 1 };
 enum { BUDA_BFP_ORDER_LITTLE = 0, BUDA_BFP_ORDER_BIG = 1 };
 typedef struct buda_bfp_policy {

@@ -87,13 +87,13 @@ int ref_set_threads(int n)
 /* ---------------------------------------------------------------------------------------------
  * POLICY switches: every choice the published description leaves open for the block-float bytes, as one
  * process-wide record (default: all zero, faces in order 0 1 2 3).  "Truncate bits to fit in the BFP format mantissa
- * size, optionally round before truncation" (docs/public/dataformats.rst:80-81) names both roundings; the drawings
+ * size, optionally round before truncation" (docs/public/dataformats.rst:80-81) names truncation and a rounding it does not specify (to nearest even, or half an ulp added before the truncation); the drawings
  * docs/public/images/bfp{8,4,2}_blocks.png show 32-bit rows without saying which end holds the first exponent /
  * datum.  When real tile bytes of the reference's converter are available, the combination that reproduces them
  * is set here and, identically, in the CUDA library.
  * ------------------------------------------------------------------------------------------- */
 typedef struct {
-    uint32_t rounding;       /* 0 nearest even, 1 truncate */
+    uint32_t rounding;       /* 0 nearest even, 1 truncate, 2 add half an ulp then truncate (nearest, ties away from zero) */
     uint32_t overflow;       /* 0 saturate, 1 raise the block exponent by one and re-encode the block */
     uint8_t face_order[4];   /* face stored at position p of the record */
     uint32_t exponent_order; /* 0: exponent of block k in byte k; 1: in byte k ^ 3 (big-endian 32-bit words) */
@@ -111,7 +111,7 @@ int ref_set_bfp_policy(const ref_bfp_policy *p)
         if (p->face_order[i] > 3) return 1;
         seen |= 1 << p->face_order[i];
     }
-    if (seen != 15 || p->rounding > 1 || p->overflow > 1 || p->exponent_order > 1 || p->datum_order > 1) return 1;
+    if (seen != 15 || p->rounding > 2 || p->overflow > 1 || p->exponent_order > 1 || p->datum_order > 1) return 1;
     g_pol = *p;
     return 0;
 }
@@ -264,6 +264,7 @@ static inline uint32_t bfp_encode_datum(uint32_t bits, uint32_t block_exp, int m
             uint32_t rem = sig & ((1u << shift) - 1u);
             uint32_t half = 1u << (shift - 1);
             if (!g_pol.rounding && (rem > half || (rem == half && (kept & 1u)))) kept++;
+            else if (g_pol.rounding == 2 && rem >= half) kept++;   /* add half, then truncate: ties away from zero */
             /* POLICY (overflow): a round-up past the largest magnitude saturates here; under the other policy the
              * caller raises the block exponent and encodes the block again */
             if (kept > qmax) *over = 1;
@@ -338,6 +339,7 @@ static inline uint32_t bfp_a_encode_datum(uint16_t h, uint32_t block_exp, int m,
         } else {
             uint32_t kept = sig >> shift, rem = sig & ((1u << shift) - 1u), half = 1u << (shift - 1);
             if (!g_pol.rounding && (rem > half || (rem == half && (kept & 1u)))) kept++;
+            else if (g_pol.rounding == 2 && rem >= half) kept++;   /* add half, then truncate: ties away from zero */
             if (kept > qmax) *over = 1;
             q = kept > qmax ? qmax : kept;
         }

@@ -8,7 +8,8 @@ ties to even; a round-up past the largest magnitude saturates; zero / denormal i
 encode the largest magnitude; a zero magnitude is stored with sign 0; datum i occupies bits [i*(m+1), (i+1)*(m+1))
 of the block's little-endian bit string; decode (-1)^s * q * 2^(E-127-(m-1)), q = 0 -> +0.0.
 
-The choices that change bytes are also available the other way round (Policy): truncation instead of rounding, a
+The choices that change bytes are also available the other way round (Policy): truncation, or "add half, then truncate"
+(nearest, ties away from zero), instead of rounding to nearest even; a
 shared exponent raised by one instead of saturation, another face order, and exponents / datums counted from the top
 end of each 32-bit word.  The default Policy() is the frozen spec above.
 """
@@ -21,7 +22,7 @@ SPEC_VERSION = 1
 
 class Policy:
     def __init__(self, rounding=0, overflow=0, face_order=(0, 1, 2, 3), exponent_order=0, datum_order=0):
-        self.rounding = rounding              # 0 nearest even, 1 truncate
+        self.rounding = rounding              # 0 nearest even, 1 truncate, 2 nearest with ties away from zero (add half, then truncate)
         self.overflow = overflow              # 0 saturate, 1 raise the shared exponent by one
         self.face_order = tuple(face_order)   # face stored first, second, third, fourth
         self.exponent_order = exponent_order  # 0: exponent of block k in byte k, 1: in byte k ^ 3
@@ -52,6 +53,8 @@ def _quantise(bits16, exps, E, m, policy):
             fl = math.floor(v)
             rem = v - fl
             if policy.rounding == 0 and (rem > Fraction(1, 2) or (rem == Fraction(1, 2) and fl % 2 == 1)):
+                fl += 1
+            elif policy.rounding == 2 and rem >= Fraction(1, 2):
                 fl += 1
             qs.append(fl)
     return qs

@@ -98,6 +98,8 @@ POLICIES = [
     Policy(face_order=(0, 2, 1, 3)),
     Policy(rounding=1, overflow=1, face_order=(3, 1, 2, 0), exponent_order=1, datum_order=1),
     Policy(rounding=0, overflow=1, face_order=(1, 0, 3, 2), exponent_order=1, datum_order=1),
+    Policy(rounding=2),
+    Policy(rounding=2, overflow=1, face_order=(2, 3, 0, 1), datum_order=1),
 ]
 
 

@@ -478,6 +478,15 @@ def test_policy_switches_one_by_one(oracle):
         R.set_bfp_policy(R.BfpPolicy(rounding=1))
         E, d = R.bfp_pack_block(blk, 7)
         assert (E, d[0], d[1]) == (127, 64, 65)
+        # "add half, then truncate": a tie goes away from zero whatever the kept bit: 1.0078125 = 64.5/64 -> 65 (nearest even: 64),
+        # 1.0234375 = 65.5/64 -> 66 either way, and anything below the tie still goes down
+        blk[2], blk[3] = f(1.0078125), f(-1.00390625)
+        R.set_bfp_policy(None)
+        E, d = R.bfp_pack_block(blk, 7)
+        assert (E, d[0], d[1], d[2], d[3]) == (127, 64, 66, 64, 0x80 | 64)
+        R.set_bfp_policy(R.BfpPolicy(rounding=2))
+        E, d = R.bfp_pack_block(blk, 7)
+        assert (E, d[0], d[1], d[2], d[3]) == (127, 64, 66, 65, 0x80 | 64)
         # overflow: 1.99609375 rounds up to 128 > 127: saturate keeps E, bump raises E and halves every magnitude
         blk[:] = 0
         blk[0], blk[1] = f(1.99609375), f(-1.0)

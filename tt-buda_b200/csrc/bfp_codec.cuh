@@ -33,9 +33,10 @@ struct BfpTraits {
 };
 
 // Integer encoder of one value (used for blocks at the ends of the exponent range, and by the general
-// kernel flavour after a shared exponent was raised).  trunc: drop the low bits instead of rounding to
+// kernel flavour after a shared exponent was raised).  rmode: 0 round the dropped bits to nearest even, 1 drop them,
+// 2 add half an ulp of the kept width and then drop them (nearest, ties away from zero) -- instead of rounding to
 // nearest even.  *over is set when the magnitude of a finite value came out above the largest one.
-__device__ __forceinline__ uint32_t bfp_encode_datum_int(uint32_t bits, uint32_t E, int m, bool trunc = false, bool *over = nullptr)
+__device__ __forceinline__ uint32_t bfp_encode_datum_int(uint32_t bits, uint32_t E, int m, int rmode = 0, bool *over = nullptr)
 {
     const uint32_t qmax = (1u << m) - 1u;
     uint32_t e = (bits >> 23) & 0xffu, q;
@@ -50,7 +51,7 @@ __device__ __forceinline__ uint32_t bfp_encode_datum_int(uint32_t bits, uint32_t
             q = 0;
         } else {
             uint32_t kept = sig >> shift, rem = sig & ((1u << shift) - 1u), half = 1u << (shift - 1u);
-            kept += (!trunc && (rem > half || (rem == half && (kept & 1u)))) ? 1u : 0u;
+            kept += ((rmode == 0 && (rem > half || (rem == half && (kept & 1u)))) || (rmode == 2 && rem >= half)) ? 1u : 0u;
             if (over && kept > qmax) *over = true;
             q = kept < qmax ? kept : qmax;
         }
@@ -95,13 +96,21 @@ __device__ __forceinline__ uint32_t bfp_block_exponent(const uint32_t (&x)[16])
     return __float_as_uint(mf) >> 23;
 }
 
-// |x| * S + 1.5 * 2^23 in one fused multiply-add: rounded to nearest even, or toward zero (= truncation of the
-// magnitude, every operand being non-negative).  The magnitude sits in the low bits of the result, unsaturated.
-template <bool RZ>
+// |x| * S + 1.5 * 2^23 in one fused multiply-add: rounded to nearest even (R = 0), or toward zero (R = 1: truncation of
+// the magnitude, every operand being non-negative).  The magnitude sits in the low bits of the result, unsaturated.
+// R = 2, half an ulp added before the truncation: the constant is 1.5 * 2^22 + 0.5, where the unit in the last place is
+// one half, so the truncated sum counts floor(2 v + 1) halves and q = floor(v + 0.5) is that count shifted right by
+// one; it is handed back on top of 1.5 * 2^23 like the other two.
+template <int R>
 __device__ __forceinline__ uint32_t bfp_quantise_bits(uint32_t xbits, float S)
 {
     float r;
-    if (RZ)
+    if (R == 2) {
+        asm("{\n\t.reg .f32 t;\n\tabs.ftz.f32 t, %1;\n\tfma.rz.ftz.f32 %0, t, %2, %3;\n\t}"
+            : "=f"(r) : "f"(__uint_as_float(xbits)), "f"(S), "f"(6291456.5f));
+        return kMagicBits + ((__float_as_uint(r) - 0x4ac00000u) >> 1);
+    }
+    if (R == 1)
         asm("{\n\t.reg .f32 t;\n\tabs.ftz.f32 t, %1;\n\tfma.rz.ftz.f32 %0, t, %2, %3;\n\t}"
             : "=f"(r) : "f"(__uint_as_float(xbits)), "f"(S), "f"(12582912.0f));
     else
@@ -156,23 +165,23 @@ __device__ __forceinline__ void bfp_pack_datums(const uint32_t (&x)[16], const u
 
 // One block through the integer encoder.  Returns true when a finite magnitude rounded up past the largest one.
 template <int M>
-__device__ __forceinline__ bool bfp_encode16_int(const uint32_t (&x)[16], uint32_t E, bool trunc, uint32_t (&out)[BfpTraits<M>::words])
+__device__ __forceinline__ bool bfp_encode16_int(const uint32_t (&x)[16], uint32_t E, int rmode, uint32_t (&out)[BfpTraits<M>::words])
 {
     bool over = false;
 #pragma unroll
     for (int w = 0; w < BfpTraits<M>::words; w++) out[w] = 0;
 #pragma unroll
     for (int i = 0; i < 16; i++) {
-        uint32_t d = bfp_encode_datum_int(x[i], E, M, trunc, &over);
+        uint32_t d = bfp_encode_datum_int(x[i], E, M, rmode, &over);
         out[(i * (M + 1)) / 32] |= d << ((i * (M + 1)) % 32);
     }
     return over;
 }
 
 // Encode one block.  x: the 16 values as binary32 bit patterns.  Returns the shared exponent and
-// the packed datums (out[0] holds datums 0.., little-endian).  RZ: truncate instead of rounding to nearest even (the
-// same instruction count: only the rounding mode of the multiply-add differs).
-template <int M, bool RZ = false>
+// the packed datums (out[0] holds datums 0.., little-endian).  R: rounding (0 nearest even; 1 truncate, the same
+// instruction count: only the rounding mode of the multiply-add differs; 2 half added before the truncation).
+template <int M, int R = 0>
 __device__ __forceinline__ void bfp_encode16(const uint32_t (&x)[16], uint32_t &E_out,
                                              uint32_t (&out)[BfpTraits<M>::words])
 {
@@ -184,10 +193,10 @@ __device__ __forceinline__ void bfp_encode16(const uint32_t (&x)[16], uint32_t &
         const float S = __uint_as_float((uint32_t)(M + 253 - (int)E) << 23);  // 2^(M-1+127-E)
         uint32_t y[16];
 #pragma unroll
-        for (int i = 0; i < 16; i++) y[i] = min(bfp_quantise_bits<RZ>(x[i], S), kMagicBits + qmax);  // Inf / NaN and round-ups saturate here
+        for (int i = 0; i < 16; i++) y[i] = min(bfp_quantise_bits<R>(x[i], S), kMagicBits + qmax);  // Inf / NaN and round-ups saturate here
         bfp_pack_datums<M>(x, y, out);
     } else {
-        (void)bfp_encode16_int<M>(x, E, RZ, out);
+        (void)bfp_encode16_int<M>(x, E, R, out);
     }
 }
 
@@ -197,9 +206,9 @@ __device__ __forceinline__ void bfp_encode16(const uint32_t (&x)[16], uint32_t &
 // (Inlined on purpose: a call that takes the block by reference would pin the 16 values to local memory for the whole
 // kernel, and every access of the hot path would go through it -- measured at 0.65 of the plain kernel's speed.)
 template <int M>
-__device__ __forceinline__ void bfp_encode16_raised(const uint32_t (&x)[16], uint32_t E, bool trunc, uint32_t (&out)[BfpTraits<M>::words])
+__device__ __forceinline__ void bfp_encode16_raised(const uint32_t (&x)[16], uint32_t E, int rmode, uint32_t (&out)[BfpTraits<M>::words])
 {
-    (void)bfp_encode16_int<M>(x, E, trunc, out);
+    (void)bfp_encode16_int<M>(x, E, rmode, out);
 }
 
 // raise_limit: the shared exponent may be raised while it is below this (255; 143 = 31 + 112 for the widened
@@ -214,12 +223,15 @@ __device__ __forceinline__ void bfp_encode16_policy(const uint32_t (&x)[16], uin
     if (E + 1u >= (uint32_t)M && E <= (uint32_t)(M + 252)) {
         const float S = __uint_as_float((uint32_t)(M + 253 - (int)E) << 23);
         uint32_t y[16];
-        if (pol.trunc) {
+        if (pol.rmode == 1) {
 #pragma unroll
-            for (int i = 0; i < 16; i++) y[i] = bfp_quantise_bits<true>(x[i], S);
+            for (int i = 0; i < 16; i++) y[i] = bfp_quantise_bits<1>(x[i], S);
+        } else if (pol.rmode == 2) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) y[i] = bfp_quantise_bits<2>(x[i], S);
         } else {
 #pragma unroll
-            for (int i = 0; i < 16; i++) y[i] = bfp_quantise_bits<false>(x[i], S);
+            for (int i = 0; i < 16; i++) y[i] = bfp_quantise_bits<0>(x[i], S);
         }
         uint32_t top = 0;
 #pragma unroll
@@ -230,11 +242,11 @@ __device__ __forceinline__ void bfp_encode16_policy(const uint32_t (&x)[16], uin
         over = top > kMagicBits + qmax;     // below the limit every value of the block is finite
         bfp_pack_datums<M>(x, y, out);
     } else {
-        over = bfp_encode16_int<M>(x, E, pol.trunc != 0, out);
+        over = bfp_encode16_int<M>(x, E, pol.rmode, out);
     }
     if (pol.bump && over && E < raise_limit) {
         E += 1u;
-        bfp_encode16_raised<M>(x, E, pol.trunc != 0, out);
+        bfp_encode16_raised<M>(x, E, pol.rmode, out);
     }
     E_out = E;
     if (pol.datum_be) {

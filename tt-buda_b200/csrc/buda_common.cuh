@@ -68,7 +68,7 @@ __host__ __device__ constexpr int box_tiles_for(int es, bool block_float) { retu
 // the drawings docs/public/images/bfp{8,4,2}_blocks.png do not say which end of a 32-bit word holds datum 0).
 // All zero = the layout this library writes by default.  Only the general kernel flavour reads it.
 struct BfpPolicy {
-    uint8_t trunc;        // rounding of the dropped mantissa bits: 0 nearest even, 1 truncate
+    uint8_t rmode;        // rounding of the dropped mantissa bits: 0 nearest even, 1 truncate, 2 half an ulp added before the truncation
     uint8_t bump;         // a round-up past the largest magnitude: 0 saturates, 1 raises the shared exponent by one
     uint8_t exp_be;       // exponent section: 0 block k in byte k, 1 big-endian inside each 32-bit word (byte k ^ 3)
     uint8_t datum_be;     // mantissa section: 0 datum i in bits [i(m+1), (i+1)(m+1)) of the block, 1 the fields of each 32-bit word reversed
@@ -82,7 +82,7 @@ __host__ __device__ inline BfpPolicy default_policy()
 }
 __host__ __device__ inline bool policy_is_default(const BfpPolicy &p)
 {
-    return !p.trunc && !p.bump && !p.exp_be && !p.datum_be && p.face_pos[0] == 0 && p.face_pos[1] == 1 && p.face_pos[2] == 2 &&
+    return !p.rmode && !p.bump && !p.exp_be && !p.datum_be && p.face_pos[0] == 0 && p.face_pos[1] == 1 && p.face_pos[2] == 2 &&
            p.face_pos[3] == 3;
 }
 

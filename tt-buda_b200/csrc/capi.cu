@@ -1103,7 +1103,7 @@ int buda_set_bfp_policy(const buda_bfp_policy *policy)
 {
     buda_bfp_policy pub = {0, 0, {0, 1, 2, 3}, 0, 0};
     if (policy) pub = *policy;
-    if (pub.rounding > 1 || pub.overflow > 1 || pub.exponent_order > 1 || pub.datum_order > 1)
+    if (pub.rounding > 2 || pub.overflow > 1 || pub.exponent_order > 1 || pub.datum_order > 1)
         return fail(BUDA_RUNTIME_ERROR, "unknown block-float policy value");
     BfpPolicy p = default_policy();
     bool seen[4] = {false, false, false, false};
@@ -1114,7 +1114,7 @@ int buda_set_bfp_policy(const buda_bfp_policy *policy)
         p.face_at[pos] = (uint8_t)f;
         p.face_pos[f] = (uint8_t)pos;
     }
-    p.trunc = (uint8_t)pub.rounding;
+    p.rmode = (uint8_t)pub.rounding;
     p.bump = (uint8_t)pub.overflow;
     p.exp_be = (uint8_t)pub.exponent_order;
     p.datum_be = (uint8_t)pub.datum_order;
@@ -1293,7 +1293,7 @@ static int gemm_scatter_impl(const void *A, int64_t M, int64_t K, int64_t lda, c
     {
         const BfpPolicy pol = current_policy();
         BfpPolicy layout = pol;
-        layout.trunc = layout.bump = 0;   // rounding and overflow do not change how bytes are read back
+        layout.rmode = layout.bump = 0;   // rounding and overflow do not change how bytes are read back
         if (!policy_is_default(layout))
             return fail(BUDA_RUNTIME_ERROR, "the matmul reads weight images in the default byte layout; the current block-float policy changes it");
     }

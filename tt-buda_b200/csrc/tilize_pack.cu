@@ -255,7 +255,8 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
     // general flavour (all uniform over the launch): only a raised exponent needs the policy encoder; truncation is the
     // plain encoder with another rounding mode, a reversed datum order one permute per word afterwards
     const bool plain_codec = !P || !job.pol.bump;
-    const bool trunc = P && job.pol.trunc, datum_be = P && job.pol.datum_be;
+    const int rmode = P ? (int)job.pol.rmode : 0;
+    const bool datum_be = P && job.pol.datum_be;
     uint32_t it = 0;
     for (;; ++it) {
         const int s = it % S;
@@ -292,7 +293,7 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
                     const uint4 v0 = *reinterpret_cast<const uint4 *>(p), v1 = *reinterpret_cast<const uint4 *>(p + 16);
                     const uint32_t h[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
                     // packed-pair encoder; false at the ends of the exponent range
-                    if (!AF && plain_codec && !trunc) encoded = bfp_encode16_bf16<MM>(h, E, d);
+                    if (!AF && plain_codec && rmode == 0) encoded = bfp_encode16_bf16<MM>(h, E, d);
                     if (!encoded) {
 #pragma unroll
                         for (int k = 0; k < 8; k++) {
@@ -308,8 +309,9 @@ pack_staged_kernel(const __grid_constant__ TileJob job, const __grid_constant__ 
                 }
                 if (!encoded) {
                     if (!plain_codec) bfp_encode16_policy<MM>(x, E, d, job.pol, AF ? 143u : 255u);
-                    else if (trunc) bfp_encode16<MM, true>(x, E, d);
-                    else bfp_encode16<MM, false>(x, E, d);
+                    else if (rmode == 1) bfp_encode16<MM, 1>(x, E, d);
+                    else if (rmode == 2) bfp_encode16<MM, 2>(x, E, d);
+                    else bfp_encode16<MM, 0>(x, E, d);
                 }
                 if (plain_codec && datum_be) {
 #pragma unroll
@@ -375,19 +377,19 @@ __device__ __forceinline__ uint32_t absmax4_bits(const uint32_t (&x)[4])
 // The exponents next to 0 and 255, where the scale of the fast path is not a normal float: integer arithmetic,
 // kept out of line because almost no block takes it.
 __device__ __noinline__ uint32_t encode4_any_exp(uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3, uint32_t E, int m,
-                                                 bool trunc = false, bool *over = nullptr)
+                                                 int rmode = 0, bool *over = nullptr)
 {
-    return bfp_encode_datum_int(x0, E, m, trunc, over) | (bfp_encode_datum_int(x1, E, m, trunc, over) << (m + 1)) |
-           (bfp_encode_datum_int(x2, E, m, trunc, over) << (2 * (m + 1))) | (bfp_encode_datum_int(x3, E, m, trunc, over) << (3 * (m + 1)));
+    return bfp_encode_datum_int(x0, E, m, rmode, over) | (bfp_encode_datum_int(x1, E, m, rmode, over) << (m + 1)) |
+           (bfp_encode_datum_int(x2, E, m, rmode, over) << (2 * (m + 1))) | (bfp_encode_datum_int(x3, E, m, rmode, over) << (3 * (m + 1)));
 }
 
 // Four data of one block, shared exponent E already known, packed at (M + 1) bits each.  In the usual exponent
 // range the magnitudes come out of one fused multiply-add each (round to nearest even into the low bits of
 // 1.5 * 2^23) and everything after it works on the four data at once, one byte each: saturation is per element,
 // then the sign bits are gathered with byte permutes and dropped where the magnitude is zero.
-// trunc / over: general flavour only (truncation instead of rounding; *over reports a finite magnitude above the largest).
+// rmode / over: general flavour only (another rounding of the dropped bits; *over reports a finite magnitude above the largest).
 template <int M>
-__device__ __forceinline__ uint32_t encode4_shared_exp(const uint32_t (&x)[4], uint32_t E, bool trunc = false, bool *over = nullptr)
+__device__ __forceinline__ uint32_t encode4_shared_exp(const uint32_t (&x)[4], uint32_t E, int rmode = 0, bool *over = nullptr)
 {
     constexpr uint32_t qmax = BfpTraits<M>::qmax;
     const bool fast = (E + 1u >= (uint32_t)M) && (E <= (uint32_t)(M + 252));
@@ -396,7 +398,7 @@ __device__ __forceinline__ uint32_t encode4_shared_exp(const uint32_t (&x)[4], u
         uint32_t r[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            const uint32_t y = trunc ? bfp_quantise_bits<true>(x[i], S) : bfp_quantise_bits<false>(x[i], S);
+            const uint32_t y = rmode == 1 ? bfp_quantise_bits<1>(x[i], S) : rmode == 2 ? bfp_quantise_bits<2>(x[i], S) : bfp_quantise_bits<0>(x[i], S);
             if (over && y > kMagicBits + qmax) *over = true;
             r[i] = min(y, kMagicBits + qmax);   // low byte = magnitude (the constant's low byte is 0)
         }
@@ -413,7 +415,7 @@ __device__ __forceinline__ uint32_t encode4_shared_exp(const uint32_t (&x)[4], u
         const uint32_t t = D | (D >> 6);
         return (t | (t >> 12)) & 0xffu;
     }
-    return encode4_any_exp(x[0], x[1], x[2], x[3], E, M, trunc, over);
+    return encode4_any_exp(x[0], x[1], x[2], x[3], E, M, rmode, over);
 }
 
 template <int ES>
@@ -518,14 +520,14 @@ __device__ __forceinline__ void direct_encode_store(uint32_t (&x)[4], uint32_t b
         uint32_t packed;
         if constexpr (G) {
             bool over = false;
-            packed = encode4_shared_exp<MM>(x, E, pol.trunc != 0, &over);
+            packed = encode4_shared_exp<MM>(x, E, (int)pol.rmode, &over);
             // the block spans four lanes: any of them rounding up raises the exponent for all
             uint32_t ov = over ? 1u : 0u;
             ov |= __shfl_xor_sync(0xffffffffu, ov, 1, 4);
             ov |= __shfl_xor_sync(0xffffffffu, ov, 2, 4);
             if (pol.bump && ov && E < (AF ? 143u : 255u)) {
                 E += 1u;
-                packed = encode4_any_exp(x[0], x[1], x[2], x[3], E, MM, pol.trunc != 0);
+                packed = encode4_any_exp(x[0], x[1], x[2], x[3], E, MM, (int)pol.rmode);
             }
         } else {
             packed = encode4_shared_exp<MM>(x, E);
