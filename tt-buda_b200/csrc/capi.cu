@@ -280,7 +280,9 @@ int fill_entry(const TileJob &j, const void *rm, void *q, uint32_t band_first, u
 int launch_uniform(int direction, DevCtx *ctx, TileJob &job, const PtrTable &pt, int nb, int mant, int es, int a_format, int path,
                    int vec_ok, cudaStream_t stream)
 {
-    const BfpPolicy pol = current_policy();
+    BfpPolicy pol = current_policy();
+    if (direction == 1) pol.rmode = pol.bump = 0;   // a reader does not care how the writer rounded: keeps the plain flavour where only those differ
+    if (mant == 0 || mant == kLf8) pol.rmode = pol.bump = pol.exp_be = pol.datum_be = 0;   // formats without a shared exponent: only the face order applies
     cudaError_t e;
     if (policy_is_default(pol)) {
         e = direction == 0 ? launch_tilize(job, pt, nb, mant, es, a_format, path, vec_ok, ctx->sm_count, stream, ctx->status)
@@ -688,7 +690,9 @@ int jobs_device(int direction, int n, const buda_tensor_job *jobs, int rm_df, in
     int mant, es;
     if (int rc = classify(rm_df, q_df, mant, es, direction == 1)) return rc;
     const int a_format = half_side(rm_df, q_df);
-    const BfpPolicy pol = current_policy();
+    BfpPolicy pol = current_policy();
+    if (direction == 1) pol.rmode = pol.bump = 0;   // a reader does not care how the writer rounded: keeps the plain flavour where only those differ
+    if (mant == 0 || mant == kLf8) pol.rmode = pol.bump = pol.exp_be = pol.datum_be = 0;   // formats without a shared exponent: only the face order applies
     GenTable *tab = new GenTable;
     tab->n = 0;
     tab->pad = 0;
