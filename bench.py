@@ -247,6 +247,28 @@ def profile_one(torch, cuda_ops, dev, name, reps=20, nt=8):
         else:
             fn = lambda: cuda_ops.unpack_untilize_batch(imgs, cuda_ops.DF.Bfp8_b, SHAPE, outs=xs)
         work, unit = nt * ELEMS * 3.0625 / 1e9, "GB/s"
+    elif name in ("tilize_fp32", "untilize_fp32", "tilize_int8", "untilize_int8"):
+        # plain relayout (no format change): 2 x element size per element
+        if name.endswith("int8"):
+            xs = [torch.randint(-128, 128, SHAPE, device=dev, dtype=torch.int8) for _ in range(nt)]
+            df, es = cuda_ops.DF.Int8, 1
+        else:
+            xs = [torch.randn(SHAPE, device=dev) for _ in range(nt)]
+            df, es = cuda_ops.DF.Float32, 4
+        imgs = cuda_ops.tilize_pack_batch(xs, df)
+        if name.startswith("tilize"):
+            fn = lambda: cuda_ops.tilize_pack_batch(xs, df, outs=imgs)
+        else:
+            fn = lambda: cuda_ops.unpack_untilize_batch(imgs, df, SHAPE, outs=xs)
+        work, unit = nt * ELEMS * 2 * es / 1e9, "GB/s"
+    elif name in ("pack_lf8", "unpack_lf8"):
+        xs = [torch.randn(SHAPE, device=dev) for _ in range(nt)]
+        imgs = cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Lf8)
+        if name == "pack_lf8":
+            fn = lambda: cuda_ops.tilize_pack_batch(xs, cuda_ops.DF.Lf8, outs=imgs)
+        else:
+            fn = lambda: cuda_ops.unpack_untilize_batch(imgs, cuda_ops.DF.Lf8, SHAPE, outs=xs)
+        work, unit = nt * ELEMS * 5 / 1e9, "GB/s"
     elif name in ("pack_jobs", "unpack_jobs"):
         # the general kernel flavour (job table) on a uniform batch
         xs = [torch.randn(SHAPE, device=dev) for _ in range(nt)]
@@ -342,7 +364,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (for profiler captures)")
     ap.add_argument("--tensors", type=int, default=N_TENSORS,
                     help="tensors per GPU batch; anything but 64 is a reduced case for profiler captures")
-    ap.add_argument("--profile-kernel", default=None, choices=["bare_streams", "gemm", "i8gemm", "pack_jobs", "unpack_jobs", "pack", "unpack", "pack_direct", "unpack_direct", "pack_bf16", "unpack_bf16", "quantize", "dequantize", "requantize"],
+    ap.add_argument("--profile-kernel", default=None, choices=["bare_streams", "gemm", "i8gemm", "tilize_fp32", "untilize_fp32", "tilize_int8", "untilize_int8", "pack_lf8", "unpack_lf8", "pack_jobs", "unpack_jobs", "pack", "unpack", "pack_direct", "unpack_direct", "pack_bf16", "unpack_bf16", "quantize", "dequantize", "requantize"],
                     help="run only this secondary kernel a few times and exit (small, self-ending case for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
