@@ -442,9 +442,16 @@ unpack_direct_kernel(const __grid_constant__ TileJob job, const __grid_constant_
                     const uint32_t d = packed >> (i * (MM + 1));
                     const uint32_t qb = kMagicBits | (d & BfpTraits<MM>::qmax);
                     const uint32_t signbit = (d << (31 - MM)) & 0x80000000u;
-                    float mag = __fmul_rn(__fadd_rn(__uint_as_float(qb), -12582912.0f), sc);
-                    if (MM == 1 && !AF) mag = __fmul_rn(mag, post);
-                    const float val = __fadd_rn(__uint_as_float(__float_as_uint(mag) | signbit), 0.0f);
+                    float val;
+                    if (MM == 1 && !AF) {
+                        // the scale may need a second factor (2^128 is not a binary32): multiply twice, then sign and +0
+                        float mag = __fmul_rn(__fmul_rn(__fadd_rn(__uint_as_float(qb), -12582912.0f), sc), post);
+                        val = __fadd_rn(__uint_as_float(__float_as_uint(mag) | signbit), 0.0f);
+                    } else {
+                        // q * (+-scale) + (+0): the sign rides on the scale, and the +0 addend turns a zero magnitude with its
+                        // sign bit set into +0.0; one multiply-add where a multiply, an OR and an add stood
+                        val = __fmaf_rn(__fadd_rn(__uint_as_float(qb), -12582912.0f), __uint_as_float(__float_as_uint(sc) ^ signbit), 0.0f);
+                    }
                     x[i] = __float_as_uint(val);
                     if (ES == 2) x[i] = AF ? (pack_half2(val, 0.0f) & 0xffffu) : (x[i] >> 16);
                 }
