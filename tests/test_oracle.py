@@ -619,3 +619,27 @@ def test_lf8_oracle_agrees_with_an_independent_e5m2_conversion(oracle):
     assert np.array_equal(codesh[~nanh], th8.view(torch.uint8).numpy()[~nanh])
     backh = oracle.unpack_untilize(imgh, oracle.Lf8, x.shape, np.float16)
     assert np.array_equal(backh.view(np.uint16), (codesh.astype(np.uint16) << 8))
+
+
+def test_policy_finder_recovers_the_policy_an_image_was_written_under(oracle):
+    """oracle/find_bfp_policy.py: the search a maintainer runs when real tile bytes of the reference's converter appear."""
+    from oracle import find_bfp_policy as F
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((1, 1, 64, 64)).astype(np.float32)
+    x.reshape(-1)[::37] *= 1e3                     # outliers: blocks with small values next to a large one
+    x[0, 0, 0, :16] = 1.99609375                   # a block that rounds up past the largest magnitude (overflow rule shows)
+    x[0, 0, 1, :16] = np.float32(1.0078125)        # ties (the three roundings differ)
+    want = (2, 1, (2, 0, 3, 1), 1, 0)
+    try:
+        oracle.set_bfp_policy(oracle.BfpPolicy(*want))
+        image = oracle.tilize_pack(x, oracle.Bfp8_b)
+    finally:
+        oracle.set_bfp_policy(None)
+    ranked = F.rank_policies(x, image, oracle.Bfp8_b)
+    exact = [p for n, p in ranked if n == 0]
+    assert exact == [want]
+    # the default image is found as the default policy, and the switches the data cannot show come back as alternatives
+    flat = np.full((1, 1, 32, 32), 1.0, np.float32)
+    ranked = F.rank_policies(flat, oracle.tilize_pack(flat, oracle.Bfp8_b), oracle.Bfp8_b)
+    exact = [p for n, p in ranked if n == 0]
+    assert (0, 0, (0, 1, 2, 3), 0, 0) in exact and len(exact) > 1
