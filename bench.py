@@ -818,6 +818,12 @@ def main():
             flops_rank = 2.0 * M * (N / world) * K
             link_bytes = M * (N / world) * 2 * (world - 1)
             t_floor = max(flops_rank / (tensor_peak_tflops() * 1e12), link_bytes / 770e9)
+            # What a launch of whole-K tiles can reach with stores that run at the bare rate: nothing can be sent before the
+            # first round of tiles is done, and the last round's stores have no compute beside them.
+            tiles_rank = ((M + 511) // 512) * ((N // world) // 256)
+            pairs_max = max(1, torch.cuda.get_device_properties(dev).multi_processor_count // 2)
+            rounds = max(1, -(-tiles_rank // pairs_max))
+            pipe_bound = max(ms_local / rounds + ms_bare, ms_local + ms_bare / rounds) if ms_bare else None
             extras["column_parallel_gemm_8192x4096x16384"] = {
                 "TFLOP/s_without_gather": round(2.0 * M * N * K / (ms_local * 1e-3) / 1e12, 1), "ms_without_gather": round(ms_local, 4),
                 "TFLOP/s_with_all_gather": round(2.0 * M * N * K / (ms_gather * 1e-3) / 1e12, 1), "ms_with_all_gather": round(ms_gather, 4),
@@ -829,6 +835,9 @@ def main():
                 "bare_peer_stores_ms": round(ms_bare, 4) if ms_bare else None,
                 "bare_peer_stores_gbs_per_gpu": round(link_bytes / (ms_bare * 1e-3) / 1e9, 1) if ms_bare else None,
                 "fused_scatter_vs_matmul_plus_bare_stores": round(ms_fused / (ms_local + ms_bare), 3) if ms_bare else None,
+                "fused_peer_store_route_bound_ms": round(pipe_bound, 4) if pipe_bound else None,
+                "fused_peer_store_route_frac_of_bound": round(pipe_bound / ms_peer, 3) if pipe_bound else None,
+                "bound": "max(first round of tiles + bare stores, matmul + last round's bare stores); rounds = %d" % rounds,
                 "fused_scatter_floor_ms": round(t_floor * 1e3, 4), "fused_scatter_frac_of_floor": round(t_floor * 1e3 / ms_fused, 3),
                 "floor": "max(flops / measured bf16 burst peak, bytes leaving this GPU / 770 GB/s measured peer copy)",
                 "bands": 8}
