@@ -76,3 +76,31 @@ def test_plain_relayout_with_both_sides_above_4_gib(big, oracle):
     assert torch.equal(img, img_direct)
     rc, st = ops._cabi.device_status()
     assert rc == 0 and st == 0
+
+
+def test_host_buffer_pipeline_with_a_tensor_above_4_gib(big, oracle):
+    """The sliced host pipeline (buda_tilize_pack_host / buda_unpack_untilize_host) forms host-side offsets above 2^32 too."""
+    import ctypes
+
+    ops, x = big
+    cabi = ops._cabi
+    shape = list(x.shape)
+    xh = x.cpu()                                   # pageable host memory: the entry point stages it itself
+    gq = ops.QueueGeom.for_shape(shape)
+    n = cabi.tilized_bytes(gq, shape, int(ops.DF.Bfp8_b))
+    img = torch.empty(n, dtype=torch.uint8)
+    st = cabi.u64x4(cabi.dense_strides(shape, 4))
+    cabi.check(cabi.lib.buda_tilize_pack_host(xh.data_ptr(), int(ops.DF.Float32), cabi.u32x4(shape), st, ctypes.byref(gq),
+                                              int(ops.DF.Bfp8_b), 0, img.data_ptr(), n, None))
+    want = ops.tilize_pack(x, ops.DF.Bfp8_b).cpu()
+    assert torch.equal(img, want)
+    del want
+    y = torch.empty(shape, dtype=torch.float32)
+    cabi.check(cabi.lib.buda_unpack_untilize_host(img.data_ptr(), int(ops.DF.Bfp8_b), 0, ctypes.byref(gq), y.data_ptr(),
+                                                  int(ops.DF.Float32), cabi.u32x4(shape), st, None))
+    rows = 64
+    tail_bytes = (rows // 32) * (C_COLS // 32) * 1088
+    ref = oracle.unpack_untilize(img[-tail_bytes:].numpy(), oracle.Bfp8_b, (1, 1, rows, C_COLS))
+    assert np.array_equal(y[:, :, R_ROWS - rows:, :].contiguous().numpy().view(np.uint32), ref.view(np.uint32))
+    rc, st_ = cabi.device_status()
+    assert rc == 0 and st_ == 0
