@@ -104,3 +104,32 @@ def test_host_buffer_pipeline_with_a_tensor_above_4_gib(big, oracle):
     assert np.array_equal(y[:, :, R_ROWS - rows:, :].contiguous().numpy().view(np.uint32), ref.view(np.uint32))
     rc, st_ = cabi.device_status()
     assert rc == 0 and st_ == 0
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 32, 262144), (1, 1, 131072, 32), (256, 4, 32, 32), (3, 5, 96, 4128)])
+@pytest.mark.parametrize("df_name", ["Bfp8_b", "Bfp2_b", "Float16_b"])
+def test_extreme_aspect_ratios_against_the_oracle(oracle, shape, df_name):
+    """One tile row of 8192 tiles, 4096 tile rows of one tile, a thousand single-tile slices, a ragged width: whole images
+    against the oracle on both kernel paths, and back."""
+    if not torch.cuda.is_available():
+        pytest.fail("these tests need a CUDA device; there is no CPU fallback to test")
+    from pybuda import cuda_ops as ops
+
+    g = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(shape, generator=g) * torch.exp(torch.empty(shape).uniform_(-3.0, 3.0, generator=g))
+    if df_name == "Float16_b":
+        x = x.bfloat16()
+        xn = x.view(torch.int16).numpy().view(np.uint16)
+        want = oracle.tilize_pack(xn, oracle.Float16_b, src_df=oracle.Float16_b)
+    else:
+        want = oracle.tilize_pack(x.numpy(), getattr(oracle, df_name))
+    df = getattr(ops.DF, df_name)
+    for path in (0, 1):
+        img = ops.tilize_pack(x.cuda(), df, path=path)
+        assert np.array_equal(img.cpu().numpy(), want), path
+        y = ops.unpack_untilize(img, df, shape, dtype=x.dtype, path=path).cpu()
+        if df_name == "Float16_b":
+            assert torch.equal(y.view(torch.int16), x.view(torch.int16)), path
+        else:
+            ref = oracle.unpack_untilize(want, getattr(oracle, df_name), shape)
+            assert np.array_equal(y.numpy().view(np.uint32), ref.view(np.uint32)), path
