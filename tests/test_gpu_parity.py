@@ -617,3 +617,46 @@ def test_stream_probe_library_runs_and_rejects_bad_arguments(ops):
     assert lib.buda_probe_stream(5, 0, 131072, 1, ctypes.byref(ms), None) == 1
     assert lib.buda_probe_stream(0, 0, 131072, 0, ctypes.byref(ms), None) == 1
     assert ops._cabi.device_status() == (0, 0)
+
+
+# ------------------------------------------------------------------------------------------------
+# quantise ops with the scales and inputs nobody plans for: zero, negative, infinite, NaN and denormal scales; NaN,
+# infinities and huge values in the data.  The golden chain is torch arithmetic (division / multiplication, round half
+# to even, clamp, cast); whatever IEEE arithmetic makes of these is the answer.
+# ------------------------------------------------------------------------------------------------
+def test_quant_ops_with_special_scales_and_inputs(ops, oracle):
+    inf, nan = float("inf"), float("nan")
+    g = torch.Generator().manual_seed(91)
+    x = torch.randn(64, 32, generator=g) * 50
+    x[0, :8] = torch.tensor([nan, inf, -inf, 1e38, -1e38, 0.0, -0.0, 1e-45])
+    x[1, :4] = torch.tensor([0.5, 1.5, 2.5, -0.5])                      # ties
+    per_tensor = [0.0, -0.0, -0.25, inf, -inf, nan, 1e-45, 1e-39, 3e38, 1.0]
+    for sv in per_tensor:
+        s = torch.tensor([sv])
+        for zp in (0, 3, -128):
+            got = ops.quantize(x.cuda(), s.cuda(), zp).cpu().numpy()
+            assert np.array_equal(got, oracle.quantize(x.numpy(), s.numpy(), zp)), (sv, zp)
+            # and the torch expression itself (the golden evaluation), where its result is defined
+            with np.errstate(all="ignore"):
+                t = torch.clamp(torch.round(x / s) + zp, -128, 127)
+            ok = ~torch.isnan(t)
+            assert np.array_equal(got[ok.numpy()], t[ok].to(torch.int8).numpy()), (sv, zp)
+        q = torch.randint(-128, 128, (64, 32), generator=g, dtype=torch.int8)
+        got = ops.dequantize(q.cuda(), s.cuda(), 3).cpu().numpy()
+        want = oracle.dequantize(q.numpy(), s.numpy(), 3)
+        # 0 * inf and anything * NaN are NaN on both sides; which NaN (sign, payload) is not part of the golden chain
+        assert np.array_equal(np.isnan(got), np.isnan(want)), sv
+        assert np.array_equal(got.view(np.uint32)[~np.isnan(want)], want.view(np.uint32)[~np.isnan(want)]), sv
+        acc = torch.randint(-2 ** 31, 2 ** 31 - 1, (64, 32), generator=g, dtype=torch.int32)
+        acc[0, :4] = torch.tensor([2 ** 31 - 1, -2 ** 31, 0, 1])
+        assert np.array_equal(ops.buda_requantize(acc.cuda(), s.cuda(), 0).cpu().numpy(), oracle.buda_requantize(acc.numpy(), s.numpy(), 0)), sv
+    # the same values as per-axis scales, mixed in one vector
+    s = torch.tensor(per_tensor + [0.05] * 22)
+    assert np.array_equal(ops.quantize(x.cuda(), s.cuda(), 1, axis=-1).cpu().numpy(), oracle.quantize(x.numpy(), s.numpy(), 1, axis=-1))
+    acc = torch.randint(-2 ** 20, 2 ** 20, (64, 32), generator=g, dtype=torch.int32)
+    so = torch.rand(32, generator=g) + 0.5
+    so[3], so[5] = 0.0, inf
+    assert np.array_equal(ops.requantize(acc.cuda(), s.cuda(), so.cuda(), 2, axis=-1).cpu().numpy(),
+                          oracle.requantize(acc.numpy(), s.numpy(), so.numpy(), 2, axis=-1))
+    rc, st = ops._cabi.device_status()
+    assert rc == 0 and st == 0
