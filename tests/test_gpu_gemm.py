@@ -285,3 +285,39 @@ def test_i8_matmul_refuses_bad_arguments(ops):
     img = torch.zeros(4 * 8 * 1024, dtype=torch.uint8, device="cuda")
     with pytest.raises(ops._cabi.BudaError, match="scale"):
         ops.i8_matmul(a, img, 256, scale=torch.ones(7), out="int8")
+
+
+def test_weight_blocks_at_the_ends_of_the_exponent_range(ops, oracle, kernel):
+    """Blocks whose shared exponent is below 7 hold values under 2^-126 and enter the product as zero; every other finite
+    block -- down to exponent 7 and up to 253 -- enters exactly.  One-hot activations make the product a copy of weight rows."""
+    K, N, M = 64, 256, 256
+    w = torch.zeros(1, 1, K, N)
+    g = torch.Generator().manual_seed(5)
+    base = torch.randint(1, 128, (K, N), generator=g).float() * torch.where(torch.rand(K, N, generator=g) < 0.5, -1.0, 1.0)
+    # rows of K use different magnitudes: 2^-135 (exponent field 3 after the block maximum), 2^-125, 1, 2^100, 2^119
+    scales = {0: 2.0 ** -140, 1: 2.0 ** -128, 2: 2.0 ** -126, 3: 1.0, 4: 2.0 ** 100, 5: 2.0 ** 119}
+    for k in range(K):
+        w[0, 0, k] = base[k] * scales[k % 6]
+    img = ops.tilize_pack(w.cuda(), ops.DF.Bfp8_b)
+    ref_img = oracle.tilize_pack(w.numpy(), oracle.Bfp8_b)
+    assert np.array_equal(img.cpu().numpy(), ref_img)
+    wd = torch.from_numpy(oracle.unpack_untilize(ref_img, oracle.Bfp8_b, (1, 1, K, N)))[0, 0]
+    exps = torch.from_numpy(ref_img.reshape(-1, 1088)[:, :64].astype(np.int32))          # [tile, block]
+    a = torch.zeros(M, K)
+    ks = torch.arange(M) % K
+    a[torch.arange(M), ks] = 1.0
+    c = ops.bfp8b_matmul(a.bfloat16().cuda(), img, N).cpu().float()
+    # expected: decoded weights, with the blocks of exponent < 7 taken as zero
+    want = wd.clone()
+    for kt in range(K // 32):
+        for nt in range(N // 32):
+            e = exps[kt * (N // 32) + nt]
+            for blk in range(64):
+                if int(e[blk]) < 7:
+                    face, fr = divmod(blk, 16)
+                    r0, c0 = kt * 32 + (face >> 1) * 16 + fr, nt * 32 + (face & 1) * 16
+                    want[r0, c0:c0 + 16] = 0.0
+    assert (exps < 7).any() and (exps >= 7).any()
+    assert torch.equal(c, want[ks].bfloat16().float())
+    rc, st = ops._cabi.device_status()
+    assert rc == 0 and st == 0
