@@ -27,7 +27,10 @@
 //                 CTAs' barriers (multicast commit).  peer: relays "my activations landed" to the leader
 //   warps 0-7     epilogue for this CTA's 2 x 128 rows (two warps per tensor-memory lane quadrant, half
 //                 of the columns each); both CTAs' epilogues release the accumulators on the leader's
-//                 acc_empty barrier.  In a launch that also feeds peer devices the same warps then forward
+//                 acc_empty barrier.  A one-device launch writes each 32-row x 64-column piece (bfloat16, or
+//                 requantised int8) into one of the warp's two staging buffers in shared memory and hands it to the
+//                 copy engine as one bulk tensor store; 4-byte outputs and launches that feed peers store from
+//                 registers.  In a launch that also feeds peer devices the same warps then forward
 //                 the piece they wrote to the peers' copies while the next tile's MMAs run: one plain store per
 //                 peer, or ONE multimem store to the multicast address of the matrix, which the NVSwitch
 //                 replicates to every device of the group
@@ -61,7 +64,8 @@ constexpr int kTmemCols = 512;
 constexpr int kEpiStageBytes = 2 * 32 * 128;   // per epilogue warp: two buffers of what it hands to one bulk tensor store
 
 
-// Shared-memory plan (the same for a launch that also writes peers' memory, kScatter).
+// Shared-memory plan (the same for a launch that also writes peers' memory, kScatter): 3 x 32 KB of activations,
+// 4 x 16 KB of weight operand, 8 x 8 KB of epilogue staging, barriers.
 template <bool kScatter>
 struct Layout {
     static constexpr int kAStages = 3;                  // activation ring (per CTA: two 128-row boxes per stage); the fourth
