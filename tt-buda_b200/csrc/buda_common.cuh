@@ -349,6 +349,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 
 // try_wait that lets the hardware park the thread for up to `hint_ns` (it wakes as soon as the phase
 // completes), so a long wait costs no issue slots that working warps could use
+// non-blocking probe of a barrier phase (try_wait may suspend the thread for a while; this never does)
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 __device__ __forceinline__ bool mbar_try_wait_parked(uint64_t *bar, uint32_t parity, uint32_t hint_ns)
 {
     uint32_t ok;

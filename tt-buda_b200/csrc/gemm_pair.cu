@@ -252,9 +252,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
                 for (uint32_t kb = 0; kb < p.k_blocks; kb++, i++) {
                     const int s = i % kAStages, t = i % kBStages;
-                    if (!mbar_wait_bounded(&full_a[s], (i / kAStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT) ||
-                        !mbar_wait_bounded_cluster(&peer_a[s], (i / kAStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT) ||
-                        !mbar_wait_bounded_cluster(&full_b[t], (i / kBStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT)) {
+                    // The three barriers of this k-block are probed back to back, so the probes' latencies overlap, and
+                    // only a barrier that is not complete yet is waited for.  This thread is the pair's only source of
+                    // MMAs: with one probe after the other it spent a fifth of its time in their round trips even when
+                    // everything was ready (0.810 -> 0.767 ms on 8192 x 4096 x 16384).
+                    const bool r0 = mbar_test_wait(&full_a[s], (i / kAStages) & 1u);
+                    const bool r1 = mbar_test_wait(&peer_a[s], (i / kAStages) & 1u);
+                    const bool r2 = mbar_test_wait(&full_b[t], (i / kBStages) & 1u);
+                    if (!(r0 && r1 && r2) &&
+                        (!mbar_wait_bounded(&full_a[s], (i / kAStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT) ||
+                         !mbar_wait_bounded_cluster(&peer_a[s], (i / kAStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT) ||
+                         !mbar_wait_bounded_cluster(&full_b[t], (i / kBStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT))) {
                         ok = false;
                         break;
                     }
