@@ -19,12 +19,13 @@
 //
 // Pair tile: 512 rows x 256 columns (two M = 256 accumulators, all 512 tensor-memory columns of both
 // SMs); k-block = 128 bytes of K (64 bfloat16 / 128 int8).  In each CTA (rank r = 0 leader, 1 peer):
-//   warp 8        producer: TMA-loads this CTA's two 128-row activation boxes per k-block
+//   warp 8        producer: TMA-loads this CTA's two 128-row activation boxes per k-block; the loads of both CTAs
+//                 are counted on ONE barrier in the leader (the load's .cta_group::2 form; each CTA fetches its own boxes)
 //   warps 10..17  weights: this CTA's 128 columns of the k-block, global -> registers -> N-major swizzled
 //                 operand stage (Bfp8: decoded to bfloat16; Int8: the 16-byte face rows are copied as they are),
 //                 then arrive on the LEADER's full_b barrier
 //   warp 9        leader: one thread issues the MMAs for the pair and commits completion to both
-//                 CTAs' barriers (multicast commit).  peer: relays "my activations landed" to the leader
+//                 CTAs' barriers (multicast commit).  peer: idle
 //   warps 0-7     epilogue for this CTA's 2 x 128 rows (two warps per tensor-memory lane quadrant, half
 //                 of the columns each); both CTAs' epilogues release the accumulators on the leader's
 //                 acc_empty barrier.  A one-device launch writes each 32-row x 64-column piece (bfloat16, or
@@ -74,7 +75,7 @@ struct Layout {
     static constexpr int kSmemB = kSmemA + kAStages * kABytes;
     static constexpr int kSmemEpi = kSmemB + kBStages * kBBytes;      // per epilogue warp: two pieces of 32 rows x 64 bfloat16 columns, 128-byte swizzle
     static constexpr int kSmemBar = kSmemEpi + kEpiWarps * kEpiStageBytes;
-    static constexpr int kNumBars = 3 * kAStages + 2 * kBStages + 2;
+    static constexpr int kNumBars = 2 * kAStages + 2 * kBStages + 2;
     static constexpr int kSmemBytes = kSmemBar + kNumBars * 8 + 16 + 1024;
 };
 
@@ -106,6 +107,17 @@ struct KindTraits<kKindI8> {
     // weight operand stage, N-major: one 128-column atom per 8-deep k group, groups 1024 B apart
     static constexpr uint32_t kBLbo = 1024, kBSbo = 1024;
 };
+
+// TMA tile load whose completion is counted on a barrier of the pair's leader CTA (given as a shared::cluster address):
+// both CTAs' activation boxes land on ONE barrier, so the issuing thread waits for one thing and nobody relays.
+__device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorMap *tmap, int x, int y, uint32_t leader_bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(leader_bar)
+        : "memory");
+}
 
 template <int Kind>
 __device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
@@ -160,9 +172,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint8_t *sA = smem + kSmemA;
     uint8_t *sB = smem + kSmemB;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kSmemBar);
-    uint64_t *full_a = bars;                    // [kAStages] this CTA's activations landed (TMA bytes)
-    uint64_t *peer_a = full_a + kAStages;       // [kAStages] leader only: the peer's activations landed
-    uint64_t *empty_a = peer_a + kAStages;      // [kAStages] MMAs reading the activations are done (both CTAs)
+    uint64_t *full_a = bars;                    // [kAStages] leader only: both CTAs' activations landed (TMA bytes of both)
+    uint64_t *empty_a = full_a + kAStages;      // [kAStages] MMAs reading the activations are done (both CTAs)
     uint64_t *full_b = empty_a + kAStages;      // [kBStages] leader only: both CTAs' decoded weights written
     uint64_t *empty_b = full_b + kBStages;      // [kBStages] MMAs reading the decoded weights are done (both CTAs)
     uint64_t *acc_full = empty_b + kBStages;    // accumulators complete (both CTAs)
@@ -178,7 +189,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (tid == 0) {
         for (int s = 0; s < kAStages; s++) {
             mbar_init(&full_a[s], 1);
-            mbar_init(&peer_a[s], 1);
             mbar_init(&empty_a[s], 1);
         }
         for (int t = 0; t < kBStages; t++) {
@@ -217,21 +227,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         ok = false;
                         break;
                     }
-                    mbar_arrive_expect_tx(&full_a[s], kABytes);
-                    tma_load_2d(sA + s * kABytes, &tmap_a, (int)(kb * kBK), row0, &full_a[s]);
-                    tma_load_2d(sA + s * kABytes + kABytes / 2, &tmap_a, (int)(kb * kBK), row0 + 256, &full_a[s]);
+                    const uint32_t leader_bar = map_to_cta(smem_u32(&full_a[s]), 0);
+                    if (rank == 0) mbar_arrive_expect_tx(&full_a[s], 2 * kABytes);   // this CTA's boxes and the partner's
+                    tma_load_2d_pair(sA + s * kABytes, &tmap_a, (int)(kb * kBK), row0, leader_bar);
+                    tma_load_2d_pair(sA + s * kABytes + kABytes / 2, &tmap_a, (int)(kb * kBK), row0 + 256, leader_bar);
                 }
             }
             const uint32_t back = i < (uint32_t)kAStages ? i : (uint32_t)kAStages;
-            if (!ok || *abort_flag) {
-                // let the copies already issued land before shared memory is released
+            if ((!ok || *abort_flag) && rank == 0) {
+                // let the copies already issued land before shared memory is released (the partner's are counted on this
+                // CTA's barriers too, and the partner stays until the closing cluster barrier)
                 for (uint32_t k = 1; k <= back; k++) {
                     const uint32_t j = i - k;
                     uint64_t t0 = global_timer_ns();
                     while (!mbar_try_wait(&full_a[j % kAStages], (j / kAStages) & 1u) && global_timer_ns() - t0 < 100000000ull) {
                     }
                 }
-            } else {
+            } else if (ok && !*abort_flag) {
                 // the leader's last commits arrive on this CTA's barriers asynchronously: see them land before leaving
                 for (uint32_t k = 1; k <= back; k++) {
                     const uint32_t j = i - k;
@@ -252,16 +264,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
                 for (uint32_t kb = 0; kb < p.k_blocks; kb++, i++) {
                     const int s = i % kAStages, t = i % kBStages;
-                    // The three barriers of this k-block are probed back to back, so the probes' latencies overlap, and
+                    // The two barriers of this k-block are probed back to back, so the probes' latencies overlap, and
                     // only a barrier that is not complete yet is waited for.  This thread is the pair's only source of
-                    // MMAs: with one probe after the other it spent a fifth of its time in their round trips even when
-                    // everything was ready (0.810 -> 0.767 ms on 8192 x 4096 x 16384).
+                    // MMAs: with one probe after the other (then three: the partner's activations had a barrier
+                    // of their own) it spent a fifth of its time in their round trips even when everything was ready
+                    // (0.810 -> 0.767 ms on 8192 x 4096 x 16384).
                     const bool r0 = mbar_test_wait(&full_a[s], (i / kAStages) & 1u);
-                    const bool r1 = mbar_test_wait(&peer_a[s], (i / kAStages) & 1u);
                     const bool r2 = mbar_test_wait(&full_b[t], (i / kBStages) & 1u);
-                    if (!(r0 && r1 && r2) &&
-                        (!mbar_wait_bounded(&full_a[s], (i / kAStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT) ||
-                         !mbar_wait_bounded_cluster(&peer_a[s], (i / kAStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT) ||
+                    if (!(r0 && r2) &&
+                        (!mbar_wait_bounded_cluster(&full_a[s], (i / kAStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT) ||
                          !mbar_wait_bounded_cluster(&full_b[t], (i / kBStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT))) {
                         ok = false;
                         break;
@@ -283,20 +294,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     umma_commit_pair(&empty_b[t]);
                 }
                 if (ok) umma_commit_pair(acc_full);
-            }
-        } else if (lane == 0) {
-            // -------------------------------------------------------------- relay (peer): activations landed
-            uint32_t i = 0;
-            bool ok = true;
-            for (uint32_t tile = pair; tile < total_tiles && ok; tile += num_pairs) {
-                for (uint32_t kb = 0; kb < p.k_blocks; kb++, i++) {
-                    const int s = i % kAStages;
-                    if (!mbar_wait_bounded(&full_a[s], (i / kAStages) & 1u, abort_flag, p.status, BUDA_DEVSTAT_GEMM_WAIT)) {
-                        ok = false;
-                        break;
-                    }
-                    mbar_arrive_cluster(map_to_cta(smem_u32(&peer_a[s]), 0));
-                }
             }
         }
         __syncwarp();
